@@ -1,0 +1,86 @@
+// C ABI of librtp_b200.so. Every function takes raw device pointers and a CUDA stream, returns 0 on
+// success or a negative error code, and never synchronises the device. Python binds these with ctypes.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RTP_MAX_WORLD 8
+
+// ------------------------------------------------------------------------------------------- GEMM
+// D[M,N] = epilogue( A * B^T (+ C) ),  bf16 operands, fp32 accumulation on tcgen05 tensor cores.
+typedef struct {
+  const void* a; long long lda; int a_mn;  // a_mn = 0: A is [M,K] row-major. 1: A is stored [K,M] row-major.
+  const void* b; long long ldb; int b_mn;  // b_mn = 0: B is [N,K] row-major. 1: B is stored [K,N] row-major.
+  int M, N, K;
+  void* d; long long ldd; int d_fp32;
+  const void* c; long long ldc; int c_fp32;   // optional accumulate source
+  const void* bias;                           // optional bf16 [N]
+  int act;                                    // 0 none, 1 relu, 2 gelu
+  const void* mask; long long ldmask; float mask_scale;  // optional: out = mask > 0 ? out * scale : 0
+  float drop_p; unsigned long long seed, offset;          // dropout on the output when drop_p > 0
+  unsigned long long* status;                 // device status word (0 = ok)
+  int num_ctas;                               // 0 = one CTA per SM
+  int bn;                                     // 0 = auto, else 128 or 256
+} RtpGemmArgs;
+int rtp_gemm(const RtpGemmArgs* args, void* stream);
+
+// ---------------------------------------------------------------------------- rotated linear layers
+// Workspace of one rank (peer-mapped): [flag block][W slot 0][W slot 1][G slot 0][G slot 1].
+typedef struct {
+  int rank, world;
+  void* ws[RTP_MAX_WORLD];         // workspace base of every rank, as mapped in this process
+  unsigned long long slot_bytes;   // capacity of each of the four slots
+  int ctas;                        // CTAs per rank (same value on every rank)
+  unsigned long long timeout_ns;
+} RtpRing;
+
+typedef struct {
+  int mode;                 // 0: column (shard [out/N, in], outputs concatenated); 1: row (shard [out, in/N], summed)
+  int M;                    // rows (tokens) of this rank's batch
+  int in_features, out_features;  // of the full layer
+  const void* home;         // this rank's flat shard: weight, then (optionally) bias at bias_off
+  long long bias_off;       // element offset of the bias inside the flat shard, -1: no bias
+  unsigned long long shard_bytes;  // bytes of the flat shard that travel (multiple of 16)
+  const void* x; long long ldx;    // [M, in]
+  void* y; long long ldy;          // [M, out]
+  int act;                         // activation applied to y (column mode only)
+  float drop_p; unsigned long long seed, offset;  // dropout applied to y after the activation
+} RtpLinearFwd;
+int rtp_linear_fwd(const RtpRing* ring, const RtpLinearFwd* op, void* stream);
+
+typedef struct {
+  int mode, M, in_features, out_features;
+  const void* home; long long bias_off; unsigned long long shard_bytes;
+  const void* x; long long ldx;    // saved input [M, in]
+  const void* dy; long long ldy;   // [M, out]
+  void* dx; long long lddx;        // [M, in], may be null (first layer)
+  void* grad_home;                 // flat gradient of the home shard (same layout as home), bf16
+  const float* dbias_full;         // fp32 column sums of dy: [out] (may be null when there is no bias)
+  const void* mask; long long ldmask; float mask_scale;  // optional mask applied to dx (activation/dropout backward)
+} RtpLinearBwd;
+int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream);
+
+// Single-GPU emulation of `world` ranks in one cooperative launch (for tests with fewer GPUs than ranks).
+int rtp_linear_fwd_emu(const RtpRing* rings, const RtpLinearFwd* ops, int world, void* stream);
+int rtp_linear_bwd_emu(const RtpRing* rings, const RtpLinearBwd* ops, int world, void* stream);
+
+// ------------------------------------------------------------------------------------- workspace
+unsigned long long rtp_ws_bytes(unsigned long long slot_bytes);
+int rtp_ws_create(unsigned long long slot_bytes, void** out);   // cudaMalloc + zero flag block
+int rtp_ws_destroy(void* ws);
+int rtp_ws_reset(void* ws, void* stream);                        // zero the flag block
+int rtp_ws_ipc_get(void* ws, void* handle64);                    // 64-byte cudaIpcMemHandle
+int rtp_ws_ipc_open(const void* handle64, void** out);
+int rtp_ws_ipc_close(void* mapped);
+int rtp_ws_status(void* ws, unsigned long long* host_out, void* stream);  // reads the status word (synchronises stream)
+void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i);
+void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i);
+int rtp_sm_count(void);
+const char* rtp_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif

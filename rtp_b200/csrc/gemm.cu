@@ -1,0 +1,464 @@
+// Host side of the rotation GEMM kernel: tensor-map encoding, program builders for the plain GEMM and
+// for the rotated (column/row) linear layers in forward and backward, and the launchers.
+//
+// Rotation schedule (forward): rank r uses shard (r+i)%N at step i, the same visiting order as the
+// reference's ColumnParallelLinear.forward (rtp/module/linear.py:204-236).  Because NVSwitch gives
+// every pair of GPUs the same bandwidth, a shard is not forwarded hop by hop: its owner pushes it from
+// its (read-only) home buffer straight into the slot of the rank that needs it next, so no rank ever
+// waits for a neighbour to finish forwarding.  Backward visits shards in the order r-1, r-2, ..., r
+// (rtp/module/collectives.py:281-317), weights again pushed by their owners, while the gradient of
+// each shard travels rank to rank and picks up one contribution per hop until it reaches its owner.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cooperative_groups.h>
+#include <mutex>
+#include <string>
+#include <cstring>
+#include <cstdio>
+#include "api.h"
+#include "gemm_kernel.cuh"
+
+namespace {
+
+thread_local std::string g_err;
+int fail(const std::string& s) { g_err = s; return -1; }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [outer, inner] view with row pitch `ld` elements.
+// box = [box_outer rows, 64 elements], 128-byte swizzle, zero fill outside the tensor.
+int make_map(CUtensorMap* m, const void* ptr, long long inner, long long outer, long long ld, int box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail("cuTensorMapEncodeTiled entry point not found");
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return fail("TMA operand base is not 16-byte aligned");
+  if ((ld * 2) % 16 != 0) return fail("TMA operand row pitch is not a multiple of 16 bytes");
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return 0;
+}
+// operand stored [rows, k] row-major (K-major)
+int make_map_k(CUtensorMap* m, const void* ptr, long long rows, long long k, long long ld) {
+  return make_map(m, ptr, k, rows, ld, 128);
+}
+// operand stored [k, mn] row-major (MN-major)
+int make_map_mn(CUtensorMap* m, const void* ptr, long long mn, long long k, long long ld) {
+  return make_map(m, ptr, mn, k, ld, 64);
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+void init_phase(RtpPhase& ph) {
+  memset(&ph, 0, sizeof(ph));
+  ph.wait_ctr[0] = ph.wait_ctr[1] = -1;
+  ph.done_ctr[0] = ph.done_ctr[1] = -1;
+  ph.credit_ctr = -1;
+  ph.bn = 128;
+}
+void init_program(RtpProgram& p) {
+  memset(&p, 0, sizeof(p));
+  p.timeout_ns = 2000000000ull;
+}
+
+bool aligned16(const void* p, long long ld_elems, int elem_bytes) {
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && ((ld_elems * elem_bytes) & 15) == 0;
+}
+void set_vec_ok(RtpPhase& ph) {
+  bool ok = aligned16(ph.d, ph.ldd, ph.d_fp32 ? 4 : 2);
+  if (ph.c) ok = ok && aligned16(ph.c, ph.ldc, ph.c_fp32 ? 4 : 2);
+  if (ph.mask) ok = ok && aligned16(ph.mask, ph.ldmask, 2);
+  ph.vec_ok = ok ? 1 : 0;
+}
+int pick_bn(int M, int N, int ctas) {
+  long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+  return (t256 >= ctas) ? 256 : 128;
+}
+uint32_t drop_threshold(float p) {
+  if (p <= 0.f) return 0;
+  double t = (double)p * 4294967296.0;
+  if (t > 4294967295.0) t = 4294967295.0;
+  return (uint32_t)t;
+}
+
+template <int NEMU>
+int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(rtp::rtp_gemm_kernel<NEMU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         rtp::kSmemBytes);
+    if (e != cudaSuccess) return fail(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(rtp::kNumThreads);
+  cfg.dynamicSmemBytes = rtp::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  int nat = 0;
+  if (cooperative) {
+    at[0].id = cudaLaunchAttributeCooperative;
+    at[0].val.cooperative = 1;
+    nat = 1;
+  }
+  cfg.attrs = at;
+  cfg.numAttrs = nat;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rtp::rtp_gemm_kernel<NEMU>, params);
+  if (e != cudaSuccess) return fail(std::string("launch rtp_gemm_kernel: ") + cudaGetErrorString(e));
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// workspace layout
+// ------------------------------------------------------------------------------------------------
+constexpr unsigned long long kFlagBytes = 4096;
+static_assert(sizeof(RtpFlagBlock) <= kFlagBytes, "flag block too large");
+RtpFlagBlock* ws_flags(void* ws) { return reinterpret_cast<RtpFlagBlock*>(ws); }
+uint8_t* ws_wslot(void* ws, unsigned long long slot_bytes, int i) {
+  return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)i * slot_bytes;
+}
+uint8_t* ws_gslot(void* ws, unsigned long long slot_bytes, int i) {
+  return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)(2 + i) * slot_bytes;
+}
+int mod(int a, int n) { return ((a % n) + n) % n; }
+
+// ------------------------------------------------------------------------------------------------
+// program builders
+// ------------------------------------------------------------------------------------------------
+int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
+  init_program(P);
+  const int N = R.world, r = R.rank;
+  if (N < 1 || N > RTP_MAX_WORLD) return fail("world size out of range");
+  if (N > RTP_MAX_PHASES) return fail("too many phases");
+  const bool col = op.mode == 0;
+  if (col ? (op.out_features % N) : (op.in_features % N)) return fail("features not divisible by world size");
+  const int Os = col ? op.out_features / N : op.out_features;  // rows of a weight shard
+  const int Ks = col ? op.in_features : op.in_features / N;    // columns of a weight shard
+  if (N > 1 && op.shard_bytes > R.slot_bytes) return fail("shard larger than workspace slot");
+  if (op.shard_bytes % 16) return fail("shard_bytes must be a multiple of 16");
+  void* ws = R.ws[r];
+  P.flags = ws ? ws_flags(ws) : nullptr;
+  P.status = ws ? &ws_flags(ws)->status.v : nullptr;
+  P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
+
+  // maps: 0 = x, 1 = home, 2 = W slot 0, 3 = W slot 1
+  if (make_map_k(&P.maps[0], op.x, op.M, op.in_features, op.ldx)) return -1;
+  if (make_map_k(&P.maps[1], op.home, Os, Ks, Ks)) return -1;
+  if (N > 1) {
+    if (make_map_k(&P.maps[2], ws_wslot(ws, R.slot_bytes, 0), Os, Ks, Ks)) return -1;
+    if (make_map_k(&P.maps[3], ws_wslot(ws, R.slot_bytes, 1), Os, Ks, Ks)) return -1;
+  }
+  const int bn = pick_bn(op.M, col ? Os : op.out_features, R.ctas);
+  P.n_phases = N;
+  for (int i = 0; i < N; ++i) {
+    RtpPhase& ph = P.phases[i];
+    init_phase(ph);
+    const int j = mod(r + i, N);
+    const int slot = (i - 1) & 1;
+    const uint8_t* src = (i == 0) ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, slot);
+    ph.a_map = 0;
+    ph.b_map = (i == 0) ? 1 : 2 + slot;
+    ph.M = op.M;
+    ph.N = Os;
+    ph.K = Ks;
+    ph.bn = bn;
+    ph.ldd = op.ldy;
+    ph.d = reinterpret_cast<__nv_bfloat16*>(op.y) + (col ? (long long)j * Os : 0);
+    if (!col) {
+      ph.a_off_k = j * Ks;
+      if (i > 0) { ph.c = op.y; ph.ldc = op.ldy; }
+    }
+    if (op.bias_off >= 0) ph.bias = reinterpret_cast<const __nv_bfloat16*>(src) + op.bias_off;
+    // activation / dropout act on the finished output: every step in column mode, the last one in row mode
+    if (col || i == N - 1) {
+      ph.act = op.act;
+      ph.drop_thresh = drop_threshold(op.drop_p);
+      ph.drop_scale = op.drop_p > 0.f ? 1.f / (1.f - op.drop_p) : 1.f;
+      ph.drop_seed = op.seed;
+      ph.drop_offset = op.offset + (unsigned long long)(col ? j : 0);
+    }
+    if (i > 0) {
+      ph.wait_ctr[0] = RTP_CTR_W0 + slot;
+      ph.wait_rel[0] = (i - 1) / 2;
+      ph.done_ctr[0] = RTP_CTR_W0 + slot;
+    }
+    set_vec_ok(ph);
+  }
+  P.n_pushes = N - 1;
+  for (int i = 0; i + 1 < N; ++i) {
+    RtpPush& pu = P.pushes[i];
+    memset(&pu, 0, sizeof(pu));
+    const int t = mod(r - (i + 1), N);
+    const int slot = i & 1;
+    pu.src = op.home;
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
+    pu.bytes = op.shard_bytes;
+    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
+    pu.credit_ctr = RTP_CTR_W0 + slot;
+    pu.credit_rel = i / 2;
+    pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
+  }
+  P.uses_inc[RTP_CTR_W0] = N / 2;        // ceil((N-1)/2)
+  P.uses_inc[RTP_CTR_W1] = (N - 1) / 2;  // floor((N-1)/2)
+  return 0;
+}
+
+int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
+  init_program(P);
+  const int N = R.world, r = R.rank;
+  if (N < 1 || N > RTP_MAX_WORLD || 2 * N > RTP_MAX_PHASES) return fail("world size out of range");
+  const bool col = op.mode == 0;
+  if (col ? (op.out_features % N) : (op.in_features % N)) return fail("features not divisible by world size");
+  const int Os = col ? op.out_features / N : op.out_features;
+  const int Ks = col ? op.in_features : op.in_features / N;
+  if (N > 1 && op.shard_bytes > R.slot_bytes) return fail("shard larger than workspace slot");
+  void* ws = R.ws[r];
+  P.flags = ws ? ws_flags(ws) : nullptr;
+  P.status = ws ? &ws_flags(ws)->status.v : nullptr;
+  P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
+  const int up = mod(r + 1, N);
+
+  // maps: 0 = dy (MN-major view: k = tokens), 1 = x (MN-major view), 2 = dy (K-major view: k = out),
+  //       3 = home W (MN-major view: k = shard rows), 4/5 = W slots 0/1
+  if (make_map_mn(&P.maps[0], op.dy, op.out_features, op.M, op.ldy)) return -1;
+  if (make_map_mn(&P.maps[1], op.x, op.in_features, op.M, op.ldx)) return -1;
+  if (op.dx) {
+    if (make_map_k(&P.maps[2], op.dy, op.M, op.out_features, op.ldy)) return -1;
+    if (make_map_mn(&P.maps[3], op.home, Ks, Os, Ks)) return -1;
+    if (N > 1) {
+      if (make_map_mn(&P.maps[4], ws_wslot(ws, R.slot_bytes, 0), Ks, Os, Ks)) return -1;
+      if (make_map_mn(&P.maps[5], ws_wslot(ws, R.slot_bytes, 1), Ks, Os, Ks)) return -1;
+    }
+  }
+  int np = 0;
+  for (int s = 0; s < N; ++s) {
+    const int j = mod(r - 1 - s, N);
+    const int wslot = s & 1;        // weights used at step s sit in W slot s%2 (home at the last step)
+    const int gin = (s - 1) & 1;    // incoming gradient partial sits in G slot (s-1)%2
+    const int gout = s & 1;         // outgoing partial goes to the next rank's G slot s%2
+    const bool last = s == N - 1;
+    // ---- wgrad: dW_j = dy_j^T x  (+ incoming partial) -> next rank's slot, or home at the last step
+    {
+      RtpPhase& ph = P.phases[np++];
+      init_phase(ph);
+      ph.a_map = 0; ph.a_mn = 1;
+      ph.b_map = 1; ph.b_mn = 1;
+      ph.M = Os; ph.N = Ks; ph.K = op.M;
+      if (col) ph.a_off_mn = j * Os; else ph.b_off_mn = j * Ks;
+      ph.bn = pick_bn(ph.M, ph.N, R.ctas);
+      uint8_t* dst = last ? reinterpret_cast<uint8_t*>(op.grad_home) : ws_gslot(R.ws[up], R.slot_bytes, gout);
+      ph.d = dst; ph.ldd = Ks;
+      const uint8_t* cin = nullptr;
+      if (s > 0) {
+        cin = ws_gslot(ws, R.slot_bytes, gin);
+        ph.c = cin; ph.ldc = Ks;
+        ph.wait_ctr[0] = RTP_CTR_G0 + gin; ph.wait_rel[0] = (s - 1) / 2;
+        ph.done_ctr[0] = RTP_CTR_G0 + gin;
+      }
+      if (!last) {
+        ph.credit_ptr = &ws_flags(R.ws[up])->done[RTP_CTR_G0 + gout].v;
+        ph.credit_ctr = RTP_CTR_G0 + gout; ph.credit_rel = s / 2;
+        ph.arrive_ptr = &ws_flags(R.ws[up])->arrive[RTP_CTR_G0 + gout].v;
+      }
+      if (op.bias_off >= 0 && op.dbias_full) {
+        ph.vec_out = reinterpret_cast<__nv_bfloat16*>(dst) + op.bias_off;
+        ph.vec_in = cin ? reinterpret_cast<const __nv_bfloat16*>(cin) + op.bias_off : nullptr;
+        ph.vec_add = op.dbias_full + (col ? (long long)j * Os : 0);
+        ph.vec_len = Os;
+      }
+      set_vec_ok(ph);
+    }
+    // ---- dgrad: column: dx += dy_j W_j ; row: dx_j = dy W_j
+    if (op.dx) {
+      RtpPhase& ph = P.phases[np++];
+      init_phase(ph);
+      ph.a_map = 2; ph.a_mn = 0;
+      ph.b_map = last ? 3 : 4 + wslot; ph.b_mn = 1;
+      ph.M = op.M; ph.N = Ks; ph.K = Os;
+      if (col) ph.a_off_k = j * Os;
+      ph.bn = pick_bn(ph.M, ph.N, R.ctas);
+      ph.ldd = op.lddx;
+      ph.d = reinterpret_cast<__nv_bfloat16*>(op.dx) + (col ? 0 : (long long)j * Ks);
+      if (col && s > 0) { ph.c = op.dx; ph.ldc = op.lddx; }
+      if (op.mask && (!col || last)) {
+        ph.mask = reinterpret_cast<const __nv_bfloat16*>(op.mask) + (col ? 0 : (long long)j * Ks);
+        ph.ldmask = op.ldmask; ph.mask_scale = op.mask_scale;
+      }
+      if (!last) {
+        ph.wait_ctr[0] = RTP_CTR_W0 + wslot; ph.wait_rel[0] = s / 2;
+        ph.done_ctr[0] = RTP_CTR_W0 + wslot;
+      }
+      set_vec_ok(ph);
+    }
+  }
+  P.n_phases = np;
+  // weight pushes: at step s the owner q sends its home shard to rank q+1+s, which uses it at its step s
+  P.n_pushes = op.dx ? N - 1 : 0;
+  for (int s = 0; s + 1 < N && op.dx; ++s) {
+    RtpPush& pu = P.pushes[s];
+    memset(&pu, 0, sizeof(pu));
+    const int t = mod(r + 1 + s, N);
+    const int slot = s & 1;
+    pu.src = op.home;
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
+    pu.bytes = op.shard_bytes;
+    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
+    pu.credit_ctr = RTP_CTR_W0 + slot;
+    pu.credit_rel = s / 2;
+    pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
+  }
+  if (op.dx) {
+    P.uses_inc[RTP_CTR_W0] = N / 2;
+    P.uses_inc[RTP_CTR_W1] = (N - 1) / 2;
+  }
+  P.uses_inc[RTP_CTR_G0] = N / 2;
+  P.uses_inc[RTP_CTR_G1] = (N - 1) / 2;
+  return 0;
+}
+
+template <int NEMU, class Op, class Builder>
+int run_emu(const RtpRing* rings, const Op* ops, Builder build, cudaStream_t stream) {
+  static rtp::GemmParams<NEMU> params;  // large; keep off the stack
+  for (int e = 0; e < NEMU; ++e)
+    if (build(rings[e], ops[e], params.prog[e])) return -1;
+  params.ctas_per_rank = rings[0].ctas;
+  return launch<NEMU>(params, rings[0].ctas * NEMU, true, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* rtp_last_error(void) { return g_err.c_str(); }
+int rtp_sm_count(void) { return sm_count(); }
+
+int rtp_gemm(const RtpGemmArgs* a, void* stream) {
+  static thread_local rtp::GemmParams<1> params;
+  RtpProgram& P = params.prog[0];
+  init_program(P);
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return fail("empty GEMM");
+  if (a->a_mn ? make_map_mn(&P.maps[0], a->a, a->M, a->K, a->lda) : make_map_k(&P.maps[0], a->a, a->M, a->K, a->lda))
+    return -1;
+  if (a->b_mn ? make_map_mn(&P.maps[1], a->b, a->N, a->K, a->ldb) : make_map_k(&P.maps[1], a->b, a->N, a->K, a->ldb))
+    return -1;
+  const int ctas = a->num_ctas > 0 ? a->num_ctas : sm_count();
+  RtpPhase& ph = P.phases[0];
+  init_phase(ph);
+  ph.a_map = 0; ph.b_map = 1; ph.a_mn = a->a_mn; ph.b_mn = a->b_mn;
+  ph.M = a->M; ph.N = a->N; ph.K = a->K;
+  ph.bn = a->bn ? a->bn : pick_bn(a->M, a->N, ctas);
+  if (ph.bn != 128 && ph.bn != 256) return fail("bn must be 128 or 256");
+  ph.d = a->d; ph.ldd = a->ldd; ph.d_fp32 = a->d_fp32;
+  ph.c = a->c; ph.ldc = a->ldc; ph.c_fp32 = a->c_fp32;
+  ph.bias = a->bias; ph.act = a->act;
+  ph.mask = a->mask; ph.ldmask = a->ldmask; ph.mask_scale = a->mask_scale;
+  ph.drop_thresh = drop_threshold(a->drop_p);
+  ph.drop_scale = a->drop_p > 0.f ? 1.f / (1.f - a->drop_p) : 1.f;
+  ph.drop_seed = a->seed; ph.drop_offset = a->offset;
+  set_vec_ok(ph);
+  P.n_phases = 1;
+  P.status = a->status;
+  if (!P.status) return fail("status word required");
+  params.ctas_per_rank = ctas;
+  const int tiles = ((a->M + 127) / 128) * ((a->N + ph.bn - 1) / ph.bn);
+  const int grid = tiles < ctas ? tiles : ctas;
+  params.ctas_per_rank = grid;
+  return launch<1>(params, grid, false, (cudaStream_t)stream);
+}
+
+int rtp_linear_fwd(const RtpRing* ring, const RtpLinearFwd* op, void* stream) {
+  static thread_local rtp::GemmParams<1> params;
+  if (build_linear_fwd(*ring, *op, params.prog[0])) return -1;
+  if (!params.prog[0].status) return fail("ring workspace required");
+  params.ctas_per_rank = ring->ctas;
+  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream);
+}
+int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream) {
+  static thread_local rtp::GemmParams<1> params;
+  if (build_linear_bwd(*ring, *op, params.prog[0])) return -1;
+  if (!params.prog[0].status) return fail("ring workspace required");
+  params.ctas_per_rank = ring->ctas;
+  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream);
+}
+int rtp_linear_fwd_emu(const RtpRing* rings, const RtpLinearFwd* ops, int world, void* stream) {
+  if (world == 2) return run_emu<2>(rings, ops, build_linear_fwd, (cudaStream_t)stream);
+  if (world == 4) return run_emu<4>(rings, ops, build_linear_fwd, (cudaStream_t)stream);
+  return fail("emulation supports 2 or 4 ranks");
+}
+int rtp_linear_bwd_emu(const RtpRing* rings, const RtpLinearBwd* ops, int world, void* stream) {
+  if (world == 2) return run_emu<2>(rings, ops, build_linear_bwd, (cudaStream_t)stream);
+  if (world == 4) return run_emu<4>(rings, ops, build_linear_bwd, (cudaStream_t)stream);
+  return fail("emulation supports 2 or 4 ranks");
+}
+
+// ------------------------------------------------------------------------------------- workspace
+unsigned long long rtp_ws_bytes(unsigned long long slot_bytes) { return kFlagBytes + 4 * slot_bytes; }
+int rtp_ws_create(unsigned long long slot_bytes, void** out) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, rtp_ws_bytes(slot_bytes));
+  if (e != cudaSuccess) return fail(std::string("cudaMalloc workspace: ") + cudaGetErrorString(e));
+  e = cudaMemset(p, 0, kFlagBytes);
+  if (e != cudaSuccess) return fail(std::string("cudaMemset workspace: ") + cudaGetErrorString(e));
+  *out = p;
+  return 0;
+}
+int rtp_ws_destroy(void* ws) { return cudaFree(ws) == cudaSuccess ? 0 : fail("cudaFree failed"); }
+int rtp_ws_reset(void* ws, void* stream) {
+  return cudaMemsetAsync(ws, 0, kFlagBytes, (cudaStream_t)stream) == cudaSuccess ? 0 : fail("memset failed");
+}
+int rtp_ws_ipc_get(void* ws, void* handle64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ws);
+  if (e != cudaSuccess) return fail(std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e));
+  static_assert(sizeof(h) == 64, "ipc handle size");
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+int rtp_ws_ipc_open(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  cudaError_t e = cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail(std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e));
+  return 0;
+}
+int rtp_ws_ipc_close(void* mapped) {
+  return cudaIpcCloseMemHandle(mapped) == cudaSuccess ? 0 : fail("cudaIpcCloseMemHandle failed");
+}
+int rtp_ws_status(void* ws, unsigned long long* host_out, void* stream) {
+  cudaError_t e = cudaMemcpyAsync(host_out, &ws_flags(ws)->status.v, 8, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(std::string("status copy: ") + cudaGetErrorString(e));
+  e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(std::string("status sync: ") + cudaGetErrorString(e));
+  return 0;
+}
+void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i) { return ws_wslot(ws, slot_bytes, i); }
+void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i) { return ws_gslot(ws, slot_bytes, i); }
+
+}  // extern "C"

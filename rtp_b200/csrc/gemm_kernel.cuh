@@ -1,0 +1,420 @@
+// The rotation GEMM kernel: a persistent, warp-specialised tcgen05 kernel that runs an RtpProgram.
+//
+//   warp 0      TMA producer: streams 128x64 (A) and bn x 64 (B) bf16 tiles into a 4-stage smem ring
+//   warp 1      UMMA issuer: one elected thread issues tcgen05.mma into one of two TMEM accumulators
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, apply bias/activation/mask/dropout/accumulate,
+//               store to local or peer global memory, then bump the phase's counters
+//   warps 6-7   pushers: copy this rank's home shard into a peer's workspace slot (NVLink P2P stores),
+//               bounded by the peer's slot-free counter, then bump the peer's arrival counter
+//
+// All cross-rank waits are on 64-bit counters with an iteration/time limit; on expiry the CTA marks
+// the status word, drains what it has in flight, frees its TMEM and returns.
+#pragma once
+#include "common.cuh"
+#include "gemm_program.h"
+
+namespace rtp {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBK * 2;          // 16 KB
+constexpr int kBBytesMax = 256 * kBK * 2;       // 32 KB
+constexpr int kStageBytes = kABytes + kBBytesMax;
+constexpr int kTmemCols = 512;
+constexpr int kNumThreads = 256;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+
+struct SmemCtrl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+template <int NEMU>
+struct GemmParams {
+  RtpProgram prog[NEMU];
+  int ctas_per_rank;
+};
+
+__device__ __forceinline__ unsigned long long fill_target(const RtpFlagBlock* fb, int ctr, int rel, int plus,
+                                                          int G) {
+  // counters count one unit per CTA per fill of the slot
+  return (fb->uses[ctr].v + (unsigned long long)(rel + plus)) * (unsigned long long)G;
+}
+
+template <int NEMU>
+__global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_constant__ GemmParams<NEMU> params) {
+  extern __shared__ uint8_t smem_raw[];
+  const int G = params.ctas_per_rank;
+  const int vrank = (NEMU == 1) ? 0 : (int)(blockIdx.x / G);
+  const int cta = (NEMU == 1) ? (int)blockIdx.x : (int)(blockIdx.x % G);
+  const RtpProgram& P = params.prog[vrank];
+
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SmemCtrl* ctl = reinterpret_cast<SmemCtrl*>(tiles + kStages * kStageBytes);
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  unsigned long long* status = P.status;
+  const unsigned long long timeout_ns = P.timeout_ns;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&ctl->tmem_full[a], 1);
+      mbar_init(&ctl->tmem_empty[a], 4);
+    }
+    mbar_init(&ctl->drain, 1);
+    ctl->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t issued_parity[kStages];
+      bool issued[kStages];
+      for (int s = 0; s < kStages; ++s) { issued[s] = false; issued_parity[s] = 0; }
+      bool ok = true;
+      for (int p = 0; p < P.n_phases && ok; ++p) {
+        const RtpPhase& ph = P.phases[p];
+        const int tiles_m = (ph.M + kBM - 1) / kBM;
+        const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
+        const int total = tiles_m * tiles_n;
+        if (cta >= total) continue;
+        for (int w = 0; w < 2 && ok; ++w) {
+          if (ph.wait_ctr[w] >= 0) {
+            ok = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
+                                 fill_target(P.flags, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
+                                 timeout_ns, ST_TIMEOUT_ARRIVAL);
+          }
+        }
+        if (!ok) break;
+        if (ph.wait_ctr[0] >= 0 || ph.wait_ctr[1] >= 0) fence_proxy_async();
+        const CUtensorMap* ma = &P.maps[ph.a_map];
+        const CUtensorMap* mb = &P.maps[ph.b_map];
+        const int kblocks = (ph.K + kBK - 1) / kBK;
+        const uint32_t tx = kABytes + ph.bn * kBK * 2;
+        for (int t = cta; t < total && ok; t += G) {
+          const int m0 = (t % tiles_m) * kBM;
+          const int n0 = (t / tiles_m) * ph.bn;
+          for (int kb = 0; kb < kblocks; ++kb) {
+            if (!mbar_wait(&ctl->empty[stage], phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
+            uint8_t* sa = tiles + stage * kStageBytes;
+            uint8_t* sb = sa + kABytes;
+            mbar_arrive_expect_tx(&ctl->full[stage], tx);
+            issued[stage] = true;
+            issued_parity[stage] = phase;
+            const int k0 = kb * kBK;
+            if (!ph.a_mn) {
+              tma_load_2d(sa, ma, k0 + ph.a_off_k, m0 + ph.a_off_mn, &ctl->full[stage]);
+            } else {
+              tma_load_2d(sa, ma, m0 + ph.a_off_mn, k0 + ph.a_off_k, &ctl->full[stage]);
+              tma_load_2d(sa + 8192, ma, m0 + 64 + ph.a_off_mn, k0 + ph.a_off_k, &ctl->full[stage]);
+            }
+            if (!ph.b_mn) {
+              for (int i = 0; i < ph.bn / 128; ++i)
+                tma_load_2d(sb + i * 16384, mb, k0 + ph.b_off_k, n0 + i * 128 + ph.b_off_mn, &ctl->full[stage]);
+            } else {
+              for (int i = 0; i < ph.bn / 64; ++i)
+                tma_load_2d(sb + i * 8192, mb, n0 + i * 64 + ph.b_off_mn, k0 + ph.b_off_k, &ctl->full[stage]);
+            }
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+      if (!ok) {
+        // gave up: wait (bounded) until every copy this thread issued has landed before the CTA exits
+        for (int s = 0; s < kStages; ++s) {
+          if (!issued[s]) continue;
+          unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(&ctl->full[s], issued_parity[s])) {
+            if (globaltimer_ns() - t0 > 2000000ull) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      bool issued_any = false;
+      for (int p = 0; p < P.n_phases && ok; ++p) {
+        const RtpPhase& ph = P.phases[p];
+        const int tiles_m = (ph.M + kBM - 1) / kBM;
+        const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
+        const int total = tiles_m * tiles_n;
+        const int kblocks = (ph.K + kBK - 1) / kBK;
+        const uint32_t idesc = make_idesc_bf16(kBM, ph.bn, ph.a_mn, ph.b_mn);
+        const uint32_t a_lbo = ph.a_mn ? 8192u : 16u, b_lbo = ph.b_mn ? 8192u : 16u;
+        const uint32_t a_kstep = ph.a_mn ? 2048u : 32u, b_kstep = ph.b_mn ? 2048u : 32u;
+        for (int t = cta; t < total && ok; t += G) {
+          if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
+          for (int kb = 0; kb < kblocks; ++kb) {
+            if (!mbar_wait(&ctl->full[stage], phase, abort_flag, status, timeout_ns)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
+            const uint32_t sb = sa + kABytes;
+#pragma unroll
+            for (int kk = 0; kk < kBK / 16; ++kk) {
+              const uint64_t da = make_smem_desc(sa + kk * a_kstep, a_lbo, 1024);
+              const uint64_t db = make_smem_desc(sb + kk * b_kstep, b_lbo, 1024);
+              umma_bf16(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            }
+            issued_any = true;
+            umma_commit(&ctl->empty[stage]);  // frees the smem stage once these MMAs have read it
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          umma_commit(&ctl->tmem_full[acc]);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+      }
+      if (!ok && issued_any) {
+        // make sure no MMA is still reading smem / writing TMEM before tear-down
+        umma_commit(&ctl->drain);
+        unsigned long long t0 = globaltimer_ns();
+        while (!mbar_try_wait(&ctl->drain, 0)) {
+          if (globaltimer_ns() - t0 > 2000000ull) break;
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    const int epi_tid = (warp - 2) * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int p = 0; p < P.n_phases; ++p) {
+      const RtpPhase& ph = P.phases[p];
+      const int tiles_m = (ph.M + kBM - 1) / kBM;
+      const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
+      const int total = tiles_m * tiles_n;
+      const bool has_tiles = cta < total;
+      const bool does_vec = (ph.vec_out != nullptr) && cta == 0;
+      if (ok && (has_tiles || does_vec)) {
+        // operands of the accumulate / bias reads must have arrived; the destination slot must be free
+        uint32_t good = 1;
+        if (lane == 0) {
+          for (int w = 0; w < 2 && good; ++w)
+            if (ph.wait_ctr[w] >= 0)
+              good = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
+                                     fill_target(P.flags, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
+                                     timeout_ns, ST_TIMEOUT_ARRIVAL);
+          if (good && ph.credit_ptr)
+            good = wait_counter_ge(ph.credit_ptr, fill_target(P.flags, ph.credit_ctr, ph.credit_rel, 0, G),
+                                   abort_flag, status, timeout_ns, ST_TIMEOUT_CREDIT);
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) ok = false;
+      }
+      for (int t = cta; t < total && ok; t += G) {
+        const int m0 = (t % tiles_m) * kBM;
+        const int n0 = (t / tiles_m) * ph.bn;
+        uint32_t good = 1;
+        if (lane == 0) good = mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, status, timeout_ns);
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) { ok = false; break; }
+        tc_fence_after();
+        const int row = m0 + quad * 32 + lane;
+        const bool row_ok = row < ph.M;
+        for (int cb = 0; cb < ph.bn / 32; ++cb) {
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256 + cb * 32), r);
+          tmem_ld_wait();
+          const int col0 = n0 + cb * 32;
+          if (!row_ok || col0 >= ph.N) continue;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {  // groups of 8 columns
+            const int col = col0 + g * 8;
+            if (col >= ph.N) break;
+            const int nvalid = min(8, ph.N - col);
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+            const bool vec = ph.vec_ok && nvalid == 8;
+            if (ph.c) {
+              if (ph.c_fp32) {
+                const float* cp = reinterpret_cast<const float*>(ph.c) + (long long)row * ph.ldc + col;
+                if (vec) {
+                  float4 c0 = __ldcg(reinterpret_cast<const float4*>(cp));
+                  float4 c1 = __ldcg(reinterpret_cast<const float4*>(cp) + 1);
+                  v[0] += c0.x; v[1] += c0.y; v[2] += c0.z; v[3] += c0.w;
+                  v[4] += c1.x; v[5] += c1.y; v[6] += c1.z; v[7] += c1.w;
+                } else {
+                  for (int i = 0; i < nvalid; ++i) v[i] += __ldcg(cp + i);
+                }
+              } else {
+                const __nv_bfloat16* cp = reinterpret_cast<const __nv_bfloat16*>(ph.c) + (long long)row * ph.ldc + col;
+                if (vec) {
+                  uint4 c = __ldcg(reinterpret_cast<const uint4*>(cp));
+                  v[0] += bf16_lo(c.x); v[1] += bf16_hi(c.x); v[2] += bf16_lo(c.y); v[3] += bf16_hi(c.y);
+                  v[4] += bf16_lo(c.z); v[5] += bf16_hi(c.z); v[6] += bf16_lo(c.w); v[7] += bf16_hi(c.w);
+                } else {
+                  for (int i = 0; i < nvalid; ++i)
+                    v[i] += __bfloat162float(__ldcg(cp + i));
+                }
+              }
+            }
+            if (ph.bias) {
+              const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(ph.bias) + col;
+              for (int i = 0; i < nvalid; ++i) v[i] += __bfloat162float(__ldcg(bp + i));
+            }
+            if (ph.act == 1) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = fmaxf(v[i], 0.f);
+            } else if (ph.act == 2) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = 0.5f * v[i] * (1.f + erff(v[i] * 0.70710678118654752f));
+            }
+            if (ph.mask) {
+              const __nv_bfloat16* mp = reinterpret_cast<const __nv_bfloat16*>(ph.mask) + (long long)row * ph.ldmask + col;
+              if (vec) {
+                uint4 m = __ldcg(reinterpret_cast<const uint4*>(mp));
+                const uint32_t mw[4] = {m.x, m.y, m.z, m.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  v[2 * i] = bf16_lo(mw[i]) > 0.f ? v[2 * i] * ph.mask_scale : 0.f;
+                  v[2 * i + 1] = bf16_hi(mw[i]) > 0.f ? v[2 * i + 1] * ph.mask_scale : 0.f;
+                }
+              } else {
+                for (int i = 0; i < nvalid; ++i)
+                  v[i] = __bfloat162float(__ldcg(mp + i)) > 0.f ? v[i] * ph.mask_scale : 0.f;
+              }
+            }
+            if (ph.drop_thresh) {
+              // element index = position in the logical [M, N] output; 8 | col so two philox calls cover the group
+              const unsigned long long e = (unsigned long long)row * (unsigned long long)ph.N + (unsigned long long)col;
+              uint4 r0 = philox4x32(ph.drop_seed, ph.drop_offset, e >> 2);
+              uint4 r1 = philox4x32(ph.drop_seed, ph.drop_offset, (e >> 2) + 1);
+              const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = rw[i] >= ph.drop_thresh ? v[i] * ph.drop_scale : 0.f;
+            }
+            if (ph.d_fp32) {
+              float* dp = reinterpret_cast<float*>(ph.d) + (long long)row * ph.ldd + col;
+              if (vec) {
+                reinterpret_cast<float4*>(dp)[0] = make_float4(v[0], v[1], v[2], v[3]);
+                reinterpret_cast<float4*>(dp)[1] = make_float4(v[4], v[5], v[6], v[7]);
+              } else {
+                for (int i = 0; i < nvalid; ++i) dp[i] = v[i];
+              }
+            } else {
+              __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(ph.d) + (long long)row * ph.ldd + col;
+              if (vec) {
+                *reinterpret_cast<uint4*>(dp) =
+                    make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+              } else {
+                for (int i = 0; i < nvalid; ++i) dp[i] = __float2bfloat16(v[i]);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      // small vector job (bias-gradient hop) by CTA 0
+      if (ok && does_vec) {
+        for (int i = epi_tid; i < ph.vec_len; i += 128) {
+          float x = ph.vec_add[i];
+          if (ph.vec_in) {
+            x += ph.vec_fp32 ? __ldcg(reinterpret_cast<const float*>(ph.vec_in) + i)
+                             : __bfloat162float(__ldcg(reinterpret_cast<const __nv_bfloat16*>(ph.vec_in) + i));
+          }
+          if (ph.vec_fp32) reinterpret_cast<float*>(ph.vec_out)[i] = x;
+          else reinterpret_cast<__nv_bfloat16*>(ph.vec_out)[i] = __float2bfloat16(x);
+        }
+      }
+      // phase end: publish "read done" / "data arrived". Every CTA signals, also one without tiles.
+      const bool signals = ph.done_ctr[0] >= 0 || ph.done_ctr[1] >= 0 || ph.arrive_ptr != nullptr;
+      if (signals) {
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (epi_tid == 0 && ok) {
+          for (int w = 0; w < 2; ++w)
+            if (ph.done_ctr[w] >= 0) red_release_sys_add(&P.flags->done[ph.done_ctr[w]].v, 1ull);
+          if (ph.arrive_ptr) red_release_sys_add(ph.arrive_ptr, 1ull);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ pushers (2 warps)
+    const int ptid = (warp - 6) * 32 + lane;
+    bool ok = true;
+    for (int j = 0; j < P.n_pushes; ++j) {
+      const RtpPush& pu = P.pushes[j];
+      uint32_t good = 1;
+      if (ok && lane == 0 && pu.credit_ptr)
+        good = wait_counter_ge(pu.credit_ptr, fill_target(P.flags, pu.credit_ctr, pu.credit_rel, 0, G), abort_flag,
+                               status, timeout_ns, ST_TIMEOUT_CREDIT);
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) ok = false;
+      if (ok) {
+        const unsigned long long units = pu.bytes >> 4;
+        const unsigned long long per = (units + G - 1) / G;
+        const unsigned long long lo = per * (unsigned long long)cta;
+        unsigned long long hi = lo + per;
+        if (hi > units) hi = units;
+        const uint4* src = reinterpret_cast<const uint4*>(pu.src);
+        uint4* dst = reinterpret_cast<uint4*>(pu.dst);
+        unsigned long long i = lo + ptid;
+        for (; i + 192 < hi; i += 256) {
+          uint4 a = __ldg(src + i), b = __ldg(src + i + 64), c = __ldg(src + i + 128), d = __ldg(src + i + 192);
+          dst[i] = a; dst[i + 64] = b; dst[i + 128] = c; dst[i + 192] = d;
+        }
+        for (; i < hi; i += 64) dst[i] = __ldg(src + i);
+        __threadfence_system();
+      }
+      asm volatile("bar.sync 2, 64;" ::: "memory");
+      if (ptid == 0 && ok && pu.arrive_ptr) red_release_sys_add(pu.arrive_ptr, 1ull);
+    }
+  }
+
+  // ---------------------------------------------------------------------- tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && P.flags) {
+    __threadfence();
+    unsigned long long prev = atomicAdd(&P.flags->done_ctas.v, 1ull);
+    if (prev == (unsigned long long)(G - 1)) {
+      for (int k = 0; k < RTP_NUM_CTR; ++k) P.flags->uses[k].v += (unsigned long long)P.uses_inc[k];
+      P.flags->done_ctas.v = 0;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace rtp

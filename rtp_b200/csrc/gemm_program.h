@@ -1,0 +1,96 @@
+// Host/device description of one launch of the rotation GEMM kernel.
+//
+// A launch executes a small *program*: an ordered list of GEMM phases (each a tiled
+// D = epilogue(A * B^T) over tcgen05 tensor cores) and an ordered list of push jobs (bulk copies of a
+// weight shard into a peer GPU's workspace slot).  Phases and pushes synchronise with other ranks
+// only through monotonically increasing 64-bit counters that live in each rank's peer-mapped flag
+// block; a plain single-GPU GEMM is a program with one phase, no pushes and no counters.
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+#define RTP_MAX_MAPS 8
+#define RTP_MAX_PHASES 16
+#define RTP_MAX_PUSHES 8
+#define RTP_MAX_EMU_RANKS 4
+
+// indices into FlagBlock::arrive / ::done / ::uses
+#define RTP_CTR_W0 0
+#define RTP_CTR_W1 1
+#define RTP_CTR_G0 2
+#define RTP_CTR_G1 3
+#define RTP_NUM_CTR 4
+
+// Per-rank flag block (peer-mapped). Every word sits in its own 128-byte line.
+struct alignas(128) RtpFlagWord {
+  unsigned long long v;
+  unsigned long long pad[15];
+};
+struct RtpFlagBlock {
+  RtpFlagWord arrive[RTP_NUM_CTR];  // bumped by the producer's CTAs after their stores into the slot
+  RtpFlagWord done[RTP_NUM_CTR];    // bumped by this rank's CTAs once they finished reading the slot
+  RtpFlagWord uses[RTP_NUM_CTR];    // number of completed fills of the slot (same on every rank)
+  RtpFlagWord done_ctas;            // CTAs of the running launch that have finished
+  RtpFlagWord status;               // 0 = ok, else first error code
+};
+
+struct RtpPhase {
+  // operands (bf16). *_mn = 1: the operand is stored with its M (or N) index contiguous.
+  int a_map, b_map;
+  int a_mn, b_mn;
+  int a_off_mn, a_off_k;  // element offsets added to the tile coordinates
+  int b_off_mn, b_off_k;
+  int M, N, K;
+  int bn;  // tile width: 128 or 256
+  // epilogue
+  void* d;
+  long long ldd;
+  int d_fp32;
+  int vec_ok;  // 1: 16-byte vector accesses of d/c/mask rows are aligned
+  const void* c;  // optional accumulate source (same shape as d)
+  long long ldc;
+  int c_fp32;
+  int act;             // 0 none, 1 relu, 2 gelu(erf)
+  const void* bias;    // optional bf16[N]
+  const void* mask;    // optional bf16 [M, N]: out = mask > 0 ? out * mask_scale : 0
+  long long ldmask;
+  float mask_scale;
+  uint32_t drop_thresh;  // 0: no dropout. keep element if philox word >= thresh
+  float drop_scale;
+  unsigned long long drop_seed, drop_offset;
+  // optional vector job done by CTA 0 at the end of the phase: vec_out[i] = vec_in[i] + vec_add[i] (bf16/fp32 per flags)
+  void* vec_out;
+  const void* vec_in;
+  const float* vec_add;
+  int vec_len;
+  int vec_fp32;  // dtype of vec_out / vec_in
+  // synchronisation (all optional)
+  int wait_ctr[2];  // local arrival counters that must reach fill (uses + rel + 1) before operands are read
+  int wait_rel[2];
+  unsigned long long* credit_ptr;  // remote `done` counter that must reach fill (uses + rel) before d is written
+  int credit_ctr;
+  int credit_rel;
+  int done_ctr[2];                 // local `done` counters bumped when this CTA has finished the phase
+  unsigned long long* arrive_ptr;  // remote `arrive` counter bumped when this CTA has finished the phase
+};
+
+struct RtpPush {
+  const void* src;
+  void* dst;  // peer memory
+  unsigned long long bytes;  // multiple of 16
+  unsigned long long* credit_ptr;  // remote `done` counter of the destination slot
+  int credit_ctr;
+  int credit_rel;
+  unsigned long long* arrive_ptr;  // remote `arrive` counter of the destination slot
+};
+
+struct alignas(64) RtpProgram {
+  CUtensorMap maps[RTP_MAX_MAPS];
+  RtpPhase phases[RTP_MAX_PHASES];
+  RtpPush pushes[RTP_MAX_PUSHES];
+  int n_phases, n_pushes;
+  RtpFlagBlock* flags;  // this rank's flag block (may be null when nothing synchronises)
+  int uses_inc[RTP_NUM_CTR];  // added to flags->uses[] by the last CTA of the launch
+  unsigned long long* status;  // status word (flags->status or a plain device word)
+  unsigned long long timeout_ns;
+};

@@ -1,0 +1,147 @@
+"""ctypes binding of librtp_b200.so (the hand-written sm_100a kernels).
+
+The shared library is built in-tree by ``rtp_b200/csrc/build.py`` and loaded lazily.  On a machine
+with a GPU the library is mandatory: :func:`lib` raises instead of falling back to PyTorch kernels.
+"""
+import ctypes as C
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "librtp_b200.so")
+MAX_WORLD = 8
+
+_lock = threading.Lock()
+_lib = None
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("lda", C.c_longlong), ("a_mn", C.c_int),
+        ("b", C.c_void_p), ("ldb", C.c_longlong), ("b_mn", C.c_int),
+        ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+        ("d", C.c_void_p), ("ldd", C.c_longlong), ("d_fp32", C.c_int),
+        ("c", C.c_void_p), ("ldc", C.c_longlong), ("c_fp32", C.c_int),
+        ("bias", C.c_void_p), ("act", C.c_int),
+        ("mask", C.c_void_p), ("ldmask", C.c_longlong), ("mask_scale", C.c_float),
+        ("drop_p", C.c_float), ("seed", C.c_ulonglong), ("offset", C.c_ulonglong),
+        ("status", C.c_void_p), ("num_ctas", C.c_int), ("bn", C.c_int),
+    ]
+
+
+class Ring(C.Structure):
+    _fields_ = [
+        ("rank", C.c_int), ("world", C.c_int),
+        ("ws", C.c_void_p * MAX_WORLD),
+        ("slot_bytes", C.c_ulonglong),
+        ("ctas", C.c_int),
+        ("timeout_ns", C.c_ulonglong),
+    ]
+
+
+class LinearFwd(C.Structure):
+    _fields_ = [
+        ("mode", C.c_int), ("M", C.c_int), ("in_features", C.c_int), ("out_features", C.c_int),
+        ("home", C.c_void_p), ("bias_off", C.c_longlong), ("shard_bytes", C.c_ulonglong),
+        ("x", C.c_void_p), ("ldx", C.c_longlong),
+        ("y", C.c_void_p), ("ldy", C.c_longlong),
+        ("act", C.c_int),
+        ("drop_p", C.c_float), ("seed", C.c_ulonglong), ("offset", C.c_ulonglong),
+    ]
+
+
+class LinearBwd(C.Structure):
+    _fields_ = [
+        ("mode", C.c_int), ("M", C.c_int), ("in_features", C.c_int), ("out_features", C.c_int),
+        ("home", C.c_void_p), ("bias_off", C.c_longlong), ("shard_bytes", C.c_ulonglong),
+        ("x", C.c_void_p), ("ldx", C.c_longlong),
+        ("dy", C.c_void_p), ("ldy", C.c_longlong),
+        ("dx", C.c_void_p), ("lddx", C.c_longlong),
+        ("grad_home", C.c_void_p),
+        ("dbias_full", C.c_void_p),
+        ("mask", C.c_void_p), ("ldmask", C.c_longlong), ("mask_scale", C.c_float),
+    ]
+
+
+def available() -> bool:
+    """True when the compiled library exists and a CUDA device is present."""
+    return os.path.exists(LIB_PATH) and torch.cuda.is_available()
+
+
+def lib():
+    """Load (once) and return the ctypes handle. Raises if the library is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m rtp_b200.csrc.build` "
+                "(the CUDA kernels are mandatory on a GPU machine; there is no PyTorch fallback)")
+        L = C.CDLL(LIB_PATH)
+        L.rtp_last_error.restype = C.c_char_p
+        L.rtp_ws_bytes.restype = C.c_ulonglong
+        L.rtp_ws_bytes.argtypes = [C.c_ulonglong]
+        L.rtp_ws_wslot.restype = C.c_void_p
+        L.rtp_ws_wslot.argtypes = [C.c_void_p, C.c_ulonglong, C.c_int]
+        L.rtp_ws_gslot.restype = C.c_void_p
+        L.rtp_ws_gslot.argtypes = [C.c_void_p, C.c_ulonglong, C.c_int]
+        L.rtp_ws_create.argtypes = [C.c_ulonglong, C.POINTER(C.c_void_p)]
+        L.rtp_ws_destroy.argtypes = [C.c_void_p]
+        L.rtp_ws_reset.argtypes = [C.c_void_p, C.c_void_p]
+        L.rtp_ws_ipc_get.argtypes = [C.c_void_p, C.c_void_p]
+        L.rtp_ws_ipc_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        L.rtp_ws_ipc_close.argtypes = [C.c_void_p]
+        L.rtp_ws_status.argtypes = [C.c_void_p, C.POINTER(C.c_ulonglong), C.c_void_p]
+        L.rtp_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+        L.rtp_linear_fwd.argtypes = [C.POINTER(Ring), C.POINTER(LinearFwd), C.c_void_p]
+        L.rtp_linear_bwd.argtypes = [C.POINTER(Ring), C.POINTER(LinearBwd), C.c_void_p]
+        L.rtp_linear_fwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(LinearFwd), C.c_int, C.c_void_p]
+        L.rtp_linear_bwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(LinearBwd), C.c_int, C.c_void_p]
+        _lib = L
+    return _lib
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        msg = lib().rtp_last_error()
+        raise RuntimeError(f"{what} failed: {msg.decode() if msg else rc}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_status_words = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """A per-device int64 word that kernels outside a ring use to report bounded-wait expiries."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev.type, dev.index)
+    w = _status_words.get(key)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int64, device=dev)
+        _status_words[key] = w
+    return w
+
+
+STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "wait for a peer's data timed out",
+                3: "wait for a peer's free slot timed out", 4: "bad argument"}
+
+
+class RotationTimeout(RuntimeError):
+    """A bounded device-side wait expired; the kernel returned early and its outputs are invalid."""
+
+
+def check_status(device=None):
+    """Synchronously read the status word and raise RotationTimeout if a kernel reported an error."""
+    w = status_word(device)
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        raise RotationTimeout(STATUS_NAMES.get(v, f"status {v}"))
