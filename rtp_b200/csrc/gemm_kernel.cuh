@@ -218,8 +218,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const int total = tiles_m * tiles_n;
       const bool has_tiles = cta < total;
       const bool does_vec = (ph.vec_out != nullptr) && cta == 0;
-      if (ok && (has_tiles || does_vec)) {
-        // operands of the accumulate / bias reads must have arrived; the destination slot must be free
+      (void)has_tiles;
+      if (ok) {
+        // Operands of the accumulate / bias reads must have arrived and the destination slot must be free.
+        // A CTA without tiles waits too: the counters only mean "every CTA is past fill u" if no CTA
+        // publishes its signal for fill u+1 before fill u+1 exists.
         uint32_t good = 1;
         if (lane == 0) {
           for (int w = 0; w < 2 && good; ++w)

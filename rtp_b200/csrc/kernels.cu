@@ -1,0 +1,754 @@
+// Memory-bound kernels of the training step, written for sm_100a: fused dropout+residual+LayerNorm
+// (and RMSNorm), softmax cross-entropy (loss and logit gradient in one pass over the row), rotated
+// embedding gather/scatter, short-sequence causal attention, column sums for bias gradients,
+// multi-tensor Adam(W) with value clipping, and small elementwise helpers.
+// All tensors are bf16 unless stated; statistics and reductions are fp32.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <string>
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace rtp;
+
+namespace {
+thread_local std::string k_err;
+int kfail(const char* what, cudaError_t e) {
+  k_err = std::string(what) + ": " + cudaGetErrorString(e);
+  return -1;
+}
+#define LAUNCH_CHECK(name)                                 \
+  do {                                                     \
+    cudaError_t e__ = cudaGetLastError();                  \
+    if (e__ != cudaSuccess) return kfail(name, e__);       \
+  } while (0)
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// block-wide sum over up to 1024 threads; `red` is a 32-float smem scratch
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (w == 0) t = warp_sum(t);
+  if (threadIdx.x == 0) red[0] = t;
+  __syncthreads();
+  return red[0];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : -INFINITY;
+  if (w == 0) t = warp_max(t);
+  if (threadIdx.x == 0) red[0] = t;
+  __syncthreads();
+  return red[0];
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  f[0] = bf16_lo(u.x); f[1] = bf16_hi(u.x); f[2] = bf16_lo(u.y); f[3] = bf16_hi(u.y);
+  f[4] = bf16_lo(u.z); f[5] = bf16_hi(u.z); f[6] = bf16_lo(u.w); f[7] = bf16_hi(u.w);
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+// dropout keep flags for 8 consecutive elements starting at e (e % 8 == 0)
+__device__ __forceinline__ void keep8(uint64_t seed, uint64_t offset, uint64_t e, uint32_t thresh, bool* k) {
+  uint4 r0 = philox4x32(seed, offset, e >> 2), r1 = philox4x32(seed, offset, (e >> 2) + 1);
+  k[0] = r0.x >= thresh; k[1] = r0.y >= thresh; k[2] = r0.z >= thresh; k[3] = r0.w >= thresh;
+  k[4] = r1.x >= thresh; k[5] = r1.y >= thresh; k[6] = r1.z >= thresh; k[7] = r1.w >= thresh;
+}
+uint32_t host_thresh(float p) {
+  if (p <= 0.f) return 0;
+  double t = (double)p * 4294967296.0;
+  if (t > 4294967295.0) t = 4294967295.0;
+  return (uint32_t)t;
+}
+
+// ------------------------------------------------------------------------------------------------
+// h = x + dropout(sub);  y = norm(h) * gamma (+ beta).  rms = 0: LayerNorm, 1: RMSNorm.
+// One block per row, D % 8 == 0. Saves h (bf16) and the row statistics for backward.
+// ------------------------------------------------------------------------------------------------
+__global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ sub,
+                                const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
+                                __nv_bfloat16* __restrict__ h_out, __nv_bfloat16* __restrict__ y,
+                                float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int D, float eps,
+                                int rms, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset) {
+  __shared__ float red[32];
+  extern __shared__ float rowbuf[];  // D floats
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const size_t base = (size_t)row * D;
+    float s = 0.f;
+    for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + base + c), v);
+      if (sub) {
+        float u[8];
+        unpack8(*reinterpret_cast<const uint4*>(sub + base + c), u);
+        if (thresh) {
+          bool k[8];
+          keep8(seed, offset, base + c, thresh, k);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) u[i] = k[i] ? u[i] * drop_scale : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += u[i];
+      }
+      // round to bf16 first: backward sees exactly the saved h
+      uint4 hp = pack8(v);
+      unpack8(hp, v);
+      if (h_out) *reinterpret_cast<uint4*>(h_out + base + c) = hp;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { rowbuf[c + i] = v[i]; s += v[i]; }
+    }
+    float mean = 0.f;
+    if (!rms) mean = block_sum(s, red) / D;
+    float q = 0.f;
+    for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { float d = rowbuf[c + i] - mean; q += d * d; }
+    }
+    const float var = block_sum(q, red) / D;
+    const float rstd = rsqrtf(var + eps);
+    if (threadIdx.x == 0) {
+      if (mean_out) mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+    for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
+      float g[8], b[8], o[8];
+      unpack8(*reinterpret_cast<const uint4*>(gamma + c), g);
+      if (beta) unpack8(*reinterpret_cast<const uint4*>(beta + c), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = (rowbuf[c + i] - mean) * rstd * g[i] + (beta ? b[i] : 0.f);
+      *reinterpret_cast<uint4*>(y + base + c) = pack8(o);
+    }
+    __syncthreads();
+  }
+}
+
+// Backward: dh = d(norm)/dh ; dx = dh ; dsub = dropout_mask * dh ; dgamma/dbeta accumulated with atomics (fp32).
+__global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                                const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                                const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                                __nv_bfloat16* __restrict__ dsub, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                int M, int D, int rms, uint32_t thresh, float drop_scale, uint64_t seed,
+                                uint64_t offset, const __nv_bfloat16* __restrict__ dres) {
+  __shared__ float red[32];
+  extern __shared__ float sm[];  // 2*D floats: per-block dgamma / dbeta partials
+  float* pg = sm;
+  float* pb = sm + D;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) { pg[c] = 0.f; pb[c] = 0.f; }
+  __syncthreads();
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const size_t base = (size_t)row * D;
+    const float mean = rms ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
+      float g[8], d[8], hv[8];
+      unpack8(*reinterpret_cast<const uint4*>(gamma + c), g);
+      unpack8(*reinterpret_cast<const uint4*>(dy + base + c), d);
+      unpack8(*reinterpret_cast<const uint4*>(h + base + c), hv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = (hv[i] - mean) * rstd;
+        const float dg = d[i] * g[i];
+        s1 += dg;
+        s2 += dg * xh;
+        pg[c + i] += d[i] * xh;   // each column is owned by one thread of the block: no race
+        pb[c + i] += d[i];
+      }
+    }
+    s1 = rms ? 0.f : block_sum(s1, red) / D;
+    s2 = block_sum(s2, red) / D;
+    for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
+      float g[8], d[8], hv[8], o[8];
+      unpack8(*reinterpret_cast<const uint4*>(gamma + c), g);
+      unpack8(*reinterpret_cast<const uint4*>(dy + base + c), d);
+      unpack8(*reinterpret_cast<const uint4*>(h + base + c), hv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = (hv[i] - mean) * rstd;
+        o[i] = (d[i] * g[i] - s1 - xh * s2) * rstd;
+      }
+      if (dres) {  // gradient that reaches h along a second path (pre-norm residual stream)
+        float e[8];
+        unpack8(*reinterpret_cast<const uint4*>(dres + base + c), e);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += e[i];
+      }
+      *reinterpret_cast<uint4*>(dx + base + c) = pack8(o);
+      if (dsub) {
+        if (thresh) {
+          bool k[8];
+          keep8(seed, offset, base + c, thresh, k);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = k[i] ? o[i] * drop_scale : 0.f;
+        }
+        *reinterpret_cast<uint4*>(dsub + base + c) = pack8(o);
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    atomicAdd(dgamma + c, pg[c]);
+    if (dbeta) atomicAdd(dbeta + c, pb[c]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Softmax cross-entropy over rows of bf16 logits [M, V] (row pitch ld). Writes the per-row loss (fp32)
+// and overwrites the logits with grad_scale * (softmax - onehot), i.e. the gradient of
+// grad_scale * sum_rows(loss). Rows whose target equals ignore_index give zero loss and gradient.
+// ------------------------------------------------------------------------------------------------
+__global__ void ce_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ target,
+                          float* __restrict__ loss, int M, int V, float grad_scale, long long ignore_index,
+                          int write_grad) {
+  __shared__ float red[32];
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    __nv_bfloat16* lp = logits + (size_t)row * ld;
+    const long long t = target[row];
+    float mx = -INFINITY;
+    for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(lp + c), v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, v[i]);
+    }
+    mx = block_max(mx, red);
+    float se = 0.f;
+    for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(lp + c), v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) se += __expf(v[i] - mx);
+    }
+    se = block_sum(se, red);
+    const float lse = mx + __logf(se);
+    const bool ignored = (t == ignore_index) || t < 0 || t >= V;
+    if (threadIdx.x == 0) loss[row] = ignored ? 0.f : lse - __bfloat162float(lp[t]);
+    __syncthreads();
+    if (write_grad) {
+      const float inv = 1.f / se;
+      for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(lp + c), v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float p = __expf(v[i] - mx) * inv;
+          if (c + i == t) p -= 1.f;
+          v[i] = ignored ? 0.f : p * grad_scale;
+        }
+        *reinterpret_cast<uint4*>(lp + c) = pack8(v);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Embedding gather for one visiting table shard [V, Ds]: out[t, col_off + c] =
+//   dropout(table[ids[t], c] * scale + pe[t / tokens_per_pos, col_off + c])
+// ------------------------------------------------------------------------------------------------
+__global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ table, const long long* __restrict__ ids,
+                                 const __nv_bfloat16* __restrict__ pe, long long ld_pe, int tokens_per_pos,
+                                 __nv_bfloat16* __restrict__ out, long long ld_out, int col_off, int T, int Ds, int D,
+                                 float scale, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset) {
+  const int per_row = Ds / 8;
+  const long long total = (long long)T * per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / per_row), c = (int)(i % per_row) * 8;
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(table + (size_t)ids[t] * Ds + c), v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] *= scale;
+    if (pe) {
+      float p[8];
+      unpack8(*reinterpret_cast<const uint4*>(pe + (size_t)(t / tokens_per_pos) * ld_pe + col_off + c), p);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] += p[k];
+    }
+    if (thresh) {
+      bool kp[8];
+      keep8(seed, offset, (uint64_t)t * D + col_off + c, thresh, kp);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = kp[k] ? v[k] * drop_scale : 0.f;
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * ld_out + col_off + c) = pack8(v);
+  }
+}
+// Scatter-add of the output gradient into a (zeroed or incoming) table-shard gradient [V, Ds].
+__global__ void embed_bwd_kernel(__nv_bfloat16* __restrict__ gtable, const long long* __restrict__ ids,
+                                 const __nv_bfloat16* __restrict__ dy, long long ld_dy, int col_off, int T, int Ds,
+                                 int D, float scale, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset) {
+  const int per_row = Ds / 8;
+  const long long total = (long long)T * per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / per_row), c = (int)(i % per_row) * 8;
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(dy + (size_t)t * ld_dy + col_off + c), v);
+    if (thresh) {
+      bool kp[8];
+      keep8(seed, offset, (uint64_t)t * D + col_off + c, thresh, kp);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = kp[k] ? v[k] * drop_scale : 0.f;
+    }
+    __nv_bfloat162* g = reinterpret_cast<__nv_bfloat162*>(gtable + (size_t)ids[t] * Ds + c);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) atomicAdd(g + k, __floats2bfloat162_rn(v[2 * k] * scale, v[2 * k + 1] * scale));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Short-sequence attention (S <= 128, head_dim 64) on packed projections.
+// qkv: [T, 3*D] with T = S*B tokens (token = s*B + b). The projection comes out of a column-rotated
+// linear, so its columns are grouped per shard: shard j holds [q_j | k_j | v_j], each D/nshard wide.
+// out: [T, D], column = head*64 + d. One block per (batch, head).
+// ------------------------------------------------------------------------------------------------
+constexpr int kHd = 64;
+__device__ __forceinline__ int qkv_col(int head, int which, int D, int nshard, int heads) {
+  const int hps = heads / nshard;  // heads per shard
+  const int j = head / hps, hl = head % hps;
+  return j * (3 * (D / nshard)) + which * (D / nshard) + hl * kHd;
+}
+
+__global__ void attn_small_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out, int S,
+                                      int B, int heads, int nshard, int causal, float sm_scale, uint32_t thresh,
+                                      float drop_scale, uint64_t seed, uint64_t offset) {
+  extern __shared__ float smf[];
+  const int D = heads * kHd;
+  const int b = blockIdx.x / heads, h = blockIdx.x % heads;
+  float* q = smf;                 // [S][65]
+  float* k = q + S * 65;
+  float* v = k + S * 65;
+  float* p = v + S * 65;          // [S][S+1]
+  const int cq = qkv_col(h, 0, D, nshard, heads), ck = qkv_col(h, 1, D, nshard, heads), cv = qkv_col(h, 2, D, nshard, heads);
+  for (int i = threadIdx.x; i < S * 8; i += blockDim.x) {
+    const int s = i / 8, c = (i % 8) * 8;
+    const size_t rowp = (size_t)(s * B + b) * (3 * D);
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(qkv + rowp + cq + c), f);
+    for (int e = 0; e < 8; ++e) q[s * 65 + c + e] = f[e] * sm_scale;
+    unpack8(*reinterpret_cast<const uint4*>(qkv + rowp + ck + c), f);
+    for (int e = 0; e < 8; ++e) k[s * 65 + c + e] = f[e];
+    unpack8(*reinterpret_cast<const uint4*>(qkv + rowp + cv + c), f);
+    for (int e = 0; e < 8; ++e) v[s * 65 + c + e] = f[e];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) {
+    const int r = i / S, c = i % S;
+    float acc = -INFINITY;
+    if (!causal || c <= r) {
+      acc = 0.f;
+#pragma unroll 16
+      for (int e = 0; e < kHd; ++e) acc += q[r * 65 + e] * k[c * 65 + e];
+    }
+    p[r * (S + 1) + c] = acc;
+  }
+  __syncthreads();
+  // softmax per row: one warp per row
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int r = warp; r < S; r += nw) {
+    float mx = -INFINITY;
+    for (int c = lane; c < S; c += 32) mx = fmaxf(mx, p[r * (S + 1) + c]);
+    mx = warp_max(mx);
+    float se = 0.f;
+    for (int c = lane; c < S; c += 32) {
+      float e = __expf(p[r * (S + 1) + c] - mx);
+      p[r * (S + 1) + c] = e;
+      se += e;
+    }
+    se = warp_sum(se);
+    const float inv = 1.f / se;
+    for (int c = lane; c < S; c += 32) {
+      float pv = p[r * (S + 1) + c] * inv;
+      if (thresh) {
+        const uint64_t e = ((uint64_t)blockIdx.x * S + r) * S + c;
+        pv = dropout_keep(seed, offset, e, thresh) ? pv * drop_scale : 0.f;
+      }
+      p[r * (S + 1) + c] = pv;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < S * kHd; i += blockDim.x) {
+    const int r = i / kHd, e = i % kHd;
+    float acc = 0.f;
+    const int lim = causal ? r + 1 : S;
+    for (int c = 0; c < lim; ++c) acc += p[r * (S + 1) + c] * v[c * 65 + e];
+    out[(size_t)(r * B + b) * D + h * kHd + e] = __float2bfloat16(acc);
+  }
+}
+
+__global__ void attn_small_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ dout,
+                                      __nv_bfloat16* __restrict__ dqkv, int S, int B, int heads, int nshard,
+                                      int causal, float sm_scale, uint32_t thresh, float drop_scale, uint64_t seed,
+                                      uint64_t offset) {
+  extern __shared__ float smf[];
+  const int D = heads * kHd;
+  const int b = blockIdx.x / heads, h = blockIdx.x % heads;
+  float* q = smf;                 // [S][65] (pre-scaled)
+  float* k = q + S * 65;
+  float* v = k + S * 65;
+  float* go = v + S * 65;         // dO
+  float* p = go + S * 65;         // [S][S+1] softmax probabilities (no dropout)
+  float* ds = p + S * (S + 1);    // [S][S+1] dP then dS
+  const int cq = qkv_col(h, 0, D, nshard, heads), ck = qkv_col(h, 1, D, nshard, heads), cv = qkv_col(h, 2, D, nshard, heads);
+  for (int i = threadIdx.x; i < S * 8; i += blockDim.x) {
+    const int s = i / 8, c = (i % 8) * 8;
+    const size_t rowp = (size_t)(s * B + b) * (3 * D);
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(qkv + rowp + cq + c), f);
+    for (int e = 0; e < 8; ++e) q[s * 65 + c + e] = f[e] * sm_scale;
+    unpack8(*reinterpret_cast<const uint4*>(qkv + rowp + ck + c), f);
+    for (int e = 0; e < 8; ++e) k[s * 65 + c + e] = f[e];
+    unpack8(*reinterpret_cast<const uint4*>(qkv + rowp + cv + c), f);
+    for (int e = 0; e < 8; ++e) v[s * 65 + c + e] = f[e];
+    unpack8(*reinterpret_cast<const uint4*>(dout + (size_t)(s * B + b) * D + h * kHd + c), f);
+    for (int e = 0; e < 8; ++e) go[s * 65 + c + e] = f[e];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) {
+    const int r = i / S, c = i % S;
+    float acc = -INFINITY, dp = 0.f;
+    if (!causal || c <= r) {
+      acc = 0.f;
+#pragma unroll 16
+      for (int e = 0; e < kHd; ++e) {
+        acc += q[r * 65 + e] * k[c * 65 + e];
+        dp += go[r * 65 + e] * v[c * 65 + e];
+      }
+    }
+    p[r * (S + 1) + c] = acc;
+    ds[r * (S + 1) + c] = dp;   // dP of the dropped probabilities
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int r = warp; r < S; r += nw) {
+    float mx = -INFINITY;
+    for (int c = lane; c < S; c += 32) mx = fmaxf(mx, p[r * (S + 1) + c]);
+    mx = warp_max(mx);
+    float se = 0.f;
+    for (int c = lane; c < S; c += 32) {
+      float e = __expf(p[r * (S + 1) + c] - mx);
+      p[r * (S + 1) + c] = e;
+      se += e;
+    }
+    se = warp_sum(se);
+    const float inv = 1.f / se;
+    float dot = 0.f;
+    for (int c = lane; c < S; c += 32) {
+      const float pv = p[r * (S + 1) + c] * inv;
+      float m = 1.f;
+      if (thresh) {
+        const uint64_t e = ((uint64_t)blockIdx.x * S + r) * S + c;
+        m = dropout_keep(seed, offset, e, thresh) ? drop_scale : 0.f;
+      }
+      const float dpv = ds[r * (S + 1) + c] * m;  // gradient wrt the un-dropped probability
+      p[r * (S + 1) + c] = pv;
+      ds[r * (S + 1) + c] = dpv;
+      dot += dpv * pv;
+    }
+    dot = warp_sum(dot);
+    for (int c = lane; c < S; c += 32) {
+      const float pv = p[r * (S + 1) + c];
+      const float dsv = pv * (ds[r * (S + 1) + c] - dot);
+      // keep the dropped probability in p for dV
+      float m = 1.f;
+      if (thresh) {
+        const uint64_t e = ((uint64_t)blockIdx.x * S + r) * S + c;
+        m = dropout_keep(seed, offset, e, thresh) ? drop_scale : 0.f;
+      }
+      p[r * (S + 1) + c] = pv * m;
+      ds[r * (S + 1) + c] = dsv;
+    }
+  }
+  __syncthreads();
+  // dQ = dS K * scale ; dK = dS^T Q(pre-scaled) ; dV = Pd^T dO
+  for (int i = threadIdx.x; i < S * kHd; i += blockDim.x) {
+    const int r = i / kHd, e = i % kHd;
+    float dq = 0.f, dk = 0.f, dv = 0.f;
+    for (int c = 0; c < S; ++c) {
+      dq += ds[r * (S + 1) + c] * k[c * 65 + e];
+      dk += ds[c * (S + 1) + r] * q[c * 65 + e];
+      dv += p[c * (S + 1) + r] * go[c * 65 + e];
+    }
+    const size_t rowp = (size_t)(r * B + b) * (3 * D);
+    dqkv[rowp + cq + e] = __float2bfloat16(dq * sm_scale);
+    dqkv[rowp + ck + e] = __float2bfloat16(dk);
+    dqkv[rowp + cv + e] = __float2bfloat16(dv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Column sums of a bf16 matrix [M, N] (pitch ld) into fp32 out[N] (must be zeroed by the caller).
+// ------------------------------------------------------------------------------------------------
+__global__ void colsum_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N, float* __restrict__ out,
+                              int rows_per_block) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= N) return;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(M, r0 + rows_per_block);
+  float a0 = 0.f, a1 = 0.f;
+  for (int r = r0; r < r1; ++r) {
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(x + (size_t)r * ld + c);
+    a0 += bf16_lo(u);
+    a1 += bf16_hi(u);
+  }
+  atomicAdd(out + c, a0);
+  atomicAdd(out + c + 1, a1);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Multi-tensor Adam / AdamW with optional gradient value clipping.
+// ------------------------------------------------------------------------------------------------
+__global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int* __restrict__ block_start, int ntensors,
+                            const long long* __restrict__ step_ptr, float lr, float beta1, float beta2, float eps,
+                            float weight_decay, int adamw, float clip_value, float grad_scale) {
+  // locate the tensor this block works on
+  int lo = 0, hi = ntensors - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (block_start[mid] <= (int)blockIdx.x) lo = mid; else hi = mid - 1;
+  }
+  const RtpAdamTensor t = tensors[lo];
+  const long long step = *step_ptr;
+  const float bc1 = 1.f - powf(beta1, (float)step);
+  const float bc2 = 1.f - powf(beta2, (float)step);
+  const float step_size = lr * t.lr_mult / bc1;
+  const float inv_sqrt_bc2 = rsqrtf(bc2);
+  const long long base = (long long)((int)blockIdx.x - block_start[lo]) * (blockDim.x * 8);
+  const long long i0 = base + threadIdx.x * 8;
+  if (i0 >= t.n) return;
+  const int cnt = (int)min((long long)8, t.n - i0);
+  __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(t.p) + i0;
+  const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(t.g) + i0;
+  float pv[8], gv[8], mv[8], vv[8];
+  const bool vec = cnt == 8 && ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15) == 0;
+  if (vec) {
+    unpack8(*reinterpret_cast<const uint4*>(p), pv);
+    unpack8(*reinterpret_cast<const uint4*>(g), gv);
+  } else {
+    for (int i = 0; i < cnt; ++i) { pv[i] = __bfloat162float(p[i]); gv[i] = __bfloat162float(g[i]); }
+  }
+  if (t.state_fp32) {
+    float* m = reinterpret_cast<float*>(t.m) + i0;
+    float* v = reinterpret_cast<float*>(t.v) + i0;
+    for (int i = 0; i < cnt; ++i) { mv[i] = m[i]; vv[i] = v[i]; }
+  } else {
+    const __nv_bfloat16* m = reinterpret_cast<const __nv_bfloat16*>(t.m) + i0;
+    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(t.v) + i0;
+    for (int i = 0; i < cnt; ++i) { mv[i] = __bfloat162float(m[i]); vv[i] = __bfloat162float(v[i]); }
+  }
+  for (int i = 0; i < cnt; ++i) {
+    float gg = gv[i] * grad_scale;
+    if (clip_value > 0.f) gg = fminf(fmaxf(gg, -clip_value), clip_value);
+    if (weight_decay != 0.f) {
+      if (adamw) pv[i] *= 1.f - lr * t.lr_mult * weight_decay; else gg += weight_decay * pv[i];
+    }
+    mv[i] = beta1 * mv[i] + (1.f - beta1) * gg;
+    vv[i] = beta2 * vv[i] + (1.f - beta2) * gg * gg;
+    pv[i] -= step_size * mv[i] / (sqrtf(vv[i]) * inv_sqrt_bc2 + eps);
+  }
+  if (vec) *reinterpret_cast<uint4*>(p) = pack8(pv);
+  else for (int i = 0; i < cnt; ++i) p[i] = __float2bfloat16(pv[i]);
+  if (t.state_fp32) {
+    float* m = reinterpret_cast<float*>(t.m) + i0;
+    float* v = reinterpret_cast<float*>(t.v) + i0;
+    for (int i = 0; i < cnt; ++i) { m[i] = mv[i]; v[i] = vv[i]; }
+  } else {
+    __nv_bfloat16* m = reinterpret_cast<__nv_bfloat16*>(t.m) + i0;
+    __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(t.v) + i0;
+    for (int i = 0; i < cnt; ++i) { m[i] = __float2bfloat16(mv[i]); v[i] = __float2bfloat16(vv[i]); }
+  }
+}
+
+// out = a + b (bf16), n % 8 == 0 handled vectorised, tail scalar
+__global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, long long n) {
+  const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
+  if (i + 8 <= n) {
+    float x[8], y[8];
+    unpack8(*reinterpret_cast<const uint4*>(a + i), x);
+    unpack8(*reinterpret_cast<const uint4*>(b + i), y);
+    for (int k = 0; k < 8; ++k) x[k] += y[k];
+    *reinterpret_cast<uint4*>(out + i) = pack8(x);
+  } else {
+    for (long long k = i; k < n; ++k) out[k] = __float2bfloat16(__bfloat162float(a[k]) + __bfloat162float(b[k]));
+  }
+}
+// fp32 vector -> bf16 (used for LayerNorm parameter gradients accumulated in fp32)
+__global__ void cast_f32_bf16_kernel(const float* in, __nv_bfloat16* out, long long n, float scale) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16(in[i] * scale);
+}
+// sum of fp32 vector * scale -> out[0] (single block)
+__global__ void sum_kernel(const float* in, float* out, int n, float scale) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += in[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) out[0] = s * scale;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* rtp_kernels_last_error(void) { return k_err.c_str(); }
+
+int rtp_norm_fwd(const void* x, const void* sub, const void* gamma, const void* beta, void* h_out, void* y,
+                 float* mean, float* rstd, int M, int D, float eps, int rms, float drop_p, unsigned long long seed,
+                 unsigned long long offset, void* stream) {
+  if (D % 8) { k_err = "norm: D must be a multiple of 8"; return -1; }
+  const int threads = D >= 2048 ? 256 : 128;
+  const int grid = M < 148 * 8 ? M : 148 * 8;
+  const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
+  norm_fwd_kernel<<<grid, threads, D * sizeof(float), (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)sub, (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta,
+      (__nv_bfloat16*)h_out, (__nv_bfloat16*)y, mean, rstd, M, D, eps, rms, host_thresh(drop_p), ds, seed, offset);
+  LAUNCH_CHECK("norm_fwd");
+  return 0;
+}
+int rtp_norm_bwd(const void* dy, const void* h, const void* gamma, const float* mean, const float* rstd, void* dx,
+                 void* dsub, float* dgamma, float* dbeta, int M, int D, int rms, float drop_p,
+                 unsigned long long seed, unsigned long long offset, const void* dres, void* stream) {
+  if (D % 8) { k_err = "norm: D must be a multiple of 8"; return -1; }
+  const int threads = D >= 2048 ? 256 : 128;
+  int grid = 148 * 2;
+  if (grid > M) grid = M;
+  const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
+  const size_t smem = 2 * (size_t)D * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(norm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return kfail("norm_bwd attr", e);
+  }
+  norm_bwd_kernel<<<grid, threads, smem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)gamma, mean, rstd, (__nv_bfloat16*)dx,
+      (__nv_bfloat16*)dsub, dgamma, dbeta, M, D, rms, host_thresh(drop_p), ds, seed, offset,
+      (const __nv_bfloat16*)dres);
+  LAUNCH_CHECK("norm_bwd");
+  return 0;
+}
+int rtp_cross_entropy(void* logits, long long ld, const long long* target, float* loss, int M, int V, float grad_scale,
+                      long long ignore_index, int write_grad, void* stream) {
+  if (V % 8 || ld % 8) { k_err = "cross_entropy: V and ld must be multiples of 8"; return -1; }
+  const int grid = M < 148 * 8 ? M : 148 * 8;
+  ce_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits, ld, target, loss, M, V, grad_scale,
+                                                    ignore_index, write_grad);
+  LAUNCH_CHECK("cross_entropy");
+  return 0;
+}
+int rtp_embed_fwd(const void* table, const long long* ids, const void* pe, long long ld_pe, int tokens_per_pos,
+                  void* out, long long ld_out, int col_off, int T, int Ds, int D, float scale, float drop_p,
+                  unsigned long long seed, unsigned long long offset, void* stream) {
+  if (Ds % 8 || col_off % 8 || ld_out % 8) { k_err = "embed: widths must be multiples of 8"; return -1; }
+  const long long total = (long long)T * (Ds / 8);
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
+  embed_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)table, ids, (const __nv_bfloat16*)pe,
+                                                           ld_pe, tokens_per_pos, (__nv_bfloat16*)out, ld_out, col_off,
+                                                           T, Ds, D, scale, host_thresh(drop_p), ds, seed, offset);
+  LAUNCH_CHECK("embed_fwd");
+  return 0;
+}
+int rtp_embed_bwd(void* gtable, const long long* ids, const void* dy, long long ld_dy, int col_off, int T, int Ds,
+                  int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset, void* stream) {
+  if (Ds % 8 || col_off % 8 || ld_dy % 8) { k_err = "embed: widths must be multiples of 8"; return -1; }
+  const long long total = (long long)T * (Ds / 8);
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
+  embed_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)gtable, ids, (const __nv_bfloat16*)dy, ld_dy,
+                                                           col_off, T, Ds, D, scale, host_thresh(drop_p), ds, seed,
+                                                           offset);
+  LAUNCH_CHECK("embed_bwd");
+  return 0;
+}
+static size_t attn_smem(int S, bool bwd) {
+  size_t f = (size_t)(bwd ? 4 : 3) * S * 65 + (size_t)(bwd ? 2 : 1) * S * (S + 1);
+  return f * sizeof(float);
+}
+int rtp_attn_small_fwd(const void* qkv, void* out, int S, int B, int heads, int nshard, int causal, float sm_scale,
+                       float drop_p, unsigned long long seed, unsigned long long offset, void* stream) {
+  if (S > 128 || heads % nshard) { k_err = "attn_small: S must be <= 128 and heads divisible by shards"; return -1; }
+  const size_t smem = attn_smem(S, false);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attn_small_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return kfail("attn fwd attr", e);
+  }
+  const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
+  attn_small_fwd_kernel<<<B * heads, 128, smem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, S, B, heads, nshard, causal, sm_scale, host_thresh(drop_p), ds,
+      seed, offset);
+  LAUNCH_CHECK("attn_small_fwd");
+  return 0;
+}
+int rtp_attn_small_bwd(const void* qkv, const void* dout, void* dqkv, int S, int B, int heads, int nshard, int causal,
+                       float sm_scale, float drop_p, unsigned long long seed, unsigned long long offset, void* stream) {
+  if (heads % nshard) { k_err = "attn_small: heads must be divisible by shards"; return -1; }
+  const size_t smem = attn_smem(S, true);
+  if (smem > 227 * 1024) { k_err = "attn_small backward: sequence too long for shared memory (S <= 96)"; return -1; }
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attn_small_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return kfail("attn bwd attr", e);
+  }
+  const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
+  attn_small_bwd_kernel<<<B * heads, 128, smem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dqkv, S, B, heads, nshard, causal,
+      sm_scale, host_thresh(drop_p), ds, seed, offset);
+  LAUNCH_CHECK("attn_small_bwd");
+  return 0;
+}
+int rtp_colsum(const void* x, long long ld, int M, int N, float* out, void* stream) {
+  if (N % 2 || ld % 2) { k_err = "colsum: N and ld must be even"; return -1; }
+  cudaError_t e = cudaMemsetAsync(out, 0, (size_t)N * sizeof(float), (cudaStream_t)stream);
+  if (e != cudaSuccess) return kfail("colsum memset", e);
+  const int rows_per_block = 64;
+  dim3 grid((N / 2 + 127) / 128, (M + rows_per_block - 1) / rows_per_block);
+  colsum_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ld, M, N, out, rows_per_block);
+  LAUNCH_CHECK("colsum");
+  return 0;
+}
+int rtp_adam(const RtpAdamTensor* tensors_dev, const int* block_start_dev, int ntensors, int total_blocks,
+             const long long* step_dev, float lr, float beta1, float beta2, float eps, float weight_decay, int adamw,
+             float clip_value, float grad_scale, void* stream) {
+  if (ntensors <= 0 || total_blocks <= 0) return 0;
+  adam_kernel<<<total_blocks, 256, 0, (cudaStream_t)stream>>>(tensors_dev, block_start_dev, ntensors, step_dev, lr,
+                                                              beta1, beta2, eps, weight_decay, adamw, clip_value,
+                                                              grad_scale);
+  LAUNCH_CHECK("adam");
+  return 0;
+}
+int rtp_add(const void* a, const void* b, void* out, long long n, void* stream) {
+  const long long blocks = (n + 2047) / 2048;
+  add_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+                                                                 (__nv_bfloat16*)out, n);
+  LAUNCH_CHECK("add");
+  return 0;
+}
+int rtp_cast_f32_bf16(const float* in, void* out, long long n, float scale, void* stream) {
+  cast_f32_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(in, (__nv_bfloat16*)out, n, scale);
+  LAUNCH_CHECK("cast");
+  return 0;
+}
+int rtp_sum_f32(const float* in, float* out, int n, float scale, void* stream) {
+  sum_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(in, out, n, scale);
+  LAUNCH_CHECK("sum");
+  return 0;
+}
+
+}  // extern "C"

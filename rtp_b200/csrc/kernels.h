@@ -1,0 +1,46 @@
+// C ABI of the memory-bound kernels (see kernels.cu). Same conventions as api.h.
+#pragma once
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct {
+  void* p;        // bf16 parameter
+  const void* g;  // bf16 gradient
+  void* m;        // first moment (fp32 or bf16)
+  void* v;        // second moment
+  long long n;
+  float lr_mult;  // 1/N for biases that are stored as b/N on every rank
+  int state_fp32;
+} RtpAdamTensor;
+
+const char* rtp_kernels_last_error(void);
+int rtp_norm_fwd(const void* x, const void* sub, const void* gamma, const void* beta, void* h_out, void* y,
+                 float* mean, float* rstd, int M, int D, float eps, int rms, float drop_p, unsigned long long seed,
+                 unsigned long long offset, void* stream);
+int rtp_norm_bwd(const void* dy, const void* h, const void* gamma, const float* mean, const float* rstd, void* dx,
+                 void* dsub, float* dgamma, float* dbeta, int M, int D, int rms, float drop_p,
+                 unsigned long long seed, unsigned long long offset, const void* dres, void* stream);
+int rtp_cross_entropy(void* logits, long long ld, const long long* target, float* loss, int M, int V, float grad_scale,
+                      long long ignore_index, int write_grad, void* stream);
+int rtp_embed_fwd(const void* table, const long long* ids, const void* pe, long long ld_pe, int tokens_per_pos,
+                  void* out, long long ld_out, int col_off, int T, int Ds, int D, float scale, float drop_p,
+                  unsigned long long seed, unsigned long long offset, void* stream);
+int rtp_embed_bwd(void* gtable, const long long* ids, const void* dy, long long ld_dy, int col_off, int T, int Ds,
+                  int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset, void* stream);
+int rtp_attn_small_fwd(const void* qkv, void* out, int S, int B, int heads, int nshard, int causal, float sm_scale,
+                       float drop_p, unsigned long long seed, unsigned long long offset, void* stream);
+int rtp_attn_small_bwd(const void* qkv, const void* dout, void* dqkv, int S, int B, int heads, int nshard, int causal,
+                       float sm_scale, float drop_p, unsigned long long seed, unsigned long long offset, void* stream);
+int rtp_colsum(const void* x, long long ld, int M, int N, float* out, void* stream);
+int rtp_adam(const RtpAdamTensor* tensors_dev, const int* block_start_dev, int ntensors, int total_blocks,
+             const long long* step_dev, float lr, float beta1, float beta2, float eps, float weight_decay, int adamw,
+             float clip_value, float grad_scale, void* stream);
+int rtp_add(const void* a, const void* b, void* out, long long n, void* stream);
+int rtp_cast_f32_bf16(const float* in, void* out, long long n, float scale, void* stream);
+int rtp_sum_f32(const float* in, float* out, int n, float scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

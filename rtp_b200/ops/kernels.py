@@ -1,0 +1,167 @@
+"""ctypes front-ends of the memory-bound sm_100a kernels (norms, cross-entropy, embedding, short-sequence
+attention, column sums, Adam). Raw functions on contiguous bf16 CUDA tensors; autograd wrappers live in
+``rtp_b200.ops.functional``."""
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+_declared = False
+
+
+class AdamTensor(C.Structure):
+    _fields_ = [("p", C.c_void_p), ("g", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
+                ("n", C.c_longlong), ("lr_mult", C.c_float), ("state_fp32", C.c_int)]
+
+
+def _L():
+    global _declared
+    L = _lib.lib()
+    if not _declared:
+        vp, ll, i, f, ull = C.c_void_p, C.c_longlong, C.c_int, C.c_float, C.c_ulonglong
+        L.rtp_kernels_last_error.restype = C.c_char_p
+        L.rtp_norm_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, f, i, f, ull, ull, vp]
+        L.rtp_norm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, f, ull, ull, vp, vp]
+        L.rtp_cross_entropy.argtypes = [vp, ll, vp, vp, i, i, f, ll, i, vp]
+        L.rtp_embed_fwd.argtypes = [vp, vp, vp, ll, i, vp, ll, i, i, i, i, f, f, ull, ull, vp]
+        L.rtp_embed_bwd.argtypes = [vp, vp, vp, ll, i, i, i, i, f, f, ull, ull, vp]
+        L.rtp_attn_small_fwd.argtypes = [vp, vp, i, i, i, i, i, f, f, ull, ull, vp]
+        L.rtp_attn_small_bwd.argtypes = [vp, vp, vp, i, i, i, i, i, f, f, ull, ull, vp]
+        L.rtp_colsum.argtypes = [vp, ll, i, i, vp, vp]
+        L.rtp_adam.argtypes = [vp, vp, i, i, vp, f, f, f, f, f, i, f, f, vp]
+        L.rtp_add.argtypes = [vp, vp, vp, ll, vp]
+        L.rtp_cast_f32_bf16.argtypes = [vp, vp, ll, f, vp]
+        L.rtp_sum_f32.argtypes = [vp, vp, i, f, vp]
+        _declared = True
+    return L
+
+
+def _check(rc, what):
+    if rc != 0:
+        msg = _L().rtp_kernels_last_error()
+        raise RuntimeError(f"{what} failed: {msg.decode() if msg else rc}")
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def norm_fwd(x, sub, gamma, beta, *, eps=1e-5, rms=False, drop_p=0.0, seed=0, offset=0, save_h=True):
+    """h = x + dropout(sub); y = LayerNorm/RMSNorm(h). Returns (y, h, mean, rstd)."""
+    M, D = x.shape
+    y = torch.empty_like(x)
+    h = torch.empty_like(x) if save_h else None
+    mean = None if rms else torch.empty(M, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+    _check(_L().rtp_norm_fwd(_p(x), _p(sub), _p(gamma), _p(beta), _p(h), _p(y), _p(mean), _p(rstd), M, D, eps,
+                             int(rms), float(drop_p), seed, offset, _lib.stream_ptr()), "norm_fwd")
+    return y, h, mean, rstd
+
+
+def norm_bwd(dy, h, gamma, mean, rstd, *, rms=False, has_beta=True, drop_p=0.0, seed=0, offset=0, want_dsub=True,
+             dres=None):
+    """Returns (dx, dsub, dgamma_fp32, dbeta_fp32)."""
+    M, D = dy.shape
+    dx = torch.empty_like(dy)
+    dsub = torch.empty_like(dy) if want_dsub else None
+    dgamma = torch.zeros(D, dtype=torch.float32, device=dy.device)
+    dbeta = torch.zeros(D, dtype=torch.float32, device=dy.device) if has_beta else None
+    _check(_L().rtp_norm_bwd(_p(dy), _p(h), _p(gamma), _p(mean), _p(rstd), _p(dx), _p(dsub), _p(dgamma), _p(dbeta),
+                             M, D, int(rms), float(drop_p), seed, offset, _p(dres), _lib.stream_ptr()), "norm_bwd")
+    return dx, dsub, dgamma, dbeta
+
+
+def cross_entropy_(logits, target, *, grad_scale=1.0, ignore_index=-100, write_grad=True):
+    """Per-row loss (fp32 [M]); overwrites ``logits`` with ``grad_scale * (softmax - onehot)``."""
+    M, V = logits.shape
+    loss = torch.empty(M, dtype=torch.float32, device=logits.device)
+    _check(_L().rtp_cross_entropy(_p(logits), logits.stride(0), _p(target), _p(loss), M, V, float(grad_scale),
+                                  int(ignore_index), int(write_grad), _lib.stream_ptr()), "cross_entropy")
+    return loss
+
+
+def embed_fwd(table, ids, out, col_off, *, D, scale=1.0, pe=None, tokens_per_pos=1, drop_p=0.0, seed=0, offset=0):
+    T = ids.numel()
+    Ds = table.shape[1]
+    _check(_L().rtp_embed_fwd(_p(table), _p(ids), _p(pe), pe.stride(0) if pe is not None else 0, tokens_per_pos,
+                              _p(out), out.stride(0), col_off, T, Ds, D, float(scale), float(drop_p), seed, offset,
+                              _lib.stream_ptr()), "embed_fwd")
+    return out
+
+
+def embed_bwd(gtable, ids, dy, col_off, *, D, scale=1.0, drop_p=0.0, seed=0, offset=0):
+    T = ids.numel()
+    Ds = gtable.shape[1]
+    _check(_L().rtp_embed_bwd(_p(gtable), _p(ids), _p(dy), dy.stride(0), col_off, T, Ds, D, float(scale),
+                              float(drop_p), seed, offset, _lib.stream_ptr()), "embed_bwd")
+    return gtable
+
+
+def attn_small_fwd(qkv, S, B, heads, *, nshard=1, causal=True, drop_p=0.0, seed=0, offset=0, sm_scale=None):
+    D = heads * 64
+    out = torch.empty(S * B, D, dtype=qkv.dtype, device=qkv.device)
+    sc = sm_scale if sm_scale is not None else 64 ** -0.5
+    _check(_L().rtp_attn_small_fwd(_p(qkv), _p(out), S, B, heads, nshard, int(causal), sc, float(drop_p), seed, offset,
+                                   _lib.stream_ptr()), "attn_small_fwd")
+    return out
+
+
+def attn_small_bwd(qkv, dout, S, B, heads, *, nshard=1, causal=True, drop_p=0.0, seed=0, offset=0, sm_scale=None):
+    dqkv = torch.empty_like(qkv)
+    sc = sm_scale if sm_scale is not None else 64 ** -0.5
+    _check(_L().rtp_attn_small_bwd(_p(qkv), _p(dout), _p(dqkv), S, B, heads, nshard, int(causal), sc, float(drop_p),
+                                   seed, offset, _lib.stream_ptr()), "attn_small_bwd")
+    return dqkv
+
+
+def colsum(x, out=None):
+    M, N = x.shape
+    if out is None:
+        out = torch.empty(N, dtype=torch.float32, device=x.device)
+    _check(_L().rtp_colsum(_p(x), x.stride(0), M, N, _p(out), _lib.stream_ptr()), "colsum")
+    return out
+
+
+def add(a, b, out=None):
+    if out is None:
+        out = torch.empty_like(a)
+    _check(_L().rtp_add(_p(a), _p(b), _p(out), a.numel(), _lib.stream_ptr()), "add")
+    return out
+
+
+def cast_f32_bf16(src, dst, scale=1.0):
+    _check(_L().rtp_cast_f32_bf16(_p(src), _p(dst), src.numel(), float(scale), _lib.stream_ptr()), "cast")
+    return dst
+
+
+def sum_f32(src, out, scale=1.0):
+    _check(_L().rtp_sum_f32(_p(src), _p(out), src.numel(), float(scale), _lib.stream_ptr()), "sum")
+    return out
+
+
+class AdamPlan:
+    """Device-resident descriptor table for the multi-tensor Adam kernel (built once, reused every step)."""
+
+    BLOCK_ELEMS = 2048
+
+    def __init__(self, entries, device):
+        # entries: list of (p, g, m, v, lr_mult)
+        arr = (AdamTensor * len(entries))()
+        starts = []
+        total = 0
+        self.keep = entries
+        for k, (p, g, m, v, lr_mult) in enumerate(entries):
+            arr[k].p, arr[k].g, arr[k].m, arr[k].v = p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr()
+            arr[k].n, arr[k].lr_mult, arr[k].state_fp32 = p.numel(), float(lr_mult), int(m.dtype == torch.float32)
+            starts.append(total)
+            total += (p.numel() + self.BLOCK_ELEMS - 1) // self.BLOCK_ELEMS
+        raw = bytes(arr)
+        self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
+        self.starts = torch.tensor(starts, dtype=torch.int32, device=device)
+        self.n = len(entries)
+        self.total_blocks = total
+
+    def step(self, step_dev, lr, beta1, beta2, eps, weight_decay=0.0, adamw=False, clip_value=0.0, grad_scale=1.0):
+        _check(_L().rtp_adam(_p(self.table), _p(self.starts), self.n, self.total_blocks, _p(step_dev), lr, beta1,
+                             beta2, eps, weight_decay, int(adamw), clip_value, grad_scale, _lib.stream_ptr()), "adam")

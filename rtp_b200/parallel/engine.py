@@ -1,0 +1,171 @@
+"""Fused rotation engine: peer-mapped workspace + launch of the sm_100a rotation kernels.
+
+One engine exists per (process, ring).  It owns a ``cudaMalloc``'d workspace — flag block, two weight
+slots and two travelling-gradient slots — whose CUDA-IPC handle is exchanged once over the ring's
+process group; afterwards every kernel launch only passes raw pointers.  The kernels themselves push
+weight shards from their owner's home buffer into the consumer's slot with NVLink P2P stores and
+synchronise through monotonically increasing counters (see csrc/gemm_kernel.cuh), so there is no NCCL
+send/recv, no copy kernel and no host involvement between rotation steps.
+"""
+import ctypes as C
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib, kernels as K
+from .context import RingContext
+
+_engines: Dict[object, "FusedEngine"] = {}
+_reserved_bytes = 0
+DEFAULT_TIMEOUT_NS = 2_000_000_000
+
+
+def reserve_shard_bytes(nbytes: int):
+    """Rotated modules announce their shard size at construction so that the workspace, which is
+    allocated at the first fused call, can hold the largest one."""
+    global _reserved_bytes
+    _reserved_bytes = max(_reserved_bytes, int(nbytes))
+
+
+def _round_up(x, a):
+    return (x + a - 1) // a * a
+
+
+class FusedEngine:
+    def __init__(self, ctx: RingContext, slot_bytes: int, ctas: Optional[int] = None,
+                 timeout_ns: int = DEFAULT_TIMEOUT_NS):
+        L = _lib.lib()
+        self.ctx = ctx
+        self.slot_bytes = _round_up(max(slot_bytes, 256), 1 << 16)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        ws = C.c_void_p()
+        _lib.check(L.rtp_ws_create(self.slot_bytes if ctx.world > 1 else 256, C.byref(ws)), "rtp_ws_create")
+        self.ws_local = ws.value
+        self.mapped = {}
+        ptrs = [None] * ctx.world
+        ptrs[ctx.rank] = self.ws_local
+        if ctx.world > 1:
+            handle = (C.c_char * 64)()
+            _lib.check(L.rtp_ws_ipc_get(self.ws_local, handle), "rtp_ws_ipc_get")
+            gathered = [None] * ctx.world
+            dist.all_gather_object(gathered, bytes(handle), group=ctx.group)
+            for r, h in enumerate(gathered):
+                if r == ctx.rank:
+                    continue
+                out = C.c_void_p()
+                buf = C.create_string_buffer(h, 64)
+                _lib.check(L.rtp_ws_ipc_open(buf, C.byref(out)), "rtp_ws_ipc_open")
+                ptrs[r] = out.value
+                self.mapped[r] = out.value
+            dist.barrier(group=ctx.group)
+        self.ring = _lib.Ring()
+        self.ring.rank, self.ring.world = ctx.rank, ctx.world
+        for r in range(ctx.world):
+            self.ring.ws[r] = ptrs[r]
+        self.ring.slot_bytes = self.slot_bytes
+        self.ring.ctas = ctas or L.rtp_sm_count()
+        self.ring.timeout_ns = timeout_ns
+        self._host_status = C.c_ulonglong(0)
+
+    def check(self):
+        """Read the workspace status word (synchronises the stream); raise if a bounded wait expired."""
+        _lib.check(_lib.lib().rtp_ws_status(self.ws_local, C.byref(self._host_status), _lib.stream_ptr()),
+                   "rtp_ws_status")
+        v = self._host_status.value
+        if v:
+            _lib.check(_lib.lib().rtp_ws_reset(self.ws_local, _lib.stream_ptr()), "rtp_ws_reset")
+            raise _lib.RotationTimeout(_lib.STATUS_NAMES.get(v, f"status {v}"))
+
+
+def get_engine(ctx: RingContext) -> FusedEngine:
+    key = (id(ctx.group), ctx.rank, ctx.world, torch.cuda.current_device())
+    eng = _engines.get(key)
+    if eng is None:
+        eng = FusedEngine(ctx, _reserved_bytes)
+        _engines[key] = eng
+    return eng
+
+
+def check_all():
+    for e in _engines.values():
+        e.check()
+
+
+# --------------------------------------------------------------------------------------------------
+# rotated linear on the fused kernels
+# --------------------------------------------------------------------------------------------------
+def _linear_desc(module, row):
+    lay = module._layout
+    has_bias = module.linear.bias is not None
+    bias_off = lay.offset_of("bias") if has_bias else -1
+    shard_bytes = _round_up(lay.numel * 2, 16)
+    return has_bias, bias_off, shard_bytes
+
+
+def linear_fwd_raw(eng, flat, layout_info, x2d, row, in_f, out_f, act=0, drop_p=0.0, seed=0, offset=0, out=None):
+    has_bias, bias_off, shard_bytes = layout_info
+    M = x2d.shape[0]
+    y = out if out is not None else torch.empty(M, out_f, dtype=torch.bfloat16, device=x2d.device)
+    op = _lib.LinearFwd()
+    op.mode, op.M, op.in_features, op.out_features = int(row), M, in_f, out_f
+    op.home, op.bias_off, op.shard_bytes = flat.data_ptr(), bias_off, shard_bytes
+    op.x, op.ldx = x2d.data_ptr(), x2d.stride(0)
+    op.y, op.ldy = y.data_ptr(), y.stride(0)
+    op.act, op.drop_p, op.seed, op.offset = act, drop_p, seed, offset
+    _lib.check(_lib.lib().rtp_linear_fwd(C.byref(eng.ring), C.byref(op), _lib.stream_ptr()), "rtp_linear_fwd")
+    return y
+
+
+def linear_bwd_raw(eng, flat, layout_info, x2d, dy2d, row, in_f, out_f, need_dx=True, mask=None, mask_scale=1.0,
+                   grad_out=None):
+    has_bias, bias_off, shard_bytes = layout_info
+    M = x2d.shape[0]
+    gflat = grad_out if grad_out is not None else torch.empty_like(flat)
+    dx = torch.empty(M, in_f, dtype=torch.bfloat16, device=x2d.device) if need_dx else None
+    dbias = K.colsum(dy2d) if has_bias else None
+    op = _lib.LinearBwd()
+    op.mode, op.M, op.in_features, op.out_features = int(row), M, in_f, out_f
+    op.home, op.bias_off, op.shard_bytes = flat.data_ptr(), bias_off, shard_bytes
+    op.x, op.ldx = x2d.data_ptr(), x2d.stride(0)
+    op.dy, op.ldy = dy2d.data_ptr(), dy2d.stride(0)
+    if dx is not None:
+        op.dx, op.lddx = dx.data_ptr(), dx.stride(0)
+    op.grad_home = gflat.data_ptr()
+    op.dbias_full = dbias.data_ptr() if dbias is not None else None
+    if mask is not None:
+        op.mask, op.ldmask, op.mask_scale = mask.data_ptr(), mask.stride(0), mask_scale
+    _lib.check(_lib.lib().rtp_linear_bwd(C.byref(eng.ring), C.byref(op), _lib.stream_ptr()), "rtp_linear_bwd")
+    return dx, gflat
+
+
+class _FusedLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, module, row, x, *params):
+        eng = get_engine(module.ring)
+        x2d = x.reshape(-1, x.shape[-1])
+        if x2d.stride(1) != 1 or (x2d.stride(0) * 2) % 16:
+            x2d = x2d.contiguous()
+        info = _linear_desc(module, row)
+        y = linear_fwd_raw(eng, module._full_param, info, x2d, row, module.in_features, module.out_features)
+        ctx.module, ctx.row, ctx.info, ctx.eng = module, row, info, eng
+        ctx.save_for_backward(x2d)
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], module.out_features)
+
+    @staticmethod
+    def backward(ctx, dy):
+        module = ctx.module
+        (x2d,) = ctx.saved_tensors
+        dy2d = dy.reshape(-1, dy.shape[-1])
+        if not dy2d.is_contiguous():
+            dy2d = dy2d.contiguous()
+        dx, gflat = linear_bwd_raw(ctx.eng, module._full_param, ctx.info, x2d, dy2d, ctx.row, module.in_features,
+                                   module.out_features, need_dx=ctx.needs_input_grad[2])
+        module._last_flat_grad = gflat
+        views = module._layout.views(gflat)
+        return (None, None, dx.view(ctx.x_shape) if dx is not None else None, *views)
+
+
+def fused_linear(module, x, row=False):
+    return _FusedLinearFn.apply(module, row, x, *module.shard_parameters())

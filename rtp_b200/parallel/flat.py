@@ -57,6 +57,9 @@ class RotatedModule(nn.Module):
                 p.rtp_sharded = True
         self._layout = layout
         self._full_param = flat
+        if flat.is_cuda:
+            from .engine import reserve_shard_bytes
+            reserve_shard_bytes(layout.numel * flat.element_size())
 
     def _apply(self, fn, recurse=True):
         out = super()._apply(fn, recurse)

@@ -252,6 +252,9 @@ def rotated_apply(ctx: RingContext, fn: Callable, params: Sequence[torch.Tensor]
     """
     if combine not in ("cat", "sum"):
         raise ValueError(combine)
+    if inplace and owner is not None and getattr(owner, "_displaced", False):
+        raise RuntimeError("in-place rotated layer called while its shards are displaced: the backward of the "
+                           "previous grad-mode forward has not run yet (use the out-of-place layer for that)")
     needs_bwd = torch.is_grad_enabled() and (
         any(p.requires_grad for p in params)
         or any(isinstance(t, torch.Tensor) and t.requires_grad for t in inputs))
