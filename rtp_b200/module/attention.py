@@ -128,6 +128,12 @@ class ParallelMultiheadAttention(RotatedModule):
     def shard_names(self):
         return list(self._names)
 
+    def shard_spec(self):
+        kinds = {"in_proj_weight": ("qkv", 0), "in_proj_bias": ("qkv", 0), "q_proj_weight": ("split", 0),
+                 "k_proj_weight": ("split", 0), "v_proj_weight": ("split", 0), "out_proj.weight": ("split", 1),
+                 "out_proj.bias": ("sum",), "bias_k": ("split", 2), "bias_v": ("split", 2)}
+        return {f"MultiheadAttention.{n}": kinds[n] for n in self._names}
+
     @property
     def layers(self):
         return [self.MultiheadAttention] * self.world_size

@@ -46,6 +46,12 @@ class ColumnParallelConv2d(RotatedModule):
     def shard_names(self):
         return ["weight", "bias"][: len(self.shard_parameters())]
 
+    def shard_spec(self):
+        spec = {"conv.weight": ("split", 0)}
+        if self.conv.bias is not None:
+            spec["conv.bias"] = ("split", 0)
+        return spec
+
     @property
     def convs(self):
         return [self.conv] * self.world_size

@@ -54,6 +54,9 @@ class ParallelEmbedding(RotatedModule):
     def shard_names(self):
         return ["weight"]
 
+    def shard_spec(self):
+        return {"embedding.weight": ("split", 1)}
+
     @property
     def embeddings(self):
         return [self.embedding] * self.world_size

@@ -89,6 +89,18 @@ class _RotatedLinearBase(RotatedModule):
     def shard_names(self):
         return ["weight", "bias"][: len(self.shard_parameters())]
 
+    def shard_spec(self):
+        """How each registered tensor relates to the unsharded layer (used by rtp_b200.checkpoint)."""
+        if self.row:
+            spec = {"linear.weight": ("split", 1)}
+            if self.linear.bias is not None:
+                spec["linear.bias"] = ("sum",)
+        else:
+            spec = {"linear.weight": ("split", 0)}
+            if self.linear.bias is not None:
+                spec["linear.bias"] = ("split", 0)
+        return spec
+
     @property
     def linears(self):
         """The reference exposes N aliased replicas; here there is one shard module."""

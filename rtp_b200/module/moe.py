@@ -100,6 +100,9 @@ class WeightMOELayer(RotatedModule):
     def shard_names(self):
         return list(self._pnames)
 
+    def shard_spec(self):
+        return {f"experts.{n}": ("expert", self.num_local_experts) for n in self._pnames}
+
     def forward(self, *input: Tensor, **kwargs: Any) -> Tensor:
         assert len(input) == 1, "only single input Tensor supported"
         assert len(input[0].shape) == 3, "input Tensor must have dimensions: (s)equence, (t)oken, (m)odel"

@@ -117,6 +117,9 @@ class WeightTop2Gate(RotatedModule):
     def shard_names(self):
         return ["weight"]
 
+    def shard_spec(self):
+        return {"wg.weight": ("split", 0)}
+
     def logits(self, input: torch.Tensor) -> torch.Tensor:
         def fn(j, views, x):
             return F.linear(x, views[0])
