@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Headline benchmark: training throughput of the rotated transformer LM (README config of the reference:
+vocab 10240, ninp 2048, nhid 2048, nhead 32, 10 decoder layers, seq_len 32, batch 32 per GPU, dropout 0.1,
+clip 0.05, Adam lr 1e-3) in bf16 on synthetic uniform token ids with random-init weights.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework (fused sm_100a path)
+    python bench.py --impl reference --gpus N ...            # the unmodified reference from baseline/_ref
+
+For N > 1 launch one process per GPU (torchrun); RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* come from the
+environment.  Timing is on the device (CUDA events), bracketed by barrier + synchronize, max over ranks;
+rank 0 prints one JSON line.  Weak scaling: every GPU trains its own batch of 32 sequences.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+CONFIGS = {
+    # name: vocab, d_model, ffn, heads, layers, seq_len, batch per GPU, dropout, clip
+    "readme": dict(vocab=10240, ninp=2048, nhid=2048, nhead=32, nlayers=10, seq_len=32, batch=32, dropout=0.1,
+                   clip=0.05, initrange=0.1, lr=1e-3),
+    "tiny": dict(vocab=1024, ninp=256, nhid=1024, nhead=4, nlayers=2, seq_len=32, batch=8, dropout=0.1, clip=0.05,
+                 initrange=0.1, lr=1e-3),
+}
+METRIC = "tokens/s/box"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="rtp_b200", choices=["rtp_b200", "reference"])
+    ap.add_argument("--config", default="readme", choices=sorted(CONFIGS))
+    ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # clocks under load: ignore idle samples far below the busy ones
+        busy = [c for c in sm if c >= 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def setup_dist(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            # convenience: re-launch under torchrun
+            port = 29500 + os.getpid() % 2000
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", str(port)] + sys.argv
+            os.execv(sys.executable, cmd)
+        raise SystemExit(f"WORLD_SIZE={world} but --gpus {args.gpus}")
+    torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29531")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    return rank, local, world
+
+
+def synthetic_batches(cfg, n, rank, device="cpu", pin=True):
+    """n pairs (ids, targets) of shape [seq_len, batch]; targets are the inputs shifted by one token."""
+    import torch
+    g = torch.Generator().manual_seed(1000 + rank)
+    out = []
+    for _ in range(n):
+        stream = torch.randint(0, cfg["vocab"], (cfg["seq_len"] + 1, cfg["batch"]), generator=g, dtype=torch.int64)
+        ids, tgt = stream[:-1].contiguous(), stream[1:].contiguous()
+        if pin:
+            ids, tgt = ids.pin_memory(), tgt.pin_memory()
+        out.append((ids, tgt))
+    return out
+
+
+def max_over_ranks(x, world):
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def timed_loop(step_fn, batches, steps, warmup, world, flush, sync_each):
+    """Returns device milliseconds for `steps` calls of step_fn (max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    for i in range(warmup):
+        step_fn(*batches[i % len(batches)])
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        if flush is not None:
+            flush.zero_()          # write a buffer larger than L2 between iterations
+        step_fn(*batches[(warmup + i) % len(batches)])
+        if sync_each:
+            sync_each()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    return max_over_ranks(e0.elapsed_time(e1), world)
+
+
+def run_ours(args, cfg, rank, local, world):
+    import torch
+    sys.path.insert(0, ROOT)
+    from rtp_b200.models.transformer_lm_rtp import TransformerLM
+    from rtp_b200.models.fused_lm import FusedLMTrainer
+    torch.manual_seed(0)
+    dev = torch.device("cuda", local)
+    model = TransformerLM(cfg["vocab"], cfg["ninp"], cfg["nhead"], cfg["nhid"], cfg["dropout"], cfg["initrange"],
+                          cfg["nlayers"], world, rank)
+    with torch.no_grad():
+        for p in model.parameters():     # random init of every weight, U(-initrange, initrange); LayerNorm stays 1/0
+            if p.dim() > 1:
+                p.uniform_(-cfg["initrange"], cfg["initrange"])
+    model = model.to(device=dev, dtype=torch.bfloat16)
+    trainer = FusedLMTrainer(model, lr=cfg["lr"], clip_value=cfg["clip"], use_graph=not args.no_graph)
+    nb = max(8, args.steps + args.warmup)
+    pinned = synthetic_batches(cfg, min(nb, 64), rank)
+    dev_batches = [(a.to(dev), b.to(dev)) for a, b in pinned]
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    torch.cuda.reset_peak_memory_stats()
+
+    def step_dev(ids, tgt):
+        return trainer.step(ids, tgt)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed_loop(step_dev, dev_batches, args.steps, max(args.warmup, 3), world, flush, None)
+    clocks = sampler.stop()
+    trainer.check()
+    loss = float(trainer._static["loss"].item())
+    e2e = None
+    if not args.no_e2e:
+        last = {}
+
+        def step_e2e(ids, tgt):           # public API: pinned host inputs in, loss value out, every step
+            last["loss"] = trainer.step(ids, tgt)
+
+        def read_loss():
+            last["v"] = float(last["loss"].item())
+        ms_e2e = timed_loop(step_e2e, pinned, args.steps, 3, world, flush, read_loss)
+        tok = cfg["seq_len"] * cfg["batch"] * world * args.steps
+        e2e = {"value": tok / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+               "h2d_bytes_per_step": 2 * cfg["seq_len"] * cfg["batch"] * 8, "d2h_bytes_per_step": 4}
+        trainer.check()
+    peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    ws_gb = trainer.eng.slot_bytes * 4 / 2 ** 30 if world > 1 else 0.0
+    return ms, clocks, loss, e2e, peak + ws_gb, trainer.launches_per_step + 1
+
+
+def run_reference(args, cfg, rank, local, world):
+    """The reference's own rotated LM (rtp.models.transformer_lm_rtp.TransformerLM, out-of-place modules,
+    NCCL send/recv rotation, ATen/cuBLAS kernels), driven by the loop of its benchmark script
+    (benchmarks/rtp_benchmark.py:126-213: zero_grad, forward, CrossEntropyLoss, backward, clip_grad_value_,
+    Adam.step, loss.item())."""
+    import torch
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "rtp")):
+        return None
+    sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
+    sys.path.insert(0, ref)
+    torch.set_default_dtype(torch.bfloat16)   # the reference ignores dtype=, and .to(bf16) breaks its aliasing
+    from rtp.models.transformer_lm_rtp import TransformerLM
+    torch.manual_seed(0)
+    dev = torch.device("cuda", local)
+    model = TransformerLM(cfg["vocab"], cfg["ninp"], cfg["nhead"], cfg["nhid"], cfg["dropout"], cfg["initrange"],
+                          cfg["nlayers"], world, rank, device=dev)
+    with torch.no_grad():                     # the reference leaves the attention in-projection uninitialised
+        for name, p in model.named_parameters():
+            if p.dim() > 1:
+                p.uniform_(-cfg["initrange"], cfg["initrange"])
+            elif "in_proj_bias" in name:
+                p.zero_()
+    model = model.to(dev)                     # as benchmarks/rtp_benchmark.py:48-62 does (moves the PE buffer)
+    torch.set_default_dtype(torch.float32)
+    crit = torch.nn.CrossEntropyLoss()
+    opt = torch.optim.Adam(model.parameters(), lr=cfg["lr"])
+    nb = max(8, args.steps + args.warmup)
+    pinned = synthetic_batches(cfg, min(nb, 64), rank)
+    dev_batches = [(a.to(dev), b.to(dev)) for a, b in pinned]
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    torch.cuda.reset_peak_memory_stats()
+    last = {}
+
+    def step(ids, tgt):
+        ids = ids.to(dev, non_blocking=True)
+        tgt = tgt.to(dev, non_blocking=True)
+        model.train()
+        opt.zero_grad()
+        output = model(ids)
+        loss = crit(output.view(-1, cfg["vocab"]), tgt.view(-1)) / world
+        loss.backward()
+        torch.nn.utils.clip_grad_value_(model.parameters(), cfg["clip"])
+        opt.step()
+        last["loss"] = loss.detach() * world
+        del loss, output     # keeps the reference's grad-ready hooks from stacking across steps
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed_loop(step, dev_batches, args.steps, max(args.warmup, 3), world, flush, None)
+    clocks = sampler.stop()
+    loss = float(last["loss"].item())
+    e2e = None
+    if not args.no_e2e:
+        def read_loss():
+            last["v"] = float(last["loss"].item())
+        ms_e2e = timed_loop(step, pinned, args.steps, 3, world, flush, read_loss)
+        tok = cfg["seq_len"] * cfg["batch"] * world * args.steps
+        e2e = {"value": tok / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+               "h2d_bytes_per_step": 2 * cfg["seq_len"] * cfg["batch"] * 8, "d2h_bytes_per_step": 4}
+    peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    return ms, clocks, loss, e2e, peak, 0
+
+
+def main():
+    args = parse()
+    cfg = CONFIGS[args.config]
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "rtp")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/rtp is missing (reference not installed)"}))
+        return
+    import torch
+    if not torch.cuda.is_available():
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device"}))
+            return
+        raise SystemExit("bench.py needs a CUDA device")
+    rank, local, world = setup_dist(args)
+    t_wall = time.time()
+    res = run_ours(args, cfg, rank, local, world) if args.impl == "rtp_b200" else run_reference(args, cfg, rank, local, world)
+    ms, clocks, loss, e2e, peak_gb, launches = res
+    tokens = cfg["seq_len"] * cfg["batch"] * world * args.steps
+    value = tokens / (ms / 1e3)
+    peak_gb = max_over_ranks(peak_gb, world)
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
+            "impl": args.impl, "peak_gb_per_gpu": peak_gb, "final_loss": loss,
+            "config": {"model": "RTP TransformerLM (README config)" if args.config == "readme" else args.config,
+                       "vocab": cfg["vocab"], "ninp": cfg["ninp"], "nhid": cfg["nhid"], "nhead": cfg["nhead"],
+                       "layers": cfg["nlayers"], "seq_len": cfg["seq_len"], "batch_per_gpu": cfg["batch"],
+                       "global_batch": cfg["batch"] * world, "dropout": cfg["dropout"], "clip": cfg["clip"],
+                       "optimizer": "Adam lr 1e-3", "parallelism": f"rtp{world}",
+                       "l2": "192 MiB buffer written between timed iterations (L2 flush)",
+                       "cuda_graph": (not args.no_graph) if args.impl == "rtp_b200" else False},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps if args.impl == "rtp_b200" else None,
+            "wall_s": time.time() - t_wall,
+        }
+        print(json.dumps(out))
+    import torch.distributed as dist
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -21,6 +21,7 @@ typedef struct {
   int act;                                    // 0 none, 1 relu, 2 gelu
   const void* mask; long long ldmask; float mask_scale;  // optional: out = mask > 0 ? out * scale : 0
   float drop_p; unsigned long long seed, offset;          // dropout on the output when drop_p > 0
+  const unsigned long long* step_ptr;                     // optional device step counter mixed into the dropout offset
   unsigned long long* status;                 // device status word (0 = ok)
   int num_ctas;                               // 0 = one CTA per SM
   int bn;                                     // 0 = auto, else 128 or 256
@@ -48,6 +49,7 @@ typedef struct {
   void* y; long long ldy;          // [M, out]
   int act;                         // activation applied to y (column mode only)
   float drop_p; unsigned long long seed, offset;  // dropout applied to y after the activation
+  const unsigned long long* step_ptr;             // optional device step counter mixed into the dropout offset
 } RtpLinearFwd;
 int rtp_linear_fwd(const RtpRing* ring, const RtpLinearFwd* op, void* stream);
 
@@ -60,6 +62,8 @@ typedef struct {
   void* grad_home;                 // flat gradient of the home shard (same layout as home), bf16
   const float* dbias_full;         // fp32 column sums of dy: [out] (may be null when there is no bias)
   const void* mask; long long ldmask; float mask_scale;  // optional mask applied to dx (activation/dropout backward)
+  int dx_accumulate;               // 1: add the input gradient to what dx already holds
+  int grad_accumulate;             // 1: add the weight gradient to what grad_home already holds
 } RtpLinearBwd;
 int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream);
 

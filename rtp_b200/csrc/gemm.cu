@@ -203,6 +203,7 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
       ph.drop_scale = op.drop_p > 0.f ? 1.f / (1.f - op.drop_p) : 1.f;
       ph.drop_seed = op.seed;
       ph.drop_offset = op.offset + (unsigned long long)(col ? j : 0);
+      ph.drop_step_ptr = op.step_ptr;
     }
     if (i > 0) {
       ph.wait_ctr[0] = RTP_CTR_W0 + slot;
@@ -239,6 +240,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   const int Os = col ? op.out_features / N : op.out_features;
   const int Ks = col ? op.in_features : op.in_features / N;
   if (N > 1 && op.shard_bytes > R.slot_bytes) return fail("shard larger than workspace slot");
+  if (op.grad_accumulate && N > 1) return fail("grad_accumulate is only supported on a 1-rank ring");
   void* ws = R.ws[r];
   P.flags = ws ? ws_flags(ws) : nullptr;
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
@@ -282,6 +284,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
         ph.wait_ctr[0] = RTP_CTR_G0 + gin; ph.wait_rel[0] = (s - 1) / 2;
         ph.done_ctr[0] = RTP_CTR_G0 + gin;
       }
+      if (op.grad_accumulate && N == 1) { cin = reinterpret_cast<const uint8_t*>(op.grad_home); ph.c = cin; ph.ldc = Ks; }
       if (!last) {
         ph.credit_ptr = &ws_flags(R.ws[up])->done[RTP_CTR_G0 + gout].v;
         ph.credit_ctr = RTP_CTR_G0 + gout; ph.credit_rel = s / 2;
@@ -306,7 +309,8 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
       ph.bn = pick_bn(ph.M, ph.N, R.ctas);
       ph.ldd = op.lddx;
       ph.d = reinterpret_cast<__nv_bfloat16*>(op.dx) + (col ? 0 : (long long)j * Ks);
-      if (col && s > 0) { ph.c = op.dx; ph.ldc = op.lddx; }
+      if (col && (s > 0 || op.dx_accumulate)) { ph.c = op.dx; ph.ldc = op.lddx; }
+      if (!col && op.dx_accumulate) { ph.c = ph.d; ph.ldc = op.lddx; }
       if (op.mask && (!col || last)) {
         ph.mask = reinterpret_cast<const __nv_bfloat16*>(op.mask) + (col ? 0 : (long long)j * Ks);
         ph.ldmask = op.ldmask; ph.mask_scale = op.mask_scale;
@@ -381,7 +385,7 @@ int rtp_gemm(const RtpGemmArgs* a, void* stream) {
   ph.mask = a->mask; ph.ldmask = a->ldmask; ph.mask_scale = a->mask_scale;
   ph.drop_thresh = drop_threshold(a->drop_p);
   ph.drop_scale = a->drop_p > 0.f ? 1.f / (1.f - a->drop_p) : 1.f;
-  ph.drop_seed = a->seed; ph.drop_offset = a->offset;
+  ph.drop_seed = a->seed; ph.drop_offset = a->offset; ph.drop_step_ptr = a->step_ptr;
   set_vec_ok(ph);
   P.n_phases = 1;
   P.status = a->status;

@@ -217,6 +217,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
       const int total = tiles_m * tiles_n;
       const bool has_tiles = cta < total;
+      const unsigned long long drop_off =
+          ph.drop_offset + (ph.drop_step_ptr ? __ldg(ph.drop_step_ptr) * 65536ull : 0ull);
       const bool does_vec = (ph.vec_out != nullptr) && cta == 0;
       (void)has_tiles;
       if (ok) {
@@ -315,8 +317,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             if (ph.drop_thresh) {
               // element index = position in the logical [M, N] output; 8 | col so two philox calls cover the group
               const unsigned long long e = (unsigned long long)row * (unsigned long long)ph.N + (unsigned long long)col;
-              uint4 r0 = philox4x32(ph.drop_seed, ph.drop_offset, e >> 2);
-              uint4 r1 = philox4x32(ph.drop_seed, ph.drop_offset, (e >> 2) + 1);
+              uint4 r0 = philox4x32(ph.drop_seed, drop_off, e >> 2);
+              uint4 r1 = philox4x32(ph.drop_seed, drop_off, (e >> 2) + 1);
               const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
               for (int i = 0; i < 8; ++i) v[i] = rw[i] >= ph.drop_thresh ? v[i] * ph.drop_scale : 0.f;

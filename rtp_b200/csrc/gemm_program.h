@@ -58,6 +58,7 @@ struct RtpPhase {
   uint32_t drop_thresh;  // 0: no dropout. keep element if philox word >= thresh
   float drop_scale;
   unsigned long long drop_seed, drop_offset;
+  const unsigned long long* drop_step_ptr;  // optional device counter: offset += *ptr * 65536 (graph replays get fresh masks)
   // optional vector job done by CTA 0 at the end of the phase: vec_out[i] = vec_in[i] + vec_add[i] (bf16/fp32 per flags)
   void* vec_out;
   const void* vec_in;

@@ -87,9 +87,11 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
                                 const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
                                 __nv_bfloat16* __restrict__ h_out, __nv_bfloat16* __restrict__ y,
                                 float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int D, float eps,
-                                int rms, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset) {
+                                int rms, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset,
+                                const unsigned long long* __restrict__ step_ptr) {
   __shared__ float red[32];
-  extern __shared__ float rowbuf[];  // D floats
+  extern __shared__ float rowbuf[];
+  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;  // D floats
   for (int row = blockIdx.x; row < M; row += gridDim.x) {
     const size_t base = (size_t)row * D;
     float s = 0.f;
@@ -146,8 +148,10 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv
                                 const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
                                 __nv_bfloat16* __restrict__ dsub, float* __restrict__ dgamma, float* __restrict__ dbeta,
                                 int M, int D, int rms, uint32_t thresh, float drop_scale, uint64_t seed,
-                                uint64_t offset, const __nv_bfloat16* __restrict__ dres) {
+                                uint64_t offset, const __nv_bfloat16* __restrict__ dres,
+                                const unsigned long long* __restrict__ step_ptr) {
   __shared__ float red[32];
+  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   extern __shared__ float sm[];  // 2*D floats: per-block dgamma / dbeta partials
   float* pg = sm;
   float* pb = sm + D;
@@ -267,7 +271,9 @@ __global__ void ce_kernel(__nv_bfloat16* __restrict__ logits, long long ld, cons
 __global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ table, const long long* __restrict__ ids,
                                  const __nv_bfloat16* __restrict__ pe, long long ld_pe, int tokens_per_pos,
                                  __nv_bfloat16* __restrict__ out, long long ld_out, int col_off, int T, int Ds, int D,
-                                 float scale, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset) {
+                                 float scale, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset,
+                                 const unsigned long long* __restrict__ step_ptr) {
+  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   const int per_row = Ds / 8;
   const long long total = (long long)T * per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -294,7 +300,9 @@ __global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ table, const 
 // Scatter-add of the output gradient into a (zeroed or incoming) table-shard gradient [V, Ds].
 __global__ void embed_bwd_kernel(__nv_bfloat16* __restrict__ gtable, const long long* __restrict__ ids,
                                  const __nv_bfloat16* __restrict__ dy, long long ld_dy, int col_off, int T, int Ds,
-                                 int D, float scale, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset) {
+                                 int D, float scale, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset,
+                                 const unsigned long long* __restrict__ step_ptr) {
+  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   const int per_row = Ds / 8;
   const long long total = (long long)T * per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -328,8 +336,10 @@ __device__ __forceinline__ int qkv_col(int head, int which, int D, int nshard, i
 
 __global__ void attn_small_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out, int S,
                                       int B, int heads, int nshard, int causal, float sm_scale, uint32_t thresh,
-                                      float drop_scale, uint64_t seed, uint64_t offset) {
+                                      float drop_scale, uint64_t seed, uint64_t offset,
+                                      const unsigned long long* __restrict__ step_ptr) {
   extern __shared__ float smf[];
+  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   const int D = heads * kHd;
   const int b = blockIdx.x / heads, h = blockIdx.x % heads;
   float* q = smf;                 // [S][65]
@@ -396,8 +406,9 @@ __global__ void attn_small_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, __n
 __global__ void attn_small_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ dout,
                                       __nv_bfloat16* __restrict__ dqkv, int S, int B, int heads, int nshard,
                                       int causal, float sm_scale, uint32_t thresh, float drop_scale, uint64_t seed,
-                                      uint64_t offset) {
+                                      uint64_t offset, const unsigned long long* __restrict__ step_ptr) {
   extern __shared__ float smf[];
+  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   const int D = heads * kHd;
   const int b = blockIdx.x / heads, h = blockIdx.x % heads;
   float* q = smf;                 // [S][65] (pre-scaled)
@@ -611,20 +622,22 @@ const char* rtp_kernels_last_error(void) { return k_err.c_str(); }
 
 int rtp_norm_fwd(const void* x, const void* sub, const void* gamma, const void* beta, void* h_out, void* y,
                  float* mean, float* rstd, int M, int D, float eps, int rms, float drop_p, unsigned long long seed,
-                 unsigned long long offset, void* stream) {
+                 unsigned long long offset, const unsigned long long* step_ptr, void* stream) {
   if (D % 8) { k_err = "norm: D must be a multiple of 8"; return -1; }
   const int threads = D >= 2048 ? 256 : 128;
   const int grid = M < 148 * 8 ? M : 148 * 8;
   const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
   norm_fwd_kernel<<<grid, threads, D * sizeof(float), (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)sub, (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta,
-      (__nv_bfloat16*)h_out, (__nv_bfloat16*)y, mean, rstd, M, D, eps, rms, host_thresh(drop_p), ds, seed, offset);
+      (__nv_bfloat16*)h_out, (__nv_bfloat16*)y, mean, rstd, M, D, eps, rms, host_thresh(drop_p), ds, seed, offset,
+      step_ptr);
   LAUNCH_CHECK("norm_fwd");
   return 0;
 }
 int rtp_norm_bwd(const void* dy, const void* h, const void* gamma, const float* mean, const float* rstd, void* dx,
                  void* dsub, float* dgamma, float* dbeta, int M, int D, int rms, float drop_p,
-                 unsigned long long seed, unsigned long long offset, const void* dres, void* stream) {
+                 unsigned long long seed, unsigned long long offset, const void* dres,
+                 const unsigned long long* step_ptr, void* stream) {
   if (D % 8) { k_err = "norm: D must be a multiple of 8"; return -1; }
   const int threads = D >= 2048 ? 256 : 128;
   int grid = 148 * 2;
@@ -638,7 +651,7 @@ int rtp_norm_bwd(const void* dy, const void* h, const void* gamma, const float* 
   norm_bwd_kernel<<<grid, threads, smem, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)gamma, mean, rstd, (__nv_bfloat16*)dx,
       (__nv_bfloat16*)dsub, dgamma, dbeta, M, D, rms, host_thresh(drop_p), ds, seed, offset,
-      (const __nv_bfloat16*)dres);
+      (const __nv_bfloat16*)dres, step_ptr);
   LAUNCH_CHECK("norm_bwd");
   return 0;
 }
@@ -653,7 +666,8 @@ int rtp_cross_entropy(void* logits, long long ld, const long long* target, float
 }
 int rtp_embed_fwd(const void* table, const long long* ids, const void* pe, long long ld_pe, int tokens_per_pos,
                   void* out, long long ld_out, int col_off, int T, int Ds, int D, float scale, float drop_p,
-                  unsigned long long seed, unsigned long long offset, void* stream) {
+                  unsigned long long seed, unsigned long long offset, const unsigned long long* step_ptr,
+                  void* stream) {
   if (Ds % 8 || col_off % 8 || ld_out % 8) { k_err = "embed: widths must be multiples of 8"; return -1; }
   const long long total = (long long)T * (Ds / 8);
   int grid = (int)((total + 255) / 256);
@@ -661,12 +675,14 @@ int rtp_embed_fwd(const void* table, const long long* ids, const void* pe, long 
   const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
   embed_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)table, ids, (const __nv_bfloat16*)pe,
                                                            ld_pe, tokens_per_pos, (__nv_bfloat16*)out, ld_out, col_off,
-                                                           T, Ds, D, scale, host_thresh(drop_p), ds, seed, offset);
+                                                           T, Ds, D, scale, host_thresh(drop_p), ds, seed, offset,
+                                                           step_ptr);
   LAUNCH_CHECK("embed_fwd");
   return 0;
 }
 int rtp_embed_bwd(void* gtable, const long long* ids, const void* dy, long long ld_dy, int col_off, int T, int Ds,
-                  int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset, void* stream) {
+                  int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset,
+                  const unsigned long long* step_ptr, void* stream) {
   if (Ds % 8 || col_off % 8 || ld_dy % 8) { k_err = "embed: widths must be multiples of 8"; return -1; }
   const long long total = (long long)T * (Ds / 8);
   int grid = (int)((total + 255) / 256);
@@ -674,7 +690,7 @@ int rtp_embed_bwd(void* gtable, const long long* ids, const void* dy, long long 
   const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
   embed_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)gtable, ids, (const __nv_bfloat16*)dy, ld_dy,
                                                            col_off, T, Ds, D, scale, host_thresh(drop_p), ds, seed,
-                                                           offset);
+                                                           offset, step_ptr);
   LAUNCH_CHECK("embed_bwd");
   return 0;
 }
@@ -683,7 +699,8 @@ static size_t attn_smem(int S, bool bwd) {
   return f * sizeof(float);
 }
 int rtp_attn_small_fwd(const void* qkv, void* out, int S, int B, int heads, int nshard, int causal, float sm_scale,
-                       float drop_p, unsigned long long seed, unsigned long long offset, void* stream) {
+                       float drop_p, unsigned long long seed, unsigned long long offset,
+                       const unsigned long long* step_ptr, void* stream) {
   if (S > 128 || heads % nshard) { k_err = "attn_small: S must be <= 128 and heads divisible by shards"; return -1; }
   const size_t smem = attn_smem(S, false);
   if (smem > 48 * 1024) {
@@ -693,12 +710,13 @@ int rtp_attn_small_fwd(const void* qkv, void* out, int S, int B, int heads, int 
   const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
   attn_small_fwd_kernel<<<B * heads, 128, smem, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, S, B, heads, nshard, causal, sm_scale, host_thresh(drop_p), ds,
-      seed, offset);
+      seed, offset, step_ptr);
   LAUNCH_CHECK("attn_small_fwd");
   return 0;
 }
 int rtp_attn_small_bwd(const void* qkv, const void* dout, void* dqkv, int S, int B, int heads, int nshard, int causal,
-                       float sm_scale, float drop_p, unsigned long long seed, unsigned long long offset, void* stream) {
+                       float sm_scale, float drop_p, unsigned long long seed, unsigned long long offset,
+                       const unsigned long long* step_ptr, void* stream) {
   if (heads % nshard) { k_err = "attn_small: heads must be divisible by shards"; return -1; }
   const size_t smem = attn_smem(S, true);
   if (smem > 227 * 1024) { k_err = "attn_small backward: sequence too long for shared memory (S <= 96)"; return -1; }
@@ -709,7 +727,7 @@ int rtp_attn_small_bwd(const void* qkv, const void* dout, void* dqkv, int S, int
   const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
   attn_small_bwd_kernel<<<B * heads, 128, smem, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dqkv, S, B, heads, nshard, causal,
-      sm_scale, host_thresh(drop_p), ds, seed, offset);
+      sm_scale, host_thresh(drop_p), ds, seed, offset, step_ptr);
   LAUNCH_CHECK("attn_small_bwd");
   return 0;
 }

@@ -18,21 +18,26 @@ typedef struct {
 const char* rtp_kernels_last_error(void);
 int rtp_norm_fwd(const void* x, const void* sub, const void* gamma, const void* beta, void* h_out, void* y,
                  float* mean, float* rstd, int M, int D, float eps, int rms, float drop_p, unsigned long long seed,
-                 unsigned long long offset, void* stream);
+                 unsigned long long offset, const unsigned long long* step_ptr, void* stream);
 int rtp_norm_bwd(const void* dy, const void* h, const void* gamma, const float* mean, const float* rstd, void* dx,
                  void* dsub, float* dgamma, float* dbeta, int M, int D, int rms, float drop_p,
-                 unsigned long long seed, unsigned long long offset, const void* dres, void* stream);
+                 unsigned long long seed, unsigned long long offset, const void* dres,
+                 const unsigned long long* step_ptr, void* stream);
 int rtp_cross_entropy(void* logits, long long ld, const long long* target, float* loss, int M, int V, float grad_scale,
                       long long ignore_index, int write_grad, void* stream);
 int rtp_embed_fwd(const void* table, const long long* ids, const void* pe, long long ld_pe, int tokens_per_pos,
                   void* out, long long ld_out, int col_off, int T, int Ds, int D, float scale, float drop_p,
-                  unsigned long long seed, unsigned long long offset, void* stream);
+                  unsigned long long seed, unsigned long long offset, const unsigned long long* step_ptr,
+                  void* stream);
 int rtp_embed_bwd(void* gtable, const long long* ids, const void* dy, long long ld_dy, int col_off, int T, int Ds,
-                  int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset, void* stream);
+                  int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset,
+                  const unsigned long long* step_ptr, void* stream);
 int rtp_attn_small_fwd(const void* qkv, void* out, int S, int B, int heads, int nshard, int causal, float sm_scale,
-                       float drop_p, unsigned long long seed, unsigned long long offset, void* stream);
+                       float drop_p, unsigned long long seed, unsigned long long offset,
+                       const unsigned long long* step_ptr, void* stream);
 int rtp_attn_small_bwd(const void* qkv, const void* dout, void* dqkv, int S, int B, int heads, int nshard, int causal,
-                       float sm_scale, float drop_p, unsigned long long seed, unsigned long long offset, void* stream);
+                       float sm_scale, float drop_p, unsigned long long seed, unsigned long long offset,
+                       const unsigned long long* step_ptr, void* stream);
 int rtp_colsum(const void* x, long long ld, int M, int N, float* out, void* stream);
 int rtp_adam(const RtpAdamTensor* tensors_dev, const int* block_start_dev, int ntensors, int total_blocks,
              const long long* step_dev, float lr, float beta1, float beta2, float eps, float weight_decay, int adamw,

@@ -26,7 +26,7 @@ class GemmArgs(C.Structure):
         ("c", C.c_void_p), ("ldc", C.c_longlong), ("c_fp32", C.c_int),
         ("bias", C.c_void_p), ("act", C.c_int),
         ("mask", C.c_void_p), ("ldmask", C.c_longlong), ("mask_scale", C.c_float),
-        ("drop_p", C.c_float), ("seed", C.c_ulonglong), ("offset", C.c_ulonglong),
+        ("drop_p", C.c_float), ("seed", C.c_ulonglong), ("offset", C.c_ulonglong), ("step_ptr", C.c_void_p),
         ("status", C.c_void_p), ("num_ctas", C.c_int), ("bn", C.c_int),
     ]
 
@@ -48,7 +48,7 @@ class LinearFwd(C.Structure):
         ("x", C.c_void_p), ("ldx", C.c_longlong),
         ("y", C.c_void_p), ("ldy", C.c_longlong),
         ("act", C.c_int),
-        ("drop_p", C.c_float), ("seed", C.c_ulonglong), ("offset", C.c_ulonglong),
+        ("drop_p", C.c_float), ("seed", C.c_ulonglong), ("offset", C.c_ulonglong), ("step_ptr", C.c_void_p),
     ]
 
 
@@ -62,6 +62,7 @@ class LinearBwd(C.Structure):
         ("grad_home", C.c_void_p),
         ("dbias_full", C.c_void_p),
         ("mask", C.c_void_p), ("ldmask", C.c_longlong), ("mask_scale", C.c_float),
+        ("dx_accumulate", C.c_int), ("grad_accumulate", C.c_int),
     ]
 
 

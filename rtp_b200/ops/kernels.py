@@ -21,13 +21,13 @@ def _L():
     if not _declared:
         vp, ll, i, f, ull = C.c_void_p, C.c_longlong, C.c_int, C.c_float, C.c_ulonglong
         L.rtp_kernels_last_error.restype = C.c_char_p
-        L.rtp_norm_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, f, i, f, ull, ull, vp]
-        L.rtp_norm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, f, ull, ull, vp, vp]
+        L.rtp_norm_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, f, i, f, ull, ull, vp, vp]
+        L.rtp_norm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, f, ull, ull, vp, vp, vp]
         L.rtp_cross_entropy.argtypes = [vp, ll, vp, vp, i, i, f, ll, i, vp]
-        L.rtp_embed_fwd.argtypes = [vp, vp, vp, ll, i, vp, ll, i, i, i, i, f, f, ull, ull, vp]
-        L.rtp_embed_bwd.argtypes = [vp, vp, vp, ll, i, i, i, i, f, f, ull, ull, vp]
-        L.rtp_attn_small_fwd.argtypes = [vp, vp, i, i, i, i, i, f, f, ull, ull, vp]
-        L.rtp_attn_small_bwd.argtypes = [vp, vp, vp, i, i, i, i, i, f, f, ull, ull, vp]
+        L.rtp_embed_fwd.argtypes = [vp, vp, vp, ll, i, vp, ll, i, i, i, i, f, f, ull, ull, vp, vp]
+        L.rtp_embed_bwd.argtypes = [vp, vp, vp, ll, i, i, i, i, f, f, ull, ull, vp, vp]
+        L.rtp_attn_small_fwd.argtypes = [vp, vp, i, i, i, i, i, f, f, ull, ull, vp, vp]
+        L.rtp_attn_small_bwd.argtypes = [vp, vp, vp, i, i, i, i, i, f, f, ull, ull, vp, vp]
         L.rtp_colsum.argtypes = [vp, ll, i, i, vp, vp]
         L.rtp_adam.argtypes = [vp, vp, i, i, vp, f, f, f, f, f, i, f, f, vp]
         L.rtp_add.argtypes = [vp, vp, vp, ll, vp]
@@ -47,28 +47,33 @@ def _p(t):
     return None if t is None else t.data_ptr()
 
 
-def norm_fwd(x, sub, gamma, beta, *, eps=1e-5, rms=False, drop_p=0.0, seed=0, offset=0, save_h=True):
+def norm_fwd(x, sub, gamma, beta, *, eps=1e-5, rms=False, drop_p=0.0, seed=0, offset=0, save_h=True, step=None,
+             out=None, h_out=None, mean_out=None, rstd_out=None):
     """h = x + dropout(sub); y = LayerNorm/RMSNorm(h). Returns (y, h, mean, rstd)."""
     M, D = x.shape
-    y = torch.empty_like(x)
-    h = torch.empty_like(x) if save_h else None
-    mean = None if rms else torch.empty(M, dtype=torch.float32, device=x.device)
-    rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+    y = out if out is not None else torch.empty_like(x)
+    h = h_out if h_out is not None else (torch.empty_like(x) if save_h else None)
+    mean = None if rms else (mean_out if mean_out is not None else torch.empty(M, dtype=torch.float32, device=x.device))
+    rstd = rstd_out if rstd_out is not None else torch.empty(M, dtype=torch.float32, device=x.device)
     _check(_L().rtp_norm_fwd(_p(x), _p(sub), _p(gamma), _p(beta), _p(h), _p(y), _p(mean), _p(rstd), M, D, eps,
-                             int(rms), float(drop_p), seed, offset, _lib.stream_ptr()), "norm_fwd")
+                             int(rms), float(drop_p), seed, offset, _p(step), _lib.stream_ptr()), "norm_fwd")
     return y, h, mean, rstd
 
 
 def norm_bwd(dy, h, gamma, mean, rstd, *, rms=False, has_beta=True, drop_p=0.0, seed=0, offset=0, want_dsub=True,
-             dres=None):
+             dres=None, step=None, dgamma=None, dbeta=None, dx=None, dsub=None):
     """Returns (dx, dsub, dgamma_fp32, dbeta_fp32)."""
     M, D = dy.shape
-    dx = torch.empty_like(dy)
-    dsub = torch.empty_like(dy) if want_dsub else None
-    dgamma = torch.zeros(D, dtype=torch.float32, device=dy.device)
-    dbeta = torch.zeros(D, dtype=torch.float32, device=dy.device) if has_beta else None
+    dx = dx if dx is not None else torch.empty_like(dy)
+    if dsub is None and want_dsub:
+        dsub = torch.empty_like(dy)
+    if dgamma is None:  # caller-provided buffers are accumulated into (they must be zeroed by the caller)
+        dgamma = torch.zeros(D, dtype=torch.float32, device=dy.device)
+    if dbeta is None and has_beta:
+        dbeta = torch.zeros(D, dtype=torch.float32, device=dy.device)
     _check(_L().rtp_norm_bwd(_p(dy), _p(h), _p(gamma), _p(mean), _p(rstd), _p(dx), _p(dsub), _p(dgamma), _p(dbeta),
-                             M, D, int(rms), float(drop_p), seed, offset, _p(dres), _lib.stream_ptr()), "norm_bwd")
+                             M, D, int(rms), float(drop_p), seed, offset, _p(dres), _p(step), _lib.stream_ptr()),
+           "norm_bwd")
     return dx, dsub, dgamma, dbeta
 
 
@@ -81,37 +86,49 @@ def cross_entropy_(logits, target, *, grad_scale=1.0, ignore_index=-100, write_g
     return loss
 
 
-def embed_fwd(table, ids, out, col_off, *, D, scale=1.0, pe=None, tokens_per_pos=1, drop_p=0.0, seed=0, offset=0):
+def cross_entropy_into(logits, target, loss, *, grad_scale=1.0, ignore_index=-100, write_grad=True):
+    """Same as :func:`cross_entropy_` but writes the per-row loss into a caller-provided fp32 buffer."""
+    M, V = logits.shape
+    _check(_L().rtp_cross_entropy(_p(logits), logits.stride(0), _p(target), _p(loss), M, V, float(grad_scale),
+                                  int(ignore_index), int(write_grad), _lib.stream_ptr()), "cross_entropy")
+    return loss
+
+
+def embed_fwd(table, ids, out, col_off, *, D, scale=1.0, pe=None, tokens_per_pos=1, drop_p=0.0, seed=0, offset=0,
+              step=None):
     T = ids.numel()
     Ds = table.shape[1]
     _check(_L().rtp_embed_fwd(_p(table), _p(ids), _p(pe), pe.stride(0) if pe is not None else 0, tokens_per_pos,
                               _p(out), out.stride(0), col_off, T, Ds, D, float(scale), float(drop_p), seed, offset,
-                              _lib.stream_ptr()), "embed_fwd")
+                              _p(step), _lib.stream_ptr()), "embed_fwd")
     return out
 
 
-def embed_bwd(gtable, ids, dy, col_off, *, D, scale=1.0, drop_p=0.0, seed=0, offset=0):
+def embed_bwd(gtable, ids, dy, col_off, *, D, scale=1.0, drop_p=0.0, seed=0, offset=0, step=None):
     T = ids.numel()
     Ds = gtable.shape[1]
     _check(_L().rtp_embed_bwd(_p(gtable), _p(ids), _p(dy), dy.stride(0), col_off, T, Ds, D, float(scale),
-                              float(drop_p), seed, offset, _lib.stream_ptr()), "embed_bwd")
+                              float(drop_p), seed, offset, _p(step), _lib.stream_ptr()), "embed_bwd")
     return gtable
 
 
-def attn_small_fwd(qkv, S, B, heads, *, nshard=1, causal=True, drop_p=0.0, seed=0, offset=0, sm_scale=None):
+def attn_small_fwd(qkv, S, B, heads, *, nshard=1, causal=True, drop_p=0.0, seed=0, offset=0, sm_scale=None, step=None,
+                   out=None):
     D = heads * 64
-    out = torch.empty(S * B, D, dtype=qkv.dtype, device=qkv.device)
+    if out is None:
+        out = torch.empty(S * B, D, dtype=qkv.dtype, device=qkv.device)
     sc = sm_scale if sm_scale is not None else 64 ** -0.5
     _check(_L().rtp_attn_small_fwd(_p(qkv), _p(out), S, B, heads, nshard, int(causal), sc, float(drop_p), seed, offset,
-                                   _lib.stream_ptr()), "attn_small_fwd")
+                                   _p(step), _lib.stream_ptr()), "attn_small_fwd")
     return out
 
 
-def attn_small_bwd(qkv, dout, S, B, heads, *, nshard=1, causal=True, drop_p=0.0, seed=0, offset=0, sm_scale=None):
-    dqkv = torch.empty_like(qkv)
+def attn_small_bwd(qkv, dout, S, B, heads, *, nshard=1, causal=True, drop_p=0.0, seed=0, offset=0, sm_scale=None,
+                   step=None, out=None):
+    dqkv = out if out is not None else torch.empty_like(qkv)
     sc = sm_scale if sm_scale is not None else 64 ** -0.5
     _check(_L().rtp_attn_small_bwd(_p(qkv), _p(dout), _p(dqkv), S, B, heads, nshard, int(causal), sc, float(drop_p),
-                                   seed, offset, _lib.stream_ptr()), "attn_small_bwd")
+                                   seed, offset, _p(step), _lib.stream_ptr()), "attn_small_bwd")
     return dqkv
 
 

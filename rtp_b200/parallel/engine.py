@@ -103,7 +103,8 @@ def _linear_desc(module, row):
     return has_bias, bias_off, shard_bytes
 
 
-def linear_fwd_raw(eng, flat, layout_info, x2d, row, in_f, out_f, act=0, drop_p=0.0, seed=0, offset=0, out=None):
+def linear_fwd_raw(eng, flat, layout_info, x2d, row, in_f, out_f, act=0, drop_p=0.0, seed=0, offset=0, out=None,
+                   step=None):
     has_bias, bias_off, shard_bytes = layout_info
     M = x2d.shape[0]
     y = out if out is not None else torch.empty(M, out_f, dtype=torch.bfloat16, device=x2d.device)
@@ -113,17 +114,20 @@ def linear_fwd_raw(eng, flat, layout_info, x2d, row, in_f, out_f, act=0, drop_p=
     op.x, op.ldx = x2d.data_ptr(), x2d.stride(0)
     op.y, op.ldy = y.data_ptr(), y.stride(0)
     op.act, op.drop_p, op.seed, op.offset = act, drop_p, seed, offset
+    op.step_ptr = step.data_ptr() if step is not None else None
     _lib.check(_lib.lib().rtp_linear_fwd(C.byref(eng.ring), C.byref(op), _lib.stream_ptr()), "rtp_linear_fwd")
     return y
 
 
 def linear_bwd_raw(eng, flat, layout_info, x2d, dy2d, row, in_f, out_f, need_dx=True, mask=None, mask_scale=1.0,
-                   grad_out=None):
+                   grad_out=None, dx_out=None, dx_accumulate=False, dbias_buf=None):
     has_bias, bias_off, shard_bytes = layout_info
     M = x2d.shape[0]
     gflat = grad_out if grad_out is not None else torch.empty_like(flat)
-    dx = torch.empty(M, in_f, dtype=torch.bfloat16, device=x2d.device) if need_dx else None
-    dbias = K.colsum(dy2d) if has_bias else None
+    dx = None
+    if need_dx:
+        dx = dx_out if dx_out is not None else torch.empty(M, in_f, dtype=torch.bfloat16, device=x2d.device)
+    dbias = K.colsum(dy2d, dbias_buf) if has_bias else None
     op = _lib.LinearBwd()
     op.mode, op.M, op.in_features, op.out_features = int(row), M, in_f, out_f
     op.home, op.bias_off, op.shard_bytes = flat.data_ptr(), bias_off, shard_bytes
@@ -135,6 +139,7 @@ def linear_bwd_raw(eng, flat, layout_info, x2d, dy2d, row, in_f, out_f, need_dx=
     op.dbias_full = dbias.data_ptr() if dbias is not None else None
     if mask is not None:
         op.mask, op.ldmask, op.mask_scale = mask.data_ptr(), mask.stride(0), mask_scale
+    op.dx_accumulate = int(dx_accumulate)
     _lib.check(_lib.lib().rtp_linear_bwd(C.byref(eng.ring), C.byref(op), _lib.stream_ptr()), "rtp_linear_bwd")
     return dx, gflat
 
@@ -169,3 +174,11 @@ class _FusedLinearFn(torch.autograd.Function):
 
 def fused_linear(module, x, row=False):
     return _FusedLinearFn.apply(module, row, x, *module.shard_parameters())
+
+
+def embed_fwd_rot(eng, flat, V, Ds, ids, out, D, scale, pe, tokens_per_pos, drop_p, seed, offset, step):
+    raise NotImplementedError("fused embedding rotation for rings of more than one rank")
+
+
+def embed_bwd_rot(eng, trainer, st, dx0):
+    raise NotImplementedError("fused embedding rotation for rings of more than one rank")
