@@ -67,6 +67,31 @@ typedef struct {
 } RtpLinearBwd;
 int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream);
 
+// Rotated embedding lookup: the table is sharded along the embedding dim ([V, D/N] per rank); shard j fills
+// columns [j*D/N, (j+1)*D/N) of out.  out = dropout(table[ids] * scale + pe[t / tokens_per_pos]).
+typedef struct {
+  const void* home; unsigned long long shard_bytes;
+  int V, Ds, D;
+  const long long* ids; int T;
+  void* out; long long ld_out;
+  float scale;
+  const void* pe; long long ld_pe; int tokens_per_pos;
+  float drop_p; unsigned long long seed, offset; const unsigned long long* step_ptr;
+} RtpEmbedFwd;
+int rtp_embed_fwd_rot(const RtpRing* ring, const RtpEmbedFwd* op, void* stream);
+
+// Ring reduce-scatter over column blocks: every rank holds a dense [rows, N*cols] bf16 matrix `src` (pitch ld);
+// rank r ends up with sum over ranks of column block r in `out` (dense [rows, cols]).  Used for the gradient of
+// the rotated embedding table.
+typedef struct {
+  const void* src; long long ld;
+  int rows, cols;
+  void* out;
+} RtpReduceScatter;
+int rtp_reduce_scatter_cols(const RtpRing* ring, const RtpReduceScatter* op, void* stream);
+int rtp_embed_fwd_rot_emu(const RtpRing* rings, const RtpEmbedFwd* ops, int world, void* stream);
+int rtp_reduce_scatter_cols_emu(const RtpRing* rings, const RtpReduceScatter* ops, int world, void* stream);
+
 // Single-GPU emulation of `world` ranks in one cooperative launch (for tests with fewer GPUs than ranks).
 int rtp_linear_fwd_emu(const RtpRing* rings, const RtpLinearFwd* ops, int world, void* stream);
 int rtp_linear_bwd_emu(const RtpRing* rings, const RtpLinearBwd* ops, int world, void* stream);
@@ -84,6 +109,7 @@ void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i);
 void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i);
 int rtp_sm_count(void);
 const char* rtp_last_error(void);
+void rtp_debug_force_stages(int n);   // tuning aid: cap the smem pipeline depth (0 = automatic)
 
 #ifdef __cplusplus
 }

@@ -107,6 +107,18 @@ uint32_t drop_threshold(float p) {
   return (uint32_t)t;
 }
 
+// Pipeline geometry: the stage must hold the widest B tile of the program; narrower tiles get more stages.
+int g_force_stages = 0;
+void finalize_program(RtpProgram& P) {
+  int bn = 128;
+  for (int i = 0; i < P.n_phases; ++i)
+    if (P.phases[i].kind == RTP_KIND_GEMM && P.phases[i].bn > bn) bn = P.phases[i].bn;
+  P.stage_bytes = rtp::kABytes + bn * rtp::kBK * 2;
+  P.n_stages = rtp::kTileBytes / P.stage_bytes;
+  if (P.n_stages > rtp::kMaxStages) P.n_stages = rtp::kMaxStages;
+  if (g_force_stages > 0 && g_force_stages < P.n_stages) P.n_stages = g_force_stages;
+}
+
 template <int NEMU>
 int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cudaStream_t stream) {
   static bool attr_set = false;
@@ -130,6 +142,7 @@ int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cuda
   }
   cfg.attrs = at;
   cfg.numAttrs = nat;
+  for (int e = 0; e < NEMU; ++e) finalize_program(const_cast<RtpProgram&>(params.prog[e]));
   cudaError_t e = cudaLaunchKernelEx(&cfg, rtp::rtp_gemm_kernel<NEMU>, params);
   if (e != cudaSuccess) return fail(std::string("launch rtp_gemm_kernel: ") + cudaGetErrorString(e));
   return 0;
@@ -347,6 +360,98 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   return 0;
 }
 
+int build_embed_fwd(const RtpRing& R, const RtpEmbedFwd& op, RtpProgram& P) {
+  init_program(P);
+  const int N = R.world, r = R.rank;
+  if (N < 1 || N > RTP_MAX_WORLD) return fail("world size out of range");
+  if (op.Ds % 8 || op.Ds * N != op.D) return fail("embedding: D must be N * Ds with Ds a multiple of 8");
+  if (N > 1 && op.shard_bytes > R.slot_bytes) return fail("shard larger than workspace slot");
+  if (op.shard_bytes % 16) return fail("shard_bytes must be a multiple of 16");
+  void* ws = R.ws[r];
+  P.flags = ws ? ws_flags(ws) : nullptr;
+  P.status = ws ? &ws_flags(ws)->status.v : nullptr;
+  P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
+  P.n_phases = N;
+  for (int i = 0; i < N; ++i) {
+    RtpPhase& ph = P.phases[i];
+    init_phase(ph);
+    const int j = mod(r + i, N);
+    const int slot = (i - 1) & 1;
+    ph.kind = RTP_KIND_GATHER;
+    ph.M = ph.N = ph.K = 0;
+    ph.g_table = (i == 0) ? op.home : ws_wslot(ws, R.slot_bytes, slot);
+    ph.g_ids = op.ids;
+    ph.g_tokens = op.T; ph.g_cols = op.Ds; ph.g_dim = op.D; ph.g_col_off = j * op.Ds; ph.g_tpp = op.tokens_per_pos;
+    ph.g_scale = op.scale; ph.g_pe = op.pe; ph.g_ldpe = op.ld_pe;
+    ph.d = reinterpret_cast<__nv_bfloat16*>(op.out) + (long long)j * op.Ds;
+    ph.ldd = op.ld_out;
+    ph.drop_thresh = drop_threshold(op.drop_p);
+    ph.drop_scale = op.drop_p > 0.f ? 1.f / (1.f - op.drop_p) : 1.f;
+    ph.drop_seed = op.seed; ph.drop_offset = op.offset; ph.drop_step_ptr = op.step_ptr;
+    if (i > 0) {
+      ph.wait_ctr[0] = RTP_CTR_W0 + slot;
+      ph.wait_rel[0] = (i - 1) / 2;
+      ph.done_ctr[0] = RTP_CTR_W0 + slot;
+    }
+  }
+  P.n_pushes = N - 1;
+  for (int i = 0; i + 1 < N; ++i) {
+    RtpPush& pu = P.pushes[i];
+    memset(&pu, 0, sizeof(pu));
+    const int t = mod(r - (i + 1), N);
+    const int slot = i & 1;
+    pu.src = op.home;
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
+    pu.bytes = op.shard_bytes;
+    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
+    pu.credit_ctr = RTP_CTR_W0 + slot;
+    pu.credit_rel = i / 2;
+    pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
+  }
+  P.uses_inc[RTP_CTR_W0] = N / 2;
+  P.uses_inc[RTP_CTR_W1] = (N - 1) / 2;
+  return 0;
+}
+
+int build_reduce_scatter(const RtpRing& R, const RtpReduceScatter& op, RtpProgram& P) {
+  init_program(P);
+  const int N = R.world, r = R.rank;
+  if (N < 1 || N > RTP_MAX_WORLD) return fail("world size out of range");
+  if (op.cols % 8 || op.ld % 8) return fail("reduce_scatter: cols and ld must be multiples of 8");
+  if (N > 1 && (unsigned long long)op.rows * op.cols * 2 > R.slot_bytes) return fail("block larger than workspace slot");
+  void* ws = R.ws[r];
+  P.flags = ws ? ws_flags(ws) : nullptr;
+  P.status = ws ? &ws_flags(ws)->status.v : nullptr;
+  P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
+  const int up = mod(r + 1, N);
+  P.n_phases = N;
+  for (int s = 0; s < N; ++s) {
+    RtpPhase& ph = P.phases[s];
+    init_phase(ph);
+    const int j = mod(r - 1 - s, N);
+    const int gin = (s - 1) & 1, gout = s & 1;
+    const bool last = s == N - 1;
+    ph.kind = RTP_KIND_VECADD;
+    ph.M = ph.N = ph.K = 0;
+    ph.v_src = reinterpret_cast<const __nv_bfloat16*>(op.src) + (long long)j * op.cols;
+    ph.v_ld = op.ld; ph.v_rows = op.rows; ph.v_cols = op.cols;
+    ph.d = last ? op.out : (void*)ws_gslot(R.ws[up], R.slot_bytes, gout);
+    if (s > 0) {
+      ph.c = ws_gslot(ws, R.slot_bytes, gin);
+      ph.wait_ctr[0] = RTP_CTR_G0 + gin; ph.wait_rel[0] = (s - 1) / 2;
+      ph.done_ctr[0] = RTP_CTR_G0 + gin;
+    }
+    if (!last) {
+      ph.credit_ptr = &ws_flags(R.ws[up])->done[RTP_CTR_G0 + gout].v;
+      ph.credit_ctr = RTP_CTR_G0 + gout; ph.credit_rel = s / 2;
+      ph.arrive_ptr = &ws_flags(R.ws[up])->arrive[RTP_CTR_G0 + gout].v;
+    }
+  }
+  P.uses_inc[RTP_CTR_G0] = N / 2;
+  P.uses_inc[RTP_CTR_G1] = (N - 1) / 2;
+  return 0;
+}
+
 template <int NEMU, class Op, class Builder>
 int run_emu(const RtpRing* rings, const Op* ops, Builder build, cudaStream_t stream) {
   static rtp::GemmParams<NEMU> params;  // large; keep off the stack
@@ -361,6 +466,7 @@ int run_emu(const RtpRing* rings, const Op* ops, Builder build, cudaStream_t str
 extern "C" {
 
 const char* rtp_last_error(void) { return g_err.c_str(); }
+void rtp_debug_force_stages(int n) { g_force_stages = n; }
 int rtp_sm_count(void) { return sm_count(); }
 
 int rtp_gemm(const RtpGemmArgs* a, void* stream) {
@@ -410,6 +516,30 @@ int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream) {
   if (!params.prog[0].status) return fail("ring workspace required");
   params.ctas_per_rank = ring->ctas;
   return launch<1>(params, ring->ctas, false, (cudaStream_t)stream);
+}
+int rtp_embed_fwd_rot(const RtpRing* ring, const RtpEmbedFwd* op, void* stream) {
+  static thread_local rtp::GemmParams<1> params;
+  if (build_embed_fwd(*ring, *op, params.prog[0])) return -1;
+  if (!params.prog[0].status) return fail("ring workspace required");
+  params.ctas_per_rank = ring->ctas;
+  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream);
+}
+int rtp_reduce_scatter_cols(const RtpRing* ring, const RtpReduceScatter* op, void* stream) {
+  static thread_local rtp::GemmParams<1> params;
+  if (build_reduce_scatter(*ring, *op, params.prog[0])) return -1;
+  if (!params.prog[0].status) return fail("ring workspace required");
+  params.ctas_per_rank = ring->ctas;
+  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream);
+}
+int rtp_embed_fwd_rot_emu(const RtpRing* rings, const RtpEmbedFwd* ops, int world, void* stream) {
+  if (world == 2) return run_emu<2>(rings, ops, build_embed_fwd, (cudaStream_t)stream);
+  if (world == 4) return run_emu<4>(rings, ops, build_embed_fwd, (cudaStream_t)stream);
+  return fail("emulation supports 2 or 4 ranks");
+}
+int rtp_reduce_scatter_cols_emu(const RtpRing* rings, const RtpReduceScatter* ops, int world, void* stream) {
+  if (world == 2) return run_emu<2>(rings, ops, build_reduce_scatter, (cudaStream_t)stream);
+  if (world == 4) return run_emu<4>(rings, ops, build_reduce_scatter, (cudaStream_t)stream);
+  return fail("emulation supports 2 or 4 ranks");
 }
 int rtp_linear_fwd_emu(const RtpRing* rings, const RtpLinearFwd* ops, int world, void* stream) {
   if (world == 2) return run_emu<2>(rings, ops, build_linear_fwd, (cudaStream_t)stream);

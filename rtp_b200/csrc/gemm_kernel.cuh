@@ -17,17 +17,16 @@ namespace rtp {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kStages = 4;
+constexpr int kMaxStages = 8;
 constexpr int kABytes = kBM * kBK * 2;          // 16 KB
-constexpr int kBBytesMax = 256 * kBK * 2;       // 32 KB
-constexpr int kStageBytes = kABytes + kBBytesMax;
+constexpr int kTileBytes = 196608;              // smem ring: 4 stages of 48 KB (bn 256) or 6 stages of 32 KB (bn 128)
 constexpr int kTmemCols = 512;
 constexpr int kNumThreads = 256;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kSmemBytes = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 
 struct SmemCtrl {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain;
@@ -56,7 +55,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
   const RtpProgram& P = params.prog[vrank];
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SmemCtrl* ctl = reinterpret_cast<SmemCtrl*>(tiles + kStages * kStageBytes);
+  SmemCtrl* ctl = reinterpret_cast<SmemCtrl*>(tiles + kTileBytes);
+  const int kStages = P.n_stages;          // uniform for the launch: set by the host from the widest tile
+  const int kStageBytes = P.stage_bytes;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   unsigned long long* status = P.status;
   const unsigned long long timeout_ns = P.timeout_ns;
@@ -91,8 +92,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t issued_parity[kStages];
-      bool issued[kStages];
+      uint32_t issued_parity[kMaxStages];
+      bool issued[kMaxStages];
       for (int s = 0; s < kStages; ++s) { issued[s] = false; issued_parity[s] = 0; }
       bool ok = true;
       for (int p = 0; p < P.n_phases && ok; ++p) {
@@ -239,6 +240,56 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) ok = false;
       }
+      if (ok && ph.kind == RTP_KIND_GATHER) {
+        // embedding rows of the visiting table shard -> column block of the output
+        const int per_row = ph.g_cols >> 3;
+        const long long items = (long long)ph.g_tokens * per_row;
+        const __nv_bfloat16* table = reinterpret_cast<const __nv_bfloat16*>(ph.g_table);
+        const __nv_bfloat16* pe = reinterpret_cast<const __nv_bfloat16*>(ph.g_pe);
+        __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(ph.d);
+        for (long long it = (long long)cta * 128 + epi_tid; it < items; it += (long long)G * 128) {
+          const int t = (int)(it / per_row), c = (int)(it % per_row) * 8;
+          uint4 raw = __ldcg(reinterpret_cast<const uint4*>(table + (size_t)ph.g_ids[t] * ph.g_cols + c));
+          float v[8] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y),
+                        bf16_lo(raw.z), bf16_hi(raw.z), bf16_lo(raw.w), bf16_hi(raw.w)};
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[k] *= ph.g_scale;
+          if (pe) {
+            uint4 pr = *reinterpret_cast<const uint4*>(pe + (size_t)(t / ph.g_tpp) * ph.g_ldpe + ph.g_col_off + c);
+            v[0] += bf16_lo(pr.x); v[1] += bf16_hi(pr.x); v[2] += bf16_lo(pr.y); v[3] += bf16_hi(pr.y);
+            v[4] += bf16_lo(pr.z); v[5] += bf16_hi(pr.z); v[6] += bf16_lo(pr.w); v[7] += bf16_hi(pr.w);
+          }
+          if (ph.drop_thresh) {
+            const unsigned long long e = (unsigned long long)t * ph.g_dim + ph.g_col_off + c;
+            uint4 r0 = philox4x32(ph.drop_seed, drop_off, e >> 2), r1 = philox4x32(ph.drop_seed, drop_off, (e >> 2) + 1);
+            const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = rw[k] >= ph.drop_thresh ? v[k] * ph.drop_scale : 0.f;
+          }
+          *reinterpret_cast<uint4*>(outp + (size_t)t * ph.ldd + c) =
+              make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        }
+      } else if (ok && ph.kind == RTP_KIND_VECADD) {
+        const int per_row = ph.v_cols >> 3;
+        const long long items = (long long)ph.v_rows * per_row;
+        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(ph.v_src);
+        const __nv_bfloat16* cin = reinterpret_cast<const __nv_bfloat16*>(ph.c);
+        __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(ph.d);
+        for (long long it = (long long)cta * 128 + epi_tid; it < items; it += (long long)G * 128) {
+          const long long r = it / per_row;
+          const int c = (int)(it % per_row) * 8;
+          uint4 a = *reinterpret_cast<const uint4*>(src + r * ph.v_ld + c);
+          float v[8] = {bf16_lo(a.x), bf16_hi(a.x), bf16_lo(a.y), bf16_hi(a.y),
+                        bf16_lo(a.z), bf16_hi(a.z), bf16_lo(a.w), bf16_hi(a.w)};
+          if (cin) {
+            uint4 b = __ldcg(reinterpret_cast<const uint4*>(cin + r * ph.v_cols + c));
+            v[0] += bf16_lo(b.x); v[1] += bf16_hi(b.x); v[2] += bf16_lo(b.y); v[3] += bf16_hi(b.y);
+            v[4] += bf16_lo(b.z); v[5] += bf16_hi(b.z); v[6] += bf16_lo(b.w); v[7] += bf16_hi(b.w);
+          }
+          *reinterpret_cast<uint4*>(outp + r * ph.v_cols + c) =
+              make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        }
+      }
       for (int t = cta; t < total && ok; t += G) {
         const int m0 = (t % tiles_m) * kBM;
         const int n0 = (t / tiles_m) * ph.bn;
@@ -290,7 +341,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             }
             if (ph.bias) {
               const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(ph.bias) + col;
-              for (int i = 0; i < nvalid; ++i) v[i] += __bfloat162float(__ldcg(bp + i));
+              if (nvalid == 8 && (reinterpret_cast<uintptr_t>(bp) & 15) == 0) {
+                const uint4 b = __ldcg(reinterpret_cast<const uint4*>(bp));   // one 16-byte load for 8 columns
+                v[0] += bf16_lo(b.x); v[1] += bf16_hi(b.x); v[2] += bf16_lo(b.y); v[3] += bf16_hi(b.y);
+                v[4] += bf16_lo(b.z); v[5] += bf16_hi(b.z); v[6] += bf16_lo(b.w); v[7] += bf16_hi(b.w);
+              } else {
+                for (int i = 0; i < nvalid; ++i) v[i] += __bfloat162float(__ldcg(bp + i));
+              }
             }
             if (ph.act == 1) {
 #pragma unroll

@@ -34,7 +34,23 @@ struct RtpFlagBlock {
   RtpFlagWord status;               // 0 = ok, else first error code
 };
 
+#define RTP_KIND_GEMM 0
+#define RTP_KIND_GATHER 1   // embedding lookup from a visiting table shard
+#define RTP_KIND_VECADD 2   // out[r, c] = src[r, c] (+ in[r, c]): one hop of a ring reduce-scatter
+
 struct RtpPhase {
+  int kind;
+  // ---- RTP_KIND_GATHER: out[t, c] = dropout(table[ids[t], c] * scale + pe[t / tpp, col_off + c]); out = d (pitch ldd)
+  const void* g_table;       // [V, g_cols] bf16, home shard or a workspace slot
+  const long long* g_ids;
+  int g_tokens, g_cols, g_dim, g_col_off, g_tpp;
+  float g_scale;
+  const void* g_pe;
+  long long g_ldpe;
+  // ---- RTP_KIND_VECADD: d[r, c] = v_src[r * v_ld + c] (+ c[r, c]);  d and c are dense [v_rows, v_cols]
+  const void* v_src;
+  long long v_ld;
+  int v_rows, v_cols;
   // operands (bf16). *_mn = 1: the operand is stored with its M (or N) index contiguous.
   int a_map, b_map;
   int a_mn, b_mn;
@@ -90,6 +106,7 @@ struct alignas(64) RtpProgram {
   RtpPhase phases[RTP_MAX_PHASES];
   RtpPush pushes[RTP_MAX_PUSHES];
   int n_phases, n_pushes;
+  int n_stages, stage_bytes;  // smem pipeline geometry (host: finalize_program)
   RtpFlagBlock* flags;  // this rank's flag block (may be null when nothing synchronises)
   int uses_inc[RTP_NUM_CTR];  // added to flags->uses[] by the last CTA of the launch
   unsigned long long* status;  // status word (flags->status or a plain device word)

@@ -555,14 +555,27 @@ __global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int
   } else {
     for (int i = 0; i < cnt; ++i) { pv[i] = __bfloat162float(p[i]); gv[i] = __bfloat162float(g[i]); }
   }
+  const bool svec = cnt == 8 && ((reinterpret_cast<uintptr_t>(t.m) | reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
   if (t.state_fp32) {
     float* m = reinterpret_cast<float*>(t.m) + i0;
     float* v = reinterpret_cast<float*>(t.v) + i0;
-    for (int i = 0; i < cnt; ++i) { mv[i] = m[i]; vv[i] = v[i]; }
+    if (svec) {
+      const float4 a = reinterpret_cast<const float4*>(m)[0], b = reinterpret_cast<const float4*>(m)[1];
+      const float4 c = reinterpret_cast<const float4*>(v)[0], d = reinterpret_cast<const float4*>(v)[1];
+      mv[0] = a.x; mv[1] = a.y; mv[2] = a.z; mv[3] = a.w; mv[4] = b.x; mv[5] = b.y; mv[6] = b.z; mv[7] = b.w;
+      vv[0] = c.x; vv[1] = c.y; vv[2] = c.z; vv[3] = c.w; vv[4] = d.x; vv[5] = d.y; vv[6] = d.z; vv[7] = d.w;
+    } else {
+      for (int i = 0; i < cnt; ++i) { mv[i] = m[i]; vv[i] = v[i]; }
+    }
   } else {
     const __nv_bfloat16* m = reinterpret_cast<const __nv_bfloat16*>(t.m) + i0;
     const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(t.v) + i0;
-    for (int i = 0; i < cnt; ++i) { mv[i] = __bfloat162float(m[i]); vv[i] = __bfloat162float(v[i]); }
+    if (svec) {
+      unpack8(*reinterpret_cast<const uint4*>(m), mv);
+      unpack8(*reinterpret_cast<const uint4*>(v), vv);
+    } else {
+      for (int i = 0; i < cnt; ++i) { mv[i] = __bfloat162float(m[i]); vv[i] = __bfloat162float(v[i]); }
+    }
   }
   for (int i = 0; i < cnt; ++i) {
     float gg = gv[i] * grad_scale;
@@ -579,11 +592,23 @@ __global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int
   if (t.state_fp32) {
     float* m = reinterpret_cast<float*>(t.m) + i0;
     float* v = reinterpret_cast<float*>(t.v) + i0;
-    for (int i = 0; i < cnt; ++i) { m[i] = mv[i]; v[i] = vv[i]; }
+    if (svec) {
+      reinterpret_cast<float4*>(m)[0] = make_float4(mv[0], mv[1], mv[2], mv[3]);
+      reinterpret_cast<float4*>(m)[1] = make_float4(mv[4], mv[5], mv[6], mv[7]);
+      reinterpret_cast<float4*>(v)[0] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      reinterpret_cast<float4*>(v)[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    } else {
+      for (int i = 0; i < cnt; ++i) { m[i] = mv[i]; v[i] = vv[i]; }
+    }
   } else {
     __nv_bfloat16* m = reinterpret_cast<__nv_bfloat16*>(t.m) + i0;
     __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(t.v) + i0;
-    for (int i = 0; i < cnt; ++i) { m[i] = __float2bfloat16(mv[i]); v[i] = __float2bfloat16(vv[i]); }
+    if (svec) {
+      *reinterpret_cast<uint4*>(m) = pack8(mv);
+      *reinterpret_cast<uint4*>(v) = pack8(vv);
+    } else {
+      for (int i = 0; i < cnt; ++i) { m[i] = __float2bfloat16(mv[i]); v[i] = __float2bfloat16(vv[i]); }
+    }
   }
 }
 

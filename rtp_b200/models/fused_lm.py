@@ -176,6 +176,8 @@ class FusedLMTrainer:
         st["dctx"] = torch.empty(M, D, dtype=bf, device=dev)
         st["dqkv"] = torch.empty(M, 3 * D, dtype=bf, device=dev)
         st["dbias"] = torch.empty(max(3 * D, V, H), dtype=torch.float32, device=dev)
+        if self.N > 1:
+            st["emb_dense"] = torch.empty(V, D, dtype=bf, device=dev)
         return st
 
     # ------------------------------------------------------------------------------------------

@@ -66,6 +66,22 @@ class LinearBwd(C.Structure):
     ]
 
 
+class EmbedFwd(C.Structure):
+    _fields_ = [
+        ("home", C.c_void_p), ("shard_bytes", C.c_ulonglong),
+        ("V", C.c_int), ("Ds", C.c_int), ("D", C.c_int),
+        ("ids", C.c_void_p), ("T", C.c_int),
+        ("out", C.c_void_p), ("ld_out", C.c_longlong),
+        ("scale", C.c_float),
+        ("pe", C.c_void_p), ("ld_pe", C.c_longlong), ("tokens_per_pos", C.c_int),
+        ("drop_p", C.c_float), ("seed", C.c_ulonglong), ("offset", C.c_ulonglong), ("step_ptr", C.c_void_p),
+    ]
+
+
+class ReduceScatter(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("ld", C.c_longlong), ("rows", C.c_int), ("cols", C.c_int), ("out", C.c_void_p)]
+
+
 def available() -> bool:
     """True when the compiled library exists and a CUDA device is present."""
     return os.path.exists(LIB_PATH) and torch.cuda.is_available()
@@ -101,6 +117,10 @@ def lib():
         L.rtp_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
         L.rtp_linear_fwd.argtypes = [C.POINTER(Ring), C.POINTER(LinearFwd), C.c_void_p]
         L.rtp_linear_bwd.argtypes = [C.POINTER(Ring), C.POINTER(LinearBwd), C.c_void_p]
+        L.rtp_embed_fwd_rot.argtypes = [C.POINTER(Ring), C.POINTER(EmbedFwd), C.c_void_p]
+        L.rtp_reduce_scatter_cols.argtypes = [C.POINTER(Ring), C.POINTER(ReduceScatter), C.c_void_p]
+        L.rtp_embed_fwd_rot_emu.argtypes = [C.POINTER(Ring), C.POINTER(EmbedFwd), C.c_int, C.c_void_p]
+        L.rtp_reduce_scatter_cols_emu.argtypes = [C.POINTER(Ring), C.POINTER(ReduceScatter), C.c_int, C.c_void_p]
         L.rtp_linear_fwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(LinearFwd), C.c_int, C.c_void_p]
         L.rtp_linear_bwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(LinearBwd), C.c_int, C.c_void_p]
         _lib = L

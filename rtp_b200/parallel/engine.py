@@ -177,8 +177,45 @@ def fused_linear(module, x, row=False):
 
 
 def embed_fwd_rot(eng, flat, V, Ds, ids, out, D, scale, pe, tokens_per_pos, drop_p, seed, offset, step):
-    raise NotImplementedError("fused embedding rotation for rings of more than one rank")
+    """Rotated embedding lookup (+ scale, positional encoding, dropout) in one launch of the rotation kernel."""
+    op = _lib.EmbedFwd()
+    op.home, op.shard_bytes = flat.data_ptr(), _round_up(flat.numel() * 2, 16)
+    op.V, op.Ds, op.D = V, Ds, D
+    op.ids, op.T = ids.data_ptr(), ids.numel()
+    op.out, op.ld_out = out.data_ptr(), out.stride(0)
+    op.scale = scale
+    if pe is not None:
+        op.pe, op.ld_pe = pe.data_ptr(), pe.stride(0)
+    op.tokens_per_pos = tokens_per_pos
+    op.drop_p, op.seed, op.offset = drop_p, seed, offset
+    op.step_ptr = step.data_ptr() if step is not None else None
+    _lib.check(_lib.lib().rtp_embed_fwd_rot(C.byref(eng.ring), C.byref(op), _lib.stream_ptr()), "rtp_embed_fwd_rot")
+    return out
+
+
+def reduce_scatter_cols(eng, src, out):
+    """Ring reduce-scatter of the column blocks of ``src`` [rows, N*cols]; ``out`` [rows, cols] receives the
+    sum over ranks of this rank's block."""
+    op = _lib.ReduceScatter()
+    op.src, op.ld = src.data_ptr(), src.stride(0)
+    op.rows, op.cols = out.shape[0], out.shape[1]
+    op.out = out.data_ptr()
+    _lib.check(_lib.lib().rtp_reduce_scatter_cols(C.byref(eng.ring), C.byref(op), _lib.stream_ptr()),
+               "rtp_reduce_scatter_cols")
+    return out
 
 
 def embed_bwd_rot(eng, trainer, st, dx0):
-    raise NotImplementedError("fused embedding rotation for rings of more than one rank")
+    """Embedding backward on a ring: dense local scatter-add into a [V, D] buffer, then a ring reduce-scatter
+    over the embedding-dim blocks delivers each owner the summed gradient of its [V, D/N] shard."""
+    import math
+    D = trainer.D
+    V = trainer.emb.embedding.weight.shape[0]
+    dense = st.get("emb_dense")
+    if dense is None:
+        dense = torch.empty(V, D, dtype=torch.bfloat16, device=dx0.device)
+        st["emb_dense"] = dense
+    dense.zero_()
+    K.embed_bwd(dense, st["ids"].view(-1), dx0, 0, D=D, scale=math.sqrt(D), drop_p=trainer.p_drop,
+                seed=trainer.seed, offset=1, step=trainer.rng_step)
+    reduce_scatter_cols(eng, dense, trainer.emb._layout.views(trainer.emb_gflat)[0])

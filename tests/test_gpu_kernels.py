@@ -1,0 +1,138 @@
+"""Memory-bound sm_100a kernels vs plain PyTorch fp32 references."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _close(a, b, tol):
+    err = (a.float() - b.float()).abs().max().item()
+    assert err <= tol * max(b.float().abs().max().item(), 1e-6), err
+
+
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_fwd_bwd(rms):
+    from rtp_b200.ops import kernels as K
+    torch.manual_seed(0)
+    M, D = 1000, 2048
+    x = torch.randn(M, D, device="cuda", dtype=BF)
+    sub = torch.randn(M, D, device="cuda", dtype=BF)
+    g = (torch.randn(D, device="cuda") * 0.1 + 1).to(BF)
+    b = None if rms else (torch.randn(D, device="cuda") * 0.1).to(BF)
+    y, h, mean, rstd = K.norm_fwd(x, sub, g, b, rms=rms)
+    hr = (x.float() + sub.float()).to(BF).float().requires_grad_(True)
+    gr = g.float().requires_grad_(True)
+    br = None if rms else b.float().requires_grad_(True)
+    yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-5) * gr if rms else F.layer_norm(hr, (D,), gr, br, 1e-5)
+    _close(y, yr, 1e-2)
+    dy = torch.randn(M, D, device="cuda", dtype=BF)
+    yr.backward(dy.float())
+    dx, dsub, dg, db = K.norm_bwd(dy, h, g, mean, rstd, rms=rms, has_beta=not rms)
+    _close(dx, hr.grad, 1e-2)
+    _close(dsub, hr.grad, 1e-2)
+    _close(dg, gr.grad, 1e-2)
+    if not rms:
+        _close(db, br.grad, 1e-2)
+
+
+def test_norm_dropout_mask_is_reproduced_in_backward():
+    from rtp_b200.ops import kernels as K
+    torch.manual_seed(0)
+    M, D = 512, 1024
+    x = torch.zeros(M, D, device="cuda", dtype=BF)
+    sub = torch.ones(M, D, device="cuda", dtype=BF)
+    g = torch.ones(D, device="cuda", dtype=BF)
+    y, h, mean, rstd = K.norm_fwd(x, sub, g, None, rms=True, drop_p=0.3, seed=5, offset=9)
+    kept = h != 0
+    assert abs(kept.float().mean().item() - 0.7) < 0.01
+    dy = torch.ones(M, D, device="cuda", dtype=BF)
+    dx, dsub, _, _ = K.norm_bwd(dy, h, g, mean, rstd, rms=True, has_beta=False, drop_p=0.3, seed=5, offset=9)
+    same = ((dsub != 0) == kept) | (dx == 0)
+    assert same.float().mean().item() > 0.999
+
+
+def test_cross_entropy():
+    from rtp_b200.ops import kernels as K
+    torch.manual_seed(0)
+    M, V = 1000, 10240
+    lg = (torch.randn(M, V, device="cuda") * 3).to(BF)
+    t = torch.randint(0, V, (M,), device="cuda")
+    t[5] = -100
+    lr = lg.float().requires_grad_(True)
+    lossr = F.cross_entropy(lr, t, reduction="none", ignore_index=-100)
+    (lossr.sum() * 0.5).backward()
+    l2 = lg.clone()
+    loss = K.cross_entropy_(l2, t, grad_scale=0.5)
+    _close(loss, lossr, 1e-3)
+    _close(l2, lr.grad, 2e-2)
+
+
+def test_embedding_shards():
+    from rtp_b200.ops import kernels as K
+    torch.manual_seed(0)
+    V, D, S, B, N = 1024, 256, 32, 8, 2
+    Ds = D // N
+    table = torch.randn(V, D, device="cuda", dtype=BF)
+    ids = torch.randint(0, V, (S, B), device="cuda")
+    pe = torch.randn(64, D, device="cuda", dtype=BF)
+    out = torch.empty(S * B, D, device="cuda", dtype=BF)
+    for j in range(N):
+        K.embed_fwd(table[:, j * Ds:(j + 1) * Ds].contiguous(), ids.view(-1), out, j * Ds, D=D, scale=16.0, pe=pe,
+                    tokens_per_pos=B)
+    r = table[ids.view(-1)].float() * 16.0 + pe[:S].float().repeat_interleave(B, 0)
+    _close(out, r, 1e-2)
+    dy = torch.randn(S * B, D, device="cuda", dtype=BF)
+    gt = torch.zeros(V, Ds, device="cuda", dtype=BF)
+    K.embed_bwd(gt, ids.view(-1), dy, Ds, D=D, scale=16.0)
+    rr = torch.zeros(V, Ds, device="cuda").index_add_(0, ids.view(-1), dy[:, Ds:2 * Ds].float() * 16.0)
+    _close(gt, rr, 3e-2)
+
+
+@pytest.mark.parametrize("S,B,H,N", [(32, 4, 8, 1), (32, 4, 8, 2), (64, 2, 4, 4), (96, 2, 2, 1), (17, 3, 4, 2)])
+def test_attention_small(S, B, H, N):
+    from rtp_b200.ops import kernels as K
+    torch.manual_seed(0)
+    D = H * 64
+    q, k, v = [torch.randn(S, B, H, 64, device="cuda") for _ in range(3)]
+    hp = H // N
+    parts = [t[:, :, j * hp:(j + 1) * hp].reshape(S * B, hp * 64) for j in range(N) for t in (q, k, v)]
+    qkv = torch.cat(parts, 1).to(BF).contiguous()
+    qr, kr, vr = [t.to(BF).float().requires_grad_(True) for t in (q, k, v)]
+    o = F.scaled_dot_product_attention(qr.permute(1, 2, 0, 3), kr.permute(1, 2, 0, 3), vr.permute(1, 2, 0, 3),
+                                       is_causal=True)
+    oref = o.permute(2, 0, 1, 3).reshape(S * B, D)
+    out = K.attn_small_fwd(qkv, S, B, H, nshard=N, causal=True)
+    _close(out, oref, 2e-2)
+    do = torch.randn(S * B, D, device="cuda", dtype=BF)
+    oref.backward(do.float())
+    dqkv = K.attn_small_bwd(qkv, do, S, B, H, nshard=N, causal=True)
+    gparts = [t.grad[:, :, j * hp:(j + 1) * hp].reshape(S * B, hp * 64) for j in range(N) for t in (qr, kr, vr)]
+    _close(dqkv, torch.cat(gparts, 1), 2e-2)
+
+
+def test_colsum_and_adam():
+    from rtp_b200.ops import kernels as K
+    torch.manual_seed(0)
+    x = torch.randn(1000, 2048, device="cuda", dtype=BF)
+    _close(K.colsum(x), x.float().sum(0), 1e-3)
+    for state_dtype in (torch.float32, BF):
+        ps = [torch.randn(n, device="cuda").to(BF) for n in (5000, 2048 * 7 + 3, 100000)]
+        gs = [torch.randn_like(p) for p in ps]
+        ref_p = [p.float().clone().requires_grad_(True) for p in ps]
+        opt = torch.optim.Adam(ref_p, lr=1e-2)
+        ms = [torch.zeros(p.numel(), device="cuda", dtype=state_dtype) for p in ps]
+        vs = [torch.zeros(p.numel(), device="cuda", dtype=state_dtype) for p in ps]
+        plan = K.AdamPlan([(p, g, m, v, 1.0) for p, g, m, v in zip(ps, gs, ms, vs)], "cuda")
+        step = torch.zeros(1, dtype=torch.int64, device="cuda")
+        for _ in range(3):
+            for rp, g in zip(ref_p, gs):
+                rp.grad = g.float().clamp(-0.5, 0.5)
+            opt.step()
+            step += 1
+            plan.step(step, 1e-2, 0.9, 0.999, 1e-8, clip_value=0.5)
+        for p, rp in zip(ps, ref_p):
+            _close(p, rp.detach(), 2e-2)

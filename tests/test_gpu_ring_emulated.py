@@ -1,0 +1,187 @@
+"""Multi-rank rotation protocol on ONE GPU: the kernel is launched cooperatively with N x G CTAs, CTA group e
+plays rank e on its own workspace, so weight pushes, arrival/credit counters and the travelling-gradient ring
+run exactly as across GPUs (peer pointers simply point into the same device)."""
+import ctypes as C
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _close(a, b, tol, what=""):
+    err = (a.float() - b.float()).abs().max().item()
+    assert err <= tol * max(b.float().abs().max().item(), 1e-6), (what, err)
+
+
+def _rings(world, slot_bytes, ctas, L, _lib):
+    wss = []
+    for _ in range(world):
+        p = C.c_void_p()
+        _lib.check(L.rtp_ws_create(slot_bytes, C.byref(p)), "ws")
+        wss.append(p.value)
+    rings = (_lib.Ring * world)()
+    for r in range(world):
+        rings[r].rank, rings[r].world = r, world
+        for q in range(world):
+            rings[r].ws[q] = wss[q]
+        rings[r].slot_bytes, rings[r].ctas, rings[r].timeout_ns = slot_bytes, ctas, 500_000_000
+    return wss, rings
+
+
+def _status_ok(wss, L, _lib):
+    st = C.c_ulonglong(0)
+    for w in wss:
+        L.rtp_ws_status(w, C.byref(st), _lib.stream_ptr())
+        assert st.value == 0, f"rotation kernel reported status {st.value}"
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("shape", [(256, 512, 1024), (1000, 2048, 2048)])
+def test_rotated_linear_fwd_bwd(world, mode, shape):
+    from rtp_b200.ops import _lib, kernels as K
+    L = _lib.lib()
+    torch.manual_seed(0)
+    M, IN, OUT = shape
+    G_ = 148 // world
+    full_w = (torch.randn(OUT, IN, device="cuda") * 0.05).to(BF)
+    full_b = (torch.randn(OUT, device="cuda") * 0.1).to(BF)
+    Os, Ks = (OUT // world, IN) if mode == 0 else (OUT, IN // world)
+    bias_off = (Os * Ks + 63) // 64 * 64
+    nflat = bias_off + (Os + 63) // 64 * 64
+    slot_bytes = (nflat * 2 + 65535) // 65536 * 65536
+    wss, rings = _rings(world, slot_bytes, G_, L, _lib)
+    ops = (_lib.LinearFwd * world)()
+    homes, xs, ys = [], [], []
+    for r in range(world):
+        flat = torch.zeros(nflat, device="cuda", dtype=BF)
+        if mode == 0:
+            flat[:Os * Ks] = full_w[r * Os:(r + 1) * Os].reshape(-1)
+            flat[bias_off:bias_off + Os] = full_b[r * Os:(r + 1) * Os]
+        else:
+            flat[:Os * Ks] = full_w[:, r * Ks:(r + 1) * Ks].reshape(-1)
+            flat[bias_off:bias_off + Os] = (full_b.float() / world).to(BF)
+        x = torch.randn(M, IN, device="cuda", dtype=BF)
+        y = torch.zeros(M, OUT, device="cuda", dtype=BF)
+        homes.append(flat); xs.append(x); ys.append(y)
+        ops[r].mode, ops[r].M, ops[r].in_features, ops[r].out_features = mode, M, IN, OUT
+        ops[r].home, ops[r].bias_off, ops[r].shard_bytes = flat.data_ptr(), bias_off, nflat * 2
+        ops[r].x, ops[r].ldx, ops[r].y, ops[r].ldy = x.data_ptr(), IN, y.data_ptr(), OUT
+    for _ in range(3):      # the counters are monotonic: repeated launches must keep working
+        _lib.check(L.rtp_linear_fwd_emu(rings, ops, world, _lib.stream_ptr()), "fwd_emu")
+    torch.cuda.synchronize()
+    _status_ok(wss, L, _lib)
+    for r in range(world):
+        _close(ys[r], xs[r].float() @ full_w.float().t() + full_b.float(), 1.5e-2, f"fwd rank {r}")
+    bops = (_lib.LinearBwd * world)()
+    dys, dxs, gfs, keep = [], [], [], []
+    for r in range(world):
+        dy = torch.randn(M, OUT, device="cuda", dtype=BF) * 0.1
+        dx = torch.zeros(M, IN, device="cuda", dtype=BF)
+        gf = torch.zeros(nflat, device="cuda", dtype=BF)
+        db = K.colsum(dy)
+        dys.append(dy); dxs.append(dx); gfs.append(gf); keep.append(db)
+        bops[r].mode, bops[r].M, bops[r].in_features, bops[r].out_features = mode, M, IN, OUT
+        bops[r].home, bops[r].bias_off, bops[r].shard_bytes = homes[r].data_ptr(), bias_off, nflat * 2
+        bops[r].x, bops[r].ldx, bops[r].dy, bops[r].ldy = xs[r].data_ptr(), IN, dy.data_ptr(), OUT
+        bops[r].dx, bops[r].lddx = dx.data_ptr(), IN
+        bops[r].grad_home, bops[r].dbias_full = gf.data_ptr(), db.data_ptr()
+    for _ in range(2):
+        _lib.check(L.rtp_linear_bwd_emu(rings, bops, world, _lib.stream_ptr()), "bwd_emu")
+    torch.cuda.synchronize()
+    _status_ok(wss, L, _lib)
+    gw_full = sum(dys[r].float().t() @ xs[r].float() for r in range(world))
+    gb_full = sum(dys[r].float().sum(0) for r in range(world))
+    for r in range(world):
+        _close(dxs[r], dys[r].float() @ full_w.float(), 1.5e-2, f"dx rank {r}")
+        w = gfs[r][:Os * Ks].view(Os, Ks)
+        b = gfs[r][bias_off:bias_off + Os]
+        if mode == 0:
+            _close(w, gw_full[r * Os:(r + 1) * Os], 2e-2, "dW")
+            _close(b, gb_full[r * Os:(r + 1) * Os], 2e-2, "db")
+        else:
+            _close(w, gw_full[:, r * Ks:(r + 1) * Ks], 2e-2, "dW")
+            _close(b, gb_full, 2e-2, "db")
+    for w in wss:
+        L.rtp_ws_destroy(w)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_rotated_embedding_and_reduce_scatter(world):
+    from rtp_b200.ops import _lib
+    L = _lib.lib()
+    torch.manual_seed(0)
+    V, D, S, B = 1000, 512, 32, 8
+    Ds, T, G_ = D // world, S * B, 148 // world
+    table = torch.randn(V, D, device="cuda", dtype=BF)
+    pe = torch.randn(64, D, device="cuda", dtype=BF)
+    slot_bytes = (V * Ds * 2 + 65535) // 65536 * 65536
+    wss, rings = _rings(world, slot_bytes, G_, L, _lib)
+    ops = (_lib.EmbedFwd * world)()
+    keep, idss, outs = [], [], []
+    for r in range(world):
+        home = table[:, r * Ds:(r + 1) * Ds].contiguous()
+        ids = torch.randint(0, V, (T,), device="cuda")
+        out = torch.zeros(T, D, device="cuda", dtype=BF)
+        keep.append(home); idss.append(ids); outs.append(out)
+        ops[r].home, ops[r].shard_bytes = home.data_ptr(), V * Ds * 2
+        ops[r].V, ops[r].Ds, ops[r].D = V, Ds, D
+        ops[r].ids, ops[r].T = ids.data_ptr(), T
+        ops[r].out, ops[r].ld_out, ops[r].scale = out.data_ptr(), D, 3.0
+        ops[r].pe, ops[r].ld_pe, ops[r].tokens_per_pos = pe.data_ptr(), D, B
+    for _ in range(3):
+        _lib.check(L.rtp_embed_fwd_rot_emu(rings, ops, world, _lib.stream_ptr()), "embed emu")
+    torch.cuda.synchronize()
+    _status_ok(wss, L, _lib)
+    for r in range(world):
+        ref = table[idss[r]].float() * 3.0 + pe[:S].float().repeat_interleave(B, 0)
+        _close(outs[r], ref, 1e-2, f"embedding rank {r}")
+    rops = (_lib.ReduceScatter * world)()
+    srcs, routs = [], []
+    for r in range(world):
+        src = torch.randn(V, D, device="cuda", dtype=BF)
+        o = torch.zeros(V, Ds, device="cuda", dtype=BF)
+        srcs.append(src); routs.append(o)
+        rops[r].src, rops[r].ld, rops[r].rows, rops[r].cols, rops[r].out = src.data_ptr(), D, V, Ds, o.data_ptr()
+    for _ in range(2):
+        _lib.check(L.rtp_reduce_scatter_cols_emu(rings, rops, world, _lib.stream_ptr()), "rs emu")
+    torch.cuda.synchronize()
+    _status_ok(wss, L, _lib)
+    tot = sum(s.float() for s in srcs)
+    for r in range(world):
+        _close(routs[r], tot[:, r * Ds:(r + 1) * Ds], 2e-2, f"reduce-scatter rank {r}")
+    for w in wss:
+        L.rtp_ws_destroy(w)
+
+
+def test_missing_producer_times_out_and_returns():
+    """A rank whose peer never runs must not hang: the bounded wait expires, the kernel returns, the status word
+    says which wait gave up and the context stays usable."""
+    from rtp_b200.ops import _lib
+    L = _lib.lib()
+    torch.manual_seed(0)
+    world, M, IN, OUT = 2, 128, 256, 256
+    Os, Ks = OUT // world, IN
+    nflat = Os * Ks + 128
+    slot_bytes = 1 << 17
+    wss, rings = _rings(world, slot_bytes, 8, L, _lib)
+    rings[0].timeout_ns = 200_000_000      # 0.2 s
+    flat = torch.zeros(nflat, device="cuda", dtype=BF)
+    x = torch.randn(M, IN, device="cuda", dtype=BF)
+    y = torch.zeros(M, OUT, device="cuda", dtype=BF)
+    op = _lib.LinearFwd()
+    op.mode, op.M, op.in_features, op.out_features = 0, M, IN, OUT
+    op.home, op.bias_off, op.shard_bytes = flat.data_ptr(), Os * Ks, nflat * 2
+    op.x, op.ldx, op.y, op.ldy = x.data_ptr(), IN, y.data_ptr(), OUT
+    # only rank 0's kernel is launched; nothing ever fills its slot
+    _lib.check(L.rtp_linear_fwd(C.byref(rings[0]), C.byref(op), _lib.stream_ptr()), "fwd")
+    torch.cuda.synchronize()
+    st = C.c_ulonglong(0)
+    L.rtp_ws_status(wss[0], C.byref(st), _lib.stream_ptr())
+    assert st.value == 2, st.value           # "wait for a peer's data timed out"
+    z = torch.ones(4, device="cuda").sum().item()
+    assert z == 4.0                          # the context is alive
+    for w in wss:
+        L.rtp_ws_destroy(w)
