@@ -18,7 +18,7 @@ class ParallelMultiheadAttention(SubParallelMultiheadAttention):
         ctx = get_context(group)
         super().__init__(embed_dim, num_heads, ctx.world, ctx.rank, dropout, bias, add_bias_kv, add_zero_attn, kdim,
                          vdim, batch_first, device, dtype)
-        self.group = ctx.group
+        self.ring = ctx
 
     def forward(self, query: Tensor, key: Tensor, value: Tensor, key_padding_mask: Optional[Tensor] = None,
                 need_weights: bool = True, attn_mask: Optional[Tensor] = None, average_attn_weights: bool = True,

@@ -92,7 +92,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ---------------------------------------------------------------------------------------------
-// TMA (tiled bulk tensor copies, global -> shared, no multicast anywhere in this library)
+// TMA (tiled bulk tensor copies, global -> shared; every copy targets the issuing CTA only)
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(

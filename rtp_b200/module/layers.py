@@ -29,16 +29,16 @@ class ColumnParallelLinear(nn.Module):
                  device=None, dtype=None, linear_layer=None, group=None, **unused):
         super().__init__()
         ctx = _ctx(group, world_size, rank)
-        self.world_size, self.rank, self.group = ctx.world, ctx.rank, ctx.group
+        self.world_size, self.rank, self.ring = ctx.world, ctx.rank, ctx
         self.in_features, self.out_features, self.gather_output = in_features, out_features, gather_output
         self.linear = ModelParallelLinear(in_features, out_features, bias=bias, device=device, dtype=dtype,
                                           world_size=ctx.world, rank=ctx.rank)
         self.linear.affine_weight(linear_layer)
 
     def forward(self, input_):
-        x = copy_to_model_parallel_region(input_, self.group)
+        x = copy_to_model_parallel_region(input_, self.ring.group)
         out = self.linear(x)
-        return gather_from_model_parallel_region(out, self.group) if self.gather_output else out
+        return gather_from_model_parallel_region(out, self.ring.group) if self.gather_output else out
 
 
 class ParallelEmbedding(nn.Module):
@@ -47,7 +47,7 @@ class ParallelEmbedding(nn.Module):
                  group=None, gather_output=True, **unused):
         super().__init__()
         ctx = _ctx(group, world_size, rank)
-        self.world_size, self.rank, self.group, self.gather_output = ctx.world, ctx.rank, ctx.group, gather_output
+        self.world_size, self.rank, self.ring, self.gather_output = ctx.world, ctx.rank, ctx, gather_output
         self.embedding = ModelParallelEmbedding(num_embeddings, embedding_dim, ctx.world, ctx.rank,
                                                 padding_idx=padding_idx, max_norm=max_norm, norm_type=norm_type,
                                                 scale_grad_by_freq=scale_grad_by_freq, sparse=sparse, device=device,
@@ -56,7 +56,7 @@ class ParallelEmbedding(nn.Module):
 
     def forward(self, input_):
         out = self.embedding(input_)
-        return gather_from_model_parallel_region(out, self.group) if self.gather_output else out
+        return gather_from_model_parallel_region(out, self.ring.group) if self.gather_output else out
 
 
 class ParallelMultiheadAttention(nn.Module):
@@ -67,7 +67,7 @@ class ParallelMultiheadAttention(nn.Module):
                  MultiheadAttention_layer=None, group=None):
         super().__init__()
         ctx = _ctx(group, world_size, rank)
-        self.world_size, self.rank, self.group, self.batch_first = ctx.world, ctx.rank, ctx.group, batch_first
+        self.world_size, self.rank, self.ring, self.batch_first = ctx.world, ctx.rank, ctx, batch_first
         self.MultiheadAttention = SubParallelMultiheadAttention(embed_dim, num_heads, ctx.world, ctx.rank, dropout,
                                                                 bias, add_bias_kv, add_zero_attn, kdim, vdim,
                                                                 batch_first, device, dtype)
@@ -80,9 +80,9 @@ class ParallelMultiheadAttention(nn.Module):
         same = (key is value) and (query is key)
         if self.batch_first and batched:
             query, key, value = [t.transpose(1, 0) for t in (query, key, value)]
-        q = copy_to_model_parallel_region(query, self.group)
-        k, v = (q, q) if same else (copy_to_model_parallel_region(key, self.group),
-                                    copy_to_model_parallel_region(value, self.group))
+        q = copy_to_model_parallel_region(query, self.ring.group)
+        k, v = (q, q) if same else (copy_to_model_parallel_region(key, self.ring.group),
+                                    copy_to_model_parallel_region(value, self.ring.group))
         out, w = multi_head_attention_forward(
             q, k, v, sub.embed_dim_per_partition, sub.num_heads_per_partition, sub.in_proj_weight, sub.in_proj_bias,
             sub.bias_k, sub.bias_v, sub.add_zero_attn, sub.dropout, sub.out_proj.weight, sub.out_proj.bias,
@@ -90,7 +90,7 @@ class ParallelMultiheadAttention(nn.Module):
             use_separate_proj_weight=not sub._qkv_same_embed_dim, q_proj_weight=sub.q_proj_weight,
             k_proj_weight=sub.k_proj_weight, v_proj_weight=sub.v_proj_weight,
             average_attn_weights=average_attn_weights, is_causal=is_causal, E_div=self.world_size)
-        out = reduce_from_model_parallel_region(out, self.group)
+        out = reduce_from_model_parallel_region(out, self.ring.group)
         if self.batch_first and batched:
             out = out.transpose(1, 0)
         return out, w
@@ -102,11 +102,11 @@ class ColumnParallelConv2d(nn.Module):
                  Conv2d_layer=None, group=None):
         super().__init__()
         ctx = _ctx(group, world_size, rank)
-        self.world_size, self.rank, self.group, self.gather_output = ctx.world, ctx.rank, ctx.group, gather_output
+        self.world_size, self.rank, self.ring, self.gather_output = ctx.world, ctx.rank, ctx, gather_output
         self.conv = ModelParallelConv2d(in_channels, out_channels, kernel_size, stride, padding, dilation, groups,
                                         bias, padding_mode, device, dtype, world_size=ctx.world, rank=ctx.rank)
         self.conv.affine_weight(Conv2d_layer)
 
     def forward(self, input_):
-        out = self.conv(copy_to_model_parallel_region(input_, self.group))
-        return gather_from_conv_parallel_region(out, self.group) if self.gather_output else out
+        out = self.conv(copy_to_model_parallel_region(input_, self.ring.group))
+        return gather_from_conv_parallel_region(out, self.ring.group) if self.gather_output else out

@@ -46,7 +46,7 @@ class MOELayer(nn.Module):
         self.gate = gate
         self.experts = cast(ModuleList, experts) if isinstance(experts, ModuleList) else ModuleList([experts])
         ctx = get_context(group)
-        self.group, self.world_size = ctx.group, ctx.world
+        self.ring, self.world_size = ctx, ctx.world
         for expert in self.experts:
             for p in expert.parameters():
                 p.expert = True  # type: ignore
@@ -59,12 +59,12 @@ class MOELayer(nn.Module):
         reshaped = input[0].reshape(-1, d_model)
         self.l_aux, combine_weights, dispatch_mask = self.gate(reshaped)
         dispatched = _dispatch(dispatch_mask, reshaped)
-        dispatched = _AllToAll.apply(self.group, dispatched)
+        dispatched = _AllToAll.apply(self.ring.group, dispatched)
         dispatched = dispatched.reshape(self.world_size, self.num_local_experts, -1, d_model)
         chunks = dispatched.chunk(self.num_local_experts, dim=1)
         outs = [expert(chunk) for chunk, expert in zip(chunks, self.experts)]
         expert_output = torch.cat(outs, dim=1)
-        expert_output = _AllToAll.apply(self.group, expert_output)
+        expert_output = _AllToAll.apply(self.ring.group, expert_output)
         expert_output = expert_output.reshape(self.world_size * self.num_local_experts, -1, d_model)
         combined = _combine(combine_weights, expert_output)
         return combined.reshape(input[0].shape)

@@ -34,6 +34,12 @@ class RingContext:
     rank: int
     world: int
 
+    def __deepcopy__(self, memo):
+        return self          # immutable; process groups cannot be copied or pickled
+
+    def __reduce__(self):
+        raise TypeError("a RingContext holds a process group and cannot be pickled")
+
     def global_rank(self, ring_rank: int) -> int:
         """Rank in the default group of ring member ``ring_rank`` (what isend/irecv expect)."""
         if self.group is None or not dist.is_initialized():

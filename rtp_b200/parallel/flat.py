@@ -9,6 +9,7 @@ that travels around the ring (the reference builds the same aliasing with ``set_
 Moving the module (``.to()``, ``.cuda()``, ``.bfloat16()``) re-creates the flat buffer afterwards, so
 dtype/device moves never break the aliasing.
 """
+import copy
 from typing import List
 
 import torch
@@ -31,9 +32,12 @@ class RotatedModule(nn.Module):
             raise ValueError(f"rank={rank} does not match the process group ({self.ring.rank})")
         self.world_size = self.ring.world
         self.rank = self.ring.rank
-        self.group = self.ring.group
         self._displaced = False
         self._last_flat_grad = None
+
+    @property
+    def group(self):
+        return self.ring.group
 
     # -- flat buffer ------------------------------------------------------------------------
     def shard_parameters(self) -> List[nn.Parameter]:
@@ -66,6 +70,16 @@ class RotatedModule(nn.Module):
         if getattr(self, "_layout", None) is not None:
             self._flatten()
         return out
+
+    def __deepcopy__(self, memo):
+        # nn.Parameter.__deepcopy__ clones its data, which would detach the copies from the copied flat buffer
+        new = self.__class__.__new__(self.__class__)
+        memo[id(self)] = new
+        for k, v in self.__dict__.items():
+            new.__dict__[k] = copy.deepcopy(v, memo)
+        if getattr(new, "_layout", None) is not None:
+            new._flatten()
+        return new
 
     @property
     def flat_param(self) -> torch.Tensor:

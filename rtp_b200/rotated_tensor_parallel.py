@@ -106,14 +106,18 @@ class RotatedTensorParallel(nn.Module):
     def __init__(self, module: nn.Module, group: Optional[Any] = None, inplace: bool = False):
         super().__init__()
         ctx = get_context(group)
-        self.group, self.rank, self.world_size = ctx.group, ctx.rank, ctx.world
+        self.ring, self.rank, self.world_size = ctx, ctx.rank, ctx.world
         self.inplace = inplace
         self.FlyweightModule_list: List[FlyweightWarpper] = []
         self.module = self._visit(module)
 
+    @property
+    def group(self):
+        return self.ring.group
+
     # -- recursive replacement ---------------------------------------------------------------
     def _wrap(self, shard, rules, **kw):
-        fw = FlyweightWarpper(shard, group=self.group, inplace=self.inplace, **kw)
+        fw = FlyweightWarpper(shard, group=self.ring.group, inplace=self.inplace, **kw)
         fw._shard_rules = rules
         self.FlyweightModule_list.append(fw)
         return fw
@@ -174,7 +178,7 @@ class RotatedTensorParallel(nn.Module):
         s = ParallelMultiheadAttention(m.embed_dim, m.num_heads, dropout=m.dropout, bias=m.in_proj_bias is not None,
                                        add_bias_kv=m.bias_k is not None, add_zero_attn=m.add_zero_attn, kdim=m.kdim,
                                        vdim=m.vdim, batch_first=m.batch_first, device=m.out_proj.weight.device,
-                                       dtype=m.out_proj.weight.dtype, group=self.group)
+                                       dtype=m.out_proj.weight.dtype, group=self.ring.group)
         s.affine_weight(m)
         kinds = {"in_proj_weight": ("qkv", 0), "in_proj_bias": ("qkv", 0), "q_proj_weight": ("split", 0),
                  "k_proj_weight": ("split", 0), "v_proj_weight": ("split", 0), "out_proj.weight": ("split", 1),

@@ -1,0 +1,26 @@
+"""Fused rotation across real GPUs (2, and 4/8 when present): child processes under torchrun, one per GPU.
+NVLS is switched off for NCCL and the library's own kernels use plain peer stores only."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(world):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29700 + world), os.path.join(HERE, "_multi_gpu_worker.py")]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and "MULTI_GPU_OK" in p.stdout, p.stdout[-4000:] + p.stderr[-4000:]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_ring_matches_functional(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run(world)
