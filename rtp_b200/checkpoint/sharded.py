@@ -22,7 +22,7 @@ def sharding_plan(model: torch.nn.Module) -> Dict[str, Tuple]:
     """Map state_dict key -> rule for every tensor that is sharded: ("split", dim), ("qkv", dim),
     ("sum",) for biases stored as b/N, ("expert", L) for whole local experts. Other keys are replicated."""
     plan = {}
-    for path, mod in model.named_modules():
+    for path, mod in model.named_modules(remove_duplicate=False):
         if isinstance(mod, RotatedModule):
             for k, rule in mod.shard_spec().items():
                 plan[f"{path}.{k}" if path else k] = tuple(rule)
@@ -33,9 +33,10 @@ def _shard_tensor(full: torch.Tensor, rule: Tuple, rank: int, world: int) -> tor
     kind = rule[0]
     if kind == "split":
         return torch.chunk(full, world, dim=rule[1])[rank].clone()
-    if kind == "qkv":
-        blocks = torch.chunk(full, 3 * world, dim=rule[1])
-        return torch.cat([blocks[rank], blocks[rank + world], blocks[rank + 2 * world]], dim=rule[1])
+    if kind in ("qkv", "packed"):
+        parts = 3 if kind == "qkv" else rule[2]
+        blocks = torch.chunk(full, parts * world, dim=rule[1])
+        return torch.cat([blocks[rank + k * world] for k in range(parts)], dim=rule[1])
     if kind == "sum":
         return full / world
     raise ValueError(kind)
@@ -45,9 +46,10 @@ def _unshard_tensors(shards: List[torch.Tensor], rule: Tuple) -> torch.Tensor:
     kind, world = rule[0], len(shards)
     if kind == "split":
         return torch.cat(shards, dim=rule[1])
-    if kind == "qkv":
-        parts = [torch.chunk(s, 3, dim=rule[1]) for s in shards]
-        return torch.cat([parts[r][k] for k in range(3) for r in range(world)], dim=rule[1])
+    if kind in ("qkv", "packed"):
+        n = 3 if kind == "qkv" else rule[2]
+        parts = [torch.chunk(s, n, dim=rule[1]) for s in shards]
+        return torch.cat([parts[r][k] for k in range(n) for r in range(world)], dim=rule[1])
     if kind == "sum":
         return shards[0] * world
     raise ValueError(kind)

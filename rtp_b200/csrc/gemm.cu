@@ -109,10 +109,19 @@ uint32_t drop_threshold(float p) {
 
 // Pipeline geometry: the stage must hold the widest B tile of the program; narrower tiles get more stages.
 int g_force_stages = 0;
-void finalize_program(RtpProgram& P) {
+void finalize_program(RtpProgram& P, int ctas) {
+  long long acc = 0;
+  for (int i = 0; i < P.n_phases; ++i) {
+    RtpPhase& ph = P.phases[i];
+    if (ph.kind != RTP_KIND_GEMM) { ph.cta_off = 0; continue; }
+    const long long tiles = (long long)((ph.M + 127) / 128) * ((ph.N + ph.bn - 1) / ph.bn);
+    ph.cta_off = (int)(acc % ctas);
+    acc += tiles;
+  }
   int bn = 128;
   for (int i = 0; i < P.n_phases; ++i)
     if (P.phases[i].kind == RTP_KIND_GEMM && P.phases[i].bn > bn) bn = P.phases[i].bn;
+  // spread the tiles of successive phases over the grid (ctas = grid size of one rank)
   P.stage_bytes = rtp::kABytes + bn * rtp::kBK * 2;
   P.n_stages = rtp::kTileBytes / P.stage_bytes;
   if (P.n_stages > rtp::kMaxStages) P.n_stages = rtp::kMaxStages;
@@ -142,7 +151,7 @@ int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cuda
   }
   cfg.attrs = at;
   cfg.numAttrs = nat;
-  for (int e = 0; e < NEMU; ++e) finalize_program(const_cast<RtpProgram&>(params.prog[e]));
+  for (int e = 0; e < NEMU; ++e) finalize_program(const_cast<RtpProgram&>(params.prog[e]), params.ctas_per_rank);
   cudaError_t e = cudaLaunchKernelEx(&cfg, rtp::rtp_gemm_kernel<NEMU>, params);
   if (e != cudaSuccess) return fail(std::string("launch rtp_gemm_kernel: ") + cudaGetErrorString(e));
   return 0;

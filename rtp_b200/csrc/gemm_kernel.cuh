@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
   const int kStageBytes = P.stage_bytes;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   unsigned long long* status = P.status;
-  const unsigned long long timeout_ns = P.timeout_ns;
+  const unsigned long long wait_ns = P.timeout_ns;           // cross-rank counter waits
+  const unsigned long long timeout_ns = 2 * P.timeout_ns;   // CTA-internal mbarrier waits (report the root cause first)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -101,12 +102,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const int tiles_m = (ph.M + kBM - 1) / kBM;
         const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
         const int total = tiles_m * tiles_n;
-        if (cta >= total) continue;
+        if ((cta - ph.cta_off + G) % G >= total) continue;
         for (int w = 0; w < 2 && ok; ++w) {
           if (ph.wait_ctr[w] >= 0) {
             ok = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
                                  fill_target(P.flags, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
-                                 timeout_ns, ST_TIMEOUT_ARRIVAL);
+                                 wait_ns, ST_TIMEOUT_ARRIVAL);
           }
         }
         if (!ok) break;
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const CUtensorMap* mb = &P.maps[ph.b_map];
         const int kblocks = (ph.K + kBK - 1) / kBK;
         const uint32_t tx = kABytes + ph.bn * kBK * 2;
-        for (int t = cta; t < total && ok; t += G) {
+        for (int t = (cta - ph.cta_off + G) % G; t < total && ok; t += G) {
           const int m0 = (t % tiles_m) * kBM;
           const int n0 = (t / tiles_m) * ph.bn;
           for (int kb = 0; kb < kblocks; ++kb) {
@@ -172,7 +173,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const uint32_t idesc = make_idesc_bf16(kBM, ph.bn, ph.a_mn, ph.b_mn);
         const uint32_t a_lbo = ph.a_mn ? 8192u : 16u, b_lbo = ph.b_mn ? 8192u : 16u;
         const uint32_t a_kstep = ph.a_mn ? 2048u : 32u, b_kstep = ph.b_mn ? 2048u : 32u;
-        for (int t = cta; t < total && ok; t += G) {
+        for (int t = (cta - ph.cta_off + G) % G; t < total && ok; t += G) {
           if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
@@ -232,10 +233,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             if (ph.wait_ctr[w] >= 0)
               good = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
                                      fill_target(P.flags, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
-                                     timeout_ns, ST_TIMEOUT_ARRIVAL);
+                                     wait_ns, ST_TIMEOUT_ARRIVAL);
           if (good && ph.credit_ptr)
             good = wait_counter_ge(ph.credit_ptr, fill_target(P.flags, ph.credit_ctr, ph.credit_rel, 0, G),
-                                   abort_flag, status, timeout_ns, ST_TIMEOUT_CREDIT);
+                                   abort_flag, status, wait_ns, ST_TIMEOUT_CREDIT);
         }
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) ok = false;
@@ -290,7 +291,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
               make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
         }
       }
-      for (int t = cta; t < total && ok; t += G) {
+      for (int t = (cta - ph.cta_off + G) % G; t < total && ok; t += G) {
         const int m0 = (t % tiles_m) * kBM;
         const int n0 = (t / tiles_m) * ph.bn;
         uint32_t good = 1;
@@ -437,7 +438,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       uint32_t good = 1;
       if (ok && lane == 0 && pu.credit_ptr)
         good = wait_counter_ge(pu.credit_ptr, fill_target(P.flags, pu.credit_ctr, pu.credit_rel, 0, G), abort_flag,
-                               status, timeout_ns, ST_TIMEOUT_CREDIT);
+                               status, wait_ns, ST_TIMEOUT_CREDIT);
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) ok = false;
       if (ok) {

@@ -58,6 +58,7 @@ struct RtpPhase {
   int b_off_mn, b_off_k;
   int M, N, K;
   int bn;  // tile width: 128 or 256
+  int cta_off;  // tile t of this phase runs on CTA (t + cta_off) % G, so that successive phases fill different SMs
   // epilogue
   void* d;
   long long ldd;

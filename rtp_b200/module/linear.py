@@ -68,9 +68,12 @@ class _RotatedLinearBase(RotatedModule):
                  init_method: Callable[[torch.Tensor], torch.Tensor] = init.xavier_normal_, stride: int = 1,
                  keep_master_weight_for_test: bool = False, device=None, dtype=None, group=None,
                  linear_layer: Optional[nn.Linear] = None, world_size: Optional[int] = None,
-                 rank: Optional[int] = None):
+                 rank: Optional[int] = None, packed_parts: int = 1):
         super().__init__()
         self._setup_ring(group, world_size, rank)
+        # packed_parts > 1: the full weight stacks `packed_parts` equally sized projections along the output dim
+        # (e.g. q, k, v) and every shard holds its slice of EACH of them: rows [p0_r; p1_r; ...]
+        self.packed_parts = packed_parts
         self.in_features, self.out_features = in_features, out_features
         self.gather_weight = gather_weight
         cls = ModelParallelLinear2 if self.row else ModelParallelLinear
@@ -96,9 +99,10 @@ class _RotatedLinearBase(RotatedModule):
             if self.linear.bias is not None:
                 spec["linear.bias"] = ("sum",)
         else:
-            spec = {"linear.weight": ("split", 0)}
+            rule = ("split", 0) if self.packed_parts == 1 else ("packed", 0, self.packed_parts)
+            spec = {"linear.weight": rule}
             if self.linear.bias is not None:
-                spec["linear.bias"] = ("split", 0)
+                spec["linear.bias"] = rule
         return spec
 
     @property

@@ -106,7 +106,8 @@ class WeightMOELayer(RotatedModule):
     def forward(self, *input: Tensor, **kwargs: Any) -> Tensor:
         assert len(input) == 1, "only single input Tensor supported"
         assert len(input[0].shape) == 3, "input Tensor must have dimensions: (s)equence, (t)oken, (m)odel"
-        assert input[0].shape[0] % len(self.experts) == 0, "num tokens must be order of number of local experts"
+        assert (input[0].shape[0] * input[0].shape[1]) % len(self.experts) == 0, \
+            "number of tokens must be a multiple of the number of local experts"
         d_model = input[0].shape[2]
         reshaped = input[0].reshape(-1, d_model)
         self.l_aux, combine_weights, dispatch_mask = self.gate(reshaped)

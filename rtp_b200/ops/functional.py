@@ -1,0 +1,109 @@
+"""Autograd front-ends of the sm_100a kernels for models written against the module API.
+
+``use_kernels(x)`` is true for bf16 CUDA tensors unless the functional backend was requested; every function
+below has a plain PyTorch evaluation for CPU / fp32 tensors so that the same model code runs on gloo."""
+import torch
+import torch.nn.functional as F
+
+from ..parallel.context import get_backend
+
+
+def use_kernels(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16 and get_backend() != "functional"
+
+
+class _NormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, rms):
+        from . import kernels as K
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        y, h, mean, rstd = K.norm_fwd(x2, None, weight, bias, eps=eps, rms=rms, save_h=False)
+        ctx.save_for_backward(x2, weight, mean, rstd)
+        ctx.rms, ctx.has_bias, ctx.shape = rms, bias is not None, x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import kernels as K
+        x2, weight, mean, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dx, _, dg, db = K.norm_bwd(dy2, x2, weight, mean, rstd, rms=ctx.rms, has_beta=ctx.has_bias, want_dsub=False)
+        return dx.view(ctx.shape), dg.to(weight.dtype), (db.to(weight.dtype) if ctx.has_bias else None), None, None
+
+
+def layer_norm(x, weight, bias, eps=1e-5):
+    if use_kernels(x) and x.shape[-1] % 8 == 0:
+        return _NormFn.apply(x, weight, bias, eps, False)
+    return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+
+
+def rms_norm(x, weight, eps=1e-5):
+    if use_kernels(x) and x.shape[-1] % 8 == 0:
+        return _NormFn.apply(x, weight, None, eps, True)
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
+
+
+class _CrossEntropyFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, target, ignore_index):
+        from . import kernels as K
+        lg = logits.reshape(-1, logits.shape[-1])
+        work = lg.clone() if (not lg.is_contiguous() or logits.requires_grad) else lg
+        work = work.contiguous()
+        t = target.reshape(-1)
+        n = (t != ignore_index).sum().clamp(min=1)
+        rows = K.cross_entropy_(work, t, grad_scale=1.0, ignore_index=ignore_index)
+        ctx.save_for_backward(work, n)
+        ctx.shape = logits.shape
+        return rows.sum() / n
+
+    @staticmethod
+    def backward(ctx, g):
+        work, n = ctx.saved_tensors
+        return (work * (g / n).to(work.dtype)).view(ctx.shape), None, None
+
+
+def cross_entropy(logits, target, ignore_index=-100):
+    """Mean token cross-entropy; the softmax gradient is produced in the same pass over the logits."""
+    if use_kernels(logits) and logits.shape[-1] % 8 == 0:
+        return _CrossEntropyFn.apply(logits, target, ignore_index)
+    return F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), target.reshape(-1), ignore_index=ignore_index)
+
+
+class _SmallAttnFn(torch.autograd.Function):
+    """q, k, v: [B, S, H, 64] -> [B, S, H, 64]; runs the short-sequence kernel on a packed [S*B, 3*H*64] buffer."""
+
+    @staticmethod
+    def forward(ctx, q, k, v):
+        from . import kernels as K
+        B, S, H, hd = q.shape
+        packed = torch.cat([t.permute(1, 0, 2, 3).reshape(S * B, H * hd) for t in (q, k, v)], dim=1).contiguous()
+        out = K.attn_small_fwd(packed, S, B, H, nshard=1, causal=True)
+        ctx.save_for_backward(packed)
+        ctx.dims = (B, S, H, hd)
+        return out.view(S, B, H, hd).permute(1, 0, 2, 3)
+
+    @staticmethod
+    def backward(ctx, do):
+        from . import kernels as K
+        (packed,) = ctx.saved_tensors
+        B, S, H, hd = ctx.dims
+        do2 = do.permute(1, 0, 2, 3).reshape(S * B, H * hd).contiguous()
+        dqkv = K.attn_small_bwd(packed, do2, S, B, H, nshard=1, causal=True)
+        D = H * hd
+        parts = [dqkv[:, i * D:(i + 1) * D].view(S, B, H, hd).permute(1, 0, 2, 3) for i in range(3)]
+        return tuple(parts)
+
+
+def causal_attention(q, k, v):
+    """Causal self-attention on [B, S, H, hd] tensors."""
+    B, S, H, hd = q.shape
+    if use_kernels(q) and hd == 64 and S <= 96:
+        return _SmallAttnFn.apply(q, k, v)
+    if use_kernels(q):
+        from .flash import flash_attention_available, flash_attention
+        if flash_attention_available(S, hd):
+            return flash_attention(q, k, v, causal=True)
+    o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+    return o.transpose(1, 2)

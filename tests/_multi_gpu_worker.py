@@ -65,7 +65,7 @@ def main():
             x.grad = None
 
     # ---- whole LM: fused trainer vs functional autograd path
-    V, D, H, NH, L, S, B = 1024, 256, 1024, 8, 2, 32, 8
+    V, D, H, NH, L, S, B = 1024, 512, 1024, 8, 2, 32, 8
     torch.manual_seed(0)
     full = PlainLM(V, D, NH, H, 0.0, 0.1, L)
     g = torch.Generator().manual_seed(1)
