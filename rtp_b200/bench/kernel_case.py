@@ -1,0 +1,142 @@
+"""Single-kernel cases for timing and profiling (used by the ncu summaries under profiles/).
+
+    python -m rtp_b200.bench.kernel_case gemm --m 8192 --n 4096 --k 4096 --layout nt --iters 5
+    python -m rtp_b200.bench.kernel_case norm_fwd --m 65536 --d 2048
+    python -m rtp_b200.bench.kernel_case adam --n 200000000
+
+Every case allocates inputs larger than the 126 MB L2 (or cycles through several copies), runs 2 warm-up launches and
+``--iters`` timed launches (CUDA events) and prints achieved TFLOP/s or GB/s next to the measured peaks of
+MEASURED_PEAKS.json when that file is present."""
+import argparse
+import json
+import os
+
+import torch
+
+
+def _peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            d = json.load(f)
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def _time(fn, iters, warm=2):
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(warm + i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm", "norm_fwd", "norm_bwd", "ce", "adam", "attn_fwd", "attn_bwd", "colsum",
+                                     "embed"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--d", type=int, default=2048)
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--copies", type=int, default=4, help="operand copies cycled through so that inputs are cold")
+    ap.add_argument("--seq", type=int, default=32)
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--heads", type=int, default=32)
+    a = ap.parse_args(argv)
+    from ..ops import gemm as G, kernels as K, _lib
+    dev, bf = "cuda", torch.bfloat16
+    hbm, tf, src = _peaks()
+    torch.manual_seed(0)
+    if a.case == "gemm":
+        M, N, Kd = a.m, a.n, a.k
+        a_mn = a.layout == "tn"
+        b_mn = a.layout in ("nn", "tn")
+        As = [torch.randn((Kd, M) if a_mn else (M, Kd), device=dev, dtype=bf) for _ in range(a.copies)]
+        Bs = [torch.randn((Kd, N) if b_mn else (N, Kd), device=dev, dtype=bf) for _ in range(a.copies)]
+        out = torch.empty(M, N, device=dev, dtype=bf)
+        bias = torch.randn(N, device=dev, dtype=bf) if a.bias else None
+        ms = _time(lambda i: G.gemm(As[i % a.copies], Bs[i % a.copies], a_mn=a_mn, b_mn=b_mn, out=out, bn=a.bn,
+                                    bias=bias), a.iters)
+        _lib.check_status()
+        t = 2.0 * M * N * Kd / ms / 1e9
+        print(json.dumps({"case": "gemm", "layout": a.layout, "M": M, "N": N, "K": Kd, "us": ms * 1e3, "tflops": t,
+                          "frac_of_cublas_peak": t / tf, "peaks": src}))
+        return
+    if a.case in ("norm_fwd", "norm_bwd"):
+        M, D = a.m * 8, a.d
+        x = torch.randn(M, D, device=dev, dtype=bf)
+        sub = torch.randn(M, D, device=dev, dtype=bf)
+        g = torch.ones(D, device=dev, dtype=bf)
+        b = torch.zeros(D, device=dev, dtype=bf)
+        if a.case == "norm_fwd":
+            ms = _time(lambda i: K.norm_fwd(x, sub, g, b, drop_p=0.1, seed=1, offset=i), a.iters)
+            nbytes = 4 * M * D * 2
+        else:
+            y, h, mean, rstd = K.norm_fwd(x, sub, g, b)
+            ms = _time(lambda i: K.norm_bwd(x, h, g, mean, rstd, drop_p=0.1, seed=1, offset=i), a.iters)
+            nbytes = 4 * M * D * 2
+        print(json.dumps({"case": a.case, "M": M, "D": D, "us": ms * 1e3, "GBs": nbytes / ms / 1e6,
+                          "frac_of_copy_peak": nbytes / ms / 1e6 / hbm, "peaks": src}))
+        return
+    if a.case == "ce":
+        M, V = a.m, 10240
+        lg = [torch.randn(M, V, device=dev, dtype=bf) for _ in range(2)]
+        t = torch.randint(0, V, (M,), device=dev)
+        ms = _time(lambda i: K.cross_entropy_(lg[i % 2], t), a.iters)
+        nbytes = M * V * 2 * 4        # three reads + one write of the row
+        print(json.dumps({"case": "ce", "M": M, "V": V, "us": ms * 1e3, "GBs": nbytes / ms / 1e6,
+                          "frac_of_copy_peak": nbytes / ms / 1e6 / hbm, "peaks": src}))
+        return
+    if a.case == "adam":
+        n = a.n * 1024 * 16 if a.n < 1 << 20 else a.n
+        p = torch.randn(n, device=dev).to(bf)
+        g = torch.randn(n, device=dev).to(bf)
+        m1, m2 = torch.zeros_like(p), torch.zeros_like(p)
+        plan = K.AdamPlan([(p, g, m1, m2, 1.0)], dev)
+        step = torch.ones(1, dtype=torch.int64, device=dev)
+        ms = _time(lambda i: plan.step(step, 1e-3, 0.9, 0.999, 1e-8, clip_value=0.05), a.iters)
+        nbytes = n * 2 * 7
+        print(json.dumps({"case": "adam", "n": n, "us": ms * 1e3, "GBs": nbytes / ms / 1e6,
+                          "frac_of_copy_peak": nbytes / ms / 1e6 / hbm, "peaks": src}))
+        return
+    if a.case in ("attn_fwd", "attn_bwd"):
+        S, B, H = a.seq, a.batch, a.heads
+        qkv = torch.randn(S * B, 3 * H * 64, device=dev, dtype=bf)
+        do = torch.randn(S * B, H * 64, device=dev, dtype=bf)
+        if a.case == "attn_fwd":
+            ms = _time(lambda i: K.attn_small_fwd(qkv, S, B, H, drop_p=0.1, seed=1, offset=i), a.iters)
+        else:
+            ms = _time(lambda i: K.attn_small_bwd(qkv, do, S, B, H, drop_p=0.1, seed=1, offset=i), a.iters)
+        print(json.dumps({"case": a.case, "S": S, "B": B, "H": H, "us": ms * 1e3}))
+        return
+    if a.case == "colsum":
+        x = torch.randn(a.m * 8, a.d, device=dev, dtype=bf)
+        ms = _time(lambda i: K.colsum(x), a.iters)
+        nbytes = x.numel() * 2
+        print(json.dumps({"case": "colsum", "us": ms * 1e3, "GBs": nbytes / ms / 1e6,
+                          "frac_of_copy_peak": nbytes / ms / 1e6 / hbm, "peaks": src}))
+        return
+    if a.case == "embed":
+        V, D, T = 50304, a.d, a.m * 8
+        table = torch.randn(V, D, device=dev, dtype=bf)
+        ids = torch.randint(0, V, (T,), device=dev)
+        out = torch.empty(T, D, device=dev, dtype=bf)
+        ms = _time(lambda i: K.embed_fwd(table, ids, out, 0, D=D, scale=2.0), a.iters)
+        nbytes = T * D * 2 * 2
+        print(json.dumps({"case": "embed", "us": ms * 1e3, "GBs": nbytes / ms / 1e6,
+                          "frac_of_copy_peak": nbytes / ms / 1e6 / hbm, "peaks": src}))
+
+
+if __name__ == "__main__":
+    main()

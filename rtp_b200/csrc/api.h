@@ -28,6 +28,24 @@ typedef struct {
 } RtpGemmArgs;
 int rtp_gemm(const RtpGemmArgs* args, void* stream);
 
+// Batched GEMM over windows of two 2-D tensors: batch z = (zo, zi), zi = z % batch_inner.  Operand X (stored
+// [x_rows, x_cols] row-major, pitch ldx) is read at row/column offsets zo * x_bo_* + zi * x_bi_* (in the operand's
+// own (mn, k) coordinates); the output moves by zo * d_bo + zi * d_bi elements.  Used for attention, where the
+// per-head matrices are column windows of [B*S, H*hd] projections.
+typedef struct {
+  const void* a; long long lda; int a_mn; long long a_rows, a_cols;
+  const void* b; long long ldb; int b_mn; long long b_rows, b_cols;
+  int M, N, K, batch, batch_inner;
+  int a_bo_mn, a_bo_k, a_bi_mn, a_bi_k;
+  int b_bo_mn, b_bo_k, b_bi_mn, b_bi_k;
+  void* d; long long ldd, d_bo, d_bi;
+  float alpha;
+  int causal;      // 1: skip tiles above the diagonal; 2: stop the contraction at the diagonal
+  int bn;          // 0 = auto
+  unsigned long long* status;
+} RtpGemmBatched;
+int rtp_gemm_batched(const RtpGemmBatched* args, void* stream);
+
 // ---------------------------------------------------------------------------- rotated linear layers
 // Workspace of one rank (peer-mapped): [flag block][W slot 0][W slot 1][G slot 0][G slot 1].
 typedef struct {

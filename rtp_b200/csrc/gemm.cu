@@ -57,8 +57,8 @@ int make_map(CUtensorMap* m, const void* ptr, long long inner, long long outer, 
   return 0;
 }
 // operand stored [rows, k] row-major (K-major)
-int make_map_k(CUtensorMap* m, const void* ptr, long long rows, long long k, long long ld) {
-  return make_map(m, ptr, k, rows, ld, 128);
+int make_map_k(CUtensorMap* m, const void* ptr, long long rows, long long k, long long ld, int box_rows = 128) {
+  return make_map(m, ptr, k, rows, ld, box_rows);
 }
 // operand stored [k, mn] row-major (MN-major)
 int make_map_mn(CUtensorMap* m, const void* ptr, long long mn, long long k, long long ld) {
@@ -81,6 +81,10 @@ void init_phase(RtpPhase& ph) {
   ph.done_ctr[0] = ph.done_ctr[1] = -1;
   ph.credit_ctr = -1;
   ph.bn = 128;
+  ph.batch = 1;
+  ph.batch_inner = 1;
+  ph.b_box = 128;
+  ph.alpha = 1.f;
 }
 void init_program(RtpProgram& p) {
   memset(&p, 0, sizeof(p));
@@ -110,13 +114,27 @@ uint32_t drop_threshold(float p) {
 // Pipeline geometry: the stage must hold the widest B tile of the program; narrower tiles get more stages.
 int g_force_stages = 0;
 void finalize_program(RtpProgram& P, int ctas) {
+  // Tile t of a phase runs on CTA (t + cta_off) % ctas.  Successive phases start where the previous one ended, so
+  // that small per-step GEMMs fill the whole grid.  A phase that accumulates into the output of an earlier phase
+  // (C == that phase's D) must keep that phase's mapping: the read-modify-write of a tile then stays inside one CTA,
+  // ordered by program order.
   long long acc = 0;
   for (int i = 0; i < P.n_phases; ++i) {
     RtpPhase& ph = P.phases[i];
     if (ph.kind != RTP_KIND_GEMM) { ph.cta_off = 0; continue; }
-    const long long tiles = (long long)((ph.M + 127) / 128) * ((ph.N + ph.bn - 1) / ph.bn);
-    ph.cta_off = (int)(acc % ctas);
-    acc += tiles;
+    const long long tiles = (long long)((ph.M + 127) / 128) * ((ph.N + ph.bn - 1) / ph.bn) * ph.batch;
+    int chained = -1;
+    if (ph.c)
+      for (int k = 0; k < i; ++k)
+        if (P.phases[k].kind == RTP_KIND_GEMM && P.phases[k].d == ph.c && P.phases[k].M == ph.M &&
+            P.phases[k].N == ph.N && P.phases[k].bn == ph.bn)
+          chained = k;
+    if (chained >= 0) {
+      ph.cta_off = P.phases[chained].cta_off;
+    } else {
+      ph.cta_off = (int)(acc % ctas);
+      acc += tiles;
+    }
   }
   int bn = 128;
   for (int i = 0; i < P.n_phases; ++i)
@@ -508,6 +526,41 @@ int rtp_gemm(const RtpGemmArgs* a, void* stream) {
   params.ctas_per_rank = ctas;
   const int tiles = ((a->M + 127) / 128) * ((a->N + ph.bn - 1) / ph.bn);
   const int grid = tiles < ctas ? tiles : ctas;
+  params.ctas_per_rank = grid;
+  return launch<1>(params, grid, false, (cudaStream_t)stream);
+}
+
+int rtp_gemm_batched(const RtpGemmBatched* a, void* stream) {
+  static thread_local rtp::GemmParams<1> params;
+  RtpProgram& P = params.prog[0];
+  init_program(P);
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch <= 0 || a->batch_inner <= 0) return fail("empty batched GEMM");
+  const int bn = a->bn ? a->bn : (a->N <= 64 ? 64 : (a->N <= 128 ? 128 : 256));
+  if (bn != 64 && bn != 128 && bn != 256) return fail("bn must be 64, 128 or 256");
+  const int b_box = bn == 64 ? 64 : 128;
+  if (a->a_mn ? make_map_mn(&P.maps[0], a->a, a->a_cols, a->a_rows, a->lda)
+              : make_map_k(&P.maps[0], a->a, a->a_rows, a->a_cols, a->lda))
+    return -1;
+  if (a->b_mn ? make_map_mn(&P.maps[1], a->b, a->b_cols, a->b_rows, a->ldb)
+              : make_map_k(&P.maps[1], a->b, a->b_rows, a->b_cols, a->ldb, b_box))
+    return -1;
+  RtpPhase& ph = P.phases[0];
+  init_phase(ph);
+  ph.a_map = 0; ph.b_map = 1; ph.a_mn = a->a_mn; ph.b_mn = a->b_mn;
+  ph.M = a->M; ph.N = a->N; ph.K = a->K; ph.bn = bn; ph.b_box = b_box;
+  ph.batch = a->batch; ph.batch_inner = a->batch_inner;
+  ph.a_bo_mn = a->a_bo_mn; ph.a_bo_k = a->a_bo_k; ph.a_bi_mn = a->a_bi_mn; ph.a_bi_k = a->a_bi_k;
+  ph.b_bo_mn = a->b_bo_mn; ph.b_bo_k = a->b_bo_k; ph.b_bi_mn = a->b_bi_mn; ph.b_bi_k = a->b_bi_k;
+  ph.d = a->d; ph.ldd = a->ldd; ph.d_bo = a->d_bo; ph.d_bi = a->d_bi;
+  ph.causal = a->causal; ph.alpha = a->alpha;
+  set_vec_ok(ph);
+  if ((a->d_bo | a->d_bi) & 7) ph.vec_ok = 0;
+  P.n_phases = 1;
+  P.status = a->status;
+  if (!P.status) return fail("status word required");
+  const long long tiles = (long long)((a->M + 127) / 128) * ((a->N + bn - 1) / bn) * a->batch;
+  const int ctas = sm_count();
+  const int grid = tiles < ctas ? (int)tiles : ctas;
   params.ctas_per_rank = grid;
   return launch<1>(params, grid, false, (cudaStream_t)stream);
 }

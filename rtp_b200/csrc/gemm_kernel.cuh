@@ -22,7 +22,9 @@ constexpr int kABytes = kBM * kBK * 2;          // 16 KB
 constexpr int kTileBytes = 196608;              // smem ring: 4 stages of 48 KB (bn 256) or 6 stages of 32 KB (bn 128)
 constexpr int kTmemCols = 512;
 constexpr int kNumThreads = 256;
-constexpr int kSmemBytes = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kStagePitch = 144;                // bytes per staged output row: 64 bf16 + 16 pad (conflict-free 16 B writes)
+constexpr int kStagingBytes = 4 * 32 * kStagePitch;
+constexpr int kSmemBytes = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kStagingBytes;
 
 struct SmemCtrl {
   uint64_t full[kMaxStages];
@@ -56,6 +58,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemCtrl* ctl = reinterpret_cast<SmemCtrl*>(tiles + kTileBytes);
+  uint8_t* staging = tiles + kTileBytes + 256;
   const int kStages = P.n_stages;          // uniform for the launch: set by the host from the widest tile
   const int kStageBytes = P.stage_bytes;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
@@ -101,7 +104,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const RtpPhase& ph = P.phases[p];
         const int tiles_m = (ph.M + kBM - 1) / kBM;
         const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
-        const int total = tiles_m * tiles_n;
+        const int per_batch = tiles_m * tiles_n;
+        const int total = per_batch * ph.batch;
         if ((cta - ph.cta_off + G) % G >= total) continue;
         for (int w = 0; w < 2 && ok; ++w) {
           if (ph.wait_ctr[w] >= 0) {
@@ -114,11 +118,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         if (ph.wait_ctr[0] >= 0 || ph.wait_ctr[1] >= 0) fence_proxy_async();
         const CUtensorMap* ma = &P.maps[ph.a_map];
         const CUtensorMap* mb = &P.maps[ph.b_map];
-        const int kblocks = (ph.K + kBK - 1) / kBK;
+        const int kblocks_full = (ph.K + kBK - 1) / kBK;
         const uint32_t tx = kABytes + ph.bn * kBK * 2;
         for (int t = (cta - ph.cta_off + G) % G; t < total && ok; t += G) {
-          const int m0 = (t % tiles_m) * kBM;
-          const int n0 = (t / tiles_m) * ph.bn;
+          const int z = t / per_batch, tt = t % per_batch;
+          const int m0 = (tt % tiles_m) * kBM;
+          const int n0 = (tt / tiles_m) * ph.bn;
+          if (ph.causal == 1 && n0 > m0 + kBM - 1) continue;
+          const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + kBM + kBK - 1) / kBK) : kblocks_full;
+          const int zo = z / ph.batch_inner, zi = z % ph.batch_inner;
+          const int a_mn0 = m0 + ph.a_off_mn + zo * ph.a_bo_mn + zi * ph.a_bi_mn;
+          const int a_k0 = ph.a_off_k + zo * ph.a_bo_k + zi * ph.a_bi_k;
+          const int b_mn0 = n0 + ph.b_off_mn + zo * ph.b_bo_mn + zi * ph.b_bi_mn;
+          const int b_k0 = ph.b_off_k + zo * ph.b_bo_k + zi * ph.b_bi_k;
           for (int kb = 0; kb < kblocks; ++kb) {
             if (!mbar_wait(&ctl->empty[stage], phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
             uint8_t* sa = tiles + stage * kStageBytes;
@@ -128,17 +140,17 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             issued_parity[stage] = phase;
             const int k0 = kb * kBK;
             if (!ph.a_mn) {
-              tma_load_2d(sa, ma, k0 + ph.a_off_k, m0 + ph.a_off_mn, &ctl->full[stage]);
+              tma_load_2d(sa, ma, k0 + a_k0, a_mn0, &ctl->full[stage]);
             } else {
-              tma_load_2d(sa, ma, m0 + ph.a_off_mn, k0 + ph.a_off_k, &ctl->full[stage]);
-              tma_load_2d(sa + 8192, ma, m0 + 64 + ph.a_off_mn, k0 + ph.a_off_k, &ctl->full[stage]);
+              tma_load_2d(sa, ma, a_mn0, k0 + a_k0, &ctl->full[stage]);
+              tma_load_2d(sa + 8192, ma, a_mn0 + 64, k0 + a_k0, &ctl->full[stage]);
             }
             if (!ph.b_mn) {
-              for (int i = 0; i < ph.bn / 128; ++i)
-                tma_load_2d(sb + i * 16384, mb, k0 + ph.b_off_k, n0 + i * 128 + ph.b_off_mn, &ctl->full[stage]);
+              for (int i = 0; i < ph.bn / ph.b_box; ++i)
+                tma_load_2d(sb + i * ph.b_box * 128, mb, k0 + b_k0, b_mn0 + i * ph.b_box, &ctl->full[stage]);
             } else {
               for (int i = 0; i < ph.bn / 64; ++i)
-                tma_load_2d(sb + i * 8192, mb, n0 + i * 64 + ph.b_off_mn, k0 + ph.b_off_k, &ctl->full[stage]);
+                tma_load_2d(sb + i * 8192, mb, b_mn0 + i * 64, k0 + b_k0, &ctl->full[stage]);
             }
             if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
@@ -168,12 +180,18 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const RtpPhase& ph = P.phases[p];
         const int tiles_m = (ph.M + kBM - 1) / kBM;
         const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
-        const int total = tiles_m * tiles_n;
-        const int kblocks = (ph.K + kBK - 1) / kBK;
+        const int per_batch = tiles_m * tiles_n;
+        const int total = per_batch * ph.batch;
+        const int kblocks_full = (ph.K + kBK - 1) / kBK;
         const uint32_t idesc = make_idesc_bf16(kBM, ph.bn, ph.a_mn, ph.b_mn);
         const uint32_t a_lbo = ph.a_mn ? 8192u : 16u, b_lbo = ph.b_mn ? 8192u : 16u;
         const uint32_t a_kstep = ph.a_mn ? 2048u : 32u, b_kstep = ph.b_mn ? 2048u : 32u;
         for (int t = (cta - ph.cta_off + G) % G; t < total && ok; t += G) {
+          const int tt = t % per_batch;
+          const int m0 = (tt % tiles_m) * kBM;
+          const int n0 = (tt / tiles_m) * ph.bn;
+          if (ph.causal == 1 && n0 > m0 + kBM - 1) continue;
+          const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + kBM + kBK - 1) / kBK) : kblocks_full;
           if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
@@ -217,7 +235,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const RtpPhase& ph = P.phases[p];
       const int tiles_m = (ph.M + kBM - 1) / kBM;
       const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
-      const int total = tiles_m * tiles_n;
+      const int per_batch = tiles_m * tiles_n;
+      const int total = per_batch * ph.batch;
       const bool has_tiles = cta < total;
       const unsigned long long drop_off =
           ph.drop_offset + (ph.drop_step_ptr ? __ldg(ph.drop_step_ptr) * 65536ull : 0ull);
@@ -292,8 +311,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         }
       }
       for (int t = (cta - ph.cta_off + G) % G; t < total && ok; t += G) {
-        const int m0 = (t % tiles_m) * kBM;
-        const int n0 = (t / tiles_m) * ph.bn;
+        const int z = t / per_batch, tt = t % per_batch;
+        const int m0 = (tt % tiles_m) * kBM;
+        const int n0 = (tt / tiles_m) * ph.bn;
+        if (ph.causal == 1 && n0 > m0 + kBM - 1) continue;
+        const long long zoff_d = (long long)(z / ph.batch_inner) * ph.d_bo + (long long)(z % ph.batch_inner) * ph.d_bi;
+        const long long zoff_c = (long long)(z / ph.batch_inner) * ph.c_bo + (long long)(z % ph.batch_inner) * ph.c_bi;
         uint32_t good = 1;
         if (lane == 0) good = mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, status, timeout_ns);
         good = __shfl_sync(0xffffffffu, good, 0);
@@ -301,13 +324,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         tc_fence_after();
         const int row = m0 + quad * 32 + lane;
         const bool row_ok = row < ph.M;
+        const bool staged = !ph.d_fp32 && ph.vec_ok && (ph.N & 7) == 0;
+        uint8_t* stg = staging + (warp - 2) * (32 * kStagePitch);
         for (int cb = 0; cb < ph.bn / 32; ++cb) {
           uint32_t r[32];
           __syncwarp();
           tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256 + cb * 32), r);
           tmem_ld_wait();
           const int col0 = n0 + cb * 32;
-          if (!row_ok || col0 >= ph.N) continue;
+          if (row_ok && col0 < ph.N) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {  // groups of 8 columns
             const int col = col0 + g * 8;
@@ -315,11 +340,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             const int nvalid = min(8, ph.N - col);
             float v[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * ph.alpha;
             const bool vec = ph.vec_ok && nvalid == 8;
             if (ph.c) {
               if (ph.c_fp32) {
-                const float* cp = reinterpret_cast<const float*>(ph.c) + (long long)row * ph.ldc + col;
+                const float* cp = reinterpret_cast<const float*>(ph.c) + zoff_c + (long long)row * ph.ldc + col;
                 if (vec) {
                   float4 c0 = __ldcg(reinterpret_cast<const float4*>(cp));
                   float4 c1 = __ldcg(reinterpret_cast<const float4*>(cp) + 1);
@@ -329,7 +354,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
                   for (int i = 0; i < nvalid; ++i) v[i] += __ldcg(cp + i);
                 }
               } else {
-                const __nv_bfloat16* cp = reinterpret_cast<const __nv_bfloat16*>(ph.c) + (long long)row * ph.ldc + col;
+                const __nv_bfloat16* cp = reinterpret_cast<const __nv_bfloat16*>(ph.c) + zoff_c + (long long)row * ph.ldc + col;
                 if (vec) {
                   uint4 c = __ldcg(reinterpret_cast<const uint4*>(cp));
                   v[0] += bf16_lo(c.x); v[1] += bf16_hi(c.x); v[2] += bf16_lo(c.y); v[3] += bf16_hi(c.y);
@@ -382,15 +407,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
               for (int i = 0; i < 8; ++i) v[i] = rw[i] >= ph.drop_thresh ? v[i] * ph.drop_scale : 0.f;
             }
             if (ph.d_fp32) {
-              float* dp = reinterpret_cast<float*>(ph.d) + (long long)row * ph.ldd + col;
+              float* dp = reinterpret_cast<float*>(ph.d) + zoff_d + (long long)row * ph.ldd + col;
               if (vec) {
                 reinterpret_cast<float4*>(dp)[0] = make_float4(v[0], v[1], v[2], v[3]);
                 reinterpret_cast<float4*>(dp)[1] = make_float4(v[4], v[5], v[6], v[7]);
               } else {
                 for (int i = 0; i < nvalid; ++i) dp[i] = v[i];
               }
+            } else if (staged) {
+              // park the 16 bytes in this warp's staging rows; they leave the SM as full 128-byte lines below
+              *reinterpret_cast<uint4*>(stg + lane * kStagePitch + (cb & 1) * 64 + g * 16) =
+                  make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
             } else {
-              __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(ph.d) + (long long)row * ph.ldd + col;
+              __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(ph.d) + zoff_d + (long long)row * ph.ldd + col;
               if (vec) {
                 *reinterpret_cast<uint4*>(dp) =
                     make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
@@ -398,6 +427,24 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
                 for (int i = 0; i < nvalid; ++i) dp[i] = __float2bfloat16(v[i]);
               }
             }
+          }
+          }
+          if (staged && (cb & 1)) {
+            // coalesced write-out of 32 rows x 64 columns: 8 lanes cover one row's 128 bytes, 4 rows per instruction
+            __syncwarp();
+            const int pair_col0 = n0 + (cb - 1) * 32;
+            __nv_bfloat16* dbase = reinterpret_cast<__nv_bfloat16*>(ph.d) + zoff_d;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int rr = k * 4 + (lane >> 3);
+              const int grow = m0 + quad * 32 + rr;
+              const int gcol = pair_col0 + (lane & 7) * 8;
+              if (grow < ph.M && gcol < ph.N) {
+                const uint4 val = *reinterpret_cast<const uint4*>(stg + rr * kStagePitch + (lane & 7) * 16);
+                *reinterpret_cast<uint4*>(dbase + (long long)grow * ph.ldd + gcol) = val;
+              }
+            }
+            __syncwarp();
           }
         }
         tc_fence_before();
@@ -450,9 +497,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const uint4* src = reinterpret_cast<const uint4*>(pu.src);
         uint4* dst = reinterpret_cast<uint4*>(pu.dst);
         unsigned long long i = lo + ptid;
-        for (; i + 192 < hi; i += 256) {
-          uint4 a = __ldg(src + i), b = __ldg(src + i + 64), c = __ldg(src + i + 128), d = __ldg(src + i + 192);
-          dst[i] = a; dst[i + 64] = b; dst[i + 128] = c; dst[i + 192] = d;
+        for (; i + 448 < hi; i += 512) {   // 8 x 16 B per thread in flight
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = __ldg(src + i + 64 * u);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) dst[i + 64 * u] = v[u];
         }
         for (; i < hi; i += 64) dst[i] = __ldg(src + i);
         __threadfence_system();

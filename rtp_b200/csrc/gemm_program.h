@@ -58,6 +58,16 @@ struct RtpPhase {
   int b_off_mn, b_off_k;
   int M, N, K;
   int bn;  // tile width: 128 or 256
+  // batching: `batch` independent GEMMs whose operands are windows of the same 2-D tensors.  Batch z = (zo, zi) with
+  // zi = z % batch_inner; the window of operand X starts at (mn, k) += zo * x_bo_{mn,k} + zi * x_bi_{mn,k} and the
+  // output / accumulate pointers move by zo * d_bo + zi * d_bi elements.
+  int batch, batch_inner;
+  int a_bo_mn, a_bo_k, a_bi_mn, a_bi_k;
+  int b_bo_mn, b_bo_k, b_bi_mn, b_bi_k;
+  long long d_bo, d_bi, c_bo, c_bi;
+  int b_box;      // rows per TMA box of a K-major B operand (64 or 128)
+  int causal;     // 1: skip tiles entirely above the diagonal (n0 > m0 + 127); 2: stop the k loop at the diagonal
+  float alpha;    // accumulator scale applied first in the epilogue
   int cta_off;  // tile t of this phase runs on CTA (t + cta_off) % G, so that successive phases fill different SMs
   // epilogue
   void* d;

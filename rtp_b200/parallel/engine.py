@@ -35,10 +35,20 @@ def _round_up(x, a):
 class FusedEngine:
     def __init__(self, ctx: RingContext, slot_bytes: int, ctas: Optional[int] = None,
                  timeout_ns: int = DEFAULT_TIMEOUT_NS):
-        L = _lib.lib()
         self.ctx = ctx
-        self.slot_bytes = _round_up(max(slot_bytes, 256), 1 << 16)
         self.device = torch.device("cuda", torch.cuda.current_device())
+        self.ctas = ctas or _lib.lib().rtp_sm_count()
+        self.timeout_ns = timeout_ns
+        self.ws_local = None
+        self.mapped = {}
+        self._host_status = C.c_ulonglong(0)
+        self._allocate(slot_bytes)
+
+    def _allocate(self, slot_bytes: int):
+        """Create the local workspace and map every peer's (collective over the ring)."""
+        L = _lib.lib()
+        ctx = self.ctx
+        self.slot_bytes = _round_up(max(slot_bytes, 256), 1 << 16)
         ws = C.c_void_p()
         _lib.check(L.rtp_ws_create(self.slot_bytes if ctx.world > 1 else 256, C.byref(ws)), "rtp_ws_create")
         self.ws_local = ws.value
@@ -64,9 +74,22 @@ class FusedEngine:
         for r in range(ctx.world):
             self.ring.ws[r] = ptrs[r]
         self.ring.slot_bytes = self.slot_bytes
-        self.ring.ctas = ctas or L.rtp_sm_count()
-        self.ring.timeout_ns = timeout_ns
-        self._host_status = C.c_ulonglong(0)
+        self.ring.ctas = self.ctas
+        self.ring.timeout_ns = self.timeout_ns
+
+    def grow(self, slot_bytes: int):
+        """Replace the workspace by a larger one. Collective: every rank of the ring must call it at the same
+        point of the program (it does when the need arises from constructing the same model everywhere)."""
+        L = _lib.lib()
+        torch.cuda.synchronize()
+        if self.ctx.world > 1:
+            dist.barrier(group=self.ctx.group)          # nobody is still pushing into the old slots
+        for ptr in self.mapped.values():
+            L.rtp_ws_ipc_close(ptr)
+        if self.ctx.world > 1:
+            dist.barrier(group=self.ctx.group)
+        L.rtp_ws_destroy(self.ws_local)
+        self._allocate(slot_bytes)
 
     def check(self):
         """Read the workspace status word (synchronises the stream); raise if a bounded wait expired."""
@@ -84,6 +107,8 @@ def get_engine(ctx: RingContext) -> FusedEngine:
     if eng is None:
         eng = FusedEngine(ctx, _reserved_bytes)
         _engines[key] = eng
+    elif ctx.world > 1 and _reserved_bytes > eng.slot_bytes:
+        eng.grow(_reserved_bytes)
     return eng
 
 

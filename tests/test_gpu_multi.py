@@ -15,7 +15,7 @@ def _run(world):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29700 + world), os.path.join(HERE, "_multi_gpu_worker.py")]
-    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert p.returncode == 0 and "MULTI_GPU_OK" in p.stdout, p.stdout[-4000:] + p.stderr[-4000:]
 
 
