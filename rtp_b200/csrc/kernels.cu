@@ -612,6 +612,73 @@ __global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Causal softmax over rows of a score matrix stack [rows_total, S] (row r belongs to query i = r % S).
+// In place: p[i, j] = softmax_j(scale * s[i, j]) for j <= i, 0 for j > i (those entries may hold anything).
+// ------------------------------------------------------------------------------------------------
+__global__ void causal_softmax_kernel(__nv_bfloat16* __restrict__ s, long long rows, int S, float scale) {
+  __shared__ float red[32];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    __nv_bfloat16* p = s + row * S;
+    const int i = (int)(row % S);
+    float mx = -INFINITY;
+    for (int c = threadIdx.x * 8; c <= i; c += blockDim.x * 8) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(p + c), v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) if (c + k <= i) mx = fmaxf(mx, v[k] * scale);
+    }
+    mx = block_max(mx, red);
+    float se = 0.f;
+    for (int c = threadIdx.x * 8; c <= i; c += blockDim.x * 8) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(p + c), v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) if (c + k <= i) se += __expf(v[k] * scale - mx);
+    }
+    se = block_sum(se, red);
+    const float inv = 1.f / se;
+    for (int c = threadIdx.x * 8; c < S; c += blockDim.x * 8) {
+      float v[8];
+      if (c <= i) unpack8(*reinterpret_cast<const uint4*>(p + c), v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = (c + k <= i) ? __expf(v[k] * scale - mx) * inv : 0.f;
+      *reinterpret_cast<uint4*>(p + c) = pack8(v);
+    }
+    __syncthreads();
+  }
+}
+// dS = scale * P * (dP - sum_j P dP), written over dP; entries above the diagonal become 0.
+__global__ void causal_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ pm, __nv_bfloat16* __restrict__ dp,
+                                          long long rows, int S, float scale) {
+  __shared__ float red[32];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* p = pm + row * S;
+    __nv_bfloat16* d = dp + row * S;
+    const int i = (int)(row % S);
+    float dot = 0.f;
+    for (int c = threadIdx.x * 8; c <= i; c += blockDim.x * 8) {
+      float a[8], b[8];
+      unpack8(*reinterpret_cast<const uint4*>(p + c), a);
+      unpack8(*reinterpret_cast<const uint4*>(d + c), b);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) if (c + k <= i) dot += a[k] * b[k];
+    }
+    dot = block_sum(dot, red);
+    for (int c = threadIdx.x * 8; c < S; c += blockDim.x * 8) {
+      float a[8], b[8], o[8];
+      if (c <= i) {
+        unpack8(*reinterpret_cast<const uint4*>(p + c), a);
+        unpack8(*reinterpret_cast<const uint4*>(d + c), b);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = (c + k <= i) ? scale * a[k] * (b[k] - dot) : 0.f;
+      *reinterpret_cast<uint4*>(d + c) = pack8(o);
+    }
+    __syncthreads();
+  }
+}
+
 // out = a + b (bf16), n % 8 == 0 handled vectorised, tail scalar
 __global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, long long n) {
   const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
@@ -774,6 +841,21 @@ int rtp_adam(const RtpAdamTensor* tensors_dev, const int* block_start_dev, int n
                                                               beta1, beta2, eps, weight_decay, adamw, clip_value,
                                                               grad_scale);
   LAUNCH_CHECK("adam");
+  return 0;
+}
+int rtp_causal_softmax(void* s, long long rows, int S, float scale, void* stream) {
+  if (S % 8) { k_err = "causal_softmax: S must be a multiple of 8"; return -1; }
+  const int grid = rows < 148 * 16 ? (int)rows : 148 * 16;
+  causal_softmax_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)s, rows, S, scale);
+  LAUNCH_CHECK("causal_softmax");
+  return 0;
+}
+int rtp_causal_softmax_bwd(const void* p, void* dp, long long rows, int S, float scale, void* stream) {
+  if (S % 8) { k_err = "causal_softmax_bwd: S must be a multiple of 8"; return -1; }
+  const int grid = rows < 148 * 16 ? (int)rows : 148 * 16;
+  causal_softmax_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)p, (__nv_bfloat16*)dp, rows, S,
+                                                                   scale);
+  LAUNCH_CHECK("causal_softmax_bwd");
   return 0;
 }
 int rtp_add(const void* a, const void* b, void* out, long long n, void* stream) {

@@ -42,6 +42,8 @@ int rtp_colsum(const void* x, long long ld, int M, int N, float* out, void* stre
 int rtp_adam(const RtpAdamTensor* tensors_dev, const int* block_start_dev, int ntensors, int total_blocks,
              const long long* step_dev, float lr, float beta1, float beta2, float eps, float weight_decay, int adamw,
              float clip_value, float grad_scale, void* stream);
+int rtp_causal_softmax(void* s, long long rows, int S, float scale, void* stream);
+int rtp_causal_softmax_bwd(const void* p, void* dp, long long rows, int S, float scale, void* stream);
 int rtp_add(const void* a, const void* b, void* out, long long n, void* stream);
 int rtp_cast_f32_bf16(const float* in, void* out, long long n, float scale, void* stream);
 int rtp_sum_f32(const float* in, float* out, int n, float scale, void* stream);

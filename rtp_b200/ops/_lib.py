@@ -31,6 +31,18 @@ class GemmArgs(C.Structure):
     ]
 
 
+class GemmBatched(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("lda", C.c_longlong), ("a_mn", C.c_int), ("a_rows", C.c_longlong), ("a_cols", C.c_longlong),
+        ("b", C.c_void_p), ("ldb", C.c_longlong), ("b_mn", C.c_int), ("b_rows", C.c_longlong), ("b_cols", C.c_longlong),
+        ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("batch", C.c_int), ("batch_inner", C.c_int),
+        ("a_bo_mn", C.c_int), ("a_bo_k", C.c_int), ("a_bi_mn", C.c_int), ("a_bi_k", C.c_int),
+        ("b_bo_mn", C.c_int), ("b_bo_k", C.c_int), ("b_bi_mn", C.c_int), ("b_bi_k", C.c_int),
+        ("d", C.c_void_p), ("ldd", C.c_longlong), ("d_bo", C.c_longlong), ("d_bi", C.c_longlong),
+        ("alpha", C.c_float), ("causal", C.c_int), ("bn", C.c_int), ("status", C.c_void_p),
+    ]
+
+
 class Ring(C.Structure):
     _fields_ = [
         ("rank", C.c_int), ("world", C.c_int),
@@ -115,6 +127,7 @@ def lib():
         L.rtp_ws_ipc_close.argtypes = [C.c_void_p]
         L.rtp_ws_status.argtypes = [C.c_void_p, C.POINTER(C.c_ulonglong), C.c_void_p]
         L.rtp_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+        L.rtp_gemm_batched.argtypes = [C.POINTER(GemmBatched), C.c_void_p]
         L.rtp_linear_fwd.argtypes = [C.POINTER(Ring), C.POINTER(LinearFwd), C.c_void_p]
         L.rtp_linear_bwd.argtypes = [C.POINTER(Ring), C.POINTER(LinearBwd), C.c_void_p]
         L.rtp_embed_fwd_rot.argtypes = [C.POINTER(Ring), C.POINTER(EmbedFwd), C.c_void_p]

@@ -31,6 +31,8 @@ def _L():
         L.rtp_colsum.argtypes = [vp, ll, i, i, vp, vp]
         L.rtp_adam.argtypes = [vp, vp, i, i, vp, f, f, f, f, f, i, f, f, vp]
         L.rtp_add.argtypes = [vp, vp, vp, ll, vp]
+        L.rtp_causal_softmax.argtypes = [vp, ll, i, f, vp]
+        L.rtp_causal_softmax_bwd.argtypes = [vp, vp, ll, i, f, vp]
         L.rtp_cast_f32_bf16.argtypes = [vp, vp, ll, f, vp]
         L.rtp_sum_f32.argtypes = [vp, vp, i, f, vp]
         _declared = True
@@ -138,6 +140,20 @@ def colsum(x, out=None):
         out = torch.empty(N, dtype=torch.float32, device=x.device)
     _check(_L().rtp_colsum(_p(x), x.stride(0), M, N, _p(out), _lib.stream_ptr()), "colsum")
     return out
+
+
+def causal_softmax_(scores, S, scale):
+    """In-place causal softmax of a stack of [S, S] bf16 score matrices (any garbage above the diagonal is zeroed)."""
+    rows = scores.numel() // S
+    _check(_L().rtp_causal_softmax(_p(scores), rows, S, float(scale), _lib.stream_ptr()), "causal_softmax")
+    return scores
+
+
+def causal_softmax_bwd_(p, dp, S, scale):
+    """dp <- scale * p * (dp - rowsum(p * dp)), zero above the diagonal."""
+    rows = p.numel() // S
+    _check(_L().rtp_causal_softmax_bwd(_p(p), _p(dp), rows, S, float(scale), _lib.stream_ptr()), "causal_softmax_bwd")
+    return dp
 
 
 def add(a, b, out=None):
