@@ -28,6 +28,19 @@ CONFIGS = {
     "tiny": dict(vocab=1024, ninp=256, nhid=1024, nhead=4, nlayers=2, seq_len=32, batch=8, dropout=0.1, clip=0.05,
                  initrange=0.1, lr=1e-3),
 }
+# secondary configs (module path: rotated modules + autograd on the same kernels)
+CONFIGS["gpt1.3b"] = dict(family="gpt", vocab=50304, ninp=2048, nhid=8192, nhead=16, nlayers=24, seq_len=2048, batch=8,
+                          dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
+CONFIGS["gpt-small"] = dict(family="gpt", vocab=8192, ninp=512, nhid=2048, nhead=8, nlayers=4, seq_len=256, batch=4,
+                            dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
+CONFIGS["llama13b"] = dict(family="llama", vocab=32000, ninp=5120, nhid=13824, nhead=40, nlayers=40, seq_len=2048,
+                           batch=4, dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
+CONFIGS["llama-small"] = dict(family="llama", vocab=8192, ninp=512, nhid=1536, nhead=8, nlayers=4, seq_len=256, batch=4,
+                              dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
+CONFIGS["moe"] = dict(family="moe", vocab=32000, ninp=2048, nhid=8192, nhead=16, nlayers=12, seq_len=1024, batch=8,
+                      n_experts=8, capacity_factor=1.25, dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
+CONFIGS["moe-small"] = dict(family="moe", vocab=8192, ninp=512, nhid=1024, nhead=8, nlayers=2, seq_len=128, batch=4,
+                            n_experts=8, capacity_factor=1.25, dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
 METRIC = "tokens/s/box"
 
 
@@ -215,6 +228,65 @@ def run_ours(args, cfg, rank, local, world):
     return ms, clocks, loss, e2e, peak + ws_gb, trainer.launches_per_step + 1
 
 
+def run_ours_module(args, cfg, rank, local, world):
+    """GPT / Llama / MoE configs: rotated modules + autograd; linears, attention, norms, activations, embedding,
+    cross-entropy and Adam all run on the library's kernels (inputs are [batch, seq])."""
+    import torch
+    sys.path.insert(0, ROOT)
+    from rtp_b200.optim import ShardedAdamW
+    torch.manual_seed(0)
+    dev = torch.device("cuda", local)
+    fam = cfg["family"]
+    if fam == "gpt":
+        from rtp_b200.models.gpt import GPT, GPTConfig
+        model = GPT(GPTConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"]))
+    elif fam == "llama":
+        from rtp_b200.models.llama import Llama, LlamaConfig
+        model = Llama(LlamaConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"]))
+    else:
+        from rtp_b200.models.moe_lm import MoELM, MoEConfig
+        model = MoELM(MoEConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["n_experts"],
+                                cfg["capacity_factor"], cfg["seq_len"]))
+    model = model.to(device=dev, dtype=torch.bfloat16)
+    opt = ShardedAdamW(model.parameters(), lr=cfg["lr"], weight_decay=0.01)
+    nb = min(max(4, args.steps + args.warmup), 16)
+    pinned = [(a.t().contiguous().pin_memory(), b.t().contiguous().pin_memory())
+              for a, b in synthetic_batches(cfg, nb, rank, pin=False)]
+    dev_batches = [(a.to(dev), b.to(dev)) for a, b in pinned]
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    torch.cuda.reset_peak_memory_stats()
+    last = {}
+
+    def step(ids, tgt):
+        ids = ids.to(dev, non_blocking=True)
+        tgt = tgt.to(dev, non_blocking=True)
+        opt.zero_grad(set_to_none=True)
+        loss = model(ids, tgt)
+        (loss / world).backward()
+        opt.step()
+        last["loss"] = loss.detach()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed_loop(step, dev_batches, args.steps, max(args.warmup, 3), world, flush, None)
+    clocks = sampler.stop()
+    from rtp_b200.parallel import engine
+    from rtp_b200.ops import _lib
+    engine.check_all()
+    _lib.check_status(dev)
+    loss = float(last["loss"].item())
+    e2e = None
+    if not args.no_e2e:
+        def read_loss():
+            last["v"] = float(last["loss"].item())
+        ms_e2e = timed_loop(step, pinned, args.steps, 3, world, flush, read_loss)
+        tok = cfg["seq_len"] * cfg["batch"] * world * args.steps
+        e2e = {"value": tok / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+               "h2d_bytes_per_step": 2 * cfg["seq_len"] * cfg["batch"] * 8, "d2h_bytes_per_step": 4}
+    peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    return ms, clocks, loss, e2e, peak, 1
+
+
 def run_reference(args, cfg, rank, local, world):
     """The reference's own rotated LM (rtp.models.transformer_lm_rtp.TransformerLM, out-of-place modules,
     NCCL send/recv rotation, ATen/cuBLAS kernels), driven by the loop of its benchmark script
@@ -293,7 +365,17 @@ def main():
         raise SystemExit("bench.py needs a CUDA device")
     rank, local, world = setup_dist(args)
     t_wall = time.time()
-    res = run_ours(args, cfg, rank, local, world) if args.impl == "rtp_b200" else run_reference(args, cfg, rank, local, world)
+    if args.impl == "reference":
+        if cfg.get("family") in ("llama", "moe"):
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the reference ships no Llama model and its MoE "
+                                  "capacity is fixed at factor 1.0; only the dense transformer LM is compared"}))
+            return
+        res = run_reference(args, cfg, rank, local, world)
+    elif "family" in cfg:
+        res = run_ours_module(args, cfg, rank, local, world)
+    else:
+        res = run_ours(args, cfg, rank, local, world)
     ms, clocks, loss, e2e, peak_gb, launches = res
     tokens = cfg["seq_len"] * cfg["batch"] * world * args.steps
     value = tokens / (ms / 1e3)
@@ -305,6 +387,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "impl": args.impl, "peak_gb_per_gpu": peak_gb, "final_loss": loss,
             "config": {"model": "RTP TransformerLM (README config)" if args.config == "readme" else args.config,
+                       "path": "module+autograd" if ("family" in cfg and args.impl == "rtp_b200") else "fused trainer",
                        "vocab": cfg["vocab"], "ninp": cfg["ninp"], "nhid": cfg["nhid"], "nhead": cfg["nhead"],
                        "layers": cfg["nlayers"], "seq_len": cfg["seq_len"], "batch_per_gpu": cfg["batch"],
                        "global_batch": cfg["batch"] * world, "dropout": cfg["dropout"], "clip": cfg["clip"],

@@ -679,6 +679,71 @@ __global__ void causal_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ pm, 
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Activations (n % 8 == 0).  mode 0: y = gelu(x) (erf form).  mode 1: y = silu(g) * u with g, u the two column halves
+// selected by pointers.  Backward kernels recompute from the saved pre-activations.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+  return cdf + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+__global__ void gelu_fwd_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, long long n) {
+  const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  float v[8];
+  unpack8(*reinterpret_cast<const uint4*>(x + i), v);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = gelu_f(v[k]);
+  *reinterpret_cast<uint4*>(y + i) = pack8(v);
+}
+__global__ void gelu_bwd_kernel(const __nv_bfloat16* x, const __nv_bfloat16* dy, __nv_bfloat16* dx, long long n) {
+  const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  float v[8], g[8];
+  unpack8(*reinterpret_cast<const uint4*>(x + i), v);
+  unpack8(*reinterpret_cast<const uint4*>(dy + i), g);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = g[k] * gelu_grad_f(v[k]);
+  *reinterpret_cast<uint4*>(dx + i) = pack8(v);
+}
+// g, u: [rows, cols] windows with pitch ld (elements); y dense [rows, cols]
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* g, const __nv_bfloat16* u, long long ld, __nv_bfloat16* y,
+                                  long long rows, int cols) {
+  const long long it = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const int per = cols / 8;
+  if (it >= rows * per) return;
+  const long long r = it / per;
+  const int c = (int)(it % per) * 8;
+  float a[8], b[8];
+  unpack8(*reinterpret_cast<const uint4*>(g + r * ld + c), a);
+  unpack8(*reinterpret_cast<const uint4*>(u + r * ld + c), b);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a[k] = a[k] / (1.f + __expf(-a[k])) * b[k];
+  *reinterpret_cast<uint4*>(y + r * cols + c) = pack8(a);
+}
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* g, const __nv_bfloat16* u, long long ld, const __nv_bfloat16* dy,
+                                  __nv_bfloat16* dg, __nv_bfloat16* du, long long ldo, long long rows, int cols) {
+  const long long it = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const int per = cols / 8;
+  if (it >= rows * per) return;
+  const long long r = it / per;
+  const int c = (int)(it % per) * 8;
+  float a[8], b[8], d[8], og[8], ou[8];
+  unpack8(*reinterpret_cast<const uint4*>(g + r * ld + c), a);
+  unpack8(*reinterpret_cast<const uint4*>(u + r * ld + c), b);
+  unpack8(*reinterpret_cast<const uint4*>(dy + r * cols + c), d);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float sg = 1.f / (1.f + __expf(-a[k]));
+    const float silu = a[k] * sg;
+    ou[k] = d[k] * silu;
+    og[k] = d[k] * b[k] * (sg + silu * (1.f - sg));
+  }
+  *reinterpret_cast<uint4*>(dg + r * ldo + c) = pack8(og);
+  *reinterpret_cast<uint4*>(du + r * ldo + c) = pack8(ou);
+}
+
 // out = a + b (bf16), n % 8 == 0 handled vectorised, tail scalar
 __global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, long long n) {
   const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
@@ -856,6 +921,37 @@ int rtp_causal_softmax_bwd(const void* p, void* dp, long long rows, int S, float
   causal_softmax_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)p, (__nv_bfloat16*)dp, rows, S,
                                                                    scale);
   LAUNCH_CHECK("causal_softmax_bwd");
+  return 0;
+}
+int rtp_gelu_fwd(const void* x, void* y, long long n, void* stream) {
+  if (n % 8) { k_err = "gelu: n must be a multiple of 8"; return -1; }
+  gelu_fwd_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, n);
+  LAUNCH_CHECK("gelu_fwd");
+  return 0;
+}
+int rtp_gelu_bwd(const void* x, const void* dy, void* dx, long long n, void* stream) {
+  if (n % 8) { k_err = "gelu: n must be a multiple of 8"; return -1; }
+  gelu_bwd_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
+                                                                                 (__nv_bfloat16*)dx, n);
+  LAUNCH_CHECK("gelu_bwd");
+  return 0;
+}
+int rtp_swiglu_fwd(const void* g, const void* u, long long ld, void* y, long long rows, int cols, void* stream) {
+  if (cols % 8 || ld % 8) { k_err = "swiglu: cols and ld must be multiples of 8"; return -1; }
+  const long long items = rows * (cols / 8);
+  swiglu_fwd_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, ld,
+                                                                                   (__nv_bfloat16*)y, rows, cols);
+  LAUNCH_CHECK("swiglu_fwd");
+  return 0;
+}
+int rtp_swiglu_bwd(const void* g, const void* u, long long ld, const void* dy, void* dg, void* du, long long ldo,
+                   long long rows, int cols, void* stream) {
+  if (cols % 8 || ld % 8 || ldo % 8) { k_err = "swiglu: cols and ld must be multiples of 8"; return -1; }
+  const long long items = rows * (cols / 8);
+  swiglu_bwd_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, ld, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dg, (__nv_bfloat16*)du, ldo, rows,
+      cols);
+  LAUNCH_CHECK("swiglu_bwd");
   return 0;
 }
 int rtp_add(const void* a, const void* b, void* out, long long n, void* stream) {

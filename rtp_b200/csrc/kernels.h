@@ -44,6 +44,11 @@ int rtp_adam(const RtpAdamTensor* tensors_dev, const int* block_start_dev, int n
              float clip_value, float grad_scale, void* stream);
 int rtp_causal_softmax(void* s, long long rows, int S, float scale, void* stream);
 int rtp_causal_softmax_bwd(const void* p, void* dp, long long rows, int S, float scale, void* stream);
+int rtp_gelu_fwd(const void* x, void* y, long long n, void* stream);
+int rtp_gelu_bwd(const void* x, const void* dy, void* dx, long long n, void* stream);
+int rtp_swiglu_fwd(const void* g, const void* u, long long ld, void* y, long long rows, int cols, void* stream);
+int rtp_swiglu_bwd(const void* g, const void* u, long long ld, const void* dy, void* dg, void* du, long long ldo,
+                   long long rows, int cols, void* stream);
 int rtp_add(const void* a, const void* b, void* out, long long n, void* stream);
 int rtp_cast_f32_bf16(const float* in, void* out, long long n, float scale, void* stream);
 int rtp_sum_f32(const float* in, float* out, int n, float scale, void* stream);

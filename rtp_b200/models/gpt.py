@@ -15,6 +15,8 @@ import torch.nn.functional as F
 from ..module.attention import ParallelMultiheadAttention
 from ..module.embedding import ParallelEmbedding
 from ..module.linear import ColumnParallelLinear, RowParallelLinear
+from ..module.norm import LayerNorm
+from ..ops import functional as FO
 
 
 @dataclass
@@ -37,9 +39,9 @@ class GPTBlock(nn.Module):
     def __init__(self, cfg: GPTConfig, device=None, dtype=None, group=None):
         super().__init__()
         kw = dict(device=device, dtype=dtype, group=group)
-        self.ln1 = nn.LayerNorm(cfg.d_model, device=device, dtype=dtype)
+        self.ln1 = LayerNorm(cfg.d_model, device=device, dtype=dtype)
         self.attn = ParallelMultiheadAttention(cfg.d_model, cfg.n_heads, dropout=cfg.dropout, batch_first=True, **kw)
-        self.ln2 = nn.LayerNorm(cfg.d_model, device=device, dtype=dtype)
+        self.ln2 = LayerNorm(cfg.d_model, device=device, dtype=dtype)
         self.fc1 = ColumnParallelLinear(cfg.d_model, cfg.d_ff, **kw)
         self.fc2 = RowParallelLinear(cfg.d_ff, cfg.d_model, **kw)
         self.drop = nn.Dropout(cfg.dropout)
@@ -47,7 +49,7 @@ class GPTBlock(nn.Module):
     def forward(self, x):
         h = self.ln1(x)
         x = x + self.drop(self.attn(h, h, h, need_weights=False, is_causal=True)[0])
-        x = x + self.drop(self.fc2(F.gelu(self.fc1(self.ln2(x)))))
+        x = x + self.drop(self.fc2(FO.gelu(self.fc1(self.ln2(x)))))
         return x
 
 
@@ -59,7 +61,7 @@ class GPT(nn.Module):
         self.pos = nn.Parameter(torch.zeros(cfg.max_seq_len, cfg.d_model, device=device, dtype=dtype))
         self.drop = nn.Dropout(cfg.dropout)
         self.blocks = nn.ModuleList([GPTBlock(cfg, device, dtype, group) for _ in range(cfg.n_layers)])
-        self.ln_f = nn.LayerNorm(cfg.d_model, device=device, dtype=dtype)
+        self.ln_f = LayerNorm(cfg.d_model, device=device, dtype=dtype)
         self.head = ColumnParallelLinear(cfg.d_model, cfg.vocab_size, bias=False, device=device, dtype=dtype, group=group)
         self.reset_parameters()
 
@@ -81,7 +83,7 @@ class GPT(nn.Module):
         logits = self.head(self.ln_f(x))
         if targets is None:
             return logits
-        return F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.reshape(-1))
+        return FO.cross_entropy(logits, targets)
 
     def num_parameters_global(self, world: int) -> int:
         n = 0

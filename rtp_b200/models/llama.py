@@ -15,6 +15,7 @@ import torch.nn.functional as F
 from ..module.embedding import ParallelEmbedding
 from ..module.linear import ColumnParallelLinear, RowParallelLinear
 from ..parallel.context import get_context
+from ..ops import functional as FO
 
 
 @dataclass
@@ -41,7 +42,6 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
 
     def forward(self, x):
-        from ..ops import functional as FO
         if FO.use_kernels(x):
             return FO.rms_norm(x, self.weight, self.eps)
         xf = x.float()
@@ -90,11 +90,10 @@ class LlamaBlock(nn.Module):
         q = apply_rope(q.view(B, S, cfg.n_heads, hd), cos, sin)
         k = apply_rope(k.view(B, S, cfg.n_heads, hd), cos, sin)
         v = v.view(B, S, cfg.n_heads, hd)
-        from ..ops import functional as FO
         a = FO.causal_attention(q, k, v)                         # [B, S, H, hd]
         x = x + self.proj(a.reshape(B, S, D))
         g, u = self._split_packed(self.gate_up(self.norm2(x)), 2)
-        x = x + self.down(F.silu(g) * u)
+        x = x + self.down(FO.swiglu(g, u))
         return x
 
 
@@ -120,4 +119,4 @@ class Llama(nn.Module):
         logits = self.head(self.norm(x))
         if targets is None:
             return logits
-        return F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.reshape(-1))
+        return FO.cross_entropy(logits, targets)

@@ -10,6 +10,8 @@ import torch.nn.functional as F
 from ..module.attention import ParallelMultiheadAttention
 from ..module.embedding import ParallelEmbedding
 from ..module.linear import ColumnParallelLinear
+from ..module.norm import LayerNorm
+from ..ops import functional as FO
 from ..module.moe import WeightMOELayer
 from ..module.top2gate import WeightTop2Gate
 from ..parallel.context import get_context
@@ -46,10 +48,10 @@ class MoEBlock(nn.Module):
         ctx = get_context(group)
         if cfg.n_experts % ctx.world:
             raise ValueError("number of experts must be divisible by the ring size")
-        self.ln1 = nn.LayerNorm(cfg.d_model, device=device, dtype=dtype)
+        self.ln1 = LayerNorm(cfg.d_model, device=device, dtype=dtype)
         self.attn = ParallelMultiheadAttention(cfg.d_model, cfg.n_heads, dropout=cfg.dropout, batch_first=True,
                                                device=device, dtype=dtype, group=group)
-        self.ln2 = nn.LayerNorm(cfg.d_model, device=device, dtype=dtype)
+        self.ln2 = LayerNorm(cfg.d_model, device=device, dtype=dtype)
         self.gate = WeightTop2Gate(cfg.d_model, cfg.n_experts, device=device, dtype=dtype, group=group,
                                    capacity_factor=cfg.capacity_factor)
         experts = nn.ModuleList([Expert(cfg.d_model, cfg.d_ff) for _ in range(cfg.n_experts // ctx.world)])
@@ -69,7 +71,7 @@ class MoELM(nn.Module):
         self.tok = ParallelEmbedding(cfg.vocab_size, cfg.d_model, device=device, dtype=dtype, group=group)
         self.pos = nn.Parameter(torch.zeros(cfg.max_seq_len, cfg.d_model, device=device, dtype=dtype))
         self.blocks = nn.ModuleList([MoEBlock(cfg, device, dtype, group) for _ in range(cfg.n_layers)])
-        self.ln_f = nn.LayerNorm(cfg.d_model, device=device, dtype=dtype)
+        self.ln_f = LayerNorm(cfg.d_model, device=device, dtype=dtype)
         self.head = ColumnParallelLinear(cfg.d_model, cfg.vocab_size, bias=False, device=device, dtype=dtype, group=group)
         with torch.no_grad():
             for p in self.parameters():
@@ -85,6 +87,6 @@ class MoELM(nn.Module):
         logits = self.head(self.ln_f(x))
         if targets is None:
             return logits
-        ce = F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.reshape(-1))
+        ce = FO.cross_entropy(logits, targets)
         aux = sum(blk.moe_layer.l_aux for blk in self.blocks) / len(self.blocks)
         return ce + self.cfg.aux_loss_weight * aux.float()

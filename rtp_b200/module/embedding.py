@@ -63,6 +63,11 @@ class ParallelEmbedding(RotatedModule):
 
     def forward(self, input_: torch.Tensor) -> torch.Tensor:  # type: ignore
         pad, mx, nt, sg = self.padding_idx, self.max_norm, self.norm_type, self.scale_grad_by_freq
+        from ..parallel import fused
+        if pad is None and mx is None and not sg and self._full_param.is_cuda and \
+                fused.use_fused(self._full_param, self._full_param) and self.embedding_dim_per_partition % 8 == 0:
+            from ..parallel.engine import fused_embedding
+            return fused_embedding(self, input_)
 
         def fn(j, views, ids):
             return F.embedding(ids, views[0], pad, mx, nt, sg, False)

@@ -107,3 +107,49 @@ def causal_attention(q, k, v):
             return flash_attention(q, k, v, causal=True)
     o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
     return o.transpose(1, 2)
+
+
+class _GeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        from . import kernels as K
+        xc = x.contiguous()
+        ctx.save_for_backward(xc)
+        return K.gelu_fwd(xc)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import kernels as K
+        (x,) = ctx.saved_tensors
+        return K.gelu_bwd(x, dy.contiguous())
+
+
+def gelu(x):
+    if use_kernels(x) and x.numel() % 8 == 0:
+        return _GeluFn.apply(x)
+    return F.gelu(x)
+
+
+class _SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, u):
+        from . import kernels as K
+        shape = g.shape
+        g2, u2 = g.reshape(-1, shape[-1]).contiguous(), u.reshape(-1, shape[-1]).contiguous()
+        ctx.save_for_backward(g2, u2)
+        ctx.shape = shape
+        return K.swiglu_fwd(g2, u2).view(shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import kernels as K
+        g2, u2 = ctx.saved_tensors
+        dg, du = K.swiglu_bwd(g2, u2, dy.reshape(-1, ctx.shape[-1]).contiguous())
+        return dg.view(ctx.shape), du.view(ctx.shape)
+
+
+def swiglu(g, u):
+    """silu(g) * u."""
+    if use_kernels(g) and g.shape[-1] % 8 == 0:
+        return _SwigluFn.apply(g, u)
+    return F.silu(g) * u

@@ -31,6 +31,10 @@ def _L():
         L.rtp_colsum.argtypes = [vp, ll, i, i, vp, vp]
         L.rtp_adam.argtypes = [vp, vp, i, i, vp, f, f, f, f, f, i, f, f, vp]
         L.rtp_add.argtypes = [vp, vp, vp, ll, vp]
+        L.rtp_gelu_fwd.argtypes = [vp, vp, ll, vp]
+        L.rtp_gelu_bwd.argtypes = [vp, vp, vp, ll, vp]
+        L.rtp_swiglu_fwd.argtypes = [vp, vp, ll, vp, ll, i, vp]
+        L.rtp_swiglu_bwd.argtypes = [vp, vp, ll, vp, vp, vp, ll, ll, i, vp]
         L.rtp_causal_softmax.argtypes = [vp, ll, i, f, vp]
         L.rtp_causal_softmax_bwd.argtypes = [vp, vp, ll, i, f, vp]
         L.rtp_cast_f32_bf16.argtypes = [vp, vp, ll, f, vp]
@@ -154,6 +158,34 @@ def causal_softmax_bwd_(p, dp, S, scale):
     rows = p.numel() // S
     _check(_L().rtp_causal_softmax_bwd(_p(p), _p(dp), rows, S, float(scale), _lib.stream_ptr()), "causal_softmax_bwd")
     return dp
+
+
+def gelu_fwd(x):
+    y = torch.empty_like(x)
+    _check(_L().rtp_gelu_fwd(_p(x), _p(y), x.numel(), _lib.stream_ptr()), "gelu_fwd")
+    return y
+
+
+def gelu_bwd(x, dy):
+    dx = torch.empty_like(x)
+    _check(_L().rtp_gelu_bwd(_p(x), _p(dy), _p(dx), x.numel(), _lib.stream_ptr()), "gelu_bwd")
+    return dx
+
+
+def swiglu_fwd(g, u):
+    """g, u: [rows, cols] views with a common row pitch (e.g. the two halves of a packed projection)."""
+    rows, cols = g.shape
+    y = torch.empty(rows, cols, dtype=g.dtype, device=g.device)
+    _check(_L().rtp_swiglu_fwd(_p(g), _p(u), g.stride(0), _p(y), rows, cols, _lib.stream_ptr()), "swiglu_fwd")
+    return y
+
+
+def swiglu_bwd(g, u, dy):
+    rows, cols = g.shape
+    dg, du = torch.empty(rows, cols, dtype=g.dtype, device=g.device), torch.empty(rows, cols, dtype=g.dtype, device=g.device)
+    _check(_L().rtp_swiglu_bwd(_p(g), _p(u), g.stride(0), _p(dy), _p(dg), _p(du), cols, rows, cols, _lib.stream_ptr()),
+           "swiglu_bwd")
+    return dg, du
 
 
 def add(a, b, out=None):

@@ -244,3 +244,101 @@ def embed_bwd_rot(eng, trainer, st, dx0):
     K.embed_bwd(dense, st["ids"].view(-1), dx0, 0, D=D, scale=math.sqrt(D), drop_p=trainer.p_drop,
                 seed=trainer.seed, offset=1, step=trainer.rng_step)
     reduce_scatter_cols(eng, dense, trainer.emb._layout.views(trainer.emb_gflat)[0])
+
+
+# --------------------------------------------------------------------------------------------------
+# generic autograd pieces for the module path
+# --------------------------------------------------------------------------------------------------
+class _FusedSubLinearFn(torch.autograd.Function):
+    """Rotated linear on a (sub-)range of a module's flat shard: ``spec`` = (ring, flat, info, row, in_f, out_f,
+    [(offset, numel, shape), ...]) lists where the given parameters live inside ``flat``."""
+
+    @staticmethod
+    def forward(ctx, spec, x, *params):
+        ring, flat, info, row, in_f, out_f, places = spec
+        eng = get_engine(ring)
+        x2d = x.reshape(-1, x.shape[-1])
+        if x2d.stride(1) != 1 or (x2d.stride(0) * 2) % 16 or x2d.data_ptr() % 16:
+            x2d = x2d.contiguous()
+        y = linear_fwd_raw(eng, flat, info, x2d, row, in_f, out_f)
+        ctx.spec, ctx.eng = spec, eng
+        ctx.save_for_backward(x2d)
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], out_f)
+
+    @staticmethod
+    def backward(ctx, dy):
+        ring, flat, info, row, in_f, out_f, places = ctx.spec
+        (x2d,) = ctx.saved_tensors
+        dy2d = dy.reshape(-1, dy.shape[-1])
+        if not dy2d.is_contiguous():
+            dy2d = dy2d.contiguous()
+        dx, gflat = linear_bwd_raw(ctx.eng, flat, info, x2d, dy2d, row, in_f, out_f, need_dx=ctx.needs_input_grad[1])
+        grads = [gflat[off:off + n].view(shape) for off, n, shape in places]
+        return (None, dx.view(ctx.x_shape) if dx is not None else None, *grads)
+
+
+def fused_mha(module, x, causal: bool):
+    """Self-attention of a ``ParallelMultiheadAttention`` on the fused kernels: column-rotated packed QKV projection,
+    local attention over all heads, row-rotated output projection.  ``x``: [L, B, E] (or [B, L, E] when batch_first)."""
+    from ..ops import functional as FO
+    from ..ops.flash import flash_attention, flash_attention_available
+    from ..ops import kernels as KK
+    sub = module.MultiheadAttention
+    lay, flat = module._layout, module._full_param
+    N, E, H = module.world_size, module.embed_dim, module.num_heads
+    hd = E // H
+    o_inw, o_inb = lay.offset_of("in_proj_weight"), lay.offset_of("in_proj_bias")
+    o_ow, o_ob = lay.offset_of("out_proj.weight"), lay.offset_of("out_proj.bias")
+    qkv_flat, out_flat = flat[o_inw:o_ow], flat[o_ow:]
+    spec_qkv = (module.ring, qkv_flat, (True, o_inb - o_inw, _round_up(qkv_flat.numel() * 2, 16)), False, E, 3 * E,
+                [(0, sub.in_proj_weight.numel(), sub.in_proj_weight.shape),
+                 (o_inb - o_inw, sub.in_proj_bias.numel(), sub.in_proj_bias.shape)])
+    spec_out = (module.ring, out_flat, (True, o_ob - o_ow, _round_up(out_flat.numel() * 2, 16)), True, E, E,
+                [(0, sub.out_proj.weight.numel(), sub.out_proj.weight.shape),
+                 (o_ob - o_ow, sub.out_proj.bias.numel(), sub.out_proj.bias.shape)])
+    bf = module.batch_first
+    if bf:
+        B, L = x.shape[0], x.shape[1]
+    else:
+        L, B = x.shape[0], x.shape[1]
+    qkv = _FusedSubLinearFn.apply(spec_qkv, x, sub.in_proj_weight, sub.in_proj_bias)       # [.., 3E] grouped per shard
+    packed = qkv.reshape(*x.shape[:2], N, 3, H // N, hd)
+    q, k, v = [packed[:, :, :, i].reshape(*x.shape[:2], H, hd) for i in range(3)]
+    if not bf:
+        q, k, v = [t.transpose(0, 1) for t in (q, k, v)]                                    # [B, L, H, hd]
+    ctxv = FO.causal_attention(q, k, v)                                                       # [B, L, H, hd]
+    if not bf:
+        ctxv = ctxv.transpose(0, 1)
+    ctxv = ctxv.reshape(*x.shape[:2], E)
+    return _FusedSubLinearFn.apply(spec_out, ctxv, sub.out_proj.weight, sub.out_proj.bias)
+
+
+class _FusedEmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, module, ids, weight):
+        eng = get_engine(module.ring)
+        V, Ds = weight.shape
+        D = module.embedding_dim
+        flat_ids = ids.reshape(-1).contiguous()
+        out = torch.empty(flat_ids.numel(), D, dtype=weight.dtype, device=weight.device)
+        embed_fwd_rot(eng, module._full_param, V, Ds, flat_ids, out, D, 1.0, None, 1, 0.0, 0, 0, None)
+        ctx.module, ctx.eng = module, eng
+        ctx.save_for_backward(flat_ids)
+        ctx.dims = (V, Ds, D)
+        return out.view(*ids.shape, D)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (flat_ids,) = ctx.saved_tensors
+        V, Ds, D = ctx.dims
+        dy2 = dy.reshape(-1, D).contiguous()
+        dense = torch.zeros(V, D, dtype=dy2.dtype, device=dy2.device)
+        K.embed_bwd(dense, flat_ids, dy2, 0, D=D, scale=1.0)
+        g = torch.empty(V, Ds, dtype=dy2.dtype, device=dy2.device)
+        reduce_scatter_cols(ctx.eng, dense, g)
+        return None, None, g
+
+
+def fused_embedding(module, ids):
+    return _FusedEmbeddingFn.apply(module, ids, module.embedding.weight)
