@@ -224,7 +224,7 @@ def run_ours(args, cfg, rank, local, world):
                "h2d_bytes_per_step": 2 * cfg["seq_len"] * cfg["batch"] * 8, "d2h_bytes_per_step": 4}
         trainer.check()
     peak = torch.cuda.max_memory_allocated() / 2 ** 30
-    ws_gb = trainer.eng.slot_bytes * 4 / 2 ** 30 if world > 1 else 0.0
+    ws_gb = trainer.eng.slot_bytes * 16 / 2 ** 30 if world > 1 else 0.0
     return ms, clocks, loss, e2e, peak + ws_gb, trainer.launches_per_step + 1
 
 

@@ -77,8 +77,7 @@ int sm_count() {
 
 void init_phase(RtpPhase& ph) {
   memset(&ph, 0, sizeof(ph));
-  ph.wait_ctr[0] = ph.wait_ctr[1] = -1;
-  ph.done_ctr[0] = ph.done_ctr[1] = -1;
+  for (int w = 0; w < RTP_MAX_WAITS; ++w) { ph.wait_ctr[w] = -1; ph.done_ctr[w] = -1; }
   ph.credit_ctr = -1;
   ph.bn = 128;
   ph.batch = 1;
@@ -169,7 +168,7 @@ int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cuda
   }
   cfg.attrs = at;
   cfg.numAttrs = nat;
-  for (int e = 0; e < NEMU; ++e) finalize_program(const_cast<RtpProgram&>(params.prog[e]), params.ctas_per_rank);
+  if (NEMU == 1) finalize_program(const_cast<RtpProgram&>(params.prog[0]), params.ctas_per_rank);
   cudaError_t e = cudaLaunchKernelEx(&cfg, rtp::rtp_gemm_kernel<NEMU>, params);
   if (e != cudaSuccess) return fail(std::string("launch rtp_gemm_kernel: ") + cudaGetErrorString(e));
   return 0;
@@ -178,14 +177,14 @@ int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cuda
 // ------------------------------------------------------------------------------------------------
 // workspace layout
 // ------------------------------------------------------------------------------------------------
-constexpr unsigned long long kFlagBytes = 4096;
+constexpr unsigned long long kFlagBytes = 8192;
 static_assert(sizeof(RtpFlagBlock) <= kFlagBytes, "flag block too large");
 RtpFlagBlock* ws_flags(void* ws) { return reinterpret_cast<RtpFlagBlock*>(ws); }
 uint8_t* ws_wslot(void* ws, unsigned long long slot_bytes, int i) {
   return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)i * slot_bytes;
 }
 uint8_t* ws_gslot(void* ws, unsigned long long slot_bytes, int i) {
-  return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)(2 + i) * slot_bytes;
+  return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)(RTP_NUM_SLOTS + i) * slot_bytes;
 }
 int mod(int a, int n) { return ((a % n) + n) % n; }
 
@@ -208,23 +207,21 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
   P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
 
-  // maps: 0 = x, 1 = home, 2 = W slot 0, 3 = W slot 1
+  // maps: 0 = x, 1 = home, 1+i = weight slot i-1 (read at step i)
   if (make_map_k(&P.maps[0], op.x, op.M, op.in_features, op.ldx)) return -1;
   if (make_map_k(&P.maps[1], op.home, Os, Ks, Ks)) return -1;
-  if (N > 1) {
-    if (make_map_k(&P.maps[2], ws_wslot(ws, R.slot_bytes, 0), Os, Ks, Ks)) return -1;
-    if (make_map_k(&P.maps[3], ws_wslot(ws, R.slot_bytes, 1), Os, Ks, Ks)) return -1;
-  }
+  for (int i = 1; i < N; ++i)
+    if (make_map_k(&P.maps[1 + i], ws_wslot(ws, R.slot_bytes, i - 1), Os, Ks, Ks)) return -1;
   const int bn = pick_bn(op.M, col ? Os : op.out_features, R.ctas);
   P.n_phases = N;
   for (int i = 0; i < N; ++i) {
     RtpPhase& ph = P.phases[i];
     init_phase(ph);
     const int j = mod(r + i, N);
-    const int slot = (i - 1) & 1;
+    const int slot = i - 1;   // step i reads weight slot i-1 (filled once per launch by the owner of shard j)
     const uint8_t* src = (i == 0) ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, slot);
     ph.a_map = 0;
-    ph.b_map = (i == 0) ? 1 : 2 + slot;
+    ph.b_map = (i == 0) ? 1 : 1 + i;
     ph.M = op.M;
     ph.N = Os;
     ph.K = Ks;
@@ -247,7 +244,7 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
     }
     if (i > 0) {
       ph.wait_ctr[0] = RTP_CTR_W0 + slot;
-      ph.wait_rel[0] = (i - 1) / 2;
+      ph.wait_rel[0] = 0;
       ph.done_ctr[0] = RTP_CTR_W0 + slot;
     }
     set_vec_ok(ph);
@@ -257,24 +254,29 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
     RtpPush& pu = P.pushes[i];
     memset(&pu, 0, sizeof(pu));
     const int t = mod(r - (i + 1), N);
-    const int slot = i & 1;
+    const int slot = i;
     pu.src = op.home;
     pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
     pu.bytes = op.shard_bytes;
     pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
     pu.credit_ctr = RTP_CTR_W0 + slot;
-    pu.credit_rel = i / 2;
+    pu.credit_rel = 0;
     pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
+    P.uses_inc[RTP_CTR_W0 + slot] = 1;
   }
-  P.uses_inc[RTP_CTR_W0] = N / 2;        // ceil((N-1)/2)
-  P.uses_inc[RTP_CTR_W1] = (N - 1) / 2;  // floor((N-1)/2)
   return 0;
 }
 
 int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
+  // Backward on a ring of N ranks.  Rank r visits the shards in the order r-1, r-2, ..., r (step s handles shard
+  // j = r-1-s; weights are pushed by their owners into weight slot s).  The weight gradient of shard j computed here
+  // does not hop around the ring: NVSwitch makes every peer equally near, so it is stored straight into gradient slot
+  // number s of the OWNER j (each owner receives N-1 slots, one per peer, plus its own contribution in a local slot)
+  // and the owner adds the N contributions in one last phase.  No phase waits for another rank's compute, so all 2N
+  // GEMM phases of a launch are free to run concurrently across the grid.
   init_program(P);
   const int N = R.world, r = R.rank;
-  if (N < 1 || N > RTP_MAX_WORLD || 2 * N > RTP_MAX_PHASES) return fail("world size out of range");
+  if (N < 1 || N > RTP_MAX_WORLD || 2 * N + 1 > RTP_MAX_PHASES) return fail("world size out of range");
   const bool col = op.mode == 0;
   if (col ? (op.out_features % N) : (op.in_features % N)) return fail("features not divisible by world size");
   const int Os = col ? op.out_features / N : op.out_features;
@@ -285,28 +287,23 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   P.flags = ws ? ws_flags(ws) : nullptr;
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
   P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
-  const int up = mod(r + 1, N);
 
   // maps: 0 = dy (MN-major view: k = tokens), 1 = x (MN-major view), 2 = dy (K-major view: k = out),
-  //       3 = home W (MN-major view: k = shard rows), 4/5 = W slots 0/1
+  //       3 = home W (MN-major view: k = shard rows), 4+s = weight slot s
   if (make_map_mn(&P.maps[0], op.dy, op.out_features, op.M, op.ldy)) return -1;
   if (make_map_mn(&P.maps[1], op.x, op.in_features, op.M, op.ldx)) return -1;
   if (op.dx) {
     if (make_map_k(&P.maps[2], op.dy, op.M, op.out_features, op.ldy)) return -1;
     if (make_map_mn(&P.maps[3], op.home, Ks, Os, Ks)) return -1;
-    if (N > 1) {
-      if (make_map_mn(&P.maps[4], ws_wslot(ws, R.slot_bytes, 0), Ks, Os, Ks)) return -1;
-      if (make_map_mn(&P.maps[5], ws_wslot(ws, R.slot_bytes, 1), Ks, Os, Ks)) return -1;
-    }
+    for (int s = 0; s + 1 < N; ++s)
+      if (make_map_mn(&P.maps[4 + s], ws_wslot(ws, R.slot_bytes, s), Ks, Os, Ks)) return -1;
   }
   int np = 0;
   for (int s = 0; s < N; ++s) {
     const int j = mod(r - 1 - s, N);
-    const int wslot = s & 1;        // weights used at step s sit in W slot s%2 (home at the last step)
-    const int gin = (s - 1) & 1;    // incoming gradient partial sits in G slot (s-1)%2
-    const int gout = s & 1;         // outgoing partial goes to the next rank's G slot s%2
-    const bool last = s == N - 1;
-    // ---- wgrad: dW_j = dy_j^T x  (+ incoming partial) -> next rank's slot, or home at the last step
+    const bool last = s == N - 1;   // own shard
+    // ---- wgrad: dW_j = dy_j^T x  -> gradient slot s of owner j (own shard: straight into the home gradient when
+    //      the ring has one rank, else into the local slot N-1 that the final reduce reads)
     {
       RtpPhase& ph = P.phases[np++];
       init_phase(ph);
@@ -315,24 +312,19 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
       ph.M = Os; ph.N = Ks; ph.K = op.M;
       if (col) ph.a_off_mn = j * Os; else ph.b_off_mn = j * Ks;
       ph.bn = pick_bn(ph.M, ph.N, R.ctas);
-      uint8_t* dst = last ? reinterpret_cast<uint8_t*>(op.grad_home) : ws_gslot(R.ws[up], R.slot_bytes, gout);
+      uint8_t* dst;
+      if (N == 1) dst = reinterpret_cast<uint8_t*>(op.grad_home);
+      else dst = ws_gslot(R.ws[j], R.slot_bytes, s);
       ph.d = dst; ph.ldd = Ks;
-      const uint8_t* cin = nullptr;
-      if (s > 0) {
-        cin = ws_gslot(ws, R.slot_bytes, gin);
-        ph.c = cin; ph.ldc = Ks;
-        ph.wait_ctr[0] = RTP_CTR_G0 + gin; ph.wait_rel[0] = (s - 1) / 2;
-        ph.done_ctr[0] = RTP_CTR_G0 + gin;
-      }
-      if (op.grad_accumulate && N == 1) { cin = reinterpret_cast<const uint8_t*>(op.grad_home); ph.c = cin; ph.ldc = Ks; }
-      if (!last) {
-        ph.credit_ptr = &ws_flags(R.ws[up])->done[RTP_CTR_G0 + gout].v;
-        ph.credit_ctr = RTP_CTR_G0 + gout; ph.credit_rel = s / 2;
-        ph.arrive_ptr = &ws_flags(R.ws[up])->arrive[RTP_CTR_G0 + gout].v;
+      if (op.grad_accumulate && N == 1) { ph.c = op.grad_home; ph.ldc = Ks; }
+      if (N > 1) {
+        ph.credit_ptr = &ws_flags(R.ws[j])->done[RTP_CTR_G0 + s].v;
+        ph.credit_ctr = RTP_CTR_G0 + s; ph.credit_rel = 0;
+        ph.arrive_ptr = &ws_flags(R.ws[j])->arrive[RTP_CTR_G0 + s].v;
       }
       if (op.bias_off >= 0 && op.dbias_full) {
         ph.vec_out = reinterpret_cast<__nv_bfloat16*>(dst) + op.bias_off;
-        ph.vec_in = cin ? reinterpret_cast<const __nv_bfloat16*>(cin) + op.bias_off : nullptr;
+        ph.vec_in = (op.grad_accumulate && N == 1) ? reinterpret_cast<const __nv_bfloat16*>(op.grad_home) + op.bias_off : nullptr;
         ph.vec_add = op.dbias_full + (col ? (long long)j * Os : 0);
         ph.vec_len = Os;
       }
@@ -343,7 +335,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
       RtpPhase& ph = P.phases[np++];
       init_phase(ph);
       ph.a_map = 2; ph.a_mn = 0;
-      ph.b_map = last ? 3 : 4 + wslot; ph.b_mn = 1;
+      ph.b_map = last ? 3 : 4 + s; ph.b_mn = 1;
       ph.M = op.M; ph.N = Ks; ph.K = Os;
       if (col) ph.a_off_k = j * Os;
       ph.bn = pick_bn(ph.M, ph.N, R.ctas);
@@ -356,34 +348,44 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
         ph.ldmask = op.ldmask; ph.mask_scale = op.mask_scale;
       }
       if (!last) {
-        ph.wait_ctr[0] = RTP_CTR_W0 + wslot; ph.wait_rel[0] = s / 2;
-        ph.done_ctr[0] = RTP_CTR_W0 + wslot;
+        ph.wait_ctr[0] = RTP_CTR_W0 + s; ph.wait_rel[0] = 0;
+        ph.done_ctr[0] = RTP_CTR_W0 + s;
       }
       set_vec_ok(ph);
     }
   }
+  // ---- owner-side sum of the N gradient slots (slot s was written by rank r+1+s; slot N-1 by this rank)
+  if (N > 1) {
+    RtpPhase& ph = P.phases[np++];
+    init_phase(ph);
+    ph.kind = RTP_KIND_REDUCE;
+    ph.M = ph.N = ph.K = 0;
+    ph.d = op.grad_home;
+    ph.r_nsrc = N;
+    ph.r_n = (long long)(op.shard_bytes / 2) & ~7ll;
+    for (int s = 0; s < N; ++s) {
+      ph.r_src[s] = ws_gslot(ws, R.slot_bytes, s);
+      ph.wait_ctr[s] = RTP_CTR_G0 + s; ph.wait_rel[s] = 0;
+      ph.done_ctr[s] = RTP_CTR_G0 + s;
+      P.uses_inc[RTP_CTR_G0 + s] = 1;
+    }
+  }
   P.n_phases = np;
-  // weight pushes: at step s the owner q sends its home shard to rank q+1+s, which uses it at its step s
+  // weight pushes: the owner q sends its home shard to rank q+1+s, which uses it at its step s (weight slot s)
   P.n_pushes = op.dx ? N - 1 : 0;
   for (int s = 0; s + 1 < N && op.dx; ++s) {
     RtpPush& pu = P.pushes[s];
     memset(&pu, 0, sizeof(pu));
     const int t = mod(r + 1 + s, N);
-    const int slot = s & 1;
     pu.src = op.home;
-    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, s);
     pu.bytes = op.shard_bytes;
-    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
-    pu.credit_ctr = RTP_CTR_W0 + slot;
-    pu.credit_rel = s / 2;
-    pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
+    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + s].v;
+    pu.credit_ctr = RTP_CTR_W0 + s;
+    pu.credit_rel = 0;
+    pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + s].v;
+    P.uses_inc[RTP_CTR_W0 + s] = 1;
   }
-  if (op.dx) {
-    P.uses_inc[RTP_CTR_W0] = N / 2;
-    P.uses_inc[RTP_CTR_W1] = (N - 1) / 2;
-  }
-  P.uses_inc[RTP_CTR_G0] = N / 2;
-  P.uses_inc[RTP_CTR_G1] = (N - 1) / 2;
   return 0;
 }
 
@@ -403,7 +405,7 @@ int build_embed_fwd(const RtpRing& R, const RtpEmbedFwd& op, RtpProgram& P) {
     RtpPhase& ph = P.phases[i];
     init_phase(ph);
     const int j = mod(r + i, N);
-    const int slot = (i - 1) & 1;
+    const int slot = i - 1;
     ph.kind = RTP_KIND_GATHER;
     ph.M = ph.N = ph.K = 0;
     ph.g_table = (i == 0) ? op.home : ws_wslot(ws, R.slot_bytes, slot);
@@ -417,7 +419,7 @@ int build_embed_fwd(const RtpRing& R, const RtpEmbedFwd& op, RtpProgram& P) {
     ph.drop_seed = op.seed; ph.drop_offset = op.offset; ph.drop_step_ptr = op.step_ptr;
     if (i > 0) {
       ph.wait_ctr[0] = RTP_CTR_W0 + slot;
-      ph.wait_rel[0] = (i - 1) / 2;
+      ph.wait_rel[0] = 0;
       ph.done_ctr[0] = RTP_CTR_W0 + slot;
     }
   }
@@ -426,17 +428,16 @@ int build_embed_fwd(const RtpRing& R, const RtpEmbedFwd& op, RtpProgram& P) {
     RtpPush& pu = P.pushes[i];
     memset(&pu, 0, sizeof(pu));
     const int t = mod(r - (i + 1), N);
-    const int slot = i & 1;
+    const int slot = i;
     pu.src = op.home;
     pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
     pu.bytes = op.shard_bytes;
     pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
     pu.credit_ctr = RTP_CTR_W0 + slot;
-    pu.credit_rel = i / 2;
+    pu.credit_rel = 0;
     pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
+    P.uses_inc[RTP_CTR_W0 + slot] = 1;
   }
-  P.uses_inc[RTP_CTR_W0] = N / 2;
-  P.uses_inc[RTP_CTR_W1] = (N - 1) / 2;
   return 0;
 }
 
@@ -475,15 +476,24 @@ int build_reduce_scatter(const RtpRing& R, const RtpReduceScatter& op, RtpProgra
     }
   }
   P.uses_inc[RTP_CTR_G0] = N / 2;
-  P.uses_inc[RTP_CTR_G1] = (N - 1) / 2;
+  P.uses_inc[RTP_CTR_G0 + 1] = (N - 1) / 2;
   return 0;
 }
 
 template <int NEMU, class Op, class Builder>
 int run_emu(const RtpRing* rings, const Op* ops, Builder build, cudaStream_t stream) {
-  static rtp::GemmParams<NEMU> params;  // large; keep off the stack
-  for (int e = 0; e < NEMU; ++e)
-    if (build(rings[e], ops[e], params.prog[e])) return -1;
+  static RtpProgram progs[RTP_MAX_EMU_RANKS];
+  static rtp::GemmParams<NEMU> params;
+  for (int e = 0; e < NEMU; ++e) {
+    if (build(rings[e], ops[e], progs[e])) return -1;
+    finalize_program(progs[e], rings[0].ctas);
+  }
+  cudaError_t err = cudaMemcpyToSymbolAsync(rtp::c_emu_progs, progs, sizeof(RtpProgram) * NEMU, 0,
+                                            cudaMemcpyHostToDevice, stream);
+  if (err != cudaSuccess) return fail(std::string("copy of emulated programs: ") + cudaGetErrorString(err));
+  // the host array is reused by the next call: wait until the copy has read it
+  err = cudaStreamSynchronize(stream);
+  if (err != cudaSuccess) return fail(std::string("stream sync: ") + cudaGetErrorString(err));
   params.ctas_per_rank = rings[0].ctas;
   return launch<NEMU>(params, rings[0].ctas * NEMU, true, stream);
 }
@@ -615,7 +625,7 @@ int rtp_linear_bwd_emu(const RtpRing* rings, const RtpLinearBwd* ops, int world,
 }
 
 // ------------------------------------------------------------------------------------- workspace
-unsigned long long rtp_ws_bytes(unsigned long long slot_bytes) { return kFlagBytes + 4 * slot_bytes; }
+unsigned long long rtp_ws_bytes(unsigned long long slot_bytes) { return kFlagBytes + 2 * RTP_NUM_SLOTS * slot_bytes; }
 int rtp_ws_create(unsigned long long slot_bytes, void** out) {
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, rtp_ws_bytes(slot_bytes));

@@ -36,11 +36,14 @@ struct SmemCtrl {
   uint32_t abort_flag;
 };
 
+// One rank per launch: the program travels as a kernel parameter.  Emulated ranks (several programs in one
+// cooperative launch on one GPU) read their programs from constant memory instead, which is large enough for four.
 template <int NEMU>
 struct GemmParams {
-  RtpProgram prog[NEMU];
+  RtpProgram prog[NEMU == 1 ? 1 : 1];
   int ctas_per_rank;
 };
+__constant__ RtpProgram c_emu_progs[RTP_MAX_EMU_RANKS];
 
 __device__ __forceinline__ unsigned long long fill_target(const RtpFlagBlock* fb, int ctr, int rel, int plus,
                                                           int G) {
@@ -54,7 +57,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
   const int G = params.ctas_per_rank;
   const int vrank = (NEMU == 1) ? 0 : (int)(blockIdx.x / G);
   const int cta = (NEMU == 1) ? (int)blockIdx.x : (int)(blockIdx.x % G);
-  const RtpProgram& P = params.prog[vrank];
+  const RtpProgram& P = (NEMU == 1) ? params.prog[0] : c_emu_progs[vrank];
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemCtrl* ctl = reinterpret_cast<SmemCtrl*>(tiles + kTileBytes);
@@ -107,15 +110,17 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const int per_batch = tiles_m * tiles_n;
         const int total = per_batch * ph.batch;
         if ((cta - ph.cta_off + G) % G >= total) continue;
-        for (int w = 0; w < 2 && ok; ++w) {
+        bool any_wait = false;
+        for (int w = 0; w < RTP_MAX_WAITS && ok; ++w) {
           if (ph.wait_ctr[w] >= 0) {
+            any_wait = true;
             ok = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
                                  fill_target(P.flags, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
                                  wait_ns, ST_TIMEOUT_ARRIVAL);
           }
         }
         if (!ok) break;
-        if (ph.wait_ctr[0] >= 0 || ph.wait_ctr[1] >= 0) fence_proxy_async();
+        if (any_wait) fence_proxy_async();
         const CUtensorMap* ma = &P.maps[ph.a_map];
         const CUtensorMap* mb = &P.maps[ph.b_map];
         const int kblocks_full = (ph.K + kBK - 1) / kBK;
@@ -248,7 +253,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         // publishes its signal for fill u+1 before fill u+1 exists.
         uint32_t good = 1;
         if (lane == 0) {
-          for (int w = 0; w < 2 && good; ++w)
+          for (int w = 0; w < RTP_MAX_WAITS && good; ++w)
             if (ph.wait_ctr[w] >= 0)
               good = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
                                      fill_target(P.flags, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
@@ -308,6 +313,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           }
           *reinterpret_cast<uint4*>(outp + r * ph.v_cols + c) =
               make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        }
+      }
+      if (ok && ph.kind == RTP_KIND_REDUCE) {
+        const long long items = ph.r_n >> 3;
+        __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(ph.d);
+        for (long long it = (long long)cta * 128 + epi_tid; it < items; it += (long long)G * 128) {
+          float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int k = 0; k < ph.r_nsrc; ++k) {
+            const uint4 a = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(ph.r_src[k]) + it * 8));
+            acc8[0] += bf16_lo(a.x); acc8[1] += bf16_hi(a.x); acc8[2] += bf16_lo(a.y); acc8[3] += bf16_hi(a.y);
+            acc8[4] += bf16_lo(a.z); acc8[5] += bf16_hi(a.z); acc8[6] += bf16_lo(a.w); acc8[7] += bf16_hi(a.w);
+          }
+          *reinterpret_cast<uint4*>(outp + it * 8) = make_uint4(pack_bf16(acc8[0], acc8[1]), pack_bf16(acc8[2], acc8[3]),
+                                                                 pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
         }
       }
       for (int t = (cta - ph.cta_off + G) % G; t < total && ok; t += G) {
@@ -465,12 +484,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         }
       }
       // phase end: publish "read done" / "data arrived". Every CTA signals, also one without tiles.
-      const bool signals = ph.done_ctr[0] >= 0 || ph.done_ctr[1] >= 0 || ph.arrive_ptr != nullptr;
+      bool signals = ph.arrive_ptr != nullptr;
+      for (int w = 0; w < RTP_MAX_WAITS; ++w) signals = signals || ph.done_ctr[w] >= 0;
       if (signals) {
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (epi_tid == 0 && ok) {
-          for (int w = 0; w < 2; ++w)
+          for (int w = 0; w < RTP_MAX_WAITS; ++w)
             if (ph.done_ctr[w] >= 0) red_release_sys_add(&P.flags->done[ph.done_ctr[w]].v, 1ull);
           if (ph.arrive_ptr) red_release_sys_add(ph.arrive_ptr, 1ull);
         }

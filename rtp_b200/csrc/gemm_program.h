@@ -9,17 +9,17 @@
 #include <cuda.h>
 #include <stdint.h>
 
-#define RTP_MAX_MAPS 8
-#define RTP_MAX_PHASES 16
+#define RTP_MAX_MAPS 12
+#define RTP_MAX_PHASES 18
 #define RTP_MAX_PUSHES 8
 #define RTP_MAX_EMU_RANKS 4
 
 // indices into FlagBlock::arrive / ::done / ::uses
+#define RTP_NUM_SLOTS 8            // weight slots W0..W7 and gradient slots G0..G7 per rank
 #define RTP_CTR_W0 0
-#define RTP_CTR_W1 1
-#define RTP_CTR_G0 2
-#define RTP_CTR_G1 3
-#define RTP_NUM_CTR 4
+#define RTP_CTR_G0 8
+#define RTP_NUM_CTR 16
+#define RTP_MAX_WAITS 8
 
 // Per-rank flag block (peer-mapped). Every word sits in its own 128-byte line.
 struct alignas(128) RtpFlagWord {
@@ -37,6 +37,7 @@ struct RtpFlagBlock {
 #define RTP_KIND_GEMM 0
 #define RTP_KIND_GATHER 1   // embedding lookup from a visiting table shard
 #define RTP_KIND_VECADD 2   // out[r, c] = src[r, c] (+ in[r, c]): one hop of a ring reduce-scatter
+#define RTP_KIND_REDUCE 3   // out[i] = sum_k src_k[i] over r_nsrc flat bf16 buffers (owner-side sum of gradient slots)
 
 struct RtpPhase {
   int kind;
@@ -51,6 +52,10 @@ struct RtpPhase {
   const void* v_src;
   long long v_ld;
   int v_rows, v_cols;
+  // ---- RTP_KIND_REDUCE
+  const void* r_src[RTP_NUM_SLOTS];
+  int r_nsrc;
+  long long r_n;  // elements, multiple of 8
   // operands (bf16). *_mn = 1: the operand is stored with its M (or N) index contiguous.
   int a_map, b_map;
   int a_mn, b_mn;
@@ -93,12 +98,12 @@ struct RtpPhase {
   int vec_len;
   int vec_fp32;  // dtype of vec_out / vec_in
   // synchronisation (all optional)
-  int wait_ctr[2];  // local arrival counters that must reach fill (uses + rel + 1) before operands are read
-  int wait_rel[2];
+  int wait_ctr[RTP_MAX_WAITS];  // local arrival counters that must reach fill (uses + rel + 1) before operands are read
+  int wait_rel[RTP_MAX_WAITS];
   unsigned long long* credit_ptr;  // remote `done` counter that must reach fill (uses + rel) before d is written
   int credit_ctr;
   int credit_rel;
-  int done_ctr[2];                 // local `done` counters bumped when this CTA has finished the phase
+  int done_ctr[RTP_MAX_WAITS];     // local `done` counters bumped when this CTA has finished the phase
   unsigned long long* arrive_ptr;  // remote `arrive` counter bumped when this CTA has finished the phase
 };
 

@@ -7,7 +7,7 @@
 
 namespace {
 
-// [0, 4096): flag/status block of the rotation kernel.  [4096, ...): fp32 column sums of dy.
+// [0, 8192): flag/status block of the rotation kernel.  [8192, ...): fp32 column sums of dy.
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not a device pointer.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[RTP_NOALLOC_SCRATCH_BYTES];
 
@@ -53,9 +53,9 @@ int rtp_linear_bwd_noalloc(const void* x, long long ldx, const void* dy, long lo
   if (scratch_for_current_device(&scratch)) return -1;
   cudaStream_t s = (cudaStream_t)stream;
   // the flag/status block must start at zero; the column sums are zeroed by rtp_colsum itself
-  cudaError_t e = cudaMemsetAsync(scratch, 0, 4096, s);
+  cudaError_t e = cudaMemsetAsync(scratch, 0, 8192, s);
   if (e != cudaSuccess) return nfail(std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
-  float* dbias = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + 4096);
+  float* dbias = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + 8192);
   if (bias_off >= 0) {
     if (rtp_colsum(dy, ldy, M, out_features, dbias, stream)) return nfail(rtp_kernels_last_error());
   }

@@ -12,7 +12,7 @@
 //
 // Limits and rules:
 //   * out_features <= RTP_NOALLOC_MAX_OUT_FEATURES, else the call fails with a clear error and launches nothing.
-//     The array costs RTP_NOALLOC_SCRATCH_BYTES (about 260 KB) of device memory on every GPU that loads the
+//     The array costs RTP_NOALLOC_SCRATCH_BYTES (about 264 KB) of device memory on every GPU that loads the
 //     library, from load until the process exits.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and sets a kernel
 //     attribute.  Make that first call before starting any stream capture.
@@ -28,7 +28,7 @@ extern "C" {
 #endif
 
 #define RTP_NOALLOC_MAX_OUT_FEATURES 65536
-#define RTP_NOALLOC_SCRATCH_BYTES (4096 + 4 * RTP_NOALLOC_MAX_OUT_FEATURES)
+#define RTP_NOALLOC_SCRATCH_BYTES (8192 + 4 * RTP_NOALLOC_MAX_OUT_FEATURES)
 
 int rtp_linear_bwd_noalloc(const void* x, long long ldx, const void* dy, long long ldy, const void* w,
                            long long bias_off, int M, int in_features, int out_features, void* dx, long long lddx,
