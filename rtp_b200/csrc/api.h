@@ -85,6 +85,34 @@ typedef struct {
 } RtpLinearBwd;
 int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream);
 
+// Rotating experts (MoE): rank r owns n_local whole experts; x / y hold the dispatched tokens expert-major
+// ([world*n_local*cap, features], expert g = rows [g*cap, (g+1)*cap)).  One launch applies ONE linear of every
+// expert (y_g = act(x_g W_g^T + b_g)) while the flat range that holds the local experts' (weight, bias) blocks
+// visits every rank.  Tokens never leave their GPU.
+typedef struct {
+  int cap, n_local, in_features, out_features;
+  const void* home;                    // n_local blocks: weight [out, in] at e*expert_stride, bias at + bias_off
+  long long expert_stride, bias_off;   // elements (bias_off -1: no bias)
+  unsigned long long shard_bytes;
+  const void* x; long long ldx;
+  void* y; long long ldy;
+  int act;
+} RtpExpertFwd;
+int rtp_expert_fwd(const RtpRing* ring, const RtpExpertFwd* op, void* stream);
+typedef struct {
+  int cap, n_local, in_features, out_features;
+  const void* home; long long expert_stride, bias_off; unsigned long long shard_bytes;
+  const void* x; long long ldx;
+  const void* dy; long long ldy;
+  void* dx; long long lddx;            // may be null
+  void* grad_home;                     // same layout as home
+  const float* dbias_full;             // fp32 [world*n_local, out] per-expert column sums of dy (null: no bias)
+  const void* mask; long long ldmask; float mask_scale;   // optional activation backward applied to dx
+} RtpExpertBwd;
+int rtp_expert_bwd(const RtpRing* ring, const RtpExpertBwd* op, void* stream);
+int rtp_expert_fwd_emu(const RtpRing* rings, const RtpExpertFwd* ops, int world, void* stream);
+int rtp_expert_bwd_emu(const RtpRing* rings, const RtpExpertBwd* ops, int world, void* stream);
+
 // Rotated embedding lookup: the table is sharded along the embedding dim ([V, D/N] per rank); shard j fills
 // columns [j*D/N, (j+1)*D/N) of out.  out = dropout(table[ids] * scale + pe[t / tokens_per_pos]).
 typedef struct {
@@ -127,6 +155,8 @@ void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i);
 void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i);
 int rtp_sm_count(void);
 const char* rtp_last_error(void);
+void rtp_set_pair_mode(int on);        // 1: CTA pairs (cta_group::2 UMMA, half of the B tile per SM); default from env RTP_PAIR
+void rtp_debug_set_trace(unsigned long long* device_buffer_768_words);  // tuning aid: globaltimer timeline of CTA 0 of rtp_gemm launches (null = off)
 void rtp_debug_force_stages(int n);   // tuning aid: cap the smem pipeline depth (0 = automatic)
 
 #ifdef __cplusplus

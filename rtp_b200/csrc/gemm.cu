@@ -15,6 +15,7 @@
 #include <string>
 #include <cstring>
 #include <cstdio>
+#include <cstdlib>
 #include "api.h"
 #include "gemm_kernel.cuh"
 
@@ -99,7 +100,20 @@ void set_vec_ok(RtpPhase& ph) {
   if (ph.mask) ok = ok && aligned16(ph.mask, ph.ldmask, 2);
   ph.vec_ok = ok ? 1 : 0;
 }
+// CTA-pair mode (cta_group::2): 0 = off, 1 = on for launches whose grid is even.  Default from RTP_PAIR.
+int g_pair = -1;
+bool pair_mode() {
+  if (g_pair < 0) {
+    const char* e = getenv("RTP_PAIR");
+    g_pair = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_pair == 1;
+}
 int pick_bn(int M, int N, int ctas) {
+  if (pair_mode()) {
+    long long t256 = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    return (t256 >= ctas / 2) ? 256 : 128;
+  }
   long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
   return (t256 >= ctas) ? 256 : 128;
 }
@@ -112,7 +126,9 @@ uint32_t drop_threshold(float p) {
 
 // Pipeline geometry: the stage must hold the widest B tile of the program; narrower tiles get more stages.
 int g_force_stages = 0;
-void finalize_program(RtpProgram& P, int ctas) {
+void finalize_program(RtpProgram& P, int ctas, bool pair) {
+  const int tm = pair ? 256 : 128;
+  if (pair) ctas /= 2;
   // Tile t of a phase runs on CTA (t + cta_off) % ctas.  Successive phases start where the previous one ended, so
   // that small per-step GEMMs fill the whole grid.  A phase that accumulates into the output of an earlier phase
   // (C == that phase's D) must keep that phase's mapping: the read-modify-write of a tile then stays inside one CTA,
@@ -121,7 +137,7 @@ void finalize_program(RtpProgram& P, int ctas) {
   for (int i = 0; i < P.n_phases; ++i) {
     RtpPhase& ph = P.phases[i];
     if (ph.kind != RTP_KIND_GEMM) { ph.cta_off = 0; continue; }
-    const long long tiles = (long long)((ph.M + 127) / 128) * ((ph.N + ph.bn - 1) / ph.bn) * ph.batch;
+    const long long tiles = (long long)((ph.M + tm - 1) / tm) * ((ph.N + ph.bn - 1) / ph.bn) * ph.batch;
     int chained = -1;
     if (ph.c)
       for (int k = 0; k < i; ++k)
@@ -135,21 +151,22 @@ void finalize_program(RtpProgram& P, int ctas) {
       acc += tiles;
     }
   }
-  int bn = 128;
-  for (int i = 0; i < P.n_phases; ++i)
-    if (P.phases[i].kind == RTP_KIND_GEMM && P.phases[i].bn > bn) bn = P.phases[i].bn;
-  // spread the tiles of successive phases over the grid (ctas = grid size of one rank)
+  int bn = pair ? 64 : 128;   // widest B tile staged by ONE CTA
+  for (int i = 0; i < P.n_phases; ++i) {
+    const int w = pair ? P.phases[i].bn / 2 : P.phases[i].bn;
+    if (P.phases[i].kind == RTP_KIND_GEMM && w > bn) bn = w;
+  }
   P.stage_bytes = rtp::kABytes + bn * rtp::kBK * 2;
   P.n_stages = rtp::kTileBytes / P.stage_bytes;
   if (P.n_stages > rtp::kMaxStages) P.n_stages = rtp::kMaxStages;
   if (g_force_stages > 0 && g_force_stages < P.n_stages) P.n_stages = g_force_stages;
 }
 
-template <int NEMU>
-int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cudaStream_t stream) {
+template <int NEMU, bool PAIR>
+int launch_impl(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(rtp::rtp_gemm_kernel<NEMU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(rtp::rtp_gemm_kernel<NEMU, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          rtp::kSmemBytes);
     if (e != cudaSuccess) return fail(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     attr_set = true;
@@ -159,19 +176,33 @@ int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cuda
   cfg.blockDim = dim3(rtp::kNumThreads);
   cfg.dynamicSmemBytes = rtp::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   int nat = 0;
   if (cooperative) {
-    at[0].id = cudaLaunchAttributeCooperative;
-    at[0].val.cooperative = 1;
-    nat = 1;
+    at[nat].id = cudaLaunchAttributeCooperative;
+    at[nat].val.cooperative = 1;
+    ++nat;
+  }
+  if (PAIR) {
+    at[nat].id = cudaLaunchAttributeClusterDimension;
+    at[nat].val.clusterDim.x = 2;
+    at[nat].val.clusterDim.y = 1;
+    at[nat].val.clusterDim.z = 1;
+    ++nat;
   }
   cfg.attrs = at;
   cfg.numAttrs = nat;
-  if (NEMU == 1) finalize_program(const_cast<RtpProgram&>(params.prog[0]), params.ctas_per_rank);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, rtp::rtp_gemm_kernel<NEMU>, params);
+  if (NEMU == 1) finalize_program(const_cast<RtpProgram&>(params.prog[0]), params.ctas_per_rank, PAIR);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, rtp::rtp_gemm_kernel<NEMU, PAIR>, params);
   if (e != cudaSuccess) return fail(std::string("launch rtp_gemm_kernel: ") + cudaGetErrorString(e));
   return 0;
+}
+// `allow_pair`: the caller built the program with pair-compatible tensor maps and tile widths
+template <int NEMU>
+int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cudaStream_t stream, bool allow_pair = false) {
+  if (NEMU == 1 && allow_pair && pair_mode() && grid % 2 == 0 && params.ctas_per_rank % 2 == 0)
+    return launch_impl<1, true>(reinterpret_cast<const rtp::GemmParams<1>&>(params), grid, cooperative, stream);
+  return launch_impl<NEMU, false>(params, grid, cooperative, stream);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -209,10 +240,11 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
 
   // maps: 0 = x, 1 = home, 1+i = weight slot i-1 (read at step i)
   if (make_map_k(&P.maps[0], op.x, op.M, op.in_features, op.ldx)) return -1;
-  if (make_map_k(&P.maps[1], op.home, Os, Ks, Ks)) return -1;
-  for (int i = 1; i < N; ++i)
-    if (make_map_k(&P.maps[1 + i], ws_wslot(ws, R.slot_bytes, i - 1), Os, Ks, Ks)) return -1;
   const int bn = pick_bn(op.M, col ? Os : op.out_features, R.ctas);
+  const int b_box = pair_mode() ? bn / 2 : 128;
+  if (make_map_k(&P.maps[1], op.home, Os, Ks, Ks, b_box)) return -1;
+  for (int i = 1; i < N; ++i)
+    if (make_map_k(&P.maps[1 + i], ws_wslot(ws, R.slot_bytes, i - 1), Os, Ks, Ks, b_box)) return -1;
   P.n_phases = N;
   for (int i = 0; i < N; ++i) {
     RtpPhase& ph = P.phases[i];
@@ -226,6 +258,7 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
     ph.N = Os;
     ph.K = Ks;
     ph.bn = bn;
+    ph.b_box = b_box;
     ph.ldd = op.ldy;
     ph.d = reinterpret_cast<__nv_bfloat16*>(op.y) + (col ? (long long)j * Os : 0);
     if (!col) {
@@ -389,6 +422,166 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   return 0;
 }
 
+int build_expert_fwd(const RtpRing& R, const RtpExpertFwd& op, RtpProgram& P) {
+  init_program(P);
+  const int N = R.world, r = R.rank, L = op.n_local;
+  if (N < 1 || N > RTP_MAX_WORLD || L < 1) return fail("world size out of range");
+  if (N * L > RTP_MAX_PHASES || 1 + N * L > RTP_MAX_MAPS) return fail("too many experts for one launch");
+  if (N > 1 && op.shard_bytes > R.slot_bytes) return fail("shard larger than workspace slot");
+  if (op.shard_bytes % 16) return fail("shard_bytes must be a multiple of 16");
+  void* ws = R.ws[r];
+  P.flags = ws ? ws_flags(ws) : nullptr;
+  P.status = ws ? &ws_flags(ws)->status.v : nullptr;
+  P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
+  const long long rows = (long long)N * L * op.cap;
+  if (make_map_k(&P.maps[0], op.x, rows, op.in_features, op.ldx)) return -1;
+  const int bn = pick_bn(op.cap, op.out_features, R.ctas);
+  const int b_box = pair_mode() ? bn / 2 : 128;
+  int np = 0;
+  for (int i = 0; i < N; ++i) {
+    const int j = mod(r + i, N);
+    const uint8_t* src = (i == 0) ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, i - 1);
+    for (int e = 0; e < L; ++e) {
+      const int g = j * L + e;
+      const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(src) + (long long)e * op.expert_stride;
+      const int mi = 1 + i * L + e;
+      if (make_map_k(&P.maps[mi], w, op.out_features, op.in_features, op.in_features, b_box)) return -1;
+      RtpPhase& ph = P.phases[np++];
+      init_phase(ph);
+      ph.a_map = 0; ph.b_map = mi;
+      ph.a_off_mn = g * op.cap;
+      ph.M = op.cap; ph.N = op.out_features; ph.K = op.in_features;
+      ph.bn = bn; ph.b_box = b_box;
+      ph.d = reinterpret_cast<__nv_bfloat16*>(op.y) + (long long)g * op.cap * op.ldy;
+      ph.ldd = op.ldy;
+      if (op.bias_off >= 0) ph.bias = w + op.bias_off;
+      ph.act = op.act;
+      if (i > 0) {
+        ph.wait_ctr[0] = RTP_CTR_W0 + (i - 1); ph.wait_rel[0] = 0;
+        if (e == L - 1) ph.done_ctr[0] = RTP_CTR_W0 + (i - 1);
+      }
+      set_vec_ok(ph);
+    }
+  }
+  P.n_phases = np;
+  P.n_pushes = N - 1;
+  for (int i = 0; i + 1 < N; ++i) {
+    RtpPush& pu = P.pushes[i];
+    memset(&pu, 0, sizeof(pu));
+    const int t = mod(r - (i + 1), N);
+    pu.src = op.home;
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, i);
+    pu.bytes = op.shard_bytes;
+    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + i].v;
+    pu.credit_ctr = RTP_CTR_W0 + i;
+    pu.credit_rel = 0;
+    pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + i].v;
+    P.uses_inc[RTP_CTR_W0 + i] = 1;
+  }
+  return 0;
+}
+
+int build_expert_bwd(const RtpRing& R, const RtpExpertBwd& op, RtpProgram& P) {
+  init_program(P);
+  const int N = R.world, r = R.rank, L = op.n_local;
+  if (N < 1 || N > RTP_MAX_WORLD || L < 1) return fail("world size out of range");
+  if (2 * N * L + 1 > RTP_MAX_PHASES || 3 + N * L > RTP_MAX_MAPS) return fail("too many experts for one launch");
+  if (N > 1 && op.shard_bytes > R.slot_bytes) return fail("shard larger than workspace slot");
+  void* ws = R.ws[r];
+  P.flags = ws ? ws_flags(ws) : nullptr;
+  P.status = ws ? &ws_flags(ws)->status.v : nullptr;
+  P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
+  const long long rows = (long long)N * L * op.cap;
+  // maps: 0 = dy (tokens are k), 1 = x (tokens are k), 2 = dy (out is k), 3.. = expert weights (home / slots)
+  if (make_map_mn(&P.maps[0], op.dy, op.out_features, rows, op.ldy)) return -1;
+  if (make_map_mn(&P.maps[1], op.x, op.in_features, rows, op.ldx)) return -1;
+  if (op.dx && make_map_k(&P.maps[2], op.dy, rows, op.out_features, op.ldy)) return -1;
+  int np = 0;
+  for (int s = 0; s < N; ++s) {
+    const int j = mod(r - 1 - s, N);
+    const bool last = s == N - 1;
+    const uint8_t* wsrc = last ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, s);
+    uint8_t* gdst = (N == 1) ? reinterpret_cast<uint8_t*>(op.grad_home) : ws_gslot(R.ws[j], R.slot_bytes, s);
+    for (int e = 0; e < L; ++e) {
+      const int g = j * L + e;
+      {  // wgrad of expert g
+        RtpPhase& ph = P.phases[np++];
+        init_phase(ph);
+        ph.a_map = 0; ph.a_mn = 1; ph.a_off_k = g * op.cap;
+        ph.b_map = 1; ph.b_mn = 1; ph.b_off_k = g * op.cap;
+        ph.M = op.out_features; ph.N = op.in_features; ph.K = op.cap;
+        ph.bn = pick_bn(ph.M, ph.N, R.ctas);
+        __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(gdst) + (long long)e * op.expert_stride;
+        ph.d = d; ph.ldd = op.in_features;
+        if (N > 1) {
+          ph.credit_ptr = &ws_flags(R.ws[j])->done[RTP_CTR_G0 + s].v;
+          ph.credit_ctr = RTP_CTR_G0 + s; ph.credit_rel = 0;
+          if (e == L - 1) ph.arrive_ptr = &ws_flags(R.ws[j])->arrive[RTP_CTR_G0 + s].v;
+        }
+        if (op.bias_off >= 0 && op.dbias_full) {
+          ph.vec_out = d + op.bias_off;
+          ph.vec_add = op.dbias_full + (long long)g * op.out_features;
+          ph.vec_len = op.out_features;
+        }
+        set_vec_ok(ph);
+      }
+      if (op.dx) {  // dgrad of expert g
+        const int mi = 3 + s * L + e;
+        const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(wsrc) + (long long)e * op.expert_stride;
+        if (make_map_mn(&P.maps[mi], w, op.in_features, op.out_features, op.in_features)) return -1;
+        RtpPhase& ph = P.phases[np++];
+        init_phase(ph);
+        ph.a_map = 2; ph.a_off_mn = g * op.cap;
+        ph.b_map = mi; ph.b_mn = 1;
+        ph.M = op.cap; ph.N = op.in_features; ph.K = op.out_features;
+        ph.bn = pick_bn(ph.M, ph.N, R.ctas);
+        ph.d = reinterpret_cast<__nv_bfloat16*>(op.dx) + (long long)g * op.cap * op.lddx;
+        ph.ldd = op.lddx;
+        if (op.mask) {
+          ph.mask = reinterpret_cast<const __nv_bfloat16*>(op.mask) + (long long)g * op.cap * op.ldmask;
+          ph.ldmask = op.ldmask; ph.mask_scale = op.mask_scale;
+        }
+        if (!last) {
+          ph.wait_ctr[0] = RTP_CTR_W0 + s; ph.wait_rel[0] = 0;
+          if (e == L - 1) ph.done_ctr[0] = RTP_CTR_W0 + s;
+        }
+        set_vec_ok(ph);
+      }
+    }
+  }
+  if (N > 1) {
+    RtpPhase& ph = P.phases[np++];
+    init_phase(ph);
+    ph.kind = RTP_KIND_REDUCE;
+    ph.M = ph.N = ph.K = 0;
+    ph.d = op.grad_home;
+    ph.r_nsrc = N;
+    ph.r_n = (long long)(op.shard_bytes / 2) & ~7ll;
+    for (int s = 0; s < N; ++s) {
+      ph.r_src[s] = ws_gslot(ws, R.slot_bytes, s);
+      ph.wait_ctr[s] = RTP_CTR_G0 + s; ph.wait_rel[s] = 0;
+      ph.done_ctr[s] = RTP_CTR_G0 + s;
+      P.uses_inc[RTP_CTR_G0 + s] = 1;
+    }
+  }
+  P.n_phases = np;
+  P.n_pushes = op.dx ? N - 1 : 0;
+  for (int s = 0; s + 1 < N && op.dx; ++s) {
+    RtpPush& pu = P.pushes[s];
+    memset(&pu, 0, sizeof(pu));
+    const int t = mod(r + 1 + s, N);
+    pu.src = op.home;
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, s);
+    pu.bytes = op.shard_bytes;
+    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + s].v;
+    pu.credit_ctr = RTP_CTR_W0 + s;
+    pu.credit_rel = 0;
+    pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + s].v;
+    P.uses_inc[RTP_CTR_W0 + s] = 1;
+  }
+  return 0;
+}
+
 int build_embed_fwd(const RtpRing& R, const RtpEmbedFwd& op, RtpProgram& P) {
   init_program(P);
   const int N = R.world, r = R.rank;
@@ -486,7 +679,7 @@ int run_emu(const RtpRing* rings, const Op* ops, Builder build, cudaStream_t str
   static rtp::GemmParams<NEMU> params;
   for (int e = 0; e < NEMU; ++e) {
     if (build(rings[e], ops[e], progs[e])) return -1;
-    finalize_program(progs[e], rings[0].ctas);
+    finalize_program(progs[e], rings[0].ctas, false);
   }
   cudaError_t err = cudaMemcpyToSymbolAsync(rtp::c_emu_progs, progs, sizeof(RtpProgram) * NEMU, 0,
                                             cudaMemcpyHostToDevice, stream);
@@ -504,6 +697,9 @@ extern "C" {
 
 const char* rtp_last_error(void) { return g_err.c_str(); }
 void rtp_debug_force_stages(int n) { g_force_stages = n; }
+void rtp_set_pair_mode(int on) { g_pair = on ? 1 : 0; }
+unsigned long long* g_trace = nullptr;
+void rtp_debug_set_trace(unsigned long long* device_buffer_768_words) { g_trace = device_buffer_768_words; }
 int rtp_sm_count(void) { return sm_count(); }
 
 int rtp_gemm(const RtpGemmArgs* a, void* stream) {
@@ -513,15 +709,19 @@ int rtp_gemm(const RtpGemmArgs* a, void* stream) {
   if (a->M <= 0 || a->N <= 0 || a->K <= 0) return fail("empty GEMM");
   if (a->a_mn ? make_map_mn(&P.maps[0], a->a, a->M, a->K, a->lda) : make_map_k(&P.maps[0], a->a, a->M, a->K, a->lda))
     return -1;
-  if (a->b_mn ? make_map_mn(&P.maps[1], a->b, a->N, a->K, a->ldb) : make_map_k(&P.maps[1], a->b, a->N, a->K, a->ldb))
-    return -1;
   const int ctas = a->num_ctas > 0 ? a->num_ctas : sm_count();
+  const int bn_sel = a->bn ? a->bn : pick_bn(a->M, a->N, ctas);
+  if (bn_sel != 128 && bn_sel != 256) return fail("bn must be 128 or 256");
+  const bool pair = pair_mode();
+  const int b_box = pair ? bn_sel / 2 : 128;   // a pair stages half of the B tile per CTA
+  if (a->b_mn ? make_map_mn(&P.maps[1], a->b, a->N, a->K, a->ldb) : make_map_k(&P.maps[1], a->b, a->N, a->K, a->ldb, b_box))
+    return -1;
   RtpPhase& ph = P.phases[0];
   init_phase(ph);
   ph.a_map = 0; ph.b_map = 1; ph.a_mn = a->a_mn; ph.b_mn = a->b_mn;
   ph.M = a->M; ph.N = a->N; ph.K = a->K;
-  ph.bn = a->bn ? a->bn : pick_bn(a->M, a->N, ctas);
-  if (ph.bn != 128 && ph.bn != 256) return fail("bn must be 128 or 256");
+  ph.bn = bn_sel;
+  ph.b_box = b_box;
   ph.d = a->d; ph.ldd = a->ldd; ph.d_fp32 = a->d_fp32;
   ph.c = a->c; ph.ldc = a->ldc; ph.c_fp32 = a->c_fp32;
   ph.bias = a->bias; ph.act = a->act;
@@ -532,12 +732,15 @@ int rtp_gemm(const RtpGemmArgs* a, void* stream) {
   set_vec_ok(ph);
   P.n_phases = 1;
   P.status = a->status;
+  P.trace = g_trace;
   if (!P.status) return fail("status word required");
   params.ctas_per_rank = ctas;
-  const int tiles = ((a->M + 127) / 128) * ((a->N + ph.bn - 1) / ph.bn);
-  const int grid = tiles < ctas ? tiles : ctas;
+  const int tiles = pair ? 2 * ((a->M + 255) / 256) * ((a->N + ph.bn - 1) / ph.bn)
+                         : ((a->M + 127) / 128) * ((a->N + ph.bn - 1) / ph.bn);
+  int grid = tiles < ctas ? tiles : ctas;
+  if (pair) grid &= ~1;
   params.ctas_per_rank = grid;
-  return launch<1>(params, grid, false, (cudaStream_t)stream);
+  return launch<1>(params, grid, false, (cudaStream_t)stream, pair);
 }
 
 int rtp_gemm_batched(const RtpGemmBatched* a, void* stream) {
@@ -580,14 +783,38 @@ int rtp_linear_fwd(const RtpRing* ring, const RtpLinearFwd* op, void* stream) {
   if (build_linear_fwd(*ring, *op, params.prog[0])) return -1;
   if (!params.prog[0].status) return fail("ring workspace required");
   params.ctas_per_rank = ring->ctas;
-  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream);
+  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream, true);
 }
 int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream) {
   static thread_local rtp::GemmParams<1> params;
   if (build_linear_bwd(*ring, *op, params.prog[0])) return -1;
   if (!params.prog[0].status) return fail("ring workspace required");
   params.ctas_per_rank = ring->ctas;
-  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream);
+  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream, true);
+}
+int rtp_expert_fwd(const RtpRing* ring, const RtpExpertFwd* op, void* stream) {
+  static thread_local rtp::GemmParams<1> params;
+  if (build_expert_fwd(*ring, *op, params.prog[0])) return -1;
+  if (!params.prog[0].status) return fail("ring workspace required");
+  params.ctas_per_rank = ring->ctas;
+  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream, true);
+}
+int rtp_expert_bwd(const RtpRing* ring, const RtpExpertBwd* op, void* stream) {
+  static thread_local rtp::GemmParams<1> params;
+  if (build_expert_bwd(*ring, *op, params.prog[0])) return -1;
+  if (!params.prog[0].status) return fail("ring workspace required");
+  params.ctas_per_rank = ring->ctas;
+  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream, true);
+}
+int rtp_expert_fwd_emu(const RtpRing* rings, const RtpExpertFwd* ops, int world, void* stream) {
+  if (world == 2) return run_emu<2>(rings, ops, build_expert_fwd, (cudaStream_t)stream);
+  if (world == 4) return run_emu<4>(rings, ops, build_expert_fwd, (cudaStream_t)stream);
+  return fail("emulation supports 2 or 4 ranks");
+}
+int rtp_expert_bwd_emu(const RtpRing* rings, const RtpExpertBwd* ops, int world, void* stream) {
+  if (world == 2) return run_emu<2>(rings, ops, build_expert_bwd, (cudaStream_t)stream);
+  if (world == 4) return run_emu<4>(rings, ops, build_expert_bwd, (cudaStream_t)stream);
+  return fail("emulation supports 2 or 4 ranks");
 }
 int rtp_embed_fwd_rot(const RtpRing* ring, const RtpEmbedFwd* op, void* stream) {
   static thread_local rtp::GemmParams<1> params;

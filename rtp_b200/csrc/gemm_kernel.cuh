@@ -51,10 +51,13 @@ __device__ __forceinline__ unsigned long long fill_target(const RtpFlagBlock* fb
   return (fb->uses[ctr].v + (unsigned long long)(rel + plus)) * (unsigned long long)G;
 }
 
-template <int NEMU>
+// PAIR = true: launched with clusters of two CTAs; one UMMA (cta_group::2, M = 256) spans the pair.
+template <int NEMU, bool PAIR>
 __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_constant__ GemmParams<NEMU> params) {
   extern __shared__ uint8_t smem_raw[];
   const int G = params.ctas_per_rank;
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;   // 0 = leader of the pair
+  constexpr int TM = PAIR ? 2 * kBM : kBM;                 // rows of an output tile of one scheduling unit
   const int vrank = (NEMU == 1) ? 0 : (int)(blockIdx.x / G);
   const int cta = (NEMU == 1) ? (int)blockIdx.x : (int)(blockIdx.x % G);
   const RtpProgram& P = (NEMU == 1) ? params.prog[0] : c_emu_progs[vrank];
@@ -71,26 +74,30 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // scheduling unit = CTA, or CTA pair; GU units per rank
+  const int unit = PAIR ? (cta >> 1) : cta;
+  const int GU = PAIR ? (G >> 1) : G;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->full[s], PAIR ? 2 : 1);      // pair: one arrive.expect_tx from each CTA's producer (leader's barrier)
       mbar_init(&ctl->empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&ctl->tmem_full[a], 1);
-      mbar_init(&ctl->tmem_empty[a], 4);
+      mbar_init(&ctl->tmem_empty[a], PAIR ? 8 : 4);  // pair: the epilogue warps of both CTAs arrive on the leader's barrier
     }
     mbar_init(&ctl->drain, 1);
     ctl->abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(&ctl->tmem_base, kTmemCols);
-    tmem_relinquish();
+    if (PAIR) { tmem_alloc_pair(&ctl->tmem_base, kTmemCols); tmem_relinquish_pair(); }
+    else { tmem_alloc(&ctl->tmem_base, kTmemCols); tmem_relinquish(); }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();      // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
@@ -101,15 +108,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       uint32_t phase = 0;
       uint32_t issued_parity[kMaxStages];
       bool issued[kMaxStages];
+      int tr_n = 0;
       for (int s = 0; s < kStages; ++s) { issued[s] = false; issued_parity[s] = 0; }
       bool ok = true;
       for (int p = 0; p < P.n_phases && ok; ++p) {
         const RtpPhase& ph = P.phases[p];
-        const int tiles_m = (ph.M + kBM - 1) / kBM;
+        const int tiles_m = (ph.M + TM - 1) / TM;
         const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
         const int per_batch = tiles_m * tiles_n;
         const int total = per_batch * ph.batch;
-        if ((cta - ph.cta_off + G) % G >= total) continue;
+        if ((unit - ph.cta_off + GU) % GU >= total) continue;
         bool any_wait = false;
         for (int w = 0; w < RTP_MAX_WAITS && ok; ++w) {
           if (ph.wait_ctr[w] >= 0) {
@@ -124,80 +132,132 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const CUtensorMap* ma = &P.maps[ph.a_map];
         const CUtensorMap* mb = &P.maps[ph.b_map];
         const int kblocks_full = (ph.K + kBK - 1) / kBK;
-        const uint32_t tx = kABytes + ph.bn * kBK * 2;
-        for (int t = (cta - ph.cta_off + G) % G; t < total && ok; t += G) {
+        const int p_a_mn = ph.a_mn;
+        const int p_b_mn = ph.b_mn;
+        const int p_b_box = ph.b_box;
+        const int p_bn = ph.bn;
+        const int p_causal = ph.causal;
+        const int p_batch_inner = ph.batch_inner;
+        const int p_a_off_mn = ph.a_off_mn;
+        const int p_a_off_k = ph.a_off_k;
+        const int p_b_off_mn = ph.b_off_mn;
+        const int p_b_off_k = ph.b_off_k;
+        const int p_a_bo_mn = ph.a_bo_mn;
+        const int p_a_bo_k = ph.a_bo_k;
+        const int p_a_bi_mn = ph.a_bi_mn;
+        const int p_a_bi_k = ph.a_bi_k;
+        const int p_b_bo_mn = ph.b_bo_mn;
+        const int p_b_bo_k = ph.b_bo_k;
+        const int p_b_bi_mn = ph.b_bi_mn;
+        const int p_b_bi_k = ph.b_bi_k;
+        const int p_cta_off = ph.cta_off;
+        const int bn_local = PAIR ? p_bn / 2 : p_bn;     // B rows staged by this CTA
+        const uint32_t tx = kABytes + bn_local * kBK * 2;
+        for (int t = (unit - p_cta_off + GU) % GU; t < total && ok; t += GU) {
           const int z = t / per_batch, tt = t % per_batch;
-          const int m0 = (tt % tiles_m) * kBM;
-          const int n0 = (tt / tiles_m) * ph.bn;
-          if (ph.causal == 1 && n0 > m0 + kBM - 1) continue;
-          const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + kBM + kBK - 1) / kBK) : kblocks_full;
-          const int zo = z / ph.batch_inner, zi = z % ph.batch_inner;
-          const int a_mn0 = m0 + ph.a_off_mn + zo * ph.a_bo_mn + zi * ph.a_bi_mn;
-          const int a_k0 = ph.a_off_k + zo * ph.a_bo_k + zi * ph.a_bi_k;
-          const int b_mn0 = n0 + ph.b_off_mn + zo * ph.b_bo_mn + zi * ph.b_bi_mn;
-          const int b_k0 = ph.b_off_k + zo * ph.b_bo_k + zi * ph.b_bi_k;
+          const int m0u = (tt % tiles_m) * TM;              // first row of the unit's tile
+          const int m0 = m0u + (int)crank * kBM;            // first row of this CTA's half
+          const int n0 = (tt / tiles_m) * p_bn;
+          if (p_causal == 1 && n0 > m0u + TM - 1) continue;
+          const int kblocks = p_causal == 2 ? min(kblocks_full, (m0u + TM + kBK - 1) / kBK) : kblocks_full;
+          const int zo = z / p_batch_inner, zi = z % p_batch_inner;
+          const int a_mn0 = m0 + p_a_off_mn + zo * p_a_bo_mn + zi * p_a_bi_mn;
+          const int a_k0 = p_a_off_k + zo * p_a_bo_k + zi * p_a_bi_k;
+          const int b_mn0 = n0 + (int)crank * bn_local + p_b_off_mn + zo * p_b_bo_mn + zi * p_b_bi_mn;
+          const int b_k0 = p_b_off_k + zo * p_b_bo_k + zi * p_b_bi_k;
+          if (P.trace && cta == 0 && tr_n < 60) P.trace[0 * 256 + tr_n * 4 + 0] = globaltimer_ns();
           for (int kb = 0; kb < kblocks; ++kb) {
             if (!mbar_wait(&ctl->empty[stage], phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
             uint8_t* sa = tiles + stage * kStageBytes;
             uint8_t* sb = sa + kABytes;
-            mbar_arrive_expect_tx(&ctl->full[stage], tx);
             issued[stage] = true;
             issued_parity[stage] = phase;
             const int k0 = kb * kBK;
-            if (!ph.a_mn) {
-              tma_load_2d(sa, ma, k0 + a_k0, a_mn0, &ctl->full[stage]);
+            if (PAIR) {
+              // both CTAs of the pair post their bytes on the LEADER's barrier; copies land in the issuing CTA's smem
+              const uint32_t lbar = mapa_u32(smem_u32(&ctl->full[stage]), 0);
+              mbar_arrive_expect_tx_cluster(lbar, tx);
+              if (!p_a_mn) {
+                tma_load_2d_pair(sa, ma, k0 + a_k0, a_mn0, lbar);
+              } else {
+                tma_load_2d_pair(sa, ma, a_mn0, k0 + a_k0, lbar);
+                tma_load_2d_pair(sa + 8192, ma, a_mn0 + 64, k0 + a_k0, lbar);
+              }
+              if (!p_b_mn) {
+                for (int i = 0; i < bn_local / p_b_box; ++i)
+                  tma_load_2d_pair(sb + i * p_b_box * 128, mb, k0 + b_k0, b_mn0 + i * p_b_box, lbar);
+              } else {
+                for (int i = 0; i < bn_local / 64; ++i)
+                  tma_load_2d_pair(sb + i * 8192, mb, b_mn0 + i * 64, k0 + b_k0, lbar);
+              }
             } else {
-              tma_load_2d(sa, ma, a_mn0, k0 + a_k0, &ctl->full[stage]);
-              tma_load_2d(sa + 8192, ma, a_mn0 + 64, k0 + a_k0, &ctl->full[stage]);
-            }
-            if (!ph.b_mn) {
-              for (int i = 0; i < ph.bn / ph.b_box; ++i)
-                tma_load_2d(sb + i * ph.b_box * 128, mb, k0 + b_k0, b_mn0 + i * ph.b_box, &ctl->full[stage]);
-            } else {
-              for (int i = 0; i < ph.bn / 64; ++i)
-                tma_load_2d(sb + i * 8192, mb, b_mn0 + i * 64, k0 + b_k0, &ctl->full[stage]);
+              mbar_arrive_expect_tx(&ctl->full[stage], tx);
+              if (!p_a_mn) {
+                tma_load_2d(sa, ma, k0 + a_k0, a_mn0, &ctl->full[stage]);
+              } else {
+                tma_load_2d(sa, ma, a_mn0, k0 + a_k0, &ctl->full[stage]);
+                tma_load_2d(sa + 8192, ma, a_mn0 + 64, k0 + a_k0, &ctl->full[stage]);
+              }
+              if (!p_b_mn) {
+                for (int i = 0; i < p_bn / p_b_box; ++i)
+                  tma_load_2d(sb + i * p_b_box * 128, mb, k0 + b_k0, b_mn0 + i * p_b_box, &ctl->full[stage]);
+              } else {
+                for (int i = 0; i < p_bn / 64; ++i)
+                  tma_load_2d(sb + i * 8192, mb, b_mn0 + i * 64, k0 + b_k0, &ctl->full[stage]);
+              }
             }
             if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
+          if (P.trace && cta == 0 && tr_n < 60) P.trace[0 * 256 + tr_n * 4 + 1] = globaltimer_ns();
+          ++tr_n;
         }
       }
       if (!ok) {
         // gave up: wait (bounded) until every copy this thread issued has landed before the CTA exits
-        for (int s = 0; s < kStages; ++s) {
-          if (!issued[s]) continue;
+        if (PAIR && crank != 0) {
+          // the barrier that tracks this CTA's copies lives in the leader: give the copies time to land instead
           unsigned long long t0 = globaltimer_ns();
-          while (!mbar_try_wait(&ctl->full[s], issued_parity[s])) {
-            if (globaltimer_ns() - t0 > 2000000ull) break;
+          while (globaltimer_ns() - t0 < 200000ull) { }
+        } else {
+          for (int s = 0; s < kStages; ++s) {
+            if (!issued[s]) continue;
+            unsigned long long t0 = globaltimer_ns();
+            while (!mbar_try_wait(&ctl->full[s], issued_parity[s])) {
+              if (globaltimer_ns() - t0 > 2000000ull) break;
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
+    if (lane == 0 && crank == 0) {     // in a pair only the leader issues; its UMMAs drive both SMs
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
       bool issued_any = false;
+      int tr_m = 0;
       for (int p = 0; p < P.n_phases && ok; ++p) {
         const RtpPhase& ph = P.phases[p];
-        const int tiles_m = (ph.M + kBM - 1) / kBM;
+        const int tiles_m = (ph.M + TM - 1) / TM;
         const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
         const int per_batch = tiles_m * tiles_n;
         const int total = per_batch * ph.batch;
         const int kblocks_full = (ph.K + kBK - 1) / kBK;
-        const uint32_t idesc = make_idesc_bf16(kBM, ph.bn, ph.a_mn, ph.b_mn);
+        const uint32_t idesc = make_idesc_bf16(TM, ph.bn, ph.a_mn, ph.b_mn);
         const uint32_t a_lbo = ph.a_mn ? 8192u : 16u, b_lbo = ph.b_mn ? 8192u : 16u;
         const uint32_t a_kstep = ph.a_mn ? 2048u : 32u, b_kstep = ph.b_mn ? 2048u : 32u;
-        for (int t = (cta - ph.cta_off + G) % G; t < total && ok; t += G) {
+        for (int t = (unit - ph.cta_off + GU) % GU; t < total && ok; t += GU) {
           const int tt = t % per_batch;
-          const int m0 = (tt % tiles_m) * kBM;
+          const int m0 = (tt % tiles_m) * TM;
           const int n0 = (tt / tiles_m) * ph.bn;
-          if (ph.causal == 1 && n0 > m0 + kBM - 1) continue;
-          const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + kBM + kBK - 1) / kBK) : kblocks_full;
+          if (ph.causal == 1 && n0 > m0 + TM - 1) continue;
+          const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + TM + kBK - 1) / kBK) : kblocks_full;
+          if (P.trace && cta == 0 && tr_m < 60) P.trace[1 * 256 + tr_m * 4 + 0] = globaltimer_ns();
           if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
+          if (P.trace && cta == 0 && tr_m < 60) P.trace[1 * 256 + tr_m * 4 + 1] = globaltimer_ns();
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
           for (int kb = 0; kb < kblocks; ++kb) {
@@ -209,14 +269,18 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             for (int kk = 0; kk < kBK / 16; ++kk) {
               const uint64_t da = make_smem_desc(sa + kk * a_kstep, a_lbo, 1024);
               const uint64_t db = make_smem_desc(sb + kk * b_kstep, b_lbo, 1024);
-              umma_bf16(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              if (PAIR) umma_bf16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              else umma_bf16(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             }
             issued_any = true;
-            umma_commit(&ctl->empty[stage]);  // frees the smem stage once these MMAs have read it
+            // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
+            if (PAIR) umma_commit_pair(&ctl->empty[stage]); else umma_commit(&ctl->empty[stage]);
             if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
           if (!ok) break;
-          umma_commit(&ctl->tmem_full[acc]);
+          if (PAIR) umma_commit_pair(&ctl->tmem_full[acc]); else umma_commit(&ctl->tmem_full[acc]);
+          if (P.trace && cta == 0 && tr_m < 60) P.trace[1 * 256 + tr_m * 4 + 2] = globaltimer_ns();
+          ++tr_m;
           if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
       }
@@ -236,9 +300,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    int tr_e = 0;
     for (int p = 0; p < P.n_phases; ++p) {
       const RtpPhase& ph = P.phases[p];
-      const int tiles_m = (ph.M + kBM - 1) / kBM;
+      const int tiles_m = (ph.M + TM - 1) / TM;
       const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
       const int per_batch = tiles_m * tiles_n;
       const int total = per_batch * ph.batch;
@@ -329,41 +394,73 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
                                                                  pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
         }
       }
-      for (int t = (cta - ph.cta_off + G) % G; t < total && ok; t += G) {
+      // phase fields used per element live in registers (reading them from parameter space inside the loops costs a
+      // dependent constant load each time)
+      const int e_M = ph.M;
+      const int e_N = ph.N;
+      const int e_bn = ph.bn;
+      const float e_alpha = ph.alpha;
+      const const void* e_c = ph.c;
+      const long long e_ldc = ph.ldc;
+      const int e_c_fp32 = ph.c_fp32;
+      const const void* e_bias = ph.bias;
+      const int e_act = ph.act;
+      const const void* e_mask = ph.mask;
+      const long long e_ldmask = ph.ldmask;
+      const float e_mask_scale = ph.mask_scale;
+      const uint32_t e_drop_thresh = ph.drop_thresh;
+      const float e_drop_scale = ph.drop_scale;
+      const unsigned long long e_drop_seed = ph.drop_seed;
+      void* const e_d = ph.d;
+      const long long e_ldd = ph.ldd;
+      const int e_d_fp32 = ph.d_fp32;
+      const int e_vec_ok = ph.vec_ok;
+      const int e_causal = ph.causal;
+      const int e_batch_inner = ph.batch_inner;
+      const long long e_d_bo = ph.d_bo;
+      const long long e_d_bi = ph.d_bi;
+      const long long e_c_bo = ph.c_bo;
+      const long long e_c_bi = ph.c_bi;
+      const int e_cta_off = ph.cta_off;
+      for (int t = (unit - e_cta_off + GU) % GU; t < total && ok; t += GU) {
         const int z = t / per_batch, tt = t % per_batch;
-        const int m0 = (tt % tiles_m) * kBM;
-        const int n0 = (tt / tiles_m) * ph.bn;
-        if (ph.causal == 1 && n0 > m0 + kBM - 1) continue;
-        const long long zoff_d = (long long)(z / ph.batch_inner) * ph.d_bo + (long long)(z % ph.batch_inner) * ph.d_bi;
-        const long long zoff_c = (long long)(z / ph.batch_inner) * ph.c_bo + (long long)(z % ph.batch_inner) * ph.c_bi;
+        const int m0u = (tt % tiles_m) * TM;
+        const int m0 = m0u + (int)crank * kBM;
+        const int n0 = (tt / tiles_m) * e_bn;
+        if (e_causal == 1 && n0 > m0u + TM - 1) continue;
+        const long long zoff_d = (long long)(z / e_batch_inner) * e_d_bo + (long long)(z % e_batch_inner) * e_d_bi;
+        const long long zoff_c = (long long)(z / e_batch_inner) * e_c_bo + (long long)(z % e_batch_inner) * e_c_bi;
         uint32_t good = 1;
+        const bool tr_on = P.trace && cta == 0 && warp == 2 && lane == 0 && tr_e < 60;
+        if (tr_on) P.trace[2 * 256 + tr_e * 4 + 0] = globaltimer_ns();
         if (lane == 0) good = mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, status, timeout_ns);
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) { ok = false; break; }
         tc_fence_after();
+        if (tr_on) P.trace[2 * 256 + tr_e * 4 + 1] = globaltimer_ns();
         const int row = m0 + quad * 32 + lane;
-        const bool row_ok = row < ph.M;
-        const bool staged = !ph.d_fp32 && ph.vec_ok && (ph.N & 7) == 0;
+        const bool row_ok = row < e_M;
+        const bool staged = !e_d_fp32 && e_vec_ok && (e_N & 7) == 0;
         uint8_t* stg = staging + (warp - 2) * (32 * kStagePitch);
-        for (int cb = 0; cb < ph.bn / 32; ++cb) {
+        for (int cb = 0; cb < e_bn / 32; ++cb) {
           uint32_t r[32];
           __syncwarp();
           tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256 + cb * 32), r);
           tmem_ld_wait();
           const int col0 = n0 + cb * 32;
-          if (row_ok && col0 < ph.N) {
+          if (row_ok && col0 < e_N) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {  // groups of 8 columns
             const int col = col0 + g * 8;
-            if (col >= ph.N) break;
-            const int nvalid = min(8, ph.N - col);
+            if (col >= e_N) break;
+            const int nvalid = min(8, e_N - col);
             float v[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * ph.alpha;
-            const bool vec = ph.vec_ok && nvalid == 8;
-            if (ph.c) {
-              if (ph.c_fp32) {
-                const float* cp = reinterpret_cast<const float*>(ph.c) + zoff_c + (long long)row * ph.ldc + col;
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * e_alpha;
+            const bool vec = e_vec_ok && nvalid == 8;
+            if (e_c) {
+              if (e_c_fp32) {
+                const float* cp = reinterpret_cast<const float*>(e_c) + zoff_c + (long long)row * e_ldc + col;
                 if (vec) {
                   float4 c0 = __ldcg(reinterpret_cast<const float4*>(cp));
                   float4 c1 = __ldcg(reinterpret_cast<const float4*>(cp) + 1);
@@ -373,7 +470,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
                   for (int i = 0; i < nvalid; ++i) v[i] += __ldcg(cp + i);
                 }
               } else {
-                const __nv_bfloat16* cp = reinterpret_cast<const __nv_bfloat16*>(ph.c) + zoff_c + (long long)row * ph.ldc + col;
+                const __nv_bfloat16* cp = reinterpret_cast<const __nv_bfloat16*>(e_c) + zoff_c + (long long)row * e_ldc + col;
                 if (vec) {
                   uint4 c = __ldcg(reinterpret_cast<const uint4*>(cp));
                   v[0] += bf16_lo(c.x); v[1] += bf16_hi(c.x); v[2] += bf16_lo(c.y); v[3] += bf16_hi(c.y);
@@ -384,8 +481,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
                 }
               }
             }
-            if (ph.bias) {
-              const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(ph.bias) + col;
+            if (e_bias) {
+              const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(e_bias) + col;
               if (nvalid == 8 && (reinterpret_cast<uintptr_t>(bp) & 15) == 0) {
                 const uint4 b = __ldcg(reinterpret_cast<const uint4*>(bp));   // one 16-byte load for 8 columns
                 v[0] += bf16_lo(b.x); v[1] += bf16_hi(b.x); v[2] += bf16_lo(b.y); v[3] += bf16_hi(b.y);
@@ -394,39 +491,39 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
                 for (int i = 0; i < nvalid; ++i) v[i] += __bfloat162float(__ldcg(bp + i));
               }
             }
-            if (ph.act == 1) {
+            if (e_act == 1) {
 #pragma unroll
               for (int i = 0; i < 8; ++i) v[i] = fmaxf(v[i], 0.f);
-            } else if (ph.act == 2) {
+            } else if (e_act == 2) {
 #pragma unroll
               for (int i = 0; i < 8; ++i) v[i] = 0.5f * v[i] * (1.f + erff(v[i] * 0.70710678118654752f));
             }
-            if (ph.mask) {
-              const __nv_bfloat16* mp = reinterpret_cast<const __nv_bfloat16*>(ph.mask) + (long long)row * ph.ldmask + col;
+            if (e_mask) {
+              const __nv_bfloat16* mp = reinterpret_cast<const __nv_bfloat16*>(e_mask) + (long long)row * e_ldmask + col;
               if (vec) {
                 uint4 m = __ldcg(reinterpret_cast<const uint4*>(mp));
                 const uint32_t mw[4] = {m.x, m.y, m.z, m.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                  v[2 * i] = bf16_lo(mw[i]) > 0.f ? v[2 * i] * ph.mask_scale : 0.f;
-                  v[2 * i + 1] = bf16_hi(mw[i]) > 0.f ? v[2 * i + 1] * ph.mask_scale : 0.f;
+                  v[2 * i] = bf16_lo(mw[i]) > 0.f ? v[2 * i] * e_mask_scale : 0.f;
+                  v[2 * i + 1] = bf16_hi(mw[i]) > 0.f ? v[2 * i + 1] * e_mask_scale : 0.f;
                 }
               } else {
                 for (int i = 0; i < nvalid; ++i)
-                  v[i] = __bfloat162float(__ldcg(mp + i)) > 0.f ? v[i] * ph.mask_scale : 0.f;
+                  v[i] = __bfloat162float(__ldcg(mp + i)) > 0.f ? v[i] * e_mask_scale : 0.f;
               }
             }
-            if (ph.drop_thresh) {
+            if (e_drop_thresh) {
               // element index = position in the logical [M, N] output; 8 | col so two philox calls cover the group
-              const unsigned long long e = (unsigned long long)row * (unsigned long long)ph.N + (unsigned long long)col;
-              uint4 r0 = philox4x32(ph.drop_seed, drop_off, e >> 2);
-              uint4 r1 = philox4x32(ph.drop_seed, drop_off, (e >> 2) + 1);
+              const unsigned long long e = (unsigned long long)row * (unsigned long long)e_N + (unsigned long long)col;
+              uint4 r0 = philox4x32(e_drop_seed, drop_off, e >> 2);
+              uint4 r1 = philox4x32(e_drop_seed, drop_off, (e >> 2) + 1);
               const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = rw[i] >= ph.drop_thresh ? v[i] * ph.drop_scale : 0.f;
+              for (int i = 0; i < 8; ++i) v[i] = rw[i] >= e_drop_thresh ? v[i] * e_drop_scale : 0.f;
             }
-            if (ph.d_fp32) {
-              float* dp = reinterpret_cast<float*>(ph.d) + zoff_d + (long long)row * ph.ldd + col;
+            if (e_d_fp32) {
+              float* dp = reinterpret_cast<float*>(e_d) + zoff_d + (long long)row * e_ldd + col;
               if (vec) {
                 reinterpret_cast<float4*>(dp)[0] = make_float4(v[0], v[1], v[2], v[3]);
                 reinterpret_cast<float4*>(dp)[1] = make_float4(v[4], v[5], v[6], v[7]);
@@ -438,7 +535,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
               *reinterpret_cast<uint4*>(stg + lane * kStagePitch + (cb & 1) * 64 + g * 16) =
                   make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
             } else {
-              __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(ph.d) + zoff_d + (long long)row * ph.ldd + col;
+              __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(e_d) + zoff_d + (long long)row * e_ldd + col;
               if (vec) {
                 *reinterpret_cast<uint4*>(dp) =
                     make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
@@ -452,15 +549,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             // coalesced write-out of 32 rows x 64 columns: 8 lanes cover one row's 128 bytes, 4 rows per instruction
             __syncwarp();
             const int pair_col0 = n0 + (cb - 1) * 32;
-            __nv_bfloat16* dbase = reinterpret_cast<__nv_bfloat16*>(ph.d) + zoff_d;
+            __nv_bfloat16* dbase = reinterpret_cast<__nv_bfloat16*>(e_d) + zoff_d;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const int rr = k * 4 + (lane >> 3);
               const int grow = m0 + quad * 32 + rr;
               const int gcol = pair_col0 + (lane & 7) * 8;
-              if (grow < ph.M && gcol < ph.N) {
+              if (grow < e_M && gcol < e_N) {
                 const uint4 val = *reinterpret_cast<const uint4*>(stg + rr * kStagePitch + (lane & 7) * 16);
-                *reinterpret_cast<uint4*>(dbase + (long long)grow * ph.ldd + gcol) = val;
+                *reinterpret_cast<uint4*>(dbase + (long long)grow * e_ldd + gcol) = val;
               }
             }
             __syncwarp();
@@ -468,7 +565,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+        if (tr_on) P.trace[2 * 256 + tr_e * 4 + 2] = globaltimer_ns();
+        ++tr_e;
+        if (lane == 0) {
+          if (PAIR && crank != 0) mbar_arrive_cluster(mapa_u32(smem_u32(&ctl->tmem_empty[acc]), 0));
+          else mbar_arrive(&ctl->tmem_empty[acc]);
+        }
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       // small vector job (bias-gradient hop) by CTA 0
@@ -535,9 +637,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
   // ---------------------------------------------------------------------- tear-down
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();      // neither CTA leaves while the other may still signal its barriers or read its smem
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && P.flags) {
     __threadfence();

@@ -127,4 +127,5 @@ struct alignas(64) RtpProgram {
   int uses_inc[RTP_NUM_CTR];  // added to flags->uses[] by the last CTA of the launch
   unsigned long long* status;  // status word (flags->status or a plain device word)
   unsigned long long timeout_ns;
+  unsigned long long* trace;  // optional debug timeline of CTA 0: [role][tile][event] globaltimer stamps (see gemm_kernel.cuh)
 };

@@ -81,136 +81,183 @@ uint32_t host_thresh(float p) {
 
 // ------------------------------------------------------------------------------------------------
 // h = x + dropout(sub);  y = norm(h) * gamma (+ beta).  rms = 0: LayerNorm, 1: RMSNorm.
-// One block per row, D % 8 == 0. Saves h (bf16) and the row statistics for backward.
+// One 256-thread block per row; the row lives in registers (NG groups of 8 columns per thread, D <= 2048 * NG), so
+// global memory is touched exactly once per tensor.  Saves h (bf16) and the row statistics for backward.
 // ------------------------------------------------------------------------------------------------
-__global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ sub,
-                                const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
-                                __nv_bfloat16* __restrict__ h_out, __nv_bfloat16* __restrict__ y,
-                                float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int D, float eps,
-                                int rms, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset,
-                                const unsigned long long* __restrict__ step_ptr) {
-  __shared__ float red[32];
-  extern __shared__ float rowbuf[];
-  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;  // D floats
+__device__ __forceinline__ float2 block_sum2(float a, float b, float2* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  a = warp_sum(a);
+  b = warp_sum(b);
+  __syncthreads();
+  if (lane == 0) red[w] = make_float2(a, b);
+  __syncthreads();
+  float2 t = (lane < nw) ? red[lane] : make_float2(0.f, 0.f);
+  t.x = warp_sum(t.x);
+  t.y = warp_sum(t.y);
+  return t;
+}
+
+template <int NG>
+__global__ void __launch_bounds__(256) norm_fwd_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ sub, const __nv_bfloat16* __restrict__ gamma,
+    const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ h_out, __nv_bfloat16* __restrict__ y,
+    float* __restrict__ mean_out, float* __restrict__ rstd_out, int M, int D, float eps, int rms, uint32_t thresh,
+    float drop_scale, uint64_t seed, uint64_t offset, const unsigned long long* __restrict__ step_ptr) {
+  __shared__ float2 red[32];
+  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
+  float g[NG][8], bt[NG][8];
+#pragma unroll
+  for (int q = 0; q < NG; ++q) {
+    const int c = (q * 256 + threadIdx.x) * 8;
+    if (c < D) {
+      unpack8(*reinterpret_cast<const uint4*>(gamma + c), g[q]);
+      if (beta) unpack8(*reinterpret_cast<const uint4*>(beta + c), bt[q]);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) bt[q][i] = 0.f;
+      }
+    }
+  }
   for (int row = blockIdx.x; row < M; row += gridDim.x) {
     const size_t base = (size_t)row * D;
+    float v[NG][8];
     float s = 0.f;
-    for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
-      float v[8];
-      unpack8(*reinterpret_cast<const uint4*>(x + base + c), v);
-      if (sub) {
-        float u[8];
-        unpack8(*reinterpret_cast<const uint4*>(sub + base + c), u);
-        if (thresh) {
-          bool k[8];
-          keep8(seed, offset, base + c, thresh, k);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) u[i] = k[i] ? u[i] * drop_scale : 0.f;
+    for (int q = 0; q < NG; ++q) {
+      const int c = (q * 256 + threadIdx.x) * 8;
+      if (c < D) {
+        unpack8(__ldcs(reinterpret_cast<const uint4*>(x + base + c)), v[q]);
+        if (sub) {
+          float u[8];
+          unpack8(__ldcs(reinterpret_cast<const uint4*>(sub + base + c)), u);
+          if (thresh) {
+            bool k[8];
+            keep8(seed, offset, base + c, thresh, k);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) u[i] = k[i] ? u[i] * drop_scale : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[q][i] += u[i];
         }
+        const uint4 hp = pack8(v[q]);   // round to bf16 first: backward sees exactly the saved h
+        unpack8(hp, v[q]);
+        if (h_out) *reinterpret_cast<uint4*>(h_out + base + c) = hp;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] += u[i];
+        for (int i = 0; i < 8; ++i) s += v[q][i];
       }
-      // round to bf16 first: backward sees exactly the saved h
-      uint4 hp = pack8(v);
-      unpack8(hp, v);
-      if (h_out) *reinterpret_cast<uint4*>(h_out + base + c) = hp;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { rowbuf[c + i] = v[i]; s += v[i]; }
     }
     float mean = 0.f;
-    if (!rms) mean = block_sum(s, red) / D;
-    float q = 0.f;
-    for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
+    if (!rms) mean = block_sum2(s, 0.f, red).x / D;
+    float qq = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { float d = rowbuf[c + i] - mean; q += d * d; }
+    for (int q = 0; q < NG; ++q) {
+      const int c = (q * 256 + threadIdx.x) * 8;
+      if (c < D) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float d = v[q][i] - mean; qq += d * d; }
+      }
     }
-    const float var = block_sum(q, red) / D;
+    const float var = block_sum2(qq, 0.f, red).x / D;
     const float rstd = rsqrtf(var + eps);
     if (threadIdx.x == 0) {
       if (mean_out) mean_out[row] = mean;
       rstd_out[row] = rstd;
     }
-    for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
-      float g[8], b[8], o[8];
-      unpack8(*reinterpret_cast<const uint4*>(gamma + c), g);
-      if (beta) unpack8(*reinterpret_cast<const uint4*>(beta + c), b);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = (rowbuf[c + i] - mean) * rstd * g[i] + (beta ? b[i] : 0.f);
-      *reinterpret_cast<uint4*>(y + base + c) = pack8(o);
+    for (int q = 0; q < NG; ++q) {
+      const int c = (q * 256 + threadIdx.x) * 8;
+      if (c < D) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = (v[q][i] - mean) * rstd * g[q][i] + bt[q][i];
+        *reinterpret_cast<uint4*>(y + base + c) = pack8(o);
+      }
     }
-    __syncthreads();
   }
 }
 
-// Backward: dh = d(norm)/dh ; dx = dh ; dsub = dropout_mask * dh ; dgamma/dbeta accumulated with atomics (fp32).
-__global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
-                                const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
-                                const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
-                                __nv_bfloat16* __restrict__ dsub, float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                int M, int D, int rms, uint32_t thresh, float drop_scale, uint64_t seed,
-                                uint64_t offset, const __nv_bfloat16* __restrict__ dres,
-                                const unsigned long long* __restrict__ step_ptr) {
-  __shared__ float red[32];
+// Backward: dh = d(norm)/dh (+ dres); dx = dh; dsub = dropout_mask * dh.  Per-thread dgamma / dbeta partials stay in
+// registers across the rows of the block and are added to the fp32 outputs with one atomic per column at the end.
+template <int NG>
+__global__ void __launch_bounds__(256) norm_bwd_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ gamma,
+    const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+    __nv_bfloat16* __restrict__ dsub, float* __restrict__ dgamma, float* __restrict__ dbeta, int M, int D, int rms,
+    uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset, const __nv_bfloat16* __restrict__ dres,
+    const unsigned long long* __restrict__ step_ptr) {
+  __shared__ float2 red[32];
   if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
-  extern __shared__ float sm[];  // 2*D floats: per-block dgamma / dbeta partials
-  float* pg = sm;
-  float* pb = sm + D;
-  for (int c = threadIdx.x; c < D; c += blockDim.x) { pg[c] = 0.f; pb[c] = 0.f; }
-  __syncthreads();
+  float g[NG][8], pg[NG][8], pb[NG][8];
+#pragma unroll
+  for (int q = 0; q < NG; ++q) {
+    const int c = (q * 256 + threadIdx.x) * 8;
+    if (c < D) unpack8(*reinterpret_cast<const uint4*>(gamma + c), g[q]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { pg[q][i] = 0.f; pb[q][i] = 0.f; }
+  }
   for (int row = blockIdx.x; row < M; row += gridDim.x) {
     const size_t base = (size_t)row * D;
     const float mean = rms ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
+    float d[NG][8], xh[NG][8];
     float s1 = 0.f, s2 = 0.f;
-    for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
-      float g[8], d[8], hv[8];
-      unpack8(*reinterpret_cast<const uint4*>(gamma + c), g);
-      unpack8(*reinterpret_cast<const uint4*>(dy + base + c), d);
-      unpack8(*reinterpret_cast<const uint4*>(h + base + c), hv);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float xh = (hv[i] - mean) * rstd;
-        const float dg = d[i] * g[i];
-        s1 += dg;
-        s2 += dg * xh;
-        pg[c + i] += d[i] * xh;   // each column is owned by one thread of the block: no race
-        pb[c + i] += d[i];
+    for (int q = 0; q < NG; ++q) {
+      const int c = (q * 256 + threadIdx.x) * 8;
+      if (c < D) {
+        float hv[8];
+        unpack8(__ldcs(reinterpret_cast<const uint4*>(dy + base + c)), d[q]);
+        unpack8(__ldcs(reinterpret_cast<const uint4*>(h + base + c)), hv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[q][i] = (hv[i] - mean) * rstd;
+          const float dg = d[q][i] * g[q][i];
+          s1 += dg;
+          s2 += dg * xh[q][i];
+          pg[q][i] += d[q][i] * xh[q][i];
+          pb[q][i] += d[q][i];
+        }
       }
     }
-    s1 = rms ? 0.f : block_sum(s1, red) / D;
-    s2 = block_sum(s2, red) / D;
-    for (int c = threadIdx.x * 8; c < D; c += blockDim.x * 8) {
-      float g[8], d[8], hv[8], o[8];
-      unpack8(*reinterpret_cast<const uint4*>(gamma + c), g);
-      unpack8(*reinterpret_cast<const uint4*>(dy + base + c), d);
-      unpack8(*reinterpret_cast<const uint4*>(h + base + c), hv);
+    const float2 t = block_sum2(s1, s2, red);
+    s1 = rms ? 0.f : t.x / D;
+    s2 = t.y / D;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float xh = (hv[i] - mean) * rstd;
-        o[i] = (d[i] * g[i] - s1 - xh * s2) * rstd;
-      }
-      if (dres) {  // gradient that reaches h along a second path (pre-norm residual stream)
-        float e[8];
-        unpack8(*reinterpret_cast<const uint4*>(dres + base + c), e);
+    for (int q = 0; q < NG; ++q) {
+      const int c = (q * 256 + threadIdx.x) * 8;
+      if (c < D) {
+        float o[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] += e[i];
-      }
-      *reinterpret_cast<uint4*>(dx + base + c) = pack8(o);
-      if (dsub) {
-        if (thresh) {
-          bool k[8];
-          keep8(seed, offset, base + c, thresh, k);
+        for (int i = 0; i < 8; ++i) o[i] = (d[q][i] * g[q][i] - s1 - xh[q][i] * s2) * rstd;
+        if (dres) {   // gradient that reaches h along a second path (pre-norm residual stream)
+          float e[8];
+          unpack8(__ldcs(reinterpret_cast<const uint4*>(dres + base + c)), e);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] = k[i] ? o[i] * drop_scale : 0.f;
+          for (int i = 0; i < 8; ++i) o[i] += e[i];
         }
-        *reinterpret_cast<uint4*>(dsub + base + c) = pack8(o);
+        *reinterpret_cast<uint4*>(dx + base + c) = pack8(o);
+        if (dsub) {
+          if (thresh) {
+            bool k[8];
+            keep8(seed, offset, base + c, thresh, k);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = k[i] ? o[i] * drop_scale : 0.f;
+          }
+          *reinterpret_cast<uint4*>(dsub + base + c) = pack8(o);
+        }
       }
     }
   }
-  __syncthreads();
-  for (int c = threadIdx.x; c < D; c += blockDim.x) {
-    atomicAdd(dgamma + c, pg[c]);
-    if (dbeta) atomicAdd(dbeta + c, pb[c]);
+#pragma unroll
+  for (int q = 0; q < NG; ++q) {
+    const int c = (q * 256 + threadIdx.x) * 8;
+    if (c < D) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        atomicAdd(dgamma + c + i, pg[q][i]);
+        if (dbeta) atomicAdd(dbeta + c + i, pb[q][i]);
+      }
+    }
   }
 }
 
@@ -550,8 +597,8 @@ __global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int
   float pv[8], gv[8], mv[8], vv[8];
   const bool vec = cnt == 8 && ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15) == 0;
   if (vec) {
-    unpack8(*reinterpret_cast<const uint4*>(p), pv);
-    unpack8(*reinterpret_cast<const uint4*>(g), gv);
+    unpack8(__ldcs(reinterpret_cast<const uint4*>(p)), pv);
+    unpack8(__ldcs(reinterpret_cast<const uint4*>(g)), gv);
   } else {
     for (int i = 0; i < cnt; ++i) { pv[i] = __bfloat162float(p[i]); gv[i] = __bfloat162float(g[i]); }
   }
@@ -571,8 +618,8 @@ __global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int
     const __nv_bfloat16* m = reinterpret_cast<const __nv_bfloat16*>(t.m) + i0;
     const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(t.v) + i0;
     if (svec) {
-      unpack8(*reinterpret_cast<const uint4*>(m), mv);
-      unpack8(*reinterpret_cast<const uint4*>(v), vv);
+      unpack8(__ldcs(reinterpret_cast<const uint4*>(m)), mv);
+      unpack8(__ldcs(reinterpret_cast<const uint4*>(v)), vv);
     } else {
       for (int i = 0; i < cnt; ++i) { mv[i] = __bfloat162float(m[i]); vv[i] = __bfloat162float(v[i]); }
     }
@@ -587,7 +634,7 @@ __global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int
     vv[i] = beta2 * vv[i] + (1.f - beta2) * gg * gg;
     pv[i] -= step_size * mv[i] / (sqrtf(vv[i]) * inv_sqrt_bc2 + eps);
   }
-  if (vec) *reinterpret_cast<uint4*>(p) = pack8(pv);
+  if (vec) __stcs(reinterpret_cast<uint4*>(p), pack8(pv));
   else for (int i = 0; i < cnt; ++i) p[i] = __float2bfloat16(pv[i]);
   if (t.state_fp32) {
     float* m = reinterpret_cast<float*>(t.m) + i0;
@@ -604,8 +651,8 @@ __global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int
     __nv_bfloat16* m = reinterpret_cast<__nv_bfloat16*>(t.m) + i0;
     __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(t.v) + i0;
     if (svec) {
-      *reinterpret_cast<uint4*>(m) = pack8(mv);
-      *reinterpret_cast<uint4*>(v) = pack8(vv);
+      __stcs(reinterpret_cast<uint4*>(m), pack8(mv));
+      __stcs(reinterpret_cast<uint4*>(v), pack8(vv));
     } else {
       for (int i = 0; i < cnt; ++i) { m[i] = __float2bfloat16(mv[i]); v[i] = __float2bfloat16(vv[i]); }
     }
@@ -744,6 +791,72 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* g, const __nv_bfloat16* u
   *reinterpret_cast<uint4*>(du + r * ldo + c) = pack8(ou);
 }
 
+// ------------------------------------------------------------------------------------------------
+// MoE token movement by index (top-2): slot[s, k] is the destination row (expert * capacity + position) of choice k
+// of token s, or -1.  One warp per (token, choice).  M % 8 == 0.
+// ------------------------------------------------------------------------------------------------
+__global__ void moe_scatter_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ slot,
+                                   const float* __restrict__ scale, __nv_bfloat16* __restrict__ dst, int S, int M) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= 2 * S) return;
+  const int sl = slot[w];
+  if (sl < 0) return;
+  const float sc = scale ? scale[w] : 1.f;
+  const __nv_bfloat16* a = src + (size_t)(w >> 1) * M;
+  __nv_bfloat16* d = dst + (size_t)sl * M;
+  for (int c = lane * 8; c < M; c += 256) {
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(a + c), v);
+    if (scale) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] *= sc;
+    }
+    *reinterpret_cast<uint4*>(d + c) = pack8(v);
+  }
+}
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ slot,
+                                  const float* __restrict__ scale, __nv_bfloat16* __restrict__ dst, int S, int M) {
+  const int s = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (s >= S) return;
+  const int s0 = slot[2 * s], s1 = slot[2 * s + 1];
+  const float g0 = scale ? scale[2 * s] : 1.f, g1 = scale ? scale[2 * s + 1] : 1.f;
+  for (int c = lane * 8; c < M; c += 256) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, v[8];
+    if (s0 >= 0) {
+      unpack8(*reinterpret_cast<const uint4*>(src + (size_t)s0 * M + c), v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += g0 * v[k];
+    }
+    if (s1 >= 0) {
+      unpack8(*reinterpret_cast<const uint4*>(src + (size_t)s1 * M + c), v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += g1 * v[k];
+    }
+    *reinterpret_cast<uint4*>(dst + (size_t)s * M + c) = pack8(acc);
+  }
+}
+// out[s, k] = <a[s, :], b[slot[s, k], :]>
+__global__ void moe_rowdot_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                  const int* __restrict__ slot, float* __restrict__ out, int S, int M) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= 2 * S) return;
+  const int sl = slot[w];
+  float acc = 0.f;
+  if (sl >= 0) {
+    const __nv_bfloat16* x = a + (size_t)(w >> 1) * M;
+    const __nv_bfloat16* y = b + (size_t)sl * M;
+    for (int c = lane * 8; c < M; c += 256) {
+      float u[8], v[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + c), u);
+      unpack8(*reinterpret_cast<const uint4*>(y + c), v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc += u[k] * v[k];
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) out[w] = acc;
+}
+
 // out = a + b (bf16), n % 8 == 0 handled vectorised, tail scalar
 __global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, long long n) {
   const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 8;
@@ -780,14 +893,17 @@ const char* rtp_kernels_last_error(void) { return k_err.c_str(); }
 int rtp_norm_fwd(const void* x, const void* sub, const void* gamma, const void* beta, void* h_out, void* y,
                  float* mean, float* rstd, int M, int D, float eps, int rms, float drop_p, unsigned long long seed,
                  unsigned long long offset, const unsigned long long* step_ptr, void* stream) {
-  if (D % 8) { k_err = "norm: D must be a multiple of 8"; return -1; }
-  const int threads = D >= 2048 ? 256 : 128;
+  if (D % 8 || D > 8192) { k_err = "norm: D must be a multiple of 8 and at most 8192"; return -1; }
   const int grid = M < 148 * 8 ? M : 148 * 8;
   const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
-  norm_fwd_kernel<<<grid, threads, D * sizeof(float), (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)sub, (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta,
-      (__nv_bfloat16*)h_out, (__nv_bfloat16*)y, mean, rstd, M, D, eps, rms, host_thresh(drop_p), ds, seed, offset,
-      step_ptr);
+  const int ng = (D + 2047) / 2048;
+#define RTP_NORM_FWD(NG)                                                                                              \
+  norm_fwd_kernel<NG><<<grid, 256, 0, (cudaStream_t)stream>>>(                                                       \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)sub, (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta,    \
+      (__nv_bfloat16*)h_out, (__nv_bfloat16*)y, mean, rstd, M, D, eps, rms, host_thresh(drop_p), ds, seed, offset,    \
+      step_ptr)
+  if (ng == 1) RTP_NORM_FWD(1); else if (ng == 2) RTP_NORM_FWD(2); else if (ng == 3) RTP_NORM_FWD(3); else RTP_NORM_FWD(4);
+#undef RTP_NORM_FWD
   LAUNCH_CHECK("norm_fwd");
   return 0;
 }
@@ -795,20 +911,18 @@ int rtp_norm_bwd(const void* dy, const void* h, const void* gamma, const float* 
                  void* dsub, float* dgamma, float* dbeta, int M, int D, int rms, float drop_p,
                  unsigned long long seed, unsigned long long offset, const void* dres,
                  const unsigned long long* step_ptr, void* stream) {
-  if (D % 8) { k_err = "norm: D must be a multiple of 8"; return -1; }
-  const int threads = D >= 2048 ? 256 : 128;
-  int grid = 148 * 2;
+  if (D % 8 || D > 8192) { k_err = "norm: D must be a multiple of 8 and at most 8192"; return -1; }
+  int grid = 148 * 4;
   if (grid > M) grid = M;
   const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
-  const size_t smem = 2 * (size_t)D * sizeof(float);
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(norm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return kfail("norm_bwd attr", e);
-  }
-  norm_bwd_kernel<<<grid, threads, smem, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)gamma, mean, rstd, (__nv_bfloat16*)dx,
-      (__nv_bfloat16*)dsub, dgamma, dbeta, M, D, rms, host_thresh(drop_p), ds, seed, offset,
-      (const __nv_bfloat16*)dres, step_ptr);
+  const int ng = (D + 2047) / 2048;
+#define RTP_NORM_BWD(NG)                                                                                              \
+  norm_bwd_kernel<NG><<<grid, 256, 0, (cudaStream_t)stream>>>(                                                       \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)gamma, mean, rstd, (__nv_bfloat16*)dx, \
+      (__nv_bfloat16*)dsub, dgamma, dbeta, M, D, rms, host_thresh(drop_p), ds, seed, offset,                          \
+      (const __nv_bfloat16*)dres, step_ptr)
+  if (ng == 1) RTP_NORM_BWD(1); else if (ng == 2) RTP_NORM_BWD(2); else if (ng == 3) RTP_NORM_BWD(3); else RTP_NORM_BWD(4);
+#undef RTP_NORM_BWD
   LAUNCH_CHECK("norm_bwd");
   return 0;
 }
@@ -952,6 +1066,33 @@ int rtp_swiglu_bwd(const void* g, const void* u, long long ld, const void* dy, v
       (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, ld, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dg, (__nv_bfloat16*)du, ldo, rows,
       cols);
   LAUNCH_CHECK("swiglu_bwd");
+  return 0;
+}
+int rtp_moe_scatter(const void* src, const int* slot, const float* scale, void* dst, int S, int M, long long dst_rows,
+                    void* stream) {
+  if (M % 8) { k_err = "moe: M must be a multiple of 8"; return -1; }
+  cudaError_t e = cudaMemsetAsync(dst, 0, (size_t)dst_rows * M * 2, (cudaStream_t)stream);
+  if (e != cudaSuccess) return kfail("moe memset", e);
+  const long long threads = 2ll * S * 32;
+  moe_scatter_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)src, slot, scale, (__nv_bfloat16*)dst, S, M);
+  LAUNCH_CHECK("moe_scatter");
+  return 0;
+}
+int rtp_moe_gather(const void* src, const int* slot, const float* scale, void* dst, int S, int M, void* stream) {
+  if (M % 8) { k_err = "moe: M must be a multiple of 8"; return -1; }
+  const long long threads = (long long)S * 32;
+  moe_gather_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)src, slot, scale, (__nv_bfloat16*)dst, S, M);
+  LAUNCH_CHECK("moe_gather");
+  return 0;
+}
+int rtp_moe_rowdot(const void* a, const void* b, const int* slot, float* out, int S, int M, void* stream) {
+  if (M % 8) { k_err = "moe: M must be a multiple of 8"; return -1; }
+  const long long threads = 2ll * S * 32;
+  moe_rowdot_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, slot, out, S, M);
+  LAUNCH_CHECK("moe_rowdot");
   return 0;
 }
 int rtp_add(const void* a, const void* b, void* out, long long n, void* stream) {

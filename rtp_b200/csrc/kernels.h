@@ -49,6 +49,10 @@ int rtp_gelu_bwd(const void* x, const void* dy, void* dx, long long n, void* str
 int rtp_swiglu_fwd(const void* g, const void* u, long long ld, void* y, long long rows, int cols, void* stream);
 int rtp_swiglu_bwd(const void* g, const void* u, long long ld, const void* dy, void* dg, void* du, long long ldo,
                    long long rows, int cols, void* stream);
+int rtp_moe_scatter(const void* src, const int* slot, const float* scale, void* dst, int S, int M, long long dst_rows,
+                    void* stream);
+int rtp_moe_gather(const void* src, const int* slot, const float* scale, void* dst, int S, int M, void* stream);
+int rtp_moe_rowdot(const void* a, const void* b, const int* slot, float* out, int S, int M, void* stream);
 int rtp_add(const void* a, const void* b, void* out, long long n, void* stream);
 int rtp_cast_f32_bf16(const float* in, void* out, long long n, float scale, void* stream);
 int rtp_sum_f32(const float* in, float* out, int n, float scale, void* stream);

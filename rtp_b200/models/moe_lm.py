@@ -36,10 +36,11 @@ class Expert(nn.Module):
     def __init__(self, d_model, d_ff):
         super().__init__()
         self.linear1 = nn.Linear(d_model, d_ff)
+        self.activation = nn.GELU()
         self.linear2 = nn.Linear(d_ff, d_model)
 
     def forward(self, x):
-        return self.linear2(F.gelu(self.linear1(x)))
+        return self.linear2(self.activation(self.linear1(x)))
 
 
 class MoEBlock(nn.Module):

@@ -38,6 +38,44 @@ def _combine(combine_weights: Tensor, expert_output: Tensor) -> Tensor:
     return torch.einsum("sec,ecm->sm", combine_weights, expert_output)
 
 
+def dispatch_by_index(x: Tensor, idx: Tensor, loc: Tensor, valid: Tensor, num_experts: int, capacity: int) -> Tensor:
+    """Index form of ``einsum("sec,sm->ecm", dispatch_mask, x)``: token s goes to slot ``loc[s, k]`` of expert
+    ``idx[s, k]`` for each valid choice k.  O(S*M) instead of O(S*E*C*M)."""
+    from ..ops import moe as MK
+    if MK.use_kernels(x):
+        return MK.dispatch(x, idx, loc, valid, num_experts, capacity)
+    S, M = x.shape
+    dummy = num_experts * capacity
+    slot = torch.where(valid, idx * capacity + loc, torch.full_like(idx, dummy))
+    out = x.new_zeros(dummy + 1, M)
+    out = out.index_copy(0, slot.reshape(-1), x.repeat_interleave(2, dim=0))
+    return out[:dummy].view(num_experts, capacity, M)
+
+
+def combine_by_index(expert_output: Tensor, idx: Tensor, loc: Tensor, gate: Tensor, valid: Tensor) -> Tensor:
+    """Index form of ``einsum("sec,ecm->sm", combine_weights, expert_output)``."""
+    from ..ops import moe as MK
+    if MK.use_kernels(expert_output):
+        return MK.combine(expert_output, idx, loc, gate, valid)
+    E, C, M = expert_output.shape
+    flat = torch.cat([expert_output.reshape(E * C, M), expert_output.new_zeros(1, M)])
+    slot = torch.where(valid, idx * C + loc, torch.full_like(idx, E * C))
+    g = (gate * valid).to(expert_output.dtype)
+    return (flat[slot] * g.unsqueeze(-1)).sum(dim=1)
+
+
+def _route(gate_module, x):
+    """(l_aux, dispatch fn, combine fn) from a gate: index form when the gate offers ``route``, else the dense
+    [S, E, C] tensors of the reference."""
+    if hasattr(gate_module, "route"):
+        l_aux, idx, loc, g, valid, capacity = gate_module.route(x)
+        E = getattr(gate_module, "num_experts", None) or gate_module.wg.out_features
+        return (l_aux.to(x.dtype), lambda t: dispatch_by_index(t, idx, loc, valid, E, capacity),
+                lambda eo: combine_by_index(eo, idx, loc, g, valid))
+    l_aux, combine_weights, dispatch_mask = gate_module(x)
+    return l_aux, (lambda t: _dispatch(dispatch_mask, t)), (lambda eo: _combine(combine_weights, eo))
+
+
 class MOELayer(nn.Module):
     """Expert-parallel MoE with two all-to-alls per direction (GShard algorithm 2)."""
 
@@ -57,8 +95,8 @@ class MOELayer(nn.Module):
         assert len(input[0].shape) == 3, "input Tensor must have dimensions: (s)equence, (t)oken, (m)odel"
         d_model = input[0].shape[2]
         reshaped = input[0].reshape(-1, d_model)
-        self.l_aux, combine_weights, dispatch_mask = self.gate(reshaped)
-        dispatched = _dispatch(dispatch_mask, reshaped)
+        self.l_aux, dispatch, combine = _route(self.gate, reshaped)
+        dispatched = dispatch(reshaped)
         dispatched = _AllToAll.apply(self.ring.group, dispatched)
         dispatched = dispatched.reshape(self.world_size, self.num_local_experts, -1, d_model)
         chunks = dispatched.chunk(self.num_local_experts, dim=1)
@@ -66,7 +104,7 @@ class MOELayer(nn.Module):
         expert_output = torch.cat(outs, dim=1)
         expert_output = _AllToAll.apply(self.ring.group, expert_output)
         expert_output = expert_output.reshape(self.world_size * self.num_local_experts, -1, d_model)
-        combined = _combine(combine_weights, expert_output)
+        combined = combine(expert_output)
         return combined.reshape(input[0].shape)
 
 
@@ -91,17 +129,44 @@ class WeightMOELayer(RotatedModule):
             with torch.no_grad():
                 for p, q in zip(self.experts.parameters(), original_experts.parameters()):
                     p.copy_(q)
-        self._pnames = [n for n, _ in self.experts.named_parameters()]
+        # flat order: all (weight, bias) blocks of linear1, then of linear2, then anything else, so that each linear
+        # of all local experts is one contiguous range with a uniform stride
+        names = [n for n, _ in self.experts.named_parameters()]
+
+        def key(n):
+            parts = n.split(".")
+            layer = parts[1] if len(parts) > 2 else ""
+            rank = {"linear1": 0, "linear2": 1}.get(layer, 2)
+            return (rank, int(parts[0]) if parts[0].isdigit() else 0, 0 if n.endswith("weight") else 1, n)
+        self._pnames = sorted(names, key=key)
         self._flatten()
 
     def shard_parameters(self):
-        return [p for _, p in self.experts.named_parameters()]
+        d = dict(self.experts.named_parameters())
+        return [d[n] for n in self._pnames]
 
     def shard_names(self):
         return list(self._pnames)
 
     def shard_spec(self):
         return {f"experts.{n}": ("expert", self.num_local_experts) for n in self._pnames}
+
+    def _fused_ok(self, dispatched):
+        from ..parallel import fused
+        ex = self.experts[0]
+        if not (hasattr(ex, "linear1") and hasattr(ex, "linear2") and isinstance(ex.linear1, nn.Linear)
+                and isinstance(ex.linear2, nn.Linear) and ex.linear1.bias is not None and ex.linear2.bias is not None):
+            return False
+        act = getattr(ex, "activation", None)
+        if not (act is None or isinstance(act, (nn.GELU, nn.ReLU)) or act is torch.nn.functional.gelu):
+            return False
+        if self.training and any(isinstance(m, nn.Dropout) and m.p > 0 for m in ex.modules()):
+            return False
+        if self.num_local_experts * self.world_size > 8 or dispatched.shape[1] % 8:
+            return False
+        if set(n.split(".", 1)[1] for n in self._pnames) != {"linear1.weight", "linear1.bias", "linear2.weight", "linear2.bias"}:
+            return False
+        return fused.use_fused(dispatched, self._full_param)
 
     def forward(self, *input: Tensor, **kwargs: Any) -> Tensor:
         assert len(input) == 1, "only single input Tensor supported"
@@ -110,8 +175,8 @@ class WeightMOELayer(RotatedModule):
             "number of tokens must be a multiple of the number of local experts"
         d_model = input[0].shape[2]
         reshaped = input[0].reshape(-1, d_model)
-        self.l_aux, combine_weights, dispatch_mask = self.gate(reshaped)
-        dispatched = _dispatch(dispatch_mask, reshaped)          # [E, C, M]
+        self.l_aux, dispatch, combine = _route(self.gate, reshaped)
+        dispatched = dispatch(reshaped)                          # [E, C, M]
         N, L = self.world_size, self.num_local_experts
         experts, names = self.experts, self._pnames
         training = self.training
@@ -126,8 +191,11 @@ class WeightMOELayer(RotatedModule):
             return torch.cat(outs, dim=0)
 
         stochastic = training and any(isinstance(m, nn.Dropout) and m.p > 0 for m in experts.modules())
+        if self._fused_ok(dispatched):
+            from ..parallel.engine import fused_experts
+            return combine(fused_experts(self, dispatched)).reshape(input[0].shape)
         expert_output = rotated_apply(self.ring, fn, self.shard_parameters(), self._full_param, self._layout,
                                       (dispatched,), combine="cat", cat_dim=0, inplace=self.inplace,
                                       stochastic=stochastic, owner=self)
-        combined = _combine(combine_weights, expert_output)
+        combined = combine(expert_output)
         return combined.reshape(input[0].shape)

@@ -91,6 +91,10 @@ class Top2Gate(nn.Module):
     def forward(self, input: torch.Tensor) -> Tuple[Tensor, Tensor, Tensor]:  # type: ignore
         return top2gating(self.wg(input), self.capacity_factor)
 
+    def route(self, input: torch.Tensor):
+        """Index form of the gating decision (see ``top2_routing``): no [S, E, C] tensors are built."""
+        return top2_routing(self.wg(input), self.capacity_factor)[:6]
+
 
 class WeightTop2Gate(RotatedModule):
     """Gate whose weight rows (experts) are sharded ``[E/N, D]`` and rotate; logits of all experts are
@@ -128,3 +132,6 @@ class WeightTop2Gate(RotatedModule):
 
     def forward(self, input: torch.Tensor) -> Tuple[Tensor, Tensor, Tensor]:  # type: ignore
         return top2gating(self.logits(input), self.capacity_factor)
+
+    def route(self, input: torch.Tensor):
+        return top2_routing(self.logits(input), self.capacity_factor)[:6]

@@ -90,6 +90,24 @@ class EmbedFwd(C.Structure):
     ]
 
 
+class ExpertFwd(C.Structure):
+    _fields_ = [
+        ("cap", C.c_int), ("n_local", C.c_int), ("in_features", C.c_int), ("out_features", C.c_int),
+        ("home", C.c_void_p), ("expert_stride", C.c_longlong), ("bias_off", C.c_longlong), ("shard_bytes", C.c_ulonglong),
+        ("x", C.c_void_p), ("ldx", C.c_longlong), ("y", C.c_void_p), ("ldy", C.c_longlong), ("act", C.c_int),
+    ]
+
+
+class ExpertBwd(C.Structure):
+    _fields_ = [
+        ("cap", C.c_int), ("n_local", C.c_int), ("in_features", C.c_int), ("out_features", C.c_int),
+        ("home", C.c_void_p), ("expert_stride", C.c_longlong), ("bias_off", C.c_longlong), ("shard_bytes", C.c_ulonglong),
+        ("x", C.c_void_p), ("ldx", C.c_longlong), ("dy", C.c_void_p), ("ldy", C.c_longlong),
+        ("dx", C.c_void_p), ("lddx", C.c_longlong), ("grad_home", C.c_void_p), ("dbias_full", C.c_void_p),
+        ("mask", C.c_void_p), ("ldmask", C.c_longlong), ("mask_scale", C.c_float),
+    ]
+
+
 class ReduceScatter(C.Structure):
     _fields_ = [("src", C.c_void_p), ("ld", C.c_longlong), ("rows", C.c_int), ("cols", C.c_int), ("out", C.c_void_p)]
 
@@ -134,6 +152,11 @@ def lib():
         L.rtp_reduce_scatter_cols.argtypes = [C.POINTER(Ring), C.POINTER(ReduceScatter), C.c_void_p]
         L.rtp_embed_fwd_rot_emu.argtypes = [C.POINTER(Ring), C.POINTER(EmbedFwd), C.c_int, C.c_void_p]
         L.rtp_reduce_scatter_cols_emu.argtypes = [C.POINTER(Ring), C.POINTER(ReduceScatter), C.c_int, C.c_void_p]
+        L.rtp_expert_fwd.argtypes = [C.POINTER(Ring), C.POINTER(ExpertFwd), C.c_void_p]
+        L.rtp_expert_bwd.argtypes = [C.POINTER(Ring), C.POINTER(ExpertBwd), C.c_void_p]
+        L.rtp_expert_fwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(ExpertFwd), C.c_int, C.c_void_p]
+        L.rtp_expert_bwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(ExpertBwd), C.c_int, C.c_void_p]
+        L.rtp_set_pair_mode.argtypes = [C.c_int]
         L.rtp_linear_fwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(LinearFwd), C.c_int, C.c_void_p]
         L.rtp_linear_bwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(LinearBwd), C.c_int, C.c_void_p]
         _lib = L

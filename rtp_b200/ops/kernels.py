@@ -31,6 +31,9 @@ def _L():
         L.rtp_colsum.argtypes = [vp, ll, i, i, vp, vp]
         L.rtp_adam.argtypes = [vp, vp, i, i, vp, f, f, f, f, f, i, f, f, vp]
         L.rtp_add.argtypes = [vp, vp, vp, ll, vp]
+        L.rtp_moe_scatter.argtypes = [vp, vp, vp, vp, i, i, ll, vp]
+        L.rtp_moe_gather.argtypes = [vp, vp, vp, vp, i, i, vp]
+        L.rtp_moe_rowdot.argtypes = [vp, vp, vp, vp, i, i, vp]
         L.rtp_gelu_fwd.argtypes = [vp, vp, ll, vp]
         L.rtp_gelu_bwd.argtypes = [vp, vp, vp, ll, vp]
         L.rtp_swiglu_fwd.argtypes = [vp, vp, ll, vp, ll, i, vp]
@@ -186,6 +189,29 @@ def swiglu_bwd(g, u, dy):
     _check(_L().rtp_swiglu_bwd(_p(g), _p(u), g.stride(0), _p(dy), _p(dg), _p(du), cols, rows, cols, _lib.stream_ptr()),
            "swiglu_bwd")
     return dg, du
+
+
+def moe_scatter(src, slot, scale, dst_rows):
+    """dst[slot[s, k]] = scale[s, k] * src[s] (rows without a token stay zero). slot: int32 [S, 2], -1 = dropped."""
+    S, M = src.shape
+    dst = torch.empty(dst_rows, M, dtype=src.dtype, device=src.device)
+    _check(_L().rtp_moe_scatter(_p(src), _p(slot), _p(scale), _p(dst), S, M, dst_rows, _lib.stream_ptr()), "moe_scatter")
+    return dst
+
+
+def moe_gather(src, slot, scale):
+    """dst[s] = sum_k scale[s, k] * src[slot[s, k]]."""
+    S, M = slot.shape[0], src.shape[1]
+    dst = torch.empty(S, M, dtype=src.dtype, device=src.device)
+    _check(_L().rtp_moe_gather(_p(src), _p(slot), _p(scale), _p(dst), S, M, _lib.stream_ptr()), "moe_gather")
+    return dst
+
+
+def moe_rowdot(a, b, slot):
+    S, M = a.shape
+    out = torch.empty(S, 2, dtype=torch.float32, device=a.device)
+    _check(_L().rtp_moe_rowdot(_p(a), _p(b), _p(slot), _p(out), S, M, _lib.stream_ptr()), "moe_rowdot")
+    return out
 
 
 def add(a, b, out=None):

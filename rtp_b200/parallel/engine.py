@@ -342,3 +342,92 @@ class _FusedEmbeddingFn(torch.autograd.Function):
 
 def fused_embedding(module, ids):
     return _FusedEmbeddingFn.apply(module, ids, module.embedding.weight)
+
+
+# --------------------------------------------------------------------------------------------------
+# rotating experts (one linear of every expert per launch)
+# --------------------------------------------------------------------------------------------------
+class _FusedExpertLinearFn(torch.autograd.Function):
+    """x: [E_total, cap, in] (dispatched tokens, expert-major) -> [E_total, cap, out].  ``spec`` = (ring, flat range,
+    n_local, in_f, out_f, expert_stride, bias_off, places) with places = [(offset, numel, shape)] of the given
+    parameters inside the flat range (order: e0.weight, e0.bias, e1.weight, ...)."""
+
+    @staticmethod
+    def forward(ctx, spec, x, *params):
+        ring, flat, L, in_f, out_f, stride, bias_off, places = spec
+        eng = get_engine(ring)
+        E, cap, _ = x.shape
+        x2 = x.reshape(E * cap, in_f).contiguous()
+        y = torch.empty(E * cap, out_f, dtype=torch.bfloat16, device=x.device)
+        op = _lib.ExpertFwd()
+        op.cap, op.n_local, op.in_features, op.out_features = cap, L, in_f, out_f
+        op.home, op.expert_stride, op.bias_off = flat.data_ptr(), stride, bias_off
+        op.shard_bytes = _round_up(flat.numel() * 2, 16)
+        op.x, op.ldx, op.y, op.ldy, op.act = x2.data_ptr(), in_f, y.data_ptr(), out_f, 0
+        _lib.check(_lib.lib().rtp_expert_fwd(C.byref(eng.ring), C.byref(op), _lib.stream_ptr()), "rtp_expert_fwd")
+        ctx.spec, ctx.eng = spec, eng
+        ctx.save_for_backward(x2)
+        ctx.dims = (E, cap)
+        return y.view(E, cap, out_f)
+
+    @staticmethod
+    def backward(ctx, dy):
+        ring, flat, L, in_f, out_f, stride, bias_off, places = ctx.spec
+        (x2,) = ctx.saved_tensors
+        E, cap = ctx.dims
+        dy2 = dy.reshape(E * cap, out_f).contiguous()
+        need_dx = ctx.needs_input_grad[1]
+        dx = torch.empty(E * cap, in_f, dtype=torch.bfloat16, device=dy.device) if need_dx else None
+        gflat = torch.empty_like(flat)
+        dbias = None
+        if bias_off >= 0:
+            dbias = torch.empty(E, out_f, dtype=torch.float32, device=dy.device)
+            for g in range(E):
+                K.colsum(dy2[g * cap:(g + 1) * cap], dbias[g])
+        op = _lib.ExpertBwd()
+        op.cap, op.n_local, op.in_features, op.out_features = cap, L, in_f, out_f
+        op.home, op.expert_stride, op.bias_off = flat.data_ptr(), stride, bias_off
+        op.shard_bytes = _round_up(flat.numel() * 2, 16)
+        op.x, op.ldx, op.dy, op.ldy = x2.data_ptr(), in_f, dy2.data_ptr(), out_f
+        if dx is not None:
+            op.dx, op.lddx = dx.data_ptr(), in_f
+        op.grad_home = gflat.data_ptr()
+        op.dbias_full = dbias.data_ptr() if dbias is not None else None
+        _lib.check(_lib.lib().rtp_expert_bwd(C.byref(ctx.eng.ring), C.byref(op), _lib.stream_ptr()), "rtp_expert_bwd")
+        grads = [gflat[off:off + n].view(shape) for off, n, shape in places]
+        return (None, dx.view(E, cap, in_f) if dx is not None else None, *grads)
+
+
+def fused_experts(module, dispatched):
+    """Both linears of every (rotating) expert on the fused kernels; the activation in between is an elementwise
+    kernel.  ``module`` is a ``WeightMOELayer`` whose experts expose ``linear1`` / ``linear2`` / ``activation``."""
+    from ..ops import functional as FO
+    lay, flat = module._layout, module._full_param
+    L = module.num_local_experts
+    experts = list(module.experts)
+
+    def spec_for(layer):
+        w0 = getattr(experts[0], layer).weight
+        out_f, in_f = w0.shape
+        off0 = lay.offset_of(f"0.{layer}.weight")
+        stride = (lay.offset_of(f"1.{layer}.weight") - off0) if L > 1 else 0
+        bias_off = lay.offset_of(f"0.{layer}.bias") - off0
+        end = lay.offset_of(f"{L - 1}.{layer}.bias") + ((out_f + 63) // 64) * 64
+        rng = flat[off0:end]
+        places, params = [], []
+        for e in range(L):
+            for nm in ("weight", "bias"):
+                p = getattr(getattr(experts[e], layer), nm)
+                places.append((lay.offset_of(f"{e}.{layer}.{nm}") - off0, p.numel(), p.shape))
+                params.append(p)
+        return (module.ring, rng, L, in_f, out_f, stride, bias_off, places), params
+
+    s1, p1 = spec_for("linear1")
+    s2, p2 = spec_for("linear2")
+    h = _FusedExpertLinearFn.apply(s1, dispatched, *p1)
+    act = experts[0].activation if hasattr(experts[0], "activation") else None
+    if act is None or isinstance(act, torch.nn.GELU) or act is torch.nn.functional.gelu:
+        h = FO.gelu(h)
+    else:
+        h = torch.relu(h)
+    return _FusedExpertLinearFn.apply(s2, h, *p2)

@@ -157,3 +157,36 @@ def test_long_sequence_attention_on_batched_gemm(B, S, H, hd):
     _close(q.grad, qr.grad, 3e-2)
     _close(k.grad, kr.grad, 3e-2)
     _close(v.grad, vr.grad, 3e-2)
+
+
+def test_moe_dispatch_combine_by_index_matches_dense_einsums():
+    from rtp_b200.module.top2gate import top2_routing, top2gating
+    from rtp_b200.ops import moe as MK
+    torch.manual_seed(0)
+    S, E, M = 256, 8, 128
+    logits = torch.randn(S, E, device="cuda")
+    noise = torch.randn(S, E, device="cuda")
+    l_aux, idx, loc, gate, valid, cap, _, _ = top2_routing(logits, 1.25, noise)
+    _, comb_w, disp_mask = top2gating(logits, 1.25, noise)
+    x = torch.randn(S, M, device="cuda", dtype=BF, requires_grad=True)
+    gate = gate.detach().requires_grad_(True)
+    disp = MK.dispatch(x, idx, loc, valid, E, cap)
+    ref_disp = torch.einsum("sec,sm->ecm", disp_mask.float(), x.float())
+    _close(disp, ref_disp, 1e-2)
+    eo = torch.randn(E, cap, M, device="cuda", dtype=BF, requires_grad=True)
+    y = MK.combine(eo, idx, loc, gate, valid)
+    ref_y = torch.einsum("sec,ecm->sm", comb_w.float(), eo.float())
+    _close(y, ref_y, 2e-2)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    disp.backward(torch.ones_like(disp))
+    eo_r = eo.detach().float().requires_grad_(True)
+    torch.einsum("sec,ecm->sm", comb_w.float(), eo_r).backward(dy.float())
+    _close(eo.grad, eo_r.grad, 2e-2)
+    x_r = x.detach().float().requires_grad_(True)
+    torch.einsum("sec,sm->ecm", disp_mask.float(), x_r).sum().backward()
+    _close(x.grad, x_r.grad, 1e-2)
+    # gate gradient: d y / d gate[s, k] = <dy[s], eo[slot]>
+    slot = torch.where(valid, idx * cap + loc, torch.zeros_like(idx))
+    ref_dg = (dy.float().unsqueeze(1) * eo.detach().float().reshape(E * cap, M)[slot]).sum(-1) * valid
+    _close(gate.grad, ref_dg, 2e-2)

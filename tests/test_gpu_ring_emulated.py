@@ -185,3 +185,71 @@ def test_missing_producer_times_out_and_returns():
     assert z == 4.0                          # the context is alive
     for w in wss:
         L.rtp_ws_destroy(w)
+
+
+@pytest.mark.parametrize("world,L", [(2, 2), (4, 1), (4, 2)])
+def test_rotating_experts_fwd_bwd(world, L):
+    """One linear of every expert while the expert blocks rotate: tokens of expert g only ever meet weights of g."""
+    from rtp_b200.ops import _lib, kernels as K
+    lib = _lib.lib()
+    torch.manual_seed(0)
+    cap, IN, OUT = 192, 256, 512
+    E = world * L
+    G_ = (148 // world) & ~1
+    blk_w = OUT * IN
+    bias_off = blk_w
+    stride = blk_w + (OUT + 63) // 64 * 64
+    nflat = L * stride
+    slot_bytes = (nflat * 2 + 65535) // 65536 * 65536
+    wss, rings = _rings(world, slot_bytes, G_, lib, _lib)
+    Ws = [(torch.randn(OUT, IN, device="cuda") * 0.05).to(BF) for _ in range(E)]
+    Bs = [(torch.randn(OUT, device="cuda") * 0.1).to(BF) for _ in range(E)]
+    fops = (_lib.ExpertFwd * world)()
+    homes, xs, ys = [], [], []
+    for r in range(world):
+        flat = torch.zeros(nflat, device="cuda", dtype=BF)
+        for e in range(L):
+            flat[e * stride:e * stride + blk_w] = Ws[r * L + e].reshape(-1)
+            flat[e * stride + bias_off:e * stride + bias_off + OUT] = Bs[r * L + e]
+        x = torch.randn(E * cap, IN, device="cuda", dtype=BF)
+        y = torch.zeros(E * cap, OUT, device="cuda", dtype=BF)
+        homes.append(flat); xs.append(x); ys.append(y)
+        o = fops[r]
+        o.cap, o.n_local, o.in_features, o.out_features = cap, L, IN, OUT
+        o.home, o.expert_stride, o.bias_off, o.shard_bytes = flat.data_ptr(), stride, bias_off, nflat * 2
+        o.x, o.ldx, o.y, o.ldy, o.act = x.data_ptr(), IN, y.data_ptr(), OUT, 0
+    for _ in range(2):
+        _lib.check(lib.rtp_expert_fwd_emu(rings, fops, world, _lib.stream_ptr()), "expert fwd emu")
+    torch.cuda.synchronize()
+    _status_ok(wss, lib, _lib)
+    for r in range(world):
+        ref = torch.cat([xs[r][g * cap:(g + 1) * cap].float() @ Ws[g].float().t() + Bs[g].float() for g in range(E)])
+        _close(ys[r], ref, 1.5e-2, f"expert fwd rank {r}")
+    bops = (_lib.ExpertBwd * world)()
+    dys, dxs, gfs, keep = [], [], [], []
+    for r in range(world):
+        dy = torch.randn(E * cap, OUT, device="cuda", dtype=BF) * 0.1
+        dx = torch.zeros(E * cap, IN, device="cuda", dtype=BF)
+        gf = torch.zeros(nflat, device="cuda", dtype=BF)
+        db = torch.stack([dy[g * cap:(g + 1) * cap].float().sum(0) for g in range(E)]).contiguous()
+        dys.append(dy); dxs.append(dx); gfs.append(gf); keep.append(db)
+        o = bops[r]
+        o.cap, o.n_local, o.in_features, o.out_features = cap, L, IN, OUT
+        o.home, o.expert_stride, o.bias_off, o.shard_bytes = homes[r].data_ptr(), stride, bias_off, nflat * 2
+        o.x, o.ldx, o.dy, o.ldy = xs[r].data_ptr(), IN, dy.data_ptr(), OUT
+        o.dx, o.lddx, o.grad_home, o.dbias_full = dx.data_ptr(), IN, gf.data_ptr(), db.data_ptr()
+    for _ in range(2):
+        _lib.check(lib.rtp_expert_bwd_emu(rings, bops, world, _lib.stream_ptr()), "expert bwd emu")
+    torch.cuda.synchronize()
+    _status_ok(wss, lib, _lib)
+    for r in range(world):
+        ref_dx = torch.cat([dys[r][g * cap:(g + 1) * cap].float() @ Ws[g].float() for g in range(E)])
+        _close(dxs[r], ref_dx, 1.5e-2, f"expert dx rank {r}")
+        for e in range(L):
+            g = r * L + e
+            gw = sum(dys[q][g * cap:(g + 1) * cap].float().t() @ xs[q][g * cap:(g + 1) * cap].float() for q in range(world))
+            gb = sum(dys[q][g * cap:(g + 1) * cap].float().sum(0) for q in range(world))
+            _close(gfs[r][e * stride:e * stride + blk_w].view(OUT, IN), gw, 2e-2, f"expert dW rank {r} e {e}")
+            _close(gfs[r][e * stride + bias_off:e * stride + bias_off + OUT], gb, 2e-2, f"expert db rank {r} e {e}")
+    for w in wss:
+        lib.rtp_ws_destroy(w)

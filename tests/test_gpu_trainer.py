@@ -119,3 +119,44 @@ def test_module_path_models_on_kernels(family):
         assert p.grad is not None, n
         assert _rel_err(p.grad, refp[n].grad) < 0.15 and _cos(p.grad, refp[n].grad) > 0.985, \
             (n, _rel_err(p.grad, refp[n].grad), _cos(p.grad, refp[n].grad))
+
+
+def test_moe_lm_on_kernels():
+    """MoE LM on one GPU: index dispatch/combine kernels + experts on the rotation GEMM kernel vs fp32 functional path."""
+    import rtp_b200.module.top2gate as tg
+    from rtp_b200.models.moe_lm import MoELM, MoEConfig
+    from rtp_b200.parallel.context import set_backend
+    from rtp_b200.parallel import engine
+    torch.manual_seed(0)
+    saved = tg.gumbel_rsample
+    tg.gumbel_rsample = lambda shape, device: torch.zeros(shape, device=device)
+    try:
+        cfg = MoEConfig(vocab_size=1024, d_model=256, n_layers=2, n_heads=4, d_ff=512, n_experts=8, max_seq_len=128,
+                        capacity_factor=2.0)
+        model = MoELM(cfg).to("cuda", BF)
+        ref = copy.deepcopy(model).float()
+        ids = torch.randint(0, 1024, (2, 129), device="cuda")
+        x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+        set_backend("functional")
+        try:
+            loss_ref = ref(x, y)
+            loss_ref.backward()
+        finally:
+            set_backend("auto")
+        loss = model(x, y)
+        loss.backward()
+        engine.check_all()
+        assert abs(loss.item() - loss_ref.item()) < 5e-2, (loss.item(), loss_ref.item())
+        refp = dict(ref.named_parameters())
+        bad = []
+        for n, p in model.named_parameters():
+            assert p.grad is not None, n
+            if "gate" in n:
+                continue      # routing decisions of a bf16 and an fp32 run can differ for near-tied tokens
+            # a few near-tied tokens are routed differently by the bf16 and the fp32 run, which moves whole rows of
+            # an expert's gradient: compare directions loosely
+            if _cos(p.grad, refp[n].grad) < 0.85:
+                bad.append((n, _cos(p.grad, refp[n].grad)))
+        assert not bad, bad
+    finally:
+        tg.gumbel_rsample = saved
