@@ -91,6 +91,44 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Variants on 32-bit shared-memory addresses for the hot loops: the common case (barrier already complete) is one
+// try_wait; the bounded spin lives out of line so the loop body stays small.
+__device__ __forceinline__ bool mbar_try_wait_s(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+static __device__ __noinline__ bool mbar_wait_slow_s(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                              unsigned long long* status, unsigned long long timeout_ns) {
+  unsigned long long t0 = globaltimer_ns();
+  uint32_t it = 0;
+  while (true) {
+    if (mbar_try_wait_s(bar, parity)) return true;
+    if ((++it & 0xff) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > timeout_ns) {
+        *abort_flag = 1;
+        atomicCAS(status, (unsigned long long)ST_OK, (unsigned long long)ST_TIMEOUT_MBAR);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait_s(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                            unsigned long long* status, unsigned long long timeout_ns) {
+  if (mbar_try_wait_s(bar, parity)) return true;
+  return mbar_wait_slow_s(bar, parity, abort_flag, status, timeout_ns);
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_s(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies, global -> shared; every copy targets the issuing CTA only)
 // ---------------------------------------------------------------------------------------------
@@ -98,6 +136,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_s(uint32_t smem_dst, unsigned long long map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
@@ -159,17 +203,24 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t smem_addr, uint32_t cta) {
   return r;
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes)
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes)
                : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
                                                  uint32_t leader_bar_cluster_addr) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(leader_bar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair_s(uint32_t smem_dst, unsigned long long map, int x, int y,
+                                                   uint32_t leader_bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar_cluster_addr)
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {

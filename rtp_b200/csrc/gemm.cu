@@ -699,7 +699,7 @@ const char* rtp_last_error(void) { return g_err.c_str(); }
 void rtp_debug_force_stages(int n) { g_force_stages = n; }
 void rtp_set_pair_mode(int on) { g_pair = on ? 1 : 0; }
 unsigned long long* g_trace = nullptr;
-void rtp_debug_set_trace(unsigned long long* device_buffer_768_words) { g_trace = device_buffer_768_words; }
+void rtp_debug_set_trace(unsigned long long* device_buffer_1024_words) { g_trace = device_buffer_1024_words; }
 int rtp_sm_count(void) { return sm_count(); }
 
 int rtp_gemm(const RtpGemmArgs* a, void* stream) {

@@ -103,13 +103,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (elect_one()) {     // elect.sync, not lane == 0: lets the compiler treat the TMA operands as warp-uniform
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t issued_parity[kMaxStages];
-      bool issued[kMaxStages];
+      uint32_t issued_mask = 0, issued_parity = 0;   // bit s: stage s has been filled / parity of its last fill
       int tr_n = 0;
-      for (int s = 0; s < kStages; ++s) { issued[s] = false; issued_parity[s] = 0; }
+      const uint32_t tiles_s = smem_u32(tiles);
+      const uint32_t full_s = smem_u32(&ctl->full[0]);
+      const uint32_t empty_s = smem_u32(&ctl->empty[0]);
+      const uint32_t lead_full_s = PAIR ? mapa_u32(full_s, 0) : full_s;
+      (void)lead_full_s;
       bool ok = true;
       for (int p = 0; p < P.n_phases && ok; ++p) {
         const RtpPhase& ph = P.phases[p];
@@ -129,12 +132,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         }
         if (!ok) break;
         if (any_wait) fence_proxy_async();
-        const CUtensorMap* ma = &P.maps[ph.a_map];
-        const CUtensorMap* mb = &P.maps[ph.b_map];
+        const unsigned long long ma = reinterpret_cast<unsigned long long>(&P.maps[ph.a_map]);
+        const unsigned long long mb = reinterpret_cast<unsigned long long>(&P.maps[ph.b_map]);
         const int kblocks_full = (ph.K + kBK - 1) / kBK;
         const int p_a_mn = ph.a_mn;
         const int p_b_mn = ph.b_mn;
-        const int p_b_box = ph.b_box;
         const int p_bn = ph.bn;
         const int p_causal = ph.causal;
         const int p_batch_inner = ph.batch_inner;
@@ -153,6 +155,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const int p_cta_off = ph.cta_off;
         const int bn_local = PAIR ? p_bn / 2 : p_bn;     // B rows staged by this CTA
         const uint32_t tx = kABytes + bn_local * kBK * 2;
+        // One stage = na boxes of A and nb boxes of B.  Coordinates are kept as (x, y) of the tensor map, so the
+        // k-loop only adds constants: a K-major operand advances x by 64 per k-block, an MN-major one advances y.
+        const int na = p_a_mn ? 2 : 1;                                   // MN-major A: two 64-wide boxes
+        const int nb = p_b_mn ? bn_local / 64 : bn_local / ph.b_box;
+        const int a_dx = p_a_mn ? 0 : kBK, a_dy = p_a_mn ? kBK : 0;      // per k-block
+        const int b_dx = p_b_mn ? 0 : kBK, b_dy = p_b_mn ? kBK : 0;
+        const int b_ix = p_b_mn ? 64 : 0, b_iy = p_b_mn ? 0 : ph.b_box;  // per box inside a stage
+        const uint32_t b_ismem = p_b_mn ? 8192u : (uint32_t)ph.b_box * 128u;
         for (int t = (unit - p_cta_off + GU) % GU; t < total && ok; t += GU) {
           const int z = t / per_batch, tt = t % per_batch;
           const int m0u = (tt % tiles_m) * TM;              // first row of the unit's tile
@@ -165,47 +175,30 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           const int a_k0 = p_a_off_k + zo * p_a_bo_k + zi * p_a_bi_k;
           const int b_mn0 = n0 + (int)crank * bn_local + p_b_off_mn + zo * p_b_bo_mn + zi * p_b_bi_mn;
           const int b_k0 = p_b_off_k + zo * p_b_bo_k + zi * p_b_bi_k;
+          int ax = p_a_mn ? a_mn0 : a_k0, ay = p_a_mn ? a_k0 : a_mn0;
+          int bx = p_b_mn ? b_mn0 : b_k0, by = p_b_mn ? b_k0 : b_mn0;
           if (P.trace && cta == 0 && tr_n < 60) P.trace[0 * 256 + tr_n * 4 + 0] = globaltimer_ns();
           for (int kb = 0; kb < kblocks; ++kb) {
-            if (!mbar_wait(&ctl->empty[stage], phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
-            uint8_t* sa = tiles + stage * kStageBytes;
-            uint8_t* sb = sa + kABytes;
-            issued[stage] = true;
-            issued_parity[stage] = phase;
-            const int k0 = kb * kBK;
+            if (!mbar_wait_s(empty_s + stage * 8, phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
+            const uint32_t sa = tiles_s + stage * kStageBytes;
+            const uint32_t sb = sa + kABytes;
+            issued_mask |= 1u << stage;
+            issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
             if (PAIR) {
               // both CTAs of the pair post their bytes on the LEADER's barrier; copies land in the issuing CTA's smem
-              const uint32_t lbar = mapa_u32(smem_u32(&ctl->full[stage]), 0);
+              const uint32_t lbar = lead_full_s + stage * 8;
               mbar_arrive_expect_tx_cluster(lbar, tx);
-              if (!p_a_mn) {
-                tma_load_2d_pair(sa, ma, k0 + a_k0, a_mn0, lbar);
-              } else {
-                tma_load_2d_pair(sa, ma, a_mn0, k0 + a_k0, lbar);
-                tma_load_2d_pair(sa + 8192, ma, a_mn0 + 64, k0 + a_k0, lbar);
-              }
-              if (!p_b_mn) {
-                for (int i = 0; i < bn_local / p_b_box; ++i)
-                  tma_load_2d_pair(sb + i * p_b_box * 128, mb, k0 + b_k0, b_mn0 + i * p_b_box, lbar);
-              } else {
-                for (int i = 0; i < bn_local / 64; ++i)
-                  tma_load_2d_pair(sb + i * 8192, mb, b_mn0 + i * 64, k0 + b_k0, lbar);
-              }
+              tma_load_2d_pair_s(sa, ma, ax, ay, lbar);
+              if (na == 2) tma_load_2d_pair_s(sa + 8192, ma, ax + 64, ay, lbar);
+              for (int i = 0; i < nb; ++i) tma_load_2d_pair_s(sb + i * b_ismem, mb, bx + i * b_ix, by + i * b_iy, lbar);
             } else {
-              mbar_arrive_expect_tx(&ctl->full[stage], tx);
-              if (!p_a_mn) {
-                tma_load_2d(sa, ma, k0 + a_k0, a_mn0, &ctl->full[stage]);
-              } else {
-                tma_load_2d(sa, ma, a_mn0, k0 + a_k0, &ctl->full[stage]);
-                tma_load_2d(sa + 8192, ma, a_mn0 + 64, k0 + a_k0, &ctl->full[stage]);
-              }
-              if (!p_b_mn) {
-                for (int i = 0; i < p_bn / p_b_box; ++i)
-                  tma_load_2d(sb + i * p_b_box * 128, mb, k0 + b_k0, b_mn0 + i * p_b_box, &ctl->full[stage]);
-              } else {
-                for (int i = 0; i < p_bn / 64; ++i)
-                  tma_load_2d(sb + i * 8192, mb, b_mn0 + i * 64, k0 + b_k0, &ctl->full[stage]);
-              }
+              const uint32_t bar = full_s + stage * 8;
+              mbar_arrive_expect_tx_s(bar, tx);
+              tma_load_2d_s(sa, ma, ax, ay, bar);
+              if (na == 2) tma_load_2d_s(sa + 8192, ma, ax + 64, ay, bar);
+              for (int i = 0; i < nb; ++i) tma_load_2d_s(sb + i * b_ismem, mb, bx + i * b_ix, by + i * b_iy, bar);
             }
+            ax += a_dx; ay += a_dy; bx += b_dx; by += b_dy;
             if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
           if (P.trace && cta == 0 && tr_n < 60) P.trace[0 * 256 + tr_n * 4 + 1] = globaltimer_ns();
@@ -220,9 +213,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           while (globaltimer_ns() - t0 < 200000ull) { }
         } else {
           for (int s = 0; s < kStages; ++s) {
-            if (!issued[s]) continue;
+            if (!((issued_mask >> s) & 1u)) continue;
             unsigned long long t0 = globaltimer_ns();
-            while (!mbar_try_wait(&ctl->full[s], issued_parity[s])) {
+            while (!mbar_try_wait(&ctl->full[s], (issued_parity >> s) & 1u)) {
               if (globaltimer_ns() - t0 > 2000000ull) break;
             }
           }
@@ -231,7 +224,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
-    if (lane == 0 && crank == 0) {     // in a pair only the leader issues; its UMMAs drive both SMs
+    if (crank == 0 && elect_one()) {     // in a pair only the leader issues; its UMMAs drive both SMs
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -239,6 +232,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       bool ok = true;
       bool issued_any = false;
       int tr_m = 0;
+      const uint32_t tiles_s = smem_u32(tiles);
+      const uint32_t full_s = smem_u32(&ctl->full[0]);
       for (int p = 0; p < P.n_phases && ok; ++p) {
         const RtpPhase& ph = P.phases[p];
         const int tiles_m = (ph.M + TM - 1) / TM;
@@ -248,7 +243,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const int kblocks_full = (ph.K + kBK - 1) / kBK;
         const uint32_t idesc = make_idesc_bf16(TM, ph.bn, ph.a_mn, ph.b_mn);
         const uint32_t a_lbo = ph.a_mn ? 8192u : 16u, b_lbo = ph.b_mn ? 8192u : 16u;
-        const uint32_t a_kstep = ph.a_mn ? 2048u : 32u, b_kstep = ph.b_mn ? 2048u : 32u;
+        const uint32_t a_kstep16 = ph.a_mn ? 128u : 2u, b_kstep16 = ph.b_mn ? 128u : 2u;   // k-step of 16 elements, in 16-byte units
+        const uint64_t da0 = make_smem_desc(0, a_lbo, 1024), db0 = make_smem_desc(0, b_lbo, 1024);
         for (int t = (unit - ph.cta_off + GU) % GU; t < total && ok; t += GU) {
           const int tt = t % per_batch;
           const int m0 = (tt % tiles_m) * TM;
@@ -261,14 +257,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
           for (int kb = 0; kb < kblocks; ++kb) {
-            if (!mbar_wait(&ctl->full[stage], phase, abort_flag, status, timeout_ns)) { ok = false; break; }
+            if (!mbar_wait_s(full_s + stage * 8, phase, abort_flag, status, timeout_ns)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
-            const uint32_t sb = sa + kABytes;
+            const uint32_t sa = (tiles_s + stage * kStageBytes) >> 4;   // descriptors hold the address in 16-byte units
+            const uint32_t sb = sa + (kABytes >> 4);
 #pragma unroll
             for (int kk = 0; kk < kBK / 16; ++kk) {
-              const uint64_t da = make_smem_desc(sa + kk * a_kstep, a_lbo, 1024);
-              const uint64_t db = make_smem_desc(sb + kk * b_kstep, b_lbo, 1024);
+              const uint64_t da = da0 + (uint64_t)(sa + kk * a_kstep16);
+              const uint64_t db = db0 + (uint64_t)(sb + kk * b_kstep16);
               if (PAIR) umma_bf16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
               else umma_bf16(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
             }
@@ -422,6 +418,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const long long e_c_bo = ph.c_bo;
       const long long e_c_bi = ph.c_bi;
       const int e_cta_off = ph.cta_off;
+      // vector accesses of the straight-line path: operands 16-byte aligned (vec_ok), bias too, dropout index a multiple of 4
+      const bool e_fast_ok = e_vec_ok && (!e_bias || (reinterpret_cast<uintptr_t>(e_bias) & 15) == 0) &&
+                             (!e_drop_thresh || (e_N & 3) == 0);
       for (int t = (unit - e_cta_off + GU) % GU; t < total && ok; t += GU) {
         const int z = t / per_batch, tt = t % per_batch;
         const int m0u = (tt % tiles_m) * TM;
@@ -440,15 +439,102 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         if (tr_on) P.trace[2 * 256 + tr_e * 4 + 1] = globaltimer_ns();
         const int row = m0 + quad * 32 + lane;
         const bool row_ok = row < e_M;
-        const bool staged = !e_d_fp32 && e_vec_ok && (e_N & 7) == 0;
+        const bool interior = (m0 + kBM <= e_M) && (n0 + e_bn <= e_N);
+        const bool fast = interior && e_fast_ok;
+        const bool staged = !fast && !e_d_fp32 && e_vec_ok && (e_N & 7) == 0;
         uint8_t* stg = staging + (warp - 2) * (32 * kStagePitch);
         for (int cb = 0; cb < e_bn / 32; ++cb) {
           uint32_t r[32];
           __syncwarp();
+          const bool tr_cb = tr_on && tr_e == 1 && cb < 8;
+          if (tr_cb) P.trace[3 * 256 + cb * 4 + 0] = globaltimer_ns();
           tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256 + cb * 32), r);
           tmem_ld_wait();
+          if (tr_cb) P.trace[3 * 256 + cb * 4 + 1] = globaltimer_ns();
           const int col0 = n0 + cb * 32;
-          if (row_ok && col0 < e_N) {
+          if (fast) {
+            // Interior tile with 16-byte aligned operands: straight-line code on the whole 32-column chunk, one branch
+            // per epilogue feature.  (The per-group code below handles edges and unaligned operands.)
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * e_alpha;
+            if (e_c) {
+              if (e_c_fp32) {
+                const float4* cp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(e_c) + zoff_c +
+                                                                   (long long)row * e_ldc + col0);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  const float4 c = __ldcg(cp + q);
+                  v[4 * q] += c.x; v[4 * q + 1] += c.y; v[4 * q + 2] += c.z; v[4 * q + 3] += c.w;
+                }
+              } else {
+                const uint4* cp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e_c) + zoff_c +
+                                                                 (long long)row * e_ldc + col0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint4 c = __ldcg(cp + q);
+                  v[8 * q] += bf16_lo(c.x); v[8 * q + 1] += bf16_hi(c.x); v[8 * q + 2] += bf16_lo(c.y);
+                  v[8 * q + 3] += bf16_hi(c.y); v[8 * q + 4] += bf16_lo(c.z); v[8 * q + 5] += bf16_hi(c.z);
+                  v[8 * q + 6] += bf16_lo(c.w); v[8 * q + 7] += bf16_hi(c.w);
+                }
+              }
+            }
+            if (e_bias) {
+              const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e_bias) + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 b = __ldcg(bp + q);
+                v[8 * q] += bf16_lo(b.x); v[8 * q + 1] += bf16_hi(b.x); v[8 * q + 2] += bf16_lo(b.y);
+                v[8 * q + 3] += bf16_hi(b.y); v[8 * q + 4] += bf16_lo(b.z); v[8 * q + 5] += bf16_hi(b.z);
+                v[8 * q + 6] += bf16_lo(b.w); v[8 * q + 7] += bf16_hi(b.w);
+              }
+            }
+            if (e_act == 1) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
+            } else if (e_act == 2) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = 0.5f * v[i] * (1.f + erff(v[i] * 0.70710678118654752f));
+            }
+            if (e_mask) {
+              const uint4* mp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e_mask) +
+                                                               (long long)row * e_ldmask + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 m = __ldcg(mp + q);
+                const uint32_t mw[4] = {m.x, m.y, m.z, m.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  v[8 * q + 2 * i] = bf16_lo(mw[i]) > 0.f ? v[8 * q + 2 * i] * e_mask_scale : 0.f;
+                  v[8 * q + 2 * i + 1] = bf16_hi(mw[i]) > 0.f ? v[8 * q + 2 * i + 1] * e_mask_scale : 0.f;
+                }
+              }
+            }
+            if (e_drop_thresh) {
+              const unsigned long long e4 =
+                  ((unsigned long long)row * (unsigned long long)e_N + (unsigned long long)col0) >> 2;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const uint4 rr = philox4x32(e_drop_seed, drop_off, e4 + q);
+                v[4 * q] = rr.x >= e_drop_thresh ? v[4 * q] * e_drop_scale : 0.f;
+                v[4 * q + 1] = rr.y >= e_drop_thresh ? v[4 * q + 1] * e_drop_scale : 0.f;
+                v[4 * q + 2] = rr.z >= e_drop_thresh ? v[4 * q + 2] * e_drop_scale : 0.f;
+                v[4 * q + 3] = rr.w >= e_drop_thresh ? v[4 * q + 3] * e_drop_scale : 0.f;
+              }
+            }
+            if (e_d_fp32) {
+              float4* dp = reinterpret_cast<float4*>(reinterpret_cast<float*>(e_d) + zoff_d + (long long)row * e_ldd + col0);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) dp[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+              uint8_t* sp = stg + lane * kStagePitch + (cb & 1) * 64;
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                *reinterpret_cast<uint4*>(sp + q * 16) =
+                    make_uint4(pack_bf16(v[8 * q], v[8 * q + 1]), pack_bf16(v[8 * q + 2], v[8 * q + 3]),
+                               pack_bf16(v[8 * q + 4], v[8 * q + 5]), pack_bf16(v[8 * q + 6], v[8 * q + 7]));
+            }
+          } else if (row_ok && col0 < e_N) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {  // groups of 8 columns
             const int col = col0 + g * 8;
@@ -545,8 +631,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             }
           }
           }
-          if (staged && (cb & 1)) {
+          if (tr_cb) P.trace[3 * 256 + cb * 4 + 2] = globaltimer_ns();
+          if (fast && !e_d_fp32 && (cb & 1)) {
             // coalesced write-out of 32 rows x 64 columns: 8 lanes cover one row's 128 bytes, 4 rows per instruction
+            __syncwarp();
+            __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(e_d) + zoff_d +
+                                (long long)(m0 + quad * 32 + (lane >> 3)) * e_ldd + n0 + (cb - 1) * 32 + (lane & 7) * 8;
+            const uint8_t* sp = stg + (lane >> 3) * kStagePitch + (lane & 7) * 16;
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              *reinterpret_cast<uint4*>(dp + (long long)(k * 4) * e_ldd) =
+                  *reinterpret_cast<const uint4*>(sp + k * 4 * kStagePitch);
+            __syncwarp();
+          } else if (staged && (cb & 1)) {
             __syncwarp();
             const int pair_col0 = n0 + (cb - 1) * 32;
             __nv_bfloat16* dbase = reinterpret_cast<__nv_bfloat16*>(e_d) + zoff_d;
@@ -562,6 +659,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             }
             __syncwarp();
           }
+          if (tr_cb) P.trace[3 * 256 + cb * 4 + 3] = globaltimer_ns();
         }
         tc_fence_before();
         __syncwarp();
