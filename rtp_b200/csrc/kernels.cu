@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(
     const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
     __nv_bfloat16* __restrict__ dsub, float* __restrict__ dgamma, float* __restrict__ dbeta, int M, int D, int rms,
     uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset, const __nv_bfloat16* __restrict__ dres,
-    const unsigned long long* __restrict__ step_ptr) {
+    const unsigned long long* __restrict__ step_ptr, int vec_atomics) {
   __shared__ float2 red[32];
   if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   float g[NG][8], pg[NG][8], pb[NG][8];
@@ -194,6 +194,18 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(
     if (c < D) unpack8(*reinterpret_cast<const uint4*>(gamma + c), g[q]);
 #pragma unroll
     for (int i = 0; i < 8; ++i) { pg[q][i] = 0.f; pb[q][i] = 0.f; }
+  }
+  // raw rows are fetched one row ahead, so that the loads of row i+1 are in flight during the block reduction of row i
+  uint4 nd[NG], nh[NG];
+  if (blockIdx.x < M) {
+#pragma unroll
+    for (int q = 0; q < NG; ++q) {
+      const int c = (q * 256 + threadIdx.x) * 8;
+      if (c < D) {
+        nd[q] = __ldcs(reinterpret_cast<const uint4*>(dy + (size_t)blockIdx.x * D + c));
+        nh[q] = __ldcs(reinterpret_cast<const uint4*>(h + (size_t)blockIdx.x * D + c));
+      }
+    }
   }
   for (int row = blockIdx.x; row < M; row += gridDim.x) {
     const size_t base = (size_t)row * D;
@@ -206,8 +218,8 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(
       const int c = (q * 256 + threadIdx.x) * 8;
       if (c < D) {
         float hv[8];
-        unpack8(__ldcs(reinterpret_cast<const uint4*>(dy + base + c)), d[q]);
-        unpack8(__ldcs(reinterpret_cast<const uint4*>(h + base + c)), hv);
+        unpack8(nd[q], d[q]);
+        unpack8(nh[q], hv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           xh[q][i] = (hv[i] - mean) * rstd;
@@ -216,6 +228,17 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(
           s2 += dg * xh[q][i];
           pg[q][i] += d[q][i] * xh[q][i];
           pb[q][i] += d[q][i];
+        }
+      }
+    }
+    const int nrow = row + gridDim.x;
+    if (nrow < M) {
+#pragma unroll
+      for (int q = 0; q < NG; ++q) {
+        const int c = (q * 256 + threadIdx.x) * 8;
+        if (c < D) {
+          nd[q] = __ldcs(reinterpret_cast<const uint4*>(dy + (size_t)nrow * D + c));
+          nh[q] = __ldcs(reinterpret_cast<const uint4*>(h + (size_t)nrow * D + c));
         }
       }
     }
@@ -252,10 +275,20 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(
   for (int q = 0; q < NG; ++q) {
     const int c = (q * 256 + threadIdx.x) * 8;
     if (c < D) {
+      if (!vec_atomics) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        atomicAdd(dgamma + c + i, pg[q][i]);
-        if (dbeta) atomicAdd(dbeta + c + i, pb[q][i]);
+        for (int i = 0; i < 8; ++i) {
+          atomicAdd(dgamma + c + i, pg[q][i]);
+          if (dbeta) atomicAdd(dbeta + c + i, pb[q][i]);
+        }
+        continue;
+      }
+      // 16-byte vector reductions: four columns per atomic
+      atomicAdd(reinterpret_cast<float4*>(dgamma + c), make_float4(pg[q][0], pg[q][1], pg[q][2], pg[q][3]));
+      atomicAdd(reinterpret_cast<float4*>(dgamma + c + 4), make_float4(pg[q][4], pg[q][5], pg[q][6], pg[q][7]));
+      if (dbeta) {
+        atomicAdd(reinterpret_cast<float4*>(dbeta + c), make_float4(pb[q][0], pb[q][1], pb[q][2], pb[q][3]));
+        atomicAdd(reinterpret_cast<float4*>(dbeta + c + 4), make_float4(pb[q][4], pb[q][5], pb[q][6], pb[q][7]));
       }
     }
   }
@@ -912,15 +945,16 @@ int rtp_norm_bwd(const void* dy, const void* h, const void* gamma, const float* 
                  unsigned long long seed, unsigned long long offset, const void* dres,
                  const unsigned long long* step_ptr, void* stream) {
   if (D % 8 || D > 8192) { k_err = "norm: D must be a multiple of 8 and at most 8192"; return -1; }
-  int grid = 148 * 4;
+  int grid = 148 * 2;   // few blocks: every block ends with one vector atomic per 4 columns of dgamma / dbeta
   if (grid > M) grid = M;
   const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
   const int ng = (D + 2047) / 2048;
+  const int vec_atomics = ((reinterpret_cast<uintptr_t>(dgamma) | reinterpret_cast<uintptr_t>(dbeta)) & 15) == 0;
 #define RTP_NORM_BWD(NG)                                                                                              \
   norm_bwd_kernel<NG><<<grid, 256, 0, (cudaStream_t)stream>>>(                                                       \
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)gamma, mean, rstd, (__nv_bfloat16*)dx, \
       (__nv_bfloat16*)dsub, dgamma, dbeta, M, D, rms, host_thresh(drop_p), ds, seed, offset,                          \
-      (const __nv_bfloat16*)dres, step_ptr)
+      (const __nv_bfloat16*)dres, step_ptr, vec_atomics)
   if (ng == 1) RTP_NORM_BWD(1); else if (ng == 2) RTP_NORM_BWD(2); else if (ng == 3) RTP_NORM_BWD(3); else RTP_NORM_BWD(4);
 #undef RTP_NORM_BWD
   LAUNCH_CHECK("norm_bwd");
@@ -965,6 +999,8 @@ int rtp_embed_bwd(void* gtable, const long long* ids, const void* dy, long long 
   LAUNCH_CHECK("embed_bwd");
   return 0;
 }
+static int g_attn_tc = 1;
+void rtp_set_attn_tc(int on) { g_attn_tc = on ? 1 : 0; }
 static size_t attn_smem(int S, bool bwd) {
   size_t f = (size_t)(bwd ? 4 : 3) * S * 65 + (size_t)(bwd ? 2 : 1) * S * (S + 1);
   return f * sizeof(float);
@@ -972,6 +1008,11 @@ static size_t attn_smem(int S, bool bwd) {
 int rtp_attn_small_fwd(const void* qkv, void* out, int S, int B, int heads, int nshard, int causal, float sm_scale,
                        float drop_p, unsigned long long seed, unsigned long long offset,
                        const unsigned long long* step_ptr, void* stream) {
+  if (g_attn_tc && rtp_attn_tc_supported(S, heads, nshard)) {
+    const int rc = rtp_attn_tc_fwd(qkv, out, S, B, heads, nshard, causal, sm_scale, drop_p, seed, offset, step_ptr, stream);
+    if (rc) k_err = rtp_attn_tc_last_error();
+    return rc;
+  }
   if (S > 128 || heads % nshard) { k_err = "attn_small: S must be <= 128 and heads divisible by shards"; return -1; }
   const size_t smem = attn_smem(S, false);
   if (smem > 48 * 1024) {
@@ -988,6 +1029,12 @@ int rtp_attn_small_fwd(const void* qkv, void* out, int S, int B, int heads, int 
 int rtp_attn_small_bwd(const void* qkv, const void* dout, void* dqkv, int S, int B, int heads, int nshard, int causal,
                        float sm_scale, float drop_p, unsigned long long seed, unsigned long long offset,
                        const unsigned long long* step_ptr, void* stream) {
+  if (g_attn_tc && rtp_attn_tc_supported(S, heads, nshard)) {
+    const int rc = rtp_attn_tc_bwd(qkv, dout, dqkv, S, B, heads, nshard, causal, sm_scale, drop_p, seed, offset, step_ptr,
+                                   stream);
+    if (rc) k_err = rtp_attn_tc_last_error();
+    return rc;
+  }
   if (heads % nshard) { k_err = "attn_small: heads must be divisible by shards"; return -1; }
   const size_t smem = attn_smem(S, true);
   if (smem > 227 * 1024) { k_err = "attn_small backward: sequence too long for shared memory (S <= 96)"; return -1; }

@@ -32,6 +32,18 @@ int rtp_embed_fwd(const void* table, const long long* ids, const void* pe, long 
 int rtp_embed_bwd(void* gtable, const long long* ids, const void* dy, long long ld_dy, int col_off, int T, int Ds,
                   int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset,
                   const unsigned long long* step_ptr, void* stream);
+// Tensor-core (tcgen05) kernels for S = 32 / 64, head_dim 64 (attn_tc.cu); rtp_attn_small_* route to them when they
+// apply.  rtp_set_attn_tc(0) forces the scalar kernels (A/B comparison).
+int rtp_attn_tc_supported(int S, int heads, int nshard);
+int rtp_attn_tc_error(void);
+const char* rtp_attn_tc_last_error(void);
+void rtp_set_attn_tc(int on);
+int rtp_attn_tc_fwd(const void* qkv, void* out, int S, int B, int heads, int nshard, int causal, float sm_scale,
+                    float drop_p, unsigned long long seed, unsigned long long offset,
+                    const unsigned long long* step_ptr, void* stream);
+int rtp_attn_tc_bwd(const void* qkv, const void* dout, void* dqkv, int S, int B, int heads, int nshard, int causal,
+                    float sm_scale, float drop_p, unsigned long long seed, unsigned long long offset,
+                    const unsigned long long* step_ptr, void* stream);
 int rtp_attn_small_fwd(const void* qkv, void* out, int S, int B, int heads, int nshard, int causal, float sm_scale,
                        float drop_p, unsigned long long seed, unsigned long long offset,
                        const unsigned long long* step_ptr, void* stream);

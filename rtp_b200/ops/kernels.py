@@ -28,6 +28,9 @@ def _L():
         L.rtp_embed_bwd.argtypes = [vp, vp, vp, ll, i, i, i, i, f, f, ull, ull, vp, vp]
         L.rtp_attn_small_fwd.argtypes = [vp, vp, i, i, i, i, i, f, f, ull, ull, vp, vp]
         L.rtp_attn_small_bwd.argtypes = [vp, vp, vp, i, i, i, i, i, f, f, ull, ull, vp, vp]
+        L.rtp_set_attn_tc.argtypes = [i]
+        L.rtp_set_attn_tc.restype = None
+        L.rtp_attn_tc_error.restype = i
         L.rtp_colsum.argtypes = [vp, ll, i, i, vp, vp]
         L.rtp_adam.argtypes = [vp, vp, i, i, vp, f, f, f, f, f, i, f, f, vp]
         L.rtp_add.argtypes = [vp, vp, vp, ll, vp]
@@ -139,6 +142,16 @@ def attn_small_bwd(qkv, dout, S, B, heads, *, nshard=1, causal=True, drop_p=0.0,
     _check(_L().rtp_attn_small_bwd(_p(qkv), _p(dout), _p(dqkv), S, B, heads, nshard, int(causal), sc, float(drop_p),
                                    seed, offset, _p(step), _lib.stream_ptr()), "attn_small_bwd")
     return dqkv
+
+
+def set_attn_tc(on):
+    """Route S = 32 / 64 attention to the tcgen05 kernels (default) or to the scalar kernels (A/B comparison)."""
+    _L().rtp_set_attn_tc(int(bool(on)))
+
+
+def attn_tc_error():
+    """1 if a bounded wait inside a tcgen05 attention kernel ran out since the last call (synchronises)."""
+    return int(_L().rtp_attn_tc_error())
 
 
 def colsum(x, out=None):

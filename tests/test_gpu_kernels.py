@@ -114,6 +114,29 @@ def test_attention_small(S, B, H, N):
     _close(dqkv, torch.cat(gparts, 1), 2e-2)
 
 
+@pytest.mark.parametrize("S,B,H,N,causal,p", [(32, 3, 5, 1, True, 0.0), (32, 5, 6, 2, False, 0.1), (64, 3, 3, 1, True, 0.1),
+                                              (32, 32, 32, 8, True, 0.1)])
+def test_attention_tensor_core_kernels_match_scalar_kernels(S, B, H, N, causal, p):
+    """The tcgen05 kernels (S = 32 / 64) and the scalar kernels share the layout and the dropout stream."""
+    from rtp_b200.ops import kernels as K
+    torch.manual_seed(1)
+    qkv = torch.randn(S * B, 3 * H * 64, device="cuda", dtype=BF)
+    do = torch.randn(S * B, H * 64, device="cuda", dtype=BF)
+    kw = dict(nshard=N, causal=causal, drop_p=p, seed=11, offset=5)
+    try:
+        K.set_attn_tc(False)
+        o_ref = K.attn_small_fwd(qkv, S, B, H, **kw)
+        g_ref = K.attn_small_bwd(qkv, do, S, B, H, **kw)
+    finally:
+        K.set_attn_tc(True)
+    o = K.attn_small_fwd(qkv, S, B, H, **kw)
+    g = K.attn_small_bwd(qkv, do, S, B, H, **kw)
+    torch.cuda.synchronize()
+    assert K.attn_tc_error() == 0
+    _close(o, o_ref, 2e-2)
+    _close(g, g_ref, 3e-2)
+
+
 def test_colsum_and_adam():
     from rtp_b200.ops import kernels as K
     torch.manual_seed(0)
