@@ -155,7 +155,7 @@ void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i);
 void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i);
 int rtp_sm_count(void);
 const char* rtp_last_error(void);
-void rtp_set_pair_mode(int on);        // 1: CTA pairs (cta_group::2 UMMA, half of the B tile per SM); default from env RTP_PAIR
+void rtp_set_pair_mode(int on);        // CTA pairs (cta_group::2 UMMA, half of the B tile per SM): 1 always, 0 never, -1 automatic (default; env RTP_PAIR=0/1 overrides)
 void rtp_debug_set_trace(unsigned long long* device_buffer_1024_words);  // tuning aid: globaltimer timeline of CTA 0 of rtp_gemm launches (null = off)
 void rtp_debug_force_stages(int n);   // tuning aid: cap the smem pipeline depth (0 = automatic)
 

@@ -23,6 +23,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.h"
 
 namespace {
 using namespace rtp;
@@ -31,7 +32,9 @@ constexpr int kHd = 64;
 constexpr int kRows = 128;                 // stacked rows per CTA
 constexpr int kTile = kRows * 128;         // one [128 x 64] bf16 operand tile, 128-byte rows: 16 KB
 
-__device__ unsigned int g_attn_tc_error;   // set when a bounded wait for the CTA's own UMMAs ran out
+__device__ unsigned int g_attn_tc_error;
+__device__ unsigned long long* g_attn_trace;   // tuning aid: timeline of CTA 0 (16 words), null = off
+#define ATT_STAMP(i) do { if (g_attn_trace && blockIdx.x == 0 && threadIdx.x == 0) g_attn_trace[i] = globaltimer_ns(); } while (0)   // set when a bounded wait for the CTA's own UMMAs ran out
 
 struct Ctl {
   uint64_t bar[2];
@@ -69,19 +72,29 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 __device__ __forceinline__ float lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
 
-// Stacks rows [q * S_T + s] = token (s, b_q), columns col[q] .. col[q] + 64 of `src` (row pitch ld) into a swizzled tile.
+// Stacks rows [q * S_T + s] = token (s, b_q), columns col[q] .. col[q] + 64 of `src` (row pitch ld) into swizzled tiles.
+// A thread's eight 16-byte loads per tile are all issued before the first shared-memory store, so that they overlap
+// (a store in between would order them: the compiler cannot prove that the tile and the control block do not alias).
+struct HeadRef {
+  int valid, b, col;
+};
 template <int S_T>
-__device__ __forceinline__ void load_stack(uint8_t* dst, const __nv_bfloat16* __restrict__ src, long long ld, int B,
-                                           const Ctl* ctl, const int* col, int tid) {
+__device__ __forceinline__ void fetch_stack(uint4 (&v)[8], const __nv_bfloat16* __restrict__ src, long long ld, int B,
+                                            const HeadRef (&hr)[kRows / S_T], int tid) {
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int i = it * 128 + tid;
     const int row = i >> 3, c = i & 7;
     const int q = row / S_T, s = row % S_T;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (ctl->valid[q])
-      v = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(s * B + ctl->b[q]) * ld + col[q] + c * 8));
-    *reinterpret_cast<uint4*>(dst + sw128(row, c)) = v;
+    v[it] = make_uint4(0u, 0u, 0u, 0u);
+    if (hr[q].valid) v[it] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(s * B + hr[q].b) * ld + hr[q].col + c * 8));
+  }
+}
+__device__ __forceinline__ void store_stack(uint8_t* dst, const uint4 (&v)[8], int tid) {
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int i = it * 128 + tid;
+    *reinterpret_cast<uint4*>(dst + sw128(i >> 3, i & 7)) = v[it];
   }
 }
 
@@ -90,6 +103,7 @@ __device__ __forceinline__ void setup(Ctl* ctl, int tid, int warp, int B, int he
                                       uint32_t tmem_cols) {
   constexpr int HPC = kRows / S_T;
   const int D = heads * kHd;
+  pdl_launch_dependents();
   if (tid < HPC) {
     const int bh = blockIdx.x * HPC + tid;
     const int ok = bh < n_bh;
@@ -113,6 +127,7 @@ __device__ __forceinline__ void setup(Ctl* ctl, int tid, int warp, int B, int he
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();   // set-up touched shared memory and TMEM only; the loads below need the previous kernel's output
 }
 
 // Row t of the score matrix out of TMEM, scaled; masked entries become -inf.
@@ -143,16 +158,32 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const __nv_bfloat16* _
   uint8_t* sP = sm + 3 * kTile;
   Ctl* ctl = reinterpret_cast<Ctl*>(sm + 4 * kTile);
   const int tid = threadIdx.x, warp = tid >> 5;
-  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   const int D = heads * kHd;
+  ATT_STAMP(0);
   setup<S_T>(ctl, tid, warp, B, heads, nshard, n_bh, 256);
+  ATT_STAMP(1);
+  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   const uint32_t tmem = ctl->tmem_base;
 
-  load_stack<S_T>(sQ, qkv, 3 * D, B, ctl, ctl->cq, tid);
-  load_stack<S_T>(sK, qkv, 3 * D, B, ctl, ctl->ck, tid);
-  load_stack<S_T>(sV, qkv, 3 * D, B, ctl, ctl->cv, tid);
+  {
+    HeadRef hq[HPC], hk[HPC], hv[HPC];
+#pragma unroll
+    for (int qq = 0; qq < HPC; ++qq) {
+      hq[qq] = {ctl->valid[qq], ctl->b[qq], ctl->cq[qq]};
+      hk[qq] = {ctl->valid[qq], ctl->b[qq], ctl->ck[qq]};
+      hv[qq] = {ctl->valid[qq], ctl->b[qq], ctl->cv[qq]};
+    }
+    uint4 va[8], vb[8], vc[8];
+    fetch_stack<S_T>(va, qkv, 3 * D, B, hq, tid);
+    fetch_stack<S_T>(vb, qkv, 3 * D, B, hk, tid);
+    fetch_stack<S_T>(vc, qkv, 3 * D, B, hv, tid);
+    store_stack(sQ, va, tid);
+    store_stack(sK, vb, tid);
+    store_stack(sV, vc, tid);
+  }
   fence_proxy_async();
   __syncthreads();
+  ATT_STAMP(2);
 
   if (warp == 0 && elect_one()) {
     const uint32_t idesc = make_idesc_bf16(128, S_T, 0, 0);
@@ -167,6 +198,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const __nv_bfloat16* _
   }
   wait_bar(&ctl->bar[0], 0);
   tc_fence_after();
+  ATT_STAMP(3);
 
   const int q = tid / S_T, s = tid % S_T;
   const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
@@ -206,9 +238,11 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const __nv_bfloat16* _
           make_uint4(pack2(x[8 * c8], x[8 * c8 + 1]), pack2(x[8 * c8 + 2], x[8 * c8 + 3]),
                      pack2(x[8 * c8 + 4], x[8 * c8 + 5]), pack2(x[8 * c8 + 6], x[8 * c8 + 7]));
   }
+  ATT_STAMP(4);
   fence_proxy_async();
   tc_fence_before();
   __syncthreads();   // every row of S has been read: its TMEM columns are reused for O
+  ATT_STAMP(5);
 
   if (warp == 0 && elect_one()) {
     tc_fence_after();
@@ -224,6 +258,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const __nv_bfloat16* _
   }
   wait_bar(&ctl->bar[1], 0);
   tc_fence_after();
+  ATT_STAMP(6);
   {
     float o[kHd];
     load_row<kHd>(lane_addr + q * kHd, o);
@@ -235,12 +270,14 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const __nv_bfloat16* _
                              pack2(o[8 * c8 + 4], o[8 * c8 + 5]), pack2(o[8 * c8 + 6], o[8 * c8 + 7]));
     }
   }
+  ATT_STAMP(7);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem, 256);
   }
+  ATT_STAMP(8);
 }
 
 template <int S_T>
@@ -262,35 +299,38 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const __nv_bfloat16* _
   uint8_t* sTP = sm + 7 * kTile;           // P_drop^T, same form: 32 KB
   Ctl* ctl = reinterpret_cast<Ctl*>(sm + 9 * kTile);
   const int tid = threadIdx.x, warp = tid >> 5;
-  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   const int D = heads * kHd;
+  ATT_STAMP(0);
   setup<S_T>(ctl, tid, warp, B, heads, nshard, n_bh, 512);
+  ATT_STAMP(1);
+  if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   const uint32_t tmem = ctl->tmem_base;
 
-  // the off-diagonal blocks of the transposed operands stay zero
-#pragma unroll 4
-  for (int i = tid; i < 4 * kTile / 16; i += 128) reinterpret_cast<uint4*>(sTS)[i] = make_uint4(0u, 0u, 0u, 0u);
-  load_stack<S_T>(sQ, qkv, 3 * D, B, ctl, ctl->cq, tid);
-  load_stack<S_T>(sK, qkv, 3 * D, B, ctl, ctl->ck, tid);
-  load_stack<S_T>(sV, qkv, 3 * D, B, ctl, ctl->cv, tid);
   {
-    // dO has [T, D] layout: column of head h is h * 64
-    int cg[4];
+    HeadRef hq[HPC], hk[HPC], hv[HPC], hg[HPC];
 #pragma unroll
-    for (int qq = 0; qq < HPC; ++qq) cg[qq] = ctl->h[qq] * kHd;
-#pragma unroll
-    for (int it = 0; it < 8; ++it) {
-      const int i = it * 128 + tid;
-      const int row = i >> 3, c = i & 7;
-      const int qq = row / S_T, ss = row % S_T;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (ctl->valid[qq])
-        v = __ldg(reinterpret_cast<const uint4*>(dout + (size_t)(ss * B + ctl->b[qq]) * D + cg[qq] + c * 8));
-      *reinterpret_cast<uint4*>(sG + sw128(row, c)) = v;
+    for (int qq = 0; qq < HPC; ++qq) {
+      hq[qq] = {ctl->valid[qq], ctl->b[qq], ctl->cq[qq]};
+      hk[qq] = {ctl->valid[qq], ctl->b[qq], ctl->ck[qq]};
+      hv[qq] = {ctl->valid[qq], ctl->b[qq], ctl->cv[qq]};
+      hg[qq] = {ctl->valid[qq], ctl->b[qq], ctl->h[qq] * kHd};   // dO has [T, D] layout: column of head h is h * 64
     }
+    uint4 va[8], vb[8], vc[8], vd[8];
+    fetch_stack<S_T>(va, qkv, 3 * D, B, hq, tid);
+    fetch_stack<S_T>(vb, qkv, 3 * D, B, hk, tid);
+    fetch_stack<S_T>(vc, qkv, 3 * D, B, hv, tid);
+    fetch_stack<S_T>(vd, dout, D, B, hg, tid);
+    // the off-diagonal blocks of the transposed operands stay zero (filled while the loads are in flight)
+#pragma unroll 4
+    for (int i = tid; i < 4 * kTile / 16; i += 128) reinterpret_cast<uint4*>(sTS)[i] = make_uint4(0u, 0u, 0u, 0u);
+    store_stack(sQ, va, tid);
+    store_stack(sK, vb, tid);
+    store_stack(sV, vc, tid);
+    store_stack(sG, vd, tid);
   }
   fence_proxy_async();
   __syncthreads();
+  ATT_STAMP(2);
 
   if (warp == 0 && elect_one()) {
     const uint32_t idesc = make_idesc_bf16(128, S_T, 0, 0);
@@ -311,6 +351,7 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const __nv_bfloat16* _
   }
   wait_bar(&ctl->bar[0], 0);
   tc_fence_after();
+  ATT_STAMP(3);
 
   const int q = tid / S_T, s = tid % S_T;
   const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
@@ -375,9 +416,11 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const __nv_bfloat16* _
       *reinterpret_cast<uint4*>(tp + sw128(kr, cb + c8)) = vp;
     }
   }
+  ATT_STAMP(4);
   fence_proxy_async();
   tc_fence_before();
   __syncthreads();   // S and dP have been read everywhere: their TMEM columns are reused for dQ
+  ATT_STAMP(5);
 
   if (warp == 0 && elect_one()) {
     tc_fence_after();
@@ -402,6 +445,7 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const __nv_bfloat16* _
   }
   wait_bar(&ctl->bar[1], 0);
   tc_fence_after();
+  ATT_STAMP(6);
   if (ctl->valid[q]) {
     __nv_bfloat16* rowp = dqkv + (size_t)(s * B + ctl->b[q]) * (3 * D);
     float o[kHd];
@@ -434,12 +478,14 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const __nv_bfloat16* _
     load_row<kHd>(lane_addr + 256, o);
     load_row<kHd>(lane_addr + 320, o);
   }
+  ATT_STAMP(7);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+  ATT_STAMP(8);
 }
 
 std::string g_err;
@@ -466,6 +512,11 @@ extern "C" {
 
 const char* rtp_attn_tc_last_error(void) { return g_err.c_str(); }
 
+// tuning aid: device buffer of 16 words that receives globaltimer stamps of CTA 0 (null switches it off)
+int rtp_attn_tc_set_trace(unsigned long long* device_buffer) {
+  return cudaMemcpyToSymbol(g_attn_trace, &device_buffer, sizeof(device_buffer)) == cudaSuccess ? 0 : -1;
+}
+
 int rtp_attn_tc_supported(int S, int heads, int nshard) { return (S == 32 || S == 64) && heads % nshard == 0; }
 
 // 1 if a bounded wait inside one of the kernels ran out since the last call (and clears the flag); synchronises.
@@ -487,13 +538,13 @@ int rtp_attn_tc_fwd(const void* qkv, void* out, int S, int B, int heads, int nsh
   if (S == 32) {
     static bool once = false;
     if (!once) { if (set_smem(attn_tc_fwd_kernel<32>, kFwdSmem)) return -1; once = true; }
-    attn_tc_fwd_kernel<32><<<grid, 128, kFwdSmem, (cudaStream_t)stream>>>(
+    rtp::launch_k(attn_tc_fwd_kernel<32>, dim3(grid), dim3(128), kFwdSmem, (cudaStream_t)stream, 
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, B, heads, nshard, causal, sm_scale, thresh_of(drop_p), ds, seed,
         offset, step_ptr, n_bh);
   } else {
     static bool once = false;
     if (!once) { if (set_smem(attn_tc_fwd_kernel<64>, kFwdSmem)) return -1; once = true; }
-    attn_tc_fwd_kernel<64><<<grid, 128, kFwdSmem, (cudaStream_t)stream>>>(
+    rtp::launch_k(attn_tc_fwd_kernel<64>, dim3(grid), dim3(128), kFwdSmem, (cudaStream_t)stream, 
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, B, heads, nshard, causal, sm_scale, thresh_of(drop_p), ds, seed,
         offset, step_ptr, n_bh);
   }
@@ -513,13 +564,13 @@ int rtp_attn_tc_bwd(const void* qkv, const void* dout, void* dqkv, int S, int B,
   if (S == 32) {
     static bool once = false;
     if (!once) { if (set_smem(attn_tc_bwd_kernel<32>, kBwdSmem)) return -1; once = true; }
-    attn_tc_bwd_kernel<32><<<grid, 128, kBwdSmem, (cudaStream_t)stream>>>(
+    rtp::launch_k(attn_tc_bwd_kernel<32>, dim3(grid), dim3(128), kBwdSmem, (cudaStream_t)stream, 
         (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dqkv, B, heads, nshard, causal, sm_scale,
         thresh_of(drop_p), ds, seed, offset, step_ptr, n_bh);
   } else {
     static bool once = false;
     if (!once) { if (set_smem(attn_tc_bwd_kernel<64>, kBwdSmem)) return -1; once = true; }
-    attn_tc_bwd_kernel<64><<<grid, 128, kBwdSmem, (cudaStream_t)stream>>>(
+    rtp::launch_k(attn_tc_bwd_kernel<64>, dim3(grid), dim3(128), kBwdSmem, (cudaStream_t)stream, 
         (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dqkv, B, heads, nshard, causal, sm_scale,
         thresh_of(drop_p), ds, seed, offset, step_ptr, n_bh);
   }

@@ -18,6 +18,7 @@
 #include <cstdlib>
 #include "api.h"
 #include "gemm_kernel.cuh"
+#include "launch.h"
 
 namespace {
 
@@ -100,15 +101,25 @@ void set_vec_ok(RtpPhase& ph) {
   if (ph.mask) ok = ok && aligned16(ph.mask, ph.ldmask, 2);
   ph.vec_ok = ok ? 1 : 0;
 }
-// CTA-pair mode (cta_group::2): 0 = off, 1 = on for launches whose grid is even.  Default from RTP_PAIR.
-int g_pair = -1;
-bool pair_mode() {
-  if (g_pair < 0) {
+// CTA-pair mode (cta_group::2).  Policy: 1 = always (launches with an even grid), 0 = never, -1 = automatic: pairs are
+// used when the output has at least one 256 x 256 tile per CTA, which is where halving the B traffic per SM pays for
+// the cluster launch.  RTP_PAIR=0/1 or rtp_set_pair_mode() override; the decision is taken once per program, before
+// its tensor maps are built.
+int g_pair = -2;                 // -2: environment not read yet
+thread_local bool t_pair = false;
+int pair_policy() {
+  if (g_pair == -2) {
     const char* e = getenv("RTP_PAIR");
-    g_pair = (e && e[0] == '1') ? 1 : 0;
+    g_pair = (e && e[0] == '1') ? 1 : (e && e[0] == '0') ? 0 : -1;
   }
-  return g_pair == 1;
+  return g_pair;
 }
+void decide_pair(long long M, long long N, int ctas, bool eligible = true) {
+  const int pol = pair_policy();
+  const long long t256 = ((M + 255) / 256) * ((N + 255) / 256);
+  t_pair = eligible && (pol == 1 || (pol == -1 && M >= 512 && t256 >= ctas));
+}
+bool pair_mode() { return t_pair; }
 int pick_bn(int M, int N, int ctas) {
   if (pair_mode()) {
     long long t256 = (long long)((M + 255) / 256) * ((N + 255) / 256);
@@ -176,11 +187,16 @@ int launch_impl(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative,
   cfg.blockDim = dim3(rtp::kNumThreads);
   cfg.dynamicSmemBytes = rtp::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute at[2];
+  cudaLaunchAttribute at[3];
   int nat = 0;
   if (cooperative) {
     at[nat].id = cudaLaunchAttributeCooperative;
     at[nat].val.cooperative = 1;
+    ++nat;
+  } else if (rtp::pdl_enabled()) {
+    // the kernel waits for its predecessor (griddepcontrol.wait) after its shared-memory / TMEM set-up
+    at[nat].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[nat].val.programmaticStreamSerializationAllowed = 1;
     ++nat;
   }
   if (PAIR) {
@@ -675,6 +691,7 @@ int build_reduce_scatter(const RtpRing& R, const RtpReduceScatter& op, RtpProgra
 
 template <int NEMU, class Op, class Builder>
 int run_emu(const RtpRing* rings, const Op* ops, Builder build, cudaStream_t stream) {
+  decide_pair(0, 0, 0, false);   // emulated ranks share one cooperative launch without clusters
   static RtpProgram progs[RTP_MAX_EMU_RANKS];
   static rtp::GemmParams<NEMU> params;
   for (int e = 0; e < NEMU; ++e) {
@@ -697,7 +714,7 @@ extern "C" {
 
 const char* rtp_last_error(void) { return g_err.c_str(); }
 void rtp_debug_force_stages(int n) { g_force_stages = n; }
-void rtp_set_pair_mode(int on) { g_pair = on ? 1 : 0; }
+void rtp_set_pair_mode(int on) { g_pair = on < 0 ? -1 : (on ? 1 : 0); }
 unsigned long long* g_trace = nullptr;
 void rtp_debug_set_trace(unsigned long long* device_buffer_1024_words) { g_trace = device_buffer_1024_words; }
 int rtp_sm_count(void) { return sm_count(); }
@@ -710,6 +727,7 @@ int rtp_gemm(const RtpGemmArgs* a, void* stream) {
   if (a->a_mn ? make_map_mn(&P.maps[0], a->a, a->M, a->K, a->lda) : make_map_k(&P.maps[0], a->a, a->M, a->K, a->lda))
     return -1;
   const int ctas = a->num_ctas > 0 ? a->num_ctas : sm_count();
+  decide_pair(a->M, a->N, ctas);
   const int bn_sel = a->bn ? a->bn : pick_bn(a->M, a->N, ctas);
   if (bn_sel != 128 && bn_sel != 256) return fail("bn must be 128 or 256");
   const bool pair = pair_mode();
@@ -780,6 +798,7 @@ int rtp_gemm_batched(const RtpGemmBatched* a, void* stream) {
 
 int rtp_linear_fwd(const RtpRing* ring, const RtpLinearFwd* op, void* stream) {
   static thread_local rtp::GemmParams<1> params;
+  decide_pair(op->M, op->out_features, ring->ctas, ring->world == 1 || pair_policy() == 1);   // automatic pairs: single rank only
   if (build_linear_fwd(*ring, *op, params.prog[0])) return -1;
   if (!params.prog[0].status) return fail("ring workspace required");
   params.ctas_per_rank = ring->ctas;
@@ -787,6 +806,8 @@ int rtp_linear_fwd(const RtpRing* ring, const RtpLinearFwd* op, void* stream) {
 }
 int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream) {
   static thread_local rtp::GemmParams<1> params;
+  decide_pair(op->M, op->in_features < op->out_features ? op->in_features : op->out_features, ring->ctas,
+              ring->world == 1 || pair_policy() == 1);
   if (build_linear_bwd(*ring, *op, params.prog[0])) return -1;
   if (!params.prog[0].status) return fail("ring workspace required");
   params.ctas_per_rank = ring->ctas;
@@ -794,6 +815,7 @@ int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream) {
 }
 int rtp_expert_fwd(const RtpRing* ring, const RtpExpertFwd* op, void* stream) {
   static thread_local rtp::GemmParams<1> params;
+  decide_pair(0, 0, ring->ctas);   // pairs only when forced
   if (build_expert_fwd(*ring, *op, params.prog[0])) return -1;
   if (!params.prog[0].status) return fail("ring workspace required");
   params.ctas_per_rank = ring->ctas;
@@ -801,6 +823,7 @@ int rtp_expert_fwd(const RtpRing* ring, const RtpExpertFwd* op, void* stream) {
 }
 int rtp_expert_bwd(const RtpRing* ring, const RtpExpertBwd* op, void* stream) {
   static thread_local rtp::GemmParams<1> params;
+  decide_pair(0, 0, ring->ctas);   // pairs only when forced
   if (build_expert_bwd(*ring, *op, params.prog[0])) return -1;
   if (!params.prog[0].status) return fail("ring workspace required");
   params.ctas_per_rank = ring->ctas;

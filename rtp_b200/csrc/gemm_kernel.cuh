@@ -25,16 +25,20 @@ constexpr int kNumThreads = 256;
 constexpr int kStagePitch = 144;                // bytes per staged output row: 64 bf16 + 16 pad (conflict-free 16 B writes)
 constexpr int kStagingBytes = 4 * 32 * kStagePitch;
 constexpr int kSmemBytes = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kStagingBytes;
+static_assert(kSmemBytes <= 232448, "over the 227 KB of shared memory a CTA can have");
 
 struct SmemCtrl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
+  uint64_t peer_full[kMaxStages];   // pair mode, leader only: "the other CTA's half of this stage has landed"
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain;
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
+
+static_assert(sizeof(SmemCtrl) <= 256, "control block outgrew its shared-memory slot");
 
 // One rank per launch: the program travels as a kernel parameter.  Emulated ranks (several programs in one
 // cooperative launch on one GPU) read their programs from constant memory instead, which is large enough for four.
@@ -78,17 +82,25 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
   const int unit = PAIR ? (cta >> 1) : cta;
   const int GU = PAIR ? (G >> 1) : G;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&ctl->full[s], PAIR ? 2 : 1);      // pair: one arrive.expect_tx from each CTA's producer (leader's barrier)
-      mbar_init(&ctl->empty[s], 1);
+  pdl_launch_dependents();
+#define GEMM_STAMP(i) do { if (P.trace && cta == 0) P.trace[3 * 256 + 64 + (i)] = globaltimer_ns(); } while (0)
+  if (threadIdx.x == 0) GEMM_STAMP(0);
+  if (warp == 0) {
+    // one barrier set per lane
+    if (lane < kStages) {
+      mbar_init(&ctl->full[lane], 1);
+      mbar_init(&ctl->empty[lane], 1);
+      mbar_init(&ctl->peer_full[lane], 1);
+    } else if (lane < kMaxStages + 2) {
+      const int a = lane - kMaxStages;
+      if (a >= 0) {
+        mbar_init(&ctl->tmem_full[a], 1);
+        mbar_init(&ctl->tmem_empty[a], PAIR ? 8 : 4);  // pair: the epilogue warps of both CTAs arrive on the leader's barrier
+      }
+    } else if (lane == kMaxStages + 2) {
+      mbar_init(&ctl->drain, 1);
+      ctl->abort_flag = 0;
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&ctl->tmem_full[a], 1);
-      mbar_init(&ctl->tmem_empty[a], PAIR ? 8 : 4);  // pair: the epilogue warps of both CTAs arrive on the leader's barrier
-    }
-    mbar_init(&ctl->drain, 1);
-    ctl->abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -100,6 +112,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
   if (PAIR) cluster_sync_all();      // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
+  // everything above touched only shared memory and TMEM; from here on the previous kernel of the stream must be complete
+  pdl_wait();
+  if (threadIdx.x == 0) GEMM_STAMP(1);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -111,8 +126,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const uint32_t tiles_s = smem_u32(tiles);
       const uint32_t full_s = smem_u32(&ctl->full[0]);
       const uint32_t empty_s = smem_u32(&ctl->empty[0]);
-      const uint32_t lead_full_s = PAIR ? mapa_u32(full_s, 0) : full_s;
-      (void)lead_full_s;
+
       bool ok = true;
       for (int p = 0; p < P.n_phases && ok; ++p) {
         const RtpPhase& ph = P.phases[p];
@@ -163,6 +177,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const int b_dx = p_b_mn ? 0 : kBK, b_dy = p_b_mn ? kBK : 0;
         const int b_ix = p_b_mn ? 64 : 0, b_iy = p_b_mn ? 0 : ph.b_box;  // per box inside a stage
         const uint32_t b_ismem = p_b_mn ? 8192u : (uint32_t)ph.b_box * 128u;
+        if (p == 0) GEMM_STAMP(2);
         for (int t = (unit - p_cta_off + GU) % GU; t < total && ok; t += GU) {
           const int z = t / per_batch, tt = t % per_batch;
           const int m0u = (tt % tiles_m) * TM;              // first row of the unit's tile
@@ -184,14 +199,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             const uint32_t sb = sa + kABytes;
             issued_mask |= 1u << stage;
             issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
-            if (PAIR) {
-              // both CTAs of the pair post their bytes on the LEADER's barrier; copies land in the issuing CTA's smem
-              const uint32_t lbar = lead_full_s + stage * 8;
-              mbar_arrive_expect_tx_cluster(lbar, tx);
-              tma_load_2d_pair_s(sa, ma, ax, ay, lbar);
-              if (na == 2) tma_load_2d_pair_s(sa + 8192, ma, ax + 64, ay, lbar);
-              for (int i = 0; i < nb; ++i) tma_load_2d_pair_s(sb + i * b_ismem, mb, bx + i * b_ix, by + i * b_iy, lbar);
-            } else {
+            {
+              // every CTA (also in a pair) copies into its own shared memory and completes its own barrier
               const uint32_t bar = full_s + stage * 8;
               mbar_arrive_expect_tx_s(bar, tx);
               tma_load_2d_s(sa, ma, ax, ay, bar);
@@ -207,11 +216,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       }
       if (!ok) {
         // gave up: wait (bounded) until every copy this thread issued has landed before the CTA exits
-        if (PAIR && crank != 0) {
-          // the barrier that tracks this CTA's copies lives in the leader: give the copies time to land instead
-          unsigned long long t0 = globaltimer_ns();
-          while (globaltimer_ns() - t0 < 200000ull) { }
-        } else {
+        {
           for (int s = 0; s < kStages; ++s) {
             if (!((issued_mask >> s) & 1u)) continue;
             unsigned long long t0 = globaltimer_ns();
@@ -234,6 +239,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       int tr_m = 0;
       const uint32_t tiles_s = smem_u32(tiles);
       const uint32_t full_s = smem_u32(&ctl->full[0]);
+      const uint32_t peer_full_s = smem_u32(&ctl->peer_full[0]);
+      (void)peer_full_s;
       for (int p = 0; p < P.n_phases && ok; ++p) {
         const RtpPhase& ph = P.phases[p];
         const int tiles_m = (ph.M + TM - 1) / TM;
@@ -258,6 +265,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
           for (int kb = 0; kb < kblocks; ++kb) {
             if (!mbar_wait_s(full_s + stage * 8, phase, abort_flag, status, timeout_ns)) { ok = false; break; }
+            if (PAIR && !mbar_try_wait_cluster_s(peer_full_s + stage * 8, phase)) {
+              // bounded: the slow path spins on the plain form, then the acquire is repeated once it has flipped
+              if (!mbar_wait_slow_s(peer_full_s + stage * 8, phase, abort_flag, status, timeout_ns)) { ok = false; break; }
+              mbar_try_wait_cluster_s(peer_full_s + stage * 8, phase);
+            }
             tc_fence_after();
             const uint32_t sa = (tiles_s + stage * kStageBytes) >> 4;   // descriptors hold the address in 16-byte units
             const uint32_t sb = sa + (kABytes >> 4);
@@ -286,6 +298,34 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         unsigned long long t0 = globaltimer_ns();
         while (!mbar_try_wait(&ctl->drain, 0)) {
           if (globaltimer_ns() - t0 > 2000000ull) break;
+        }
+      }
+    } else if (PAIR && crank != 0 && elect_one()) {
+      // Relay of the second CTA of a pair: its copies complete its own barriers; one arrive per stage tells the leader's
+      // UMMA issuer that this half of the stage is in place.  Walks the same (phase, tile, k-block) sequence.
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const uint32_t full_s = smem_u32(&ctl->full[0]);
+      const uint32_t lead_peer_full = mapa_u32(smem_u32(&ctl->peer_full[0]), 0);
+      for (int p = 0; p < P.n_phases && ok; ++p) {
+        const RtpPhase& ph = P.phases[p];
+        const int tiles_m = (ph.M + TM - 1) / TM;
+        const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
+        const int per_batch = tiles_m * tiles_n;
+        const int total = per_batch * ph.batch;
+        const int kblocks_full = (ph.K + kBK - 1) / kBK;
+        for (int t = (unit - ph.cta_off + GU) % GU; t < total && ok; t += GU) {
+          const int tt = t % per_batch;
+          const int m0 = (tt % tiles_m) * TM;
+          const int n0 = (tt / tiles_m) * ph.bn;
+          if (ph.causal == 1 && n0 > m0 + TM - 1) continue;
+          const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + TM + kBK - 1) / kBK) : kblocks_full;
+          for (int kb = 0; kb < kblocks; ++kb) {
+            if (!mbar_wait_s(full_s + stage * 8, phase, abort_flag, status, timeout_ns)) { ok = false; break; }
+            mbar_arrive_cluster(lead_peer_full + stage * 8);   // plain arrive: a cluster-scope release costs about a microsecond here
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+          }
         }
       }
     }
@@ -733,13 +773,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
   }
 
   // ---------------------------------------------------------------------- tear-down
+  if (threadIdx.x == 64) GEMM_STAMP(4);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) GEMM_STAMP(5);
   if (PAIR) cluster_sync_all();      // neither CTA leaves while the other may still signal its barriers or read its smem
   if (warp == 1) {
     tc_fence_after();
     if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 32) GEMM_STAMP(6);
   if (threadIdx.x == 0 && P.flags) {
     __threadfence();
     unsigned long long prev = atomicAdd(&P.flags->done_ctas.v, 1ull);

@@ -39,8 +39,60 @@ struct RtpFlagBlock {
 #define RTP_KIND_VECADD 2   // out[r, c] = src[r, c] (+ in[r, c]): one hop of a ring reduce-scatter
 #define RTP_KIND_REDUCE 3   // out[i] = sum_k src_k[i] over r_nsrc flat bf16 buffers (owner-side sum of gradient slots)
 
+// Field order matters for speed: a phase is read from the kernel-parameter bank, where the first touch of a line
+// costs a few hundred nanoseconds on the critical path of a short GEMM.  The fields that the TMA producer and the UMMA
+// issuer need come first, the epilogue's next, the ones of the rarer phase kinds last.
 struct RtpPhase {
   int kind;
+  // operands (bf16). *_mn = 1: the operand is stored with its M (or N) index contiguous.
+  int a_map, b_map;
+  int a_mn, b_mn;
+  int M, N, K;
+  int bn;  // tile width: 64, 128 or 256
+  int b_box;      // rows per TMA box of a K-major B operand (64 or 128)
+  int causal;     // 1: skip tiles entirely above the diagonal (n0 > m0 + 127); 2: stop the k loop at the diagonal
+  int cta_off;  // tile t of this phase runs on CTA (t + cta_off) % G, so that successive phases fill different SMs
+  // batching: `batch` independent GEMMs whose operands are windows of the same 2-D tensors.  Batch z = (zo, zi) with
+  // zi = z % batch_inner; the window of operand X starts at (mn, k) += zo * x_bo_{mn,k} + zi * x_bi_{mn,k} and the
+  // output / accumulate pointers move by zo * d_bo + zi * d_bi elements.
+  int batch, batch_inner;
+  int a_off_mn, a_off_k;  // element offsets added to the tile coordinates
+  int b_off_mn, b_off_k;
+  int a_bo_mn, a_bo_k, a_bi_mn, a_bi_k;
+  int b_bo_mn, b_bo_k, b_bi_mn, b_bi_k;
+  // synchronisation (all optional)
+  int wait_ctr[RTP_MAX_WAITS];  // local arrival counters that must reach fill (uses + rel + 1) before operands are read
+  int wait_rel[RTP_MAX_WAITS];
+  // epilogue
+  void* d;
+  long long ldd;
+  const void* c;  // optional accumulate source (same shape as d)
+  long long ldc;
+  const void* bias;    // optional bf16[N]
+  const void* mask;    // optional bf16 [M, N]: out = mask > 0 ? out * mask_scale : 0
+  long long ldmask;
+  int d_fp32;
+  int vec_ok;  // 1: 16-byte vector accesses of d/c/mask rows are aligned
+  int c_fp32;
+  int act;             // 0 none, 1 relu, 2 gelu(erf)
+  float alpha;    // accumulator scale applied first in the epilogue
+  float mask_scale;
+  uint32_t drop_thresh;  // 0: no dropout. keep element if philox word >= thresh
+  float drop_scale;
+  unsigned long long drop_seed, drop_offset;
+  const unsigned long long* drop_step_ptr;  // optional device counter: offset += *ptr * 65536 (graph replays get fresh masks)
+  long long d_bo, d_bi, c_bo, c_bi;
+  unsigned long long* credit_ptr;  // remote `done` counter that must reach fill (uses + rel) before d is written
+  int credit_ctr;
+  int credit_rel;
+  int done_ctr[RTP_MAX_WAITS];     // local `done` counters bumped when this CTA has finished the phase
+  unsigned long long* arrive_ptr;  // remote `arrive` counter bumped when this CTA has finished the phase
+  // optional vector job done by CTA 0 at the end of the phase: vec_out[i] = vec_in[i] + vec_add[i] (bf16/fp32 per flags)
+  void* vec_out;
+  const void* vec_in;
+  const float* vec_add;
+  int vec_len;
+  int vec_fp32;  // dtype of vec_out / vec_in
   // ---- RTP_KIND_GATHER: out[t, c] = dropout(table[ids[t], c] * scale + pe[t / tpp, col_off + c]); out = d (pitch ldd)
   const void* g_table;       // [V, g_cols] bf16, home shard or a workspace slot
   const long long* g_ids;
@@ -56,55 +108,6 @@ struct RtpPhase {
   const void* r_src[RTP_NUM_SLOTS];
   int r_nsrc;
   long long r_n;  // elements, multiple of 8
-  // operands (bf16). *_mn = 1: the operand is stored with its M (or N) index contiguous.
-  int a_map, b_map;
-  int a_mn, b_mn;
-  int a_off_mn, a_off_k;  // element offsets added to the tile coordinates
-  int b_off_mn, b_off_k;
-  int M, N, K;
-  int bn;  // tile width: 128 or 256
-  // batching: `batch` independent GEMMs whose operands are windows of the same 2-D tensors.  Batch z = (zo, zi) with
-  // zi = z % batch_inner; the window of operand X starts at (mn, k) += zo * x_bo_{mn,k} + zi * x_bi_{mn,k} and the
-  // output / accumulate pointers move by zo * d_bo + zi * d_bi elements.
-  int batch, batch_inner;
-  int a_bo_mn, a_bo_k, a_bi_mn, a_bi_k;
-  int b_bo_mn, b_bo_k, b_bi_mn, b_bi_k;
-  long long d_bo, d_bi, c_bo, c_bi;
-  int b_box;      // rows per TMA box of a K-major B operand (64 or 128)
-  int causal;     // 1: skip tiles entirely above the diagonal (n0 > m0 + 127); 2: stop the k loop at the diagonal
-  float alpha;    // accumulator scale applied first in the epilogue
-  int cta_off;  // tile t of this phase runs on CTA (t + cta_off) % G, so that successive phases fill different SMs
-  // epilogue
-  void* d;
-  long long ldd;
-  int d_fp32;
-  int vec_ok;  // 1: 16-byte vector accesses of d/c/mask rows are aligned
-  const void* c;  // optional accumulate source (same shape as d)
-  long long ldc;
-  int c_fp32;
-  int act;             // 0 none, 1 relu, 2 gelu(erf)
-  const void* bias;    // optional bf16[N]
-  const void* mask;    // optional bf16 [M, N]: out = mask > 0 ? out * mask_scale : 0
-  long long ldmask;
-  float mask_scale;
-  uint32_t drop_thresh;  // 0: no dropout. keep element if philox word >= thresh
-  float drop_scale;
-  unsigned long long drop_seed, drop_offset;
-  const unsigned long long* drop_step_ptr;  // optional device counter: offset += *ptr * 65536 (graph replays get fresh masks)
-  // optional vector job done by CTA 0 at the end of the phase: vec_out[i] = vec_in[i] + vec_add[i] (bf16/fp32 per flags)
-  void* vec_out;
-  const void* vec_in;
-  const float* vec_add;
-  int vec_len;
-  int vec_fp32;  // dtype of vec_out / vec_in
-  // synchronisation (all optional)
-  int wait_ctr[RTP_MAX_WAITS];  // local arrival counters that must reach fill (uses + rel + 1) before operands are read
-  int wait_rel[RTP_MAX_WAITS];
-  unsigned long long* credit_ptr;  // remote `done` counter that must reach fill (uses + rel) before d is written
-  int credit_ctr;
-  int credit_rel;
-  int done_ctr[RTP_MAX_WAITS];     // local `done` counters bumped when this CTA has finished the phase
-  unsigned long long* arrive_ptr;  // remote `arrive` counter bumped when this CTA has finished the phase
 };
 
 struct RtpPush {
@@ -118,14 +121,15 @@ struct RtpPush {
 };
 
 struct alignas(64) RtpProgram {
-  CUtensorMap maps[RTP_MAX_MAPS];
-  RtpPhase phases[RTP_MAX_PHASES];
-  RtpPush pushes[RTP_MAX_PUSHES];
   int n_phases, n_pushes;
   int n_stages, stage_bytes;  // smem pipeline geometry (host: finalize_program)
   RtpFlagBlock* flags;  // this rank's flag block (may be null when nothing synchronises)
-  int uses_inc[RTP_NUM_CTR];  // added to flags->uses[] by the last CTA of the launch
   unsigned long long* status;  // status word (flags->status or a plain device word)
   unsigned long long timeout_ns;
   unsigned long long* trace;  // optional debug timeline of CTA 0: [role][tile][event] globaltimer stamps (see gemm_kernel.cuh)
+  int uses_inc[RTP_NUM_CTR];  // added to flags->uses[] by the last CTA of the launch
+  alignas(64) CUtensorMap maps[RTP_MAX_MAPS];
+  RtpPhase phases[RTP_MAX_PHASES];
+  RtpPush pushes[RTP_MAX_PUSHES];
 };
+

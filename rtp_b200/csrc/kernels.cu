@@ -7,7 +7,9 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <string>
+#include <cooperative_groups.h>
 #include "common.cuh"
+#include "launch.h"
 #include "kernels.h"
 
 using namespace rtp;
@@ -603,6 +605,75 @@ __global__ void colsum_kernel(const __nv_bfloat16* __restrict__ x, long long ld,
   atomicAdd(out + c + 1, a1);
 }
 
+// Vector variant: a block of 256 threads owns 64 columns (8 column lanes x 16 bytes) and a range of rows (32 row lanes,
+// up to 8 loads in flight per thread); the row lanes are combined in shared memory.  The blocks that share a column
+// group form a thread-block cluster along y: each leaves its 64 partial sums in its own shared memory, and the first
+// block of the cluster adds them up through distributed shared memory and stores the result (no atomics, no zero-fill).
+__global__ void __launch_bounds__(256) colsum_vec_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N,
+                                                         float* __restrict__ out, int rows_per_block) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float red[32][65];
+  __shared__ float part[64];
+  const int cl = threadIdx.x & 7, rl = threadIdx.x >> 3;
+  const int c = blockIdx.x * 64 + cl * 8;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(M, r0 + rows_per_block);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if (c < N) {
+    int r = r0 + rl;
+    for (; r + 7 * 32 < r1; r += 8 * 32) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcs(reinterpret_cast<const uint4*>(x + (size_t)(r + u * 32) * ld + c));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        float f[8];
+        unpack8(v[u], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+    }
+    for (; r + 3 * 32 < r1; r += 4 * 32) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = __ldcs(reinterpret_cast<const uint4*>(x + (size_t)(r + u * 32) * ld + c));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        unpack8(v[u], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+    }
+    for (; r < r1; r += 32) {
+      float f[8];
+      unpack8(__ldcs(reinterpret_cast<const uint4*>(x + (size_t)r * ld + c)), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[rl][cl * 8 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) t += red[k][threadIdx.x];
+    part[threadIdx.x] = t;
+  }
+  cluster.sync();
+  if (cluster.block_rank() == 0 && threadIdx.x < 64) {
+    const int col = blockIdx.x * 64 + threadIdx.x;
+    float t = 0.f;
+    for (unsigned k = 0; k < cluster.num_blocks(); ++k) t += cluster.map_shared_rank(part, k)[threadIdx.x];
+    if (col < N) out[col] = t;
+  }
+  cluster.sync();   // no block leaves while its shared memory may still be read
+}
+
 // ------------------------------------------------------------------------------------------------
 // Multi-tensor Adam / AdamW with optional gradient value clipping.
 // ------------------------------------------------------------------------------------------------
@@ -1051,6 +1122,16 @@ int rtp_attn_small_bwd(const void* qkv, const void* dout, void* dqkv, int S, int
 }
 int rtp_colsum(const void* x, long long ld, int M, int N, float* out, void* stream) {
   if (N % 2 || ld % 2) { k_err = "colsum: N and ld must be even"; return -1; }
+  if (N % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    // clusters of up to 8 blocks split the rows (at least 128 rows per block)
+    int cy = 8;
+    while (cy > 1 && M < cy * 128) cy >>= 1;
+    const int rows = (M + cy - 1) / cy;
+    rtp::launch_kc(colsum_vec_kernel, dim3((N + 63) / 64, cy), dim3(256), 0, (cudaStream_t)stream, dim3(1, cy, 1),
+                   (const __nv_bfloat16*)x, ld, M, N, out, rows);
+    LAUNCH_CHECK("colsum");
+    return 0;
+  }
   cudaError_t e = cudaMemsetAsync(out, 0, (size_t)N * sizeof(float), (cudaStream_t)stream);
   if (e != cudaSuccess) return kfail("colsum memset", e);
   const int rows_per_block = 64;

@@ -36,6 +36,7 @@ int rtp_embed_bwd(void* gtable, const long long* ids, const void* dy, long long 
 // apply.  rtp_set_attn_tc(0) forces the scalar kernels (A/B comparison).
 int rtp_attn_tc_supported(int S, int heads, int nshard);
 int rtp_attn_tc_error(void);
+int rtp_attn_tc_set_trace(unsigned long long* device_buffer);
 const char* rtp_attn_tc_last_error(void);
 void rtp_set_attn_tc(int on);
 int rtp_attn_tc_fwd(const void* qkv, void* out, int S, int B, int heads, int nshard, int causal, float sm_scale,
