@@ -332,6 +332,10 @@ __device__ __forceinline__ void red_release_sys_add(unsigned long long* p, unsig
   asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
+__device__ __forceinline__ void red_relaxed_sys_add(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
 // Spin until *ctr >= want. Returns false on timeout/abort (after writing the status word).
 __device__ __forceinline__ bool wait_counter_ge(const unsigned long long* ctr, unsigned long long want,
                                                 volatile uint32_t* abort_flag, unsigned long long* status,

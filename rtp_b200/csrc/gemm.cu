@@ -137,6 +137,7 @@ uint32_t drop_threshold(float p) {
 
 // Pipeline geometry: the stage must hold the widest B tile of the program; narrower tiles get more stages.
 int g_force_stages = 0;
+unsigned long long* g_trace = nullptr;   // tuning aid, see rtp_debug_set_trace
 void finalize_program(RtpProgram& P, int ctas, bool pair) {
   const int tm = pair ? 256 : 128;
   if (pair) ctas /= 2;
@@ -715,7 +716,6 @@ extern "C" {
 const char* rtp_last_error(void) { return g_err.c_str(); }
 void rtp_debug_force_stages(int n) { g_force_stages = n; }
 void rtp_set_pair_mode(int on) { g_pair = on < 0 ? -1 : (on ? 1 : 0); }
-unsigned long long* g_trace = nullptr;
 void rtp_debug_set_trace(unsigned long long* device_buffer_1024_words) { g_trace = device_buffer_1024_words; }
 int rtp_sm_count(void) { return sm_count(); }
 
@@ -800,6 +800,7 @@ int rtp_linear_fwd(const RtpRing* ring, const RtpLinearFwd* op, void* stream) {
   static thread_local rtp::GemmParams<1> params;
   decide_pair(op->M, op->out_features, ring->ctas, ring->world == 1 || pair_policy() == 1);   // automatic pairs: single rank only
   if (build_linear_fwd(*ring, *op, params.prog[0])) return -1;
+  params.prog[0].trace = g_trace;
   if (!params.prog[0].status) return fail("ring workspace required");
   params.ctas_per_rank = ring->ctas;
   return launch<1>(params, ring->ctas, false, (cudaStream_t)stream, true);
@@ -809,6 +810,7 @@ int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream) {
   decide_pair(op->M, op->in_features < op->out_features ? op->in_features : op->out_features, ring->ctas,
               ring->world == 1 || pair_policy() == 1);
   if (build_linear_bwd(*ring, *op, params.prog[0])) return -1;
+  params.prog[0].trace = g_trace;
   if (!params.prog[0].status) return fail("ring workspace required");
   params.ctas_per_rank = ring->ctas;
   return launch<1>(params, ring->ctas, false, (cudaStream_t)stream, true);

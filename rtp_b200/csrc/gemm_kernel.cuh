@@ -348,6 +348,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           ph.drop_offset + (ph.drop_step_ptr ? __ldg(ph.drop_step_ptr) * 65536ull : 0ull);
       const bool does_vec = (ph.vec_out != nullptr) && cta == 0;
       (void)has_tiles;
+      if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 0] = globaltimer_ns();
       if (ok) {
         // Operands of the accumulate / bias reads must have arrived and the destination slot must be free.
         // A CTA without tiles waits too: the counters only mean "every CTA is past fill u" if no CTA
@@ -366,6 +367,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) ok = false;
       }
+      if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 1] = globaltimer_ns();
       if (ok && ph.kind == RTP_KIND_GATHER) {
         // embedding rows of the visiting table shard -> column block of the output
         const int per_row = ph.g_cols >> 3;
@@ -723,18 +725,26 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           else reinterpret_cast<__nv_bfloat16*>(ph.vec_out)[i] = __float2bfloat16(x);
         }
       }
+      if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 2] = globaltimer_ns();
       // phase end: publish "read done" / "data arrived". Every CTA signals, also one without tiles.
       bool signals = ph.arrive_ptr != nullptr;
       for (int w = 0; w < RTP_MAX_WAITS; ++w) signals = signals || ph.done_ctr[w] >= 0;
       if (signals) {
-        __threadfence_system();
+        // All four epilogue warps are through with the phase.  The barrier also orders their stores before the fence of
+        // the signalling thread below (a release is cumulative over what the thread has synchronised with).
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (epi_tid == 0 && ok) {
+          // "read done": the operands have been consumed, nothing written by this CTA has to be visible first
           for (int w = 0; w < RTP_MAX_WAITS; ++w)
-            if (ph.done_ctr[w] >= 0) red_release_sys_add(&P.flags->done[ph.done_ctr[w]].v, 1ull);
-          if (ph.arrive_ptr) red_release_sys_add(ph.arrive_ptr, 1ull);
+            if (ph.done_ctr[w] >= 0) red_relaxed_sys_add(&P.flags->done[ph.done_ctr[w]].v, 1ull);
+          // "data arrived": the tiles stored by this CTA (possibly into a peer's memory) come first
+          if (ph.arrive_ptr) {
+            __threadfence_system();
+            red_relaxed_sys_add(ph.arrive_ptr, 1ull);
+          }
         }
       }
+      if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 3] = globaltimer_ns();
     }
   } else {
     // ------------------------------------------------------------------ pushers (2 warps)
@@ -743,11 +753,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
     for (int j = 0; j < P.n_pushes; ++j) {
       const RtpPush& pu = P.pushes[j];
       uint32_t good = 1;
+      if (P.trace && cta == 0 && ptid == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 0] = globaltimer_ns();
       if (ok && lane == 0 && pu.credit_ptr)
         good = wait_counter_ge(pu.credit_ptr, fill_target(P.flags, pu.credit_ctr, pu.credit_rel, 0, G), abort_flag,
                                status, wait_ns, ST_TIMEOUT_CREDIT);
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) ok = false;
+      if (P.trace && cta == 0 && ptid == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 1] = globaltimer_ns();
       if (ok) {
         const unsigned long long units = pu.bytes >> 4;
         const unsigned long long per = (units + G - 1) / G;
@@ -765,10 +777,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           for (int u = 0; u < 8; ++u) dst[i + 64 * u] = v[u];
         }
         for (; i < hi; i += 64) dst[i] = __ldg(src + i);
-        __threadfence_system();
       }
       asm volatile("bar.sync 2, 64;" ::: "memory");
-      if (ptid == 0 && ok && pu.arrive_ptr) red_release_sys_add(pu.arrive_ptr, 1ull);
+      if (ptid == 0 && ok && pu.arrive_ptr) {
+        __threadfence_system();   // one cumulative release for the stores of both pusher warps
+        red_relaxed_sys_add(pu.arrive_ptr, 1ull);
+      }
+      if (P.trace && cta == 0 && ptid == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 2] = globaltimer_ns();
     }
   }
 
