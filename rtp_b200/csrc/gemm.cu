@@ -351,7 +351,6 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   int np = 0;
   for (int s = 0; s < N; ++s) {
     const int j = mod(r - 1 - s, N);
-    const bool last = s == N - 1;   // own shard
     // ---- wgrad: dW_j = dy_j^T x  -> gradient slot s of owner j (own shard: straight into the home gradient when
     //      the ring has one rank, else into the local slot N-1 that the final reduce reads)
     {
@@ -371,6 +370,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
         ph.credit_ptr = &ws_flags(R.ws[j])->done[RTP_CTR_G0 + s].v;
         ph.credit_ctr = RTP_CTR_G0 + s; ph.credit_rel = 0;
         ph.arrive_ptr = &ws_flags(R.ws[j])->arrive[RTP_CTR_G0 + s].v;
+        ph.arrive_defer = 1;   // consumed by the owner's final reduce phase only
       }
       if (op.bias_off >= 0 && op.dbias_full) {
         ph.vec_out = reinterpret_cast<__nv_bfloat16*>(dst) + op.bias_off;
@@ -380,8 +380,16 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
       }
       set_vec_ok(ph);
     }
+  }
+  // The weight-gradient phases need only local operands, so they all come first and cover the time the weight shards
+  // are in flight; the input-gradient phases follow, own shard first, then the visiting shards in order of arrival.
+  for (int q = 0; q < N && op.dx; ++q) {
+    const int s = (q == 0) ? N - 1 : q - 1;
+    const int j = mod(r - 1 - s, N);
+    const bool last = s == N - 1;   // own shard
+    const bool first_emitted = q == 0, final_emitted = q == N - 1;
     // ---- dgrad: column: dx += dy_j W_j ; row: dx_j = dy W_j
-    if (op.dx) {
+    {
       RtpPhase& ph = P.phases[np++];
       init_phase(ph);
       ph.a_map = 2; ph.a_mn = 0;
@@ -391,9 +399,9 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
       ph.bn = pick_bn(ph.M, ph.N, R.ctas);
       ph.ldd = op.lddx;
       ph.d = reinterpret_cast<__nv_bfloat16*>(op.dx) + (col ? 0 : (long long)j * Ks);
-      if (col && (s > 0 || op.dx_accumulate)) { ph.c = op.dx; ph.ldc = op.lddx; }
+      if (col && (!first_emitted || op.dx_accumulate)) { ph.c = op.dx; ph.ldc = op.lddx; }
       if (!col && op.dx_accumulate) { ph.c = ph.d; ph.ldc = op.lddx; }
-      if (op.mask && (!col || last)) {
+      if (op.mask && (!col || final_emitted)) {
         ph.mask = reinterpret_cast<const __nv_bfloat16*>(op.mask) + (col ? 0 : (long long)j * Ks);
         ph.ldmask = op.ldmask; ph.mask_scale = op.mask_scale;
       }

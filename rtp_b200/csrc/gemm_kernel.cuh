@@ -337,6 +337,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
     uint32_t acc_phase = 0;
     bool ok = true;
     int tr_e = 0;
+    unsigned long long* pending_arrive[RTP_NUM_SLOTS];   // deferred "data arrived" signals of earlier phases
+    int n_pending = 0;
     for (int p = 0; p < P.n_phases; ++p) {
       const RtpPhase& ph = P.phases[p];
       const int tiles_m = (ph.M + TM - 1) / TM;
@@ -349,6 +351,18 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const bool does_vec = (ph.vec_out != nullptr) && cta == 0;
       (void)has_tiles;
       if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 0] = globaltimer_ns();
+      if (n_pending > 0) {
+        // A phase that waits for other ranks must not sit on undelivered signals (they may be what the others wait for).
+        bool waits = ph.credit_ptr != nullptr;
+        for (int w = 0; w < RTP_MAX_WAITS; ++w) waits = waits || ph.wait_ctr[w] >= 0;
+        if (waits && ph.kind == RTP_KIND_REDUCE) {
+          if (epi_tid == 0 && ok) {
+            __threadfence_system();
+            for (int k = 0; k < n_pending; ++k) red_relaxed_sys_add(pending_arrive[k], 1ull);
+          }
+          n_pending = 0;
+        }
+      }
       if (ok) {
         // Operands of the accumulate / bias reads must have arrived and the destination slot must be free.
         // A CTA without tiles waits too: the counters only mean "every CTA is past fill u" if no CTA
@@ -421,15 +435,38 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       if (ok && ph.kind == RTP_KIND_REDUCE) {
         const long long items = ph.r_n >> 3;
         __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(ph.d);
-        for (long long it = (long long)cta * 128 + epi_tid; it < items; it += (long long)G * 128) {
-          float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int k = 0; k < ph.r_nsrc; ++k) {
-            const uint4 a = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(ph.r_src[k]) + it * 8));
-            acc8[0] += bf16_lo(a.x); acc8[1] += bf16_hi(a.x); acc8[2] += bf16_lo(a.y); acc8[3] += bf16_hi(a.y);
-            acc8[4] += bf16_lo(a.z); acc8[5] += bf16_hi(a.z); acc8[6] += bf16_lo(a.w); acc8[7] += bf16_hi(a.w);
+        const int nsrc = ph.r_nsrc;
+        const uint4* srcs[RTP_NUM_SLOTS];
+#pragma unroll
+        for (int k = 0; k < RTP_NUM_SLOTS; ++k) srcs[k] = reinterpret_cast<const uint4*>(ph.r_src[k < nsrc ? k : 0]);
+        // two items per thread and every source in flight at once (the loads are predicated, not looped over)
+        const long long stride = (long long)G * 128;
+        for (long long it = (long long)cta * 128 + epi_tid; it < items; it += 2 * stride) {
+          const long long it1 = it + stride;
+          const bool two = it1 < items;
+          uint4 a[RTP_NUM_SLOTS], b[RTP_NUM_SLOTS];
+#pragma unroll
+          for (int k = 0; k < RTP_NUM_SLOTS; ++k) {
+            a[k] = make_uint4(0u, 0u, 0u, 0u);
+            b[k] = make_uint4(0u, 0u, 0u, 0u);
+            if (k < nsrc) {
+              a[k] = __ldcg(srcs[k] + it);
+              if (two) b[k] = __ldcg(srcs[k] + it1);
+            }
           }
-          *reinterpret_cast<uint4*>(outp + it * 8) = make_uint4(pack_bf16(acc8[0], acc8[1]), pack_bf16(acc8[2], acc8[3]),
-                                                                 pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
+          float s0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, s1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int k = 0; k < RTP_NUM_SLOTS; ++k) {
+            s0[0] += bf16_lo(a[k].x); s0[1] += bf16_hi(a[k].x); s0[2] += bf16_lo(a[k].y); s0[3] += bf16_hi(a[k].y);
+            s0[4] += bf16_lo(a[k].z); s0[5] += bf16_hi(a[k].z); s0[6] += bf16_lo(a[k].w); s0[7] += bf16_hi(a[k].w);
+            s1[0] += bf16_lo(b[k].x); s1[1] += bf16_hi(b[k].x); s1[2] += bf16_lo(b[k].y); s1[3] += bf16_hi(b[k].y);
+            s1[4] += bf16_lo(b[k].z); s1[5] += bf16_hi(b[k].z); s1[6] += bf16_lo(b[k].w); s1[7] += bf16_hi(b[k].w);
+          }
+          *reinterpret_cast<uint4*>(outp + it * 8) = make_uint4(pack_bf16(s0[0], s0[1]), pack_bf16(s0[2], s0[3]),
+                                                                 pack_bf16(s0[4], s0[5]), pack_bf16(s0[6], s0[7]));
+          if (two)
+            *reinterpret_cast<uint4*>(outp + it1 * 8) = make_uint4(pack_bf16(s1[0], s1[1]), pack_bf16(s1[2], s1[3]),
+                                                                    pack_bf16(s1[4], s1[5]), pack_bf16(s1[6], s1[7]));
         }
       }
       // phase fields used per element live in registers (reading them from parameter space inside the loops costs a
@@ -727,7 +764,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       }
       if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 2] = globaltimer_ns();
       // phase end: publish "read done" / "data arrived". Every CTA signals, also one without tiles.
-      bool signals = ph.arrive_ptr != nullptr;
+      const bool defer = ph.arrive_ptr != nullptr && ph.arrive_defer && p + 1 < P.n_phases && n_pending < RTP_NUM_SLOTS;
+      bool signals = ph.arrive_ptr != nullptr || (n_pending > 0 && !defer);
       for (int w = 0; w < RTP_MAX_WAITS; ++w) signals = signals || ph.done_ctr[w] >= 0;
       if (signals) {
         // All four epilogue warps are through with the phase.  The barrier also orders their stores before the fence of
@@ -737,12 +775,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           // "read done": the operands have been consumed, nothing written by this CTA has to be visible first
           for (int w = 0; w < RTP_MAX_WAITS; ++w)
             if (ph.done_ctr[w] >= 0) red_relaxed_sys_add(&P.flags->done[ph.done_ctr[w]].v, 1ull);
-          // "data arrived": the tiles stored by this CTA (possibly into a peer's memory) come first
-          if (ph.arrive_ptr) {
+          // "data arrived": the tiles stored by this CTA (possibly into a peer's memory) come first.  Deferred signals
+          // wait for the first later phase that does not defer: their stores have had that long to complete, so the
+          // one release fence for all of them is cheap.
+          if (!defer && (n_pending > 0 || ph.arrive_ptr)) {
             __threadfence_system();
-            red_relaxed_sys_add(ph.arrive_ptr, 1ull);
+            for (int k = 0; k < n_pending; ++k) red_relaxed_sys_add(pending_arrive[k], 1ull);
+            if (ph.arrive_ptr) red_relaxed_sys_add(ph.arrive_ptr, 1ull);
           }
         }
+        if (defer) pending_arrive[n_pending++] = ph.arrive_ptr; else n_pending = 0;
       }
       if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 3] = globaltimer_ns();
     }

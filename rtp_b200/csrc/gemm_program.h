@@ -87,6 +87,8 @@ struct RtpPhase {
   int credit_rel;
   int done_ctr[RTP_MAX_WAITS];     // local `done` counters bumped when this CTA has finished the phase
   unsigned long long* arrive_ptr;  // remote `arrive` counter bumped when this CTA has finished the phase
+  int arrive_defer;  // 1: the arrive signal may wait until the end of the next phase (its consumer is a final reduce), so
+                     // that the release fence finds the stores of this phase, often into a peer's memory, already done
   // optional vector job done by CTA 0 at the end of the phase: vec_out[i] = vec_in[i] + vec_add[i] (bf16/fp32 per flags)
   void* vec_out;
   const void* vec_in;
