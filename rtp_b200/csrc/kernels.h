@@ -51,6 +51,21 @@ int rtp_attn_small_fwd(const void* qkv, void* out, int S, int B, int heads, int 
 int rtp_attn_small_bwd(const void* qkv, const void* dout, void* dqkv, int S, int B, int heads, int nshard, int causal,
                        float sm_scale, float drop_p, unsigned long long seed, unsigned long long offset,
                        const unsigned long long* step_ptr, void* stream);
+// Top-2 MoE gating on [S, E] fp32 logits (E <= 64) and its gradient; rotary position embedding (gate_rope.cu).
+const char* rtp_gate_last_error(void);
+int rtp_top2_gate_fwd(const float* logits, const float* noise, float* gates, int* idx, int* loc, float* gate_w,
+                      unsigned char* valid, float* me_sum, float* ce, float* l_aux, int S, int E, int capacity,
+                      void* stream);
+int rtp_top2_gate_bwd(const float* gates, const int* idx, const unsigned char* valid, const float* ce,
+                      const float* d_gate_w, const float* d_l_aux, float* dlogits, int S, int E, void* stream);
+int rtp_rope(const void* x, void* y, const float* cosv, const float* sinv, long long T, int H, int hd, int S, int inner,
+             int backward, void* stream);
+// Convolution as GEMM: patch matrix of an NCHW bf16 input and its adjoint (im2col.cu).
+const char* rtp_im2col_last_error(void);
+int rtp_im2col(const void* x, void* cols, int B, int C, int H, int W, int KH, int KW, int sh, int sw, int ph, int pw,
+               int dh, int dw, int Kp, void* stream);
+int rtp_col2im(const void* dcols, void* dx, int B, int C, int H, int W, int KH, int KW, int sh, int sw, int ph, int pw,
+               int dh, int dw, int Kp, void* stream);
 int rtp_colsum(const void* x, long long ld, int M, int N, float* out, void* stream);
 int rtp_adam(const RtpAdamTensor* tensors_dev, const int* block_start_dev, int ntensors, int total_blocks,
              const long long* step_dev, float lr, float beta1, float beta2, float eps, float weight_decay, int adamw,

@@ -57,6 +57,9 @@ def rope_tables(seq_len, head_dim, theta, device, dtype=torch.float32):
 
 def apply_rope(x, cos, sin):
     """x: [B, S, H, hd]; rotates pairs (x[2i], x[2i+1])."""
+    if FO.use_kernels(x) and x.shape[-1] % 16 == 0:
+        from ..ops import kernels as K
+        return K.rope(x, cos, sin, inner=1)
     x1, x2 = x[..., 0::2], x[..., 1::2]
     c, s = cos[None, :, None, :], sin[None, :, None, :]
     out = torch.stack([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1)

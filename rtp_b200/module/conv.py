@@ -6,6 +6,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from ..parallel import fused
 from ..parallel.flat import RotatedModule
 from ..parallel.rotated import rotated_apply
 from .utils import affine_weight, divide_and_check_no_remainder
@@ -59,6 +60,10 @@ class ColumnParallelConv2d(RotatedModule):
     def forward(self, input_: torch.Tensor) -> torch.Tensor:  # type: ignore
         conv = self.conv
         has_bias = conv.bias is not None
+        if fused.use_fused(input_, self._full_param):
+            from ..parallel import engine
+            if engine.fused_conv_ok(self, input_):
+                return engine.fused_conv(self, input_)
 
         def fn(j, views, x):
             # nn.Conv2d._conv_forward handles every padding_mode

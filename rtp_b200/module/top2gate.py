@@ -10,6 +10,7 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor, nn
 
+from ..parallel.context import get_backend
 from ..parallel.flat import RotatedModule
 from ..parallel.rotated import rotated_apply
 from .utils import affine_weight, divide_and_check_no_remainder
@@ -37,10 +38,21 @@ def one_hot(tensor: torch.Tensor, num_classes: int) -> Tensor:
 def top2_routing(logits: Tensor, capacity_factor: float = 1.0, noise: Optional[Tensor] = None):
     """Index form of top-2 gating: per token its two experts, slots, normalised gate values and validity.
     Returns (l_aux, idx[S,2], loc[S,2], gate[S,2], valid[S,2], capacity)."""
-    gates = F.softmax(logits, dim=1, dtype=torch.float)
-    S, E = gates.shape
+    S, E = logits.shape
     assert S % E == 0, "number of tokens must be a multiple of the number of experts"
     capacity = int(capacity_factor * 2 * S // E)
+    if logits.is_cuda and E <= 64 and get_backend() != "functional":
+        # fused kernels: softmax / top-1 / noisy top-2 per token, token-order slots in one block, no [S, E] one-hots
+        if noise is None:
+            noise = gumbel_rsample(logits.shape, device=logits.device)
+        from ..ops import kernels as K
+        l_aux, idx, loc, gate, valid = K.top2_gate(logits, capacity, noise)
+        valid = valid.bool()
+        idx = idx.long()
+        mask1 = one_hot(idx[:, 0], E) * valid[:, :1]
+        mask2 = one_hot(idx[:, 1], E) * valid[:, 1:]
+        return l_aux, idx, loc.long(), gate, valid, capacity, mask1, mask2
+    gates = F.softmax(logits, dim=1, dtype=torch.float)
     idx1 = torch.argmax(gates, dim=1)
     mask1 = one_hot(idx1, E)
     if noise is None:

@@ -32,6 +32,13 @@ def _L():
         L.rtp_set_attn_tc.restype = None
         L.rtp_attn_tc_error.restype = i
         L.rtp_colsum.argtypes = [vp, ll, i, i, vp, vp]
+        L.rtp_gate_last_error.restype = C.c_char_p
+        L.rtp_top2_gate_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp]
+        L.rtp_top2_gate_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, vp]
+        L.rtp_rope.argtypes = [vp, vp, vp, vp, ll, i, i, i, i, i, vp]
+        L.rtp_im2col_last_error.restype = C.c_char_p
+        L.rtp_im2col.argtypes = [vp, vp] + [i] * 13 + [vp]
+        L.rtp_col2im.argtypes = [vp, vp] + [i] * 13 + [vp]
         L.rtp_adam.argtypes = [vp, vp, i, i, vp, f, f, f, f, f, i, f, f, vp]
         L.rtp_add.argtypes = [vp, vp, vp, ll, vp]
         L.rtp_moe_scatter.argtypes = [vp, vp, vp, vp, i, i, ll, vp]
@@ -269,3 +276,117 @@ class AdamPlan:
     def step(self, step_dev, lr, beta1, beta2, eps, weight_decay=0.0, adamw=False, clip_value=0.0, grad_scale=1.0):
         _check(_L().rtp_adam(_p(self.table), _p(self.starts), self.n, self.total_blocks, _p(step_dev), lr, beta1,
                              beta2, eps, weight_decay, int(adamw), clip_value, grad_scale, _lib.stream_ptr()), "adam")
+
+
+def _gate_check(rc, what):
+    if rc != 0:
+        raise RuntimeError(f"{what}: {_L().rtp_gate_last_error().decode()}")
+
+
+class _Top2Gate(torch.autograd.Function):
+    """Fused top-2 routing on [S, E] logits (reference: rtp/module/top2gate.py:43-105), index form."""
+
+    @staticmethod
+    def forward(ctx, logits, noise, capacity):
+        S, E = logits.shape
+        lg = logits.detach().float().contiguous()
+        nz = noise.detach().float().contiguous() if noise is not None else None
+        dev = lg.device
+        gates = torch.empty(S, E, dtype=torch.float32, device=dev)
+        idx = torch.empty(S, 2, dtype=torch.int32, device=dev)
+        loc = torch.empty(S, 2, dtype=torch.int32, device=dev)
+        gate_w = torch.empty(S, 2, dtype=torch.float32, device=dev)
+        valid = torch.empty(S, 2, dtype=torch.uint8, device=dev)
+        me_sum = torch.empty(E, dtype=torch.float32, device=dev)
+        ce = torch.empty(E, dtype=torch.float32, device=dev)
+        l_aux = torch.empty((), dtype=torch.float32, device=dev)
+        _gate_check(_L().rtp_top2_gate_fwd(_p(lg), _p(nz), _p(gates), _p(idx), _p(loc), _p(gate_w), _p(valid), _p(me_sum),
+                                           _p(ce), _p(l_aux), S, E, int(capacity), _lib.stream_ptr()), "top2_gate_fwd")
+        ctx.save_for_backward(gates, idx, valid, ce)
+        ctx.in_dtype = logits.dtype
+        ctx.mark_non_differentiable(idx, loc, valid)
+        return l_aux, idx, loc, gate_w, valid
+
+    @staticmethod
+    def backward(ctx, d_l_aux, _di, _dl, d_gate_w, _dv):
+        gates, idx, valid, ce = ctx.saved_tensors
+        S, E = gates.shape
+        dlogits = torch.empty_like(gates)
+        dg = d_gate_w.float().contiguous() if d_gate_w is not None else torch.zeros(S, 2, device=gates.device)
+        dl = d_l_aux.float().contiguous() if d_l_aux is not None else None
+        _gate_check(_L().rtp_top2_gate_bwd(_p(gates), _p(idx), _p(valid), _p(ce), _p(dg), _p(dl), _p(dlogits), S, E,
+                                           _lib.stream_ptr()), "top2_gate_bwd")
+        return dlogits.to(ctx.in_dtype), None, None
+
+
+def top2_gate(logits, capacity, noise=None):
+    """Returns (l_aux, idx[S,2] int32, loc[S,2] int32, gate[S,2] fp32, valid[S,2] uint8); differentiable in `logits`
+    through `gate` and `l_aux`.  `noise` is added to the logits for the second choice (None: no noise)."""
+    return _Top2Gate.apply(logits, noise, capacity)
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, inner):
+        x = x.contiguous()
+        H, hd = x.shape[-2], x.shape[-1]
+        T = x.numel() // (H * hd)
+        y = torch.empty_like(x)
+        cos = cos.float().contiguous()
+        sin = sin.float().contiguous()
+        _gate_check(_L().rtp_rope(_p(x), _p(y), _p(cos), _p(sin), T, H, hd, cos.shape[0], int(inner), 0,
+                                  _lib.stream_ptr()), "rope")
+        ctx.save_for_backward(cos, sin)
+        ctx.inner = int(inner)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        dy = dy.contiguous()
+        H, hd = dy.shape[-2], dy.shape[-1]
+        T = dy.numel() // (H * hd)
+        dx = torch.empty_like(dy)
+        _gate_check(_L().rtp_rope(_p(dy), _p(dx), _p(cos), _p(sin), T, H, hd, cos.shape[0], ctx.inner, 1,
+                                  _lib.stream_ptr()), "rope backward")
+        return dx, None, None, None
+
+
+def rope(x, cos, sin, inner=1):
+    """Rotary position embedding of bf16 `x` [..., H, hd] whose flattened leading dims are tokens; token t sits at
+    position (t // inner) % S, with cos / sin of shape [S, hd / 2] (pairs (x[2i], x[2i+1]) rotate together)."""
+    return _Rope.apply(x, cos, sin, inner)
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
+def conv_out_size(H, W, kernel, stride, padding, dilation):
+    (KH, KW), (sh, sw), (ph, pw), (dh, dw) = _pair(kernel), _pair(stride), _pair(padding), _pair(dilation)
+    return (H + 2 * ph - dh * (KH - 1) - 1) // sh + 1, (W + 2 * pw - dw * (KW - 1) - 1) // sw + 1
+
+
+def im2col(x, kernel, stride=1, padding=0, dilation=1, Kp=None):
+    """Patch matrix [B*OH*OW, Kp] of a contiguous NCHW bf16 tensor; column (c, kh, kw), zero padded up to Kp."""
+    B, Cc, H, W = x.shape
+    (KH, KW), (sh, sw), (ph, pw), (dh, dw) = _pair(kernel), _pair(stride), _pair(padding), _pair(dilation)
+    OH, OW = conv_out_size(H, W, kernel, stride, padding, dilation)
+    Kp = Kp or Cc * KH * KW
+    cols = torch.empty(B * OH * OW, Kp, dtype=x.dtype, device=x.device)
+    rc = _L().rtp_im2col(_p(x), _p(cols), B, Cc, H, W, KH, KW, sh, sw, ph, pw, dh, dw, Kp, _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError("im2col: " + _L().rtp_im2col_last_error().decode())
+    return cols
+
+
+def col2im(dcols, x_shape, kernel, stride=1, padding=0, dilation=1):
+    """Adjoint of im2col: gradient with respect to the NCHW input."""
+    B, Cc, H, W = x_shape
+    (KH, KW), (sh, sw), (ph, pw), (dh, dw) = _pair(kernel), _pair(stride), _pair(padding), _pair(dilation)
+    dx = torch.empty(B, Cc, H, W, dtype=dcols.dtype, device=dcols.device)
+    rc = _L().rtp_col2im(_p(dcols), _p(dx), B, Cc, H, W, KH, KW, sh, sw, ph, pw, dh, dw, dcols.shape[1],
+                         _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError("col2im: " + _L().rtp_im2col_last_error().decode())
+    return dx

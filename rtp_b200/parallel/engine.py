@@ -197,6 +197,55 @@ class _FusedLinearFn(torch.autograd.Function):
         return (None, None, dx.view(ctx.x_shape) if dx is not None else None, *views)
 
 
+class _FusedConvFn(torch.autograd.Function):
+    """Rotated Conv2d on the rotation GEMM kernels: a column-parallel linear over the patch matrix of the input
+    (reference: rtp/module/conv.py:103-114; the flat shard [Cout/N, Cin*kh*kw] + bias is a linear shard as it is)."""
+
+    @staticmethod
+    def forward(ctx, module, x, *params):
+        eng = get_engine(module.ring)
+        conv = module.conv
+        x = x.contiguous()
+        K_ = conv.in_channels * conv.kernel_size[0] * conv.kernel_size[1]
+        cols = K.im2col(x, conv.kernel_size, conv.stride, conv.padding, conv.dilation)
+        lay = module._layout
+        has_bias = conv.bias is not None
+        info = (has_bias, lay.offset_of("bias") if has_bias else -1, _round_up(lay.numel * 2, 16))
+        y2d = linear_fwd_raw(eng, module._full_param, info, cols, False, K_, module.out_channels)
+        OH, OW = K.conv_out_size(x.shape[2], x.shape[3], conv.kernel_size, conv.stride, conv.padding, conv.dilation)
+        ctx.module, ctx.info, ctx.eng, ctx.K_ = module, info, eng, K_
+        ctx.x_shape = x.shape
+        ctx.save_for_backward(cols)
+        return y2d.view(x.shape[0], OH, OW, module.out_channels).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        module, conv = ctx.module, ctx.module.conv
+        (cols,) = ctx.saved_tensors
+        dy2d = dy.permute(0, 2, 3, 1).reshape(-1, module.out_channels)
+        if not dy2d.is_contiguous():
+            dy2d = dy2d.contiguous()
+        dcols, gflat = linear_bwd_raw(ctx.eng, module._full_param, ctx.info, cols, dy2d, False, ctx.K_,
+                                      module.out_channels, need_dx=ctx.needs_input_grad[1])
+        module._last_flat_grad = gflat
+        dx = None
+        if dcols is not None:
+            dx = K.col2im(dcols, ctx.x_shape, conv.kernel_size, conv.stride, conv.padding, conv.dilation)
+        return (None, dx, *module._layout.views(gflat))
+
+
+def fused_conv_ok(module, x) -> bool:
+    """The patch matrix must be a legal TMA operand (row pitch a multiple of 16 bytes) and the convolution plain."""
+    conv = module.conv
+    K_ = conv.in_channels * conv.kernel_size[0] * conv.kernel_size[1]
+    return (K_ % 8 == 0 and conv.groups == 1 and conv.padding_mode == "zeros" and not isinstance(conv.padding, str)
+            and x.dim() == 4)
+
+
+def fused_conv(module, x):
+    return _FusedConvFn.apply(module, x, *module.shard_parameters())
+
+
 def fused_linear(module, x, row=False):
     return _FusedLinearFn.apply(module, row, x, *module.shard_parameters())
 

@@ -213,3 +213,76 @@ def test_moe_dispatch_combine_by_index_matches_dense_einsums():
     slot = torch.where(valid, idx * cap + loc, torch.zeros_like(idx))
     ref_dg = (dy.float().unsqueeze(1) * eo.detach().float().reshape(E * cap, M)[slot]).sum(-1) * valid
     _close(gate.grad, ref_dg, 2e-2)
+
+
+@pytest.mark.parametrize("S,E,cf", [(64, 8, 1.0), (2048, 16, 1.0), (1500, 60, 0.5), (96, 2, 2.0)])
+def test_top2_gate_kernels_match_reference_routing(S, E, cf):
+    """Fused gating kernels against the dense PyTorch restatement of the reference (same injected noise)."""
+    from rtp_b200.module.top2gate import top2_routing
+    from rtp_b200.parallel.context import set_backend
+    torch.manual_seed(3)
+    logits = (torch.randn(S, E, device="cuda") * 2).requires_grad_(True)
+    noise = torch.randn(S, E, device="cuda")
+    w = torch.randn(S, 2, device="cuda")
+    set_backend("functional")
+    try:
+        ref = top2_routing(logits, cf, noise)
+        (ref[3] * w).sum().add(ref[0] * 7.0).backward()
+    finally:
+        set_backend("auto")
+    g_ref = logits.grad.clone()
+    logits.grad = None
+    out = top2_routing(logits, cf, noise)
+    (out[3] * w).sum().add(out[0] * 7.0).backward()
+    assert torch.equal(out[1], ref[1]), "experts differ"
+    assert torch.equal(out[4], ref[4]), "validity differs"
+    assert torch.equal(out[2] * out[4], ref[2] * ref[4]), "slots differ"
+    assert out[5] == ref[5]
+    _close(out[3], ref[3], 1e-5)
+    assert abs(out[0].item() - ref[0].item()) < 1e-6
+    _close(logits.grad, g_ref, 1e-4)
+
+
+def test_rope_kernel():
+    from rtp_b200.ops import kernels as K
+    from rtp_b200.models.llama import rope_tables
+    torch.manual_seed(0)
+    B, S, H, hd = 3, 50, 4, 64
+    x = torch.randn(B, S, H, hd, device="cuda", dtype=BF, requires_grad=True)
+    cos, sin = rope_tables(S, hd, 10000.0, "cuda")
+    xr = x.detach().float().requires_grad_(True)
+    x1, x2 = xr[..., 0::2], xr[..., 1::2]
+    c, s = cos[None, :, None, :], sin[None, :, None, :]
+    ref = torch.stack([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1).flatten(-2)
+    y = K.rope(x, cos, sin)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ref.backward(dy.float())
+    _close(y, ref, 1e-2)
+    _close(x.grad, xr.grad, 1e-2)
+
+
+@pytest.mark.parametrize("cin,cout,k,stride,pad", [(32, 64, 3, 1, 0), (16, 32, 3, 2, 1), (8, 24, 5, 1, 2)])
+def test_rotated_conv_on_gemm_kernels(cin, cout, k, stride, pad):
+    """Conv2d = im2col + rotation GEMM (+ col2im in backward) against F.conv2d in fp32."""
+    import torch.nn.functional as F
+    from rtp_b200.module.conv import ColumnParallelConv2d
+    from rtp_b200.ops import _lib
+    torch.manual_seed(0)
+    ref = torch.nn.Conv2d(cin, cout, k, stride=stride, padding=pad).cuda()
+    m = ColumnParallelConv2d(cin, cout, k, stride=stride, padding=pad, Conv2d_layer=ref, world_size=1, rank=0).cuda().to(BF)
+    x = torch.randn(4, cin, 14, 14, device="cuda", dtype=BF, requires_grad=True)
+    y = m(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    xr = x.detach().float().requires_grad_(True)
+    w = ref.weight.detach().to(BF).float().requires_grad_(True)
+    b = ref.bias.detach().to(BF).float().requires_grad_(True)
+    yr = F.conv2d(xr, w, b, stride=stride, padding=pad)
+    yr.backward(dy.float())
+    _close(y, yr, 2e-2)
+    _close(x.grad, xr.grad, 3e-2)
+    _close(m.conv.weight.grad, w.grad, 3e-2)
+    _close(m.conv.bias.grad, b.grad, 3e-2)
