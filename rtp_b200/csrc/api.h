@@ -68,6 +68,12 @@ typedef struct {
   int act;                         // activation applied to y (column mode only)
   float drop_p; unsigned long long seed, offset;  // dropout applied to y after the activation
   const unsigned long long* step_ptr;             // optional device step counter mixed into the dropout offset
+  // Cross-launch prefetch (all zero = every launch pushes the shards it needs itself).  The launch reads visiting shards
+  // from weight-slot bank `bank`; with no_self_push = 1 they were pushed there by the previous launch.  If next_home is
+  // set, this launch also pushes that shard (the home shard of the NEXT rotated linear on this stream, which must read
+  // bank 1 - bank with no_self_push = 1) to the ranks that will use it: next_kind 0 = forward order, 1 = backward order.
+  int bank, no_self_push;
+  const void* next_home; unsigned long long next_bytes; int next_kind;
 } RtpLinearFwd;
 int rtp_linear_fwd(const RtpRing* ring, const RtpLinearFwd* op, void* stream);
 
@@ -82,6 +88,8 @@ typedef struct {
   const void* mask; long long ldmask; float mask_scale;  // optional mask applied to dx (activation/dropout backward)
   int dx_accumulate;               // 1: add the input gradient to what dx already holds
   int grad_accumulate;             // 1: add the weight gradient to what grad_home already holds
+  int bank, no_self_push;          // cross-launch prefetch, see RtpLinearFwd
+  const void* next_home; unsigned long long next_bytes; int next_kind;
 } RtpLinearBwd;
 int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream);
 

@@ -225,16 +225,42 @@ int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cuda
 // ------------------------------------------------------------------------------------------------
 // workspace layout
 // ------------------------------------------------------------------------------------------------
-constexpr unsigned long long kFlagBytes = 8192;
+constexpr unsigned long long kFlagBytes = RTP_FLAG_BYTES;
 static_assert(sizeof(RtpFlagBlock) <= kFlagBytes, "flag block too large");
 RtpFlagBlock* ws_flags(void* ws) { return reinterpret_cast<RtpFlagBlock*>(ws); }
 uint8_t* ws_wslot(void* ws, unsigned long long slot_bytes, int i) {
   return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)i * slot_bytes;
 }
 uint8_t* ws_gslot(void* ws, unsigned long long slot_bytes, int i) {
-  return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)(RTP_NUM_SLOTS + i) * slot_bytes;
+  return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)(RTP_NUM_WBANKS * RTP_NUM_SLOTS + i) * slot_bytes;
 }
 int mod(int a, int n) { return ((a % n) + n) % n; }
+
+// Cross-launch prefetch: pushes the home shard of the NEXT rotated linear into weight-slot bank `bank` of the ranks
+// that will read it there (kind 0: forward visiting order, 1: backward visiting order).  The fills are counted by the
+// launch that consumes them.
+int add_prefetch_pushes(const RtpRing& R, RtpProgram& P, const void* home, unsigned long long bytes, int bank, int kind) {
+  const int N = R.world, r = R.rank;
+  if (!home || N == 1) return 0;
+  if (bytes > R.slot_bytes) return fail("prefetched shard larger than workspace slot");
+  if (bytes % 16) return fail("next_bytes must be a multiple of 16");
+  if (bank < 0 || bank >= RTP_NUM_WBANKS) return fail("bank out of range");
+  for (int s = 0; s + 1 < N; ++s) {
+    if (P.n_pushes >= RTP_MAX_PUSHES) return fail("too many pushes");
+    RtpPush& pu = P.pushes[P.n_pushes++];
+    memset(&pu, 0, sizeof(pu));
+    const int t = kind == 0 ? mod(r - (s + 1), N) : mod(r + 1 + s, N);
+    const int slot = bank * RTP_NUM_SLOTS + s;
+    pu.src = home;
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
+    pu.bytes = bytes;
+    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
+    pu.credit_ctr = RTP_CTR_W0 + slot;
+    pu.credit_rel = 0;
+    pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
+  }
+  return 0;
+}
 
 // ------------------------------------------------------------------------------------------------
 // program builders
@@ -250,6 +276,8 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
   const int Ks = col ? op.in_features : op.in_features / N;    // columns of a weight shard
   if (N > 1 && op.shard_bytes > R.slot_bytes) return fail("shard larger than workspace slot");
   if (op.shard_bytes % 16) return fail("shard_bytes must be a multiple of 16");
+  if (op.bank < 0 || op.bank >= RTP_NUM_WBANKS) return fail("bank out of range");
+  const int wb = op.bank * RTP_NUM_SLOTS;   // first weight slot of the bank this launch reads
   void* ws = R.ws[r];
   P.flags = ws ? ws_flags(ws) : nullptr;
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
@@ -261,13 +289,13 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
   const int b_box = pair_mode() ? bn / 2 : 128;
   if (make_map_k(&P.maps[1], op.home, Os, Ks, Ks, b_box)) return -1;
   for (int i = 1; i < N; ++i)
-    if (make_map_k(&P.maps[1 + i], ws_wslot(ws, R.slot_bytes, i - 1), Os, Ks, Ks, b_box)) return -1;
+    if (make_map_k(&P.maps[1 + i], ws_wslot(ws, R.slot_bytes, wb + i - 1), Os, Ks, Ks, b_box)) return -1;
   P.n_phases = N;
   for (int i = 0; i < N; ++i) {
     RtpPhase& ph = P.phases[i];
     init_phase(ph);
     const int j = mod(r + i, N);
-    const int slot = i - 1;   // step i reads weight slot i-1 (filled once per launch by the owner of shard j)
+    const int slot = wb + i - 1;   // step i reads weight slot i-1 of the bank (filled once by the owner of shard j)
     const uint8_t* src = (i == 0) ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, slot);
     ph.a_map = 0;
     ph.b_map = (i == 0) ? 1 : 1 + i;
@@ -296,15 +324,16 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
       ph.wait_ctr[0] = RTP_CTR_W0 + slot;
       ph.wait_rel[0] = 0;
       ph.done_ctr[0] = RTP_CTR_W0 + slot;
+      P.uses_inc[RTP_CTR_W0 + slot] = 1;
     }
     set_vec_ok(ph);
   }
-  P.n_pushes = N - 1;
-  for (int i = 0; i + 1 < N; ++i) {
+  P.n_pushes = op.no_self_push ? 0 : N - 1;
+  for (int i = 0; i + 1 < N && !op.no_self_push; ++i) {
     RtpPush& pu = P.pushes[i];
     memset(&pu, 0, sizeof(pu));
     const int t = mod(r - (i + 1), N);
-    const int slot = i;
+    const int slot = wb + i;
     pu.src = op.home;
     pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
     pu.bytes = op.shard_bytes;
@@ -312,9 +341,8 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
     pu.credit_ctr = RTP_CTR_W0 + slot;
     pu.credit_rel = 0;
     pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
-    P.uses_inc[RTP_CTR_W0 + slot] = 1;
   }
-  return 0;
+  return add_prefetch_pushes(R, P, op.next_home, op.next_bytes, 1 - op.bank, op.next_kind);
 }
 
 int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
@@ -333,6 +361,8 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   const int Ks = col ? op.in_features : op.in_features / N;
   if (N > 1 && op.shard_bytes > R.slot_bytes) return fail("shard larger than workspace slot");
   if (op.grad_accumulate && N > 1) return fail("grad_accumulate is only supported on a 1-rank ring");
+  if (op.bank < 0 || op.bank >= RTP_NUM_WBANKS) return fail("bank out of range");
+  const int wb = op.bank * RTP_NUM_SLOTS;   // first weight slot of the bank this launch reads
   void* ws = R.ws[r];
   P.flags = ws ? ws_flags(ws) : nullptr;
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
@@ -346,7 +376,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
     if (make_map_k(&P.maps[2], op.dy, op.M, op.out_features, op.ldy)) return -1;
     if (make_map_mn(&P.maps[3], op.home, Ks, Os, Ks)) return -1;
     for (int s = 0; s + 1 < N; ++s)
-      if (make_map_mn(&P.maps[4 + s], ws_wslot(ws, R.slot_bytes, s), Ks, Os, Ks)) return -1;
+      if (make_map_mn(&P.maps[4 + s], ws_wslot(ws, R.slot_bytes, wb + s), Ks, Os, Ks)) return -1;
   }
   int np = 0;
   for (int s = 0; s < N; ++s) {
@@ -406,8 +436,9 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
         ph.ldmask = op.ldmask; ph.mask_scale = op.mask_scale;
       }
       if (!last) {
-        ph.wait_ctr[0] = RTP_CTR_W0 + s; ph.wait_rel[0] = 0;
-        ph.done_ctr[0] = RTP_CTR_W0 + s;
+        ph.wait_ctr[0] = RTP_CTR_W0 + wb + s; ph.wait_rel[0] = 0;
+        ph.done_ctr[0] = RTP_CTR_W0 + wb + s;
+        P.uses_inc[RTP_CTR_W0 + wb + s] = 1;
       }
       set_vec_ok(ph);
     }
@@ -430,21 +461,20 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   }
   P.n_phases = np;
   // weight pushes: the owner q sends its home shard to rank q+1+s, which uses it at its step s (weight slot s)
-  P.n_pushes = op.dx ? N - 1 : 0;
-  for (int s = 0; s + 1 < N && op.dx; ++s) {
+  P.n_pushes = (op.dx && !op.no_self_push) ? N - 1 : 0;
+  for (int s = 0; s + 1 < N && op.dx && !op.no_self_push; ++s) {
     RtpPush& pu = P.pushes[s];
     memset(&pu, 0, sizeof(pu));
     const int t = mod(r + 1 + s, N);
     pu.src = op.home;
-    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, s);
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, wb + s);
     pu.bytes = op.shard_bytes;
-    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + s].v;
-    pu.credit_ctr = RTP_CTR_W0 + s;
+    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + wb + s].v;
+    pu.credit_ctr = RTP_CTR_W0 + wb + s;
     pu.credit_rel = 0;
-    pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + s].v;
-    P.uses_inc[RTP_CTR_W0 + s] = 1;
+    pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + wb + s].v;
   }
-  return 0;
+  return add_prefetch_pushes(R, P, op.next_home, op.next_bytes, 1 - op.bank, op.next_kind);
 }
 
 int build_expert_fwd(const RtpRing& R, const RtpExpertFwd& op, RtpProgram& P) {
@@ -885,7 +915,7 @@ int rtp_linear_bwd_emu(const RtpRing* rings, const RtpLinearBwd* ops, int world,
 }
 
 // ------------------------------------------------------------------------------------- workspace
-unsigned long long rtp_ws_bytes(unsigned long long slot_bytes) { return kFlagBytes + 2 * RTP_NUM_SLOTS * slot_bytes; }
+unsigned long long rtp_ws_bytes(unsigned long long slot_bytes) { return kFlagBytes + (RTP_NUM_WBANKS + 1) * RTP_NUM_SLOTS * slot_bytes; }
 int rtp_ws_create(unsigned long long slot_bytes, void** out) {
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, rtp_ws_bytes(slot_bytes));

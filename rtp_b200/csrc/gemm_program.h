@@ -11,14 +11,16 @@
 
 #define RTP_MAX_MAPS 12
 #define RTP_MAX_PHASES 18
-#define RTP_MAX_PUSHES 8
+#define RTP_MAX_PUSHES 16
 #define RTP_MAX_EMU_RANKS 4
 
 // indices into FlagBlock::arrive / ::done / ::uses
-#define RTP_NUM_SLOTS 8            // weight slots W0..W7 and gradient slots G0..G7 per rank
+#define RTP_NUM_SLOTS 8            // slots per bank: two banks of weight slots (W0..W7, W8..W15) and gradient slots G0..G7
+#define RTP_NUM_WBANKS 2           // a launch reads the weight shards of one bank while the next launch's shards arrive in the other
 #define RTP_CTR_W0 0
-#define RTP_CTR_G0 8
-#define RTP_NUM_CTR 16
+#define RTP_CTR_G0 (RTP_NUM_WBANKS * RTP_NUM_SLOTS)
+#define RTP_NUM_CTR (RTP_CTR_G0 + RTP_NUM_SLOTS)
+#define RTP_FLAG_BYTES 16384       // bytes reserved for the flag block at the start of a workspace
 #define RTP_MAX_WAITS 8
 
 // Per-rank flag block (peer-mapped). Every word sits in its own 128-byte line.

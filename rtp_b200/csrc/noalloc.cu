@@ -2,13 +2,15 @@
 #include <cuda_runtime.h>
 #include <string>
 #include "api.h"
+#include "gemm_program.h"
 #include "kernels.h"
 #include "noalloc.h"
 
 namespace {
 
-// [0, 8192): flag/status block of the rotation kernel.  [8192, ...): fp32 column sums of dy.
+// [0, RTP_FLAG_BYTES): flag/status block of the rotation kernel.  [RTP_FLAG_BYTES, ...): fp32 column sums of dy.
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not a device pointer.
+static_assert(RTP_NOALLOC_SCRATCH_BYTES >= RTP_FLAG_BYTES + 4 * RTP_NOALLOC_MAX_OUT_FEATURES, "scratch too small");
 static __device__ __align__(256) unsigned char g_noalloc_scratch[RTP_NOALLOC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
@@ -53,9 +55,9 @@ int rtp_linear_bwd_noalloc(const void* x, long long ldx, const void* dy, long lo
   if (scratch_for_current_device(&scratch)) return -1;
   cudaStream_t s = (cudaStream_t)stream;
   // the flag/status block must start at zero; the column sums are zeroed by rtp_colsum itself
-  cudaError_t e = cudaMemsetAsync(scratch, 0, 8192, s);
+  cudaError_t e = cudaMemsetAsync(scratch, 0, RTP_FLAG_BYTES, s);
   if (e != cudaSuccess) return nfail(std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
-  float* dbias = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + 8192);
+  float* dbias = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + RTP_FLAG_BYTES);
   if (bias_off >= 0) {
     if (rtp_colsum(dy, ldy, M, out_features, dbias, stream)) return nfail(rtp_kernels_last_error());
   }

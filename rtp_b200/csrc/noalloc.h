@@ -28,7 +28,7 @@ extern "C" {
 #endif
 
 #define RTP_NOALLOC_MAX_OUT_FEATURES 65536
-#define RTP_NOALLOC_SCRATCH_BYTES (8192 + 4 * RTP_NOALLOC_MAX_OUT_FEATURES)
+#define RTP_NOALLOC_SCRATCH_BYTES (16384 + 4 * RTP_NOALLOC_MAX_OUT_FEATURES)   /* flag block (RTP_FLAG_BYTES) + column sums */
 
 int rtp_linear_bwd_noalloc(const void* x, long long ldx, const void* dy, long long ldy, const void* w,
                            long long bias_off, int M, int in_features, int out_features, void* dx, long long lddx,

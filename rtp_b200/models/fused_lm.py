@@ -17,6 +17,7 @@ The math is the model's: post-LN decoder layers ``x = LN1(x + drop(MHA(x)))``, `
 ``FF = drop(lin2(drop(relu(lin1(x)))))`` (reference: rtp/models/transformer_lm_rtp.py:77-89,171-179).
 """
 import math
+import os
 from typing import Optional
 
 import torch
@@ -64,6 +65,11 @@ class FusedLMTrainer:
         self.dev = p0.device
         self.eng = E.get_engine(self.ring)
         self._build_descriptors()
+        # weight shards of the next rotated linear travel while the current one computes (RTP_PREFETCH=0: every launch
+        # pushes its own shards at its start)
+        self.prefetch = self.N > 1 and os.environ.get("RTP_PREFETCH", "1") != "0"
+        self._build_chain()
+        self._ci = 0
         self._graph = None
         self._static = None
         self.step_dev = torch.zeros(1, dtype=torch.int64, device=self.dev)       # Adam step
@@ -210,22 +216,41 @@ class FusedLMTrainer:
         if self._counting:
             self.launches_per_step += n
 
+    def _chain_args(self, d, kind):
+        """Cross-launch prefetch: the rotated linears of a step form one chain (forward order, then backward order).  Each
+        launch reads its visiting shards from one weight-slot bank, where the previous launch of the chain pushed them,
+        and pushes the shards of the next launch into the other bank while it computes."""
+        if not self.prefetch:
+            return {}
+        k = self._ci
+        self._ci += 1
+        assert self._chain[k] == (id(d), kind), "the chain of rotated linears changed between steps"
+        nxt = self._chain_desc[k + 1] if k + 1 < len(self._chain_desc) else None
+        return dict(bank=k & 1, pushed=k > 0, next_flat=nxt[0].flat if nxt else None, next_kind=nxt[1] if nxt else 0)
+
+    def _build_chain(self):
+        fwd = [l[n] for l in self.layers for n in ("qkv", "out", "ff1", "ff2")] + [self.head]
+        bwd = [self.head] + [l[n] for l in reversed(self.layers) for n in ("ff2", "ff1", "out", "qkv")]
+        self._chain_desc = [(d, 0) for d in fwd] + [(d, 1) for d in bwd]
+        self._chain = [(id(d), k) for d, k in self._chain_desc]
+
     def _lin_fwd(self, d, x, out, act=0, drop_p=0.0, offset=0):
         E.linear_fwd_raw(self.eng, d.flat, d.info, x, d.row, d.in_f, d.out_f, act=act, drop_p=drop_p, seed=self.seed,
-                         offset=offset, out=out, step=self.rng_step)
+                         offset=offset, out=out, step=self.rng_step, **self._chain_args(d, 0))
         self._count(1)
 
     def _lin_bwd(self, d, x, dy, st, dx_out=None, need_dx=True, mask=None, mask_scale=1.0, dx_accumulate=False):
         dbuf = st["dbias"][: d.out_f]
         E.linear_bwd_raw(self.eng, d.flat, d.info, x, dy, d.row, d.in_f, d.out_f, need_dx=need_dx, mask=mask,
                          mask_scale=mask_scale, grad_out=d.gflat, dx_out=dx_out, dx_accumulate=dx_accumulate,
-                         dbias_buf=dbuf)
+                         dbias_buf=dbuf, **self._chain_args(d, 1))
         self._count(3)  # memset + colsum + fused bwd
 
     def _step_impl(self, st):
         S, B, M, D, L = st["S"], st["B"], st["M"], self.D, self.L
         p = self.p_drop
         rs = self.rng_step
+        self._ci = 0
         # ---------------- forward
         self._embed_fwd(st)
         x = st["x0"]

@@ -61,6 +61,8 @@ class LinearFwd(C.Structure):
         ("y", C.c_void_p), ("ldy", C.c_longlong),
         ("act", C.c_int),
         ("drop_p", C.c_float), ("seed", C.c_ulonglong), ("offset", C.c_ulonglong), ("step_ptr", C.c_void_p),
+        ("bank", C.c_int), ("no_self_push", C.c_int),
+        ("next_home", C.c_void_p), ("next_bytes", C.c_ulonglong), ("next_kind", C.c_int),
     ]
 
 
@@ -75,6 +77,8 @@ class LinearBwd(C.Structure):
         ("dbias_full", C.c_void_p),
         ("mask", C.c_void_p), ("ldmask", C.c_longlong), ("mask_scale", C.c_float),
         ("dx_accumulate", C.c_int), ("grad_accumulate", C.c_int),
+        ("bank", C.c_int), ("no_self_push", C.c_int),
+        ("next_home", C.c_void_p), ("next_bytes", C.c_ulonglong), ("next_kind", C.c_int),
     ]
 
 

@@ -128,8 +128,18 @@ def _linear_desc(module, row):
     return has_bias, bias_off, shard_bytes
 
 
+def _set_prefetch(op, bank, pushed, next_flat, next_kind):
+    """Cross-launch prefetch fields of a linear op: read weight-slot bank ``bank`` (already filled by the previous launch
+    if ``pushed``) and push ``next_flat``, the home shard of the next rotated linear on the stream, into the other bank."""
+    op.bank, op.no_self_push = int(bank), int(bool(pushed))
+    if next_flat is not None:
+        op.next_home = next_flat.data_ptr()
+        op.next_bytes = _round_up(next_flat.numel() * 2, 16)
+        op.next_kind = int(next_kind)
+
+
 def linear_fwd_raw(eng, flat, layout_info, x2d, row, in_f, out_f, act=0, drop_p=0.0, seed=0, offset=0, out=None,
-                   step=None):
+                   step=None, bank=0, pushed=False, next_flat=None, next_kind=0):
     has_bias, bias_off, shard_bytes = layout_info
     M = x2d.shape[0]
     y = out if out is not None else torch.empty(M, out_f, dtype=torch.bfloat16, device=x2d.device)
@@ -140,12 +150,14 @@ def linear_fwd_raw(eng, flat, layout_info, x2d, row, in_f, out_f, act=0, drop_p=
     op.y, op.ldy = y.data_ptr(), y.stride(0)
     op.act, op.drop_p, op.seed, op.offset = act, drop_p, seed, offset
     op.step_ptr = step.data_ptr() if step is not None else None
+    _set_prefetch(op, bank, pushed, next_flat, next_kind)
     _lib.check(_lib.lib().rtp_linear_fwd(C.byref(eng.ring), C.byref(op), _lib.stream_ptr()), "rtp_linear_fwd")
     return y
 
 
 def linear_bwd_raw(eng, flat, layout_info, x2d, dy2d, row, in_f, out_f, need_dx=True, mask=None, mask_scale=1.0,
-                   grad_out=None, dx_out=None, dx_accumulate=False, dbias_buf=None):
+                   grad_out=None, dx_out=None, dx_accumulate=False, dbias_buf=None, bank=0, pushed=False, next_flat=None,
+                   next_kind=1):
     has_bias, bias_off, shard_bytes = layout_info
     M = x2d.shape[0]
     gflat = grad_out if grad_out is not None else torch.empty_like(flat)
@@ -165,6 +177,7 @@ def linear_bwd_raw(eng, flat, layout_info, x2d, dy2d, row, in_f, out_f, need_dx=
     if mask is not None:
         op.mask, op.ldmask, op.mask_scale = mask.data_ptr(), mask.stride(0), mask_scale
     op.dx_accumulate = int(dx_accumulate)
+    _set_prefetch(op, bank, pushed, next_flat, next_kind)
     _lib.check(_lib.lib().rtp_linear_bwd(C.byref(eng.ring), C.byref(op), _lib.stream_ptr()), "rtp_linear_bwd")
     return dx, gflat
 

@@ -253,3 +253,81 @@ def test_rotating_experts_fwd_bwd(world, L):
             _close(gfs[r][e * stride + bias_off:e * stride + bias_off + OUT], gb, 2e-2, f"expert db rank {r} e {e}")
     for w in wss:
         lib.rtp_ws_destroy(w)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_cross_launch_prefetch_chain(world):
+    """Two rotated linears chained A -> B -> B' (backward of B) -> A': every launch reads one weight-slot bank, filled
+    by the launch before it, and pushes the next launch's shards into the other bank.  Repeated twice: the counters of
+    both banks must stay consistent from step to step."""
+    from rtp_b200.ops import _lib, kernels as K
+    L = _lib.lib()
+    torch.manual_seed(0)
+    M, D, H = 512, 1024, 2048
+    G_ = 148 // world
+
+    def shard(full_w, full_b, r):
+        Os, Ks = full_w.shape[0] // world, full_w.shape[1]
+        bias_off = Os * Ks
+        flat = torch.zeros(bias_off + Os, device="cuda", dtype=BF)
+        flat[:bias_off] = full_w[r * Os:(r + 1) * Os].reshape(-1)
+        flat[bias_off:] = full_b[r * Os:(r + 1) * Os]
+        return flat, bias_off
+
+    wa = (torch.randn(H, D, device="cuda") * 0.05).to(BF); ba = (torch.randn(H, device="cuda") * 0.1).to(BF)
+    wb = (torch.randn(D, H, device="cuda") * 0.05).to(BF); bb = (torch.randn(D, device="cuda") * 0.1).to(BF)
+    slot_bytes = ((H * D // world + H) * 2 + 65535) // 65536 * 65536
+    wss, rings = _rings(world, slot_bytes, G_, L, _lib)
+    fa, fb = [shard(wa, ba, r) for r in range(world)], [shard(wb, bb, r) for r in range(world)]
+    xs = [torch.randn(M, D, device="cuda", dtype=BF) for _ in range(world)]
+    hs = [torch.zeros(M, H, device="cuda", dtype=BF) for _ in range(world)]
+    ys = [torch.zeros(M, D, device="cuda", dtype=BF) for _ in range(world)]
+    dys = [torch.randn(M, D, device="cuda", dtype=BF) for _ in range(world)]
+    dhs = [torch.zeros(M, H, device="cuda", dtype=BF) for _ in range(world)]
+    dxs = [torch.zeros(M, D, device="cuda", dtype=BF) for _ in range(world)]
+    ga = [torch.zeros_like(f[0]) for f in fa]; gb = [torch.zeros_like(f[0]) for f in fb]
+    A, B = (_lib.LinearFwd * world)(), (_lib.LinearFwd * world)()
+    Bb, Ab = (_lib.LinearBwd * world)(), (_lib.LinearBwd * world)()
+    for r in range(world):
+        for op, (flat, boff), x, y, inf, outf in ((A[r], fa[r], xs[r], hs[r], D, H), (B[r], fb[r], hs[r], ys[r], H, D)):
+            op.mode, op.M, op.in_features, op.out_features = 0, M, inf, outf
+            op.home, op.bias_off, op.shard_bytes = flat.data_ptr(), boff, flat.numel() * 2
+            op.x, op.ldx, op.y, op.ldy = x.data_ptr(), inf, y.data_ptr(), outf
+        A[r].bank, A[r].no_self_push = 0, 0
+        A[r].next_home, A[r].next_bytes, A[r].next_kind = fb[r][0].data_ptr(), fb[r][0].numel() * 2, 0
+        B[r].bank, B[r].no_self_push = 1, 1
+        B[r].next_home, B[r].next_bytes, B[r].next_kind = fb[r][0].data_ptr(), fb[r][0].numel() * 2, 1
+        for op, (flat, boff), x, dy, dx, g, inf, outf in ((Bb[r], fb[r], hs[r], dys[r], dhs[r], gb[r], H, D),
+                                                           (Ab[r], fa[r], xs[r], dhs[r], dxs[r], ga[r], D, H)):
+            op.mode, op.M, op.in_features, op.out_features = 0, M, inf, outf
+            op.home, op.bias_off, op.shard_bytes = flat.data_ptr(), boff, flat.numel() * 2
+            op.x, op.ldx, op.dy, op.ldy = x.data_ptr(), inf, dy.data_ptr(), outf
+            op.dx, op.lddx, op.grad_home = dx.data_ptr(), inf, g.data_ptr()
+        Bb[r].bank, Bb[r].no_self_push = 0, 1
+        Bb[r].next_home, Bb[r].next_bytes, Bb[r].next_kind = fa[r][0].data_ptr(), fa[r][0].numel() * 2, 1
+        Ab[r].bank, Ab[r].no_self_push = 1, 1
+    for _ in range(2):
+        _lib.check(L.rtp_linear_fwd_emu(rings, A, world, _lib.stream_ptr()), "A")
+        _lib.check(L.rtp_linear_fwd_emu(rings, B, world, _lib.stream_ptr()), "B")
+        _lib.check(L.rtp_linear_bwd_emu(rings, Bb, world, _lib.stream_ptr()), "B'")
+        _lib.check(L.rtp_linear_bwd_emu(rings, Ab, world, _lib.stream_ptr()), "A'")
+    torch.cuda.synchronize()
+    _status_ok(wss, L, _lib)
+    dwa = torch.zeros(H, D, device="cuda"); dwb = torch.zeros(D, H, device="cuda")
+    for r in range(world):
+        h = xs[r].float() @ wa.float().t() + ba.float()
+        _close(hs[r], h, 1.5e-2, f"A rank {r}")
+        hb = hs[r].float()
+        _close(ys[r], hb @ wb.float().t() + bb.float(), 1.5e-2, f"B rank {r}")
+        dh = dys[r].float() @ wb.float()
+        _close(dhs[r], dh, 2e-2, f"B' dx rank {r}")
+        _close(dxs[r], dhs[r].float() @ wa.float(), 2e-2, f"A' dx rank {r}")
+        dwb += dys[r].float().t() @ hb
+        dwa += dhs[r].float().t() @ xs[r].float()
+    for r in range(world):
+        Os = D // world
+        _close(gb[r][:Os * H].view(Os, H), dwb[r * Os:(r + 1) * Os], 3e-2, f"B' dW rank {r}")
+        Os = H // world
+        _close(ga[r][:Os * D].view(Os, D), dwa[r * Os:(r + 1) * Os], 3e-2, f"A' dW rank {r}")
+    for w in wss:
+        L.rtp_ws_destroy(w)
