@@ -152,15 +152,17 @@ int rtp_linear_bwd_emu(const RtpRing* rings, const RtpLinearBwd* ops, int world,
 
 // ------------------------------------------------------------------------------------- workspace
 unsigned long long rtp_ws_bytes(unsigned long long slot_bytes);
-int rtp_ws_create(unsigned long long slot_bytes, void** out);   // cudaMalloc + zero flag block
+int rtp_ws_create(unsigned long long slot_bytes, void** out);   // cudaMalloc + zero flag block; large enough for any ring size
+unsigned long long rtp_ws_bytes_world(unsigned long long slot_bytes, int world);
+int rtp_ws_create_world(unsigned long long slot_bytes, int world, void** out);   // sized for rings of exactly `world` ranks
 int rtp_ws_destroy(void* ws);
 int rtp_ws_reset(void* ws, void* stream);                        // zero the flag block
 int rtp_ws_ipc_get(void* ws, void* handle64);                    // 64-byte cudaIpcMemHandle
 int rtp_ws_ipc_open(const void* handle64, void** out);
 int rtp_ws_ipc_close(void* mapped);
 int rtp_ws_status(void* ws, unsigned long long* host_out, void* stream);  // reads the status word (synchronises stream)
-void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i);
-void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i);
+void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i, int world);   // logical weight slot i = bank * 8 + index
+void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i, int world);
 int rtp_sm_count(void);
 const char* rtp_last_error(void);
 void rtp_set_pair_mode(int on);        // CTA pairs (cta_group::2 UMMA, half of the B tile per SM): 1 always, 0 never, -1 automatic (default; env RTP_PAIR=0/1 overrides)

@@ -228,11 +228,15 @@ int launch(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cuda
 constexpr unsigned long long kFlagBytes = RTP_FLAG_BYTES;
 static_assert(sizeof(RtpFlagBlock) <= kFlagBytes, "flag block too large");
 RtpFlagBlock* ws_flags(void* ws) { return reinterpret_cast<RtpFlagBlock*>(ws); }
-uint8_t* ws_wslot(void* ws, unsigned long long slot_bytes, int i) {
-  return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)i * slot_bytes;
+// Physical layout of a workspace of a ring of `world` ranks: [flag block][bank 0: world-1 weight slots][bank 1: world-1
+// weight slots][world gradient slots].  `i` is the logical weight slot (bank * RTP_NUM_SLOTS + index in the bank).
+uint8_t* ws_wslot(void* ws, unsigned long long slot_bytes, int i, int world) {
+  const int bank = i / RTP_NUM_SLOTS, idx = i % RTP_NUM_SLOTS;
+  return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)(bank * (world - 1) + idx) * slot_bytes;
 }
-uint8_t* ws_gslot(void* ws, unsigned long long slot_bytes, int i) {
-  return reinterpret_cast<uint8_t*>(ws) + kFlagBytes + (unsigned long long)(RTP_NUM_WBANKS * RTP_NUM_SLOTS + i) * slot_bytes;
+uint8_t* ws_gslot(void* ws, unsigned long long slot_bytes, int i, int world) {
+  return reinterpret_cast<uint8_t*>(ws) + kFlagBytes +
+         (unsigned long long)(RTP_NUM_WBANKS * (world - 1) + i) * slot_bytes;
 }
 int mod(int a, int n) { return ((a % n) + n) % n; }
 
@@ -252,7 +256,7 @@ int add_prefetch_pushes(const RtpRing& R, RtpProgram& P, const void* home, unsig
     const int t = kind == 0 ? mod(r - (s + 1), N) : mod(r + 1 + s, N);
     const int slot = bank * RTP_NUM_SLOTS + s;
     pu.src = home;
-    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot, R.world);
     pu.bytes = bytes;
     pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
     pu.credit_ctr = RTP_CTR_W0 + slot;
@@ -289,14 +293,14 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
   const int b_box = pair_mode() ? bn / 2 : 128;
   if (make_map_k(&P.maps[1], op.home, Os, Ks, Ks, b_box)) return -1;
   for (int i = 1; i < N; ++i)
-    if (make_map_k(&P.maps[1 + i], ws_wslot(ws, R.slot_bytes, wb + i - 1), Os, Ks, Ks, b_box)) return -1;
+    if (make_map_k(&P.maps[1 + i], ws_wslot(ws, R.slot_bytes, wb + i - 1, R.world), Os, Ks, Ks, b_box)) return -1;
   P.n_phases = N;
   for (int i = 0; i < N; ++i) {
     RtpPhase& ph = P.phases[i];
     init_phase(ph);
     const int j = mod(r + i, N);
     const int slot = wb + i - 1;   // step i reads weight slot i-1 of the bank (filled once by the owner of shard j)
-    const uint8_t* src = (i == 0) ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, slot);
+    const uint8_t* src = (i == 0) ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, slot, R.world);
     ph.a_map = 0;
     ph.b_map = (i == 0) ? 1 : 1 + i;
     ph.M = op.M;
@@ -335,7 +339,7 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
     const int t = mod(r - (i + 1), N);
     const int slot = wb + i;
     pu.src = op.home;
-    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot, R.world);
     pu.bytes = op.shard_bytes;
     pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
     pu.credit_ctr = RTP_CTR_W0 + slot;
@@ -376,7 +380,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
     if (make_map_k(&P.maps[2], op.dy, op.M, op.out_features, op.ldy)) return -1;
     if (make_map_mn(&P.maps[3], op.home, Ks, Os, Ks)) return -1;
     for (int s = 0; s + 1 < N; ++s)
-      if (make_map_mn(&P.maps[4 + s], ws_wslot(ws, R.slot_bytes, wb + s), Ks, Os, Ks)) return -1;
+      if (make_map_mn(&P.maps[4 + s], ws_wslot(ws, R.slot_bytes, wb + s, R.world), Ks, Os, Ks)) return -1;
   }
   int np = 0;
   for (int s = 0; s < N; ++s) {
@@ -393,7 +397,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
       ph.bn = pick_bn(ph.M, ph.N, R.ctas);
       uint8_t* dst;
       if (N == 1) dst = reinterpret_cast<uint8_t*>(op.grad_home);
-      else dst = ws_gslot(R.ws[j], R.slot_bytes, s);
+      else dst = ws_gslot(R.ws[j], R.slot_bytes, s, R.world);
       ph.d = dst; ph.ldd = Ks;
       if (op.grad_accumulate && N == 1) { ph.c = op.grad_home; ph.ldc = Ks; }
       if (N > 1) {
@@ -453,7 +457,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
     ph.r_nsrc = N;
     ph.r_n = (long long)(op.shard_bytes / 2) & ~7ll;
     for (int s = 0; s < N; ++s) {
-      ph.r_src[s] = ws_gslot(ws, R.slot_bytes, s);
+      ph.r_src[s] = ws_gslot(ws, R.slot_bytes, s, R.world);
       ph.wait_ctr[s] = RTP_CTR_G0 + s; ph.wait_rel[s] = 0;
       ph.done_ctr[s] = RTP_CTR_G0 + s;
       P.uses_inc[RTP_CTR_G0 + s] = 1;
@@ -467,7 +471,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
     memset(&pu, 0, sizeof(pu));
     const int t = mod(r + 1 + s, N);
     pu.src = op.home;
-    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, wb + s);
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, wb + s, R.world);
     pu.bytes = op.shard_bytes;
     pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + wb + s].v;
     pu.credit_ctr = RTP_CTR_W0 + wb + s;
@@ -495,7 +499,7 @@ int build_expert_fwd(const RtpRing& R, const RtpExpertFwd& op, RtpProgram& P) {
   int np = 0;
   for (int i = 0; i < N; ++i) {
     const int j = mod(r + i, N);
-    const uint8_t* src = (i == 0) ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, i - 1);
+    const uint8_t* src = (i == 0) ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, i - 1, R.world);
     for (int e = 0; e < L; ++e) {
       const int g = j * L + e;
       const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(src) + (long long)e * op.expert_stride;
@@ -525,7 +529,7 @@ int build_expert_fwd(const RtpRing& R, const RtpExpertFwd& op, RtpProgram& P) {
     memset(&pu, 0, sizeof(pu));
     const int t = mod(r - (i + 1), N);
     pu.src = op.home;
-    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, i);
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, i, R.world);
     pu.bytes = op.shard_bytes;
     pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + i].v;
     pu.credit_ctr = RTP_CTR_W0 + i;
@@ -555,8 +559,8 @@ int build_expert_bwd(const RtpRing& R, const RtpExpertBwd& op, RtpProgram& P) {
   for (int s = 0; s < N; ++s) {
     const int j = mod(r - 1 - s, N);
     const bool last = s == N - 1;
-    const uint8_t* wsrc = last ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, s);
-    uint8_t* gdst = (N == 1) ? reinterpret_cast<uint8_t*>(op.grad_home) : ws_gslot(R.ws[j], R.slot_bytes, s);
+    const uint8_t* wsrc = last ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, s, R.world);
+    uint8_t* gdst = (N == 1) ? reinterpret_cast<uint8_t*>(op.grad_home) : ws_gslot(R.ws[j], R.slot_bytes, s, R.world);
     for (int e = 0; e < L; ++e) {
       const int g = j * L + e;
       {  // wgrad of expert g
@@ -613,7 +617,7 @@ int build_expert_bwd(const RtpRing& R, const RtpExpertBwd& op, RtpProgram& P) {
     ph.r_nsrc = N;
     ph.r_n = (long long)(op.shard_bytes / 2) & ~7ll;
     for (int s = 0; s < N; ++s) {
-      ph.r_src[s] = ws_gslot(ws, R.slot_bytes, s);
+      ph.r_src[s] = ws_gslot(ws, R.slot_bytes, s, R.world);
       ph.wait_ctr[s] = RTP_CTR_G0 + s; ph.wait_rel[s] = 0;
       ph.done_ctr[s] = RTP_CTR_G0 + s;
       P.uses_inc[RTP_CTR_G0 + s] = 1;
@@ -626,7 +630,7 @@ int build_expert_bwd(const RtpRing& R, const RtpExpertBwd& op, RtpProgram& P) {
     memset(&pu, 0, sizeof(pu));
     const int t = mod(r + 1 + s, N);
     pu.src = op.home;
-    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, s);
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, s, R.world);
     pu.bytes = op.shard_bytes;
     pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + s].v;
     pu.credit_ctr = RTP_CTR_W0 + s;
@@ -656,7 +660,7 @@ int build_embed_fwd(const RtpRing& R, const RtpEmbedFwd& op, RtpProgram& P) {
     const int slot = i - 1;
     ph.kind = RTP_KIND_GATHER;
     ph.M = ph.N = ph.K = 0;
-    ph.g_table = (i == 0) ? op.home : ws_wslot(ws, R.slot_bytes, slot);
+    ph.g_table = (i == 0) ? op.home : ws_wslot(ws, R.slot_bytes, slot, R.world);
     ph.g_ids = op.ids;
     ph.g_tokens = op.T; ph.g_cols = op.Ds; ph.g_dim = op.D; ph.g_col_off = j * op.Ds; ph.g_tpp = op.tokens_per_pos;
     ph.g_scale = op.scale; ph.g_pe = op.pe; ph.g_ldpe = op.ld_pe;
@@ -678,7 +682,7 @@ int build_embed_fwd(const RtpRing& R, const RtpEmbedFwd& op, RtpProgram& P) {
     const int t = mod(r - (i + 1), N);
     const int slot = i;
     pu.src = op.home;
-    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot);
+    pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot, R.world);
     pu.bytes = op.shard_bytes;
     pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
     pu.credit_ctr = RTP_CTR_W0 + slot;
@@ -711,9 +715,9 @@ int build_reduce_scatter(const RtpRing& R, const RtpReduceScatter& op, RtpProgra
     ph.M = ph.N = ph.K = 0;
     ph.v_src = reinterpret_cast<const __nv_bfloat16*>(op.src) + (long long)j * op.cols;
     ph.v_ld = op.ld; ph.v_rows = op.rows; ph.v_cols = op.cols;
-    ph.d = last ? op.out : (void*)ws_gslot(R.ws[up], R.slot_bytes, gout);
+    ph.d = last ? op.out : (void*)ws_gslot(R.ws[up], R.slot_bytes, gout, R.world);
     if (s > 0) {
-      ph.c = ws_gslot(ws, R.slot_bytes, gin);
+      ph.c = ws_gslot(ws, R.slot_bytes, gin, R.world);
       ph.wait_ctr[0] = RTP_CTR_G0 + gin; ph.wait_rel[0] = (s - 1) / 2;
       ph.done_ctr[0] = RTP_CTR_G0 + gin;
     }
@@ -915,7 +919,21 @@ int rtp_linear_bwd_emu(const RtpRing* rings, const RtpLinearBwd* ops, int world,
 }
 
 // ------------------------------------------------------------------------------------- workspace
-unsigned long long rtp_ws_bytes(unsigned long long slot_bytes) { return kFlagBytes + (RTP_NUM_WBANKS + 1) * RTP_NUM_SLOTS * slot_bytes; }
+// bytes of a workspace that serves rings of up to RTP_NUM_SLOTS ranks / of exactly `world` ranks
+unsigned long long rtp_ws_bytes(unsigned long long slot_bytes) { return kFlagBytes + ((RTP_NUM_WBANKS + 1) * RTP_NUM_SLOTS - RTP_NUM_WBANKS) * slot_bytes; }
+unsigned long long rtp_ws_bytes_world(unsigned long long slot_bytes, int world) {
+  if (world < 1) world = 1;
+  return kFlagBytes + (unsigned long long)(RTP_NUM_WBANKS * (world - 1) + world) * slot_bytes;
+}
+int rtp_ws_create_world(unsigned long long slot_bytes, int world, void** out) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, rtp_ws_bytes_world(slot_bytes, world));
+  if (e != cudaSuccess) return fail(std::string("cudaMalloc workspace: ") + cudaGetErrorString(e));
+  e = cudaMemset(p, 0, kFlagBytes);
+  if (e != cudaSuccess) { cudaFree(p); return fail("cudaMemset workspace failed"); }
+  *out = p;
+  return 0;
+}
 int rtp_ws_create(unsigned long long slot_bytes, void** out) {
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, rtp_ws_bytes(slot_bytes));
@@ -954,7 +972,7 @@ int rtp_ws_status(void* ws, unsigned long long* host_out, void* stream) {
   if (e != cudaSuccess) return fail(std::string("status sync: ") + cudaGetErrorString(e));
   return 0;
 }
-void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i) { return ws_wslot(ws, slot_bytes, i); }
-void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i) { return ws_gslot(ws, slot_bytes, i); }
+void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i, int world) { return ws_wslot(ws, slot_bytes, i, world); }
+void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i, int world) { return ws_gslot(ws, slot_bytes, i, world); }
 
 }  // extern "C"

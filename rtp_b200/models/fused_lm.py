@@ -244,7 +244,7 @@ class FusedLMTrainer:
         E.linear_bwd_raw(self.eng, d.flat, d.info, x, dy, d.row, d.in_f, d.out_f, need_dx=need_dx, mask=mask,
                          mask_scale=mask_scale, grad_out=d.gflat, dx_out=dx_out, dx_accumulate=dx_accumulate,
                          dbias_buf=dbuf, **self._chain_args(d, 1))
-        self._count(3)  # memset + colsum + fused bwd
+        self._count(2)  # column sums of dy + fused dgrad/wgrad program
 
     def _step_impl(self, st):
         S, B, M, D, L = st["S"], st["B"], st["M"], self.D, self.L

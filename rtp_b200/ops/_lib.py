@@ -138,10 +138,11 @@ def lib():
         L.rtp_ws_bytes.restype = C.c_ulonglong
         L.rtp_ws_bytes.argtypes = [C.c_ulonglong]
         L.rtp_ws_wslot.restype = C.c_void_p
-        L.rtp_ws_wslot.argtypes = [C.c_void_p, C.c_ulonglong, C.c_int]
+        L.rtp_ws_wslot.argtypes = [C.c_void_p, C.c_ulonglong, C.c_int, C.c_int]
         L.rtp_ws_gslot.restype = C.c_void_p
-        L.rtp_ws_gslot.argtypes = [C.c_void_p, C.c_ulonglong, C.c_int]
+        L.rtp_ws_gslot.argtypes = [C.c_void_p, C.c_ulonglong, C.c_int, C.c_int]
         L.rtp_ws_create.argtypes = [C.c_ulonglong, C.POINTER(C.c_void_p)]
+        L.rtp_ws_create_world.argtypes = [C.c_ulonglong, C.c_int, C.POINTER(C.c_void_p)]
         L.rtp_ws_destroy.argtypes = [C.c_void_p]
         L.rtp_ws_reset.argtypes = [C.c_void_p, C.c_void_p]
         L.rtp_ws_ipc_get.argtypes = [C.c_void_p, C.c_void_p]

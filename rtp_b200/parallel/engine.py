@@ -50,7 +50,8 @@ class FusedEngine:
         ctx = self.ctx
         self.slot_bytes = _round_up(max(slot_bytes, 256), 1 << 16)
         ws = C.c_void_p()
-        _lib.check(L.rtp_ws_create(self.slot_bytes if ctx.world > 1 else 256, C.byref(ws)), "rtp_ws_create")
+        _lib.check(L.rtp_ws_create_world(self.slot_bytes if ctx.world > 1 else 256, ctx.world, C.byref(ws)),
+                   "rtp_ws_create_world")
         self.ws_local = ws.value
         self.mapped = {}
         ptrs = [None] * ctx.world
