@@ -679,12 +679,18 @@ __global__ void __launch_bounds__(256) colsum_vec_kernel(const __nv_bfloat16* __
 // ------------------------------------------------------------------------------------------------
 __global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int* __restrict__ block_start, int ntensors,
                             const long long* __restrict__ step_ptr, float lr, float beta1, float beta2, float eps,
-                            float weight_decay, int adamw, float clip_value, float grad_scale) {
-  // locate the tensor this block works on
+                            float weight_decay, int adamw, float clip_value, float grad_scale,
+                            const int* __restrict__ block_tensor) {
+  // locate the tensor this block works on: one load from the per-block table when the caller provides it (a block lives
+  // for a few microseconds, so the seven dependent loads of a binary search are a large part of its life)
   int lo = 0, hi = ntensors - 1;
-  while (lo < hi) {
-    const int mid = (lo + hi + 1) >> 1;
-    if (block_start[mid] <= (int)blockIdx.x) lo = mid; else hi = mid - 1;
+  if (block_tensor) {
+    lo = block_tensor[blockIdx.x];
+  } else {
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (block_start[mid] <= (int)blockIdx.x) lo = mid; else hi = mid - 1;
+    }
   }
   const RtpAdamTensor t = tensors[lo];
   const long long step = *step_ptr;
@@ -1142,11 +1148,11 @@ int rtp_colsum(const void* x, long long ld, int M, int N, float* out, void* stre
 }
 int rtp_adam(const RtpAdamTensor* tensors_dev, const int* block_start_dev, int ntensors, int total_blocks,
              const long long* step_dev, float lr, float beta1, float beta2, float eps, float weight_decay, int adamw,
-             float clip_value, float grad_scale, void* stream) {
+             float clip_value, float grad_scale, const int* block_tensor_dev, void* stream) {
   if (ntensors <= 0 || total_blocks <= 0) return 0;
   adam_kernel<<<total_blocks, 256, 0, (cudaStream_t)stream>>>(tensors_dev, block_start_dev, ntensors, step_dev, lr,
                                                               beta1, beta2, eps, weight_decay, adamw, clip_value,
-                                                              grad_scale);
+                                                              grad_scale, block_tensor_dev);
   LAUNCH_CHECK("adam");
   return 0;
 }

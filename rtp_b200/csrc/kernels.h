@@ -69,7 +69,8 @@ int rtp_col2im(const void* dcols, void* dx, int B, int C, int H, int W, int KH, 
 int rtp_colsum(const void* x, long long ld, int M, int N, float* out, void* stream);
 int rtp_adam(const RtpAdamTensor* tensors_dev, const int* block_start_dev, int ntensors, int total_blocks,
              const long long* step_dev, float lr, float beta1, float beta2, float eps, float weight_decay, int adamw,
-             float clip_value, float grad_scale, void* stream);
+             float clip_value, float grad_scale, const int* block_tensor_dev /* optional: tensor index of every block */,
+             void* stream);
 int rtp_causal_softmax(void* s, long long rows, int S, float scale, void* stream);
 int rtp_causal_softmax_bwd(const void* p, void* dp, long long rows, int S, float scale, void* stream);
 int rtp_gelu_fwd(const void* x, void* y, long long n, void* stream);

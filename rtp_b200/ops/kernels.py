@@ -39,7 +39,7 @@ def _L():
         L.rtp_im2col_last_error.restype = C.c_char_p
         L.rtp_im2col.argtypes = [vp, vp] + [i] * 13 + [vp]
         L.rtp_col2im.argtypes = [vp, vp] + [i] * 13 + [vp]
-        L.rtp_adam.argtypes = [vp, vp, i, i, vp, f, f, f, f, f, i, f, f, vp]
+        L.rtp_adam.argtypes = [vp, vp, i, i, vp, f, f, f, f, f, i, f, f, vp, vp]
         L.rtp_add.argtypes = [vp, vp, vp, ll, vp]
         L.rtp_moe_scatter.argtypes = [vp, vp, vp, vp, i, i, ll, vp]
         L.rtp_moe_gather.argtypes = [vp, vp, vp, vp, i, i, vp]
@@ -272,10 +272,14 @@ class AdamPlan:
         self.starts = torch.tensor(starts, dtype=torch.int32, device=device)
         self.n = len(entries)
         self.total_blocks = total
+        # tensor index of every block: one load instead of a binary search at the start of each (short-lived) block
+        counts = torch.tensor(starts[1:] + [total], dtype=torch.int64) - torch.tensor(starts, dtype=torch.int64)
+        self.block_tensor = torch.repeat_interleave(torch.arange(len(entries), dtype=torch.int32), counts).to(device)
 
     def step(self, step_dev, lr, beta1, beta2, eps, weight_decay=0.0, adamw=False, clip_value=0.0, grad_scale=1.0):
         _check(_L().rtp_adam(_p(self.table), _p(self.starts), self.n, self.total_blocks, _p(step_dev), lr, beta1,
-                             beta2, eps, weight_decay, int(adamw), clip_value, grad_scale, _lib.stream_ptr()), "adam")
+                             beta2, eps, weight_decay, int(adamw), clip_value, grad_scale, _p(self.block_tensor),
+                             _lib.stream_ptr()), "adam")
 
 
 def _gate_check(rc, what):
