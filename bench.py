@@ -223,9 +223,9 @@ def run_ours(args, cfg, rank, local, world):
         e2e = {"value": tok / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                "h2d_bytes_per_step": 2 * cfg["seq_len"] * cfg["batch"] * 8, "d2h_bytes_per_step": 4}
         trainer.check()
-    peak = torch.cuda.max_memory_allocated() / 2 ** 30
-    ws_gb = trainer.eng.slot_bytes * 16 / 2 ** 30 if world > 1 else 0.0
-    return ms, clocks, loss, e2e, peak + ws_gb, trainer.launches_per_step + 1
+    from rtp_b200.parallel import engine as _eng
+    peak = (torch.cuda.max_memory_allocated() + _eng.workspace_bytes()) / 2 ** 30   # torch allocator + rotation workspaces
+    return ms, clocks, loss, e2e, peak, trainer.launches_per_step + 1
 
 
 def run_ours_module(args, cfg, rank, local, world):
@@ -283,7 +283,8 @@ def run_ours_module(args, cfg, rank, local, world):
         tok = cfg["seq_len"] * cfg["batch"] * world * args.steps
         e2e = {"value": tok / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                "h2d_bytes_per_step": 2 * cfg["seq_len"] * cfg["batch"] * 8, "d2h_bytes_per_step": 4}
-    peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    from rtp_b200.parallel import engine as _eng
+    peak = (torch.cuda.max_memory_allocated() + _eng.workspace_bytes()) / 2 ** 30   # torch allocator + rotation workspaces
     return ms, clocks, loss, e2e, peak, 1
 
 

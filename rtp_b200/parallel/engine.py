@@ -113,6 +113,18 @@ def get_engine(ctx: RingContext) -> FusedEngine:
     return eng
 
 
+def workspace_bytes() -> int:
+    """Device bytes held by the peer-mapped workspaces of this process (allocated with cudaMalloc, outside the
+    PyTorch caching allocator, so memory statistics of torch do not include them)."""
+    L = _lib.lib()
+    L.rtp_ws_bytes_world.restype = C.c_ulonglong
+    L.rtp_ws_bytes_world.argtypes = [C.c_ulonglong, C.c_int]
+    total = 0
+    for e in _engines.values():
+        total += int(L.rtp_ws_bytes_world(e.slot_bytes if e.ctx.world > 1 else 256, e.ctx.world))
+    return total
+
+
 def check_all():
     for e in _engines.values():
         e.check()
