@@ -154,6 +154,30 @@ def max_over_ranks(x, world):
     return t.item()
 
 
+def roofline(cfg, world, ms_per_step):
+    """Lower bound of one step of the dense LM on one rank and the fraction of it that was achieved: GEMM FLOPs at the
+    measured cuBLAS bf16 rate, optimizer bytes at the measured copy bandwidth, and the bytes a rank must move over
+    NVLink (weight shards forward and backward, gradient shards) at the measured 770 GB/s peer-copy rate; the three
+    cannot all overlap perfectly with one another, so the bound is their maximum."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        tf, hbm, src = pk.get("bf16_tflops_sustained", 1400.0), pk.get("hbm_gbs", 6650.0), "measured"
+    except Exception:
+        tf, hbm, src = 1400.0, 6650.0, "fallback"
+    D, H, V, L = cfg["ninp"], cfg["nhid"], cfg["vocab"], cfg["nlayers"]
+    tokens = cfg["seq_len"] * cfg["batch"]
+    layer_params = 4 * D * D + 2 * D * H
+    params = L * layer_params + 2 * V * D
+    flops = 6.0 * tokens * (L * layer_params + V * D)          # forward + dgrad + wgrad of every rotated linear
+    opt_bytes = 22.0 * params / world                          # bf16 p, g + fp32 m, v read; p, m, v written
+    nv_bytes = 3.0 * 2.0 * (L * layer_params + V * D) * (world - 1) / world   # W forward, W backward, dW; bf16
+    t_gemm, t_opt, t_nv = flops / (tf * 1e12) * 1e3, opt_bytes / (hbm * 1e9) * 1e3, nv_bytes / 770e9 * 1e3
+    bound = max(t_gemm + t_opt, t_nv)
+    return {"gemm_ms_at_peak": t_gemm, "optimizer_ms_at_copy_bw": t_opt, "nvlink_ms_at_770GBs": t_nv,
+            "bound_ms": bound, "achieved_frac": bound / ms_per_step, "peaks": src}
+
+
 def timed_loop(step_fn, batches, steps, warmup, world, flush, sync_each):
     """Returns device milliseconds for `steps` calls of step_fn (max over ranks)."""
     import torch
@@ -398,6 +422,8 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps if args.impl == "rtp_b200" else None,
             "wall_s": time.time() - t_wall,
         }
+        if "family" not in cfg:
+            out["roofline"] = roofline(cfg, world, ms / args.steps)
         print(json.dumps(out))
     import torch.distributed as dist
     dist.barrier()

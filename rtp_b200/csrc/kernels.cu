@@ -610,7 +610,7 @@ __global__ void colsum_kernel(const __nv_bfloat16* __restrict__ x, long long ld,
 // group form a thread-block cluster along y: each leaves its 64 partial sums in its own shared memory, and the first
 // block of the cluster adds them up through distributed shared memory and stores the result (no atomics, no zero-fill).
 __global__ void __launch_bounds__(256) colsum_vec_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N,
-                                                         float* __restrict__ out, int rows_per_block) {
+                                                         float* __restrict__ out, int rows_per_block, int atomic) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   __shared__ float red[32][65];
@@ -669,7 +669,9 @@ __global__ void __launch_bounds__(256) colsum_vec_kernel(const __nv_bfloat16* __
     const int col = blockIdx.x * 64 + threadIdx.x;
     float t = 0.f;
     for (unsigned k = 0; k < cluster.num_blocks(); ++k) t += cluster.map_shared_rank(part, k)[threadIdx.x];
-    if (col < N) out[col] = t;
+    if (col < N) {
+      if (atomic) atomicAdd(out + col, t); else out[col] = t;
+    }
   }
   cluster.sync();   // no block leaves while its shared memory may still be read
 }
@@ -677,12 +679,99 @@ __global__ void __launch_bounds__(256) colsum_vec_kernel(const __nv_bfloat16* __
 // ------------------------------------------------------------------------------------------------
 // Multi-tensor Adam / AdamW with optional gradient value clipping.
 // ------------------------------------------------------------------------------------------------
-__global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int* __restrict__ block_start, int ntensors,
-                            const long long* __restrict__ step_ptr, float lr, float beta1, float beta2, float eps,
-                            float weight_decay, int adamw, float clip_value, float grad_scale,
-                            const int* __restrict__ block_tensor) {
-  // locate the tensor this block works on: one load from the per-block table when the caller provides it (a block lives
-  // for a few microseconds, so the seven dependent loads of a binary search are a large part of its life)
+struct AdamRegs {
+  float pv[8], gv[8], mv[8], vv[8];
+  long long i0;
+  int cnt;
+  bool vec, svec;
+};
+// loads of one group of up to 8 elements (issued for both groups of a thread before either is updated)
+__device__ __forceinline__ void adam_load(const RtpAdamTensor& t, long long i0, AdamRegs& r) {
+  r.i0 = i0;
+  r.cnt = i0 < t.n ? (int)min((long long)8, t.n - i0) : 0;
+  if (r.cnt == 0) return;
+  const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(t.p) + i0;
+  const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(t.g) + i0;
+  r.vec = r.cnt == 8 && ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15) == 0;
+  if (r.vec) {
+    unpack8(__ldcs(reinterpret_cast<const uint4*>(p)), r.pv);
+    unpack8(__ldcs(reinterpret_cast<const uint4*>(g)), r.gv);
+  } else {
+    _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) { r.pv[i] = __bfloat162float(p[i]); r.gv[i] = __bfloat162float(g[i]); }
+  }
+  r.svec = r.cnt == 8 && ((reinterpret_cast<uintptr_t>(t.m) | reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
+  if (t.state_fp32) {
+    const float* m = reinterpret_cast<const float*>(t.m) + i0;
+    const float* v = reinterpret_cast<const float*>(t.v) + i0;
+    if (r.svec) {
+      const float4 a = __ldcs(reinterpret_cast<const float4*>(m)), b = __ldcs(reinterpret_cast<const float4*>(m) + 1);
+      const float4 c = __ldcs(reinterpret_cast<const float4*>(v)), d = __ldcs(reinterpret_cast<const float4*>(v) + 1);
+      r.mv[0] = a.x; r.mv[1] = a.y; r.mv[2] = a.z; r.mv[3] = a.w; r.mv[4] = b.x; r.mv[5] = b.y; r.mv[6] = b.z; r.mv[7] = b.w;
+      r.vv[0] = c.x; r.vv[1] = c.y; r.vv[2] = c.z; r.vv[3] = c.w; r.vv[4] = d.x; r.vv[5] = d.y; r.vv[6] = d.z; r.vv[7] = d.w;
+    } else {
+      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) { r.mv[i] = m[i]; r.vv[i] = v[i]; }
+    }
+  } else {
+    const __nv_bfloat16* m = reinterpret_cast<const __nv_bfloat16*>(t.m) + i0;
+    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(t.v) + i0;
+    if (r.svec) {
+      unpack8(__ldcs(reinterpret_cast<const uint4*>(m)), r.mv);
+      unpack8(__ldcs(reinterpret_cast<const uint4*>(v)), r.vv);
+    } else {
+      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) { r.mv[i] = __bfloat162float(m[i]); r.vv[i] = __bfloat162float(v[i]); }
+    }
+  }
+}
+__device__ __forceinline__ void adam_update_store(const RtpAdamTensor& t, AdamRegs& r, float lr, float beta1, float beta2,
+                                                  float eps, float weight_decay, int adamw, float clip_value,
+                                                  float grad_scale, float step_size, float inv_sqrt_bc2) {
+  if (r.cnt == 0) return;
+  _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) {
+    float gg = r.gv[i] * grad_scale;
+    if (clip_value > 0.f) gg = fminf(fmaxf(gg, -clip_value), clip_value);
+    if (weight_decay != 0.f) {
+      if (adamw) r.pv[i] *= 1.f - lr * t.lr_mult * weight_decay; else gg += weight_decay * r.pv[i];
+    }
+    r.mv[i] = beta1 * r.mv[i] + (1.f - beta1) * gg;
+    r.vv[i] = beta2 * r.vv[i] + (1.f - beta2) * gg * gg;
+    r.pv[i] -= step_size * r.mv[i] / (sqrtf(r.vv[i]) * inv_sqrt_bc2 + eps);
+  }
+  __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(t.p) + r.i0;
+  if (r.vec) __stcs(reinterpret_cast<uint4*>(p), pack8(r.pv));
+  else { _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) p[i] = __float2bfloat16(r.pv[i]); }
+  if (t.state_fp32) {
+    float* m = reinterpret_cast<float*>(t.m) + r.i0;
+    float* v = reinterpret_cast<float*>(t.v) + r.i0;
+    if (r.svec) {
+      __stcs(reinterpret_cast<float4*>(m), make_float4(r.mv[0], r.mv[1], r.mv[2], r.mv[3]));
+      __stcs(reinterpret_cast<float4*>(m) + 1, make_float4(r.mv[4], r.mv[5], r.mv[6], r.mv[7]));
+      __stcs(reinterpret_cast<float4*>(v), make_float4(r.vv[0], r.vv[1], r.vv[2], r.vv[3]));
+      __stcs(reinterpret_cast<float4*>(v) + 1, make_float4(r.vv[4], r.vv[5], r.vv[6], r.vv[7]));
+    } else {
+      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) { m[i] = r.mv[i]; v[i] = r.vv[i]; }
+    }
+  } else {
+    __nv_bfloat16* m = reinterpret_cast<__nv_bfloat16*>(t.m) + r.i0;
+    __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(t.v) + r.i0;
+    if (r.svec) {
+      __stcs(reinterpret_cast<uint4*>(m), pack8(r.mv));
+      __stcs(reinterpret_cast<uint4*>(v), pack8(r.vv));
+    } else {
+      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) { m[i] = __float2bfloat16(r.mv[i]); v[i] = __float2bfloat16(r.vv[i]); }
+    }
+  }
+}
+
+// One block = kAdamGroups x 2048 elements of one tensor; every thread owns one group of 8 elements in each 2048-element
+// sub-chunk and has the loads of all its groups in flight before it updates the first.
+constexpr int kAdamGroups = 2;
+__global__ void __launch_bounds__(256) adam_kernel(const RtpAdamTensor* __restrict__ tensors,
+                                                   const int* __restrict__ block_start, int ntensors,
+                                                   const long long* __restrict__ step_ptr, float lr, float beta1,
+                                                   float beta2, float eps, float weight_decay, int adamw,
+                                                   float clip_value, float grad_scale,
+                                                   const int* __restrict__ block_tensor) {
+  // locate the tensor this block works on: one load from the per-block table when the caller provides it
   int lo = 0, hi = ntensors - 1;
   if (block_tensor) {
     lo = block_tensor[blockIdx.x];
@@ -698,75 +787,13 @@ __global__ void adam_kernel(const RtpAdamTensor* __restrict__ tensors, const int
   const float bc2 = 1.f - powf(beta2, (float)step);
   const float step_size = lr * t.lr_mult / bc1;
   const float inv_sqrt_bc2 = rsqrtf(bc2);
-  const long long base = (long long)((int)blockIdx.x - block_start[lo]) * (blockDim.x * 8);
-  const long long i0 = base + threadIdx.x * 8;
-  if (i0 >= t.n) return;
-  const int cnt = (int)min((long long)8, t.n - i0);
-  __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(t.p) + i0;
-  const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(t.g) + i0;
-  float pv[8], gv[8], mv[8], vv[8];
-  const bool vec = cnt == 8 && ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15) == 0;
-  if (vec) {
-    unpack8(__ldcs(reinterpret_cast<const uint4*>(p)), pv);
-    unpack8(__ldcs(reinterpret_cast<const uint4*>(g)), gv);
-  } else {
-    for (int i = 0; i < cnt; ++i) { pv[i] = __bfloat162float(p[i]); gv[i] = __bfloat162float(g[i]); }
-  }
-  const bool svec = cnt == 8 && ((reinterpret_cast<uintptr_t>(t.m) | reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
-  if (t.state_fp32) {
-    float* m = reinterpret_cast<float*>(t.m) + i0;
-    float* v = reinterpret_cast<float*>(t.v) + i0;
-    if (svec) {
-      const float4 a = reinterpret_cast<const float4*>(m)[0], b = reinterpret_cast<const float4*>(m)[1];
-      const float4 c = reinterpret_cast<const float4*>(v)[0], d = reinterpret_cast<const float4*>(v)[1];
-      mv[0] = a.x; mv[1] = a.y; mv[2] = a.z; mv[3] = a.w; mv[4] = b.x; mv[5] = b.y; mv[6] = b.z; mv[7] = b.w;
-      vv[0] = c.x; vv[1] = c.y; vv[2] = c.z; vv[3] = c.w; vv[4] = d.x; vv[5] = d.y; vv[6] = d.z; vv[7] = d.w;
-    } else {
-      for (int i = 0; i < cnt; ++i) { mv[i] = m[i]; vv[i] = v[i]; }
-    }
-  } else {
-    const __nv_bfloat16* m = reinterpret_cast<const __nv_bfloat16*>(t.m) + i0;
-    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(t.v) + i0;
-    if (svec) {
-      unpack8(__ldcs(reinterpret_cast<const uint4*>(m)), mv);
-      unpack8(__ldcs(reinterpret_cast<const uint4*>(v)), vv);
-    } else {
-      for (int i = 0; i < cnt; ++i) { mv[i] = __bfloat162float(m[i]); vv[i] = __bfloat162float(v[i]); }
-    }
-  }
-  for (int i = 0; i < cnt; ++i) {
-    float gg = gv[i] * grad_scale;
-    if (clip_value > 0.f) gg = fminf(fmaxf(gg, -clip_value), clip_value);
-    if (weight_decay != 0.f) {
-      if (adamw) pv[i] *= 1.f - lr * t.lr_mult * weight_decay; else gg += weight_decay * pv[i];
-    }
-    mv[i] = beta1 * mv[i] + (1.f - beta1) * gg;
-    vv[i] = beta2 * vv[i] + (1.f - beta2) * gg * gg;
-    pv[i] -= step_size * mv[i] / (sqrtf(vv[i]) * inv_sqrt_bc2 + eps);
-  }
-  if (vec) __stcs(reinterpret_cast<uint4*>(p), pack8(pv));
-  else for (int i = 0; i < cnt; ++i) p[i] = __float2bfloat16(pv[i]);
-  if (t.state_fp32) {
-    float* m = reinterpret_cast<float*>(t.m) + i0;
-    float* v = reinterpret_cast<float*>(t.v) + i0;
-    if (svec) {
-      reinterpret_cast<float4*>(m)[0] = make_float4(mv[0], mv[1], mv[2], mv[3]);
-      reinterpret_cast<float4*>(m)[1] = make_float4(mv[4], mv[5], mv[6], mv[7]);
-      reinterpret_cast<float4*>(v)[0] = make_float4(vv[0], vv[1], vv[2], vv[3]);
-      reinterpret_cast<float4*>(v)[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
-    } else {
-      for (int i = 0; i < cnt; ++i) { m[i] = mv[i]; v[i] = vv[i]; }
-    }
-  } else {
-    __nv_bfloat16* m = reinterpret_cast<__nv_bfloat16*>(t.m) + i0;
-    __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(t.v) + i0;
-    if (svec) {
-      __stcs(reinterpret_cast<uint4*>(m), pack8(mv));
-      __stcs(reinterpret_cast<uint4*>(v), pack8(vv));
-    } else {
-      for (int i = 0; i < cnt; ++i) { m[i] = __float2bfloat16(mv[i]); v[i] = __float2bfloat16(vv[i]); }
-    }
-  }
+  const long long base = (long long)((int)blockIdx.x - block_start[lo]) * (256 * 8 * kAdamGroups);
+  AdamRegs r[kAdamGroups];
+#pragma unroll
+  for (int u = 0; u < kAdamGroups; ++u) adam_load(t, base + u * (256 * 8) + threadIdx.x * 8, r[u]);
+#pragma unroll
+  for (int u = 0; u < kAdamGroups; ++u)
+    adam_update_store(t, r[u], lr, beta1, beta2, eps, weight_decay, adamw, clip_value, grad_scale, step_size, inv_sqrt_bc2);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1129,12 +1156,19 @@ int rtp_attn_small_bwd(const void* qkv, const void* dout, void* dqkv, int S, int
 int rtp_colsum(const void* x, long long ld, int M, int N, float* out, void* stream) {
   if (N % 2 || ld % 2) { k_err = "colsum: N and ld must be even"; return -1; }
   if (N % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-    // clusters of up to 8 blocks split the rows (at least 128 rows per block)
+    // clusters of up to 8 blocks split the rows (at least 128 rows per block); very tall matrices get several
+    // clusters per column group, whose sums meet in the zeroed output by atomics
     int cy = 8;
     while (cy > 1 && M < cy * 128) cy >>= 1;
-    const int rows = (M + cy - 1) / cy;
-    rtp::launch_kc(colsum_vec_kernel, dim3((N + 63) / 64, cy), dim3(256), 0, (cudaStream_t)stream, dim3(1, cy, 1),
-                   (const __nv_bfloat16*)x, ld, M, N, out, rows);
+    int groups = 1;
+    while (groups < 64 && M / (cy * groups) > 1024) groups <<= 1;
+    const int rows = (M + cy * groups - 1) / (cy * groups);
+    if (groups > 1) {
+      cudaError_t e = cudaMemsetAsync(out, 0, (size_t)N * sizeof(float), (cudaStream_t)stream);
+      if (e != cudaSuccess) return kfail("colsum memset", e);
+    }
+    rtp::launch_kc(colsum_vec_kernel, dim3((N + 63) / 64, cy * groups), dim3(256), 0, (cudaStream_t)stream, dim3(1, cy, 1),
+                   (const __nv_bfloat16*)x, ld, M, N, out, rows, groups > 1 ? 1 : 0);
     LAUNCH_CHECK("colsum");
     return 0;
   }

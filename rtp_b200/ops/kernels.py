@@ -254,7 +254,7 @@ def sum_f32(src, out, scale=1.0):
 class AdamPlan:
     """Device-resident descriptor table for the multi-tensor Adam kernel (built once, reused every step)."""
 
-    BLOCK_ELEMS = 2048
+    BLOCK_ELEMS = 4096     # kAdamGroups * 2048 of the kernel
 
     def __init__(self, entries, device):
         # entries: list of (p, g, m, v, lr_mult)
