@@ -765,7 +765,7 @@ __device__ __forceinline__ void adam_update_store(const RtpAdamTensor& t, AdamRe
 // One block = kAdamGroups x 2048 elements of one tensor; every thread owns one group of 8 elements in each 2048-element
 // sub-chunk and has the loads of all its groups in flight before it updates the first.
 constexpr int kAdamGroups = 2;
-__global__ void __launch_bounds__(256, 3) adam_kernel(const RtpAdamTensor* __restrict__ tensors,
+__global__ void __launch_bounds__(256, 4) adam_kernel(const RtpAdamTensor* __restrict__ tensors,
                                                    const int* __restrict__ block_start, int ntensors,
                                                    const long long* __restrict__ step_ptr, float lr, float beta1,
                                                    float beta2, float eps, float weight_decay, int adamw,
