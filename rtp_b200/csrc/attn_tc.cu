@@ -32,9 +32,9 @@ constexpr int kHd = 64;
 constexpr int kRows = 128;                 // stacked rows per CTA
 constexpr int kTile = kRows * 128;         // one [128 x 64] bf16 operand tile, 128-byte rows: 16 KB
 
-__device__ unsigned int g_attn_tc_error;
+__device__ unsigned int g_attn_tc_error;        // set when a bounded wait for the CTA's own UMMAs ran out
 __device__ unsigned long long* g_attn_trace;   // tuning aid: timeline of CTA 0 (16 words), null = off
-#define ATT_STAMP(i) do { if (g_attn_trace && blockIdx.x == 0 && threadIdx.x == 0) g_attn_trace[i] = globaltimer_ns(); } while (0)   // set when a bounded wait for the CTA's own UMMAs ran out
+#define ATT_STAMP(i) do { if (g_attn_trace && blockIdx.x == 0 && threadIdx.x == 0) g_attn_trace[i] = globaltimer_ns(); } while (0)
 
 struct Ctl {
   uint64_t bar[2];
