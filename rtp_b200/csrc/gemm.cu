@@ -62,9 +62,28 @@ int make_map(CUtensorMap* m, const void* ptr, long long inner, long long outer, 
 int make_map_k(CUtensorMap* m, const void* ptr, long long rows, long long k, long long ld, int box_rows = 128) {
   return make_map(m, ptr, k, rows, ld, box_rows);
 }
-// operand stored [k, mn] row-major (MN-major)
+// operand stored [k, mn] row-major (MN-major): boxes of [64 k rows, 64 mn]
 int make_map_mn(CUtensorMap* m, const void* ptr, long long mn, long long k, long long ld) {
   return make_map(m, ptr, mn, k, ld, 64);
+}
+// Same operand as a 3-D tensor {64 mn, k, mn / 64} with box {64, 64, nblk}: ONE copy per stage delivers the nblk 64-wide
+// column blocks side by side, exactly the shared-memory layout the UMMA descriptors expect (the producer thread is
+// issue-bound, so halving its copies per k-block matters).  Needs mn % 64 == 0; *is3d tells which form was built
+// (falls back to the 2-D map otherwise, also if the driver rejects the encoding).
+int make_map_mn3(CUtensorMap* m, const void* ptr, long long mn, long long k, long long ld, int nblk, unsigned char* is3d) {
+  *is3d = 0;
+  EncodeTiledFn enc = get_encode();
+  if (enc && nblk >= 1 && mn % 64 == 0 && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (ld * 2) % 16 == 0) {
+    cuuint64_t dims[3] = {64u, (cuuint64_t)k, (cuuint64_t)(mn / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128u};
+    cuuint32_t box[3] = {64u, 64u, (cuuint32_t)nblk};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) { *is3d = 1; return 0; }
+  }
+  return make_map_mn(m, ptr, mn, k, ld);
 }
 
 int sm_count() {
@@ -374,13 +393,19 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
 
   // maps: 0 = dy (MN-major view: k = tokens), 1 = x (MN-major view), 2 = dy (K-major view: k = out),
   //       3 = home W (MN-major view: k = shard rows), 4+s = weight slot s
-  if (make_map_mn(&P.maps[0], op.dy, op.out_features, op.M, op.ldy)) return -1;
-  if (make_map_mn(&P.maps[1], op.x, op.in_features, op.M, op.ldx)) return -1;
+  // MN-major operands travel as 3-D maps (one copy per operand and k-block) when every tile offset is a multiple of 64
+  const bool m3 = Os % 64 == 0 && Ks % 64 == 0;
+  const int bn_w = pick_bn(Os, Ks, R.ctas), bn_d = pick_bn(op.M, Ks, R.ctas);
+  const int nb_w = (pair_mode() ? bn_w / 2 : bn_w) / 64, nb_d = (pair_mode() ? bn_d / 2 : bn_d) / 64;
+  if (make_map_mn3(&P.maps[0], op.dy, op.out_features, op.M, op.ldy, m3 ? 2 : 0, &P.map3d[0])) return -1;
+  if (make_map_mn3(&P.maps[1], op.x, op.in_features, op.M, op.ldx, m3 ? nb_w : 0, &P.map3d[1])) return -1;
   if (op.dx) {
     if (make_map_k(&P.maps[2], op.dy, op.M, op.out_features, op.ldy)) return -1;
-    if (make_map_mn(&P.maps[3], op.home, Ks, Os, Ks)) return -1;
+    if (make_map_mn3(&P.maps[3], op.home, Ks, Os, Ks, m3 ? nb_d : 0, &P.map3d[3])) return -1;
     for (int s = 0; s + 1 < N; ++s)
-      if (make_map_mn(&P.maps[4 + s], ws_wslot(ws, R.slot_bytes, wb + s, R.world), Ks, Os, Ks)) return -1;
+      if (make_map_mn3(&P.maps[4 + s], ws_wslot(ws, R.slot_bytes, wb + s, R.world), Ks, Os, Ks, m3 ? nb_d : 0,
+                       &P.map3d[4 + s]))
+        return -1;
   }
   int np = 0;
   for (int s = 0; s < N; ++s) {
@@ -766,7 +791,7 @@ int rtp_gemm(const RtpGemmArgs* a, void* stream) {
   RtpProgram& P = params.prog[0];
   init_program(P);
   if (a->M <= 0 || a->N <= 0 || a->K <= 0) return fail("empty GEMM");
-  if (a->a_mn ? make_map_mn(&P.maps[0], a->a, a->M, a->K, a->lda) : make_map_k(&P.maps[0], a->a, a->M, a->K, a->lda))
+  if (a->a_mn ? make_map_mn3(&P.maps[0], a->a, a->M, a->K, a->lda, 2, &P.map3d[0]) : make_map_k(&P.maps[0], a->a, a->M, a->K, a->lda))
     return -1;
   const int ctas = a->num_ctas > 0 ? a->num_ctas : sm_count();
   decide_pair(a->M, a->N, ctas);
@@ -774,7 +799,8 @@ int rtp_gemm(const RtpGemmArgs* a, void* stream) {
   if (bn_sel != 128 && bn_sel != 256) return fail("bn must be 128 or 256");
   const bool pair = pair_mode();
   const int b_box = pair ? bn_sel / 2 : 128;   // a pair stages half of the B tile per CTA
-  if (a->b_mn ? make_map_mn(&P.maps[1], a->b, a->N, a->K, a->ldb) : make_map_k(&P.maps[1], a->b, a->N, a->K, a->ldb, b_box))
+  if (a->b_mn ? make_map_mn3(&P.maps[1], a->b, a->N, a->K, a->ldb, (pair ? bn_sel / 2 : bn_sel) / 64, &P.map3d[1])
+              : make_map_k(&P.maps[1], a->b, a->N, a->K, a->ldb, b_box))
     return -1;
   RtpPhase& ph = P.phases[0];
   init_phase(ph);

@@ -177,6 +177,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const int b_dx = p_b_mn ? 0 : kBK, b_dy = p_b_mn ? kBK : 0;
         const int b_ix = p_b_mn ? 64 : 0, b_iy = p_b_mn ? 0 : ph.b_box;  // per box inside a stage
         const uint32_t b_ismem = p_b_mn ? 8192u : (uint32_t)ph.b_box * 128u;
+        const bool a3 = p_a_mn && P.map3d[ph.a_map], b3 = p_b_mn && P.map3d[ph.b_map];
         if (p == 0) GEMM_STAMP(2);
         for (int t = (unit - p_cta_off + GU) % GU; t < total && ok; t += GU) {
           const int z = t / per_batch, tt = t % per_batch;
@@ -203,9 +204,17 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
               // every CTA (also in a pair) copies into its own shared memory and completes its own barrier
               const uint32_t bar = full_s + stage * 8;
               mbar_arrive_expect_tx_s(bar, tx);
-              tma_load_2d_s(sa, ma, ax, ay, bar);
-              if (na == 2) tma_load_2d_s(sa + 8192, ma, ax + 64, ay, bar);
-              for (int i = 0; i < nb; ++i) tma_load_2d_s(sb + i * b_ismem, mb, bx + i * b_ix, by + i * b_iy, bar);
+              if (a3) {
+                tma_load_3d_s(sa, ma, 0, ay, ax >> 6, bar);       // both 64-wide halves of A in one copy
+              } else {
+                tma_load_2d_s(sa, ma, ax, ay, bar);
+                if (na == 2) tma_load_2d_s(sa + 8192, ma, ax + 64, ay, bar);
+              }
+              if (b3) {
+                tma_load_3d_s(sb, mb, 0, by, bx >> 6, bar);       // all 64-wide column blocks of B in one copy
+              } else {
+                for (int i = 0; i < nb; ++i) tma_load_2d_s(sb + i * b_ismem, mb, bx + i * b_ix, by + i * b_iy, bar);
+              }
             }
             ax += a_dx; ay += a_dy; bx += b_dx; by += b_dy;
             if (++stage == kStages) { stage = 0; phase ^= 1; }

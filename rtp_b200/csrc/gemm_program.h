@@ -132,6 +132,8 @@ struct alignas(64) RtpProgram {
   unsigned long long timeout_ns;
   unsigned long long* trace;  // optional debug timeline of CTA 0: [role][tile][event] globaltimer stamps (see gemm_kernel.cuh)
   int uses_inc[RTP_NUM_CTR];  // added to flags->uses[] by the last CTA of the launch
+  unsigned char map3d[RTP_MAX_MAPS];  // 1: the map of an MN-major operand is 3-D {64 mn, k, mn / 64}: one copy fetches all
+                                      // 64-wide column blocks of a stage (coordinates {0, k, mn / 64})
   alignas(64) CUtensorMap maps[RTP_MAX_MAPS];
   RtpPhase phases[RTP_MAX_PHASES];
   RtpPush pushes[RTP_MAX_PUSHES];
