@@ -42,3 +42,15 @@ def test_fused_conv_eligibility():
     # on CPU the module keeps evaluating through the functional engine
     y = ok(x)
     assert y.shape == (2, 64, 6, 6)
+
+
+def test_guard_bands_catch_an_overrun():
+    import pytest
+    from rtp_b200.utils.guard import check_guards, guarded_empty
+    t = guarded_empty((5, 7), torch.float32, device="cpu", band=8, name="fine")
+    t.zero_()
+    check_guards()
+    t = guarded_empty((5, 7), torch.float32, device="cpu", band=8, name="overrun")
+    torch.as_strided(t, (1,), (1,), storage_offset=t.storage_offset() + 35).fill_(3.0)   # one element past the end
+    with pytest.raises(AssertionError, match="AFTER tensor 'overrun'"):
+        check_guards()
