@@ -24,3 +24,15 @@ def test_fused_ring_matches_functional(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _run(world)
+
+
+def test_rank_leaving_between_steps_is_seen_before_the_next_launch():
+    """Failure detection with real GPUs but without any GPU fault: the leaver has nothing in flight, the survivor reads
+    the heartbeat store on the host and never launches a kernel that would wait for the missing peer."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29721", os.path.join(HERE, "_multi_gpu_leave_worker.py")]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=200)
+    assert "DETECTED rank 1 left" in p.stdout and "NOT_DETECTED" not in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
