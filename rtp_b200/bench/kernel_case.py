@@ -40,7 +40,7 @@ def _time(fn, iters, warm=2):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["gemm", "norm_fwd", "norm_bwd", "ce", "adam", "attn_fwd", "attn_bwd", "colsum",
-                                     "embed"])
+                                     "embed", "gate", "rope", "im2col"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -125,6 +125,34 @@ def main(argv=None):
         ms = _time(lambda i: K.colsum(x), a.iters)
         nbytes = x.numel() * 2
         print(json.dumps({"case": "colsum", "us": ms * 1e3, "GBs": nbytes / ms / 1e6,
+                          "frac_of_copy_peak": nbytes / ms / 1e6 / hbm, "peaks": src}))
+        return
+    if a.case == "gate":
+        S, E = a.m * 8, 64
+        logits = torch.randn(S, E, device=dev)
+        noise = torch.randn(S, E, device=dev)
+        ms = _time(lambda i: K.top2_gate(logits, 2 * S // E, noise), a.iters)
+        nbytes = S * E * 4 * 3
+        print(json.dumps({"case": "gate", "S": S, "E": E, "us": ms * 1e3, "GBs": nbytes / ms / 1e6,
+                          "frac_of_copy_peak": nbytes / ms / 1e6 / hbm, "peaks": src}))
+        return
+    if a.case == "rope":
+        B, S, H, hd = 16, a.m // 2, 16, 128
+        x = torch.randn(B, S, H, hd, device=dev, dtype=bf)
+        fr = torch.outer(torch.arange(S, device=dev, dtype=torch.float32),
+                         1.0 / (10000.0 ** (torch.arange(0, hd, 2, device=dev, dtype=torch.float32) / hd)))
+        cos, sin = fr.cos(), fr.sin()
+        ms = _time(lambda i: K.rope(x, cos, sin), a.iters)
+        nbytes = x.numel() * 2 * 2
+        print(json.dumps({"case": "rope", "shape": [B, S, H, hd], "us": ms * 1e3, "GBs": nbytes / ms / 1e6,
+                          "frac_of_copy_peak": nbytes / ms / 1e6 / hbm, "peaks": src}))
+        return
+    if a.case == "im2col":
+        B, Cc, H, W = 256, 64, 56, 56
+        x = torch.randn(B, Cc, H, W, device=dev, dtype=bf)
+        ms = _time(lambda i: K.im2col(x, 3, 1, 1, 1), a.iters)
+        nbytes = x.numel() * 2 * 10          # one read of x, nine-fold patch matrix written
+        print(json.dumps({"case": "im2col", "shape": [B, Cc, H, W], "us": ms * 1e3, "GBs": nbytes / ms / 1e6,
                           "frac_of_copy_peak": nbytes / ms / 1e6 / hbm, "peaks": src}))
         return
     if a.case == "embed":

@@ -19,20 +19,35 @@ struct ConvGeom {
   int B, C, H, W, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw, Kp;
 };
 
+// One thread per (output position m, input channel c): the position is decoded once and the thread writes the channel's
+// KH*KW consecutive patch entries (adjacent threads write adjacent channels, so a warp's stores are contiguous).
+// Threads with c == C fill the zero padding of the row up to Kp.
 __global__ void im2col_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ cols, ConvGeom g) {
-  const long long total = (long long)g.B * g.OH * g.OW * g.Kp;
-  const int K = g.C * g.KH * g.KW;
+  const int KK = g.KH * g.KW;
+  const int K = g.C * KK;
+  const int cpr = g.C + (g.Kp > K ? 1 : 0);          // work items per output row
+  const long long total = (long long)g.B * g.OH * g.OW * cpr;
+  const __nv_bfloat16 zero = __float2bfloat16(0.f);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int k = (int)(i % g.Kp);
-    const long long m = i / g.Kp;
-    __nv_bfloat16 v = __float2bfloat16(0.f);
-    if (k < K) {
-      const int kw = k % g.KW, kh = (k / g.KW) % g.KH, c = k / (g.KW * g.KH);
-      const int ow = (int)(m % g.OW), oh = (int)((m / g.OW) % g.OH), b = (int)(m / ((long long)g.OW * g.OH));
-      const int h = oh * g.sh - g.ph + kh * g.dh, w = ow * g.sw - g.pw + kw * g.dw;
-      if (h >= 0 && h < g.H && w >= 0 && w < g.W) v = x[(((long long)b * g.C + c) * g.H + h) * g.W + w];
+    const int c = (int)(i % cpr);
+    const long long m = i / cpr;
+    __nv_bfloat16* dst = cols + m * g.Kp;
+    if (c == g.C) {
+      for (int k = K; k < g.Kp; ++k) dst[k] = zero;
+      continue;
     }
-    cols[i] = v;
+    const int ow = (int)(m % g.OW), oh = (int)((m / g.OW) % g.OH), b = (int)(m / ((long long)g.OW * g.OH));
+    const __nv_bfloat16* src = x + ((long long)b * g.C + c) * g.H * g.W;
+    dst += c * KK;
+    const int h0 = oh * g.sh - g.ph, w0 = ow * g.sw - g.pw;
+    for (int kh = 0; kh < g.KH; ++kh) {
+      const int h = h0 + kh * g.dh;
+      const bool hok = h >= 0 && h < g.H;
+      for (int kw = 0; kw < g.KW; ++kw) {
+        const int w = w0 + kw * g.dw;
+        dst[kh * g.KW + kw] = (hok && w >= 0 && w < g.W) ? src[(long long)h * g.W + w] : zero;
+      }
+    }
   }
 }
 
@@ -80,9 +95,9 @@ int rtp_im2col(const void* x, void* cols, int B, int C, int H, int W, int KH, in
                int dh, int dw, int Kp, void* stream) {
   ConvGeom g;
   if (launch_geom(g, B, C, H, W, KH, KW, sh, sw, ph, pw, dh, dw, Kp)) return -1;
-  const long long total = (long long)g.B * g.OH * g.OW * g.Kp;
+  const long long total = (long long)g.B * g.OH * g.OW * (g.C + 1);
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > 148 * 32) blocks = 148 * 32;
   im2col_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)cols, g);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { g_err = std::string("im2col: ") + cudaGetErrorString(e); return -1; }
