@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       for (int p = 0; p < P.n_phases && ok; ++p) {
         const RtpPhase& ph = P.phases[p];
         const int tiles_m = (ph.M + TM - 1) / TM;
-        const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
+        const int tiles_n = (ph.N + ph.bn - 1) >> (31 - __clz(ph.bn));   // bn is a power of two
         const int per_batch = tiles_m * tiles_n;
         const int total = per_batch * ph.batch;
         if ((unit - ph.cta_off + GU) % GU >= total) continue;
@@ -154,6 +154,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const int p_bn = ph.bn;
         const int p_causal = ph.causal;
         const int p_batch_inner = ph.batch_inner;
+        const bool p_batch1 = ph.batch == 1;
         const int p_a_off_mn = ph.a_off_mn;
         const int p_a_off_k = ph.a_off_k;
         const int p_b_off_mn = ph.b_off_mn;
@@ -180,13 +181,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const bool a3 = p_a_mn && P.map3d[ph.a_map], b3 = p_b_mn && P.map3d[ph.b_map];
         if (p == 0) GEMM_STAMP(2);
         for (int t = (unit - p_cta_off + GU) % GU; t < total && ok; t += GU) {
-          const int z = t / per_batch, tt = t % per_batch;
-          const int m0u = (tt % tiles_m) * TM;              // first row of the unit's tile
+          // unbatched phases (the common case) skip the divisions by the batch geometry
+          const int z = p_batch1 ? 0 : t / per_batch, tt = p_batch1 ? t : t - z * per_batch;
+          const int tn = tt / tiles_m;
+          const int m0u = (tt - tn * tiles_m) * TM;          // first row of the unit's tile
           const int m0 = m0u + (int)crank * kBM;            // first row of this CTA's half
-          const int n0 = (tt / tiles_m) * p_bn;
+          const int n0 = tn * p_bn;
           if (p_causal == 1 && n0 > m0u + TM - 1) continue;
           const int kblocks = p_causal == 2 ? min(kblocks_full, (m0u + TM + kBK - 1) / kBK) : kblocks_full;
-          const int zo = z / p_batch_inner, zi = z % p_batch_inner;
+          const int zo = p_batch1 ? 0 : z / p_batch_inner, zi = p_batch1 ? 0 : z - zo * p_batch_inner;
           const int a_mn0 = m0 + p_a_off_mn + zo * p_a_bo_mn + zi * p_a_bi_mn;
           const int a_k0 = p_a_off_k + zo * p_a_bo_k + zi * p_a_bi_k;
           const int b_mn0 = n0 + (int)crank * bn_local + p_b_off_mn + zo * p_b_bo_mn + zi * p_b_bi_mn;
@@ -253,7 +256,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       for (int p = 0; p < P.n_phases && ok; ++p) {
         const RtpPhase& ph = P.phases[p];
         const int tiles_m = (ph.M + TM - 1) / TM;
-        const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
+        const int tiles_n = (ph.N + ph.bn - 1) >> (31 - __clz(ph.bn));   // bn is a power of two
         const int per_batch = tiles_m * tiles_n;
         const int total = per_batch * ph.batch;
         const int kblocks_full = (ph.K + kBK - 1) / kBK;
@@ -262,9 +265,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const uint32_t a_kstep16 = ph.a_mn ? 128u : 2u, b_kstep16 = ph.b_mn ? 128u : 2u;   // k-step of 16 elements, in 16-byte units
         const uint64_t da0 = make_smem_desc(0, a_lbo, 1024), db0 = make_smem_desc(0, b_lbo, 1024);
         for (int t = (unit - ph.cta_off + GU) % GU; t < total && ok; t += GU) {
-          const int tt = t % per_batch;
-          const int m0 = (tt % tiles_m) * TM;
-          const int n0 = (tt / tiles_m) * ph.bn;
+          const int tt = ph.batch == 1 ? t : t % per_batch;
+          const int tn = tt / tiles_m;
+          const int m0 = (tt - tn * tiles_m) * TM;
+          const int n0 = tn * ph.bn;
           if (ph.causal == 1 && n0 > m0 + TM - 1) continue;
           const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + TM + kBK - 1) / kBK) : kblocks_full;
           if (P.trace && cta == 0 && tr_m < 60) P.trace[1 * 256 + tr_m * 4 + 0] = globaltimer_ns();
@@ -320,14 +324,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       for (int p = 0; p < P.n_phases && ok; ++p) {
         const RtpPhase& ph = P.phases[p];
         const int tiles_m = (ph.M + TM - 1) / TM;
-        const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
+        const int tiles_n = (ph.N + ph.bn - 1) >> (31 - __clz(ph.bn));   // bn is a power of two
         const int per_batch = tiles_m * tiles_n;
         const int total = per_batch * ph.batch;
         const int kblocks_full = (ph.K + kBK - 1) / kBK;
         for (int t = (unit - ph.cta_off + GU) % GU; t < total && ok; t += GU) {
-          const int tt = t % per_batch;
-          const int m0 = (tt % tiles_m) * TM;
-          const int n0 = (tt / tiles_m) * ph.bn;
+          const int tt = ph.batch == 1 ? t : t % per_batch;
+          const int tn = tt / tiles_m;
+          const int m0 = (tt - tn * tiles_m) * TM;
+          const int n0 = tn * ph.bn;
           if (ph.causal == 1 && n0 > m0 + TM - 1) continue;
           const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + TM + kBK - 1) / kBK) : kblocks_full;
           for (int kb = 0; kb < kblocks; ++kb) {
@@ -351,7 +356,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
     for (int p = 0; p < P.n_phases; ++p) {
       const RtpPhase& ph = P.phases[p];
       const int tiles_m = (ph.M + TM - 1) / TM;
-      const int tiles_n = (ph.N + ph.bn - 1) / ph.bn;
+      const int tiles_n = (ph.N + ph.bn - 1) >> (31 - __clz(ph.bn));   // bn is a power of two
       const int per_batch = tiles_m * tiles_n;
       const int total = per_batch * ph.batch;
       const bool has_tiles = cta < total;
@@ -510,13 +515,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const bool e_fast_ok = e_vec_ok && (!e_bias || (reinterpret_cast<uintptr_t>(e_bias) & 15) == 0) &&
                              (!e_drop_thresh || (e_N & 3) == 0);
       for (int t = (unit - e_cta_off + GU) % GU; t < total && ok; t += GU) {
-        const int z = t / per_batch, tt = t % per_batch;
-        const int m0u = (tt % tiles_m) * TM;
+        const bool e_batch1 = e_batch_inner == 1 && per_batch == total;
+        const int z = e_batch1 ? 0 : t / per_batch, tt = e_batch1 ? t : t - z * per_batch;
+        const int tn = tt / tiles_m;
+        const int m0u = (tt - tn * tiles_m) * TM;
         const int m0 = m0u + (int)crank * kBM;
-        const int n0 = (tt / tiles_m) * e_bn;
+        const int n0 = tn * e_bn;
         if (e_causal == 1 && n0 > m0u + TM - 1) continue;
-        const long long zoff_d = (long long)(z / e_batch_inner) * e_d_bo + (long long)(z % e_batch_inner) * e_d_bi;
-        const long long zoff_c = (long long)(z / e_batch_inner) * e_c_bo + (long long)(z % e_batch_inner) * e_c_bi;
+        const long long zoff_d = e_batch1 ? 0ll : (long long)(z / e_batch_inner) * e_d_bo + (long long)(z % e_batch_inner) * e_d_bi;
+        const long long zoff_c = e_batch1 ? 0ll : (long long)(z / e_batch_inner) * e_c_bo + (long long)(z % e_batch_inner) * e_c_bi;
         uint32_t good = 1;
         const bool tr_on = P.trace && cta == 0 && warp == 2 && lane == 0 && tr_e < 60;
         if (tr_on) P.trace[2 * 256 + tr_e * 4 + 0] = globaltimer_ns();
