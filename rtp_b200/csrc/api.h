@@ -40,7 +40,7 @@ typedef struct {
   int b_bo_mn, b_bo_k, b_bi_mn, b_bi_k;
   void* d; long long ldd, d_bo, d_bi;
   float alpha;
-  int causal;      // 1: skip tiles above the diagonal; 2: stop the contraction at the diagonal
+  int causal;      // 1: skip tiles above the diagonal; 2: stop the contraction at the diagonal; 3: start it at the tile's first row
   int bn;          // 0 = auto
   unsigned long long* status;
 } RtpGemmBatched;

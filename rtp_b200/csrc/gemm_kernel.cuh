@@ -189,15 +189,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           const int n0 = tn * p_bn;
           if (p_causal == 1 && n0 > m0u + TM - 1) continue;
           const int kblocks = p_causal == 2 ? min(kblocks_full, (m0u + TM + kBK - 1) / kBK) : kblocks_full;
+          const int kb0 = p_causal == 3 ? m0u / kBK : 0;   // contraction index = query, output row = key: queries before the key contribute nothing
           const int zo = p_batch1 ? 0 : z / p_batch_inner, zi = p_batch1 ? 0 : z - zo * p_batch_inner;
           const int a_mn0 = m0 + p_a_off_mn + zo * p_a_bo_mn + zi * p_a_bi_mn;
           const int a_k0 = p_a_off_k + zo * p_a_bo_k + zi * p_a_bi_k;
           const int b_mn0 = n0 + (int)crank * bn_local + p_b_off_mn + zo * p_b_bo_mn + zi * p_b_bi_mn;
           const int b_k0 = p_b_off_k + zo * p_b_bo_k + zi * p_b_bi_k;
-          int ax = p_a_mn ? a_mn0 : a_k0, ay = p_a_mn ? a_k0 : a_mn0;
-          int bx = p_b_mn ? b_mn0 : b_k0, by = p_b_mn ? b_k0 : b_mn0;
+          int ax = (p_a_mn ? a_mn0 : a_k0) + kb0 * a_dx, ay = (p_a_mn ? a_k0 : a_mn0) + kb0 * a_dy;
+          int bx = (p_b_mn ? b_mn0 : b_k0) + kb0 * b_dx, by = (p_b_mn ? b_k0 : b_mn0) + kb0 * b_dy;
           if (P.trace && cta == 0 && tr_n < 60) P.trace[0 * 256 + tr_n * 4 + 0] = globaltimer_ns();
-          for (int kb = 0; kb < kblocks; ++kb) {
+          for (int kb = kb0; kb < kblocks; ++kb) {
             if (!mbar_wait_s(empty_s + stage * 8, phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
             const uint32_t sa = tiles_s + stage * kStageBytes;
             const uint32_t sb = sa + kABytes;
@@ -271,12 +272,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           const int n0 = tn * ph.bn;
           if (ph.causal == 1 && n0 > m0 + TM - 1) continue;
           const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + TM + kBK - 1) / kBK) : kblocks_full;
+          const int kb0 = ph.causal == 3 ? m0 / kBK : 0;
           if (P.trace && cta == 0 && tr_m < 60) P.trace[1 * 256 + tr_m * 4 + 0] = globaltimer_ns();
           if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
           if (P.trace && cta == 0 && tr_m < 60) P.trace[1 * 256 + tr_m * 4 + 1] = globaltimer_ns();
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
-          for (int kb = 0; kb < kblocks; ++kb) {
+          for (int kb = kb0; kb < kblocks; ++kb) {
             if (!mbar_wait_s(full_s + stage * 8, phase, abort_flag, status, timeout_ns)) { ok = false; break; }
             if (PAIR && !mbar_try_wait_cluster_s(peer_full_s + stage * 8, phase)) {
               // bounded: the slow path spins on the plain form, then the acquire is repeated once it has flipped
@@ -290,8 +292,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             for (int kk = 0; kk < kBK / 16; ++kk) {
               const uint64_t da = da0 + (uint64_t)(sa + kk * a_kstep16);
               const uint64_t db = db0 + (uint64_t)(sb + kk * b_kstep16);
-              if (PAIR) umma_bf16_pair(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
-              else umma_bf16(d_tmem, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+              if (PAIR) umma_bf16_pair(d_tmem, da, db, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+              else umma_bf16(d_tmem, da, db, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
             }
             issued_any = true;
             // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
@@ -335,7 +337,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           const int n0 = tn * ph.bn;
           if (ph.causal == 1 && n0 > m0 + TM - 1) continue;
           const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + TM + kBK - 1) / kBK) : kblocks_full;
-          for (int kb = 0; kb < kblocks; ++kb) {
+          const int kb0 = ph.causal == 3 ? m0 / kBK : 0;
+          for (int kb = kb0; kb < kblocks; ++kb) {
             if (!mbar_wait_s(full_s + stage * 8, phase, abort_flag, status, timeout_ns)) { ok = false; break; }
             mbar_arrive_cluster(lead_peer_full + stage * 8);   // plain arrive: a cluster-scope release costs about a microsecond here
             if (++stage == kStages) { stage = 0; phase ^= 1; }

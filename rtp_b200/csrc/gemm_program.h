@@ -52,7 +52,7 @@ struct RtpPhase {
   int M, N, K;
   int bn;  // tile width: 64, 128 or 256
   int b_box;      // rows per TMA box of a K-major B operand (64 or 128)
-  int causal;     // 1: skip tiles entirely above the diagonal (n0 > m0 + 127); 2: stop the k loop at the diagonal
+  int causal;     // 1: skip tiles entirely above the diagonal (n0 > m0 + 127); 2: stop the k loop at the diagonal; 3: start it at the tile's first row (transposed products)
   int cta_off;  // tile t of this phase runs on CTA (t + cta_off) % G, so that successive phases fill different SMs
   // batching: `batch` independent GEMMs whose operands are windows of the same 2-D tensors.  Batch z = (zo, zi) with
   // zi = z % batch_inner; the window of operand X starts at (mn, k) += zo * x_bo_{mn,k} + zi * x_bi_{mn,k} and the

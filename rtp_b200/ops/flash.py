@@ -61,7 +61,7 @@ class _CausalAttention(torch.autograd.Function):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         # dV_z = P_z^T dO_z : A = P read transposed (stored [q, keys]), B = dO stored [q, hd]
         _bgemm(p, True, BH * S, S, S, do, True, B * S, D, D, S, hd, S, BH, H, (0, H * S, 0, S, 0, S, hd, 0),
-               dv, D, S * D, hd)
+               dv, D, S * D, hd, causal=3)      # only queries at or after a key contribute to it
         # dP_z = dO_z V_z^T
         dp = torch.empty_like(p)
         _bgemm(do, False, B * S, D, D, v, False, B * S, D, D, S, S, hd, BH, H, (S, 0, 0, hd, S, 0, 0, hd),
@@ -71,7 +71,7 @@ class _CausalAttention(torch.autograd.Function):
         _bgemm(dp, False, BH * S, S, S, k, True, B * S, D, D, S, hd, S, BH, H, (H * S, 0, S, 0, 0, S, hd, 0),
                dq, D, S * D, hd, causal=2)
         _bgemm(dp, True, BH * S, S, S, q, True, B * S, D, D, S, hd, S, BH, H, (0, H * S, 0, S, 0, S, hd, 0),
-               dk, D, S * D, hd)
+               dk, D, S * D, hd, causal=3)
         return dq, dk, dv
 
 
