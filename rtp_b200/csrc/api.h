@@ -150,9 +150,21 @@ int rtp_reduce_scatter_cols_emu(const RtpRing* rings, const RtpReduceScatter* op
 int rtp_linear_fwd_emu(const RtpRing* rings, const RtpLinearFwd* ops, int world, void* stream);
 int rtp_linear_bwd_emu(const RtpRing* rings, const RtpLinearBwd* ops, int world, void* stream);
 
+// ------------------------------------------------------------------------------- in-place ring shift
+// Replaces every rank's buffer by its neighbour's through a small peer-mapped staging area (no second full-size buffer):
+// the transport of the memory-lean in-place rotation mode, and the library's rotate-only kernel.  direction 0 = "down"
+// (send to rank r-1, receive from r+1), 1 = "up".  world_emulated = 1 on a real ring (each process launches its own
+// rank); 2..4 emulate that many ranks on one GPU in one cooperative launch.
+unsigned long long rtp_shift_staging_bytes(int lanes);
+int rtp_shift_staging_create(int lanes, void** out);     // cudaMalloc + zeroed counters; IPC handle via rtp_ws_ipc_get
+int rtp_shift_staging_destroy(void* staging);
+int rtp_shift_max_lanes(void);
+int rtp_ring_shift(int world_emulated, void* const* buf, unsigned long long bytes, void* const* staging,
+                   void* const* dst_staging, void* const* src_staging, int direction, int lanes,
+                   unsigned long long* const* status, unsigned long long timeout_ns, void* stream);
+const char* rtp_shift_last_error(void);
+
 // ------------------------------------------------------------------------------------- workspace
-unsigned long long rtp_ws_bytes(unsigned long long slot_bytes);
-int rtp_ws_create(unsigned long long slot_bytes, void** out);   // cudaMalloc + zero flag block; large enough for any ring size
 unsigned long long rtp_ws_bytes_world(unsigned long long slot_bytes, int world);
 int rtp_ws_create_world(unsigned long long slot_bytes, int world, void** out);   // sized for rings of exactly `world` ranks
 int rtp_ws_destroy(void* ws);

@@ -497,9 +497,9 @@ uint32_t thresh_of(float p) {
   if (t > 4294967295.0) t = 4294967295.0;
   return (uint32_t)t;
 }
-template <typename K>
-int set_smem(K kernel, int bytes) {
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+template <auto Kern>
+int set_smem(int bytes) {
+  cudaError_t e = rtp::ensure_smem<Kern>(bytes);
   if (e != cudaSuccess) {
     g_err = std::string("attn_tc: cudaFuncSetAttribute: ") + cudaGetErrorString(e);
     return -1;
@@ -536,14 +536,12 @@ int rtp_attn_tc_fwd(const void* qkv, void* out, int S, int B, int heads, int nsh
   const int hpc = 128 / S;
   const int grid = (n_bh + hpc - 1) / hpc;
   if (S == 32) {
-    static bool once = false;
-    if (!once) { if (set_smem(attn_tc_fwd_kernel<32>, kFwdSmem)) return -1; once = true; }
+    if (set_smem<attn_tc_fwd_kernel<32>>(kFwdSmem)) return -1;
     rtp::launch_k(attn_tc_fwd_kernel<32>, dim3(grid), dim3(128), kFwdSmem, (cudaStream_t)stream, 
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, B, heads, nshard, causal, sm_scale, thresh_of(drop_p), ds, seed,
         offset, step_ptr, n_bh);
   } else {
-    static bool once = false;
-    if (!once) { if (set_smem(attn_tc_fwd_kernel<64>, kFwdSmem)) return -1; once = true; }
+    if (set_smem<attn_tc_fwd_kernel<64>>(kFwdSmem)) return -1;
     rtp::launch_k(attn_tc_fwd_kernel<64>, dim3(grid), dim3(128), kFwdSmem, (cudaStream_t)stream, 
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, B, heads, nshard, causal, sm_scale, thresh_of(drop_p), ds, seed,
         offset, step_ptr, n_bh);
@@ -562,14 +560,12 @@ int rtp_attn_tc_bwd(const void* qkv, const void* dout, void* dqkv, int S, int B,
   const int hpc = 128 / S;
   const int grid = (n_bh + hpc - 1) / hpc;
   if (S == 32) {
-    static bool once = false;
-    if (!once) { if (set_smem(attn_tc_bwd_kernel<32>, kBwdSmem)) return -1; once = true; }
+    if (set_smem<attn_tc_bwd_kernel<32>>(kBwdSmem)) return -1;
     rtp::launch_k(attn_tc_bwd_kernel<32>, dim3(grid), dim3(128), kBwdSmem, (cudaStream_t)stream, 
         (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dqkv, B, heads, nshard, causal, sm_scale,
         thresh_of(drop_p), ds, seed, offset, step_ptr, n_bh);
   } else {
-    static bool once = false;
-    if (!once) { if (set_smem(attn_tc_bwd_kernel<64>, kBwdSmem)) return -1; once = true; }
+    if (set_smem<attn_tc_bwd_kernel<64>>(kBwdSmem)) return -1;
     rtp::launch_k(attn_tc_bwd_kernel<64>, dim3(grid), dim3(128), kBwdSmem, (cudaStream_t)stream, 
         (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dqkv, B, heads, nshard, causal, sm_scale,
         thresh_of(drop_p), ds, seed, offset, step_ptr, n_bh);

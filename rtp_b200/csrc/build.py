@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_DIR = os.path.join(os.path.dirname(HERE), "lib")
 LIB_PATH = os.path.join(LIB_DIR, "librtp_b200.so")
-SOURCES = ["gemm.cu", "kernels.cu", "attn_tc.cu", "gate_rope.cu", "im2col.cu", "noalloc.cu"]
+SOURCES = ["gemm.cu", "kernels.cu", "attn_tc.cu", "flash_attn.cu", "ring_shift.cu", "gate_rope.cu", "im2col.cu", "noalloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-O3",

@@ -1,0 +1,908 @@
+// Flash attention on tcgen05 tensor cores: forward, dQ and dK/dV kernels (see flash_attn.h for the interface).
+//
+// One CTA = 128 query rows (forward, dQ) or 128 keys (dK/dV) of one (batch, head).  Six warps:
+//   warps 0-3  "row" threads: thread t owns TMEM lane t = row t of the tile.  The online softmax of a row (forward) and
+//              the dS algebra (backward) run in that thread's registers, without shuffles.
+//   warp 4     TMA producer: Q / K / V / dO tiles, 128 rows x 64 columns per copy, 128-byte swizzle, local memory only.
+//   warp 5     UMMA issuer (one elected thread).
+//
+// Forward, per block of 128 keys:  S = Q K^T (TMEM, double-buffered)  ->  row threads: scale, masks, running max,
+// P = exp2(S - m) as bf16 into a shared tile  ->  O += P V with O resident in TMEM.  O is rescaled in TMEM only when a
+// row's maximum has grown by more than 2^8 since the last rescale (the sum l carries the same offset, so the final
+// O / l is exact); most blocks skip the rescale.  Output: O / l and the row's log-sum-exp (log2 units).
+//
+// Backward recomputes P from Q, K and the saved log-sum-exp; nothing of size S x S touches global memory.
+//   dQ kernel   (CTA = query block): delta = rowsum(dO * O);  per key block: S, dP = dO V^T -> dS = P (dP - delta)
+//               -> dQ += dS K.
+//   dK/dV kernel (CTA = key block): per query block: S, dP -> P, dS tiles -> dV += P^T dO, dK += dS^T Q.  The P / dS
+//               tiles are written row-per-thread once and read by the UMMA as MN-major A operands (= transposed).
+// Every mbarrier wait is bounded; on expiry the CTA records a status code, drains its copies and UMMAs, frees its TMEM
+// and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "common.cuh"
+#include "flash_attn.h"
+#include "launch.h"
+#include "tmap.h"
+
+namespace {
+using namespace rtp;
+
+constexpr int kBlk = 128;              // rows of Q per CTA = keys per block
+constexpr int kSub = 16384;            // one [128 x 64] bf16 sub-tile with 128-byte rows
+constexpr int kThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleGap = 8.f;     // rescale O when a row maximum grew by more than 2^8
+
+struct DRef {                          // device copy of an RtpFlashRef
+  void* ptr;
+  long long sb, ss;
+  int col_base, hpg, gstride, hstride;
+};
+__device__ __forceinline__ int head_col(const DRef& r, int h) {
+  return r.col_base + (h / r.hpg) * r.gstride + (h % r.hpg) * r.hstride;
+}
+__device__ __forceinline__ __nv_bfloat16* row_ptr(const DRef& r, int b, int s, int h) {
+  return reinterpret_cast<__nv_bfloat16*>(r.ptr) + (long long)b * r.sb + (long long)s * r.ss + head_col(r, h);
+}
+
+struct MaskArgs {
+  const void* mask; long long mask_ld; int mask_fp32;
+  const unsigned char* kpm; long long kpm_ld;
+  int causal, Sq, Sk;
+  float scale_log2, sm_scale;
+  uint32_t thresh; float drop_scale;
+  unsigned long long seed, offset;
+  const unsigned long long* step_ptr;
+};
+
+struct alignas(64) FlashParams {
+  CUtensorMap mq, mk, mv, mdo;         // 3-D maps {columns, dim1, dim2}; *_seq1 tells which of dim1 / dim2 is the sequence
+  int q_seq1, k_seq1, v_seq1, do_seq1;
+  DRef q, k, v, o, dout, dq, dk, dv;
+  float* lse;
+  float* delta;
+  int B, H;
+  MaskArgs m;
+  unsigned long long* status;
+  unsigned long long timeout_ns;
+};
+
+struct Ctl {
+  uint64_t bar[16];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+__device__ __forceinline__ uint32_t sw128(int row, int chunk) {
+  return (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
+}
+__device__ __forceinline__ void tmem_ld32f(uint32_t taddr, float* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
+        "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]),
+        "=f"(r[16]), "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]),
+        "=f"(r[24]), "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32f(uint32_t taddr, const float* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]),
+        "f"(r[8]), "f"(r[9]), "f"(r[10]), "f"(r[11]), "f"(r[12]), "f"(r[13]), "f"(r[14]), "f"(r[15]),
+        "f"(r[16]), "f"(r[17]), "f"(r[18]), "f"(r[19]), "f"(r[20]), "f"(r[21]), "f"(r[22]), "f"(r[23]),
+        "f"(r[24]), "f"(r[25]), "f"(r[26]), "f"(r[27]), "f"(r[28]), "f"(r[29]), "f"(r[30]), "f"(r[31])
+      : "memory");
+}
+
+// Loads one [128 rows x 64 * SUB columns] tile of a (batch, head) into SUB swizzled sub-tiles.
+template <int SUB>
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, int seq1, int col, int b, int s0,
+                                          uint32_t bar) {
+  const unsigned long long m = reinterpret_cast<unsigned long long>(map);
+#pragma unroll
+  for (int u = 0; u < SUB; ++u) {
+    if (seq1) tma_load_3d_s(dst + u * kSub, m, col + u * 64, s0, b, bar);
+    else tma_load_3d_s(dst + u * kSub, m, col + u * 64, b, s0, bar);
+  }
+}
+
+// x[i] = log2-domain score of (row, col0 + i): scale, additive mask, key padding, causal and sequence bounds.
+// Masked entries become -inf.  `plain` = nothing but the scale applies to this block.
+template <int NC>
+__device__ __forceinline__ void score_chunk(float* x, int row, int col0, int b, const MaskArgs& m, bool plain) {
+#pragma unroll
+  for (int i = 0; i < NC; ++i) x[i] *= m.scale_log2;
+  if (plain) return;
+  if (m.mask && row < m.Sq) {
+    if (m.mask_fp32) {
+      const float* mp = reinterpret_cast<const float*>(m.mask) + (long long)row * m.mask_ld + col0;
+      if (col0 + NC <= m.Sk && (reinterpret_cast<uintptr_t>(mp) & 15) == 0) {
+#pragma unroll
+        for (int q = 0; q < NC / 4; ++q) {
+          const float4 v = __ldg(reinterpret_cast<const float4*>(mp) + q);
+          x[4 * q] += v.x * kLog2e; x[4 * q + 1] += v.y * kLog2e; x[4 * q + 2] += v.z * kLog2e; x[4 * q + 3] += v.w * kLog2e;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < NC; ++i) if (col0 + i < m.Sk) x[i] += __ldg(mp + i) * kLog2e;
+      }
+    } else {
+      const __nv_bfloat16* mp = reinterpret_cast<const __nv_bfloat16*>(m.mask) + (long long)row * m.mask_ld + col0;
+      if (col0 + NC <= m.Sk && (reinterpret_cast<uintptr_t>(mp) & 15) == 0) {
+#pragma unroll
+        for (int q = 0; q < NC / 8; ++q) {
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(mp) + q);
+          x[8 * q] += bf16_lo(v.x) * kLog2e; x[8 * q + 1] += bf16_hi(v.x) * kLog2e;
+          x[8 * q + 2] += bf16_lo(v.y) * kLog2e; x[8 * q + 3] += bf16_hi(v.y) * kLog2e;
+          x[8 * q + 4] += bf16_lo(v.z) * kLog2e; x[8 * q + 5] += bf16_hi(v.z) * kLog2e;
+          x[8 * q + 6] += bf16_lo(v.w) * kLog2e; x[8 * q + 7] += bf16_hi(v.w) * kLog2e;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < NC; ++i) if (col0 + i < m.Sk) x[i] += __bfloat162float(__ldg(mp + i)) * kLog2e;
+      }
+    }
+  }
+  if (m.kpm) {
+    const unsigned char* kp = m.kpm + (long long)b * m.kpm_ld + col0;
+#pragma unroll
+    for (int i = 0; i < NC; ++i) if (col0 + i < m.Sk && __ldg(kp + i)) x[i] = -INFINITY;
+  }
+  if (m.causal && col0 + NC - 1 > row) {
+#pragma unroll
+    for (int i = 0; i < NC; ++i) if (col0 + i > row) x[i] = -INFINITY;
+  }
+  if (col0 + NC > m.Sk) {
+#pragma unroll
+    for (int i = 0; i < NC; ++i) if (col0 + i >= m.Sk) x[i] = -INFINITY;
+  }
+}
+// keep bits of the NC probabilities (row, col0 ..) of head-batch bh: bit i set = kept.  Needs Sk % 4 == 0.
+template <int NC>
+__device__ __forceinline__ uint32_t keep_bits(const MaskArgs& m, unsigned long long offset, long long bh, int row, int col0) {
+  static_assert(NC <= 32, "keep mask is one word");
+  const unsigned long long e4 = (((unsigned long long)bh * m.Sq + row) * (unsigned long long)m.Sk + col0) >> 2;
+  uint32_t bits = 0;
+#pragma unroll
+  for (int g = 0; g < NC / 4; ++g) {
+    const uint4 r = philox4x32(m.seed, offset, e4 + g);
+    bits |= ((r.x >= m.thresh ? 1u : 0u) | (r.y >= m.thresh ? 2u : 0u) | (r.z >= m.thresh ? 4u : 0u) |
+             (r.w >= m.thresh ? 8u : 0u)) << (4 * g);
+  }
+  return bits;
+}
+__device__ __forceinline__ uint4 pack8f(const float* v) {
+  return make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+}
+
+// Common set-up: barriers, TMEM, abort flag.  Returns the TMEM base.
+__device__ __forceinline__ uint32_t setup_cta(Ctl* ctl, const int* counts, int nbar, int warp, int lane) {
+  pdl_launch_dependents();
+  if (warp == 4) {
+    if (lane < nbar) mbar_init(&ctl->bar[lane], counts[lane]);
+    if (lane == 31) ctl->abort_flag = 0;
+    mbar_fence_init();
+    __syncwarp();
+    tmem_alloc(&ctl->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();
+  return ctl->tmem_base;
+}
+__device__ __forceinline__ void teardown_cta(uint32_t tmem, int warp) {
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+// After an abort: wait (bounded) for the copies this thread has issued, so that none lands in a dead CTA.
+__device__ __forceinline__ void drain_loads(uint64_t* const* bars, const uint32_t* parity, const bool* issued, int n) {
+  for (int i = 0; i < n; ++i) {
+    if (!issued[i]) continue;
+    const unsigned long long t0 = globaltimer_ns();
+    while (!mbar_try_wait(bars[i], parity[i])) {
+      if (globaltimer_ns() - t0 > 2000000ull) break;
+    }
+  }
+}
+__device__ __forceinline__ void drain_mma(uint64_t* bar) {
+  umma_commit(bar);
+  const unsigned long long t0 = globaltimer_ns();
+  while (!mbar_try_wait(bar, 0)) {
+    if (globaltimer_ns() - t0 > 2000000ull) break;
+  }
+}
+
+// =====================================================================================================  forward
+// barriers
+enum { F_QFULL = 0, F_KFULL = 1, F_KEMPTY = 3, F_VFULL = 5, F_VEMPTY = 7, F_SFULL = 9, F_SEMPTY = 11, F_PFULL = 13,
+       F_PVDONE = 14, F_DRAIN = 15 };
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_constant__ FlashParams p) {
+  constexpr int SUB = HD / 64;
+  constexpr int TILE = SUB * kSub;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = sm;
+  uint8_t* sK = sQ + TILE;            // 2 stages
+  uint8_t* sV = sK + 2 * TILE;        // 2 stages
+  uint8_t* sP = sV + 2 * TILE;        // [128 x 128] bf16: two sub-tiles
+  Ctl* ctl = reinterpret_cast<Ctl*>(sP + 2 * kSub);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const MaskArgs& M = p.m;
+  const int nqb = (M.Sq + kBlk - 1) / kBlk;
+  const int BH = p.B * p.H;
+  // heaviest (last) query blocks first
+  const int qb = nqb - 1 - (int)(blockIdx.x / BH);
+  const int bh = (int)(blockIdx.x % BH);
+  const int b = bh / p.H, h = bh % p.H;
+  const int q0 = qb * kBlk;
+  int nkb = (M.Sk + kBlk - 1) / kBlk;
+  if (M.causal) nkb = min(nkb, qb + 1);
+
+  // counts by barrier index: Q/K/V full and empty 1 each, S full 1, S empty 4 (one per row warp), P full 128, rest 1
+  const int counts[16] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 4, 4, 128, 1, 1};
+  const uint32_t tmem = setup_cta(ctl, counts, 16, warp, lane);
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  unsigned long long* status = p.status;
+  const unsigned long long tmo = p.timeout_ns;
+  uint64_t* bar = ctl->bar;
+
+  if (warp == 4) {
+    // ---------------------------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      const int cq = head_col(p.q, h), ck = head_col(p.k, h), cv = head_col(p.v, h);
+      bool ok = true;
+      uint64_t* dbar[5]; uint32_t dpar[5]; bool dis[5] = {false, false, false, false, false};
+      mbar_arrive_expect_tx(&bar[F_QFULL], TILE);
+      load_tile<SUB>(smem_u32(sQ), &p.mq, p.q_seq1, cq, b, q0, smem_u32(&bar[F_QFULL]));
+      dbar[0] = &bar[F_QFULL]; dpar[0] = 0; dis[0] = true;
+      for (int j = 0; j < nkb && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!mbar_wait(&bar[F_KEMPTY + st], ph ^ 1u, abort_flag, status, tmo)) { ok = false; break; }
+        mbar_arrive_expect_tx(&bar[F_KFULL + st], TILE);
+        load_tile<SUB>(smem_u32(sK + st * TILE), &p.mk, p.k_seq1, ck, b, j * kBlk, smem_u32(&bar[F_KFULL + st]));
+        dbar[1 + st] = &bar[F_KFULL + st]; dpar[1 + st] = ph; dis[1 + st] = true;
+        if (!mbar_wait(&bar[F_VEMPTY + st], ph ^ 1u, abort_flag, status, tmo)) { ok = false; break; }
+        mbar_arrive_expect_tx(&bar[F_VFULL + st], TILE);
+        load_tile<SUB>(smem_u32(sV + st * TILE), &p.mv, p.v_seq1, cv, b, j * kBlk, smem_u32(&bar[F_VFULL + st]));
+        dbar[3 + st] = &bar[F_VFULL + st]; dpar[3 + st] = ph; dis[3 + st] = true;
+      }
+      if (!ok || *abort_flag) drain_loads(dbar, dpar, dis, 5);
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------------------------------- UMMA issuer
+    if (elect_one()) {
+      const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0), id_o = make_idesc_bf16(128, HD, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
+      bool ok = true, issued = false;
+      auto issue_s = [&](int j) {
+        const uint32_t kb = aK + (j & 1) * TILE, d = tmem + (uint32_t)((j & 1) * 128);
+#pragma unroll
+        for (int u = 0; u < SUB; ++u)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(d, make_smem_desc(aQ + u * kSub + kk * 32, 16, 1024), make_smem_desc(kb + u * kSub + kk * 32, 16, 1024),
+                      id_s, (u | kk) ? 1u : 0u);
+        umma_commit(&bar[F_KEMPTY + (j & 1)]);
+        umma_commit(&bar[F_SFULL + (j & 1)]);
+      };
+      ok = mbar_wait(&bar[F_QFULL], 0, abort_flag, status, tmo);
+      if (ok && nkb > 0) ok = mbar_wait(&bar[F_KFULL], 0, abort_flag, status, tmo);
+      if (ok && nkb > 0) { tc_fence_after(); issue_s(0); issued = true; }
+      for (int j = 0; j < nkb && ok; ++j) {
+        if (j + 1 < nkb) {
+          const int n = j + 1, st = n & 1;
+          const uint32_t ph = (uint32_t)(n >> 1) & 1u;
+          if (!mbar_wait(&bar[F_KFULL + st], ph, abort_flag, status, tmo)) { ok = false; break; }
+          if (!mbar_wait(&bar[F_SEMPTY + st], ph ^ 1u, abort_flag, status, tmo)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(n);
+        }
+        const int st = j & 1;
+        if (!mbar_wait(&bar[F_VFULL + st], (uint32_t)(j >> 1) & 1u, abort_flag, status, tmo)) { ok = false; break; }
+        if (!mbar_wait(&bar[F_PFULL], (uint32_t)j & 1u, abort_flag, status, tmo)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t vb = aV + st * TILE;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem + 256, make_smem_desc(aP + (kk >> 2) * kSub + (kk & 3) * 32, 16, 1024),
+                    make_smem_desc(vb + kk * 2048, kSub, 1024), id_o, (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&bar[F_VEMPTY + st]);
+        umma_commit(&bar[F_PVDONE]);
+      }
+      if (!ok && issued) drain_mma(&bar[F_DRAIN]);
+    }
+  } else {
+    // ---------------------------------------------------------------------------------- row threads
+    const int row = q0 + tid;
+    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const unsigned long long offset = M.offset + (M.step_ptr ? __ldg(M.step_ptr) * 65536ull : 0ull);
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkb; ++j) {
+      const int buf = j & 1;
+      uint32_t good = mbar_wait(&bar[F_SFULL + buf], (uint32_t)(j >> 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
+      if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+      tc_fence_after();
+      float s[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32f(lane_addr + (uint32_t)(buf * 128 + c * 32), s + 32 * c);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[F_SEMPTY + buf]);
+      const int col0 = j * kBlk;
+      const bool plain = !M.mask && !M.kpm && !(M.causal && j == qb) && (col0 + kBlk <= M.Sk);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) score_chunk<32>(s + 32 * c, row, col0 + 32 * c, b, M, plain);
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      const float cand = fmaxf(m_used, mx);
+      const bool need = cand > m_used + kRescaleGap;
+      const float m_new = need ? cand : m_used;
+      const float mref = (m_new == -INFINITY) ? 0.f : m_new;
+      float rs = 0.f;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) {
+        s[i] = exp2f(s[i] - mref);
+        rs += s[i];
+      }
+      if (j > 0) {
+        // P V of the previous block must be complete before the P tile is overwritten and before O is rescaled
+        good = mbar_wait(&bar[F_PVDONE], (uint32_t)(j - 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
+        if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, need)) {
+          const float alpha = need ? exp2f(m_used - cand) : 1.f;
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            float o[32];
+            tmem_ld32f(lane_addr + (uint32_t)(256 + c * 32), o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_st32f(lane_addr + (uint32_t)(256 + c * 32), o);
+          }
+          tmem_st_wait();
+          l *= alpha;
+        }
+      }
+      m_used = m_new;
+      l += rs;
+      if (M.thresh) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t keep = keep_bits<32>(M, offset, bh, min(row, M.Sq - 1), col0 + 32 * c);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[32 * c + i] = ((keep >> i) & 1u) ? s[32 * c + i] * M.drop_scale : 0.f;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 16; ++c)
+        *reinterpret_cast<uint4*>(sP + (c >> 3) * kSub + sw128(tid, c & 7)) = pack8f(s + 8 * c);
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(&bar[F_PFULL]);
+    }
+    if (ok && nkb > 0) {
+      uint32_t good = mbar_wait(&bar[F_PVDONE], (uint32_t)(nkb - 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
+      if (!__all_sync(0xffffffffu, good)) ok = false;
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = row < M.Sq ? row_ptr(p.o, b, row, h) : nullptr;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        float o[32];
+        if (nkb > 0) {
+          tmem_ld32f(lane_addr + (uint32_t)(256 + c * 32), o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= inv;
+        if (dst) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = pack8f(o + 8 * q);
+        }
+      }
+      if (row < M.Sq && p.lse) {
+        const float mref = (m_used == -INFINITY) ? 0.f : m_used;
+        p.lse[(long long)bh * M.Sq + row] = l > 0.f ? mref + log2f(l) : INFINITY;
+      }
+    }
+  }
+  teardown_cta(tmem, warp);
+}
+
+// =====================================================================================================  dQ
+enum { Q_QFULL = 0, Q_KVFULL = 1, Q_KVEMPTY = 3, Q_SDPFULL = 5, Q_DSFULL = 6, Q_DONE = 7, Q_DRAIN = 8 };
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_constant__ FlashParams p) {
+  constexpr int SUB = HD / 64;
+  constexpr int TILE = SUB * kSub;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = sm;
+  uint8_t* sG = sQ + TILE;            // dO
+  uint8_t* sK = sG + TILE;            // 2 stages
+  uint8_t* sV = sK + 2 * TILE;        // 2 stages
+  uint8_t* sS = sV + 2 * TILE;        // dS [128 x 128] bf16
+  Ctl* ctl = reinterpret_cast<Ctl*>(sS + 2 * kSub);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const MaskArgs& M = p.m;
+  const int nqb = (M.Sq + kBlk - 1) / kBlk;
+  const int BH = p.B * p.H;
+  const int qb = nqb - 1 - (int)(blockIdx.x / BH);
+  const int bh = (int)(blockIdx.x % BH);
+  const int b = bh / p.H, h = bh % p.H;
+  const int q0 = qb * kBlk;
+  int nkb = (M.Sk + kBlk - 1) / kBlk;
+  if (M.causal) nkb = min(nkb, qb + 1);
+  const int counts[16] = {1, 1, 1, 1, 1, 1, 128, 1, 1, 1, 1, 1, 1, 1, 1, 1};
+  const uint32_t tmem = setup_cta(ctl, counts, 9, warp, lane);
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  unsigned long long* status = p.status;
+  const unsigned long long tmo = p.timeout_ns;
+  uint64_t* bar = ctl->bar;
+
+  if (warp == 4) {
+    if (elect_one()) {
+      const int cq = head_col(p.q, h), ck = head_col(p.k, h), cv = head_col(p.v, h), cg = head_col(p.dout, h);
+      bool ok = true;
+      uint64_t* dbar[3]; uint32_t dpar[3]; bool dis[3] = {false, false, false};
+      mbar_arrive_expect_tx(&bar[Q_QFULL], 2 * TILE);
+      load_tile<SUB>(smem_u32(sQ), &p.mq, p.q_seq1, cq, b, q0, smem_u32(&bar[Q_QFULL]));
+      load_tile<SUB>(smem_u32(sG), &p.mdo, p.do_seq1, cg, b, q0, smem_u32(&bar[Q_QFULL]));
+      dbar[0] = &bar[Q_QFULL]; dpar[0] = 0; dis[0] = true;
+      for (int j = 0; j < nkb && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!mbar_wait(&bar[Q_KVEMPTY + st], ph ^ 1u, abort_flag, status, tmo)) { ok = false; break; }
+        mbar_arrive_expect_tx(&bar[Q_KVFULL + st], 2 * TILE);
+        load_tile<SUB>(smem_u32(sK + st * TILE), &p.mk, p.k_seq1, ck, b, j * kBlk, smem_u32(&bar[Q_KVFULL + st]));
+        load_tile<SUB>(smem_u32(sV + st * TILE), &p.mv, p.v_seq1, cv, b, j * kBlk, smem_u32(&bar[Q_KVFULL + st]));
+        dbar[1 + st] = &bar[Q_KVFULL + st]; dpar[1 + st] = ph; dis[1 + st] = true;
+      }
+      if (!ok || *abort_flag) drain_loads(dbar, dpar, dis, 3);
+    }
+  } else if (warp == 5) {
+    if (elect_one()) {
+      const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0), id_q = make_idesc_bf16(128, HD, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aG = smem_u32(sG), aK = smem_u32(sK), aV = smem_u32(sV), aS = smem_u32(sS);
+      bool ok = mbar_wait(&bar[Q_QFULL], 0, abort_flag, status, tmo);
+      bool issued = false;
+      for (int j = 0; j < nkb && ok; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&bar[Q_KVFULL + st], (uint32_t)(j >> 1) & 1u, abort_flag, status, tmo)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t kb = aK + st * TILE, vb = aV + st * TILE;
+        // S = Q K^T  (columns 0..127),  dP = dO V^T  (columns 128..255)
+#pragma unroll
+        for (int u = 0; u < SUB; ++u)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem, make_smem_desc(aQ + u * kSub + kk * 32, 16, 1024), make_smem_desc(kb + u * kSub + kk * 32, 16, 1024),
+                      id_s, (u | kk) ? 1u : 0u);
+#pragma unroll
+        for (int u = 0; u < SUB; ++u)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem + 128, make_smem_desc(aG + u * kSub + kk * 32, 16, 1024),
+                      make_smem_desc(vb + u * kSub + kk * 32, 16, 1024), id_s, (u | kk) ? 1u : 0u);
+        umma_commit(&bar[Q_SDPFULL]);
+        issued = true;
+        if (!mbar_wait(&bar[Q_DSFULL], (uint32_t)j & 1u, abort_flag, status, tmo)) { ok = false; break; }
+        tc_fence_after();
+        // dQ += dS K   (A = dS, K-major over the keys; B = K block read MN-major)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem + 256, make_smem_desc(aS + (kk >> 2) * kSub + (kk & 3) * 32, 16, 1024),
+                    make_smem_desc(kb + kk * 2048, kSub, 1024), id_q, (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&bar[Q_KVEMPTY + st]);
+        if (j == nkb - 1) umma_commit(&bar[Q_DONE]);
+      }
+      if (!ok && issued) drain_mma(&bar[Q_DRAIN]);
+    }
+  } else {
+    const int row = q0 + tid;
+    const bool live = row < M.Sq;
+    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const unsigned long long offset = M.offset + (M.step_ptr ? __ldg(M.step_ptr) * 65536ull : 0ull);
+    // delta = rowsum(dO * O), kept for the dK / dV kernel as well
+    float delta = 0.f, lse2 = INFINITY;
+    if (live) {
+      const uint4* op = reinterpret_cast<const uint4*>(row_ptr(p.o, b, row, h));
+      const uint4* gp = reinterpret_cast<const uint4*>(row_ptr(p.dout, b, row, h));
+#pragma unroll
+      for (int c = 0; c < HD / 8; ++c) {
+        const uint4 a = __ldg(op + c), g = __ldg(gp + c);
+        delta += bf16_lo(a.x) * bf16_lo(g.x) + bf16_hi(a.x) * bf16_hi(g.x) + bf16_lo(a.y) * bf16_lo(g.y) +
+                 bf16_hi(a.y) * bf16_hi(g.y) + bf16_lo(a.z) * bf16_lo(g.z) + bf16_hi(a.z) * bf16_hi(g.z) +
+                 bf16_lo(a.w) * bf16_lo(g.w) + bf16_hi(a.w) * bf16_hi(g.w);
+      }
+      p.delta[(long long)bh * M.Sq + row] = delta;
+      lse2 = p.lse[(long long)bh * M.Sq + row];
+    }
+    bool ok = true;
+    for (int j = 0; j < nkb; ++j) {
+      uint32_t good = mbar_wait(&bar[Q_SDPFULL], (uint32_t)j & 1u, abort_flag, status, tmo) ? 1u : 0u;
+      if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+      tc_fence_after();
+      const int col0 = j * kBlk;
+      const bool plain = !M.mask && !M.kpm && !(M.causal && j == qb) && (col0 + kBlk <= M.Sk);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float x[32], dp[32];
+        tmem_ld32f(lane_addr + (uint32_t)(c * 32), x);
+        tmem_ld32f(lane_addr + (uint32_t)(128 + c * 32), dp);
+        tmem_ld_wait();
+        score_chunk<32>(x, row, col0 + 32 * c, b, M, plain);
+        uint32_t keep = 0xffffffffu;
+        if (M.thresh) keep = keep_bits<32>(M, offset, bh, min(row, M.Sq - 1), col0 + 32 * c);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float pr = exp2f(x[i] - lse2);
+          const float d = ((keep >> i) & 1u) ? dp[i] * M.drop_scale : 0.f;
+          x[i] = pr * (d - delta);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(sS + (c >> 1) * kSub + sw128(tid, (c & 1) * 4 + q)) = pack8f(x + 8 * q);
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(&bar[Q_DSFULL]);
+    }
+    if (ok && nkb > 0) {
+      uint32_t good = mbar_wait(&bar[Q_DONE], 0, abort_flag, status, tmo) ? 1u : 0u;
+      if (!__all_sync(0xffffffffu, good)) ok = false;
+    }
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* dst = live ? row_ptr(p.dq, b, row, h) : nullptr;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        float o[32];
+        if (nkb > 0) {
+          tmem_ld32f(lane_addr + (uint32_t)(256 + c * 32), o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= M.sm_scale;
+        if (dst) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = pack8f(o + 8 * q);
+        }
+      }
+    }
+  }
+  teardown_cta(tmem, warp);
+}
+
+// =====================================================================================================  dK / dV
+enum { K_KVFULL = 0, K_QGFULL = 1, K_QGEMPTY = 3, K_SDPFULL = 5, K_DSFULL = 6, K_DONE = 7, K_DRAIN = 8 };
+
+template <int HD, int NS>
+__global__ void __launch_bounds__(kThreads, 1) flash_dkv_kernel(const __grid_constant__ FlashParams p) {
+  constexpr int SUB = HD / 64;
+  constexpr int TILE = SUB * kSub;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = sm;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sQ = sV + TILE;            // NS stages
+  uint8_t* sG = sQ + NS * TILE;       // NS stages (dO)
+  uint8_t* sP = sG + NS * TILE;       // dropped probabilities [q][keys]
+  uint8_t* sS = sP + 2 * kSub;        // dS [q][keys]
+  Ctl* ctl = reinterpret_cast<Ctl*>(sS + 2 * kSub);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const MaskArgs& M = p.m;
+  const int nqb = (M.Sq + kBlk - 1) / kBlk;
+  const int BH = p.B * p.H;
+  // with a causal mask the first key blocks see the most query blocks: they go first
+  const int kb = (int)(blockIdx.x / BH);
+  const int bh = (int)(blockIdx.x % BH);
+  const int b = bh / p.H, h = bh % p.H;
+  const int k0 = kb * kBlk;
+  const int i0 = M.causal ? kb : 0;
+  const int nit = nqb - i0;
+  const int counts[16] = {1, 1, 1, 1, 1, 1, 128, 1, 1, 1, 1, 1, 1, 1, 1, 1};
+  const uint32_t tmem = setup_cta(ctl, counts, 9, warp, lane);
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  unsigned long long* status = p.status;
+  const unsigned long long tmo = p.timeout_ns;
+  uint64_t* bar = ctl->bar;
+
+  if (warp == 4) {
+    if (elect_one()) {
+      const int cq = head_col(p.q, h), ck = head_col(p.k, h), cv = head_col(p.v, h), cg = head_col(p.dout, h);
+      bool ok = true;
+      uint64_t* dbar[3]; uint32_t dpar[3]; bool dis[3] = {false, false, false};
+      mbar_arrive_expect_tx(&bar[K_KVFULL], 2 * TILE);
+      load_tile<SUB>(smem_u32(sK), &p.mk, p.k_seq1, ck, b, k0, smem_u32(&bar[K_KVFULL]));
+      load_tile<SUB>(smem_u32(sV), &p.mv, p.v_seq1, cv, b, k0, smem_u32(&bar[K_KVFULL]));
+      dbar[0] = &bar[K_KVFULL]; dpar[0] = 0; dis[0] = true;
+      for (int it = 0; it < nit && ok; ++it) {
+        const int st = it % NS;
+        const uint32_t ph = (uint32_t)(it / NS) & 1u;
+        if (!mbar_wait(&bar[K_QGEMPTY + st], ph ^ 1u, abort_flag, status, tmo)) { ok = false; break; }
+        mbar_arrive_expect_tx(&bar[K_QGFULL + st], 2 * TILE);
+        load_tile<SUB>(smem_u32(sQ + st * TILE), &p.mq, p.q_seq1, cq, b, (i0 + it) * kBlk, smem_u32(&bar[K_QGFULL + st]));
+        load_tile<SUB>(smem_u32(sG + st * TILE), &p.mdo, p.do_seq1, cg, b, (i0 + it) * kBlk, smem_u32(&bar[K_QGFULL + st]));
+        dbar[1 + st] = &bar[K_QGFULL + st]; dpar[1 + st] = ph; dis[1 + st] = true;
+      }
+      if (!ok || *abort_flag) drain_loads(dbar, dpar, dis, 1 + NS);
+    }
+  } else if (warp == 5) {
+    if (elect_one()) {
+      const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0), id_t = make_idesc_bf16(128, HD, 1, 1);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aG = smem_u32(sG);
+      const uint32_t aP = smem_u32(sP), aS = smem_u32(sS);
+      bool ok = mbar_wait(&bar[K_KVFULL], 0, abort_flag, status, tmo);
+      bool issued = false;
+      for (int it = 0; it < nit && ok; ++it) {
+        const int st = it % NS;
+        if (!mbar_wait(&bar[K_QGFULL + st], (uint32_t)(it / NS) & 1u, abort_flag, status, tmo)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t qb_ = aQ + st * TILE, gb = aG + st * TILE;
+        // S = Q K^T (columns 0..127), dP = dO V^T (columns 128..255): rows = queries
+#pragma unroll
+        for (int u = 0; u < SUB; ++u)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem, make_smem_desc(qb_ + u * kSub + kk * 32, 16, 1024), make_smem_desc(aK + u * kSub + kk * 32, 16, 1024),
+                      id_s, (u | kk) ? 1u : 0u);
+#pragma unroll
+        for (int u = 0; u < SUB; ++u)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem + 128, make_smem_desc(gb + u * kSub + kk * 32, 16, 1024),
+                      make_smem_desc(aV + u * kSub + kk * 32, 16, 1024), id_s, (u | kk) ? 1u : 0u);
+        umma_commit(&bar[K_SDPFULL]);
+        issued = true;
+        if (!mbar_wait(&bar[K_DSFULL], (uint32_t)it & 1u, abort_flag, status, tmo)) { ok = false; break; }
+        tc_fence_after();
+        // dV += P^T dO, dK += dS^T Q: rows = keys; both operands are read MN-major (contraction over the 128 queries)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem + 256, make_smem_desc(aP + kk * 2048, kSub, 1024), make_smem_desc(gb + kk * 2048, kSub, 1024), id_t,
+                    (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem + 256 + HD, make_smem_desc(aS + kk * 2048, kSub, 1024), make_smem_desc(qb_ + kk * 2048, kSub, 1024),
+                    id_t, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&bar[K_QGEMPTY + st]);
+        if (it == nit - 1) umma_commit(&bar[K_DONE]);
+      }
+      if (!ok && issued) drain_mma(&bar[K_DRAIN]);
+    }
+  } else {
+    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const unsigned long long offset = M.offset + (M.step_ptr ? __ldg(M.step_ptr) * 65536ull : 0ull);
+    bool ok = true;
+    for (int it = 0; it < nit; ++it) {
+      const int qb = i0 + it;
+      const int row = qb * kBlk + tid;
+      float delta = 0.f, lse2 = INFINITY;
+      if (row < M.Sq) {
+        delta = __ldg(p.delta + (long long)bh * M.Sq + row);
+        lse2 = __ldg(p.lse + (long long)bh * M.Sq + row);
+      }
+      uint32_t good = mbar_wait(&bar[K_SDPFULL], (uint32_t)it & 1u, abort_flag, status, tmo) ? 1u : 0u;
+      if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+      tc_fence_after();
+      const bool plain = !M.mask && !M.kpm && !(M.causal && qb == kb) && (k0 + kBlk <= M.Sk);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float x[32], dp[32];
+        tmem_ld32f(lane_addr + (uint32_t)(c * 32), x);
+        tmem_ld32f(lane_addr + (uint32_t)(128 + c * 32), dp);
+        tmem_ld_wait();
+        score_chunk<32>(x, row, k0 + 32 * c, b, M, plain);
+        uint32_t keep = 0xffffffffu;
+        if (M.thresh) keep = keep_bits<32>(M, offset, bh, min(row, M.Sq - 1), k0 + 32 * c);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float pr = exp2f(x[i] - lse2);
+          const bool kp = (keep >> i) & 1u;
+          const float d = kp ? dp[i] * M.drop_scale : 0.f;
+          dp[i] = pr * (d - delta);               // dS
+          x[i] = kp ? pr * M.drop_scale : 0.f;    // dropped probability
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t off = (uint32_t)(c >> 1) * kSub + sw128(tid, (c & 1) * 4 + q);
+          *reinterpret_cast<uint4*>(sP + off) = pack8f(x + 8 * q);
+          *reinterpret_cast<uint4*>(sS + off) = pack8f(dp + 8 * q);
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(&bar[K_DSFULL]);
+    }
+    if (ok && nit > 0) {
+      uint32_t good = mbar_wait(&bar[K_DONE], 0, abort_flag, status, tmo) ? 1u : 0u;
+      if (!__all_sync(0xffffffffu, good)) ok = false;
+    }
+    if (ok) {
+      tc_fence_after();
+      const int key = k0 + tid;
+      __nv_bfloat16* dvp = key < M.Sk ? row_ptr(p.dv, b, key, h) : nullptr;
+      __nv_bfloat16* dkp = key < M.Sk ? row_ptr(p.dk, b, key, h) : nullptr;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        float o[32];
+        if (nit > 0) { tmem_ld32f(lane_addr + (uint32_t)(256 + c * 32), o); tmem_ld_wait(); }
+        else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+        }
+        if (dvp) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dvp + c * 32 + q * 8) = pack8f(o + 8 * q);
+        }
+        if (nit > 0) { tmem_ld32f(lane_addr + (uint32_t)(256 + HD + c * 32), o); tmem_ld_wait(); }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= M.sm_scale;
+        if (dkp) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dkp + c * 32 + q * 8) = pack8f(o + 8 * q);
+        }
+      }
+    }
+  }
+  teardown_cta(tmem, warp);
+}
+
+// =====================================================================================================  host
+thread_local std::string g_ferr;
+int ffail(const std::string& s) { g_ferr = s; return -1; }
+
+uint32_t thresh_of(float pdrop) {
+  if (pdrop <= 0.f) return 0u;
+  double t = (double)pdrop * 4294967296.0;
+  if (t > 4294967295.0) t = 4294967295.0;
+  return (uint32_t)t;
+}
+
+// 3-D map {width columns, dim1, dim2} over a [batch, seq, width] view; the dimension with the smaller stride comes first.
+int make_map3(CUtensorMap* m, int* seq1, const RtpFlashRef& r, int B, int S, const char* what) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return ffail("cuTensorMapEncodeTiled entry point not found");
+  if ((reinterpret_cast<uintptr_t>(r.ptr) & 15) != 0) return ffail(std::string(what) + ": base is not 16-byte aligned");
+  if ((r.sb * 2) % 16 || (r.ss * 2) % 16) return ffail(std::string(what) + ": strides must be multiples of 16 bytes");
+  if (r.width <= 0) return ffail(std::string(what) + ": width missing");
+  const bool s_first = r.ss <= r.sb || B == 1;
+  *seq1 = s_first ? 1 : 0;
+  cuuint64_t dims[3] = {(cuuint64_t)r.width, (cuuint64_t)(s_first ? S : B), (cuuint64_t)(s_first ? B : S)};
+  cuuint64_t strides[2] = {(cuuint64_t)(s_first ? r.ss : r.sb) * 2, (cuuint64_t)(s_first ? r.sb : r.ss) * 2};
+  if (B == 1) strides[1] = strides[0] * (cuuint64_t)S;   // a single batch: any legal pitch
+  cuuint32_t box[3] = {64u, s_first ? 128u : 1u, s_first ? 1u : 128u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult rc = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, r.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return ffail(std::string(what) + ": cuTensorMapEncodeTiled failed with code " + std::to_string((int)rc));
+  return 0;
+}
+DRef dref(const RtpFlashRef& r) {
+  DRef d;
+  d.ptr = r.ptr; d.sb = r.sb; d.ss = r.ss;
+  d.col_base = r.col_base; d.hpg = r.hpg > 0 ? r.hpg : 1; d.gstride = r.gstride; d.hstride = r.hstride;
+  return d;
+}
+int check_ref(const RtpFlashRef& r, const char* what, int hd) {
+  if (!r.ptr) return ffail(std::string(what) + ": null pointer");
+  if ((reinterpret_cast<uintptr_t>(r.ptr) & 15) || (r.sb % 8) || (r.ss % 8) || (r.col_base % 8) || (r.gstride % 8) ||
+      (r.hstride % 8))
+    return ffail(std::string(what) + ": rows of a head must be 16-byte aligned");
+  (void)hd;
+  return 0;
+}
+int fill_common(const RtpFlashArgs* a, FlashParams& P) {
+  if (a->head_dim != 64 && a->head_dim != 128) return ffail("flash attention: head_dim must be 64 or 128");
+  if (a->B <= 0 || a->H <= 0 || a->Sq <= 0 || a->Sk <= 0) return ffail("flash attention: empty problem");
+  if (a->causal && a->Sq != a->Sk) return ffail("flash attention: a causal mask needs Sq == Sk");
+  if (a->drop_p > 0.f && a->Sk % 4) return ffail("flash attention: dropout needs Sk to be a multiple of 4");
+  if (!a->status) return ffail("flash attention: status word required");
+  P.B = a->B; P.H = a->H;
+  P.m.mask = a->mask; P.m.mask_ld = a->mask_ld; P.m.mask_fp32 = a->mask_fp32;
+  P.m.kpm = a->kpm; P.m.kpm_ld = a->kpm_ld;
+  P.m.causal = a->causal; P.m.Sq = a->Sq; P.m.Sk = a->Sk;
+  P.m.sm_scale = a->sm_scale; P.m.scale_log2 = a->sm_scale * kLog2e;
+  P.m.thresh = thresh_of(a->drop_p);
+  P.m.drop_scale = a->drop_p > 0.f ? 1.f / (1.f - a->drop_p) : 1.f;
+  P.m.seed = a->seed; P.m.offset = a->offset; P.m.step_ptr = a->step_ptr;
+  P.status = a->status;
+  P.timeout_ns = 2000000000ull;
+  P.lse = a->lse;
+  P.delta = a->delta;
+  if (check_ref(a->q, "q", a->head_dim) || check_ref(a->k, "k", a->head_dim) || check_ref(a->v, "v", a->head_dim) ||
+      check_ref(a->o, "o", a->head_dim))
+    return -1;
+  if (make_map3(&P.mq, &P.q_seq1, a->q, a->B, a->Sq, "q")) return -1;
+  if (make_map3(&P.mk, &P.k_seq1, a->k, a->B, a->Sk, "k")) return -1;
+  if (make_map3(&P.mv, &P.v_seq1, a->v, a->B, a->Sk, "v")) return -1;
+  P.q = dref(a->q); P.k = dref(a->k); P.v = dref(a->v); P.o = dref(a->o);
+  return 0;
+}
+constexpr int smem_fwd(int hd) { return 1024 + (hd / 64) * kSub * 5 + 2 * kSub + 256; }
+constexpr int smem_dq(int hd) { return 1024 + (hd / 64) * kSub * 6 + 2 * kSub + 256; }
+constexpr int smem_dkv(int hd, int ns) { return 1024 + (hd / 64) * kSub * (2 + 2 * ns) + 4 * kSub + 256; }
+static_assert(sizeof(Ctl) <= 256, "control block");
+static_assert(smem_dq(128) <= 232448 && smem_dkv(128, 1) <= 232448 && smem_dkv(64, 2) <= 232448, "shared memory budget");
+
+template <auto Kern>
+int launch_flash(const FlashParams& P, int grid, int smem, cudaStream_t stream, const char* what) {
+  cudaError_t e = ensure_smem<Kern>(smem);
+  if (e != cudaSuccess) return ffail(std::string(what) + ": cudaFuncSetAttribute: " + cudaGetErrorString(e));
+  e = launch_k(Kern, dim3(grid), dim3(kThreads), smem, stream, P);
+  if (e != cudaSuccess) return ffail(std::string(what) + ": " + cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* rtp_flash_last_error(void) { return g_ferr.c_str(); }
+
+int rtp_flash_fwd(const RtpFlashArgs* a, void* stream) {
+  static thread_local FlashParams P;
+  if (fill_common(a, P)) return -1;
+  if (!a->lse) return ffail("flash attention: lse buffer required");
+  const int grid = ((a->Sq + kBlk - 1) / kBlk) * a->B * a->H;
+  if (a->head_dim == 64) return launch_flash<flash_fwd_kernel<64>>(P, grid, smem_fwd(64), (cudaStream_t)stream, "flash_fwd");
+  return launch_flash<flash_fwd_kernel<128>>(P, grid, smem_fwd(128), (cudaStream_t)stream, "flash_fwd");
+}
+
+int rtp_flash_bwd(const RtpFlashArgs* a, void* stream) {
+  static thread_local FlashParams P;
+  if (fill_common(a, P)) return -1;
+  if (!a->lse || !a->delta) return ffail("flash attention backward: lse and delta buffers required");
+  if (check_ref(a->dout, "dout", a->head_dim) || check_ref(a->dq, "dq", a->head_dim) || check_ref(a->dk, "dk", a->head_dim) ||
+      check_ref(a->dv, "dv", a->head_dim))
+    return -1;
+  if (make_map3(&P.mdo, &P.do_seq1, a->dout, a->B, a->Sq, "dout")) return -1;
+  P.dout = dref(a->dout); P.dq = dref(a->dq); P.dk = dref(a->dk); P.dv = dref(a->dv);
+  const int gq = ((a->Sq + kBlk - 1) / kBlk) * a->B * a->H;
+  const int gk = ((a->Sk + kBlk - 1) / kBlk) * a->B * a->H;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (a->head_dim == 64) {
+    if (launch_flash<flash_dq_kernel<64>>(P, gq, smem_dq(64), s, "flash_dq")) return -1;
+    return launch_flash<flash_dkv_kernel<64, 2>>(P, gk, smem_dkv(64, 2), s, "flash_dkv");
+  }
+  if (launch_flash<flash_dq_kernel<128>>(P, gq, smem_dq(128), s, "flash_dq")) return -1;
+  return launch_flash<flash_dkv_kernel<128, 1>>(P, gk, smem_dkv(128, 1), s, "flash_dkv");
+}
+
+}  // extern "C"

@@ -19,27 +19,15 @@
 #include "api.h"
 #include "gemm_kernel.cuh"
 #include "launch.h"
+#include "tmap.h"
 
 namespace {
 
 thread_local std::string g_err;
 int fail(const std::string& s) { g_err = s; return -1; }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
+using rtp::EncodeTiledFn;
+EncodeTiledFn get_encode() { return rtp::get_encode_tiled(); }
 
 // 2-D bf16 tensor map over a row-major [outer, inner] view with row pitch `ld` elements.
 // box = [box_outer rows, 64 elements], 128-byte swizzle, zero fill outside the tensor.
@@ -86,14 +74,18 @@ int make_map_mn3(CUtensorMap* m, const void* ptr, long long mn, long long k, lon
   return make_map_mn(m, ptr, mn, k, ld);
 }
 
+// Per-device facts are cached per device: one process may drive several GPUs.
+constexpr int kMaxDevices = 64;
+int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < kMaxDevices) ? dev : 0;
+}
 int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
+  static int n[kMaxDevices] = {0};
+  const int dev = current_device();
+  if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+  return n[dev];
 }
 
 void init_phase(RtpPhase& ph) {
@@ -195,12 +187,14 @@ void finalize_program(RtpProgram& P, int ctas, bool pair) {
 
 template <int NEMU, bool PAIR>
 int launch_impl(const rtp::GemmParams<NEMU>& params, int grid, bool cooperative, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  // the shared-memory limit is an attribute of the kernel on ONE device: set once per (instantiation, device)
+  static bool attr_set[kMaxDevices] = {false};
+  const int dev = current_device();
+  if (!attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(rtp::rtp_gemm_kernel<NEMU, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          rtp::kSmemBytes);
     if (e != cudaSuccess) return fail(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-    attr_set = true;
+    attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -945,8 +939,7 @@ int rtp_linear_bwd_emu(const RtpRing* rings, const RtpLinearBwd* ops, int world,
 }
 
 // ------------------------------------------------------------------------------------- workspace
-// bytes of a workspace that serves rings of up to RTP_NUM_SLOTS ranks / of exactly `world` ranks
-unsigned long long rtp_ws_bytes(unsigned long long slot_bytes) { return kFlagBytes + ((RTP_NUM_WBANKS + 1) * RTP_NUM_SLOTS - RTP_NUM_WBANKS) * slot_bytes; }
+// bytes of a workspace that serves rings of exactly `world` ranks
 unsigned long long rtp_ws_bytes_world(unsigned long long slot_bytes, int world) {
   if (world < 1) world = 1;
   return kFlagBytes + (unsigned long long)(RTP_NUM_WBANKS * (world - 1) + world) * slot_bytes;
@@ -957,15 +950,6 @@ int rtp_ws_create_world(unsigned long long slot_bytes, int world, void** out) {
   if (e != cudaSuccess) return fail(std::string("cudaMalloc workspace: ") + cudaGetErrorString(e));
   e = cudaMemset(p, 0, kFlagBytes);
   if (e != cudaSuccess) { cudaFree(p); return fail("cudaMemset workspace failed"); }
-  *out = p;
-  return 0;
-}
-int rtp_ws_create(unsigned long long slot_bytes, void** out) {
-  void* p = nullptr;
-  cudaError_t e = cudaMalloc(&p, rtp_ws_bytes(slot_bytes));
-  if (e != cudaSuccess) return fail(std::string("cudaMalloc workspace: ") + cudaGetErrorString(e));
-  e = cudaMemset(p, 0, kFlagBytes);
-  if (e != cudaSuccess) return fail(std::string("cudaMemset workspace: ") + cudaGetErrorString(e));
   *out = p;
   return 0;
 }

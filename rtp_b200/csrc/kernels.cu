@@ -301,12 +301,13 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(
 // and overwrites the logits with grad_scale * (softmax - onehot), i.e. the gradient of
 // grad_scale * sum_rows(loss). Rows whose target equals ignore_index give zero loss and gradient.
 // ------------------------------------------------------------------------------------------------
-__global__ void ce_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ target,
+__global__ void ce_kernel(__nv_bfloat16* logits, long long ld, const long long* __restrict__ target,
                           float* __restrict__ loss, int M, int V, float grad_scale, long long ignore_index,
-                          int write_grad) {
+                          int write_grad, __nv_bfloat16* grad, long long ldg) {
   __shared__ float red[32];
   for (int row = blockIdx.x; row < M; row += gridDim.x) {
     __nv_bfloat16* lp = logits + (size_t)row * ld;
+    __nv_bfloat16* gp = grad ? grad + (size_t)row * ldg : lp;   // the gradient may go to a buffer of its own
     const long long t = target[row];
     float mx = -INFINITY;
     for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
@@ -339,7 +340,7 @@ __global__ void ce_kernel(__nv_bfloat16* __restrict__ logits, long long ld, cons
           if (c + i == t) p -= 1.f;
           v[i] = ignored ? 0.f : p * grad_scale;
         }
-        *reinterpret_cast<uint4*>(lp + c) = pack8(v);
+        *reinterpret_cast<uint4*>(gp + c) = pack8(v);
       }
     }
     __syncthreads();
@@ -699,27 +700,33 @@ __device__ __forceinline__ void adam_load(const RtpAdamTensor& t, long long i0, 
   } else {
     _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) { r.pv[i] = __bfloat162float(p[i]); r.gv[i] = __bfloat162float(g[i]); }
   }
+  // state_fp32: 0 = both moments bf16, 1 = both fp32, 2 = first moment bf16, second moment fp32
   r.svec = r.cnt == 8 && ((reinterpret_cast<uintptr_t>(t.m) | reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
-  if (t.state_fp32) {
+  if (t.state_fp32 == 1) {
     const float* m = reinterpret_cast<const float*>(t.m) + i0;
-    const float* v = reinterpret_cast<const float*>(t.v) + i0;
     if (r.svec) {
       const float4 a = __ldcs(reinterpret_cast<const float4*>(m)), b = __ldcs(reinterpret_cast<const float4*>(m) + 1);
-      const float4 c = __ldcs(reinterpret_cast<const float4*>(v)), d = __ldcs(reinterpret_cast<const float4*>(v) + 1);
       r.mv[0] = a.x; r.mv[1] = a.y; r.mv[2] = a.z; r.mv[3] = a.w; r.mv[4] = b.x; r.mv[5] = b.y; r.mv[6] = b.z; r.mv[7] = b.w;
-      r.vv[0] = c.x; r.vv[1] = c.y; r.vv[2] = c.z; r.vv[3] = c.w; r.vv[4] = d.x; r.vv[5] = d.y; r.vv[6] = d.z; r.vv[7] = d.w;
     } else {
-      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) { r.mv[i] = m[i]; r.vv[i] = v[i]; }
+      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) r.mv[i] = m[i];
     }
   } else {
     const __nv_bfloat16* m = reinterpret_cast<const __nv_bfloat16*>(t.m) + i0;
-    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(t.v) + i0;
+    if (r.svec) unpack8(__ldcs(reinterpret_cast<const uint4*>(m)), r.mv);
+    else { _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) r.mv[i] = __bfloat162float(m[i]); }
+  }
+  if (t.state_fp32 >= 1) {
+    const float* v = reinterpret_cast<const float*>(t.v) + i0;
     if (r.svec) {
-      unpack8(__ldcs(reinterpret_cast<const uint4*>(m)), r.mv);
-      unpack8(__ldcs(reinterpret_cast<const uint4*>(v)), r.vv);
+      const float4 c = __ldcs(reinterpret_cast<const float4*>(v)), d = __ldcs(reinterpret_cast<const float4*>(v) + 1);
+      r.vv[0] = c.x; r.vv[1] = c.y; r.vv[2] = c.z; r.vv[3] = c.w; r.vv[4] = d.x; r.vv[5] = d.y; r.vv[6] = d.z; r.vv[7] = d.w;
     } else {
-      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) { r.mv[i] = __bfloat162float(m[i]); r.vv[i] = __bfloat162float(v[i]); }
+      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) r.vv[i] = v[i];
     }
+  } else {
+    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(t.v) + i0;
+    if (r.svec) unpack8(__ldcs(reinterpret_cast<const uint4*>(v)), r.vv);
+    else { _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) r.vv[i] = __bfloat162float(v[i]); }
   }
 }
 __device__ __forceinline__ void adam_update_store(const RtpAdamTensor& t, AdamRegs& r, float lr, float beta1, float beta2,
@@ -739,26 +746,31 @@ __device__ __forceinline__ void adam_update_store(const RtpAdamTensor& t, AdamRe
   __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(t.p) + r.i0;
   if (r.vec) __stcs(reinterpret_cast<uint4*>(p), pack8(r.pv));
   else { _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) p[i] = __float2bfloat16(r.pv[i]); }
-  if (t.state_fp32) {
+  if (t.state_fp32 == 1) {
     float* m = reinterpret_cast<float*>(t.m) + r.i0;
-    float* v = reinterpret_cast<float*>(t.v) + r.i0;
     if (r.svec) {
       __stcs(reinterpret_cast<float4*>(m), make_float4(r.mv[0], r.mv[1], r.mv[2], r.mv[3]));
       __stcs(reinterpret_cast<float4*>(m) + 1, make_float4(r.mv[4], r.mv[5], r.mv[6], r.mv[7]));
-      __stcs(reinterpret_cast<float4*>(v), make_float4(r.vv[0], r.vv[1], r.vv[2], r.vv[3]));
-      __stcs(reinterpret_cast<float4*>(v) + 1, make_float4(r.vv[4], r.vv[5], r.vv[6], r.vv[7]));
     } else {
-      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) { m[i] = r.mv[i]; v[i] = r.vv[i]; }
+      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) m[i] = r.mv[i];
     }
   } else {
     __nv_bfloat16* m = reinterpret_cast<__nv_bfloat16*>(t.m) + r.i0;
-    __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(t.v) + r.i0;
+    if (r.svec) __stcs(reinterpret_cast<uint4*>(m), pack8(r.mv));
+    else { _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) m[i] = __float2bfloat16(r.mv[i]); }
+  }
+  if (t.state_fp32 >= 1) {
+    float* v = reinterpret_cast<float*>(t.v) + r.i0;
     if (r.svec) {
-      __stcs(reinterpret_cast<uint4*>(m), pack8(r.mv));
-      __stcs(reinterpret_cast<uint4*>(v), pack8(r.vv));
+      __stcs(reinterpret_cast<float4*>(v), make_float4(r.vv[0], r.vv[1], r.vv[2], r.vv[3]));
+      __stcs(reinterpret_cast<float4*>(v) + 1, make_float4(r.vv[4], r.vv[5], r.vv[6], r.vv[7]));
     } else {
-      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) { m[i] = __float2bfloat16(r.mv[i]); v[i] = __float2bfloat16(r.vv[i]); }
+      _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) v[i] = r.vv[i];
     }
+  } else {
+    __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(t.v) + r.i0;
+    if (r.svec) __stcs(reinterpret_cast<uint4*>(v), pack8(r.vv));
+    else { _Pragma("unroll") for (int i = 0; i < 8; ++i) if (i < r.cnt) v[i] = __float2bfloat16(r.vv[i]); }
   }
 }
 
@@ -1066,10 +1078,14 @@ int rtp_norm_bwd(const void* dy, const void* h, const void* gamma, const float* 
 }
 int rtp_cross_entropy(void* logits, long long ld, const long long* target, float* loss, int M, int V, float grad_scale,
                       long long ignore_index, int write_grad, void* stream) {
-  if (V % 8 || ld % 8) { k_err = "cross_entropy: V and ld must be multiples of 8"; return -1; }
+  return rtp_cross_entropy_to(logits, ld, target, loss, M, V, grad_scale, ignore_index, write_grad, nullptr, 0, stream);
+}
+int rtp_cross_entropy_to(void* logits, long long ld, const long long* target, float* loss, int M, int V, float grad_scale,
+                         long long ignore_index, int write_grad, void* grad, long long ldg, void* stream) {
+  if (V % 8 || ld % 8 || (grad && ldg % 8)) { k_err = "cross_entropy: V and the row pitches must be multiples of 8"; return -1; }
   const int grid = M < 148 * 8 ? M : 148 * 8;
   ce_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits, ld, target, loss, M, V, grad_scale,
-                                                    ignore_index, write_grad);
+                                                    ignore_index, write_grad, (__nv_bfloat16*)grad, ldg);
   LAUNCH_CHECK("cross_entropy");
   return 0;
 }

@@ -25,6 +25,9 @@ int rtp_norm_bwd(const void* dy, const void* h, const void* gamma, const float* 
                  const unsigned long long* step_ptr, void* stream);
 int rtp_cross_entropy(void* logits, long long ld, const long long* target, float* loss, int M, int V, float grad_scale,
                       long long ignore_index, int write_grad, void* stream);
+// Same, but the gradient goes to `grad` (row pitch ldg) and the logits stay as they are; grad = null: in place.
+int rtp_cross_entropy_to(void* logits, long long ld, const long long* target, float* loss, int M, int V, float grad_scale,
+                         long long ignore_index, int write_grad, void* grad, long long ldg, void* stream);
 int rtp_embed_fwd(const void* table, const long long* ids, const void* pe, long long ld_pe, int tokens_per_pos,
                   void* out, long long ld_out, int col_off, int T, int Ds, int D, float scale, float drop_p,
                   unsigned long long seed, unsigned long long offset, const unsigned long long* step_ptr,

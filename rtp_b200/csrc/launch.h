@@ -16,6 +16,21 @@ inline bool pdl_enabled() {
   return on == 1;
 }
 
+// Raises the dynamic shared-memory limit of kernel `Kern` on the current device, once per (kernel, device): the
+// attribute belongs to the kernel on one device, so a process that drives several GPUs sets it on each.
+template <auto Kern>
+cudaError_t ensure_smem(int bytes) {
+  constexpr int kMaxDev = 64;
+  static bool done[kMaxDev] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDev) dev = 0;
+  if (done[dev]) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done[dev] = true;
+  return e;
+}
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
   cudaLaunchConfig_t cfg = {};

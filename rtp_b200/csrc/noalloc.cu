@@ -44,6 +44,19 @@ extern "C" {
 
 const char* rtp_noalloc_last_error(void) { return g_msg.c_str(); }
 
+int rtp_noalloc_status(void* stream, unsigned long long* host_out) {
+  if (!host_out) return nfail("rtp_noalloc_status: null output pointer");
+  void* scratch = nullptr;
+  if (scratch_for_current_device(&scratch)) return -1;
+  const RtpFlagBlock* fb = reinterpret_cast<const RtpFlagBlock*>(scratch);
+  cudaError_t e = cudaMemcpyAsync(host_out, &fb->status.v, sizeof(unsigned long long), cudaMemcpyDeviceToHost,
+                                  (cudaStream_t)stream);
+  if (e != cudaSuccess) return nfail(std::string("status copy: ") + cudaGetErrorString(e));
+  e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return nfail(std::string("status sync: ") + cudaGetErrorString(e));
+  return 0;
+}
+
 int rtp_linear_bwd_noalloc(const void* x, long long ldx, const void* dy, long long ldy, const void* w,
                            long long bias_off, int M, int in_features, int out_features, void* dx, long long lddx,
                            void* grad_flat, void* stream) {

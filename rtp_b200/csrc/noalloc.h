@@ -14,11 +14,16 @@
 //   * out_features <= RTP_NOALLOC_MAX_OUT_FEATURES, else the call fails with a clear error and launches nothing.
 //     The array costs RTP_NOALLOC_SCRATCH_BYTES (about 264 KB) of device memory on every GPU that loads the
 //     library, from load until the process exits.
-//   * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and sets a kernel
-//     attribute.  Make that first call before starting any stream capture.
+//   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, cached per device) and
+//     raises the kernel's shared-memory limit on that device (also kept per device).  Make that first call before
+//     starting any stream capture.
 //   * Every call reuses the same array and the array keeps the previous call's contents; the entry point clears
 //     the parts that must start at zero.  Two calls that overlap on the GPU (different streams, no ordering) race
 //     on it: order them on one stream or with events.
+//   * The kernel's waits are bounded; one that runs out leaves a non-zero code in a status word that also lives in
+//     the array.  The entry point returns before the kernel has run, so poll rtp_noalloc_status after the work (it
+//     copies the word to the host and synchronises the stream; it allocates nothing either).  The next call clears
+//     the word.
 //   * Nothing here calls cudaMalloc, cudaFree or any allocating library routine.  Inputs and outputs are the
 //     caller's buffers: x [M, in], dy [M, out], w = flat shard (weight [out, in], bias at element bias_off or -1),
 //     dx [M, in] (may be null), grad_flat (same layout as w).  All bf16, 16-byte aligned, row pitches in elements.
@@ -33,6 +38,9 @@ extern "C" {
 int rtp_linear_bwd_noalloc(const void* x, long long ldx, const void* dy, long long ldy, const void* w,
                            long long bias_off, int M, int in_features, int out_features, void* dx, long long lddx,
                            void* grad_flat, void* stream);
+// Copies the status word of the last rtp_linear_bwd_noalloc call on the current device into *host_out (0 = ok, else
+// the code of the first bounded wait that ran out) and synchronises `stream`.
+int rtp_noalloc_status(void* stream, unsigned long long* host_out);
 const char* rtp_noalloc_last_error(void);
 
 #ifdef __cplusplus

@@ -43,8 +43,11 @@ class _Lin:
 class FusedLMTrainer:
     def __init__(self, model, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, adamw=False,
                  clip_value: Optional[float] = None, loss_scale: Optional[float] = None, use_graph: bool = True,
-                 seed: int = 1234, group=None):
+                 seed: int = 1234, group=None, state_dtype=None):
+        """``state_dtype``: Adam moment policy, ``None`` / ``"fp32"`` (default), ``"mixed"`` or ``"bf16"``
+        (see ``rtp_b200.ops.kernels.adam_state_dtypes``)."""
         self.model = model
+        self.state_dtypes = K.adam_state_dtypes(state_dtype)
         self.ring = get_context(group)
         self.N = self.ring.world
         cfg = model.config
@@ -133,8 +136,8 @@ class FusedLMTrainer:
         entries = []
 
         def add(p, g):
-            m1 = torch.zeros_like(p)
-            m2 = torch.zeros_like(p)
+            m1 = torch.zeros_like(p, dtype=self.state_dtypes[0])
+            m2 = torch.zeros_like(p, dtype=self.state_dtypes[1])
             mult = 1.0 / getattr(p, "rtp_sum_replicated") if getattr(p, "rtp_sum_replicated", None) else 1.0
             entries.append((p.data, g, m1, m2, mult))
             p.grad = g

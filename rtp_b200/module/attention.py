@@ -138,42 +138,18 @@ class ParallelMultiheadAttention(RotatedModule):
     def layers(self):
         return [self.MultiheadAttention] * self.world_size
 
-    def _fused_ok(self, query, same_qkv, batched, key_padding_mask, need_weights, attn_mask, is_causal):
-        """Fused sm_100a path: causal self-attention on bf16 CUDA tensors, packed projection with biases, no
-        attention-probability dropout, head_dim 64/128."""
-        from ..parallel import fused
-        sub = self.MultiheadAttention
-        if not (same_qkv and batched and not need_weights and key_padding_mask is None):
-            return False
-        if not (sub._qkv_same_embed_dim and sub.in_proj_bias is not None and sub.bias_k is None and not sub.add_zero_attn):
-            return False
-        if self.training and sub.dropout > 0:
-            return False
-        if not fused.use_fused(query, self._full_param):
-            return False
-        L = query.shape[1] if self.batch_first else query.shape[0]
-        hd = sub.head_dim
-        if not ((hd == 64 and L <= 96) or (L % 128 == 0 and hd in (64, 128))):
-            return False
-        if attn_mask is not None:
-            # accept exactly the causal (square subsequent) mask
-            if attn_mask.dim() != 2 or attn_mask.shape != (L, L):
-                return False
-            causal = torch.full((L, L), float("-inf"), device=attn_mask.device, dtype=torch.float32).triu_(1)
-            if attn_mask.dtype == torch.bool:
-                return bool(torch.equal(attn_mask, causal == float("-inf")))
-            return bool(torch.equal(attn_mask.float(), causal))
-        return bool(is_causal)
-
     def forward(self, query: Tensor, key: Tensor, value: Tensor, key_padding_mask: Optional[Tensor] = None,
                 need_weights: bool = True, attn_mask: Optional[Tensor] = None, average_attn_weights: bool = True,
                 is_causal: bool = False, test_tensor=None) -> Tuple[Tensor, Optional[Tensor]]:
         sub = self.MultiheadAttention
         batched = query.dim() == 3
         same_qkv = (key is value) and (query is key)
-        if self._fused_ok(query, same_qkv, batched, key_padding_mask, need_weights, attn_mask, is_causal):
-            from ..parallel.engine import fused_mha
-            return fused_mha(self, query, True), None
+        if self._full_param.is_cuda:
+            from ..parallel import engine
+            if engine.mha_fused_ok(self, sub, query, key, value, key_padding_mask, need_weights, attn_mask, self.training):
+                return engine.fused_mha(self, sub, query, is_causal=is_causal, attn_mask=attn_mask,
+                                        key_padding_mask=key_padding_mask, need_weights=need_weights,
+                                        average_attn_weights=average_attn_weights, training=self.training)
         if self.batch_first and batched:
             query, key, value = [t.transpose(1, 0) for t in (query, key, value)]
         names = self._names

@@ -60,10 +60,10 @@ class ColumnParallelConv2d(RotatedModule):
     def forward(self, input_: torch.Tensor) -> torch.Tensor:  # type: ignore
         conv = self.conv
         has_bias = conv.bias is not None
-        if fused.use_fused(input_, self._full_param):
+        if fused.use_fused(input_, self._full_param) and not (self.inplace and self.world_size > 1):
             from ..parallel import engine
-            if engine.fused_conv_ok(self, input_):
-                return engine.fused_conv(self, input_)
+            if engine.fused_conv_ok(conv, input_):
+                return engine.fused_conv(self, conv, input_)
 
         def fn(j, views, x):
             # nn.Conv2d._conv_forward handles every padding_mode

@@ -67,7 +67,7 @@ class ParallelEmbedding(RotatedModule):
         if pad is None and mx is None and not sg and self._full_param.is_cuda and \
                 fused.use_fused(self._full_param, self._full_param) and self.embedding_dim_per_partition % 8 == 0:
             from ..parallel.engine import fused_embedding
-            return fused_embedding(self, input_)
+            return fused_embedding(self, input_, self.embedding.weight, self.embedding_dim)
 
         def fn(j, views, ids):
             return F.embedding(ids, views[0], pad, mx, nt, sg, False)

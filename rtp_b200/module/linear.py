@@ -111,7 +111,8 @@ class _RotatedLinearBase(RotatedModule):
         return [self.linear] * self.world_size
 
     def forward(self, input_: torch.Tensor) -> torch.Tensor:  # type: ignore
-        if fused.use_fused(input_, self._full_param):
+        if fused.use_fused(input_, self._full_param) and \
+                fused.linear_ok(self.row, self.in_features, self.out_features, self.world_size):
             return fused.linear(self, input_, row=self.row)
         has_bias = self.linear.bias is not None
         if self.row:

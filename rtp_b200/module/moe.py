@@ -153,6 +153,8 @@ class WeightMOELayer(RotatedModule):
 
     def _fused_ok(self, dispatched):
         from ..parallel import fused
+        if self.inplace and self.world_size > 1:
+            return False          # memory-lean mode: the expert shard itself travels (rotated_apply + ring-shift kernel)
         ex = self.experts[0]
         if not (hasattr(ex, "linear1") and hasattr(ex, "linear2") and isinstance(ex.linear1, nn.Linear)
                 and isinstance(ex.linear2, nn.Linear) and ex.linear1.bias is not None and ex.linear2.bias is not None):

@@ -112,6 +112,25 @@ class ExpertBwd(C.Structure):
     ]
 
 
+class FlashRef(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("sb", C.c_longlong), ("ss", C.c_longlong), ("width", C.c_longlong),
+                ("col_base", C.c_int), ("hpg", C.c_int), ("gstride", C.c_int), ("hstride", C.c_int)]
+
+
+class FlashArgs(C.Structure):
+    _fields_ = [
+        ("q", FlashRef), ("k", FlashRef), ("v", FlashRef), ("o", FlashRef),
+        ("dout", FlashRef), ("dq", FlashRef), ("dk", FlashRef), ("dv", FlashRef),
+        ("lse", C.c_void_p), ("delta", C.c_void_p),
+        ("B", C.c_int), ("H", C.c_int), ("Sq", C.c_int), ("Sk", C.c_int), ("head_dim", C.c_int), ("causal", C.c_int),
+        ("mask", C.c_void_p), ("mask_ld", C.c_longlong), ("mask_fp32", C.c_int),
+        ("kpm", C.c_void_p), ("kpm_ld", C.c_longlong),
+        ("sm_scale", C.c_float),
+        ("drop_p", C.c_float), ("seed", C.c_ulonglong), ("offset", C.c_ulonglong), ("step_ptr", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
 class ReduceScatter(C.Structure):
     _fields_ = [("src", C.c_void_p), ("ld", C.c_longlong), ("rows", C.c_int), ("cols", C.c_int), ("out", C.c_void_p)]
 
@@ -135,13 +154,12 @@ def lib():
                 "(the CUDA kernels are mandatory on a GPU machine; there is no PyTorch fallback)")
         L = C.CDLL(LIB_PATH)
         L.rtp_last_error.restype = C.c_char_p
-        L.rtp_ws_bytes.restype = C.c_ulonglong
-        L.rtp_ws_bytes.argtypes = [C.c_ulonglong]
+        L.rtp_ws_bytes_world.restype = C.c_ulonglong
+        L.rtp_ws_bytes_world.argtypes = [C.c_ulonglong, C.c_int]
         L.rtp_ws_wslot.restype = C.c_void_p
         L.rtp_ws_wslot.argtypes = [C.c_void_p, C.c_ulonglong, C.c_int, C.c_int]
         L.rtp_ws_gslot.restype = C.c_void_p
         L.rtp_ws_gslot.argtypes = [C.c_void_p, C.c_ulonglong, C.c_int, C.c_int]
-        L.rtp_ws_create.argtypes = [C.c_ulonglong, C.POINTER(C.c_void_p)]
         L.rtp_ws_create_world.argtypes = [C.c_ulonglong, C.c_int, C.POINTER(C.c_void_p)]
         L.rtp_ws_destroy.argtypes = [C.c_void_p]
         L.rtp_ws_reset.argtypes = [C.c_void_p, C.c_void_p]
@@ -162,6 +180,17 @@ def lib():
         L.rtp_expert_fwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(ExpertFwd), C.c_int, C.c_void_p]
         L.rtp_expert_bwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(ExpertBwd), C.c_int, C.c_void_p]
         L.rtp_set_pair_mode.argtypes = [C.c_int]
+        L.rtp_shift_staging_bytes.restype = C.c_ulonglong
+        L.rtp_shift_staging_bytes.argtypes = [C.c_int]
+        L.rtp_shift_staging_create.argtypes = [C.c_int, C.POINTER(C.c_void_p)]
+        L.rtp_shift_staging_destroy.argtypes = [C.c_void_p]
+        L.rtp_ring_shift.argtypes = [C.c_int, C.POINTER(C.c_void_p), C.c_ulonglong, C.POINTER(C.c_void_p),
+                                     C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int, C.c_int,
+                                     C.POINTER(C.c_void_p), C.c_ulonglong, C.c_void_p]
+        L.rtp_shift_last_error.restype = C.c_char_p
+        L.rtp_flash_fwd.argtypes = [C.POINTER(FlashArgs), C.c_void_p]
+        L.rtp_flash_bwd.argtypes = [C.POINTER(FlashArgs), C.c_void_p]
+        L.rtp_flash_last_error.restype = C.c_char_p
         L.rtp_linear_fwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(LinearFwd), C.c_int, C.c_void_p]
         L.rtp_linear_bwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(LinearBwd), C.c_int, C.c_void_p]
         _lib = L

@@ -45,23 +45,27 @@ def rms_norm(x, weight, eps=1e-5):
 
 
 class _CrossEntropyFn(torch.autograd.Function):
+    """Mean token cross-entropy of bf16 logits.  The input is never modified: the softmax gradient, produced in the same
+    pass over the logits, goes to a buffer of its own, and only when the logits need a gradient."""
+
     @staticmethod
     def forward(ctx, logits, target, ignore_index):
         from . import kernels as K
         lg = logits.reshape(-1, logits.shape[-1])
-        work = lg.clone() if (not lg.is_contiguous() or logits.requires_grad) else lg
-        work = work.contiguous()
+        if lg.stride(1) != 1 or lg.stride(0) % 8:
+            lg = lg.contiguous()
         t = target.reshape(-1)
         n = (t != ignore_index).sum().clamp(min=1)
-        rows = K.cross_entropy_(work, t, grad_scale=1.0, ignore_index=ignore_index)
-        ctx.save_for_backward(work, n)
+        grad = torch.empty(lg.shape, dtype=lg.dtype, device=lg.device) if ctx.needs_input_grad[0] else None
+        rows = K.cross_entropy_to(lg, t, grad, grad_scale=1.0, ignore_index=ignore_index)
+        ctx.save_for_backward(grad, n)
         ctx.shape = logits.shape
         return rows.sum() / n
 
     @staticmethod
     def backward(ctx, g):
-        work, n = ctx.saved_tensors
-        return (work * (g / n).to(work.dtype)).view(ctx.shape), None, None
+        grad, n = ctx.saved_tensors
+        return grad.mul_((g / n).to(grad.dtype)).view(ctx.shape), None, None
 
 
 def cross_entropy(logits, target, ignore_index=-100):
@@ -97,14 +101,13 @@ class _SmallAttnFn(torch.autograd.Function):
 
 
 def causal_attention(q, k, v):
-    """Causal self-attention on [B, S, H, hd] tensors."""
+    """Causal self-attention on [B, S, H, hd] tensors (views are fine: the flash kernels take strides)."""
     B, S, H, hd = q.shape
     if use_kernels(q) and hd == 64 and S <= 96:
         return _SmallAttnFn.apply(q, k, v)
-    if use_kernels(q):
-        from .flash import flash_attention_available, flash_attention
-        if flash_attention_available(S, hd):
-            return flash_attention(q, k, v, causal=True)
+    if use_kernels(q) and hd in (64, 128):
+        from .flash import flash_attention
+        return flash_attention(q, k, v, causal=True)
     o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
     return o.transpose(1, 2)
 

@@ -113,6 +113,20 @@ def cross_entropy_into(logits, target, loss, *, grad_scale=1.0, ignore_index=-10
     return loss
 
 
+def cross_entropy_to(logits, target, grad=None, *, grad_scale=1.0, ignore_index=-100):
+    """Per-row loss (fp32 [M]) of bf16 ``logits`` [M, V], which are NOT modified; when ``grad`` (bf16 [M, V]) is given it
+    receives ``grad_scale * (softmax - onehot)``."""
+    M, V = logits.shape
+    loss = torch.empty(M, dtype=torch.float32, device=logits.device)
+    L = _L()
+    L.rtp_cross_entropy_to.argtypes = [C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float,
+                                       C.c_longlong, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p]
+    _check(L.rtp_cross_entropy_to(_p(logits), logits.stride(0), _p(target), _p(loss), M, V, float(grad_scale),
+                                  int(ignore_index), int(grad is not None), _p(grad),
+                                  grad.stride(0) if grad is not None else 0, _lib.stream_ptr()), "cross_entropy")
+    return loss
+
+
 def embed_fwd(table, ids, out, col_off, *, D, scale=1.0, pe=None, tokens_per_pos=1, drop_p=0.0, seed=0, offset=0,
               step=None):
     T = ids.numel()
@@ -251,6 +265,21 @@ def sum_f32(src, out, scale=1.0):
     return out
 
 
+def adam_state_dtypes(state_dtype):
+    """(dtype of exp_avg, dtype of exp_avg_sq) for a state policy: ``"fp32"`` / ``torch.float32`` (default of the
+    optimizers), ``"mixed"`` (first moment bf16, second moment fp32) or ``"bf16"`` / ``torch.bfloat16``.
+
+    A bf16 second moment cannot follow beta2 = 0.999: its 0.1 % decay per step is below half a bf16 ulp (0.2-0.4 %),
+    so the stored value rounds back and never shrinks.  The first moment decays by 10 % per step and is safe in bf16."""
+    if state_dtype in (None, "fp32", torch.float32):
+        return torch.float32, torch.float32
+    if state_dtype == "mixed":
+        return torch.bfloat16, torch.float32
+    if state_dtype in ("bf16", torch.bfloat16):
+        return torch.bfloat16, torch.bfloat16
+    raise ValueError(f"unknown Adam state dtype {state_dtype!r}")
+
+
 class AdamPlan:
     """Device-resident descriptor table for the multi-tensor Adam kernel (built once, reused every step)."""
 
@@ -264,7 +293,16 @@ class AdamPlan:
         self.keep = entries
         for k, (p, g, m, v, lr_mult) in enumerate(entries):
             arr[k].p, arr[k].g, arr[k].m, arr[k].v = p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr()
-            arr[k].n, arr[k].lr_mult, arr[k].state_fp32 = p.numel(), float(lr_mult), int(m.dtype == torch.float32)
+            # kernel codes: 0 = both moments bf16, 1 = both fp32, 2 = first moment bf16 + second moment fp32
+            if m.dtype == torch.float32 and v.dtype == torch.float32:
+                code = 1
+            elif m.dtype == torch.bfloat16 and v.dtype == torch.float32:
+                code = 2
+            elif m.dtype == torch.bfloat16 and v.dtype == torch.bfloat16:
+                code = 0
+            else:
+                raise ValueError(f"unsupported Adam state dtypes {m.dtype} / {v.dtype}")
+            arr[k].n, arr[k].lr_mult, arr[k].state_fp32 = p.numel(), float(lr_mult), code
             starts.append(total)
             total += (p.numel() + self.BLOCK_ELEMS - 1) // self.BLOCK_ELEMS
         raw = bytes(arr)

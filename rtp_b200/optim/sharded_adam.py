@@ -52,8 +52,12 @@ def clip_grad_value_(params: Iterable[torch.Tensor], clip_value: float):
 
 class ShardedAdam(torch.optim.Optimizer):
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, adamw=False,
-                 clip_value: Optional[float] = None, group=None, state_dtype: Optional[torch.dtype] = None,
+                 clip_value: Optional[float] = None, group=None, state_dtype=None,
                  sync_replicated: bool = True):
+        """``state_dtype``: dtype policy of the moments of bf16 / fp16 parameters: ``None`` / ``"fp32"`` (default),
+        ``"mixed"`` (first moment bf16, second moment fp32) or ``"bf16"`` (both bf16, the layout ``torch.optim.Adam``
+        gives bf16 parameters; its second moment cannot decay, see ``ops.kernels.adam_state_dtypes``).  Moments of
+        fp32 / fp64 parameters always have the parameter's dtype."""
         if isinstance(params, nn.Module):
             params = params.parameters()
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
@@ -81,9 +85,13 @@ class ShardedAdam(torch.optim.Optimizer):
     def _init_state(self, p):
         st = self.state[p]
         if not st:
-            dt = self.state_dtype or (torch.float32 if p.dtype != torch.float32 and False else p.dtype)
-            st["exp_avg"] = torch.zeros_like(p, dtype=dt, memory_format=torch.preserve_format)
-            st["exp_avg_sq"] = torch.zeros_like(p, dtype=dt, memory_format=torch.preserve_format)
+            if p.dtype in (torch.bfloat16, torch.float16):
+                from ..ops.kernels import adam_state_dtypes
+                dt_m, dt_v = adam_state_dtypes(self.state_dtype)
+            else:
+                dt_m = dt_v = p.dtype
+            st["exp_avg"] = torch.zeros_like(p, dtype=dt_m, memory_format=torch.preserve_format)
+            st["exp_avg_sq"] = torch.zeros_like(p, dtype=dt_v, memory_format=torch.preserve_format)
         return st
 
     @torch.no_grad()
@@ -124,11 +132,12 @@ class ShardedAdam(torch.optim.Optimizer):
                     else:
                         grad = grad.add(p, alpha=wd)
                 m, v = st["exp_avg"], st["exp_avg_sq"]
-                gf = grad.to(m.dtype)
-                m.mul_(b1).add_(gf, alpha=1 - b1)
-                v.mul_(b2).addcmul_(gf, gf, value=1 - b2)
+                m.mul_(b1).add_(grad.to(m.dtype), alpha=1 - b1)
+                gv = grad.to(v.dtype)
+                v.mul_(b2).addcmul_(gv, gv, value=1 - b2)
                 denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)
-                p.addcdiv_(m.to(p.dtype), denom.to(p.dtype), value=-(lr * mult) / bc1)
+                upd = (m.to(denom.dtype) / denom).to(p.dtype)
+                p.add_(upd, alpha=-(lr * mult) / bc1)
 
     def _step_fused(self, params):
         from ..ops import kernels as K

@@ -1,11 +1,15 @@
 """Fused rotation engine: peer-mapped workspace + launch of the sm_100a rotation kernels.
 
-One engine exists per (process, ring).  It owns a ``cudaMalloc``'d workspace — flag block, two weight
-slots and two travelling-gradient slots — whose CUDA-IPC handle is exchanged once over the ring's
-process group; afterwards every kernel launch only passes raw pointers.  The kernels themselves push
-weight shards from their owner's home buffer into the consumer's slot with NVLink P2P stores and
-synchronise through monotonically increasing counters (see csrc/gemm_kernel.cuh), so there is no NCCL
-send/recv, no copy kernel and no host involvement between rotation steps.
+One engine exists per (process, ring).  It owns a ``cudaMalloc``'d workspace — a flag block, two banks of N-1 weight
+slots (one slot per visiting shard; the second bank receives the next launch's shards while the current launch computes)
+and N gradient slots (one per contributing rank) — whose CUDA-IPC handle is exchanged once over the ring's process
+group; afterwards every kernel launch only passes raw pointers.  The kernels themselves push weight shards from their
+owner's home buffer into the consumer's slot with NVLink P2P stores, store weight-gradient tiles straight into the
+owner's gradient slots and synchronise through monotonically increasing counters (see csrc/gemm_kernel.cuh), so there
+is no NCCL send/recv, no copy kernel and no host involvement between rotation steps.
+
+The memory-lean in-place mode (``inplace=True`` layers) uses none of these slots: the layer's single flat buffer itself
+travels, one hop per rotation step, through a small staging area (``csrc/ring_shift.cu``).
 """
 import ctypes as C
 from typing import Dict, Optional
@@ -42,6 +46,8 @@ class FusedEngine:
         self.ws_local = None
         self.mapped = {}
         self._host_status = C.c_ulonglong(0)
+        self._staging = None            # (local, {rank: mapped}) of the in-place ring shift, created on first use
+        self.shift_lanes = 32
         self._allocate(slot_bytes)
 
     def _allocate(self, slot_bytes: int):
@@ -92,6 +98,50 @@ class FusedEngine:
         L.rtp_ws_destroy(self.ws_local)
         self._allocate(slot_bytes)
 
+    # -- in-place ring shift ----------------------------------------------------------------------
+    def _ensure_staging(self):
+        """Create this rank's staging area and map the neighbours' (collective over the ring, first use only)."""
+        if self._staging is not None:
+            return self._staging
+        L = _lib.lib()
+        ctx = self.ctx
+        mine = C.c_void_p()
+        if L.rtp_shift_staging_create(self.shift_lanes, C.byref(mine)) != 0:
+            raise RuntimeError("staging: " + L.rtp_shift_last_error().decode())
+        ptrs = {ctx.rank: mine.value}
+        handle = (C.c_char * 64)()
+        _lib.check(L.rtp_ws_ipc_get(mine.value, handle), "rtp_ws_ipc_get")
+        gathered = [None] * ctx.world
+        dist.all_gather_object(gathered, bytes(handle), group=ctx.group)
+        for r in {ctx.up, ctx.down} - {ctx.rank}:
+            out = C.c_void_p()
+            buf = C.create_string_buffer(gathered[r], 64)
+            _lib.check(L.rtp_ws_ipc_open(buf, C.byref(out)), "rtp_ws_ipc_open")
+            ptrs[r] = out.value
+        dist.barrier(group=ctx.group)
+        self._staging = ptrs
+        return ptrs
+
+    def staging_bytes(self) -> int:
+        return int(_lib.lib().rtp_shift_staging_bytes(self.shift_lanes)) if self._staging is not None else 0
+
+    def shift_inplace(self, buf: torch.Tensor, direction: str):
+        """Replace ``buf`` (the same number of bytes on every rank) by the ring neighbour's buffer: ``down`` sends to rank
+        r-1 and receives from r+1 (forward rotation), ``up`` the reverse.  Only a small staging area is used."""
+        ctx = self.ctx
+        if ctx.world == 1:
+            return
+        ptrs = self._ensure_staging()
+        dst, src = (ctx.down, ctx.up) if direction == "down" else (ctx.up, ctx.down)
+        nbytes = buf.numel() * buf.element_size()
+        one = C.c_void_p * 1
+        status = _lib.status_word(buf.device)
+        rc = _lib.lib().rtp_ring_shift(1, one(buf.data_ptr()), nbytes, one(ptrs[ctx.rank]), one(ptrs[dst]), one(ptrs[src]),
+                                       0 if direction == "down" else 1, self.shift_lanes, one(status.data_ptr()),
+                                       self.timeout_ns, _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError("rtp_ring_shift: " + _lib.lib().rtp_shift_last_error().decode())
+
     def check(self):
         """Read the workspace status word (synchronises the stream); raise if a bounded wait expired."""
         _lib.check(_lib.lib().rtp_ws_status(self.ws_local, C.byref(self._host_status), _lib.stream_ptr()),
@@ -122,6 +172,7 @@ def workspace_bytes() -> int:
     total = 0
     for e in _engines.values():
         total += int(L.rtp_ws_bytes_world(e.slot_bytes if e.ctx.world > 1 else 256, e.ctx.world))
+        total += e.staging_bytes()
     return total
 
 
@@ -195,87 +246,243 @@ def linear_bwd_raw(eng, flat, layout_info, x2d, dy2d, row, in_f, out_f, need_dx=
     return dx, gflat
 
 
-class _FusedLinearFn(torch.autograd.Function):
+class LinSpec:
+    """One rotated linear inside a flat shard buffer: where weight and bias live, the full layer's sizes, and the
+    placement (offset, numel, shape) of the registered parameters whose gradients the backward returns.  ``owner`` is
+    the rotated module (it carries the ``_displaced`` flag of the in-place mode)."""
+
+    __slots__ = ("ring", "flat", "has_bias", "bias_off", "shard_bytes", "row", "in_f", "out_f", "places", "owner",
+                 "inplace")
+
+    def __init__(self, ring, flat, has_bias, bias_off, row, in_f, out_f, places, owner=None, inplace=False):
+        self.ring, self.flat, self.has_bias, self.bias_off = ring, flat, has_bias, bias_off
+        self.shard_bytes = _round_up(flat.numel() * 2, 16)
+        self.row, self.in_f, self.out_f, self.places, self.owner, self.inplace = row, in_f, out_f, places, owner, inplace
+
+    @property
+    def info(self):
+        return (self.has_bias, self.bias_off, self.shard_bytes)
+
+    @property
+    def shard_dims(self):
+        """(rows, columns) of one weight shard."""
+        N = self.ring.world
+        return (self.out_f, self.in_f // N) if self.row else (self.out_f // N, self.in_f)
+
+
+def fused_linear_ok(row: bool, in_f: int, out_f: int, world: int) -> bool:
+    """Every operand of the forward and backward programs must be a legal TMA operand: 16-byte aligned bases, row
+    pitches and tile x-offsets, i.e. the full and the per-shard feature counts must be multiples of 8."""
+    if in_f % 8 or out_f % 8:
+        return False
+    return (in_f // world) % 8 == 0 if row else (out_f // world) % 8 == 0
+
+
+def _as_2d(x):
+    x2d = x.reshape(-1, x.shape[-1])
+    if x2d.stride(1) != 1 or (x2d.stride(0) * 2) % 16 or x2d.data_ptr() % 16:
+        x2d = x2d.contiguous()
+    return x2d
+
+
+def _inplace_linear_fwd(eng, spec, x2d, needs_bwd):
+    """Memory-lean forward: the flat buffer itself visits every rank (one in-place hop per step); each step is a plain
+    GEMM of the local activations with whichever shard is here (reference: rtp/inplace/module/linear.py:210-229)."""
+    from ..ops.gemm import gemm
+    ctx = spec.ring
+    N, r = ctx.world, ctx.rank
+    Os, Ks = spec.shard_dims
+    flat = spec.flat
+    w = flat[:Os * Ks].view(Os, Ks)
+    b = flat[spec.bias_off:spec.bias_off + Os] if spec.has_bias else None
+    y = torch.empty(x2d.shape[0], spec.out_f, dtype=torch.bfloat16, device=x2d.device)
+    for i in range(N):
+        j = (r + i) % N
+        if spec.row:
+            gemm(x2d[:, j * Ks:(j + 1) * Ks], w, bias=b, c=y if i > 0 else None, out=y)
+        else:
+            gemm(x2d, w, bias=b, out=y[:, j * Os:(j + 1) * Os])
+        if i < N - 1:
+            eng.shift_inplace(flat, "down")
+    if N > 1:
+        if needs_bwd:
+            if spec.owner is not None:
+                spec.owner._displaced = True     # backward's N-1 reverse hops bring the shards home
+        else:
+            eng.shift_inplace(flat, "down")      # N-th hop: every shard is home again
+    return y
+
+
+def _inplace_linear_bwd(eng, spec, x2d, dy2d, need_dx):
+    """Backward of the in-place mode: weights hop back ("up") and the travelling gradient buffer hops with them,
+    picking up this rank's contribution at every stop (reference: rtp/inplace/module/collectives.py:75-105)."""
+    from ..ops.gemm import gemm
+    ctx = spec.ring
+    N, r = ctx.world, ctx.rank
+    Os, Ks = spec.shard_dims
+    flat = spec.flat
+    w = flat[:Os * Ks].view(Os, Ks)
+    g = torch.zeros_like(flat)
+    gw = g[:Os * Ks].view(Os, Ks)
+    gb = g[spec.bias_off:spec.bias_off + Os] if spec.has_bias else None
+    M = x2d.shape[0]
+    dx = torch.empty(M, spec.in_f, dtype=torch.bfloat16, device=x2d.device) if need_dx else None
+    for s in range(N):
+        j = (r + N - 1 - s) % N
+        if spec.row:
+            dy_j, x_j = dy2d, x2d[:, j * Ks:(j + 1) * Ks]
+        else:
+            dy_j, x_j = dy2d[:, j * Os:(j + 1) * Os], x2d
+        if need_dx:
+            if spec.row:
+                gemm(dy_j, w, b_mn=True, out=dx[:, j * Ks:(j + 1) * Ks])
+            else:
+                gemm(dy_j, w, b_mn=True, c=dx if s > 0 else None, out=dx)
+        gemm(dy_j, x_j, a_mn=True, b_mn=True, c=gw, out=gw)
+        if gb is not None:
+            gb.add_(K.colsum(dy_j).to(gb.dtype))
+        if s < N - 1:
+            eng.shift_inplace(flat, "up")
+            eng.shift_inplace(g, "up")
+    if spec.owner is not None:
+        spec.owner._displaced = False
+    return dx, g
+
+
+class _FusedSubLinearFn(torch.autograd.Function):
+    """Rotated linear described by a :class:`LinSpec` (a whole module's shard or a sub-range of it)."""
+
     @staticmethod
-    def forward(ctx, module, row, x, *params):
-        eng = get_engine(module.ring)
-        x2d = x.reshape(-1, x.shape[-1])
-        if x2d.stride(1) != 1 or (x2d.stride(0) * 2) % 16:
-            x2d = x2d.contiguous()
-        info = _linear_desc(module, row)
-        y = linear_fwd_raw(eng, module._full_param, info, x2d, row, module.in_features, module.out_features)
-        ctx.module, ctx.row, ctx.info, ctx.eng = module, row, info, eng
+    def forward(ctx, spec, x, *params):
+        eng = get_engine(spec.ring)
+        x2d = _as_2d(x)
+        needs_bwd = torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in params))
+        if spec.inplace and spec.ring.world > 1:
+            if spec.owner is not None and getattr(spec.owner, "_displaced", False):
+                raise RuntimeError("in-place rotated layer called while its shards are displaced: the backward of the "
+                                   "previous grad-mode forward has not run yet")
+            y = _inplace_linear_fwd(eng, spec, x2d, needs_bwd)
+        else:
+            y = linear_fwd_raw(eng, spec.flat, spec.info, x2d, spec.row, spec.in_f, spec.out_f)
+        ctx.spec, ctx.eng = spec, eng
         ctx.save_for_backward(x2d)
         ctx.x_shape = x.shape
-        return y.view(*x.shape[:-1], module.out_features)
+        return y.view(*x.shape[:-1], spec.out_f)
 
     @staticmethod
     def backward(ctx, dy):
-        module = ctx.module
+        spec = ctx.spec
         (x2d,) = ctx.saved_tensors
-        dy2d = dy.reshape(-1, dy.shape[-1])
-        if not dy2d.is_contiguous():
-            dy2d = dy2d.contiguous()
-        dx, gflat = linear_bwd_raw(ctx.eng, module._full_param, ctx.info, x2d, dy2d, ctx.row, module.in_features,
-                                   module.out_features, need_dx=ctx.needs_input_grad[2])
-        module._last_flat_grad = gflat
-        views = module._layout.views(gflat)
-        return (None, None, dx.view(ctx.x_shape) if dx is not None else None, *views)
+        dy2d = _as_2d(dy)
+        if spec.inplace and spec.ring.world > 1:
+            dx, gflat = _inplace_linear_bwd(ctx.eng, spec, x2d, dy2d, ctx.needs_input_grad[1])
+        else:
+            dx, gflat = linear_bwd_raw(ctx.eng, spec.flat, spec.info, x2d, dy2d, spec.row, spec.in_f, spec.out_f,
+                                       need_dx=ctx.needs_input_grad[1])
+        if spec.owner is not None:
+            spec.owner._last_flat_grad = gflat
+        grads = [gflat[off:off + n].view(shape) for off, n, shape in spec.places]
+        return (None, dx.view(ctx.x_shape) if dx is not None else None, *grads)
 
 
-class _FusedConvFn(torch.autograd.Function):
-    """Rotated Conv2d on the rotation GEMM kernels: a column-parallel linear over the patch matrix of the input
-    (reference: rtp/module/conv.py:103-114; the flat shard [Cout/N, Cin*kh*kw] + bias is a linear shard as it is)."""
-
-    @staticmethod
-    def forward(ctx, module, x, *params):
-        eng = get_engine(module.ring)
-        conv = module.conv
-        x = x.contiguous()
-        K_ = conv.in_channels * conv.kernel_size[0] * conv.kernel_size[1]
-        cols = K.im2col(x, conv.kernel_size, conv.stride, conv.padding, conv.dilation)
-        lay = module._layout
-        has_bias = conv.bias is not None
-        info = (has_bias, lay.offset_of("bias") if has_bias else -1, _round_up(lay.numel * 2, 16))
-        y2d = linear_fwd_raw(eng, module._full_param, info, cols, False, K_, module.out_channels)
-        OH, OW = K.conv_out_size(x.shape[2], x.shape[3], conv.kernel_size, conv.stride, conv.padding, conv.dilation)
-        ctx.module, ctx.info, ctx.eng, ctx.K_ = module, info, eng, K_
-        ctx.x_shape = x.shape
-        ctx.save_for_backward(cols)
-        return y2d.view(x.shape[0], OH, OW, module.out_channels).permute(0, 3, 1, 2)
-
-    @staticmethod
-    def backward(ctx, dy):
-        module, conv = ctx.module, ctx.module.conv
-        (cols,) = ctx.saved_tensors
-        dy2d = dy.permute(0, 2, 3, 1).reshape(-1, module.out_channels)
-        if not dy2d.is_contiguous():
-            dy2d = dy2d.contiguous()
-        dcols, gflat = linear_bwd_raw(ctx.eng, module._full_param, ctx.info, cols, dy2d, False, ctx.K_,
-                                      module.out_channels, need_dx=ctx.needs_input_grad[1])
-        module._last_flat_grad = gflat
-        dx = None
-        if dcols is not None:
-            dx = K.col2im(dcols, ctx.x_shape, conv.kernel_size, conv.stride, conv.padding, conv.dilation)
-        return (None, dx, *module._layout.views(gflat))
-
-
-def fused_conv_ok(module, x) -> bool:
-    """The patch matrix must be a legal TMA operand (row pitch a multiple of 16 bytes) and the convolution plain."""
-    conv = module.conv
-    K_ = conv.in_channels * conv.kernel_size[0] * conv.kernel_size[1]
-    return (K_ % 8 == 0 and conv.groups == 1 and conv.padding_mode == "zeros" and not isinstance(conv.padding, str)
-            and x.dim() == 4)
-
-
-def fused_conv(module, x):
-    return _FusedConvFn.apply(module, x, *module.shard_parameters())
+def linear_spec(owner, row, in_f, out_f, weight, bias):
+    """LinSpec of a rotated module whose flat shard is exactly [weight, bias]."""
+    lay = owner._layout
+    names = lay.names
+    places = [(lay.offset_of(names[0]), weight.numel(), weight.shape)]
+    has_bias = bias is not None
+    if has_bias:
+        places.append((lay.offset_of(names[1]), bias.numel(), bias.shape))
+    return LinSpec(owner.ring, owner._full_param, has_bias, lay.offset_of(names[1]) if has_bias else -1, row, in_f, out_f,
+                   places, owner=owner, inplace=bool(getattr(owner, "inplace", False)))
 
 
 def fused_linear(module, x, row=False):
-    return _FusedLinearFn.apply(module, row, x, *module.shard_parameters())
+    lin = module.linear
+    spec = linear_spec(module, row, module.in_features, module.out_features, lin.weight, lin.bias)
+    params = [p for p in (lin.weight, lin.bias) if p is not None]
+    return _FusedSubLinearFn.apply(spec, x, *params)
 
 
+# --------------------------------------------------------------------------------------------------
+# rotated Conv2d: a column-parallel linear over the patch matrix
+# --------------------------------------------------------------------------------------------------
+class _FusedConvFn(torch.autograd.Function):
+    """Rotated Conv2d on the rotation GEMM kernels (reference: rtp/module/conv.py:103-114; the flat shard
+    [Cout/N, Cin*kh*kw] + bias is a linear shard as it is).  When the patch length is not a multiple of 8 (a TMA row
+    pitch must be a multiple of 16 bytes) the patch matrix and a shadow copy of the weight shard are zero-padded to the
+    next multiple of 8; the shadow is what rotates, and the gradient is cut back to the real columns."""
+
+    @staticmethod
+    def forward(ctx, owner, conv, x, *params):
+        eng = get_engine(owner.ring)
+        x = x.contiguous()
+        N = owner.ring.world
+        K_ = conv.in_channels * conv.kernel_size[0] * conv.kernel_size[1]
+        Kp = _round_up(K_, 8)
+        Os = conv.out_channels                      # the shard module holds Cout / N channels
+        cols = K.im2col(x, conv.kernel_size, conv.stride, conv.padding, conv.dilation, Kp=Kp)
+        has_bias = conv.bias is not None
+        if Kp == K_:
+            lay = owner._layout
+            flat = owner._full_param
+            bias_off = lay.offset_of(lay.names[1]) if has_bias else -1
+        else:
+            bias_off = _round_up(Os * Kp, 64)
+            flat = torch.zeros(bias_off + (_round_up(Os, 64) if has_bias else 0), dtype=torch.bfloat16, device=x.device)
+            flat[:Os * Kp].view(Os, Kp)[:, :K_].copy_(conv.weight.detach().reshape(Os, K_))
+            if has_bias:
+                flat[bias_off:bias_off + Os].copy_(conv.bias.detach())
+            else:
+                bias_off = -1
+            reserve_shard_bytes(flat.numel() * 2)
+            eng = get_engine(owner.ring)
+        places = [(0, Os * Kp, (Os, Kp))] + ([(bias_off, Os, (Os,))] if has_bias else [])
+        spec = LinSpec(owner.ring, flat, has_bias, bias_off, False, Kp, Os * N, places)
+        y2d = linear_fwd_raw(eng, flat, spec.info, cols, False, Kp, Os * N)
+        OH, OW = K.conv_out_size(x.shape[2], x.shape[3], conv.kernel_size, conv.stride, conv.padding, conv.dilation)
+        ctx.owner, ctx.conv, ctx.spec, ctx.eng, ctx.K_, ctx.Kp = owner, conv, spec, eng, K_, Kp
+        ctx.x_shape = x.shape
+        ctx.save_for_backward(cols)
+        return y2d.view(x.shape[0], OH, OW, Os * N).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        owner, conv, spec = ctx.owner, ctx.conv, ctx.spec
+        (cols,) = ctx.saved_tensors
+        Cout = spec.out_f
+        dy2d = dy.permute(0, 2, 3, 1).reshape(-1, Cout)
+        if not dy2d.is_contiguous():
+            dy2d = dy2d.contiguous()
+        dcols, gflat = linear_bwd_raw(ctx.eng, spec.flat, spec.info, cols, dy2d, False, ctx.Kp, Cout,
+                                      need_dx=ctx.needs_input_grad[2])
+        dx = None
+        if dcols is not None:
+            dx = K.col2im(dcols, ctx.x_shape, conv.kernel_size, conv.stride, conv.padding, conv.dilation)
+        Os = Cout // owner.ring.world
+        gw = gflat[:Os * ctx.Kp].view(Os, ctx.Kp)[:, :ctx.K_].reshape(conv.weight.shape)
+        grads = [gw]
+        if spec.has_bias:
+            grads.append(gflat[spec.bias_off:spec.bias_off + Os])
+        if ctx.Kp == ctx.K_:
+            owner._last_flat_grad = gflat
+        return (None, None, dx, *grads)
+
+
+def fused_conv_ok(conv, x) -> bool:
+    """Plain convolutions (groups 1, zero padding, numeric padding) whose shard has a multiple of 8 output channels."""
+    return (conv.groups == 1 and conv.padding_mode == "zeros" and not isinstance(conv.padding, str) and x.dim() == 4
+            and conv.out_channels % 8 == 0)
+
+
+def fused_conv(owner, conv, x):
+    params = [p for p in (conv.weight, conv.bias) if p is not None]
+    return _FusedConvFn.apply(owner, conv, x, *params)
+
+
+# --------------------------------------------------------------------------------------------------
+# rotated embedding
+# --------------------------------------------------------------------------------------------------
 def embed_fwd_rot(eng, flat, V, Ds, ids, out, D, scale, pe, tokens_per_pos, drop_p, seed, offset, step):
     """Rotated embedding lookup (+ scale, positional encoding, dropout) in one launch of the rotation kernel."""
     op = _lib.EmbedFwd()
@@ -321,84 +528,27 @@ def embed_bwd_rot(eng, trainer, st, dx0):
     reduce_scatter_cols(eng, dense, trainer.emb._layout.views(trainer.emb_gflat)[0])
 
 
-# --------------------------------------------------------------------------------------------------
-# generic autograd pieces for the module path
-# --------------------------------------------------------------------------------------------------
-class _FusedSubLinearFn(torch.autograd.Function):
-    """Rotated linear on a (sub-)range of a module's flat shard: ``spec`` = (ring, flat, info, row, in_f, out_f,
-    [(offset, numel, shape), ...]) lists where the given parameters live inside ``flat``."""
-
-    @staticmethod
-    def forward(ctx, spec, x, *params):
-        ring, flat, info, row, in_f, out_f, places = spec
-        eng = get_engine(ring)
-        x2d = x.reshape(-1, x.shape[-1])
-        if x2d.stride(1) != 1 or (x2d.stride(0) * 2) % 16 or x2d.data_ptr() % 16:
-            x2d = x2d.contiguous()
-        y = linear_fwd_raw(eng, flat, info, x2d, row, in_f, out_f)
-        ctx.spec, ctx.eng = spec, eng
-        ctx.save_for_backward(x2d)
-        ctx.x_shape = x.shape
-        return y.view(*x.shape[:-1], out_f)
-
-    @staticmethod
-    def backward(ctx, dy):
-        ring, flat, info, row, in_f, out_f, places = ctx.spec
-        (x2d,) = ctx.saved_tensors
-        dy2d = dy.reshape(-1, dy.shape[-1])
-        if not dy2d.is_contiguous():
-            dy2d = dy2d.contiguous()
-        dx, gflat = linear_bwd_raw(ctx.eng, flat, info, x2d, dy2d, row, in_f, out_f, need_dx=ctx.needs_input_grad[1])
-        grads = [gflat[off:off + n].view(shape) for off, n, shape in places]
-        return (None, dx.view(ctx.x_shape) if dx is not None else None, *grads)
-
-
-def fused_mha(module, x, causal: bool):
-    """Self-attention of a ``ParallelMultiheadAttention`` on the fused kernels: column-rotated packed QKV projection,
-    local attention over all heads, row-rotated output projection.  ``x``: [L, B, E] (or [B, L, E] when batch_first)."""
-    from ..ops import functional as FO
-    from ..ops.flash import flash_attention, flash_attention_available
-    from ..ops import kernels as KK
-    sub = module.MultiheadAttention
-    lay, flat = module._layout, module._full_param
-    N, E, H = module.world_size, module.embed_dim, module.num_heads
-    hd = E // H
-    o_inw, o_inb = lay.offset_of("in_proj_weight"), lay.offset_of("in_proj_bias")
-    o_ow, o_ob = lay.offset_of("out_proj.weight"), lay.offset_of("out_proj.bias")
-    qkv_flat, out_flat = flat[o_inw:o_ow], flat[o_ow:]
-    spec_qkv = (module.ring, qkv_flat, (True, o_inb - o_inw, _round_up(qkv_flat.numel() * 2, 16)), False, E, 3 * E,
-                [(0, sub.in_proj_weight.numel(), sub.in_proj_weight.shape),
-                 (o_inb - o_inw, sub.in_proj_bias.numel(), sub.in_proj_bias.shape)])
-    spec_out = (module.ring, out_flat, (True, o_ob - o_ow, _round_up(out_flat.numel() * 2, 16)), True, E, E,
-                [(0, sub.out_proj.weight.numel(), sub.out_proj.weight.shape),
-                 (o_ob - o_ow, sub.out_proj.bias.numel(), sub.out_proj.bias.shape)])
-    bf = module.batch_first
-    if bf:
-        B, L = x.shape[0], x.shape[1]
-    else:
-        L, B = x.shape[0], x.shape[1]
-    qkv = _FusedSubLinearFn.apply(spec_qkv, x, sub.in_proj_weight, sub.in_proj_bias)       # [.., 3E] grouped per shard
-    packed = qkv.reshape(*x.shape[:2], N, 3, H // N, hd)
-    q, k, v = [packed[:, :, :, i].reshape(*x.shape[:2], H, hd) for i in range(3)]
-    if not bf:
-        q, k, v = [t.transpose(0, 1) for t in (q, k, v)]                                    # [B, L, H, hd]
-    ctxv = FO.causal_attention(q, k, v)                                                       # [B, L, H, hd]
-    if not bf:
-        ctxv = ctxv.transpose(0, 1)
-    ctxv = ctxv.reshape(*x.shape[:2], E)
-    return _FusedSubLinearFn.apply(spec_out, ctxv, sub.out_proj.weight, sub.out_proj.bias)
-
-
 class _FusedEmbeddingFn(torch.autograd.Function):
+    """``owner``: rotated module whose flat shard is the [V, D/N] table."""
+
     @staticmethod
-    def forward(ctx, module, ids, weight):
-        eng = get_engine(module.ring)
+    def forward(ctx, owner, D, ids, weight):
+        eng = get_engine(owner.ring)
         V, Ds = weight.shape
-        D = module.embedding_dim
         flat_ids = ids.reshape(-1).contiguous()
         out = torch.empty(flat_ids.numel(), D, dtype=weight.dtype, device=weight.device)
-        embed_fwd_rot(eng, module._full_param, V, Ds, flat_ids, out, D, 1.0, None, 1, 0.0, 0, 0, None)
-        ctx.module, ctx.eng = module, eng
+        if getattr(owner, "inplace", False) and owner.ring.world > 1:
+            # memory-lean mode: the table shard itself travels; every stop gathers its column block
+            N, r = owner.ring.world, owner.ring.rank
+            flat = owner._full_param
+            for i in range(N):
+                j = (r + i) % N
+                K.embed_fwd(flat[:V * Ds].view(V, Ds), flat_ids, out, j * Ds, D=D, scale=1.0)
+                eng.shift_inplace(flat, "down")        # N hops in all: the shards end at home (tables need no weights
+                #                                        in backward, so nothing stays displaced)
+        else:
+            embed_fwd_rot(eng, owner._full_param, V, Ds, flat_ids, out, D, 1.0, None, 1, 0.0, 0, 0, None)
+        ctx.eng = eng
         ctx.save_for_backward(flat_ids)
         ctx.dims = (V, Ds, D)
         return out.view(*ids.shape, D)
@@ -412,11 +562,216 @@ class _FusedEmbeddingFn(torch.autograd.Function):
         K.embed_bwd(dense, flat_ids, dy2, 0, D=D, scale=1.0)
         g = torch.empty(V, Ds, dtype=dy2.dtype, device=dy2.device)
         reduce_scatter_cols(ctx.eng, dense, g)
-        return None, None, g
+        return None, None, None, g
 
 
-def fused_embedding(module, ids):
-    return _FusedEmbeddingFn.apply(module, ids, module.embedding.weight)
+def fused_embedding(owner, ids, weight=None, D=None):
+    weight = weight if weight is not None else owner.embedding.weight
+    D = D if D is not None else owner.embedding_dim
+    return _FusedEmbeddingFn.apply(owner, D, ids, weight)
+
+
+# --------------------------------------------------------------------------------------------------
+# rotated multi-head attention
+# --------------------------------------------------------------------------------------------------
+class _SmallAttnPackedFn(torch.autograd.Function):
+    """Short-sequence attention (S <= 96, head_dim 64) on the packed projection [S*B, 3*D], tokens ordered s*B + b."""
+
+    @staticmethod
+    def forward(ctx, qkv, S, B, H, nshard, causal, drop_p, seed, offset):
+        qkv = qkv.contiguous()
+        out = K.attn_small_fwd(qkv, S, B, H, nshard=nshard, causal=causal, drop_p=drop_p, seed=seed, offset=offset)
+        ctx.save_for_backward(qkv)
+        ctx.cfg = (S, B, H, nshard, causal, drop_p, seed, offset)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (qkv,) = ctx.saved_tensors
+        S, B, H, nshard, causal, drop_p, seed, offset = ctx.cfg
+        dqkv = K.attn_small_bwd(qkv, dout.contiguous(), S, B, H, nshard=nshard, causal=causal, drop_p=drop_p, seed=seed,
+                                offset=offset)
+        return (dqkv,) + (None,) * 8
+
+
+_causal_mask_cache = {}
+
+
+def _is_causal_mask(mask, L):
+    """True if ``mask`` is exactly the square subsequent mask (0 on and below the diagonal, -inf / True above).  The
+    comparison synchronises, so its result is cached per mask tensor."""
+    key = (mask.data_ptr(), tuple(mask.shape), mask.dtype, mask._version)
+    hit = _causal_mask_cache.get(key)
+    if hit is None:
+        if mask.dim() != 2 or tuple(mask.shape) != (L, L):
+            hit = False
+        else:
+            causal = torch.full((L, L), float("-inf"), device=mask.device, dtype=torch.float32).triu_(1)
+            hit = bool(torch.equal(mask, causal == float("-inf"))) if mask.dtype == torch.bool else \
+                bool(torch.equal(mask.float(), causal))
+        if len(_causal_mask_cache) > 64:
+            _causal_mask_cache.clear()
+        _causal_mask_cache[key] = hit
+    return hit
+
+
+def mha_fused_ok(owner, sub, query, key, value, key_padding_mask, need_weights, attn_mask, training) -> bool:
+    """Fused sm_100a path: batched self-attention on bf16 CUDA tensors with a packed in-projection and biases, head_dim
+    64 or 128, any 2-D additive / boolean mask, key-padding mask and probability dropout.  Attention weights can be
+    returned except under training dropout (the reference returns the dropped probabilities there)."""
+    from . import fused
+    if not ((key is value) and (query is key) and query.dim() == 3):
+        return False
+    if not (sub._qkv_same_embed_dim and sub.in_proj_bias is not None and sub.bias_k is None and not sub.add_zero_attn):
+        return False
+    if need_weights and training and sub.dropout > 0:
+        return False
+    if not fused.use_fused(query, owner._full_param):
+        return False
+    if sub.head_dim not in (64, 128):
+        return False
+    N = owner.ring.world
+    if not (fused_linear_ok(False, sub.embed_dim, 3 * sub.embed_dim, N) and fused_linear_ok(True, sub.embed_dim, sub.embed_dim, N)):
+        return False
+    if attn_mask is not None and attn_mask.dim() != 2:
+        return False
+    L = query.shape[1] if sub.batch_first else query.shape[0]
+    if training and sub.dropout > 0 and L % 4:
+        return False
+    return True
+
+
+def fused_mha(owner, sub, x, *, is_causal=False, attn_mask=None, key_padding_mask=None, need_weights=False,
+              average_attn_weights=True, training=False):
+    """Self-attention of a rotated MHA shard on the fused kernels: column-rotated packed QKV projection, local attention
+    over all heads (flash kernels, or the short-sequence kernels), row-rotated output projection.  ``owner`` is the
+    rotated module (flat shard [in_proj_weight, in_proj_bias, out_proj.weight, out_proj.bias]), ``sub`` the shard module.
+    ``x``: [L, B, E] (or [B, L, E] when ``batch_first``).  Returns (output, weights or None)."""
+    from ..ops.flash import flash_attention_packed, next_dropout_offset
+    lay, flat = owner._layout, owner._full_param
+    N, E, H = owner.ring.world, sub.embed_dim, sub.num_heads
+    hd = E // H
+    inplace = bool(getattr(owner, "inplace", False))
+    o_inw, o_inb = lay.offset_of("in_proj_weight"), lay.offset_of("in_proj_bias")
+    o_ow, o_ob = lay.offset_of("out_proj.weight"), lay.offset_of("out_proj.bias")
+    bf = sub.batch_first
+    B, L = (x.shape[0], x.shape[1]) if bf else (x.shape[1], x.shape[0])
+    if inplace and N > 1:
+        # the in-place mode moves the whole flat shard: both projections travel together, twice per direction
+        spec_qkv = LinSpec(owner.ring, flat, True, o_inb, False, E, 3 * E,
+                           [(o_inw, sub.in_proj_weight.numel(), sub.in_proj_weight.shape),
+                            (o_inb, sub.in_proj_bias.numel(), sub.in_proj_bias.shape)], owner=owner, inplace=True)
+        spec_out = None
+    else:
+        qkv_flat, out_flat = flat[o_inw:o_ow], flat[o_ow:]
+        spec_qkv = LinSpec(owner.ring, qkv_flat, True, o_inb - o_inw, False, E, 3 * E,
+                           [(0, sub.in_proj_weight.numel(), sub.in_proj_weight.shape),
+                            (o_inb - o_inw, sub.in_proj_bias.numel(), sub.in_proj_bias.shape)])
+        spec_out = LinSpec(owner.ring, out_flat, True, o_ob - o_ow, True, E, E,
+                           [(0, sub.out_proj.weight.numel(), sub.out_proj.weight.shape),
+                            (o_ob - o_ow, sub.out_proj.bias.numel(), sub.out_proj.bias.shape)])
+    if spec_out is None:
+        return _mha_inplace(owner, sub, x, is_causal, attn_mask, key_padding_mask, training), None
+    qkv = _FusedSubLinearFn.apply(spec_qkv, x, sub.in_proj_weight, sub.in_proj_bias)       # [.., 3E] grouped per shard
+    qkv2d = qkv.reshape(-1, 3 * E)
+    causal = bool(is_causal) and attn_mask is None
+    if attn_mask is not None and _is_causal_mask(attn_mask, L):
+        causal, attn_mask = True, None
+    p = float(sub.dropout) if training else 0.0
+    seed = torch.initial_seed() & 0x7FFFFFFFFFFFFFFF
+    offset = next_dropout_offset() if p > 0 else 0
+    if hd == 64 and L <= 96 and not bf and attn_mask is None and key_padding_mask is None:
+        ctxv = _SmallAttnPackedFn.apply(qkv2d, L, B, H, N, causal, p, seed, offset)
+    else:
+        ctxv = flash_attention_packed(qkv2d, B, L, H, nshard=N, seq_first=not bf, causal=causal, attn_mask=attn_mask,
+                                      key_padding_mask=key_padding_mask, dropout_p=p, seed=seed, offset=offset)
+    out = _FusedSubLinearFn.apply(spec_out, ctxv.view(*x.shape[:2], E), sub.out_proj.weight, sub.out_proj.bias)
+    weights = None
+    if need_weights:
+        weights = _last_shard_weights(qkv2d.detach(), B, L, H, hd, N, owner.ring.rank, bf, causal, attn_mask,
+                                      key_padding_mask, average_attn_weights)
+    return out, weights
+
+
+def _last_shard_weights(qkv2d, B, L, H, hd, N, rank, batch_first, causal, attn_mask, key_padding_mask, average):
+    """Attention probabilities of the heads of the shard that visits last, as the reference returns them
+    (rtp/module/attention.py:227-267): [B, L, S] averaged over those heads, or [B, H/N, L, S]."""
+    j = (rank + N - 1) % N
+    hps = H // N
+    E3 = 3 * hps * hd
+    blk = qkv2d[:, j * E3:(j + 1) * E3].float()
+    t = blk.view(B, L, 3, hps, hd) if batch_first else blk.view(L, B, 3, hps, hd).transpose(0, 1)
+    q, k = t[:, :, 0].permute(0, 2, 1, 3), t[:, :, 1].permute(0, 2, 1, 3)           # [B, hps, L, hd]
+    s = torch.matmul(q, k.transpose(-1, -2)) * hd ** -0.5
+    if causal:
+        s = s + torch.full((L, L), float("-inf"), device=s.device).triu_(1)
+    if attn_mask is not None:
+        s = s.masked_fill(attn_mask, float("-inf")) if attn_mask.dtype == torch.bool else s + attn_mask.float()
+    if key_padding_mask is not None:
+        s = s.masked_fill(key_padding_mask.bool()[:, None, None, :], float("-inf"))
+    w = torch.softmax(s, dim=-1)
+    return (w.mean(dim=1) if average else w).to(torch.bfloat16)
+
+
+class _LocalLinearFn(torch.autograd.Function):
+    """y = x w^T + b on the tcgen05 GEMM kernel, single GPU (the building block of the in-place mode, where the shard
+    that is currently here is an ordinary local weight)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        from ..ops.gemm import gemm
+        x2d = _as_2d(x)
+        w2 = w if (w.stride(1) == 1 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0) else w.contiguous()
+        y = gemm(x2d, w2, bias=b.contiguous() if b is not None else None)
+        ctx.save_for_backward(x2d, w2)
+        ctx.has_bias, ctx.x_shape = b is not None, x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.gemm import gemm
+        x2d, w2 = ctx.saved_tensors
+        dy2d = _as_2d(dy)
+        dx = gemm(dy2d, w2, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw = gemm(dy2d, x2d, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
+        db = K.colsum(dy2d).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return dx, dw, db
+
+
+def local_linear(x, w, b=None):
+    return _LocalLinearFn.apply(x, w, b)
+
+
+def _mha_inplace(owner, sub, x, is_causal, attn_mask, key_padding_mask, training):
+    """In-place mode of the rotated attention: the single flat shard (both projections) travels through the staging
+    ring; every stop computes the partial output of the visiting heads with the library's GEMM and attention kernels
+    (reference: rtp/inplace/module/attention.py:258-325)."""
+    from ..ops.flash import flash_attention_packed, next_dropout_offset
+    from .rotated import rotated_apply
+    N, E, H = owner.ring.world, sub.embed_dim, sub.num_heads
+    hps = H // N
+    bf = sub.batch_first
+    B, L = (x.shape[0], x.shape[1]) if bf else (x.shape[1], x.shape[0])
+    causal = bool(is_causal) and attn_mask is None
+    if attn_mask is not None and _is_causal_mask(attn_mask, L):
+        causal, attn_mask = True, None
+    p = float(sub.dropout) if training else 0.0
+    seed = torch.initial_seed() & 0x7FFFFFFFFFFFFFFF
+    base = next_dropout_offset() if p > 0 else 0
+    for _ in range(N - 1 if p > 0 else 0):
+        next_dropout_offset()                       # one offset per visiting shard
+    names = owner._layout.names
+
+    def fn(j, views, xin):
+        prm = dict(zip(names, views))
+        qkv = local_linear(xin, prm["in_proj_weight"], prm["in_proj_bias"])            # [.., 3E/N] = [q_j | k_j | v_j]
+        ctxv = flash_attention_packed(qkv.reshape(-1, 3 * E // N), B, L, hps, nshard=1, seq_first=not bf, causal=causal,
+                                      attn_mask=attn_mask, key_padding_mask=key_padding_mask, dropout_p=p, seed=seed,
+                                      offset=base + j)
+        return local_linear(ctxv.view(*xin.shape[:2], E // N), prm["out_proj.weight"], prm["out_proj.bias"])
+
+    return rotated_apply(owner.ring, fn, owner.shard_parameters(), owner._full_param, owner._layout, (x,), combine="sum",
+                         inplace=True, stochastic=False, owner=owner)
 
 
 # --------------------------------------------------------------------------------------------------

@@ -18,3 +18,10 @@ def use_fused(x: torch.Tensor, flat: torch.Tensor) -> bool:
 def linear(module, x, row=False):
     from .engine import fused_linear
     return fused_linear(module, x, row=row)
+
+
+def linear_ok(row, in_f, out_f, world):
+    """Shapes that the fused kernels cannot take (a feature count that is not a multiple of 8, e.g. a 10-class head)
+    run on the functional engine instead."""
+    from .engine import fused_linear_ok
+    return fused_linear_ok(row, in_f, out_f, world)

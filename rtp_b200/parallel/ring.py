@@ -40,6 +40,13 @@ def shift_inplace(ctx: RingContext, buf: torch.Tensor, direction: str, chunk_ele
     """
     if ctx.world == 1:
         return
+    if buf.is_cuda and buf.is_contiguous() and (buf.numel() * buf.element_size()) % 16 == 0 and buf.data_ptr() % 16 == 0:
+        from .context import get_backend
+        if get_backend() != "functional":
+            # sm_100a ring-shift kernel: NVLink P2P stores through a peer-mapped staging area, no NCCL on the path
+            from .engine import get_engine
+            get_engine(ctx).shift_inplace(buf, direction)
+            return
     flat = buf.view(-1)
     n = flat.numel()
     stage = torch.empty(min(chunk_elems, n), dtype=flat.dtype, device=flat.device)

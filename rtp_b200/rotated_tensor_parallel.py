@@ -69,7 +69,61 @@ class FlyweightWarpper(RotatedModule):
     def module_list(self):
         return [self.module] * self.world_size
 
+    def _forward_fused(self, args, kwargs):
+        """The wrapped shard on the fused sm_100a kernels (bf16 CUDA tensors, shapes the kernels can take); returns
+        NotImplemented when the functional engine has to run it."""
+        from .parallel import fused
+        mod, N = self.module, self.world_size
+        flat = self._full_param
+        if not flat.is_cuda:
+            return NotImplemented
+        from .parallel import engine as E
+        if isinstance(mod, nn.Linear):
+            if len(args) != 1 or kwargs or not isinstance(args[0], torch.Tensor) or not fused.use_fused(args[0], flat):
+                return NotImplemented
+            row = self.row_partition
+            in_f = mod.in_features * N if row else mod.in_features
+            out_f = mod.out_features if row else mod.out_features * N
+            if not E.fused_linear_ok(row, in_f, out_f, N):
+                return NotImplemented
+            spec = E.linear_spec(self, row, in_f, out_f, mod.weight, mod.bias)
+            params = [p for p in (mod.weight, mod.bias) if p is not None]
+            return E._FusedSubLinearFn.apply(spec, args[0], *params)
+        if isinstance(mod, nn.Embedding):
+            if len(args) != 1 or kwargs or not fused.use_fused(flat, flat):
+                return NotImplemented
+            if mod.padding_idx is not None or mod.max_norm is not None or mod.scale_grad_by_freq or mod.sparse \
+                    or mod.embedding_dim % 8:
+                return NotImplemented
+            return E.fused_embedding(self, args[0], mod.weight, mod.embedding_dim * N)
+        if isinstance(mod, nn.Conv2d):
+            if len(args) != 1 or kwargs or not isinstance(args[0], torch.Tensor) or not fused.use_fused(args[0], flat):
+                return NotImplemented
+            if (self.inplace and N > 1) or not E.fused_conv_ok(mod, args[0]):
+                return NotImplemented
+            return E.fused_conv(self, mod, args[0])
+        if isinstance(mod, ParallelMultiheadAttention):
+            if len(args) < 3:
+                return NotImplemented
+            query, key, value = args[:3]
+            names = ("key_padding_mask", "need_weights", "attn_mask", "average_attn_weights", "is_causal")
+            kw = dict(zip(names, args[3:]))
+            kw.update(kwargs)
+            if set(kw) - set(names):
+                return NotImplemented
+            need_w = kw.get("need_weights", True)
+            if not E.mha_fused_ok(self, mod, query, key, value, kw.get("key_padding_mask"), need_w, kw.get("attn_mask"),
+                                  self.training):
+                return NotImplemented
+            return E.fused_mha(self, mod, query, is_causal=kw.get("is_causal", False), attn_mask=kw.get("attn_mask"),
+                               key_padding_mask=kw.get("key_padding_mask"), need_weights=need_w,
+                               average_attn_weights=kw.get("average_attn_weights", True), training=self.training)
+        return NotImplemented
+
     def forward(self, *args, **kwargs):
+        out = self._forward_fused(args, kwargs)
+        if out is not NotImplemented:
+            return out
         names, mod = self._pnames, self.module
         tensors = [a for a in args if isinstance(a, torch.Tensor)]
         tpos = [i for i, a in enumerate(args) if isinstance(a, torch.Tensor)]

@@ -34,14 +34,44 @@ def test_fused_conv_eligibility():
     from rtp_b200.parallel.engine import fused_conv_ok
     x = torch.zeros(2, 32, 8, 8)
     ok = ColumnParallelConv2d(32, 64, 3, world_size=1, rank=0)
-    first = ColumnParallelConv2d(1, 32, 3, world_size=1, rank=0)       # patch length 9: not a legal TMA row pitch
+    first = ColumnParallelConv2d(1, 32, 3, world_size=1, rank=0)       # patch length 9: padded to 16 by the fused path
     grouped = ColumnParallelConv2d(32, 64, 3, groups=2, world_size=1, rank=0)
-    assert fused_conv_ok(ok, x)
-    assert not fused_conv_ok(first, torch.zeros(2, 1, 8, 8))
-    assert not fused_conv_ok(grouped, x)
+    odd = ColumnParallelConv2d(32, 12, 3, world_size=1, rank=0)        # 12 output channels: no legal TMA row pitch
+    assert fused_conv_ok(ok.conv, x)
+    assert fused_conv_ok(first.conv, torch.zeros(2, 1, 8, 8))
+    assert not fused_conv_ok(grouped.conv, x)
+    assert not fused_conv_ok(odd.conv, x)
     # on CPU the module keeps evaluating through the functional engine
     y = ok(x)
     assert y.shape == (2, 64, 6, 6)
+
+
+def test_fused_linear_eligibility():
+    from rtp_b200.parallel.engine import fused_linear_ok
+    assert fused_linear_ok(False, 2048, 2048, 8) and fused_linear_ok(True, 2048, 2048, 8)
+    assert not fused_linear_ok(False, 64, 10, 1)          # a 10-class head
+    assert not fused_linear_ok(False, 64, 32, 8)          # 4 output rows per shard
+    assert not fused_linear_ok(True, 36, 64, 1)
+    assert not fused_linear_ok(True, 64, 64, 16)          # 4 input columns per shard
+
+
+def test_adam_state_policy():
+    import pytest
+    from rtp_b200.ops.kernels import adam_state_dtypes
+    from rtp_b200.optim import ShardedAdam
+    assert adam_state_dtypes(None) == (torch.float32, torch.float32)
+    assert adam_state_dtypes("mixed") == (torch.bfloat16, torch.float32)
+    assert adam_state_dtypes("bf16") == (torch.bfloat16, torch.bfloat16)
+    with pytest.raises(ValueError):
+        adam_state_dtypes("fp8")
+    for policy, want in ((None, (torch.float32, torch.float32)), ("mixed", (torch.bfloat16, torch.float32))):
+        p = torch.nn.Parameter(torch.ones(16, dtype=torch.bfloat16))
+        p.grad = torch.full((16,), 0.5, dtype=torch.bfloat16)
+        opt = ShardedAdam([p], lr=1e-2, state_dtype=policy)
+        opt.step()
+        st = opt.state[p]
+        assert (st["exp_avg"].dtype, st["exp_avg_sq"].dtype) == want
+        assert torch.allclose(p.detach().float(), torch.full((16,), 0.99), atol=4e-3)
 
 
 def test_guard_bands_catch_an_overrun():

@@ -19,7 +19,7 @@ def _rings(world, slot_bytes, ctas, L, _lib):
     wss = []
     for _ in range(world):
         p = C.c_void_p()
-        _lib.check(L.rtp_ws_create(slot_bytes, C.byref(p)), "ws")
+        _lib.check(L.rtp_ws_create_world(slot_bytes, world, C.byref(p)), "ws")
         wss.append(p.value)
     rings = (_lib.Ring * world)()
     for r in range(world):

@@ -29,6 +29,8 @@ def test_noalloc_linear_backward_matches_regular_entry_point():
                    C.c_int, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p]
     fn.restype = C.c_int
     L.rtp_noalloc_last_error.restype = C.c_char_p
+    L.rtp_noalloc_status.argtypes = [C.c_void_p, C.POINTER(C.c_ulonglong)]
+    L.rtp_noalloc_status.restype = C.c_int
     torch.manual_seed(0)
     M, IN, OUT = 777, 512, 1024
     bias_off = OUT * IN
@@ -44,12 +46,21 @@ def test_noalloc_linear_backward_matches_regular_entry_point():
         # allocation-free entry point: outputs are allocated here, by the caller
         dx = torch.empty(M, IN, device="cuda", dtype=BF)
         g = torch.zeros(nflat, device="cuda", dtype=BF)
+        # free bytes as the driver sees them: a cudaMalloc inside the library would show here, whereas torch's own
+        # counters only see torch's caching allocator
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         before = torch.cuda.memory_allocated()
         rc = fn(x.data_ptr(), IN, dy.data_ptr(), OUT, flat.data_ptr(), bias_off, M, IN, OUT, dx.data_ptr(), IN,
                 g.data_ptr(), torch.cuda.current_stream().cuda_stream)
         assert rc == 0, L.rtp_noalloc_last_error()
+        status = C.c_ulonglong(99)
+        assert L.rtp_noalloc_status(torch.cuda.current_stream().cuda_stream, C.byref(status)) == 0
+        assert status.value == 0, status.value        # no bounded wait ran out inside the kernel
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        if trial == 1:     # the first call may still load the kernels' module lazily; the second must not take a byte
+            assert torch.cuda.mem_get_info()[0] == free_before
         assert _rel(dx, dx_ref) < 1e-3, (trial, _rel(dx, dx_ref))
         assert _rel(g[:bias_off], g_ref[:bias_off]) < 1e-3, (trial, _rel(g[:bias_off], g_ref[:bias_off]))
         assert _rel(g[bias_off:], g_ref[bias_off:]) < 1e-3, (trial, _rel(g[bias_off:], g_ref[bias_off:]))
