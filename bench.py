@@ -5,6 +5,8 @@ clip 0.05, Adam lr 1e-3) in bf16 on synthetic uniform token ids with random-init
 
     python bench.py --gpus N --steps K --warmup W            # this framework (fused sm_100a path)
     python bench.py --impl reference --gpus N ...            # the unmodified reference from baseline/_ref
+    python bench.py --impl reference --mode dp|fsdp|tp ...   # the reference's DP / FSDP / TP baselines (same loop)
+    python bench.py --path module ...                        # this framework through rotated modules + autograd
 
 For N > 1 launch one process per GPU (torchrun); RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* come from the
 environment.  Timing is on the device (CUDA events), bracketed by barrier + synchronize, max over ranks;
@@ -41,6 +43,8 @@ CONFIGS["moe"] = dict(family="moe", vocab=32000, ninp=2048, nhid=8192, nhead=16,
                       n_experts=8, capacity_factor=1.25, dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
 CONFIGS["moe-small"] = dict(family="moe", vocab=8192, ninp=512, nhid=1024, nhead=8, nlayers=2, seq_len=128, batch=4,
                             n_experts=8, capacity_factor=1.25, dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
+# the reference's gate has a fixed capacity of 2 * tokens / experts (factor 1.0): this variant lets both arms run
+CONFIGS["moe-cf1"] = dict(CONFIGS["moe"], capacity_factor=1.0)
 METRIC = "tokens/s/box"
 
 
@@ -53,6 +57,14 @@ def parse():
     ap.add_argument("--config", default="readme", choices=sorted(CONFIGS))
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--mode", default="rtp", choices=["rtp", "dp", "fsdp", "tp"],
+                    help="reference arm only: which of the reference's parallel strategies to run")
+    ap.add_argument("--path", default="trainer", choices=["trainer", "module"],
+                    help="README config of this framework: the fused trainer (default) or rotated modules + autograd "
+                         "with a torch-style loop and ShardedAdam")
+    ap.add_argument("--adam-state", default="fp32", choices=["fp32", "mixed", "bf16"],
+                    help="dtype policy of the Adam moments of this framework (the reference arm's torch.optim.Adam "
+                         "keeps bf16 moments for bf16 parameters)")
     return ap.parse_args()
 
 
@@ -154,11 +166,15 @@ def max_over_ranks(x, world):
     return t.item()
 
 
-def roofline(cfg, world, ms_per_step):
+ADAM_BYTES = {"fp32": 22.0, "mixed": 18.0, "bf16": 14.0}    # per parameter and step: bf16 p (r+w), bf16 g (r), m, v (r+w)
+
+
+def roofline(cfg, world, ms_per_step, adam_bytes=22.0):
     """Lower bound of one step of the dense LM on one rank and the fraction of it that was achieved: GEMM FLOPs at the
     measured cuBLAS bf16 rate, optimizer bytes at the measured copy bandwidth, and the bytes a rank must move over
-    NVLink (weight shards forward and backward, gradient shards) at the measured 770 GB/s peer-copy rate; the three
-    cannot all overlap perfectly with one another, so the bound is their maximum."""
+    NVLink (weight shards forward and backward, gradient shards) at 770 GB/s per direction, the peer-copy rate measured
+    on this pool (nominal 900 GB/s); compute and optimizer are serial, the link runs beside them, so the bound is
+    max(compute + optimizer, link)."""
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             pk = json.load(f)
@@ -170,7 +186,7 @@ def roofline(cfg, world, ms_per_step):
     layer_params = 4 * D * D + 2 * D * H
     params = L * layer_params + 2 * V * D
     flops = 6.0 * tokens * (L * layer_params + V * D)          # forward + dgrad + wgrad of every rotated linear
-    opt_bytes = 22.0 * params / world                          # bf16 p, g + fp32 m, v read; p, m, v written
+    opt_bytes = adam_bytes * params / world                    # p read + written, g read, m and v read + written
     nv_bytes = 3.0 * 2.0 * (L * layer_params + V * D) * (world - 1) / world   # W forward, W backward, dW; bf16
     t_gemm, t_opt, t_nv = flops / (tf * 1e12) * 1e3, opt_bytes / (hbm * 1e9) * 1e3, nv_bytes / 770e9 * 1e3
     bound = max(t_gemm + t_opt, t_nv)
@@ -218,7 +234,8 @@ def run_ours(args, cfg, rank, local, world):
             if p.dim() > 1:
                 p.uniform_(-cfg["initrange"], cfg["initrange"])
     model = model.to(device=dev, dtype=torch.bfloat16)
-    trainer = FusedLMTrainer(model, lr=cfg["lr"], clip_value=cfg["clip"], use_graph=not args.no_graph)
+    trainer = FusedLMTrainer(model, lr=cfg["lr"], clip_value=cfg["clip"], use_graph=not args.no_graph,
+                             state_dtype=args.adam_state)
     nb = max(8, args.steps + args.warmup)
     pinned = synthetic_batches(cfg, min(nb, 64), rank)
     dev_batches = [(a.to(dev), b.to(dev)) for a, b in pinned]
@@ -272,7 +289,7 @@ def run_ours_module(args, cfg, rank, local, world):
         model = MoELM(MoEConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["n_experts"],
                                 cfg["capacity_factor"], cfg["seq_len"]))
     model = model.to(device=dev, dtype=torch.bfloat16)
-    opt = ShardedAdamW(model.parameters(), lr=cfg["lr"], weight_decay=0.01)
+    opt = ShardedAdamW(model.parameters(), lr=cfg["lr"], weight_decay=0.01, state_dtype=args.adam_state)
     nb = min(max(4, args.steps + args.warmup), 16)
     pinned = [(a.t().contiguous().pin_memory(), b.t().contiguous().pin_memory())
               for a, b in synthetic_batches(cfg, nb, rank, pin=False)]
@@ -309,36 +326,34 @@ def run_ours_module(args, cfg, rank, local, world):
                "h2d_bytes_per_step": 2 * cfg["seq_len"] * cfg["batch"] * 8, "d2h_bytes_per_step": 4}
     from rtp_b200.parallel import engine as _eng
     peak = (torch.cuda.max_memory_allocated() + _eng.workspace_bytes()) / 2 ** 30   # torch allocator + rotation workspaces
-    return ms, clocks, loss, e2e, peak, 1
+    n0 = _lib.launches
+    step(*dev_batches[0])
+    torch.cuda.synchronize()
+    return ms, clocks, loss, e2e, peak, _lib.launches - n0
 
 
-def run_reference(args, cfg, rank, local, world):
-    """The reference's own rotated LM (rtp.models.transformer_lm_rtp.TransformerLM, out-of-place modules,
-    NCCL send/recv rotation, ATen/cuBLAS kernels), driven by the loop of its benchmark script
-    (benchmarks/rtp_benchmark.py:126-213: zero_grad, forward, CrossEntropyLoss, backward, clip_grad_value_,
-    Adam.step, loss.item())."""
+def run_ours_readme_module(args, cfg, rank, local, world):
+    """README config through the public module API: the reference-layout ``TransformerLM`` built from rotated modules,
+    autograd, a torch-style loop (zero_grad, forward, cross-entropy, backward, clip, step) and ``ShardedAdam`` — the
+    path a user of the reference's API gets; every rotated layer, the attention, the norms and Adam run on the library's
+    kernels, launched eagerly (no CUDA graph)."""
     import torch
-    ref = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref, "rtp")):
-        return None
-    sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
-    sys.path.insert(0, ref)
-    torch.set_default_dtype(torch.bfloat16)   # the reference ignores dtype=, and .to(bf16) breaks its aliasing
-    from rtp.models.transformer_lm_rtp import TransformerLM
+    sys.path.insert(0, ROOT)
+    from rtp_b200.models.transformer_lm_rtp import TransformerLM
+    from rtp_b200.optim import ShardedAdam
+    from rtp_b200.ops import functional as FO
+    from rtp_b200.ops import _lib
+    from rtp_b200.parallel import engine
     torch.manual_seed(0)
     dev = torch.device("cuda", local)
     model = TransformerLM(cfg["vocab"], cfg["ninp"], cfg["nhead"], cfg["nhid"], cfg["dropout"], cfg["initrange"],
-                          cfg["nlayers"], world, rank, device=dev)
-    with torch.no_grad():                     # the reference leaves the attention in-projection uninitialised
-        for name, p in model.named_parameters():
+                          cfg["nlayers"], world, rank)
+    with torch.no_grad():
+        for p in model.parameters():
             if p.dim() > 1:
                 p.uniform_(-cfg["initrange"], cfg["initrange"])
-            elif "in_proj_bias" in name:
-                p.zero_()
-    model = model.to(dev)                     # as benchmarks/rtp_benchmark.py:48-62 does (moves the PE buffer)
-    torch.set_default_dtype(torch.float32)
-    crit = torch.nn.CrossEntropyLoss()
-    opt = torch.optim.Adam(model.parameters(), lr=cfg["lr"])
+    model = model.to(device=dev, dtype=torch.bfloat16)
+    opt = ShardedAdam(model.parameters(), lr=cfg["lr"], clip_value=cfg["clip"], state_dtype=args.adam_state)
     nb = max(8, args.steps + args.warmup)
     pinned = synthetic_batches(cfg, min(nb, 64), rank)
     dev_batches = [(a.to(dev), b.to(dev)) for a, b in pinned]
@@ -350,13 +365,127 @@ def run_reference(args, cfg, rank, local, world):
         ids = ids.to(dev, non_blocking=True)
         tgt = tgt.to(dev, non_blocking=True)
         model.train()
+        opt.zero_grad(set_to_none=True)
+        logits = model(ids)
+        loss = FO.cross_entropy(logits.view(-1, cfg["vocab"]), tgt.view(-1))
+        (loss / world).backward()
+        opt.step()
+        last["loss"] = loss.detach()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed_loop(step, dev_batches, args.steps, max(args.warmup, 3), world, flush, None)
+    clocks = sampler.stop()
+    engine.check_all()
+    _lib.check_status(dev)
+    loss = float(last["loss"].item())
+    e2e = None
+    if not args.no_e2e:
+        def read_loss():
+            last["v"] = float(last["loss"].item())
+        ms_e2e = timed_loop(step, pinned, args.steps, 3, world, flush, read_loss)
+        tok = cfg["seq_len"] * cfg["batch"] * world * args.steps
+        e2e = {"value": tok / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+               "h2d_bytes_per_step": 2 * cfg["seq_len"] * cfg["batch"] * 8, "d2h_bytes_per_step": 4}
+    peak = (torch.cuda.max_memory_allocated() + engine.workspace_bytes()) / 2 ** 30
+    n0 = _lib.launches
+    step(*dev_batches[0])
+    torch.cuda.synchronize()
+    return ms, clocks, loss, e2e, peak, _lib.launches - n0
+
+
+def _fairscale_stub():
+    """The reference's DP / FSDP / TP model files import two classes from fairscale (not installed here) at module top
+    and use them only for MoE layers.  A stand-in package that hands them the reference's own copies of those classes
+    (rtp/module/moe.py, rtp/module/top2gate.py) lets the unmodified files import."""
+    import types
+    from rtp.module.moe import MOELayer
+    from rtp.module.top2gate import Top2Gate
+    names = ["fairscale", "fairscale.nn", "fairscale.nn.moe", "fairscale.nn.moe.moe_layer", "fairscale.nn.moe.top2gate"]
+    mods = {n: types.ModuleType(n) for n in names}
+    mods["fairscale.nn.moe.moe_layer"].MOELayer = MOELayer
+    mods["fairscale.nn.moe.top2gate"].Top2Gate = Top2Gate
+    for n in names:
+        sys.modules.setdefault(n, mods[n])
+
+
+def run_reference(args, cfg, rank, local, world):
+    """The reference's own code from baseline/_ref, driven by the loop of its benchmark scripts
+    (benchmarks/rtp_benchmark.py:126-213: zero_grad, forward, CrossEntropyLoss, backward, clip_grad_value_, Adam.step,
+    loss.item()).  --mode rtp: rtp.models.transformer_lm_rtp.TransformerLM (out-of-place rotated modules, NCCL send/recv,
+    ATen/cuBLAS kernels).  --mode dp / fsdp: benchmarks/transformer_lm_dp.py wrapped in DistributedDataParallel /
+    FullyShardedDataParallel (benchmarks/dp_benchmark.py:245, fsdp_benchmark.py:251).  --mode tp:
+    rtp.models.transformer_lm_tp.TransformerLM on the global batch (benchmarks/tp_benchmark.py:244)."""
+    import torch
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "rtp")):
+        return None
+    sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
+    sys.path.insert(0, ref)
+    sys.path.insert(0, os.path.join(ref, "benchmarks"))
+    torch.set_default_dtype(torch.bfloat16)   # the reference ignores dtype=, and .to(bf16) breaks its aliasing
+    torch.manual_seed(0)
+    dev = torch.device("cuda", local)
+    mode = args.mode
+    margs = (cfg["vocab"], cfg["ninp"], cfg["nhead"], cfg["nhid"], cfg["dropout"], cfg["initrange"], cfg["nlayers"])
+    if mode == "rtp":
+        from rtp.models.transformer_lm_rtp import TransformerLM
+        if cfg.get("family") == "moe":
+            # every FFN becomes a rotating mixture of experts (rtp/models/transformer_lm_rtp.py:146-153)
+            model = TransformerLM(*margs, world, rank, is_moe=True, num_local_experts=cfg["n_experts"] // world,
+                                  device=dev)
+        else:
+            model = TransformerLM(*margs, world, rank, device=dev)
+    elif mode == "tp":
+        _fairscale_stub()
+        from rtp.models.transformer_lm_tp import TransformerLM
+        model = TransformerLM(*margs, world, rank)
+    else:
+        _fairscale_stub()
+        import transformer_lm_dp
+        model = transformer_lm_dp.TransformerLM(*margs)
+    with torch.no_grad():                     # the reference leaves the attention in-projection uninitialised
+        for name, p in model.named_parameters():
+            if not p.requires_grad:
+                continue
+            if p.dim() > 1:
+                p.uniform_(-cfg["initrange"], cfg["initrange"])
+            elif "in_proj_bias" in name:
+                p.zero_()
+    model = model.to(dev)                     # as benchmarks/rtp_benchmark.py:48-62 does (moves the PE buffer)
+    torch.set_default_dtype(torch.float32)
+    if mode == "dp":
+        from torch.nn.parallel import DistributedDataParallel
+        model = DistributedDataParallel(model)
+    elif mode == "fsdp":
+        from torch.distributed.fsdp import FullyShardedDataParallel
+        model = FullyShardedDataParallel(model)
+    crit = torch.nn.CrossEntropyLoss()
+    opt = torch.optim.Adam(model.parameters(), lr=cfg["lr"])
+    nb = max(8, args.steps + args.warmup)
+    if mode == "tp":
+        # tensor parallelism works on ONE batch, the same on every rank, of world x the per-GPU size
+        big = dict(cfg, batch=cfg["batch"] * world)
+        pinned = synthetic_batches(big, min(nb, 64), 0)
+    else:
+        pinned = synthetic_batches(cfg, min(nb, 64), rank)
+    dev_batches = [(a.to(dev), b.to(dev)) for a, b in pinned]
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    torch.cuda.reset_peak_memory_stats()
+    last = {}
+    div = world if mode == "rtp" else 1       # rotated layers sum the gradients of the ranks; DDP / FSDP average them
+
+    def step(ids, tgt):
+        ids = ids.to(dev, non_blocking=True)
+        tgt = tgt.to(dev, non_blocking=True)
+        model.train()
         opt.zero_grad()
         output = model(ids)
-        loss = crit(output.view(-1, cfg["vocab"]), tgt.view(-1)) / world
+        loss = crit(output.view(-1, cfg["vocab"]), tgt.view(-1)) / div
         loss.backward()
         torch.nn.utils.clip_grad_value_(model.parameters(), cfg["clip"])
         opt.step()
-        last["loss"] = loss.detach() * world
+        last["loss"] = loss.detach() * div
         del loss, output     # keeps the reference's grad-ready hooks from stacking across steps
 
     sampler = ClockSampler(local)
@@ -371,7 +500,7 @@ def run_reference(args, cfg, rank, local, world):
         ms_e2e = timed_loop(step, pinned, args.steps, 3, world, flush, read_loss)
         tok = cfg["seq_len"] * cfg["batch"] * world * args.steps
         e2e = {"value": tok / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-               "h2d_bytes_per_step": 2 * cfg["seq_len"] * cfg["batch"] * 8, "d2h_bytes_per_step": 4}
+               "h2d_bytes_per_step": 2 * pinned[0][0].numel() * 8, "d2h_bytes_per_step": 4}
     peak = torch.cuda.max_memory_allocated() / 2 ** 30
     return ms, clocks, loss, e2e, peak, 0
 
@@ -390,15 +519,25 @@ def main():
         raise SystemExit("bench.py needs a CUDA device")
     rank, local, world = setup_dist(args)
     t_wall = time.time()
+    module_path = args.impl == "rtp_b200" and ("family" in cfg or args.path == "module")
     if args.impl == "reference":
-        if cfg.get("family") in ("llama", "moe"):
+        why = None
+        if cfg.get("family") == "llama":
+            why = "the reference ships no Llama model (no RMSNorm / RoPE / SwiGLU): nothing to run"
+        elif cfg.get("family") == "moe" and cfg.get("capacity_factor", 1.0) != 1.0:
+            why = ("the reference's gate has a fixed capacity of 2 * tokens / experts (rtp/module/top2gate.py:52); "
+                   "run --config moe-cf1 for a both-arms comparison at capacity factor 1.0")
+        elif args.mode != "rtp" and "family" in cfg:
+            why = "the DP / FSDP / TP arms are wired for the dense README model only"
+        if why:
             if rank == 0:
-                print(json.dumps({"impl": "reference", "unavailable": "the reference ships no Llama model and its MoE "
-                                  "capacity is fixed at factor 1.0; only the dense transformer LM is compared"}))
+                print(json.dumps({"impl": "reference", "unavailable": why}))
             return
         res = run_reference(args, cfg, rank, local, world)
     elif "family" in cfg:
         res = run_ours_module(args, cfg, rank, local, world)
+    elif args.path == "module":
+        res = run_ours_readme_module(args, cfg, rank, local, world)
     else:
         res = run_ours(args, cfg, rank, local, world)
     ms, clocks, loss, e2e, peak_gb, launches = res
@@ -406,24 +545,37 @@ def main():
     value = tokens / (ms / 1e3)
     peak_gb = max_over_ranks(peak_gb, world)
     if rank == 0:
+        if args.impl == "reference":
+            path = {"rtp": "reference eager (rotated modules, NCCL send/recv)", "dp": "reference eager (DDP)",
+                    "fsdp": "reference eager (FSDP)", "tp": "reference eager (tensor parallel layers)"}[args.mode]
+            optimizer = f"torch.optim.Adam lr {cfg['lr']:g} (bf16 moments)"
+            graph = False
+        elif module_path:
+            path = "module+autograd"
+            optimizer = (f"ShardedAdamW lr {cfg['lr']:g} wd 0.01" if "family" in cfg else f"ShardedAdam lr {cfg['lr']:g}") + \
+                f" ({args.adam_state} moments)"
+            graph = False
+        else:
+            path = "fused trainer"
+            optimizer = f"Adam lr {cfg['lr']:g} ({args.adam_state} moments)"
+            graph = not args.no_graph
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
             "impl": args.impl, "peak_gb_per_gpu": peak_gb, "final_loss": loss,
             "config": {"model": "RTP TransformerLM (README config)" if args.config == "readme" else args.config,
-                       "path": "module+autograd" if ("family" in cfg and args.impl == "rtp_b200") else "fused trainer",
                        "vocab": cfg["vocab"], "ninp": cfg["ninp"], "nhid": cfg["nhid"], "nhead": cfg["nhead"],
                        "layers": cfg["nlayers"], "seq_len": cfg["seq_len"], "batch_per_gpu": cfg["batch"],
                        "global_batch": cfg["batch"] * world, "dropout": cfg["dropout"], "clip": cfg["clip"],
-                       "optimizer": "Adam lr 1e-3", "parallelism": f"rtp{world}",
-                       "l2": "192 MiB buffer written between timed iterations (L2 flush)",
-                       "cuda_graph": (not args.no_graph) if args.impl == "rtp_b200" else False},
+                       "parallelism": f"{args.mode if args.impl == 'reference' else 'rtp'}{world}",
+                       "l2": "192 MiB buffer written between timed iterations (L2 flush)"},
+            "path": path, "optimizer": optimizer, "cuda_graph": graph,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps if args.impl == "rtp_b200" else None,
             "wall_s": time.time() - t_wall,
         }
-        if "family" not in cfg:
-            out["roofline"] = roofline(cfg, world, ms / args.steps)
+        if "family" not in cfg and args.impl == "rtp_b200":
+            out["roofline"] = roofline(cfg, world, ms / args.steps, ADAM_BYTES[args.adam_state])
         print(json.dumps(out))
     import torch.distributed as dist
     dist.barrier()

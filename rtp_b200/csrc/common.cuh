@@ -157,6 +157,27 @@ __device__ __forceinline__ void tma_load_3d_s(uint32_t smem_dst, unsigned long l
       ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
+// Untiled bulk copies (both addresses 16-byte aligned, size a multiple of 16 bytes).  The load completes on an mbarrier
+// of the issuing CTA; stores belong to the issuing thread's bulk async-group.  A store may target a peer GPU's memory
+// (plain NVLink writes issued by the copy engine of the SM); loads in this library only ever read local memory.
+__device__ __forceinline__ void bulk_load_s(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_s(void* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the most recent N groups of this thread are complete (their writes performed)
+template <int N>
+__device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
+// all but the most recent N groups of this thread have finished READING their shared-memory source (it may be reused)
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+
 // Makes writes done through the generic proxy (also a peer GPU's stores, once observed with an
 // acquire load) visible to later reads through the async proxy (TMA).
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }

@@ -4,8 +4,10 @@
 //   warp 1      UMMA issuer: one elected thread issues tcgen05.mma into one of two TMEM accumulators
 //   warps 2-5   epilogue: tcgen05.ld the accumulator, apply bias/activation/mask/dropout/accumulate,
 //               store to local or peer global memory, then bump the phase's counters
-//   warps 6-7   pushers: copy this rank's home shard into a peer's workspace slot (NVLink P2P stores),
-//               bounded by the peer's slot-free counter, then bump the peer's arrival counter
+//   warp 6      pusher: copies this rank's home shard into a peer's workspace slot with bulk asynchronous copies (bulk
+//               load from local memory into a two-slot shared-memory ring, bulk store from there into the peer's memory
+//               over NVLink), bounded by the peer's slot-free counter, then bumps the peer's arrival counter
+//   warp 7      idle
 //
 // All cross-rank waits are on 64-bit counters with an iteration/time limit; on expiry the CTA marks
 // the status word, drains what it has in flight, frees its TMEM and returns.
@@ -24,7 +26,9 @@ constexpr int kTmemCols = 512;
 constexpr int kNumThreads = 256;
 constexpr int kStagePitch = 144;                // bytes per staged output row: 64 bf16 + 16 pad (conflict-free 16 B writes)
 constexpr int kStagingBytes = 4 * 32 * kStagePitch;
-constexpr int kSmemBytes = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kStagingBytes;
+constexpr int kPushChunk = 7680;                // bytes per bulk copy of a push job (two ring slots per CTA)
+constexpr int kPushRingBytes = 2 * kPushChunk;
+constexpr int kSmemBytes = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kStagingBytes + kPushRingBytes;
 static_assert(kSmemBytes <= 232448, "over the 227 KB of shared memory a CTA can have");
 
 struct SmemCtrl {
@@ -34,6 +38,7 @@ struct SmemCtrl {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain;
+  uint64_t push_full[2];            // push ring: "the bulk load into slot s has landed"
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -99,6 +104,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       }
     } else if (lane == kMaxStages + 2) {
       mbar_init(&ctl->drain, 1);
+      mbar_init(&ctl->push_full[0], 1);
+      mbar_init(&ctl->push_full[1], 1);
       ctl->abort_flag = 0;
     }
     mbar_fence_init();
@@ -807,44 +814,125 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       }
       if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 3] = globaltimer_ns();
     }
-  } else {
-    // ------------------------------------------------------------------ pushers (2 warps)
-    const int ptid = (warp - 6) * 32 + lane;
-    bool ok = true;
-    for (int j = 0; j < P.n_pushes; ++j) {
-      const RtpPush& pu = P.pushes[j];
-      uint32_t good = 1;
-      if (P.trace && cta == 0 && ptid == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 0] = globaltimer_ns();
-      if (ok && lane == 0 && pu.credit_ptr)
-        good = wait_counter_ge(pu.credit_ptr, fill_target(P.flags, pu.credit_ctr, pu.credit_rel, 0, G), abort_flag,
-                               status, wait_ns, ST_TIMEOUT_CREDIT);
-      good = __shfl_sync(0xffffffffu, good, 0);
-      if (!good) ok = false;
-      if (P.trace && cta == 0 && ptid == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 1] = globaltimer_ns();
-      if (ok) {
-        const unsigned long long units = pu.bytes >> 4;
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ pusher (one elected thread)
+    // Every CTA moves its 1/G of each push job.  The chunks of all jobs form one software pipeline: while the bulk
+    // store of chunk c leaves for the peer, the bulk load of chunk c + 1 is already in flight; at most two stores are
+    // outstanding per CTA, which across the grid keeps a few megabytes on the link.
+    if (elect_one()) {
+      uint8_t* ring = staging + kStagingBytes;
+      const uint32_t ring_s = smem_u32(ring);
+      const uint32_t pf_s = smem_u32(&ctl->push_full[0]);
+      bool ok = true;
+      uint32_t ph[2] = {0u, 0u};
+      int slot = 0;
+      int sig_job = -1;                // job whose last store is the most recent committed group (signalled one group later)
+      // next chunk to load
+      int lj = 0;
+      unsigned long long loff = 0, lhi = 0;
+      bool lvalid = false;
+      auto job_range = [&](int j, unsigned long long& lo, unsigned long long& hi) {
+        const unsigned long long units = P.pushes[j].bytes >> 4;
         const unsigned long long per = (units + G - 1) / G;
-        const unsigned long long lo = per * (unsigned long long)cta;
-        unsigned long long hi = lo + per;
+        lo = per * (unsigned long long)cta;
+        hi = lo + per;
         if (hi > units) hi = units;
-        const uint4* src = reinterpret_cast<const uint4*>(pu.src);
-        uint4* dst = reinterpret_cast<uint4*>(pu.dst);
-        unsigned long long i = lo + ptid;
-        for (; i + 448 < hi; i += 512) {   // 8 x 16 B per thread in flight
-          uint4 v[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) v[u] = __ldg(src + i + 64 * u);
-#pragma unroll
-          for (int u = 0; u < 8; ++u) dst[i + 64 * u] = v[u];
+        if (lo > hi) lo = hi;
+        lo <<= 4; hi <<= 4;
+      };
+      auto signal_job = [&](int j) {
+        // the job's stores are complete (bulk_wait): make them visible system-wide, then count this CTA in
+        fence_proxy_async();
+        __threadfence_system();
+        if (P.pushes[j].arrive_ptr) red_relaxed_sys_add(P.pushes[j].arrive_ptr, 1ull);
+        if (P.trace && cta == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 2] = globaltimer_ns();
+      };
+      // advance (lj, loff) to the next non-empty chunk; jobs without bytes for this CTA are signalled right away
+      auto next_chunk = [&]() {
+        lvalid = false;
+        while (lj < P.n_pushes) {
+          if (loff < lhi) { lvalid = true; return; }
+          ++lj;
+          if (lj < P.n_pushes) job_range(lj, loff, lhi);
         }
-        for (; i < hi; i += 64) dst[i] = __ldg(src + i);
+      };
+      if (P.n_pushes > 0) { job_range(0, loff, lhi); next_chunk(); }
+      // jobs that are empty for this CTA still count it in (the counters mean "every CTA is past this fill")
+      bool counted[RTP_MAX_PUSHES];
+      for (int j = 0; j < RTP_MAX_PUSHES; ++j) counted[j] = false;
+      uint32_t lbytes[2] = {0u, 0u};
+      int ljob[2] = {-1, -1};
+      unsigned long long loffs[2] = {0ull, 0ull};
+      bool lstart[2] = {false, false}, llast[2] = {false, false};
+      auto issue_load = [&](int s) {
+        const RtpPush& pu = P.pushes[lj];
+        const unsigned long long n = (lhi - loff) < (unsigned long long)kPushChunk ? (lhi - loff) : (unsigned long long)kPushChunk;
+        unsigned long long jlo, jhi;
+        job_range(lj, jlo, jhi);
+        lbytes[s] = (uint32_t)n; ljob[s] = lj; loffs[s] = loff;
+        lstart[s] = loff == jlo; llast[s] = loff + n == lhi;
+        mbar_arrive_expect_tx_s(pf_s + s * 8, (uint32_t)n);
+        bulk_load_s(ring_s + s * kPushChunk, reinterpret_cast<const uint8_t*>(pu.src) + loff, (uint32_t)n, pf_s + s * 8);
+        loff += n;
+        next_chunk();
+      };
+      if (lvalid) issue_load(0);
+      bool have = ljob[0] >= 0;
+      while (have && ok) {
+        const int s = slot;
+        const int j = ljob[s];
+        const RtpPush& pu = P.pushes[j];
+        if (lstart[s]) {
+          if (P.trace && cta == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 0] = globaltimer_ns();
+          if (pu.credit_ptr &&
+              !wait_counter_ge(pu.credit_ptr, fill_target(P.flags, pu.credit_ctr, pu.credit_rel, 0, G), abort_flag,
+                               status, wait_ns, ST_TIMEOUT_CREDIT)) {
+            ok = false;
+            break;
+          }
+          if (P.trace && cta == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 1] = globaltimer_ns();
+        }
+        // the load of this chunk has landed (a copy from local memory always completes; the limit guards a logic error)
+        if (!mbar_wait_s(pf_s + s * 8, ph[s], abort_flag, status, timeout_ns)) { ok = false; break; }
+        ph[s] ^= 1u;
+        ljob[s] = -1;
+        bulk_store_s(reinterpret_cast<uint8_t*>(pu.dst) + loffs[s], ring_s + s * kPushChunk, lbytes[s]);
+        bulk_commit();
+        // the previous store has read its slot: the next load may go there while this store is on the link
+        bulk_wait_read<1>();
+        have = false;
+        if (lvalid) { issue_load(s ^ 1); have = true; }
+        // a job that ended with the previous store is signalled once that store is complete
+        if (sig_job >= 0) {
+          bulk_wait<1>();
+          signal_job(sig_job);
+          counted[sig_job] = true;
+          sig_job = -1;
+        }
+        if (llast[s]) sig_job = j;
+        slot ^= 1;
       }
-      asm volatile("bar.sync 2, 64;" ::: "memory");
-      if (ptid == 0 && ok && pu.arrive_ptr) {
-        __threadfence_system();   // one cumulative release for the stores of both pusher warps
-        red_relaxed_sys_add(pu.arrive_ptr, 1ull);
+      bulk_wait<0>();
+      if (!ok) {
+        // loads may still be in flight into the ring: let them land before the CTA can exit
+        for (int s = 0; s < 2; ++s) {
+          if (ljob[s] < 0) continue;
+          const unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(&ctl->push_full[s], ph[s])) {
+            if (globaltimer_ns() - t0 > 2000000ull) break;
+          }
+        }
       }
-      if (P.trace && cta == 0 && ptid == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 2] = globaltimer_ns();
+      if (sig_job >= 0) { if (ok) signal_job(sig_job); counted[sig_job] = true; }
+      // jobs in which this CTA had nothing to move
+      for (int j = 0; j < P.n_pushes; ++j) {
+        if (counted[j] || !ok) continue;
+        const RtpPush& pu = P.pushes[j];
+        if (pu.credit_ptr &&
+            !wait_counter_ge(pu.credit_ptr, fill_target(P.flags, pu.credit_ctr, pu.credit_rel, 0, G), abort_flag, status,
+                             wait_ns, ST_TIMEOUT_CREDIT)) { ok = false; break; }
+        if (pu.arrive_ptr) red_relaxed_sys_add(pu.arrive_ptr, 1ull);
+      }
     }
   }
 

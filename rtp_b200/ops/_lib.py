@@ -197,7 +197,12 @@ def lib():
     return _lib
 
 
+launches = 0      # calls into the library that launched kernels (every entry point launches at least one)
+
+
 def check(rc: int, what: str):
+    global launches
+    launches += 1
     if rc != 0:
         msg = lib().rtp_last_error()
         raise RuntimeError(f"{what} failed: {msg.decode() if msg else rc}")

@@ -89,6 +89,7 @@ def _common(a, B, H, Sq, Sk, hd, causal, sm_scale, drop_p, seed, offset, step, d
 
 
 def _check(rc, what):
+    _lib.launches += 2 if what.endswith("bwd") else 1
     if rc != 0:
         raise RuntimeError(f"{what}: {_lib.lib().rtp_flash_last_error().decode()}")
 

@@ -57,6 +57,7 @@ def _L():
 
 
 def _check(rc, what):
+    _lib.launches += 1
     if rc != 0:
         msg = _L().rtp_kernels_last_error()
         raise RuntimeError(f"{what} failed: {msg.decode() if msg else rc}")
