@@ -45,6 +45,7 @@ CONFIGS["moe-small"] = dict(family="moe", vocab=8192, ninp=512, nhid=1024, nhead
                             n_experts=8, capacity_factor=1.25, dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
 # the reference's gate has a fixed capacity of 2 * tokens / experts (factor 1.0): this variant lets both arms run
 CONFIGS["moe-cf1"] = dict(CONFIGS["moe"], capacity_factor=1.0)
+CONFIGS["moe-small-cf1"] = dict(CONFIGS["moe-small"], capacity_factor=1.0)
 METRIC = "tokens/s/box"
 
 
@@ -361,16 +362,25 @@ def run_ours_readme_module(args, cfg, rank, local, world):
     torch.cuda.reset_peak_memory_stats()
     last = {}
 
-    def step(ids, tgt):
-        ids = ids.to(dev, non_blocking=True)
-        tgt = tgt.to(dev, non_blocking=True)
-        model.train()
-        opt.zero_grad(set_to_none=True)
+    model.train()
+
+    def raw_step(ids, tgt):
+        opt.zero_grad(set_to_none=False)         # gradient buffers keep their addresses (needed under graph replay)
         logits = model(ids)
         loss = FO.cross_entropy(logits.view(-1, cfg["vocab"]), tgt.view(-1))
         (loss / world).backward()
         opt.step()
-        last["loss"] = loss.detach()
+        return loss.detach()
+
+    if args.no_graph:
+        def step(ids, tgt):
+            last["loss"] = raw_step(ids.to(dev, non_blocking=True), tgt.to(dev, non_blocking=True))
+    else:
+        from rtp_b200.utils.graphed import GraphedStep
+        graphed = GraphedStep(raw_step, dev_batches[0])
+
+        def step(ids, tgt):
+            last["loss"] = graphed(ids, tgt)       # copies the (host or device) inputs into the graph's buffers
 
     sampler = ClockSampler(local)
     sampler.start()
@@ -389,7 +399,7 @@ def run_ours_readme_module(args, cfg, rank, local, world):
                "h2d_bytes_per_step": 2 * cfg["seq_len"] * cfg["batch"] * 8, "d2h_bytes_per_step": 4}
     peak = (torch.cuda.max_memory_allocated() + engine.workspace_bytes()) / 2 ** 30
     n0 = _lib.launches
-    step(*dev_batches[0])
+    raw_step(*dev_batches[0])                    # eager, to count the library's launches of one step
     torch.cuda.synchronize()
     return ms, clocks, loss, e2e, peak, _lib.launches - n0
 
@@ -554,7 +564,7 @@ def main():
             path = "module+autograd"
             optimizer = (f"ShardedAdamW lr {cfg['lr']:g} wd 0.01" if "family" in cfg else f"ShardedAdam lr {cfg['lr']:g}") + \
                 f" ({args.adam_state} moments)"
-            graph = False
+            graph = ("family" not in cfg) and not args.no_graph
         else:
             path = "fused trainer"
             optimizer = f"Adam lr {cfg['lr']:g} ({args.adam_state} moments)"

@@ -40,7 +40,9 @@ def _time(fn, iters, warm=2):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["gemm", "norm_fwd", "norm_bwd", "ce", "adam", "attn_fwd", "attn_bwd", "colsum",
-                                     "embed", "gate", "rope", "im2col"])
+                                     "embed", "gate", "rope", "im2col", "flash_fwd", "flash_bwd"])
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--full", action="store_true", help="flash cases: full instead of causal attention")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -109,6 +111,27 @@ def main(argv=None):
         nbytes = n * 2 * 7
         print(json.dumps({"case": "adam", "n": n, "us": ms * 1e3, "GBs": nbytes / ms / 1e6,
                           "frac_of_copy_peak": nbytes / ms / 1e6 / hbm, "peaks": src}))
+        return
+    if a.case in ("flash_fwd", "flash_bwd"):
+        # flash attention on a packed projection [B * S, 3 * H * hd]; FLOPs: 4 S^2 hd per (batch, head) forward (half of it
+        # with a causal mask), 2.5 x that in backward (five products; the kernels recompute S and dP: seven)
+        from ..ops.flash import flash_attention_packed
+        S, B, H, hd = a.seq, a.batch, a.heads, a.head_dim
+        causal = not a.full
+        qkvs = [(torch.randn(B * S, 3 * H * hd, device=dev, dtype=bf) * 0.5).requires_grad_(True) for _ in range(a.copies)]
+        flops = 4.0 * S * S * hd * B * H * (0.5 if causal else 1.0)
+        if a.case == "flash_fwd":
+            with torch.no_grad():
+                ms = _time(lambda i: flash_attention_packed(qkvs[i % a.copies], B, S, H, causal=causal), a.iters)
+        else:
+            outs = [flash_attention_packed(q, B, S, H, causal=causal) for q in qkvs]
+            do = torch.randn_like(outs[0])
+            ms = _time(lambda i: torch.autograd.grad(outs[i % a.copies], qkvs[i % a.copies], do, retain_graph=True), a.iters)
+            flops *= 2.5
+        _lib.check_status()
+        t = flops / ms / 1e9
+        print(json.dumps({"case": a.case, "S": S, "B": B, "H": H, "head_dim": hd, "causal": causal, "us": ms * 1e3,
+                          "tflops": t, "frac_of_cublas_peak": t / tf, "peaks": src}))
         return
     if a.case in ("attn_fwd", "attn_bwd"):
         S, B, H = a.seq, a.batch, a.heads

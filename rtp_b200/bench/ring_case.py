@@ -2,7 +2,7 @@
 timeline (``%globaltimer`` stamps of CTA 0 of rank 0: phase waits, tiles, signals, pushes).
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m rtp_b200.bench.ring_case \
-        --m 1024 --in-features 2048 --out-features 2048
+        --tokens 1024 --in-features 2048 --out-features 2048
 
 Used for the multi-GPU summaries under profiles/.  Run with NCCL_NVLS_ENABLE=0 when ranks may leave early."""
 import argparse
@@ -22,7 +22,7 @@ def _g(t, base, i):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--m", type=int, default=1024)
+    ap.add_argument("--tokens", type=int, default=1024, help="rows of the activation matrix")
     ap.add_argument("--in-features", type=int, default=2048)
     ap.add_argument("--out-features", type=int, default=2048)
     ap.add_argument("--calls", type=int, default=10, help="launches per captured graph")
@@ -36,7 +36,7 @@ def main(argv=None):
     L = _lib.lib()
     L.rtp_debug_set_trace.argtypes = [C.c_void_p]
     dev, bf = "cuda", torch.bfloat16
-    M, K_, Nf = a.m, a.in_features, a.out_features
+    M, K_, Nf = a.tokens, a.in_features, a.out_features
     Os = Nf // world
     eng = E.FusedEngine(RingContext(dist.group.WORLD, rank, world), (Os * K_ + Os) * 2)
     flat = torch.randn(Os * K_ + Os, device=dev, dtype=bf) * 0.02

@@ -148,6 +148,7 @@ def save_sharded(directory: str, model, optimizer=None, step: int = 0, extra=Non
                "rng_cpu": torch.get_rng_state(),
                "rng_cuda": torch.cuda.get_rng_state_all() if torch.cuda.is_available() else None}
     if optimizer is not None:
+        # a FusedLMTrainer plays the optimizer's part too: its state_dict holds the Adam moments and both step counters
         payload["optimizer"] = optimizer.state_dict()
         payload["optimizer_step"] = getattr(optimizer, "_step", None)
     path = os.path.join(directory, f"rank{ctx.rank}-of-{ctx.world}.pt")
@@ -178,16 +179,19 @@ def load_sharded(directory: str, model, optimizer=None, group=None, restore_rng:
         model.load_state_dict(payload["model"])
         if optimizer is not None and "optimizer" in payload:
             optimizer.load_state_dict(payload["optimizer"])
-            if payload.get("optimizer_step") is not None:
+            if payload.get("optimizer_step") is not None and hasattr(optimizer, "_step"):
                 optimizer._step = payload["optimizer_step"]
                 optimizer._step_dev = None
         if restore_rng:
             torch.set_rng_state(payload["rng_cpu"])
             if payload.get("rng_cuda") is not None and torch.cuda.is_available():
-                try:
-                    torch.cuda.set_rng_state_all(payload["rng_cuda"])
-                except Exception:
-                    pass
+                states = payload["rng_cuda"]
+                if len(states) != torch.cuda.device_count():
+                    # saved on a machine with another number of visible devices: restore this process's device only
+                    dev = torch.cuda.current_device()
+                    torch.cuda.set_rng_state(states[min(dev, len(states) - 1)], dev)
+                else:
+                    torch.cuda.set_rng_state_all(states)
         return payload["step"]
     # different ring size: weights only (optimizer state restarts)
     sds = [torch.load(os.path.join(directory, f"rank{r}-of-{old_world}.pt"), map_location="cpu",

@@ -143,6 +143,15 @@ typedef struct {
   void* out;
 } RtpReduceScatter;
 int rtp_reduce_scatter_cols(const RtpRing* ring, const RtpReduceScatter* op, void* stream);
+// The same reduction as ONE hop (all-to-all): `src` holds N contiguous blocks of block_elems bf16 each (block j is what
+// this rank contributes to owner j); every block travels straight to its owner and the owner adds the N contributions.
+typedef struct {
+  const void* src;
+  long long block_elems;     // multiple of 8
+  void* out;                 // [block_elems] bf16: sum over ranks of block `rank`
+} RtpReduceBlocks;
+int rtp_reduce_blocks(const RtpRing* ring, const RtpReduceBlocks* op, void* stream);
+int rtp_reduce_blocks_emu(const RtpRing* rings, const RtpReduceBlocks* ops, int world, void* stream);
 int rtp_embed_fwd_rot_emu(const RtpRing* rings, const RtpEmbedFwd* ops, int world, void* stream);
 int rtp_reduce_scatter_cols_emu(const RtpRing* rings, const RtpReduceScatter* ops, int world, void* stream);
 
@@ -178,6 +187,7 @@ void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i, int world);
 int rtp_sm_count(void);
 const char* rtp_last_error(void);
 void rtp_set_pair_mode(int on);        // CTA pairs (cta_group::2 UMMA, half of the B tile per SM): 1 always, 0 never, -1 automatic (default; env RTP_PAIR=0/1 overrides)
+void rtp_set_push_ctas(int n);         // CTAs per launch reserved for pushing shards to peers (default 0: every CTA pushes a share; env RTP_PUSH_CTAS)
 void rtp_debug_set_trace(unsigned long long* device_buffer_1024_words);  // tuning aid: globaltimer timeline of CTA 0 of rtp_gemm launches (null = off)
 void rtp_debug_force_stages(int n);   // tuning aid: cap the smem pipeline depth (0 = automatic)
 

@@ -6,8 +6,12 @@
 // every pair of GPUs the same bandwidth, a shard is not forwarded hop by hop: its owner pushes it from
 // its (read-only) home buffer straight into the slot of the rank that needs it next, so no rank ever
 // waits for a neighbour to finish forwarding.  Backward visits shards in the order r-1, r-2, ..., r
-// (rtp/module/collectives.py:281-317), weights again pushed by their owners, while the gradient of
-// each shard travels rank to rank and picks up one contribution per hop until it reaches its owner.
+// (rtp/module/collectives.py:281-317), weights again pushed by their owners.  The gradient of a shard
+// does not travel from rank to rank either: every rank stores its contribution straight into a gradient
+// slot of the owner (one slot per contributing rank) and the owner adds the N contributions in a last
+// phase: a reduce-scatter done as one all-to-all hop instead of N-1 dependent ones.
+// Sums over visiting shards (row-mode forward, column-mode input gradient) are ONE K-segmented phase whose
+// contraction walks over the shards in their order of arrival, so their output is written once.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cooperative_groups.h>
@@ -98,6 +102,12 @@ void init_phase(RtpPhase& ph) {
   ph.b_box = 128;
   ph.alpha = 1.f;
 }
+void set_peers(const RtpRing& R, RtpProgram& P) {
+  P.rank = R.rank;
+  P.world = R.world;
+  for (int t = 0; t < RTP_FLAG_MAX_WORLD; ++t)
+    P.peer_flags[t] = (t < R.world && R.ws[t]) ? reinterpret_cast<RtpFlagBlock*>(R.ws[t]) : nullptr;
+}
 void init_program(RtpProgram& p) {
   memset(&p, 0, sizeof(p));
   p.timeout_ns = 2000000000ull;
@@ -149,8 +159,26 @@ uint32_t drop_threshold(float p) {
 // Pipeline geometry: the stage must hold the widest B tile of the program; narrower tiles get more stages.
 int g_force_stages = 0;
 unsigned long long* g_trace = nullptr;   // tuning aid, see rtp_debug_set_trace
+// CTAs reserved for the push jobs of a launch (they own no GEMM tile, so their copy engine is not shared with a tile
+// pipeline and their tile memory becomes a deep copy ring).  RTP_PUSH_CTAS overrides; 0 = every CTA pushes a share.
+int g_push_ctas = -2;
+int push_cta_policy(int ctas) {
+  if (g_push_ctas == -2) {
+    const char* e = getenv("RTP_PUSH_CTAS");
+    g_push_ctas = e ? atoi(e) : -1;
+  }
+  // default 0: measured on two B200s, an SM sends to a peer at a limited rate, so a launch moves more when every CTA
+  // pushes a share than when a few reserved CTAs push everything
+  int r = g_push_ctas >= 0 ? g_push_ctas : 0;
+  if (r >= ctas) r = 0;
+  return r;
+}
 void finalize_program(RtpProgram& P, int ctas, bool pair) {
   const int tm = pair ? 256 : 128;
+  int reserved = P.n_pushes > 0 ? push_cta_policy(ctas) : 0;
+  if (pair) reserved &= ~1;
+  P.n_compute = ctas - reserved;
+  ctas = P.n_compute;
   if (pair) ctas /= 2;
   // Tile t of a phase runs on CTA (t + cta_off) % ctas.  Successive phases start where the previous one ended, so
   // that small per-step GEMMs fill the whole grid.  A phase that accumulates into the output of an earlier phase
@@ -271,7 +299,7 @@ int add_prefetch_pushes(const RtpRing& R, RtpProgram& P, const void* home, unsig
     pu.src = home;
     pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot, R.world);
     pu.bytes = bytes;
-    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
+    pu.credit_ptr = &ws_flags(R.ws[R.rank])->credit[t][RTP_CTR_W0 + slot].v;
     pu.credit_ctr = RTP_CTR_W0 + slot;
     pu.credit_rel = 0;
     pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
@@ -297,6 +325,7 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
   const int wb = op.bank * RTP_NUM_SLOTS;   // first weight slot of the bank this launch reads
   void* ws = R.ws[r];
   P.flags = ws ? ws_flags(ws) : nullptr;
+  set_peers(R, P);
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
   P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
 
@@ -307,6 +336,39 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
   if (make_map_k(&P.maps[1], op.home, Os, Ks, Ks, b_box)) return -1;
   for (int i = 1; i < N; ++i)
     if (make_map_k(&P.maps[1 + i], ws_wslot(ws, R.slot_bytes, wb + i - 1, R.world), Os, Ks, Ks, b_box)) return -1;
+  if (!col && N > 1) {
+    // Row mode on a ring: y = sum_j x[:, block j] W_j^T + sum_j b_j is ONE phase whose contraction walks over the shards
+    // in their order of arrival (own shard first), so the output is written once instead of N read-modify-write passes.
+    P.n_phases = 1;
+    RtpPhase& ph = P.phases[0];
+    init_phase(ph);
+    ph.a_map = 0; ph.b_map = 1;
+    ph.M = op.M; ph.N = Os; ph.K = Ks;
+    ph.bn = bn; ph.b_box = b_box;
+    ph.ldd = op.ldy; ph.d = op.y;
+    ph.nseg = N;
+    for (int i = 0; i < N; ++i) {
+      const int j = mod(r + i, N);
+      const int slot = wb + i - 1;
+      const uint8_t* src = (i == 0) ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, slot, R.world);
+      ph.seg_a_off_k[i] = j * Ks;
+      ph.seg_b_map[i] = (i == 0) ? 1 : 1 + i;
+      if (i > 0) {
+        ph.wait_ctr[i] = RTP_CTR_W0 + slot; ph.wait_rel[i] = 0;
+        ph.done_ctr[i] = RTP_CTR_W0 + slot;
+        P.uses_inc[RTP_CTR_W0 + slot] = 1;
+      }
+      if (op.bias_off >= 0) {
+        const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(src) + op.bias_off;
+        if (i == 0) ph.bias = b; else ph.bias_more[ph.n_bias_more++] = b;
+      }
+    }
+    ph.act = op.act;
+    ph.drop_thresh = drop_threshold(op.drop_p);
+    ph.drop_scale = op.drop_p > 0.f ? 1.f / (1.f - op.drop_p) : 1.f;
+    ph.drop_seed = op.seed; ph.drop_offset = op.offset; ph.drop_step_ptr = op.step_ptr;
+    set_vec_ok(ph);
+  } else {
   P.n_phases = N;
   for (int i = 0; i < N; ++i) {
     RtpPhase& ph = P.phases[i];
@@ -345,6 +407,7 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
     }
     set_vec_ok(ph);
   }
+  }
   P.n_pushes = op.no_self_push ? 0 : N - 1;
   for (int i = 0; i + 1 < N && !op.no_self_push; ++i) {
     RtpPush& pu = P.pushes[i];
@@ -354,7 +417,7 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
     pu.src = op.home;
     pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot, R.world);
     pu.bytes = op.shard_bytes;
-    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
+    pu.credit_ptr = &ws_flags(R.ws[R.rank])->credit[t][RTP_CTR_W0 + slot].v;
     pu.credit_ctr = RTP_CTR_W0 + slot;
     pu.credit_rel = 0;
     pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
@@ -382,6 +445,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   const int wb = op.bank * RTP_NUM_SLOTS;   // first weight slot of the bank this launch reads
   void* ws = R.ws[r];
   P.flags = ws ? ws_flags(ws) : nullptr;
+  set_peers(R, P);
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
   P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
 
@@ -420,10 +484,9 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
       ph.d = dst; ph.ldd = Ks;
       if (op.grad_accumulate && N == 1) { ph.c = op.grad_home; ph.ldc = Ks; }
       if (N > 1) {
-        ph.credit_ptr = &ws_flags(R.ws[j])->done[RTP_CTR_G0 + s].v;
+        ph.credit_ptr = &ws_flags(R.ws[R.rank])->credit[j][RTP_CTR_G0 + s].v;
         ph.credit_ctr = RTP_CTR_G0 + s; ph.credit_rel = 0;
         ph.arrive_ptr = &ws_flags(R.ws[j])->arrive[RTP_CTR_G0 + s].v;
-        ph.arrive_defer = 1;   // consumed by the owner's final reduce phase only
       }
       if (op.bias_off >= 0 && op.dbias_full) {
         ph.vec_out = reinterpret_cast<__nv_bfloat16*>(dst) + op.bias_off;
@@ -436,6 +499,33 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   }
   // The weight-gradient phases need only local operands, so they all come first and cover the time the weight shards
   // are in flight; the input-gradient phases follow, own shard first, then the visiting shards in order of arrival.
+  if (col && N > 1 && op.dx) {
+    // Column mode on a ring: dx = sum_j dy[:, block j] W_j is ONE phase whose contraction walks over the shards, own
+    // shard first, then the visiting ones in their order of arrival; dx is written once.
+    RtpPhase& ph = P.phases[np++];
+    init_phase(ph);
+    ph.a_map = 2; ph.a_mn = 0;
+    ph.b_map = 3; ph.b_mn = 1;
+    ph.M = op.M; ph.N = Ks; ph.K = Os;
+    ph.bn = pick_bn(ph.M, ph.N, R.ctas);
+    ph.ldd = op.lddx; ph.d = op.dx;
+    if (op.dx_accumulate) { ph.c = op.dx; ph.ldc = op.lddx; }
+    if (op.mask) { ph.mask = op.mask; ph.ldmask = op.ldmask; ph.mask_scale = op.mask_scale; }
+    ph.nseg = N;
+    for (int q = 0; q < N; ++q) {
+      const int s = (q == 0) ? N - 1 : q - 1;
+      const int j = mod(r - 1 - s, N);
+      const bool last = s == N - 1;   // own shard
+      ph.seg_a_off_k[q] = j * Os;
+      ph.seg_b_map[q] = last ? 3 : 4 + s;
+      if (!last) {
+        ph.wait_ctr[q] = RTP_CTR_W0 + wb + s; ph.wait_rel[q] = 0;
+        ph.done_ctr[q] = RTP_CTR_W0 + wb + s;
+        P.uses_inc[RTP_CTR_W0 + wb + s] = 1;
+      }
+    }
+    set_vec_ok(ph);
+  } else {
   for (int q = 0; q < N && op.dx; ++q) {
     const int s = (q == 0) ? N - 1 : q - 1;
     const int j = mod(r - 1 - s, N);
@@ -466,6 +556,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
       set_vec_ok(ph);
     }
   }
+  }
   // ---- owner-side sum of the N gradient slots (slot s was written by rank r+1+s; slot N-1 by this rank)
   if (N > 1) {
     RtpPhase& ph = P.phases[np++];
@@ -492,7 +583,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
     pu.src = op.home;
     pu.dst = ws_wslot(R.ws[t], R.slot_bytes, wb + s, R.world);
     pu.bytes = op.shard_bytes;
-    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + wb + s].v;
+    pu.credit_ptr = &ws_flags(R.ws[R.rank])->credit[t][RTP_CTR_W0 + wb + s].v;
     pu.credit_ctr = RTP_CTR_W0 + wb + s;
     pu.credit_rel = 0;
     pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + wb + s].v;
@@ -509,6 +600,7 @@ int build_expert_fwd(const RtpRing& R, const RtpExpertFwd& op, RtpProgram& P) {
   if (op.shard_bytes % 16) return fail("shard_bytes must be a multiple of 16");
   void* ws = R.ws[r];
   P.flags = ws ? ws_flags(ws) : nullptr;
+  set_peers(R, P);
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
   P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
   const long long rows = (long long)N * L * op.cap;
@@ -550,7 +642,7 @@ int build_expert_fwd(const RtpRing& R, const RtpExpertFwd& op, RtpProgram& P) {
     pu.src = op.home;
     pu.dst = ws_wslot(R.ws[t], R.slot_bytes, i, R.world);
     pu.bytes = op.shard_bytes;
-    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + i].v;
+    pu.credit_ptr = &ws_flags(R.ws[R.rank])->credit[t][RTP_CTR_W0 + i].v;
     pu.credit_ctr = RTP_CTR_W0 + i;
     pu.credit_rel = 0;
     pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + i].v;
@@ -567,6 +659,7 @@ int build_expert_bwd(const RtpRing& R, const RtpExpertBwd& op, RtpProgram& P) {
   if (N > 1 && op.shard_bytes > R.slot_bytes) return fail("shard larger than workspace slot");
   void* ws = R.ws[r];
   P.flags = ws ? ws_flags(ws) : nullptr;
+  set_peers(R, P);
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
   P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
   const long long rows = (long long)N * L * op.cap;
@@ -592,7 +685,7 @@ int build_expert_bwd(const RtpRing& R, const RtpExpertBwd& op, RtpProgram& P) {
         __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(gdst) + (long long)e * op.expert_stride;
         ph.d = d; ph.ldd = op.in_features;
         if (N > 1) {
-          ph.credit_ptr = &ws_flags(R.ws[j])->done[RTP_CTR_G0 + s].v;
+          ph.credit_ptr = &ws_flags(R.ws[R.rank])->credit[j][RTP_CTR_G0 + s].v;
           ph.credit_ctr = RTP_CTR_G0 + s; ph.credit_rel = 0;
           if (e == L - 1) ph.arrive_ptr = &ws_flags(R.ws[j])->arrive[RTP_CTR_G0 + s].v;
         }
@@ -651,7 +744,7 @@ int build_expert_bwd(const RtpRing& R, const RtpExpertBwd& op, RtpProgram& P) {
     pu.src = op.home;
     pu.dst = ws_wslot(R.ws[t], R.slot_bytes, s, R.world);
     pu.bytes = op.shard_bytes;
-    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + s].v;
+    pu.credit_ptr = &ws_flags(R.ws[R.rank])->credit[t][RTP_CTR_W0 + s].v;
     pu.credit_ctr = RTP_CTR_W0 + s;
     pu.credit_rel = 0;
     pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + s].v;
@@ -669,6 +762,7 @@ int build_embed_fwd(const RtpRing& R, const RtpEmbedFwd& op, RtpProgram& P) {
   if (op.shard_bytes % 16) return fail("shard_bytes must be a multiple of 16");
   void* ws = R.ws[r];
   P.flags = ws ? ws_flags(ws) : nullptr;
+  set_peers(R, P);
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
   P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
   P.n_phases = N;
@@ -703,7 +797,7 @@ int build_embed_fwd(const RtpRing& R, const RtpEmbedFwd& op, RtpProgram& P) {
     pu.src = op.home;
     pu.dst = ws_wslot(R.ws[t], R.slot_bytes, slot, R.world);
     pu.bytes = op.shard_bytes;
-    pu.credit_ptr = &ws_flags(R.ws[t])->done[RTP_CTR_W0 + slot].v;
+    pu.credit_ptr = &ws_flags(R.ws[R.rank])->credit[t][RTP_CTR_W0 + slot].v;
     pu.credit_ctr = RTP_CTR_W0 + slot;
     pu.credit_rel = 0;
     pu.arrive_ptr = &ws_flags(R.ws[t])->arrive[RTP_CTR_W0 + slot].v;
@@ -720,6 +814,7 @@ int build_reduce_scatter(const RtpRing& R, const RtpReduceScatter& op, RtpProgra
   if (N > 1 && (unsigned long long)op.rows * op.cols * 2 > R.slot_bytes) return fail("block larger than workspace slot");
   void* ws = R.ws[r];
   P.flags = ws ? ws_flags(ws) : nullptr;
+  set_peers(R, P);
   P.status = ws ? &ws_flags(ws)->status.v : nullptr;
   P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
   const int up = mod(r + 1, N);
@@ -741,13 +836,60 @@ int build_reduce_scatter(const RtpRing& R, const RtpReduceScatter& op, RtpProgra
       ph.done_ctr[0] = RTP_CTR_G0 + gin;
     }
     if (!last) {
-      ph.credit_ptr = &ws_flags(R.ws[up])->done[RTP_CTR_G0 + gout].v;
+      ph.credit_ptr = &ws_flags(R.ws[R.rank])->credit[up][RTP_CTR_G0 + gout].v;
       ph.credit_ctr = RTP_CTR_G0 + gout; ph.credit_rel = s / 2;
       ph.arrive_ptr = &ws_flags(R.ws[up])->arrive[RTP_CTR_G0 + gout].v;
     }
   }
   P.uses_inc[RTP_CTR_G0] = N / 2;
   P.uses_inc[RTP_CTR_G0 + 1] = (N - 1) / 2;
+  return 0;
+}
+
+// Reduce-scatter of N contiguous blocks as ONE hop: rank r pushes block j (j != r) of its block-major buffer straight
+// into a gradient slot of owner j (bulk copies over NVLink, all peers at once), and sums the N-1 blocks it receives with
+// its own block r.  Slot s of an owner is written by rank owner + 1 + s, the same convention as the weight gradients.
+int build_reduce_blocks(const RtpRing& R, const RtpReduceBlocks& op, RtpProgram& P) {
+  init_program(P);
+  const int N = R.world, r = R.rank;
+  if (N < 1 || N > RTP_MAX_WORLD) return fail("world size out of range");
+  if (op.block_elems % 8) return fail("reduce_blocks: block_elems must be a multiple of 8");
+  const unsigned long long bytes = (unsigned long long)op.block_elems * 2;
+  if (N > 1 && bytes > R.slot_bytes) return fail("block larger than workspace slot");
+  void* ws = R.ws[r];
+  P.flags = ws ? ws_flags(ws) : nullptr;
+  set_peers(R, P);
+  P.status = ws ? &ws_flags(ws)->status.v : nullptr;
+  P.timeout_ns = R.timeout_ns ? R.timeout_ns : 2000000000ull;
+  const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(op.src);
+  RtpPhase& ph = P.phases[0];
+  init_phase(ph);
+  ph.kind = RTP_KIND_REDUCE;
+  ph.M = ph.N = ph.K = 0;
+  ph.d = op.out;
+  ph.r_nsrc = N;
+  ph.r_n = op.block_elems;
+  for (int s = 0; s + 1 < N; ++s) {
+    ph.r_src[s] = ws_gslot(ws, R.slot_bytes, s, R.world);
+    ph.wait_ctr[s] = RTP_CTR_G0 + s; ph.wait_rel[s] = 0;
+    ph.done_ctr[s] = RTP_CTR_G0 + s;
+    P.uses_inc[RTP_CTR_G0 + s] = 1;
+  }
+  ph.r_src[N - 1] = src + (long long)r * op.block_elems;      // own block: read in place
+  P.n_phases = 1;
+  P.n_pushes = N - 1;
+  for (int s = 0; s + 1 < N; ++s) {
+    RtpPush& pu = P.pushes[s];
+    memset(&pu, 0, sizeof(pu));
+    const int j = mod(r - 1 - s, N);                           // owner that receives my block j in its slot s
+    pu.src = src + (long long)j * op.block_elems;
+    pu.dst = ws_gslot(R.ws[j], R.slot_bytes, s, R.world);
+    pu.bytes = bytes;
+    pu.credit_ptr = &ws_flags(R.ws[R.rank])->credit[j][RTP_CTR_G0 + s].v;
+    pu.credit_ctr = RTP_CTR_G0 + s;
+    pu.credit_rel = 0;
+    pu.arrive_ptr = &ws_flags(R.ws[j])->arrive[RTP_CTR_G0 + s].v;
+  }
   return 0;
 }
 
@@ -776,6 +918,7 @@ extern "C" {
 
 const char* rtp_last_error(void) { return g_err.c_str(); }
 void rtp_debug_force_stages(int n) { g_force_stages = n; }
+void rtp_set_push_ctas(int n) { g_push_ctas = n < 0 ? -1 : n; }
 void rtp_set_pair_mode(int on) { g_pair = on < 0 ? -1 : (on ? 1 : 0); }
 void rtp_debug_set_trace(unsigned long long* device_buffer_1024_words) { g_trace = device_buffer_1024_words; }
 int rtp_sm_count(void) { return sm_count(); }
@@ -916,6 +1059,18 @@ int rtp_reduce_scatter_cols(const RtpRing* ring, const RtpReduceScatter* op, voi
   if (!params.prog[0].status) return fail("ring workspace required");
   params.ctas_per_rank = ring->ctas;
   return launch<1>(params, ring->ctas, false, (cudaStream_t)stream);
+}
+int rtp_reduce_blocks(const RtpRing* ring, const RtpReduceBlocks* op, void* stream) {
+  static thread_local rtp::GemmParams<1> params;
+  if (build_reduce_blocks(*ring, *op, params.prog[0])) return -1;
+  if (!params.prog[0].status) return fail("ring workspace required");
+  params.ctas_per_rank = ring->ctas;
+  return launch<1>(params, ring->ctas, false, (cudaStream_t)stream);
+}
+int rtp_reduce_blocks_emu(const RtpRing* rings, const RtpReduceBlocks* ops, int world, void* stream) {
+  if (world == 2) return run_emu<2>(rings, ops, build_reduce_blocks, (cudaStream_t)stream);
+  if (world == 4) return run_emu<4>(rings, ops, build_reduce_blocks, (cudaStream_t)stream);
+  return fail("emulation supports 2 or 4 ranks");
 }
 int rtp_embed_fwd_rot_emu(const RtpRing* rings, const RtpEmbedFwd* ops, int world, void* stream) {
   if (world == 2) return run_emu<2>(rings, ops, build_embed_fwd, (cudaStream_t)stream);

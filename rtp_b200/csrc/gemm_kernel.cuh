@@ -7,7 +7,8 @@
 //   warp 6      pusher: copies this rank's home shard into a peer's workspace slot with bulk asynchronous copies (bulk
 //               load from local memory into a two-slot shared-memory ring, bulk store from there into the peer's memory
 //               over NVLink), bounded by the peer's slot-free counter, then bumps the peer's arrival counter
-//   warp 7      idle
+//   warp 7      signaller: release fence + "data arrived" signal of phases whose output goes to another rank, so that the
+//               epilogue warps never wait for their NVLink stores to be acknowledged
 //
 // All cross-rank waits are on 64-bit counters with an iteration/time limit; on expiry the CTA marks
 // the status word, drains what it has in flight, frees its TMEM and returns.
@@ -26,9 +27,15 @@ constexpr int kTmemCols = 512;
 constexpr int kNumThreads = 256;
 constexpr int kStagePitch = 144;                // bytes per staged output row: 64 bf16 + 16 pad (conflict-free 16 B writes)
 constexpr int kStagingBytes = 4 * 32 * kStagePitch;
-constexpr int kPushChunk = 7680;                // bytes per bulk copy of a push job (two ring slots per CTA)
+// Push rings.  A CTA that also runs GEMM tiles has a small ring of its own (its shared memory belongs to the tile
+// pipeline); a CTA reserved for pushing uses the idle tile pipeline's memory as a deep ring.
+constexpr int kPushChunk = 7680;                // small ring: bytes per bulk copy, two slots
 constexpr int kPushRingBytes = 2 * kPushChunk;
-constexpr int kSmemBytes = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kStagingBytes + kPushRingBytes;
+constexpr int kBigPushChunk = 16384;            // deep ring: 12 slots in the tile area
+constexpr int kMaxPushSlots = 12;
+static_assert(kMaxPushSlots * kBigPushChunk <= 196608, "deep push ring must fit the tile area");
+constexpr int kCtlBytes = 512;                  // barriers and CTA-wide words
+constexpr int kSmemBytes = kTileBytes + 1024 /*align slack*/ + kCtlBytes + kStagingBytes + kPushRingBytes;
 static_assert(kSmemBytes <= 232448, "over the 227 KB of shared memory a CTA can have");
 
 struct SmemCtrl {
@@ -38,12 +45,13 @@ struct SmemCtrl {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain;
-  uint64_t push_full[2];            // push ring: "the bulk load into slot s has landed"
+  uint64_t push_full[kMaxPushSlots];   // push ring: "the bulk load into slot s has landed"
   uint32_t tmem_base;
   uint32_t abort_flag;
+  uint32_t handed;                  // phases the epilogue warps have handed to the signaller warp
 };
 
-static_assert(sizeof(SmemCtrl) <= 256, "control block outgrew its shared-memory slot");
+static_assert(sizeof(SmemCtrl) <= kCtlBytes, "control block outgrew its shared-memory slot");
 
 // One rank per launch: the program travels as a kernel parameter.  Emulated ranks (several programs in one
 // cooperative launch on one GPU) read their programs from constant memory instead, which is large enough for four.
@@ -60,6 +68,146 @@ __device__ __forceinline__ unsigned long long fill_target(const RtpFlagBlock* fb
   return (fb->uses[ctr].v + (unsigned long long)(rel + plus)) * (unsigned long long)G;
 }
 
+// a slot may be written again once `uses + rel` of its fills have been read completely (credits count whole fills)
+__device__ __forceinline__ unsigned long long credit_target(const RtpFlagBlock* fb, int ctr, int rel) {
+  return fb->uses[ctr].v + (unsigned long long)rel;
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Push jobs of one CTA: its share (index / sharers) of every job moves through a ring of NS shared-memory slots with
+// bulk asynchronous copies: bulk load from local memory, then bulk store into the peer's slot over NVLink.  All chunks
+// of all jobs form one software pipeline: NS - 1 loads are in flight while stores leave; at most LAG + 1 stores are
+// outstanding, and a job is signalled ("data arrived") once its last store is complete.
+// ------------------------------------------------------------------------------------------------------------------
+struct PushCtx {
+  const RtpProgram* P;
+  int G, cta, index, sharers;
+  uint8_t* ring;
+  uint64_t* bars;
+  volatile uint32_t* abort_flag;
+  unsigned long long* status;
+  unsigned long long wait_ns, timeout_ns;
+};
+
+template <int NS, int CHUNK, int LAG>
+__device__ __noinline__ void run_pushes(const PushCtx& c) {
+  const RtpProgram& P = *c.P;
+  const uint32_t ring_s = smem_u32(c.ring);
+  const uint32_t pf_s = smem_u32(c.bars);
+  bool ok = true;
+  uint32_t ph_bits = 0;                 // parity of the next completion of every slot's barrier
+  // byte range of job j that this CTA moves
+  auto job_range = [&](int j, unsigned long long& lo, unsigned long long& hi) {
+    const unsigned long long units = P.pushes[j].bytes >> 4;
+    const unsigned long long per = (units + c.sharers - 1) / c.sharers;
+    lo = per * (unsigned long long)c.index;
+    hi = lo + per;
+    if (hi > units) hi = units;
+    if (lo > hi) lo = hi;
+    lo <<= 4; hi <<= 4;
+  };
+  auto signal_job = [&](int j) {
+    if (P.trace && c.cta == P.n_compute % c.G && j < 8) P.trace[3 * 256 + 200 + j * 4 + 3] = globaltimer_ns();
+    // the job's stores are complete: make them visible system-wide, then count this CTA in
+    fence_proxy_async();
+    __threadfence_system();
+    if (P.pushes[j].arrive_ptr) red_relaxed_sys_add(P.pushes[j].arrive_ptr, 1ull);
+    if (P.trace && c.cta == P.n_compute % c.G && j < 8) P.trace[3 * 256 + 200 + j * 4 + 2] = globaltimer_ns();
+  };
+  // chunk cursor of the loader
+  int lj = 0;
+  unsigned long long loff = 0, lhi = 0;
+  bool lvalid = false;
+  auto next_chunk = [&]() {
+    lvalid = false;
+    while (lj < P.n_pushes) {
+      if (loff < lhi) { lvalid = true; return; }
+      ++lj;
+      if (lj < P.n_pushes) job_range(lj, loff, lhi);
+    }
+  };
+  job_range(0, loff, lhi);
+  next_chunk();
+  // per ring slot: what was loaded there
+  uint32_t s_bytes[NS];
+  int s_job[NS];
+  unsigned long long s_off[NS];
+  bool s_start[NS], s_last[NS];
+  for (int i = 0; i < NS; ++i) s_job[i] = -1;
+  auto issue_load = [&](int s) {
+    const RtpPush& pu = P.pushes[lj];
+    const unsigned long long n = (lhi - loff) < (unsigned long long)CHUNK ? (lhi - loff) : (unsigned long long)CHUNK;
+    unsigned long long jlo, jhi;
+    job_range(lj, jlo, jhi);
+    s_bytes[s] = (uint32_t)n; s_job[s] = lj; s_off[s] = loff;
+    s_start[s] = loff == jlo; s_last[s] = loff + n == lhi;
+    mbar_arrive_expect_tx_s(pf_s + s * 8, (uint32_t)n);
+    bulk_load_s(ring_s + s * CHUNK, reinterpret_cast<const uint8_t*>(pu.src) + loff, (uint32_t)n, pf_s + s * 8);
+    loff += n;
+    next_chunk();
+  };
+  // jobs whose last store has been committed but not yet signalled, in commit order: (job, index of its last store)
+  int q_job[RTP_MAX_PUSHES], q_at[RTP_MAX_PUSHES];
+  int q_head = 0, q_tail = 0;
+  bool counted[RTP_MAX_PUSHES];
+  for (int j = 0; j < RTP_MAX_PUSHES; ++j) counted[j] = false;
+  int n_loaded = 0, n_stored = 0;
+  for (; n_loaded < NS - 1 && lvalid; ++n_loaded) issue_load(n_loaded % NS);
+  while (n_stored < n_loaded && ok) {
+    const int s = n_stored % NS;
+    const int j = s_job[s];
+    const RtpPush& pu = P.pushes[j];
+    if (s_start[s]) {
+      if (P.trace && c.cta == P.n_compute % c.G && j < 8) P.trace[3 * 256 + 200 + j * 4 + 0] = globaltimer_ns();
+      if (pu.credit_ptr && !wait_counter_ge(pu.credit_ptr, credit_target(P.flags, pu.credit_ctr, pu.credit_rel), c.abort_flag,
+                                            c.status, c.wait_ns, ST_TIMEOUT_CREDIT)) {
+        ok = false;
+        break;
+      }
+      if (P.trace && c.cta == P.n_compute % c.G && j < 8) P.trace[3 * 256 + 200 + j * 4 + 1] = globaltimer_ns();
+    }
+    // the load of this chunk has landed (a copy from local memory always completes; the limit guards a logic error)
+    if (!mbar_wait_s(pf_s + s * 8, (ph_bits >> s) & 1u, c.abort_flag, c.status, c.timeout_ns)) { ok = false; break; }
+    ph_bits ^= 1u << s;
+    s_job[s] = -1;
+    bulk_store_s(reinterpret_cast<uint8_t*>(pu.dst) + s_off[s], ring_s + s * CHUNK, s_bytes[s]);
+    bulk_commit();
+    if (s_last[s]) { q_job[q_tail] = j; q_at[q_tail] = n_stored; ++q_tail; }
+    ++n_stored;
+    // the store before this one has read its slot: that slot takes the next load
+    bulk_wait_read<1>();
+    if (lvalid) { issue_load(n_loaded % NS); ++n_loaded; }
+    // jobs whose last store is complete are announced
+    if (q_head < q_tail && q_at[q_head] < n_stored - LAG) {
+      bulk_wait<LAG>();
+      while (q_head < q_tail && q_at[q_head] < n_stored - LAG) {
+        signal_job(q_job[q_head]);
+        counted[q_job[q_head]] = true;
+        ++q_head;
+      }
+    }
+  }
+  bulk_wait<0>();
+  if (!ok) {
+    // loads may still be in flight into the ring: let them land before the CTA can exit
+    for (int s = 0; s < NS; ++s) {
+      if (s_job[s] < 0) continue;
+      const unsigned long long t0 = globaltimer_ns();
+      while (!mbar_try_wait(c.bars + s, (ph_bits >> s) & 1u)) {
+        if (globaltimer_ns() - t0 > 2000000ull) break;
+      }
+    }
+  }
+  while (q_head < q_tail) {
+    if (ok) signal_job(q_job[q_head]);
+    counted[q_job[q_head]] = true;
+    ++q_head;
+  }
+  // jobs in which this CTA had nothing to move
+  for (int j = 0; j < P.n_pushes && ok; ++j)
+    if (!counted[j] && P.pushes[j].arrive_ptr) red_relaxed_sys_add(P.pushes[j].arrive_ptr, 1ull);
+}
+
 // PAIR = true: launched with clusters of two CTAs; one UMMA (cta_group::2, M = 256) spans the pair.
 template <int NEMU, bool PAIR>
 __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_constant__ GemmParams<NEMU> params) {
@@ -73,7 +221,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemCtrl* ctl = reinterpret_cast<SmemCtrl*>(tiles + kTileBytes);
-  uint8_t* staging = tiles + kTileBytes + 256;
+  uint8_t* staging = tiles + kTileBytes + kCtlBytes;
   const int kStages = P.n_stages;          // uniform for the launch: set by the host from the widest tile
   const int kStageBytes = P.stage_bytes;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
@@ -85,7 +233,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
   const int lane = threadIdx.x & 31;
   // scheduling unit = CTA, or CTA pair; GU units per rank
   const int unit = PAIR ? (cta >> 1) : cta;
-  const int GU = PAIR ? (G >> 1) : G;
+  // CTAs [0, n_comp) own GEMM tiles; the rest (if any) are reserved for the push jobs of the launch
+  const int n_comp = (P.n_compute > 0 && P.n_compute < G) ? P.n_compute : G;
+  const bool tile_cta = cta < n_comp;
+  const int GU = PAIR ? (n_comp >> 1) : n_comp;
 
   pdl_launch_dependents();
 #define GEMM_STAMP(i) do { if (P.trace && cta == 0) P.trace[3 * 256 + 64 + (i)] = globaltimer_ns(); } while (0)
@@ -104,9 +255,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       }
     } else if (lane == kMaxStages + 2) {
       mbar_init(&ctl->drain, 1);
-      mbar_init(&ctl->push_full[0], 1);
-      mbar_init(&ctl->push_full[1], 1);
+      for (int i = 0; i < kMaxPushSlots; ++i) mbar_init(&ctl->push_full[i], 1);
       ctl->abort_flag = 0;
+      ctl->handed = 0;
     }
     mbar_fence_init();
   }
@@ -125,7 +276,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (elect_one()) {     // elect.sync, not lane == 0: lets the compiler treat the TMA operands as warp-uniform
+    if (tile_cta && elect_one()) {     // elect.sync, not lane == 0: lets the compiler treat the TMA operands as warp-uniform
       int stage = 0;
       uint32_t phase = 0;
       uint32_t issued_mask = 0, issued_parity = 0;   // bit s: stage s has been filled / parity of its last fill
@@ -142,8 +293,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const int per_batch = tiles_m * tiles_n;
         const int total = per_batch * ph.batch;
         if ((unit - ph.cta_off + GU) % GU >= total) continue;
+        const int nseg = ph.nseg > 1 ? ph.nseg : 1;
         bool any_wait = false;
-        for (int w = 0; w < RTP_MAX_WAITS && ok; ++w) {
+        for (int w = 0; w < RTP_MAX_WAITS && ok && nseg == 1; ++w) {
           if (ph.wait_ctr[w] >= 0) {
             any_wait = true;
             ok = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
@@ -153,8 +305,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         }
         if (!ok) break;
         if (any_wait) fence_proxy_async();
+        uint32_t seg_ready = 0;          // segments whose shard has been seen to have arrived
         const unsigned long long ma = reinterpret_cast<unsigned long long>(&P.maps[ph.a_map]);
-        const unsigned long long mb = reinterpret_cast<unsigned long long>(&P.maps[ph.b_map]);
+        unsigned long long mb = reinterpret_cast<unsigned long long>(&P.maps[ph.b_map]);
         const int kblocks_full = (ph.K + kBK - 1) / kBK;
         const int p_a_mn = ph.a_mn;
         const int p_b_mn = ph.b_mn;
@@ -185,7 +338,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const int b_dx = p_b_mn ? 0 : kBK, b_dy = p_b_mn ? kBK : 0;
         const int b_ix = p_b_mn ? 64 : 0, b_iy = p_b_mn ? 0 : ph.b_box;  // per box inside a stage
         const uint32_t b_ismem = p_b_mn ? 8192u : (uint32_t)ph.b_box * 128u;
-        const bool a3 = p_a_mn && P.map3d[ph.a_map], b3 = p_b_mn && P.map3d[ph.b_map];
+        const bool a3 = p_a_mn && P.map3d[ph.a_map];
+        bool b3 = p_b_mn && P.map3d[ph.b_map];
         if (p == 0) GEMM_STAMP(2);
         for (int t = (unit - p_cta_off + GU) % GU; t < total && ok; t += GU) {
           // unbatched phases (the common case) skip the divisions by the batch geometry
@@ -205,6 +359,25 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           int ax = (p_a_mn ? a_mn0 : a_k0) + kb0 * a_dx, ay = (p_a_mn ? a_k0 : a_mn0) + kb0 * a_dy;
           int bx = (p_b_mn ? b_mn0 : b_k0) + kb0 * b_dx, by = (p_b_mn ? b_k0 : b_mn0) + kb0 * b_dy;
           if (P.trace && cta == 0 && tr_n < 60) P.trace[0 * 256 + tr_n * 4 + 0] = globaltimer_ns();
+          for (int sg = 0; sg < nseg && ok; ++sg) {
+          if (nseg > 1) {
+            // next shard of the contraction: its own tensor map, A moves to the matching k-range
+            if (!((seg_ready >> sg) & 1u)) {
+              if (ph.wait_ctr[sg] >= 0) {
+                ok = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[sg]].v,
+                                     fill_target(P.flags, ph.wait_ctr[sg], ph.wait_rel[sg], 1, G), abort_flag, status,
+                                     wait_ns, ST_TIMEOUT_ARRIVAL);
+                if (!ok) break;
+                fence_proxy_async();
+              }
+              seg_ready |= 1u << sg;
+            }
+            mb = reinterpret_cast<unsigned long long>(&P.maps[ph.seg_b_map[sg]]);
+            b3 = p_b_mn && P.map3d[ph.seg_b_map[sg]];
+            const int ak = a_k0 + ph.seg_a_off_k[sg];
+            ax = p_a_mn ? a_mn0 : ak; ay = p_a_mn ? ak : a_mn0;
+            bx = p_b_mn ? b_mn0 : b_k0; by = p_b_mn ? b_k0 : b_mn0;
+          }
           for (int kb = kb0; kb < kblocks; ++kb) {
             if (!mbar_wait_s(empty_s + stage * 8, phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
             const uint32_t sa = tiles_s + stage * kStageBytes;
@@ -230,6 +403,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             ax += a_dx; ay += a_dy; bx += b_dx; by += b_dy;
             if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
+          }
           if (P.trace && cta == 0 && tr_n < 60) P.trace[0 * 256 + tr_n * 4 + 1] = globaltimer_ns();
           ++tr_n;
         }
@@ -249,7 +423,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
-    if (crank == 0 && elect_one()) {     // in a pair only the leader issues; its UMMAs drive both SMs
+    if (!tile_cta) {
+      // reserved for pushing: no tiles
+    } else if (crank == 0 && elect_one()) {     // in a pair only the leader issues; its UMMAs drive both SMs
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -278,7 +454,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           const int m0 = (tt - tn * tiles_m) * TM;
           const int n0 = tn * ph.bn;
           if (ph.causal == 1 && n0 > m0 + TM - 1) continue;
-          const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + TM + kBK - 1) / kBK) : kblocks_full;
+          const int kblocks = (ph.causal == 2 ? min(kblocks_full, (m0 + TM + kBK - 1) / kBK) : kblocks_full) *
+                              (ph.nseg > 1 ? ph.nseg : 1);      // K-segmented: the segments follow one another
           const int kb0 = ph.causal == 3 ? m0 / kBK : 0;
           if (P.trace && cta == 0 && tr_m < 60) P.trace[1 * 256 + tr_m * 4 + 0] = globaltimer_ns();
           if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort_flag, status, timeout_ns)) { ok = false; break; }
@@ -343,7 +520,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           const int m0 = (tt - tn * tiles_m) * TM;
           const int n0 = tn * ph.bn;
           if (ph.causal == 1 && n0 > m0 + TM - 1) continue;
-          const int kblocks = ph.causal == 2 ? min(kblocks_full, (m0 + TM + kBK - 1) / kBK) : kblocks_full;
+          const int kblocks = (ph.causal == 2 ? min(kblocks_full, (m0 + TM + kBK - 1) / kBK) : kblocks_full) *
+                              (ph.nseg > 1 ? ph.nseg : 1);
           const int kb0 = ph.causal == 3 ? m0 / kBK : 0;
           for (int kb = kb0; kb < kblocks; ++kb) {
             if (!mbar_wait_s(full_s + stage * 8, phase, abort_flag, status, timeout_ns)) { ok = false; break; }
@@ -361,8 +539,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
     uint32_t acc_phase = 0;
     bool ok = true;
     int tr_e = 0;
-    unsigned long long* pending_arrive[RTP_NUM_SLOTS];   // deferred "data arrived" signals of earlier phases
-    int n_pending = 0;
     for (int p = 0; p < P.n_phases; ++p) {
       const RtpPhase& ph = P.phases[p];
       const int tiles_m = (ph.M + TM - 1) / TM;
@@ -375,18 +551,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const bool does_vec = (ph.vec_out != nullptr) && cta == 0;
       (void)has_tiles;
       if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 0] = globaltimer_ns();
-      if (n_pending > 0) {
-        // A phase that waits for other ranks must not sit on undelivered signals (they may be what the others wait for).
-        bool waits = ph.credit_ptr != nullptr;
-        for (int w = 0; w < RTP_MAX_WAITS; ++w) waits = waits || ph.wait_ctr[w] >= 0;
-        if (waits && ph.kind == RTP_KIND_REDUCE) {
-          if (epi_tid == 0 && ok) {
-            __threadfence_system();
-            for (int k = 0; k < n_pending; ++k) red_relaxed_sys_add(pending_arrive[k], 1ull);
-          }
-          n_pending = 0;
-        }
-      }
       if (ok) {
         // Operands of the accumulate / bias reads must have arrived and the destination slot must be free.
         // A CTA without tiles waits too: the counters only mean "every CTA is past fill u" if no CTA
@@ -399,7 +563,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
                                      fill_target(P.flags, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
                                      wait_ns, ST_TIMEOUT_ARRIVAL);
           if (good && ph.credit_ptr)
-            good = wait_counter_ge(ph.credit_ptr, fill_target(P.flags, ph.credit_ctr, ph.credit_rel, 0, G),
+            good = wait_counter_ge(ph.credit_ptr, credit_target(P.flags, ph.credit_ctr, ph.credit_rel),
                                    abort_flag, status, wait_ns, ST_TIMEOUT_CREDIT);
         }
         good = __shfl_sync(0xffffffffu, good, 0);
@@ -503,6 +667,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const long long e_ldc = ph.ldc;
       const int e_c_fp32 = ph.c_fp32;
       const const void* e_bias = ph.bias;
+      const int e_nbias_more = ph.n_bias_more;
       const int e_act = ph.act;
       const const void* e_mask = ph.mask;
       const long long e_ldmask = ph.ldmask;
@@ -522,9 +687,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const long long e_c_bi = ph.c_bi;
       const int e_cta_off = ph.cta_off;
       // vector accesses of the straight-line path: operands 16-byte aligned (vec_ok), bias too, dropout index a multiple of 4
-      const bool e_fast_ok = e_vec_ok && (!e_bias || (reinterpret_cast<uintptr_t>(e_bias) & 15) == 0) &&
-                             (!e_drop_thresh || (e_N & 3) == 0);
-      for (int t = (unit - e_cta_off + GU) % GU; t < total && ok; t += GU) {
+      bool e_bias_al = !e_bias || (reinterpret_cast<uintptr_t>(e_bias) & 15) == 0;
+      for (int nb = 0; nb < e_nbias_more; ++nb) e_bias_al = e_bias_al && (reinterpret_cast<uintptr_t>(ph.bias_more[nb]) & 15) == 0;
+      const bool e_fast_ok = e_vec_ok && e_bias_al && (!e_drop_thresh || (e_N & 3) == 0);
+      for (int t = tile_cta ? (unit - e_cta_off + GU) % GU : total; t < total && ok; t += GU) {
         const bool e_batch1 = e_batch_inner == 1 && per_batch == total;
         const int z = e_batch1 ? 0 : t / per_batch, tt = e_batch1 ? t : t - z * per_batch;
         const int tn = tt / tiles_m;
@@ -585,13 +751,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
               }
             }
             if (e_bias) {
-              const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e_bias) + col0);
+              for (int nb = 0; nb <= e_nbias_more; ++nb) {
+                const void* bsrc = nb == 0 ? e_bias : ph.bias_more[nb - 1];
+                const uint4* bp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bsrc) + col0);
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint4 b = __ldcg(bp + q);
-                v[8 * q] += bf16_lo(b.x); v[8 * q + 1] += bf16_hi(b.x); v[8 * q + 2] += bf16_lo(b.y);
-                v[8 * q + 3] += bf16_hi(b.y); v[8 * q + 4] += bf16_lo(b.z); v[8 * q + 5] += bf16_hi(b.z);
-                v[8 * q + 6] += bf16_lo(b.w); v[8 * q + 7] += bf16_hi(b.w);
+                for (int q = 0; q < 4; ++q) {
+                  const uint4 b = __ldcg(bp + q);
+                  v[8 * q] += bf16_lo(b.x); v[8 * q + 1] += bf16_hi(b.x); v[8 * q + 2] += bf16_lo(b.y);
+                  v[8 * q + 3] += bf16_hi(b.y); v[8 * q + 4] += bf16_lo(b.z); v[8 * q + 5] += bf16_hi(b.z);
+                  v[8 * q + 6] += bf16_lo(b.w); v[8 * q + 7] += bf16_hi(b.w);
+                }
               }
             }
             if (e_act == 1) {
@@ -673,13 +842,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
               }
             }
             if (e_bias) {
-              const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(e_bias) + col;
-              if (nvalid == 8 && (reinterpret_cast<uintptr_t>(bp) & 15) == 0) {
-                const uint4 b = __ldcg(reinterpret_cast<const uint4*>(bp));   // one 16-byte load for 8 columns
-                v[0] += bf16_lo(b.x); v[1] += bf16_hi(b.x); v[2] += bf16_lo(b.y); v[3] += bf16_hi(b.y);
-                v[4] += bf16_lo(b.z); v[5] += bf16_hi(b.z); v[6] += bf16_lo(b.w); v[7] += bf16_hi(b.w);
-              } else {
-                for (int i = 0; i < nvalid; ++i) v[i] += __bfloat162float(__ldcg(bp + i));
+              for (int nb = 0; nb <= e_nbias_more; ++nb) {
+                const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(nb == 0 ? e_bias : ph.bias_more[nb - 1]) + col;
+                if (nvalid == 8 && (reinterpret_cast<uintptr_t>(bp) & 15) == 0) {
+                  const uint4 b = __ldcg(reinterpret_cast<const uint4*>(bp));   // one 16-byte load for 8 columns
+                  v[0] += bf16_lo(b.x); v[1] += bf16_hi(b.x); v[2] += bf16_lo(b.y); v[3] += bf16_hi(b.y);
+                  v[4] += bf16_lo(b.z); v[5] += bf16_hi(b.z); v[6] += bf16_lo(b.w); v[7] += bf16_hi(b.w);
+                } else {
+                  for (int i = 0; i < nvalid; ++i) v[i] += __bfloat162float(__ldcg(bp + i));
+                }
               }
             }
             if (e_act == 1) {
@@ -790,148 +961,87 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       }
       if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 2] = globaltimer_ns();
       // phase end: publish "read done" / "data arrived". Every CTA signals, also one without tiles.
-      const bool defer = ph.arrive_ptr != nullptr && ph.arrive_defer && p + 1 < P.n_phases && n_pending < RTP_NUM_SLOTS;
-      bool signals = ph.arrive_ptr != nullptr || (n_pending > 0 && !defer);
+      bool signals = ph.arrive_ptr != nullptr;
       for (int w = 0; w < RTP_MAX_WAITS; ++w) signals = signals || ph.done_ctr[w] >= 0;
       if (signals) {
-        // All four epilogue warps are through with the phase.  The barrier also orders their stores before the fence of
-        // the signalling thread below (a release is cumulative over what the thread has synchronised with).
+        // All four epilogue warps are through with the phase.
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (epi_tid == 0 && ok) {
-          // "read done": the operands have been consumed, nothing written by this CTA has to be visible first
+        // "read done": the operands have been consumed, nothing written by this CTA has to be visible first
+        // The CTA that completes the count of a fill (every CTA reports once per fill) tells all other ranks: whoever
+        // writes this slot next finds the credit in its own memory.
+        if (epi_tid == 0 && ok)
           for (int w = 0; w < RTP_MAX_WAITS; ++w)
-            if (ph.done_ctr[w] >= 0) red_relaxed_sys_add(&P.flags->done[ph.done_ctr[w]].v, 1ull);
-          // "data arrived": the tiles stored by this CTA (possibly into a peer's memory) come first.  Deferred signals
-          // wait for the first later phase that does not defer: their stores have had that long to complete, so the
-          // one release fence for all of them is cheap.
-          if (!defer && (n_pending > 0 || ph.arrive_ptr)) {
-            __threadfence_system();
-            for (int k = 0; k < n_pending; ++k) red_relaxed_sys_add(pending_arrive[k], 1ull);
-            if (ph.arrive_ptr) red_relaxed_sys_add(ph.arrive_ptr, 1ull);
-          }
+            if (ph.done_ctr[w] >= 0) {
+              const int c = ph.done_ctr[w];
+              const unsigned long long old = atomicAdd(&P.flags->done[c].v, 1ull);
+              if ((old + 1ull) % (unsigned long long)G == 0ull)
+                for (int t = 0; t < P.world; ++t)     // this rank included: it may be the next writer of its own slot
+                  red_relaxed_sys_add(&P.peer_flags[t]->credit[P.rank][c].v, 1ull);
+            }
+        // "data arrived": the tiles stored by this CTA (possibly into a peer's memory) must be visible first.  Waiting
+        // for the NVLink stores to be acknowledged costs microseconds, so the release fence and the signal are handed
+        // to the signaller warp through a CTA-wide counter (a counter, not a barrier: this warp may be several phases
+        // ahead of the signaller).  The chain "stores of the four warps -> bar.sync 1 -> release of the counter ->
+        // acquire by the signaller" orders them before its fence.
+        if (ph.arrive_ptr && epi_tid == 0) {
+          __threadfence_block();
+          atomicAdd(&ctl->handed, 1u);
         }
-        if (defer) pending_arrive[n_pending++] = ph.arrive_ptr; else n_pending = 0;
       }
       if (P.trace && cta == 0 && warp == 2 && lane == 0 && p < 16) P.trace[3 * 256 + 128 + p * 4 + 3] = globaltimer_ns();
     }
   } else if (warp == 6) {
     // ------------------------------------------------------------------ pusher (one elected thread)
-    // Every CTA moves its 1/G of each push job.  The chunks of all jobs form one software pipeline: while the bulk
-    // store of chunk c leaves for the peer, the bulk load of chunk c + 1 is already in flight; at most two stores are
-    // outstanding per CTA, which across the grid keeps a few megabytes on the link.
-    if (elect_one()) {
-      uint8_t* ring = staging + kStagingBytes;
-      const uint32_t ring_s = smem_u32(ring);
-      const uint32_t pf_s = smem_u32(&ctl->push_full[0]);
-      bool ok = true;
-      uint32_t ph[2] = {0u, 0u};
-      int slot = 0;
-      int sig_job = -1;                // job whose last store is the most recent committed group (signalled one group later)
-      // next chunk to load
-      int lj = 0;
-      unsigned long long loff = 0, lhi = 0;
-      bool lvalid = false;
-      auto job_range = [&](int j, unsigned long long& lo, unsigned long long& hi) {
-        const unsigned long long units = P.pushes[j].bytes >> 4;
-        const unsigned long long per = (units + G - 1) / G;
-        lo = per * (unsigned long long)cta;
-        hi = lo + per;
-        if (hi > units) hi = units;
-        if (lo > hi) lo = hi;
-        lo <<= 4; hi <<= 4;
-      };
-      auto signal_job = [&](int j) {
-        // the job's stores are complete (bulk_wait): make them visible system-wide, then count this CTA in
-        fence_proxy_async();
-        __threadfence_system();
-        if (P.pushes[j].arrive_ptr) red_relaxed_sys_add(P.pushes[j].arrive_ptr, 1ull);
-        if (P.trace && cta == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 2] = globaltimer_ns();
-      };
-      // advance (lj, loff) to the next non-empty chunk; jobs without bytes for this CTA are signalled right away
-      auto next_chunk = [&]() {
-        lvalid = false;
-        while (lj < P.n_pushes) {
-          if (loff < lhi) { lvalid = true; return; }
-          ++lj;
-          if (lj < P.n_pushes) job_range(lj, loff, lhi);
+    // CTAs [n_compute, G) are reserved for pushing when the program has push jobs: they own no GEMM tile, so their copy
+    // engine is not shared with a tile pipeline and their tile memory serves as a deep ring.  Without reserved CTAs
+    // every CTA moves 1/G of each job through its small ring.
+    if (elect_one() && P.n_pushes > 0) {
+      const int n_comp = P.n_compute > 0 ? P.n_compute : G;
+      PushCtx pc;
+      pc.P = &P; pc.G = G; pc.cta = cta;
+      pc.abort_flag = abort_flag; pc.status = status; pc.wait_ns = wait_ns; pc.timeout_ns = timeout_ns;
+      pc.bars = &ctl->push_full[0];
+      if (n_comp < G) {
+        if (cta < n_comp) {
+          // nothing to move: count this CTA in for every fill right away (the fill is complete only when the CTAs that
+          // do write have counted themselves in, after their stores)
+          for (int j = 0; j < P.n_pushes; ++j)
+            if (P.pushes[j].arrive_ptr) red_relaxed_sys_add(P.pushes[j].arrive_ptr, 1ull);
+        } else {
+          pc.ring = tiles; pc.index = cta - n_comp; pc.sharers = G - n_comp;
+          run_pushes<kMaxPushSlots, kBigPushChunk, 6>(pc);
         }
-      };
-      if (P.n_pushes > 0) { job_range(0, loff, lhi); next_chunk(); }
-      // jobs that are empty for this CTA still count it in (the counters mean "every CTA is past this fill")
-      bool counted[RTP_MAX_PUSHES];
-      for (int j = 0; j < RTP_MAX_PUSHES; ++j) counted[j] = false;
-      uint32_t lbytes[2] = {0u, 0u};
-      int ljob[2] = {-1, -1};
-      unsigned long long loffs[2] = {0ull, 0ull};
-      bool lstart[2] = {false, false}, llast[2] = {false, false};
-      auto issue_load = [&](int s) {
-        const RtpPush& pu = P.pushes[lj];
-        const unsigned long long n = (lhi - loff) < (unsigned long long)kPushChunk ? (lhi - loff) : (unsigned long long)kPushChunk;
-        unsigned long long jlo, jhi;
-        job_range(lj, jlo, jhi);
-        lbytes[s] = (uint32_t)n; ljob[s] = lj; loffs[s] = loff;
-        lstart[s] = loff == jlo; llast[s] = loff + n == lhi;
-        mbar_arrive_expect_tx_s(pf_s + s * 8, (uint32_t)n);
-        bulk_load_s(ring_s + s * kPushChunk, reinterpret_cast<const uint8_t*>(pu.src) + loff, (uint32_t)n, pf_s + s * 8);
-        loff += n;
-        next_chunk();
-      };
-      if (lvalid) issue_load(0);
-      bool have = ljob[0] >= 0;
-      while (have && ok) {
-        const int s = slot;
-        const int j = ljob[s];
-        const RtpPush& pu = P.pushes[j];
-        if (lstart[s]) {
-          if (P.trace && cta == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 0] = globaltimer_ns();
-          if (pu.credit_ptr &&
-              !wait_counter_ge(pu.credit_ptr, fill_target(P.flags, pu.credit_ctr, pu.credit_rel, 0, G), abort_flag,
-                               status, wait_ns, ST_TIMEOUT_CREDIT)) {
-            ok = false;
-            break;
-          }
-          if (P.trace && cta == 0 && j < 8) P.trace[3 * 256 + 200 + j * 4 + 1] = globaltimer_ns();
-        }
-        // the load of this chunk has landed (a copy from local memory always completes; the limit guards a logic error)
-        if (!mbar_wait_s(pf_s + s * 8, ph[s], abort_flag, status, timeout_ns)) { ok = false; break; }
-        ph[s] ^= 1u;
-        ljob[s] = -1;
-        bulk_store_s(reinterpret_cast<uint8_t*>(pu.dst) + loffs[s], ring_s + s * kPushChunk, lbytes[s]);
-        bulk_commit();
-        // the previous store has read its slot: the next load may go there while this store is on the link
-        bulk_wait_read<1>();
-        have = false;
-        if (lvalid) { issue_load(s ^ 1); have = true; }
-        // a job that ended with the previous store is signalled once that store is complete
-        if (sig_job >= 0) {
-          bulk_wait<1>();
-          signal_job(sig_job);
-          counted[sig_job] = true;
-          sig_job = -1;
-        }
-        if (llast[s]) sig_job = j;
-        slot ^= 1;
+      } else {
+        pc.ring = staging + kStagingBytes; pc.index = cta; pc.sharers = G;
+        run_pushes<2, kPushChunk, 1>(pc);
       }
-      bulk_wait<0>();
-      if (!ok) {
-        // loads may still be in flight into the ring: let them land before the CTA can exit
-        for (int s = 0; s < 2; ++s) {
-          if (ljob[s] < 0) continue;
-          const unsigned long long t0 = globaltimer_ns();
-          while (!mbar_try_wait(&ctl->push_full[s], ph[s])) {
-            if (globaltimer_ns() - t0 > 2000000ull) break;
-          }
+    }
+  }
+  else if (warp == 7) {
+    // ------------------------------------------------------------------ signaller
+    // For every phase that announces its output to another rank: wait until the epilogue warps have handed the phase
+    // over, issue ONE cumulative system-scope release fence (it completes when the CTA's stores, NVLink ones included,
+    // have been acknowledged) and bump the consumer's arrival counter.  The epilogue warps are already at work on the
+    // next phase meanwhile.
+    if (lane == 0) {
+      uint32_t want = 0;
+      for (int p = 0; p < P.n_phases; ++p) {
+        unsigned long long* ap = P.phases[p].arrive_ptr;
+        if (!ap) continue;
+        ++want;
+        // bounded: the epilogue warps hand every such phase over, also after an abort
+        const unsigned long long t0 = globaltimer_ns();
+        bool got = true;
+        while (*reinterpret_cast<volatile uint32_t*>(&ctl->handed) < want) {
+          if (globaltimer_ns() - t0 > 2 * timeout_ns) { got = false; break; }
+          __nanosleep(32);
         }
-      }
-      if (sig_job >= 0) { if (ok) signal_job(sig_job); counted[sig_job] = true; }
-      // jobs in which this CTA had nothing to move
-      for (int j = 0; j < P.n_pushes; ++j) {
-        if (counted[j] || !ok) continue;
-        const RtpPush& pu = P.pushes[j];
-        if (pu.credit_ptr &&
-            !wait_counter_ge(pu.credit_ptr, fill_target(P.flags, pu.credit_ctr, pu.credit_rel, 0, G), abort_flag, status,
-                             wait_ns, ST_TIMEOUT_CREDIT)) { ok = false; break; }
-        if (pu.arrive_ptr) red_relaxed_sys_add(pu.arrive_ptr, 1ull);
+        if (!got) break;
+        __threadfence_block();
+        if (!*abort_flag) {
+          __threadfence_system();
+          red_relaxed_sys_add(ap, 1ull);
+        }
       }
     }
   }

@@ -20,7 +20,8 @@
 #define RTP_CTR_W0 0
 #define RTP_CTR_G0 (RTP_NUM_WBANKS * RTP_NUM_SLOTS)
 #define RTP_NUM_CTR (RTP_CTR_G0 + RTP_NUM_SLOTS)
-#define RTP_FLAG_BYTES 16384       // bytes reserved for the flag block at the start of a workspace
+#define RTP_FLAG_BYTES 65536       // bytes reserved for the flag block at the start of a workspace
+#define RTP_FLAG_MAX_WORLD 8
 #define RTP_MAX_WAITS 8
 
 // Per-rank flag block (peer-mapped). Every word sits in its own 128-byte line.
@@ -30,8 +31,12 @@ struct alignas(128) RtpFlagWord {
 };
 struct RtpFlagBlock {
   RtpFlagWord arrive[RTP_NUM_CTR];  // bumped by the producer's CTAs after their stores into the slot
-  RtpFlagWord done[RTP_NUM_CTR];    // bumped by this rank's CTAs once they finished reading the slot
+  RtpFlagWord done[RTP_NUM_CTR];    // bumped (locally) by this rank's CTAs once they finished reading the slot
   RtpFlagWord uses[RTP_NUM_CTR];    // number of completed fills of the slot (same on every rank)
+  // credit[t][c]: how many fills of slot c of RANK t have been read completely.  Written by rank t (the CTA that
+  // completes a fill's `done` count tells every other rank), read by whoever wants to write that slot next: a producer
+  // polls its OWN memory, never a peer's (a load from peer memory is an NVLink round trip of microseconds).
+  RtpFlagWord credit[RTP_FLAG_MAX_WORLD][RTP_NUM_CTR];
   RtpFlagWord done_ctas;            // CTAs of the running launch that have finished
   RtpFlagWord status;               // 0 = ok, else first error code
 };
@@ -62,6 +67,12 @@ struct RtpPhase {
   int b_off_mn, b_off_k;
   int a_bo_mn, a_bo_k, a_bi_mn, a_bi_k;
   int b_bo_mn, b_bo_k, b_bi_mn, b_bi_k;
+  // K-segmented phase (nseg > 1): the contraction runs over nseg segments of K elements each; segment i reads A at
+  // k-offset seg_a_off_k[i] and B through tensor map seg_b_map[i] (from k = 0), after local arrival counter wait_ctr[i]
+  // (if >= 0).  One accumulator, one epilogue: a sum over visiting weight shards needs no read-modify-write of D.
+  int nseg;
+  int seg_a_off_k[RTP_MAX_WAITS];
+  int seg_b_map[RTP_MAX_WAITS];
   // synchronisation (all optional)
   int wait_ctr[RTP_MAX_WAITS];  // local arrival counters that must reach fill (uses + rel + 1) before operands are read
   int wait_rel[RTP_MAX_WAITS];
@@ -71,6 +82,8 @@ struct RtpPhase {
   const void* c;  // optional accumulate source (same shape as d)
   long long ldc;
   const void* bias;    // optional bf16[N]
+  const void* bias_more[RTP_MAX_WAITS - 1];  // further bias vectors added on top (K-segmented row-mode forward: one per shard)
+  int n_bias_more;
   const void* mask;    // optional bf16 [M, N]: out = mask > 0 ? out * mask_scale : 0
   long long ldmask;
   int d_fp32;
@@ -84,13 +97,11 @@ struct RtpPhase {
   unsigned long long drop_seed, drop_offset;
   const unsigned long long* drop_step_ptr;  // optional device counter: offset += *ptr * 65536 (graph replays get fresh masks)
   long long d_bo, d_bi, c_bo, c_bi;
-  unsigned long long* credit_ptr;  // remote `done` counter that must reach fill (uses + rel) before d is written
+  unsigned long long* credit_ptr;  // local credit counter of the destination (rank, slot): must reach uses + rel before d is written
   int credit_ctr;
   int credit_rel;
   int done_ctr[RTP_MAX_WAITS];     // local `done` counters bumped when this CTA has finished the phase
   unsigned long long* arrive_ptr;  // remote `arrive` counter bumped when this CTA has finished the phase
-  int arrive_defer;  // 1: the arrive signal may wait until the end of the next phase (its consumer is a final reduce), so
-                     // that the release fence finds the stores of this phase, often into a peer's memory, already done
   // optional vector job done by CTA 0 at the end of the phase: vec_out[i] = vec_in[i] + vec_add[i] (bf16/fp32 per flags)
   void* vec_out;
   const void* vec_in;
@@ -118,7 +129,7 @@ struct RtpPush {
   const void* src;
   void* dst;  // peer memory
   unsigned long long bytes;  // multiple of 16
-  unsigned long long* credit_ptr;  // remote `done` counter of the destination slot
+  unsigned long long* credit_ptr;  // local credit counter of the destination (rank, slot)
   int credit_ctr;
   int credit_rel;
   unsigned long long* arrive_ptr;  // remote `arrive` counter of the destination slot
@@ -127,7 +138,10 @@ struct RtpPush {
 struct alignas(64) RtpProgram {
   int n_phases, n_pushes;
   int n_stages, stage_bytes;  // smem pipeline geometry (host: finalize_program)
+  int n_compute;              // CTAs [0, n_compute) run GEMM tiles, [n_compute, grid) only push (0 / grid: none reserved)
   RtpFlagBlock* flags;  // this rank's flag block (may be null when nothing synchronises)
+  RtpFlagBlock* peer_flags[RTP_FLAG_MAX_WORLD];  // every rank's flag block as mapped here (credits are written there)
+  int rank, world;
   unsigned long long* status;  // status word (flags->status or a plain device word)
   unsigned long long timeout_ns;
   unsigned long long* trace;  // optional debug timeline of CTA 0: [role][tile][event] globaltimer stamps (see gemm_kernel.cuh)

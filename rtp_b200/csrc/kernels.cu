@@ -381,10 +381,12 @@ __global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ table, const 
   }
 }
 // Scatter-add of the output gradient into a (zeroed or incoming) table-shard gradient [V, Ds].
+// blk_cols > 0: gtable is block-major, [Ds / blk_cols][V][blk_cols] (one contiguous [V, blk_cols] block per owner of an
+// embedding-dim shard); blk_cols = 0: plain [V, Ds].
 __global__ void embed_bwd_kernel(__nv_bfloat16* __restrict__ gtable, const long long* __restrict__ ids,
                                  const __nv_bfloat16* __restrict__ dy, long long ld_dy, int col_off, int T, int Ds,
                                  int D, float scale, uint32_t thresh, float drop_scale, uint64_t seed, uint64_t offset,
-                                 const unsigned long long* __restrict__ step_ptr) {
+                                 const unsigned long long* __restrict__ step_ptr, int blk_cols, int V) {
   if (step_ptr) offset += __ldg(step_ptr) * 65536ull;
   const int per_row = Ds / 8;
   const long long total = (long long)T * per_row;
@@ -398,7 +400,9 @@ __global__ void embed_bwd_kernel(__nv_bfloat16* __restrict__ gtable, const long 
 #pragma unroll
       for (int k = 0; k < 8; ++k) v[k] = kp[k] ? v[k] * drop_scale : 0.f;
     }
-    __nv_bfloat162* g = reinterpret_cast<__nv_bfloat162*>(gtable + (size_t)ids[t] * Ds + c);
+    __nv_bfloat162* g = blk_cols > 0
+        ? reinterpret_cast<__nv_bfloat162*>(gtable + ((size_t)(c / blk_cols) * V + (size_t)ids[t]) * blk_cols + (c % blk_cols))
+        : reinterpret_cast<__nv_bfloat162*>(gtable + (size_t)ids[t] * Ds + c);
 #pragma unroll
     for (int k = 0; k < 4; ++k) atomicAdd(g + k, __floats2bfloat162_rn(v[2 * k] * scale, v[2 * k + 1] * scale));
   }
@@ -1108,14 +1112,22 @@ int rtp_embed_fwd(const void* table, const long long* ids, const void* pe, long 
 int rtp_embed_bwd(void* gtable, const long long* ids, const void* dy, long long ld_dy, int col_off, int T, int Ds,
                   int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset,
                   const unsigned long long* step_ptr, void* stream) {
-  if (Ds % 8 || col_off % 8 || ld_dy % 8) { k_err = "embed: widths must be multiples of 8"; return -1; }
+  return rtp_embed_bwd_blocks(gtable, ids, dy, ld_dy, col_off, T, Ds, D, scale, drop_p, seed, offset, step_ptr, 0, 0, stream);
+}
+int rtp_embed_bwd_blocks(void* gtable, const long long* ids, const void* dy, long long ld_dy, int col_off, int T, int Ds,
+                         int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset,
+                         const unsigned long long* step_ptr, int blk_cols, int V, void* stream) {
+  if (Ds % 8 || col_off % 8 || ld_dy % 8 || blk_cols % 8 || (blk_cols > 0 && Ds % blk_cols)) {
+    k_err = "embed: widths must be multiples of 8";
+    return -1;
+  }
   const long long total = (long long)T * (Ds / 8);
   int grid = (int)((total + 255) / 256);
   if (grid > 148 * 16) grid = 148 * 16;
   const float ds = drop_p > 0.f ? 1.f / (1.f - drop_p) : 1.f;
   embed_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)gtable, ids, (const __nv_bfloat16*)dy, ld_dy,
                                                            col_off, T, Ds, D, scale, host_thresh(drop_p), ds, seed,
-                                                           offset, step_ptr);
+                                                           offset, step_ptr, blk_cols, V);
   LAUNCH_CHECK("embed_bwd");
   return 0;
 }

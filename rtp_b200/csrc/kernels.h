@@ -35,6 +35,11 @@ int rtp_embed_fwd(const void* table, const long long* ids, const void* pe, long 
 int rtp_embed_bwd(void* gtable, const long long* ids, const void* dy, long long ld_dy, int col_off, int T, int Ds,
                   int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset,
                   const unsigned long long* step_ptr, void* stream);
+// Same scatter-add into a block-major gradient [Ds / blk_cols][V][blk_cols]: one contiguous [V, blk_cols] block per owner
+// of an embedding-dim shard, ready to be pushed to that owner.
+int rtp_embed_bwd_blocks(void* gtable, const long long* ids, const void* dy, long long ld_dy, int col_off, int T, int Ds,
+                         int D, float scale, float drop_p, unsigned long long seed, unsigned long long offset,
+                         const unsigned long long* step_ptr, int blk_cols, int V, void* stream);
 // Tensor-core (tcgen05) kernels for S = 32 / 64, head_dim 64 (attn_tc.cu); rtp_attn_small_* route to them when they
 // apply.  rtp_set_attn_tc(0) forces the scalar kernels (A/B comparison).
 int rtp_attn_tc_supported(int S, int heads, int nshard);

@@ -12,7 +12,7 @@
 //
 // Limits and rules:
 //   * out_features <= RTP_NOALLOC_MAX_OUT_FEATURES, else the call fails with a clear error and launches nothing.
-//     The array costs RTP_NOALLOC_SCRATCH_BYTES (about 264 KB) of device memory on every GPU that loads the
+//     The array costs RTP_NOALLOC_SCRATCH_BYTES (320 KB) of device memory on every GPU that loads the
 //     library, from load until the process exits.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, cached per device) and
 //     raises the kernel's shared-memory limit on that device (also kept per device).  Make that first call before
@@ -33,7 +33,7 @@ extern "C" {
 #endif
 
 #define RTP_NOALLOC_MAX_OUT_FEATURES 65536
-#define RTP_NOALLOC_SCRATCH_BYTES (16384 + 4 * RTP_NOALLOC_MAX_OUT_FEATURES)   /* flag block (RTP_FLAG_BYTES) + column sums */
+#define RTP_NOALLOC_SCRATCH_BYTES (65536 + 4 * RTP_NOALLOC_MAX_OUT_FEATURES)   /* flag block (RTP_FLAG_BYTES) + column sums */
 
 int rtp_linear_bwd_noalloc(const void* x, long long ldx, const void* dy, long long ldy, const void* w,
                            long long bias_off, int M, int in_features, int out_features, void* dx, long long lddx,

@@ -153,6 +153,8 @@ class FusedLMTrainer:
         for k, p in enumerate(self.ln_params):
             add(p, self.ln_grad16[k * D:(k + 1) * D])
         self.adam_entries = entries
+        by_ptr = {p.data_ptr(): n for n, p in self.model.named_parameters()}
+        self._entry_names = {e[0].data_ptr(): by_ptr[e[0].data_ptr()] for e in entries}
         self.plan = K.AdamPlan(entries, self.dev)
 
     # ------------------------------------------------------------------------------------------
@@ -164,14 +166,18 @@ class FusedLMTrainer:
         st["tgt"] = torch.zeros(S, B, dtype=torch.int64, device=dev)
         st["x0"] = torch.empty(M, D, dtype=bf, device=dev)
         acts = []
+        slabs = []
         for _ in range(self.L):
-            a = dict(qkv=torch.empty(M, 3 * D, dtype=bf, device=dev), ctx=torch.empty(M, D, dtype=bf, device=dev),
-                     sa=torch.empty(M, D, dtype=bf, device=dev), h1=torch.empty(M, D, dtype=bf, device=dev),
-                     x1=torch.empty(M, D, dtype=bf, device=dev), a1=torch.empty(M, H, dtype=bf, device=dev),
-                     f=torch.empty(M, D, dtype=bf, device=dev), h2=torch.empty(M, D, dtype=bf, device=dev),
-                     x2=torch.empty(M, D, dtype=bf, device=dev),
-                     mean1=torch.empty(M, dtype=torch.float32, device=dev), rstd1=torch.empty(M, dtype=torch.float32, device=dev),
-                     mean2=torch.empty(M, dtype=torch.float32, device=dev), rstd2=torch.empty(M, dtype=torch.float32, device=dev))
+            # all bf16 activations of a layer come out of one slab, so that a dead layer's memory can be lent out whole
+            sizes = dict(qkv=3 * D, ctx=D, sa=D, h1=D, x1=D, a1=H, f=D, h2=D, x2=D)
+            slab = torch.empty(M * sum(sizes.values()), dtype=bf, device=dev)
+            slabs.append(slab)
+            a, off = {}, 0
+            for name, w in sizes.items():
+                a[name] = slab[off:off + M * w].view(M, w)
+                off += M * w
+            for name in ("mean1", "rstd1", "mean2", "rstd2"):
+                a[name] = torch.empty(M, dtype=torch.float32, device=dev)
             acts.append(a)
         st["acts"] = acts
         st["logits"] = torch.empty(M, V, dtype=bf, device=dev)
@@ -186,7 +192,11 @@ class FusedLMTrainer:
         st["dqkv"] = torch.empty(M, 3 * D, dtype=bf, device=dev)
         st["dbias"] = torch.empty(max(3 * D, V, H), dtype=torch.float32, device=dev)
         if self.N > 1:
-            st["emb_dense"] = torch.empty(V, D, dtype=bf, device=dev)
+            # Block-major scatter buffer of the embedding gradient ([N, V, D/N]).  It is only alive after the backward of
+            # every layer, so it lives on top of the activations of the LAST layer (whose backward ran first).
+            need = V * D
+            buf = slabs[-1][:need] if slabs[-1].numel() >= need else torch.empty(need, dtype=bf, device=dev)
+            st["emb_dense"] = buf.view(self.N, V, D // self.N)
         return st
 
     # ------------------------------------------------------------------------------------------
@@ -350,6 +360,29 @@ class FusedLMTrainer:
             self._graph = g
         self._graph.replay()
         return st["loss"]
+
+    # ------------------------------------------------------------------------------------------
+    def state_dict(self):
+        """Optimizer side of a checkpoint: Adam moments of every parameter (keyed by parameter name), the Adam step and
+        the dropout step counter.  Together with ``model.state_dict()`` a run resumes bit-exactly."""
+        names = {id(p): n for n, p in self.model.named_parameters()}
+        moments = {}
+        for (p_data, g, m1, m2, mult) in self.adam_entries:
+            moments[self._entry_names[p_data.data_ptr()]] = (m1.detach().cpu().clone(), m2.detach().cpu().clone())
+        del names
+        return {"moments": moments, "adam_step": int(self.step_dev.item()), "rng_step": int(self.rng_step.item()),
+                "state_dtypes": [str(d) for d in self.state_dtypes]}
+
+    def load_state_dict(self, sd):
+        if [str(d) for d in self.state_dtypes] != list(sd["state_dtypes"]):
+            raise ValueError(f"checkpoint holds Adam moments as {sd['state_dtypes']}, this trainer as "
+                             f"{[str(d) for d in self.state_dtypes]}")
+        for (p_data, g, m1, m2, mult) in self.adam_entries:
+            a, b = sd["moments"][self._entry_names[p_data.data_ptr()]]
+            m1.copy_(a)
+            m2.copy_(b)
+        self.step_dev.fill_(sd["adam_step"])
+        self.rng_step.fill_(sd["rng_step"])
 
     def check(self):
         """Raise if any kernel of the previous steps reported an expired wait (synchronises)."""

@@ -113,7 +113,8 @@ def multi_head_attention_forward(
     else:
         m4 = None
         if amask is not None:
-            m4 = amask.view(-1, num_heads, L, S2) if amask.shape[0] == B * num_heads else amask.unsqueeze(0)
+            # [B * heads, 1 or L, S] (key padding merged in) or [1, L, S]: both broadcast over the query axis
+            m4 = amask.view(B, num_heads, amask.shape[1], S2) if amask.shape[0] == B * num_heads else amask.unsqueeze(0)
         ctxv = F.scaled_dot_product_attention(q.view(B, num_heads, L, hd), k.view(B, num_heads, S2, hd),
                                               v.view(B, num_heads, S2, hd), attn_mask=m4, dropout_p=dropout_p)
         ctxv = ctxv.reshape(B * num_heads, L, hd)

@@ -131,6 +131,10 @@ class FlashArgs(C.Structure):
     ]
 
 
+class ReduceBlocks(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("block_elems", C.c_longlong), ("out", C.c_void_p)]
+
+
 class ReduceScatter(C.Structure):
     _fields_ = [("src", C.c_void_p), ("ld", C.c_longlong), ("rows", C.c_int), ("cols", C.c_int), ("out", C.c_void_p)]
 
@@ -174,6 +178,8 @@ def lib():
         L.rtp_embed_fwd_rot.argtypes = [C.POINTER(Ring), C.POINTER(EmbedFwd), C.c_void_p]
         L.rtp_reduce_scatter_cols.argtypes = [C.POINTER(Ring), C.POINTER(ReduceScatter), C.c_void_p]
         L.rtp_embed_fwd_rot_emu.argtypes = [C.POINTER(Ring), C.POINTER(EmbedFwd), C.c_int, C.c_void_p]
+        L.rtp_reduce_blocks.argtypes = [C.POINTER(Ring), C.POINTER(ReduceBlocks), C.c_void_p]
+        L.rtp_reduce_blocks_emu.argtypes = [C.POINTER(Ring), C.POINTER(ReduceBlocks), C.c_int, C.c_void_p]
         L.rtp_reduce_scatter_cols_emu.argtypes = [C.POINTER(Ring), C.POINTER(ReduceScatter), C.c_int, C.c_void_p]
         L.rtp_expert_fwd.argtypes = [C.POINTER(Ring), C.POINTER(ExpertFwd), C.c_void_p]
         L.rtp_expert_bwd.argtypes = [C.POINTER(Ring), C.POINTER(ExpertBwd), C.c_void_p]

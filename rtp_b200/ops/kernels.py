@@ -146,6 +146,21 @@ def embed_bwd(gtable, ids, dy, col_off, *, D, scale=1.0, drop_p=0.0, seed=0, off
     return gtable
 
 
+def embed_bwd_blocks(gblocks, ids, dy, *, scale=1.0, drop_p=0.0, seed=0, offset=0, step=None):
+    """Scatter-add of ``dy`` [T, D] into a zeroed block-major gradient ``gblocks`` [N, V, D / N]: block j is the
+    contiguous [V, D / N] contribution to the owner of embedding-dim shard j."""
+    N, V, Ds = gblocks.shape
+    D = N * Ds
+    T = ids.numel()
+    L = _L()
+    L.rtp_embed_bwd_blocks.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int,
+                                       C.c_float, C.c_float, C.c_ulonglong, C.c_ulonglong, C.c_void_p, C.c_int, C.c_int,
+                                       C.c_void_p]
+    _check(L.rtp_embed_bwd_blocks(_p(gblocks), _p(ids), _p(dy), dy.stride(0), 0, T, D, D, float(scale), float(drop_p), seed,
+                                  offset, _p(step), Ds, V, _lib.stream_ptr()), "embed_bwd_blocks")
+    return gblocks
+
+
 def attn_small_fwd(qkv, S, B, heads, *, nshard=1, causal=True, drop_p=0.0, seed=0, offset=0, sm_scale=None, step=None,
                    out=None):
     D = heads * 64

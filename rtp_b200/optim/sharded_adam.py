@@ -109,6 +109,8 @@ class ShardedAdam(torch.optim.Optimizer):
             and len(self.param_groups) == 1
         if fusable:
             self._step_fused(params)
+            from ..ops import rng
+            rng.advance(params[0].device)       # the kernels' dropout masks change with every optimizer step
         else:
             self._step_torch(params)
         return loss

@@ -252,12 +252,14 @@ class LinSpec:
     the rotated module (it carries the ``_displaced`` flag of the in-place mode)."""
 
     __slots__ = ("ring", "flat", "has_bias", "bias_off", "shard_bytes", "row", "in_f", "out_f", "places", "owner",
-                 "inplace")
+                 "inplace", "grad_mode")
 
     def __init__(self, ring, flat, has_bias, bias_off, row, in_f, out_f, places, owner=None, inplace=False):
         self.ring, self.flat, self.has_bias, self.bias_off = ring, flat, has_bias, bias_off
         self.shard_bytes = _round_up(flat.numel() * 2, 16)
         self.row, self.in_f, self.out_f, self.places, self.owner, self.inplace = row, in_f, out_f, places, owner, inplace
+        # a spec is built per call, outside autograd.Function.forward (which always runs with grad mode off)
+        self.grad_mode = torch.is_grad_enabled()
 
     @property
     def info(self):
@@ -356,7 +358,8 @@ class _FusedSubLinearFn(torch.autograd.Function):
     def forward(ctx, spec, x, *params):
         eng = get_engine(spec.ring)
         x2d = _as_2d(x)
-        needs_bwd = torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in params))
+        # whether a backward will follow: grad mode at call time (it is always off in here) and an input that wants a gradient
+        needs_bwd = spec.grad_mode and any(ctx.needs_input_grad)
         if spec.inplace and spec.ring.world > 1:
             if spec.owner is not None and getattr(spec.owner, "_displaced", False):
                 raise RuntimeError("in-place rotated layer called while its shards are displaced: the backward of the "
@@ -512,20 +515,26 @@ def reduce_scatter_cols(eng, src, out):
     return out
 
 
+def reduce_blocks(eng, blocks, out):
+    """One-hop reduce-scatter: ``blocks`` [N, ...] holds this rank's contribution to every owner (block j for owner j,
+    contiguous); each block travels straight to its owner and ``out`` receives the sum over ranks of block ``rank``."""
+    op = _lib.ReduceBlocks()
+    op.src, op.block_elems, op.out = blocks.data_ptr(), blocks[0].numel(), out.data_ptr()
+    _lib.check(_lib.lib().rtp_reduce_blocks(C.byref(eng.ring), C.byref(op), _lib.stream_ptr()), "rtp_reduce_blocks")
+    return out
+
+
 def embed_bwd_rot(eng, trainer, st, dx0):
-    """Embedding backward on a ring: dense local scatter-add into a [V, D] buffer, then a ring reduce-scatter
-    over the embedding-dim blocks delivers each owner the summed gradient of its [V, D/N] shard."""
+    """Embedding backward on a ring: local scatter-add into a block-major [N, V, D/N] buffer, then every block goes
+    straight to the owner of that embedding-dim shard, who adds the N contributions (one hop instead of N-1)."""
     import math
-    D = trainer.D
+    D, N = trainer.D, trainer.N
     V = trainer.emb.embedding.weight.shape[0]
-    dense = st.get("emb_dense")
-    if dense is None:
-        dense = torch.empty(V, D, dtype=torch.bfloat16, device=dx0.device)
-        st["emb_dense"] = dense
-    dense.zero_()
-    K.embed_bwd(dense, st["ids"].view(-1), dx0, 0, D=D, scale=math.sqrt(D), drop_p=trainer.p_drop,
-                seed=trainer.seed, offset=1, step=trainer.rng_step)
-    reduce_scatter_cols(eng, dense, trainer.emb._layout.views(trainer.emb_gflat)[0])
+    blocks = st["emb_dense"]
+    blocks.zero_()
+    K.embed_bwd_blocks(blocks, st["ids"].view(-1), dx0, scale=math.sqrt(D), drop_p=trainer.p_drop, seed=trainer.seed,
+                       offset=1, step=trainer.rng_step)
+    reduce_blocks(eng, blocks, trainer.emb._layout.views(trainer.emb_gflat)[0])
 
 
 class _FusedEmbeddingFn(torch.autograd.Function):
@@ -558,10 +567,13 @@ class _FusedEmbeddingFn(torch.autograd.Function):
         (flat_ids,) = ctx.saved_tensors
         V, Ds, D = ctx.dims
         dy2 = dy.reshape(-1, D).contiguous()
-        dense = torch.zeros(V, D, dtype=dy2.dtype, device=dy2.device)
-        K.embed_bwd(dense, flat_ids, dy2, 0, D=D, scale=1.0)
+        N = D // Ds
+        blocks = torch.zeros(N, V, Ds, dtype=dy2.dtype, device=dy2.device)
+        K.embed_bwd_blocks(blocks, flat_ids, dy2)
+        if N == 1:
+            return None, None, None, blocks[0]
         g = torch.empty(V, Ds, dtype=dy2.dtype, device=dy2.device)
-        reduce_scatter_cols(ctx.eng, dense, g)
+        reduce_blocks(ctx.eng, blocks, g)
         return None, None, None, g
 
 
@@ -578,20 +590,21 @@ class _SmallAttnPackedFn(torch.autograd.Function):
     """Short-sequence attention (S <= 96, head_dim 64) on the packed projection [S*B, 3*D], tokens ordered s*B + b."""
 
     @staticmethod
-    def forward(ctx, qkv, S, B, H, nshard, causal, drop_p, seed, offset):
+    def forward(ctx, qkv, S, B, H, nshard, causal, drop_p, seed, offset, step=None):
         qkv = qkv.contiguous()
-        out = K.attn_small_fwd(qkv, S, B, H, nshard=nshard, causal=causal, drop_p=drop_p, seed=seed, offset=offset)
+        out = K.attn_small_fwd(qkv, S, B, H, nshard=nshard, causal=causal, drop_p=drop_p, seed=seed, offset=offset,
+                               step=step)
         ctx.save_for_backward(qkv)
-        ctx.cfg = (S, B, H, nshard, causal, drop_p, seed, offset)
+        ctx.cfg = (S, B, H, nshard, causal, drop_p, seed, offset, step)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         (qkv,) = ctx.saved_tensors
-        S, B, H, nshard, causal, drop_p, seed, offset = ctx.cfg
+        S, B, H, nshard, causal, drop_p, seed, offset, step = ctx.cfg
         dqkv = K.attn_small_bwd(qkv, dout.contiguous(), S, B, H, nshard=nshard, causal=causal, drop_p=drop_p, seed=seed,
-                                offset=offset)
-        return (dqkv,) + (None,) * 8
+                                offset=offset, step=step)
+        return (dqkv,) + (None,) * 9
 
 
 _causal_mask_cache = {}
@@ -680,11 +693,15 @@ def fused_mha(owner, sub, x, *, is_causal=False, attn_mask=None, key_padding_mas
     p = float(sub.dropout) if training else 0.0
     seed = torch.initial_seed() & 0x7FFFFFFFFFFFFFFF
     offset = next_dropout_offset() if p > 0 else 0
+    step = None
+    if p > 0:
+        from ..ops import rng
+        step = rng.step_tensor(x.device)       # fresh masks at every optimizer step, also under CUDA-graph replay
     if hd == 64 and L <= 96 and not bf and attn_mask is None and key_padding_mask is None:
-        ctxv = _SmallAttnPackedFn.apply(qkv2d, L, B, H, N, causal, p, seed, offset)
+        ctxv = _SmallAttnPackedFn.apply(qkv2d, L, B, H, N, causal, p, seed, offset, step)
     else:
         ctxv = flash_attention_packed(qkv2d, B, L, H, nshard=N, seq_first=not bf, causal=causal, attn_mask=attn_mask,
-                                      key_padding_mask=key_padding_mask, dropout_p=p, seed=seed, offset=offset)
+                                      key_padding_mask=key_padding_mask, dropout_p=p, seed=seed, offset=offset, step=step)
     out = _FusedSubLinearFn.apply(spec_out, ctxv.view(*x.shape[:2], E), sub.out_proj.weight, sub.out_proj.bias)
     weights = None
     if need_weights:
@@ -760,6 +777,10 @@ def _mha_inplace(owner, sub, x, is_causal, attn_mask, key_padding_mask, training
     base = next_dropout_offset() if p > 0 else 0
     for _ in range(N - 1 if p > 0 else 0):
         next_dropout_offset()                       # one offset per visiting shard
+    step = None
+    if p > 0:
+        from ..ops import rng
+        step = rng.step_tensor(x.device)
     names = owner._layout.names
 
     def fn(j, views, xin):
@@ -767,7 +788,7 @@ def _mha_inplace(owner, sub, x, is_causal, attn_mask, key_padding_mask, training
         qkv = local_linear(xin, prm["in_proj_weight"], prm["in_proj_bias"])            # [.., 3E/N] = [q_j | k_j | v_j]
         ctxv = flash_attention_packed(qkv.reshape(-1, 3 * E // N), B, L, hps, nshard=1, seq_first=not bf, causal=causal,
                                       attn_mask=attn_mask, key_padding_mask=key_padding_mask, dropout_p=p, seed=seed,
-                                      offset=base + j)
+                                      offset=base + j, step=step)
         return local_linear(ctxv.view(*xin.shape[:2], E // N), prm["out_proj.weight"], prm["out_proj.bias"])
 
     return rotated_apply(owner.ring, fn, owner.shard_parameters(), owner._full_param, owner._layout, (x,), combine="sum",

@@ -237,19 +237,21 @@ def main():
             self.fc2 = nn.Linear(128, 16)
 
         def forward(self, x):
-            x = F.relu(self.conv1(x))
-            x = F.max_pool2d(F.relu(self.conv2(x)), 2)
-            return self.fc2(F.relu(self.fc1(torch.flatten(x, 1))))
+            # smooth activations: with ReLU / max-pooling two bf16 pipelines flip masks near zero and their gradients
+            # differ by far more than rounding, which would hide what this case is about (the plumbing of the wrapper)
+            x = torch.tanh(self.conv1(x))
+            x = F.avg_pool2d(torch.tanh(self.conv2(x)), 2)
+            return self.fc2(torch.tanh(self.fc1(torch.flatten(x, 1))))
 
     torch.manual_seed(4)
     net = Net().to(dev).to(BF)
     ref32 = copy.deepcopy(net).float()
     torch.manual_seed(400 + rank)
-    img = torch.randn(8, 1, 28, 28, device=dev, dtype=BF)
-    tgt = torch.randint(0, 16, (8,), device=dev)
+    img = torch.randn(32, 1, 28, 28, device=dev, dtype=BF)
+    tgt = torch.randint(0, 16, (32,), device=dev)
     # fp32 oracle on the global batch
     img_a, tgt_a = gather_cat(img, world), gather_cat(tgt, world)
-    lo = F.cross_entropy(ref32(img_a.float()), tgt_a, reduction="sum") / 8
+    lo = F.cross_entropy(ref32(img_a.float()), tgt_a, reduction="sum") / 32
     lo.backward()
     for inplace in (False, True):
         wrapped = RotatedTensorParallel(copy.deepcopy(net), inplace=inplace)
@@ -259,7 +261,7 @@ def main():
             zero_grads(wrapped)
             n0 = _lib.launches
             out = wrapped(img)
-            (F.cross_entropy(out.float(), tgt, reduction="sum") / 8).backward()
+            (F.cross_entropy(out.float(), tgt, reduction="sum") / 32).backward()
             engine.check_all()
             if be == "auto":
                 fused_ran(n0, f"RotatedTensorParallel(inplace={inplace})")
@@ -332,8 +334,10 @@ def main():
         check(ef <= 2 * en + 1e-2, f"LM grad {n}: fused trainer {ef:.4g} vs functional {en:.4g} (fp32 oracle)")
         check(em <= 2 * en + 1e-2, f"LM grad {n}: module path {em:.4g} vs functional {en:.4g} (fp32 oracle)")
         if p.dim() == 2:
+            # the FFN's ReLU flips masks between two bf16 pipelines, so single entries move by several percent of the
+            # range; a stale or misplaced tile is off by about the whole range
             te = tile_err(p.grad, og)
-            check(te <= 0.08, f"LM grad {n}: worst tile of the fused trainer off by {te:.3g} of the range")
+            check(te <= 0.25, f"LM grad {n}: worst tile of the fused trainer off by {te:.3g} of the range")
     # ---- training: fused trainer under graph replay, and the module path with dropout + ShardedAdam
     model2 = TransformerLM(V, D, NH, H, 0.1, 0.1, L, world, rank).to(device=dev, dtype=BF)
     model3 = copy.deepcopy(model2)

@@ -152,6 +152,27 @@ def test_rotated_embedding_and_reduce_scatter(world):
     tot = sum(s.float() for s in srcs)
     for r in range(world):
         _close(routs[r], tot[:, r * Ds:(r + 1) * Ds], 2e-2, f"reduce-scatter rank {r}")
+    # the same reduction as ONE hop: block-major contributions go straight to their owners (gradient of the embedding);
+    # mixed with the ring version above on the same gradient slots, repeated so that credits and fills interleave
+    from rtp_b200.ops import kernels as K
+    bops = (_lib.ReduceBlocks * world)()
+    blocks, bouts, dys = [], [], []
+    for r in range(world):
+        dy = torch.randn(T, D, device="cuda", dtype=BF)
+        blk = torch.zeros(world, V, Ds, device="cuda", dtype=BF)
+        K.embed_bwd_blocks(blk, idss[r], dy, scale=2.0)
+        o = torch.zeros(V, Ds, device="cuda", dtype=BF)
+        blocks.append(blk); bouts.append(o); dys.append(dy)
+        bops[r].src, bops[r].block_elems, bops[r].out = blk.data_ptr(), V * Ds, o.data_ptr()
+    for _ in range(3):
+        _lib.check(L.rtp_reduce_blocks_emu(rings, bops, world, _lib.stream_ptr()), "reduce blocks emu")
+    torch.cuda.synchronize()
+    _status_ok(wss, L, _lib)
+    dense = torch.zeros(V, D, device="cuda")
+    for r in range(world):
+        dense.index_add_(0, idss[r], dys[r].float() * 2.0)
+    for r in range(world):
+        _close(bouts[r], dense[:, r * Ds:(r + 1) * Ds], 3e-2, f"one-hop reduce rank {r}")
     for w in wss:
         L.rtp_ws_destroy(w)
 

@@ -160,3 +160,64 @@ def test_moe_lm_on_kernels():
         assert not bad, bad
     finally:
         tg.gumbel_rsample = saved
+
+
+def test_linear_whose_width_the_kernels_cannot_take_runs_on_the_functional_engine():
+    """A 10-class head: out_features is not a multiple of 8, so no legal TMA row pitch exists for its gradient.  The
+    layer must evaluate (forward AND backward) instead of failing in the middle of backward."""
+    from rtp_b200.module.linear import ColumnParallelLinear, RowParallelLinear
+    torch.manual_seed(0)
+    for cls, (i, o) in ((ColumnParallelLinear, (64, 10)), (RowParallelLinear, (36, 64))):
+        full = torch.nn.Linear(i, o).to("cuda").to(BF)
+        m = cls(i, o, linear_layer=full, device="cuda", dtype=BF)
+        x = torch.randn(32, i, device="cuda", dtype=BF, requires_grad=True)
+        y = m(x)
+        y.float().sum().backward()
+        assert _rel_err(y, F.linear(x.detach().float(), full.weight.float(), full.bias.float())) < 2e-2
+        assert m.linear.weight.grad is not None and x.grad is not None
+
+
+def test_trainer_state_dict_resumes_bit_exactly():
+    """Model shards + trainer state (Adam moments, Adam step, dropout step) are all a run needs to continue."""
+    from rtp_b200.models.transformer_lm_rtp import TransformerLM
+    from rtp_b200.models.fused_lm import FusedLMTrainer
+    torch.manual_seed(0)
+    V, D, H, NH, L, S, B = 1024, 256, 512, 4, 2, 32, 8
+    model = TransformerLM(V, D, NH, H, 0.1, 0.1, L, 1, 0).to(device="cuda", dtype=BF)
+    ids = torch.randint(0, V, (S + 1, B), device="cuda")
+    x, y = ids[:-1].contiguous(), ids[1:].contiguous()
+    tr = FusedLMTrainer(model, lr=1e-3, clip_value=0.05, use_graph=False)
+    for _ in range(3):
+        tr.step(x, y)
+    sd_model = {k: v.clone() for k, v in model.state_dict().items()}
+    sd_tr = tr.state_dict()
+    assert sd_tr["adam_step"] == 3 and sd_tr["rng_step"] == 3
+    expect = [tr.step(x, y).item() for _ in range(3)]
+    model2 = TransformerLM(V, D, NH, H, 0.1, 0.1, L, 1, 0).to(device="cuda", dtype=BF)
+    model2.load_state_dict(sd_model)
+    tr2 = FusedLMTrainer(model2, lr=1e-3, clip_value=0.05, use_graph=False)
+    tr2.load_state_dict(sd_tr)
+    got = [tr2.step(x, y).item() for _ in range(3)]
+    assert got == expect, (got, expect)
+    with pytest.raises(ValueError):
+        FusedLMTrainer(model2, lr=1e-3, state_dtype="bf16").load_state_dict(sd_tr)
+
+
+def test_cross_entropy_leaves_its_input_alone():
+    from rtp_b200.ops import functional as FO
+    torch.manual_seed(0)
+    logits = torch.randn(64, 1024, device="cuda", dtype=BF)
+    t = torch.randint(0, 1024, (64,), device="cuda")
+    keep = logits.clone()
+    with torch.no_grad():
+        loss = FO.cross_entropy(logits, t)
+    assert torch.equal(logits, keep)
+    lg = logits.clone().requires_grad_(True)
+    loss2 = FO.cross_entropy(lg, t)
+    loss2.backward()
+    assert torch.equal(lg.detach(), keep)
+    ref = logits.float().requires_grad_(True)
+    lr = F.cross_entropy(ref, t)
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 1e-2 and abs(loss2.item() - lr.item()) < 1e-2
+    assert _rel_err(lg.grad, ref.grad) < 2e-2
