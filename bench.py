@@ -43,9 +43,12 @@ CONFIGS["moe"] = dict(family="moe", vocab=32000, ninp=2048, nhid=8192, nhead=16,
                       n_experts=8, capacity_factor=1.25, dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
 CONFIGS["moe-small"] = dict(family="moe", vocab=8192, ninp=512, nhid=1024, nhead=8, nlayers=2, seq_len=128, batch=4,
                             n_experts=8, capacity_factor=1.25, dropout=0.0, clip=0.0, initrange=0.02, lr=1e-4)
-# the reference's gate has a fixed capacity of 2 * tokens / experts (factor 1.0): this variant lets both arms run
-CONFIGS["moe-cf1"] = dict(CONFIGS["moe"], capacity_factor=1.0)
-CONFIGS["moe-small-cf1"] = dict(CONFIGS["moe-small"], capacity_factor=1.0)
+# The reference's gate has a fixed capacity of 2 * tokens / experts (factor 1.0), and its rotating expert layer applies
+# every local expert to the whole chunk and concatenates on the capacity axis (rtp/module/moe.py:159-163), which only
+# reshapes back with ONE local expert.  These variants (capacity factor 1.0, one expert per rank: n_experts 0 = world
+# size) are what both arms can run.
+CONFIGS["moe-cf1"] = dict(CONFIGS["moe"], capacity_factor=1.0, n_experts=0)
+CONFIGS["moe-small-cf1"] = dict(CONFIGS["moe-small"], capacity_factor=1.0, n_experts=0)
 METRIC = "tokens/s/box"
 
 
@@ -63,9 +66,10 @@ def parse():
     ap.add_argument("--path", default="trainer", choices=["trainer", "module"],
                     help="README config of this framework: the fused trainer (default) or rotated modules + autograd "
                          "with a torch-style loop and ShardedAdam")
-    ap.add_argument("--adam-state", default="fp32", choices=["fp32", "mixed", "bf16"],
-                    help="dtype policy of the Adam moments of this framework (the reference arm's torch.optim.Adam "
-                         "keeps bf16 moments for bf16 parameters)")
+    ap.add_argument("--adam-state", default="mixed", choices=["fp32", "mixed", "bf16"],
+                    help="dtype policy of the Adam moments of this framework: mixed (default here) = first moment bf16, "
+                         "second moment fp32; fp32 = both fp32 (the library's default); bf16 = both bf16, which is what "
+                         "the reference arm's torch.optim.Adam keeps for bf16 parameters")
     return ap.parse_args()
 
 
@@ -235,8 +239,10 @@ def run_ours(args, cfg, rank, local, world):
             if p.dim() > 1:
                 p.uniform_(-cfg["initrange"], cfg["initrange"])
     model = model.to(device=dev, dtype=torch.bfloat16)
+    # keep_grads=None: a large model runs each layer's Adam update right after its backward (the gradients share one
+    # scratch buffer), a small one keeps the gradients and updates in one launch
     trainer = FusedLMTrainer(model, lr=cfg["lr"], clip_value=cfg["clip"], use_graph=not args.no_graph,
-                             state_dtype=args.adam_state)
+                             state_dtype=args.adam_state, keep_grads=None)
     nb = max(8, args.steps + args.warmup)
     pinned = synthetic_batches(cfg, min(nb, 64), rank)
     dev_batches = [(a.to(dev), b.to(dev)) for a, b in pinned]
@@ -279,16 +285,17 @@ def run_ours_module(args, cfg, rank, local, world):
     torch.manual_seed(0)
     dev = torch.device("cuda", local)
     fam = cfg["family"]
+    on_dev = dict(device=dev, dtype=torch.bfloat16)      # shards are created and initialised on the GPU
     if fam == "gpt":
         from rtp_b200.models.gpt import GPT, GPTConfig
-        model = GPT(GPTConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"]))
+        model = GPT(GPTConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"]), **on_dev)
     elif fam == "llama":
         from rtp_b200.models.llama import Llama, LlamaConfig
-        model = Llama(LlamaConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"]))
+        model = Llama(LlamaConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"]), **on_dev)
     else:
         from rtp_b200.models.moe_lm import MoELM, MoEConfig
         model = MoELM(MoEConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["n_experts"],
-                                cfg["capacity_factor"], cfg["seq_len"]))
+                                cfg["capacity_factor"], cfg["seq_len"]), **on_dev)
     model = model.to(device=dev, dtype=torch.bfloat16)
     opt = ShardedAdamW(model.parameters(), lr=cfg["lr"], weight_decay=0.01, state_dtype=args.adam_state)
     nb = min(max(4, args.steps + args.warmup), 16)
@@ -433,7 +440,11 @@ def run_reference(args, cfg, rank, local, world):
     sys.path[:] = [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
     sys.path.insert(0, ref)
     sys.path.insert(0, os.path.join(ref, "benchmarks"))
-    torch.set_default_dtype(torch.bfloat16)   # the reference ignores dtype=, and .to(bf16) breaks its aliasing
+    # The reference ignores dtype=, and .to(bf16) breaks its aliasing: bf16 is selected through the default dtype.  Its MoE
+    # path cannot run in bf16 at all (rtp/module/moe.py:148 contracts an fp32 dispatch mask with the activations), so
+    # that arm runs in the reference's native fp32.
+    ref_dtype = torch.float32 if cfg.get("family") == "moe" else torch.bfloat16
+    torch.set_default_dtype(ref_dtype)
     torch.manual_seed(0)
     dev = torch.device("cuda", local)
     mode = args.mode
@@ -452,8 +463,10 @@ def run_reference(args, cfg, rank, local, world):
         model = TransformerLM(*margs, world, rank)
     else:
         _fairscale_stub()
-        import transformer_lm_dp
-        model = transformer_lm_dp.TransformerLM(*margs)
+        # each benchmark script has its own copy of the plain model (benchmarks/dp_benchmark.py:12, fsdp_benchmark.py:12)
+        import importlib
+        plain = importlib.import_module("transformer_lm_dp" if mode == "dp" else "transformer_lm_fsdp")
+        model = plain.TransformerLM(*margs)
     with torch.no_grad():                     # the reference leaves the attention in-projection uninitialised
         for name, p in model.named_parameters():
             if not p.requires_grad:
@@ -512,6 +525,7 @@ def run_reference(args, cfg, rank, local, world):
         e2e = {"value": tok / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                "h2d_bytes_per_step": 2 * pinned[0][0].numel() * 8, "d2h_bytes_per_step": 4}
     peak = torch.cuda.max_memory_allocated() / 2 ** 30
+    run_reference.dtype = "bf16" if ref_dtype == torch.bfloat16 else "fp32 (the reference's MoE path does not run in bf16)"
     return ms, clocks, loss, e2e, peak, 0
 
 
@@ -528,15 +542,18 @@ def main():
             return
         raise SystemExit("bench.py needs a CUDA device")
     rank, local, world = setup_dist(args)
+    if cfg.get("n_experts", 1) == 0:
+        cfg = dict(cfg, n_experts=world)
     t_wall = time.time()
     module_path = args.impl == "rtp_b200" and ("family" in cfg or args.path == "module")
     if args.impl == "reference":
         why = None
         if cfg.get("family") == "llama":
             why = "the reference ships no Llama model (no RMSNorm / RoPE / SwiGLU): nothing to run"
-        elif cfg.get("family") == "moe" and cfg.get("capacity_factor", 1.0) != 1.0:
-            why = ("the reference's gate has a fixed capacity of 2 * tokens / experts (rtp/module/top2gate.py:52); "
-                   "run --config moe-cf1 for a both-arms comparison at capacity factor 1.0")
+        elif cfg.get("family") == "moe" and (cfg.get("capacity_factor", 1.0) != 1.0 or cfg["n_experts"] != world):
+            why = ("the reference's gate has a fixed capacity of 2 * tokens / experts (rtp/module/top2gate.py:52) and "
+                   "its rotating expert layer only works with one expert per rank (rtp/module/moe.py:159-163); "
+                   "run --config moe-cf1 for a both-arms comparison")
         elif args.mode != "rtp" and "family" in cfg:
             why = "the DP / FSDP / TP arms are wired for the dense README model only"
         if why:
@@ -572,7 +589,9 @@ def main():
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": getattr(run_reference, "dtype", "bf16") if args.impl == "reference" else "bf16",
+            "data": "synthetic uniform token ids, random-init weights",
             "impl": args.impl, "peak_gb_per_gpu": peak_gb, "final_loss": loss,
             "config": {"model": "RTP TransformerLM (README config)" if args.config == "readme" else args.config,
                        "vocab": cfg["vocab"], "ninp": cfg["ninp"], "nhid": cfg["nhid"], "nhead": cfg["nhead"],

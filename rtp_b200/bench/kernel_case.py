@@ -24,7 +24,7 @@ def _peaks():
         return 6650.0, 1590.0, "fallback"
 
 
-def _time(fn, iters, warm=2):
+def _time(fn, iters, warm=3):
     for i in range(warm):
         fn(i)
     torch.cuda.synchronize()

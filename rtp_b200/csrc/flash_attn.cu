@@ -1,10 +1,12 @@
 // Flash attention on tcgen05 tensor cores: forward, dQ and dK/dV kernels (see flash_attn.h for the interface).
 //
-// One CTA = 128 query rows (forward, dQ) or 128 keys (dK/dV) of one (batch, head).  Six warps:
-//   warps 0-3  "row" threads: thread t owns TMEM lane t = row t of the tile.  The online softmax of a row (forward) and
-//              the dS algebra (backward) run in that thread's registers, without shuffles.
-//   warp 4     TMA producer: Q / K / V / dO tiles, 128 rows x 64 columns per copy, 128-byte swizzle, local memory only.
-//   warp 5     UMMA issuer (one elected thread).
+// One CTA = 128 query rows (forward, dQ) or 128 keys (dK/dV) of one (batch, head).  Ten warps:
+//   warps 0-7  "row" threads, two per row of the tile: thread (t, h) reads TMEM lane t and owns the key columns
+//              [64 h, 64 h + 64) of the 128-key block (warps w and w + 4 may both access lanes 32 (w % 4) ..).  The online
+//              softmax of a row (forward) and the dS algebra (backward) run in registers without shuffles; the two
+//              threads of a row exchange one partial maximum per block through shared memory (forward only).
+//   warp 8     TMA producer: Q / K / V / dO tiles, 128 rows x 64 columns per copy, 128-byte swizzle, local memory only.
+//   warp 9     UMMA issuer (one elected thread).
 //
 // Forward, per block of 128 keys:  S = Q K^T (TMEM, double-buffered)  ->  row threads: scale, masks, running max,
 // P = exp2(S - m) as bf16 into a shared tile  ->  O += P V with O resident in TMEM.  O is rescaled in TMEM only when a
@@ -36,7 +38,9 @@ using namespace rtp;
 
 constexpr int kBlk = 128;              // rows of Q per CTA = keys per block
 constexpr int kSub = 16384;            // one [128 x 64] bf16 sub-tile with 128-byte rows
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kRowThreads = 256;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleGap = 8.f;     // rescale O when a row maximum grew by more than 2^8
 
@@ -78,6 +82,12 @@ struct Ctl {
   uint64_t bar[16];
   uint32_t tmem_base;
   uint32_t abort_flag;
+};
+// Exchange area of the two threads of a row (forward): per block one partial row maximum each way, double-buffered by
+// block parity, published with a sequence number the partner spins on (bounded).
+struct Xchg {
+  float val[2][2][128];
+  uint32_t seq[2][128];
 };
 
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) {
@@ -191,7 +201,7 @@ __device__ __forceinline__ uint4 pack8f(const float* v) {
 // Common set-up: barriers, TMEM, abort flag.  Returns the TMEM base.
 __device__ __forceinline__ uint32_t setup_cta(Ctl* ctl, const int* counts, int nbar, int warp, int lane) {
   pdl_launch_dependents();
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane < nbar) mbar_init(&ctl->bar[lane], counts[lane]);
     if (lane == 31) ctl->abort_flag = 0;
     mbar_fence_init();
@@ -208,10 +218,38 @@ __device__ __forceinline__ uint32_t setup_cta(Ctl* ctl, const int* counts, int n
 __device__ __forceinline__ void teardown_cta(uint32_t tmem, int warp) {
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+}
+// Publishes `v` to the other thread of the row and returns the partner's value for sequence number `seq` (> 0).
+// Bounded: gives up (returns v) when the CTA aborts or the budget runs out.
+__device__ __forceinline__ float xchg_row(Xchg* x, int wg, int rt, uint32_t seq, float v, volatile uint32_t* abort_flag,
+                                          unsigned long long* status, unsigned long long timeout_ns, bool& ok) {
+  volatile float* mine = &x->val[seq & 1][wg][rt];
+  volatile float* theirs = &x->val[seq & 1][wg ^ 1][rt];
+  volatile uint32_t* my_seq = &x->seq[wg][rt];
+  volatile uint32_t* their_seq = &x->seq[wg ^ 1][rt];
+  *mine = v;
+  __threadfence_block();
+  *my_seq = seq;
+  uint32_t it = 0;
+  unsigned long long t0 = 0;
+  while (*their_seq < seq) {
+    if ((++it & 0x3ff) == 0) {
+      if (*abort_flag) { ok = false; return v; }
+      if (t0 == 0) t0 = globaltimer_ns();
+      else if (globaltimer_ns() - t0 > timeout_ns) {
+        *abort_flag = 1;
+        atomicCAS(status, (unsigned long long)ST_OK, (unsigned long long)ST_TIMEOUT_MBAR);
+        ok = false;
+        return v;
+      }
+    }
+  }
+  __threadfence_block();
+  return *theirs;
 }
 // After an abort: wait (bounded) for the copies this thread has issued, so that none lands in a dead CTA.
 __device__ __forceinline__ void drain_loads(uint64_t* const* bars, const uint32_t* parity, const bool* issued, int n) {
@@ -247,6 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
   uint8_t* sV = sK + 2 * TILE;        // 2 stages
   uint8_t* sP = sV + 2 * TILE;        // [128 x 128] bf16: two sub-tiles
   Ctl* ctl = reinterpret_cast<Ctl*>(sP + 2 * kSub);
+  Xchg* xc = reinterpret_cast<Xchg*>(sP + 2 * kSub + 256);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const MaskArgs& M = p.m;
   const int nqb = (M.Sq + kBlk - 1) / kBlk;
@@ -259,15 +298,16 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
   int nkb = (M.Sk + kBlk - 1) / kBlk;
   if (M.causal) nkb = min(nkb, qb + 1);
 
-  // counts by barrier index: Q/K/V full and empty 1 each, S full 1, S empty 4 (one per row warp), P full 128, rest 1
-  const int counts[16] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 4, 4, 128, 1, 1};
+  // counts by barrier index: Q/K/V full and empty 1 each, S full 1, S empty 8 (one per row warp), P full 256, rest 1
+  const int counts[16] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 8, 8, kRowThreads, 1, 1};
+  if (tid < kRowThreads) xc->seq[tid >> 7][tid & 127] = 0;
   const uint32_t tmem = setup_cta(ctl, counts, 16, warp, lane);
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   unsigned long long* status = p.status;
   const unsigned long long tmo = p.timeout_ns;
   uint64_t* bar = ctl->bar;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ---------------------------------------------------------------------------------- TMA producer
     if (elect_one()) {
       const int cq = head_col(p.q, h), ck = head_col(p.k, h), cv = head_col(p.v, h);
@@ -290,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
       }
       if (!ok || *abort_flag) drain_loads(dbar, dpar, dis, 5);
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ---------------------------------------------------------------------------------- UMMA issuer
     if (elect_one()) {
       const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0), id_o = make_idesc_bf16(128, HD, 0, 1);
@@ -335,37 +375,43 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
     }
   } else {
     // ---------------------------------------------------------------------------------- row threads
-    const int row = q0 + tid;
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const int wg = warp >> 2, rt = tid & 127;          // column half and row of this thread
+    const int row = q0 + rt;
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const unsigned long long offset = M.offset + (M.step_ptr ? __ldg(M.step_ptr) * 65536ull : 0ull);
-    float m_used = -INFINITY, l = 0.f;
+    constexpr int OC = HD / 64;                        // 32-column chunks of O per thread
+    float m_used = -INFINITY, l = 0.f;                  // l: this thread's half of the row sum
     bool ok = true;
     for (int j = 0; j < nkb; ++j) {
       const int buf = j & 1;
       uint32_t good = mbar_wait(&bar[F_SFULL + buf], (uint32_t)(j >> 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
       if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
       tc_fence_after();
-      float s[128];
+      float s[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32f(lane_addr + (uint32_t)(buf * 128 + c * 32), s + 32 * c);
+      for (int c = 0; c < 2; ++c) tmem_ld32f(lane_addr + (uint32_t)(buf * 128 + wg * 64 + c * 32), s + 32 * c);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[F_SEMPTY + buf]);
-      const int col0 = j * kBlk;
-      const bool plain = !M.mask && !M.kpm && !(M.causal && j == qb) && (col0 + kBlk <= M.Sk);
+      const int col0 = j * kBlk + wg * 64;
+      const bool plain = !M.mask && !M.kpm && !(M.causal && j == qb) && (j * kBlk + kBlk <= M.Sk);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) score_chunk<32>(s + 32 * c, row, col0 + 32 * c, b, M, plain);
+      for (int c = 0; c < 2; ++c) score_chunk<32>(s + 32 * c, row, col0 + 32 * c, b, M, plain);
       float mx = s[0];
 #pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 1; i < 64; ++i) mx = fmaxf(mx, s[i]);
+      // both threads of the row must scale with the same reference: exchange the partial maxima
+      bool xok = true;
+      mx = fmaxf(mx, xchg_row(xc, wg, rt, (uint32_t)j + 1u, mx, abort_flag, status, tmo, xok));
+      if (!__all_sync(0xffffffffu, xok ? 1u : 0u)) { ok = false; break; }
       const float cand = fmaxf(m_used, mx);
       const bool need = cand > m_used + kRescaleGap;
       const float m_new = need ? cand : m_used;
       const float mref = (m_new == -INFINITY) ? 0.f : m_new;
       float rs = 0.f;
 #pragma unroll
-      for (int i = 0; i < 128; ++i) {
+      for (int i = 0; i < 64; ++i) {
         s[i] = exp2f(s[i] - mref);
         rs += s[i];
       }
@@ -377,13 +423,13 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
         if (__any_sync(0xffffffffu, need)) {
           const float alpha = need ? exp2f(m_used - cand) : 1.f;
 #pragma unroll
-          for (int c = 0; c < HD / 32; ++c) {
+          for (int c = 0; c < OC; ++c) {
             float o[32];
-            tmem_ld32f(lane_addr + (uint32_t)(256 + c * 32), o);
+            tmem_ld32f(lane_addr + (uint32_t)(256 + (wg * OC + c) * 32), o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] *= alpha;
-            tmem_st32f(lane_addr + (uint32_t)(256 + c * 32), o);
+            tmem_st32f(lane_addr + (uint32_t)(256 + (wg * OC + c) * 32), o);
           }
           tmem_st_wait();
           l *= alpha;
@@ -393,15 +439,15 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
       l += rs;
       if (M.thresh) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           const uint32_t keep = keep_bits<32>(M, offset, bh, min(row, M.Sq - 1), col0 + 32 * c);
 #pragma unroll
           for (int i = 0; i < 32; ++i) s[32 * c + i] = ((keep >> i) & 1u) ? s[32 * c + i] * M.drop_scale : 0.f;
         }
       }
 #pragma unroll
-      for (int c = 0; c < 16; ++c)
-        *reinterpret_cast<uint4*>(sP + (c >> 3) * kSub + sw128(tid, c & 7)) = pack8f(s + 8 * c);
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(sP + wg * kSub + sw128(rt, c)) = pack8f(s + 8 * c);
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(&bar[F_PFULL]);
@@ -411,29 +457,35 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
       if (!__all_sync(0xffffffffu, good)) ok = false;
     }
     if (ok) {
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = row < M.Sq ? row_ptr(p.o, b, row, h) : nullptr;
+      bool xok = true;
+      const float l_all = l + xchg_row(xc, wg, rt, (uint32_t)nkb + 1u, l, abort_flag, status, tmo, xok);
+      if (!__all_sync(0xffffffffu, xok ? 1u : 0u)) ok = false;
+      if (ok) {
+        tc_fence_after();
+        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+        __nv_bfloat16* dst = row < M.Sq ? row_ptr(p.o, b, row, h) : nullptr;
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        float o[32];
-        if (nkb > 0) {
-          tmem_ld32f(lane_addr + (uint32_t)(256 + c * 32), o);
-          tmem_ld_wait();
-        } else {
+        for (int c = 0; c < OC; ++c) {
+          const int cc = wg * OC + c;
+          float o[32];
+          if (nkb > 0) {
+            tmem_ld32f(lane_addr + (uint32_t)(256 + cc * 32), o);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+            for (int i = 0; i < 32; ++i) o[i] = 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= inv;
+          if (dst) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + cc * 32 + q * 8) = pack8f(o + 8 * q);
+          }
         }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] *= inv;
-        if (dst) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = pack8f(o + 8 * q);
+        if (wg == 0 && row < M.Sq && p.lse) {
+          const float mref = (m_used == -INFINITY) ? 0.f : m_used;
+          p.lse[(long long)bh * M.Sq + row] = l_all > 0.f ? mref + log2f(l_all) : INFINITY;
         }
-      }
-      if (row < M.Sq && p.lse) {
-        const float mref = (m_used == -INFINITY) ? 0.f : m_used;
-        p.lse[(long long)bh * M.Sq + row] = l > 0.f ? mref + log2f(l) : INFINITY;
       }
     }
   }
@@ -465,14 +517,14 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
   const int q0 = qb * kBlk;
   int nkb = (M.Sk + kBlk - 1) / kBlk;
   if (M.causal) nkb = min(nkb, qb + 1);
-  const int counts[16] = {1, 1, 1, 1, 1, 1, 128, 1, 1, 1, 1, 1, 1, 1, 1, 1};
+  const int counts[16] = {1, 1, 1, 1, 1, 1, kRowThreads, 1, 1, 1, 1, 1, 1, 1, 1, 1};
   const uint32_t tmem = setup_cta(ctl, counts, 9, warp, lane);
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   unsigned long long* status = p.status;
   const unsigned long long tmo = p.timeout_ns;
   uint64_t* bar = ctl->bar;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (elect_one()) {
       const int cq = head_col(p.q, h), ck = head_col(p.k, h), cv = head_col(p.v, h), cg = head_col(p.dout, h);
       bool ok = true;
@@ -492,7 +544,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
       }
       if (!ok || *abort_flag) drain_loads(dbar, dpar, dis, 3);
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     if (elect_one()) {
       const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0), id_q = make_idesc_bf16(128, HD, 0, 1);
       const uint32_t aQ = smem_u32(sQ), aG = smem_u32(sG), aK = smem_u32(sK), aV = smem_u32(sV), aS = smem_u32(sS);
@@ -531,11 +583,12 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
       if (!ok && issued) drain_mma(&bar[Q_DRAIN]);
     }
   } else {
-    const int row = q0 + tid;
+    const int wg = warp >> 2, rt = tid & 127;          // column half and row of this thread
+    const int row = q0 + rt;
     const bool live = row < M.Sq;
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const unsigned long long offset = M.offset + (M.step_ptr ? __ldg(M.step_ptr) * 65536ull : 0ull);
-    // delta = rowsum(dO * O), kept for the dK / dV kernel as well
+    // delta = rowsum(dO * O), kept for the dK / dV kernel as well (both threads of a row compute it, one stores it)
     float delta = 0.f, lse2 = INFINITY;
     if (live) {
       const uint4* op = reinterpret_cast<const uint4*>(row_ptr(p.o, b, row, h));
@@ -547,7 +600,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
                  bf16_hi(a.y) * bf16_hi(g.y) + bf16_lo(a.z) * bf16_lo(g.z) + bf16_hi(a.z) * bf16_hi(g.z) +
                  bf16_lo(a.w) * bf16_lo(g.w) + bf16_hi(a.w) * bf16_hi(g.w);
       }
-      p.delta[(long long)bh * M.Sq + row] = delta;
+      if (wg == 0) p.delta[(long long)bh * M.Sq + row] = delta;
       lse2 = p.lse[(long long)bh * M.Sq + row];
     }
     bool ok = true;
@@ -558,7 +611,8 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
       const int col0 = j * kBlk;
       const bool plain = !M.mask && !M.kpm && !(M.causal && j == qb) && (col0 + kBlk <= M.Sk);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * wg + cc;
         float x[32], dp[32];
         tmem_ld32f(lane_addr + (uint32_t)(c * 32), x);
         tmem_ld32f(lane_addr + (uint32_t)(128 + c * 32), dp);
@@ -574,7 +628,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(sS + (c >> 1) * kSub + sw128(tid, (c & 1) * 4 + q)) = pack8f(x + 8 * q);
+          *reinterpret_cast<uint4*>(sS + wg * kSub + sw128(rt, cc * 4 + q)) = pack8f(x + 8 * q);
       }
       fence_proxy_async();
       tc_fence_before();
@@ -588,7 +642,8 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
       tc_fence_after();
       __nv_bfloat16* dst = live ? row_ptr(p.dq, b, row, h) : nullptr;
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int cc = 0; cc < HD / 64; ++cc) {
+        const int c = wg * (HD / 64) + cc;
         float o[32];
         if (nkb > 0) {
           tmem_ld32f(lane_addr + (uint32_t)(256 + c * 32), o);
@@ -636,14 +691,14 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dkv_kernel(const __grid_con
   const int k0 = kb * kBlk;
   const int i0 = M.causal ? kb : 0;
   const int nit = nqb - i0;
-  const int counts[16] = {1, 1, 1, 1, 1, 1, 128, 1, 1, 1, 1, 1, 1, 1, 1, 1};
+  const int counts[16] = {1, 1, 1, 1, 1, 1, kRowThreads, 1, 1, 1, 1, 1, 1, 1, 1, 1};
   const uint32_t tmem = setup_cta(ctl, counts, 9, warp, lane);
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   unsigned long long* status = p.status;
   const unsigned long long tmo = p.timeout_ns;
   uint64_t* bar = ctl->bar;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (elect_one()) {
       const int cq = head_col(p.q, h), ck = head_col(p.k, h), cv = head_col(p.v, h), cg = head_col(p.dout, h);
       bool ok = true;
@@ -663,7 +718,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dkv_kernel(const __grid_con
       }
       if (!ok || *abort_flag) drain_loads(dbar, dpar, dis, 1 + NS);
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     if (elect_one()) {
       const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0), id_t = make_idesc_bf16(128, HD, 1, 1);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aG = smem_u32(sG);
@@ -707,12 +762,13 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dkv_kernel(const __grid_con
       if (!ok && issued) drain_mma(&bar[K_DRAIN]);
     }
   } else {
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const int wg = warp >> 2, rt = tid & 127;          // column half and row of this thread
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const unsigned long long offset = M.offset + (M.step_ptr ? __ldg(M.step_ptr) * 65536ull : 0ull);
     bool ok = true;
     for (int it = 0; it < nit; ++it) {
       const int qb = i0 + it;
-      const int row = qb * kBlk + tid;
+      const int row = qb * kBlk + rt;
       float delta = 0.f, lse2 = INFINITY;
       if (row < M.Sq) {
         delta = __ldg(p.delta + (long long)bh * M.Sq + row);
@@ -723,7 +779,8 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dkv_kernel(const __grid_con
       tc_fence_after();
       const bool plain = !M.mask && !M.kpm && !(M.causal && qb == kb) && (k0 + kBlk <= M.Sk);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * wg + cc;
         float x[32], dp[32];
         tmem_ld32f(lane_addr + (uint32_t)(c * 32), x);
         tmem_ld32f(lane_addr + (uint32_t)(128 + c * 32), dp);
@@ -741,7 +798,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dkv_kernel(const __grid_con
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const uint32_t off = (uint32_t)(c >> 1) * kSub + sw128(tid, (c & 1) * 4 + q);
+          const uint32_t off = (uint32_t)wg * kSub + sw128(rt, cc * 4 + q);
           *reinterpret_cast<uint4*>(sP + off) = pack8f(x + 8 * q);
           *reinterpret_cast<uint4*>(sS + off) = pack8f(dp + 8 * q);
         }
@@ -756,11 +813,12 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dkv_kernel(const __grid_con
     }
     if (ok) {
       tc_fence_after();
-      const int key = k0 + tid;
+      const int key = k0 + rt;
       __nv_bfloat16* dvp = key < M.Sk ? row_ptr(p.dv, b, key, h) : nullptr;
       __nv_bfloat16* dkp = key < M.Sk ? row_ptr(p.dk, b, key, h) : nullptr;
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int cc = 0; cc < HD / 64; ++cc) {
+        const int c = wg * (HD / 64) + cc;
         float o[32];
         if (nit > 0) { tmem_ld32f(lane_addr + (uint32_t)(256 + c * 32), o); tmem_ld_wait(); }
         else {
@@ -855,7 +913,7 @@ int fill_common(const RtpFlashArgs* a, FlashParams& P) {
   P.q = dref(a->q); P.k = dref(a->k); P.v = dref(a->v); P.o = dref(a->o);
   return 0;
 }
-constexpr int smem_fwd(int hd) { return 1024 + (hd / 64) * kSub * 5 + 2 * kSub + 256; }
+constexpr int smem_fwd(int hd) { return 1024 + (hd / 64) * kSub * 5 + 2 * kSub + 256 + (int)sizeof(Xchg); }
 constexpr int smem_dq(int hd) { return 1024 + (hd / 64) * kSub * 6 + 2 * kSub + 256; }
 constexpr int smem_dkv(int hd, int ns) { return 1024 + (hd / 64) * kSub * (2 + 2 * ns) + 4 * kSub + 256; }
 static_assert(sizeof(Ctl) <= 256, "control block");

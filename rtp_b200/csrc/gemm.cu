@@ -173,8 +173,18 @@ int push_cta_policy(int ctas) {
   if (r >= ctas) r = 0;
   return r;
 }
+// Geometry of the small push ring (RTP_PUSH_RING): 0 = four 3840-byte chunks in flight per CTA, 1 = two of 7680 bytes.
+int push_ring_policy() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("RTP_PUSH_RING");
+    v = e ? (atoi(e) == 1 ? 1 : 0) : 0;
+  }
+  return v;
+}
 void finalize_program(RtpProgram& P, int ctas, bool pair) {
   const int tm = pair ? 256 : 128;
+  P.push_ring = push_ring_policy();
   int reserved = P.n_pushes > 0 ? push_cta_policy(ctas) : 0;
   if (pair) reserved &= ~1;
   P.n_compute = ctas - reserved;
@@ -1003,7 +1013,8 @@ int rtp_gemm_batched(const RtpGemmBatched* a, void* stream) {
 
 int rtp_linear_fwd(const RtpRing* ring, const RtpLinearFwd* op, void* stream) {
   static thread_local rtp::GemmParams<1> params;
-  decide_pair(op->M, op->out_features, ring->ctas, ring->world == 1 || pair_policy() == 1);   // automatic pairs: single rank only
+  // CTA pairs by size, on any ring (the pair protocol is local to one GPU; checked against an fp32 oracle on real rings)
+  decide_pair(op->M, ring->world > 1 && op->mode == 0 ? op->out_features / ring->world : op->out_features, ring->ctas);
   if (build_linear_fwd(*ring, *op, params.prog[0])) return -1;
   params.prog[0].trace = g_trace;
   if (!params.prog[0].status) return fail("ring workspace required");
@@ -1012,8 +1023,8 @@ int rtp_linear_fwd(const RtpRing* ring, const RtpLinearFwd* op, void* stream) {
 }
 int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream) {
   static thread_local rtp::GemmParams<1> params;
-  decide_pair(op->M, op->in_features < op->out_features ? op->in_features : op->out_features, ring->ctas,
-              ring->world == 1 || pair_policy() == 1);
+  // CTA pairs by the size of the input-gradient GEMM [M, in-per-shard], on any ring
+  decide_pair(op->M, op->mode == 0 ? op->in_features : op->in_features / ring->world, ring->ctas);
   if (build_linear_bwd(*ring, *op, params.prog[0])) return -1;
   params.prog[0].trace = g_trace;
   if (!params.prog[0].status) return fail("ring workspace required");

@@ -29,8 +29,13 @@ constexpr int kStagePitch = 144;                // bytes per staged output row: 
 constexpr int kStagingBytes = 4 * 32 * kStagePitch;
 // Push rings.  A CTA that also runs GEMM tiles has a small ring of its own (its shared memory belongs to the tile
 // pipeline); a CTA reserved for pushing uses the idle tile pipeline's memory as a deep ring.
-constexpr int kPushChunk = 7680;                // small ring: bytes per bulk copy, two slots
-constexpr int kPushRingBytes = 2 * kPushChunk;
+// A transfer to a peer costs a fixed 3 to 4 microseconds (measured on two B200s: 1 MB in 7 us, 8 MB in 18 us, 64 MB in
+// 100 us = 670 GB/s, whatever issues the copies).  What matters is therefore never to wait for one job's stores
+// before starting the next: four small chunks per CTA are outstanding at any time and a job is announced while the
+// stores of the following jobs are already on the link.
+constexpr int kPushChunk = 3840;                // small ring: bytes per bulk copy
+constexpr int kPushSlots = 4;
+constexpr int kPushRingBytes = kPushSlots * kPushChunk;
 constexpr int kBigPushChunk = 16384;            // deep ring: 12 slots in the tile area
 constexpr int kMaxPushSlots = 12;
 static_assert(kMaxPushSlots * kBigPushChunk <= 196608, "deep push ring must fit the tile area");
@@ -1013,7 +1018,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         }
       } else {
         pc.ring = staging + kStagingBytes; pc.index = cta; pc.sharers = G;
-        run_pushes<2, kPushChunk, 1>(pc);
+        if (P.push_ring == 1) run_pushes<2, 2 * kPushChunk, 1>(pc);
+        else run_pushes<kPushSlots, kPushChunk, kPushSlots - 1>(pc);
       }
     }
   }
@@ -1024,23 +1030,30 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
     // have been acknowledged) and bump the consumer's arrival counter.  The epilogue warps are already at work on the
     // next phase meanwhile.
     if (lane == 0) {
-      uint32_t want = 0;
-      for (int p = 0; p < P.n_phases; ++p) {
-        unsigned long long* ap = P.phases[p].arrive_ptr;
-        if (!ap) continue;
-        ++want;
+      // phases that announce their output, in program order
+      int n_sig = 0;
+      for (int p = 0; p < P.n_phases; ++p) n_sig += P.phases[p].arrive_ptr != nullptr;
+      int next_p = 0;         // next phase index to look at
+      uint32_t sent = 0;      // announcing phases signalled so far
+      while ((int)sent < n_sig) {
         // bounded: the epilogue warps hand every such phase over, also after an abort
         const unsigned long long t0 = globaltimer_ns();
+        uint32_t have = 0;
         bool got = true;
-        while (*reinterpret_cast<volatile uint32_t*>(&ctl->handed) < want) {
+        while ((have = *reinterpret_cast<volatile uint32_t*>(&ctl->handed)) <= sent) {
           if (globaltimer_ns() - t0 > 2 * timeout_ns) { got = false; break; }
           __nanosleep(32);
         }
         if (!got) break;
         __threadfence_block();
-        if (!*abort_flag) {
-          __threadfence_system();
-          red_relaxed_sys_add(ap, 1ull);
+        // ONE fence covers every phase handed over so far (a fence waits a link round trip: never one per phase)
+        const bool live = !*abort_flag;
+        if (live) __threadfence_system();
+        while (sent < have) {
+          while (P.phases[next_p].arrive_ptr == nullptr) ++next_p;
+          if (live) red_relaxed_sys_add(P.phases[next_p].arrive_ptr, 1ull);
+          ++next_p;
+          ++sent;
         }
       }
     }

@@ -139,6 +139,7 @@ struct alignas(64) RtpProgram {
   int n_phases, n_pushes;
   int n_stages, stage_bytes;  // smem pipeline geometry (host: finalize_program)
   int n_compute;              // CTAs [0, n_compute) run GEMM tiles, [n_compute, grid) only push (0 / grid: none reserved)
+  int push_ring;              // small push ring: 0 = four 3840-byte chunks in flight, 1 = two 7680-byte chunks
   RtpFlagBlock* flags;  // this rank's flag block (may be null when nothing synchronises)
   RtpFlagBlock* peer_flags[RTP_FLAG_MAX_WORLD];  // every rank's flag block as mapped here (credits are written there)
   int rank, world;

@@ -36,17 +36,29 @@ class _Lin:
         self.module, self.row, self.in_f, self.out_f = module, row, in_f, out_f
         self.flat = flat
         self.info = layout_info
-        self.gflat = torch.zeros_like(flat)
+        self.gflat = None     # set by the trainer: a buffer of its own, or a window of the shared gradient scratch
+        self.plan = None      # Adam plan of this layer alone (optimizer-in-backward mode)
         self.params = params  # [(param, offset, numel, lr_mult)]
 
 
 class FusedLMTrainer:
     def __init__(self, model, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, adamw=False,
                  clip_value: Optional[float] = None, loss_scale: Optional[float] = None, use_graph: bool = True,
-                 seed: int = 1234, group=None, state_dtype=None):
+                 seed: int = 1234, group=None, state_dtype=None, keep_grads: Optional[bool] = True):
         """``state_dtype``: Adam moment policy, ``None`` / ``"fp32"`` (default), ``"mixed"`` or ``"bf16"``
-        (see ``rtp_b200.ops.kernels.adam_state_dtypes``)."""
+        (see ``rtp_b200.ops.kernels.adam_state_dtypes``).
+
+        ``keep_grads=True``: every parameter's ``.grad`` holds its gradient after ``step`` and Adam runs once at the end.
+        ``keep_grads=False`` (optimizer in backward): the gradient of each rotated layer lands in ONE shared scratch
+        buffer and that layer's Adam update runs right after its backward launch, so only one layer's gradient is alive
+        at a time (the gradients are 1/4 to 1/6 of the per-rank model state); ``.grad`` is not meaningful afterwards.
+        Both modes apply the same updates.  ``keep_grads=None`` picks by size: a model whose per-rank share is under half a
+        billion parameters keeps its gradients (one Adam launch per step instead of one per layer: such a step is bound by
+        launches, not memory), a larger one updates in backward."""
         self.model = model
+        if keep_grads is None:
+            keep_grads = sum(p.numel() for p in model.parameters()) < 500_000_000
+        self.keep_grads = keep_grads
         self.state_dtypes = K.adam_state_dtypes(state_dtype)
         self.ring = get_context(group)
         self.N = self.ring.world
@@ -97,7 +109,6 @@ class FusedLMTrainer:
         m, N, D = self.model, self.N, self.D
         self.emb = m[0].embedding            # ParallelEmbedding
         self.pe = m[1].pe.view(-1, D).to(torch.bfloat16).contiguous()
-        self.emb_gflat = torch.zeros_like(self.emb._full_param)
         self.layers = []
         for li in range(self.L):
             layer = m[2 + li]
@@ -132,30 +143,51 @@ class FusedLMTrainer:
             self.ln_params += [l["n1"].weight, l["n1"].bias, l["n2"].weight, l["n2"].bias]
         self.ln_grad32 = torch.zeros(len(self.ln_params) * D, dtype=torch.float32, device=self.dev)
         self.ln_grad16 = torch.zeros(len(self.ln_params) * D, dtype=torch.bfloat16, device=self.dev)
-        # Adam plan over views of the flat buffers
+        # gradient buffers: one per layer, or windows of one scratch as large as the largest shard
+        lins = [l[k] for l in self.layers for k in ("qkv", "out", "ff1", "ff2")] + [self.head]
+        if self.keep_grads:
+            for d in lins:
+                d.gflat = torch.zeros_like(d.flat)
+            self.emb_gflat = torch.zeros_like(self.emb._full_param)
+        else:
+            nmax = max([d.flat.numel() for d in lins] + [self.emb._full_param.numel()])
+            self.gscratch = torch.zeros(nmax, dtype=torch.bfloat16, device=self.dev)
+            for d in lins:
+                d.gflat = self.gscratch[:d.flat.numel()]
+            self.emb_gflat = self.gscratch[:self.emb._full_param.numel()]
+        # Adam plans over views of the flat buffers: one for everything, or one per layer
         entries = []
 
-        def add(p, g):
+        def entry(p, g):
             m1 = torch.zeros_like(p, dtype=self.state_dtypes[0])
             m2 = torch.zeros_like(p, dtype=self.state_dtypes[1])
             mult = 1.0 / getattr(p, "rtp_sum_replicated") if getattr(p, "rtp_sum_replicated", None) else 1.0
-            entries.append((p.data, g, m1, m2, mult))
-            p.grad = g
+            e = (p.data, g, m1, m2, mult)
+            entries.append(e)
+            if self.keep_grads:
+                p.grad = g
+            return e
 
-        add(self.emb.embedding.weight, self.emb._layout.views(self.emb_gflat)[0])
-        for l in self.layers:
-            for key in ("qkv", "out", "ff1", "ff2"):
-                d = l[key]
-                for p, off, n, mult in d.params:
-                    add(p, d.gflat[off:off + n].view(p.shape))
-        for p, off, n, mult in self.head.params:
-            add(p, self.head.gflat[off:off + n].view(p.shape))
-        for k, p in enumerate(self.ln_params):
-            add(p, self.ln_grad16[k * D:(k + 1) * D])
+        emb_e = [entry(self.emb.embedding.weight, self.emb._layout.views(self.emb_gflat)[0])]
+        per_lin = []
+        for d in lins:
+            per_lin.append([entry(p, d.gflat[off:off + n].view(p.shape)) for p, off, n, mult in d.params])
+        ln_e = [entry(p, self.ln_grad16[k * D:(k + 1) * D]) for k, p in enumerate(self.ln_params)]
         self.adam_entries = entries
         by_ptr = {p.data_ptr(): n for n, p in self.model.named_parameters()}
         self._entry_names = {e[0].data_ptr(): by_ptr[e[0].data_ptr()] for e in entries}
-        self.plan = K.AdamPlan(entries, self.dev)
+        if self.keep_grads:
+            self.plan = K.AdamPlan(entries, self.dev)
+        else:
+            self.plan = None
+            self.emb_plan = K.AdamPlan(emb_e, self.dev)
+            self.ln_plan = K.AdamPlan(ln_e, self.dev)
+            for d, es in zip(lins, per_lin):
+                d.plan = K.AdamPlan(es, self.dev)
+
+    def _adam(self, plan):
+        plan.step(self.step_dev, self.lr, self.betas[0], self.betas[1], self.eps, self.wd, self.adamw, self.clip)
+        self._count(1)
 
     # ------------------------------------------------------------------------------------------
     def _alloc_static(self, S, B):
@@ -166,12 +198,12 @@ class FusedLMTrainer:
         st["tgt"] = torch.zeros(S, B, dtype=torch.int64, device=dev)
         st["x0"] = torch.empty(M, D, dtype=bf, device=dev)
         acts = []
-        slabs = []
-        for _ in range(self.L):
-            # all bf16 activations of a layer come out of one slab, so that a dead layer's memory can be lent out whole
-            sizes = dict(qkv=3 * D, ctx=D, sa=D, h1=D, x1=D, a1=H, f=D, h2=D, x2=D)
-            slab = torch.empty(M * sum(sizes.values()), dtype=bf, device=dev)
-            slabs.append(slab)
+        # all bf16 activations come out of one arena, so that memory of layers whose backward has run can be lent out
+        sizes = dict(qkv=3 * D, ctx=D, h1=D, x1=D, a1=H, h2=D, x2=D)
+        per_layer = M * sum(sizes.values())
+        arena = torch.empty(self.L * per_layer, dtype=bf, device=dev)
+        for li in range(self.L):
+            slab = arena[li * per_layer:(li + 1) * per_layer]
             a, off = {}, 0
             for name, w in sizes.items():
                 a[name] = slab[off:off + M * w].view(M, w)
@@ -180,6 +212,10 @@ class FusedLMTrainer:
                 a[name] = torch.empty(M, dtype=torch.float32, device=dev)
             acts.append(a)
         st["acts"] = acts
+        # outputs of the out-projection and of the second FFN linear are consumed by the residual + norm kernel at once
+        # and never read in backward: one buffer each serves every layer
+        st["sa"] = torch.empty(M, D, dtype=bf, device=dev)
+        st["f"] = torch.empty(M, D, dtype=bf, device=dev)
         st["logits"] = torch.empty(M, V, dtype=bf, device=dev)
         st["loss_rows"] = torch.empty(M, dtype=torch.float32, device=dev)
         st["loss"] = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -193,9 +229,9 @@ class FusedLMTrainer:
         st["dbias"] = torch.empty(max(3 * D, V, H), dtype=torch.float32, device=dev)
         if self.N > 1:
             # Block-major scatter buffer of the embedding gradient ([N, V, D/N]).  It is only alive after the backward of
-            # every layer, so it lives on top of the activations of the LAST layer (whose backward ran first).
+            # every layer, so it lives on top of the (by then dead) activations.
             need = V * D
-            buf = slabs[-1][:need] if slabs[-1].numel() >= need else torch.empty(need, dtype=bf, device=dev)
+            buf = arena[:need] if arena.numel() >= need else torch.empty(need, dtype=bf, device=dev)
             st["emb_dense"] = buf.view(self.N, V, D // self.N)
         return st
 
@@ -224,6 +260,8 @@ class FusedLMTrainer:
         else:
             E.embed_bwd_rot(self.eng, self, st, dx0)
             self._count(3)
+        if not self.keep_grads:
+            self._adam(self.emb_plan)
 
     def _count(self, n):
         if self._counting:
@@ -258,6 +296,10 @@ class FusedLMTrainer:
                          mask_scale=mask_scale, grad_out=d.gflat, dx_out=dx_out, dx_accumulate=dx_accumulate,
                          dbias_buf=dbuf, **self._chain_args(d, 1))
         self._count(2)  # column sums of dy + fused dgrad/wgrad program
+        if not self.keep_grads:
+            # The layer's shard is updated as soon as its gradient is complete.  Its home buffer is no longer read by
+            # anyone in this step: the pushes of it (by this launch or the one before) precede the update in stream order.
+            self._adam(d.plan)
 
     def _step_impl(self, st):
         S, B, M, D, L = st["S"], st["B"], st["M"], self.D, self.L
@@ -272,12 +314,12 @@ class FusedLMTrainer:
             self._lin_fwd(l["qkv"], x, a["qkv"])
             K.attn_small_fwd(a["qkv"], S, B, self.heads, nshard=self.N, causal=True, drop_p=p, seed=self.seed,
                              offset=o + 1, step=rs, out=a["ctx"])
-            self._lin_fwd(l["out"], a["ctx"], a["sa"])
-            K.norm_fwd(x, a["sa"], l["n1"].weight, l["n1"].bias, eps=l["eps"], drop_p=p, seed=self.seed, offset=o + 2,
+            self._lin_fwd(l["out"], a["ctx"], st["sa"])
+            K.norm_fwd(x, st["sa"], l["n1"].weight, l["n1"].bias, eps=l["eps"], drop_p=p, seed=self.seed, offset=o + 2,
                        step=rs, out=a["x1"], h_out=a["h1"], mean_out=a["mean1"], rstd_out=a["rstd1"])
             self._lin_fwd(l["ff1"], a["x1"], a["a1"], act=1, drop_p=p, offset=o + 3)
-            self._lin_fwd(l["ff2"], a["a1"], a["f"])
-            K.norm_fwd(a["x1"], a["f"], l["n2"].weight, l["n2"].bias, eps=l["eps"], drop_p=p, seed=self.seed,
+            self._lin_fwd(l["ff2"], a["a1"], st["f"])
+            K.norm_fwd(a["x1"], st["f"], l["n2"].weight, l["n2"].bias, eps=l["eps"], drop_p=p, seed=self.seed,
                        offset=o + 4, step=rs, out=a["x2"], h_out=a["h2"], mean_out=a["mean2"], rstd_out=a["rstd2"])
             self._count(3)
             x = a["x2"]
@@ -288,6 +330,7 @@ class FusedLMTrainer:
         self._count(2)
         # ---------------- backward
         self.ln_grad32.zero_()
+        self.step_dev.add_(1)          # the Adam step of this iteration (the updates may run inside backward)
         self._count(1)
         dx = st["dxa"]
         self._lin_bwd(self.head, x, st["logits"], st, dx_out=dx)
@@ -322,10 +365,9 @@ class FusedLMTrainer:
             dist.all_reduce(self.ln_grad32, group=self.ring.group)
             self._count(1)
         K.cast_f32_bf16(self.ln_grad32, self.ln_grad16)
-        self.step_dev.add_(1)
-        self.plan.step(self.step_dev, self.lr, self.betas[0], self.betas[1], self.eps, self.wd, self.adamw, self.clip)
+        self._adam(self.plan if self.keep_grads else self.ln_plan)
         self.rng_step.add_(1)
-        self._count(4)
+        self._count(3)
 
     # ------------------------------------------------------------------------------------------
     def step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:

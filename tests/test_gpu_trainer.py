@@ -221,3 +221,25 @@ def test_cross_entropy_leaves_its_input_alone():
     lr.backward()
     assert abs(loss.item() - lr.item()) < 1e-2 and abs(loss2.item() - lr.item()) < 1e-2
     assert _rel_err(lg.grad, ref.grad) < 2e-2
+
+
+def test_optimizer_in_backward_applies_the_same_updates():
+    """keep_grads=False (shared gradient scratch, Adam right after each layer's backward) and keep_grads=True (all
+    gradients kept, one Adam launch at the end) must walk the same trajectory, bit for bit."""
+    from rtp_b200.models.transformer_lm_rtp import TransformerLM
+    from rtp_b200.models.fused_lm import FusedLMTrainer
+    torch.manual_seed(0)
+    V, D, H, NH, L, S, B = 1024, 256, 512, 4, 2, 32, 8
+    base = TransformerLM(V, D, NH, H, 0.1, 0.1, L, 1, 0).to(device="cuda", dtype=BF)
+    ids = torch.randint(0, V, (S + 1, B), device="cuda")
+    x, y = ids[:-1].contiguous(), ids[1:].contiguous()
+    results = []
+    for keep in (True, False):
+        model = copy.deepcopy(base)
+        tr = FusedLMTrainer(model, lr=1e-3, clip_value=0.05, use_graph=not keep, keep_grads=keep, state_dtype="mixed")
+        losses = [tr.step(x, y).item() for _ in range(4)]
+        tr.check()
+        results.append((losses, [p.detach().clone() for p in model.parameters()]))
+    assert results[0][0] == results[1][0], (results[0][0], results[1][0])
+    for a, b in zip(results[0][1], results[1][1]):
+        assert torch.equal(a, b)
