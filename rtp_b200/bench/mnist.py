@@ -90,10 +90,11 @@ def worker(rank, world, args, port):
     torch.manual_seed(args.seed)
     (xtr, ytr), (xte, yte) = load_data(args, rank, world)
     rotated = args.mode in ("rtp", "rtp_inplace", "rtp_modules")
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     if args.mode == "rtp_modules":
-        model = RotatedNet().to(device)
+        model = RotatedNet().to(device, dtype)
     else:
-        model = Net().to(device)
+        model = Net().to(device, dtype)
         if args.mode in ("rtp", "rtp_inplace"):
             model = RotatedTensorParallel(model, inplace=args.mode == "rtp_inplace")
         elif args.mode == "dp" and world > 1:
@@ -110,9 +111,9 @@ def worker(rank, world, args, port):
         tot = torch.zeros(2, device=device)
         for i in range(0, xtr.size(0) - per * world + 1, per * world):
             idx = perm[i + rank * per:i + (rank + 1) * per]
-            x, y = xtr[idx].to(device), ytr[idx].to(device)
+            x, y = xtr[idx].to(device, dtype), ytr[idx].to(device)
             opt.zero_grad()
-            loss = F.nll_loss(model(x), y, reduction="sum")
+            loss = F.nll_loss(model(x).float(), y, reduction="sum")
             # rotated layers SUM gradients over the ring: scale the loss like the reference (rtp_mnist.py:78)
             (loss / (per * world) if rotated else loss / per).backward()
             opt.step()
@@ -122,7 +123,7 @@ def worker(rank, world, args, port):
         correct = torch.zeros(2, device=device)
         with torch.no_grad():
             for i in range(rank * per, xte.size(0) - per + 1, per * world):
-                x, y = xte[i:i + per].to(device), yte[i:i + per].to(device)
+                x, y = xte[i:i + per].to(device, dtype), yte[i:i + per].to(device)
                 correct += torch.tensor([(model(x).argmax(1) == y).sum().item(), float(per)], device=device)
         dist.all_reduce(correct)
         if rank == 0:
@@ -152,6 +153,8 @@ def main(argv=None):
     p.add_argument("--train-samples", dest="train_samples", type=int, default=2048)
     p.add_argument("--test-samples", dest="test_samples", type=int, default=512)
     p.add_argument("--save-model", dest="save_model", default=None)
+    p.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"],
+                   help="bf16 on CUDA puts the rotated layers on the fused sm_100a kernels (fp32 uses the functional engine)")
     args = p.parse_args(argv)
     world = args.gpus or (torch.cuda.device_count() if torch.cuda.is_available() else 1)
     port = 12355 + os.getpid() % 1000

@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const __nv_bfloat16* _
     store_stack(sK, vb, tid);
     store_stack(sV, vc, tid);
   }
-  fence_proxy_async();
+  fence_proxy_async_smem();
   __syncthreads();
   ATT_STAMP(2);
 
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const __nv_bfloat16* _
                      pack2(x[8 * c8 + 4], x[8 * c8 + 5]), pack2(x[8 * c8 + 6], x[8 * c8 + 7]));
   }
   ATT_STAMP(4);
-  fence_proxy_async();
+  fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();   // every row of S has been read: its TMEM columns are reused for O
   ATT_STAMP(5);
@@ -328,7 +328,7 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const __nv_bfloat16* _
     store_stack(sV, vc, tid);
     store_stack(sG, vd, tid);
   }
-  fence_proxy_async();
+  fence_proxy_async_smem();
   __syncthreads();
   ATT_STAMP(2);
 
@@ -417,7 +417,7 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const __nv_bfloat16* _
     }
   }
   ATT_STAMP(4);
-  fence_proxy_async();
+  fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();   // S and dP have been read everywhere: their TMEM columns are reused for dQ
   ATT_STAMP(5);

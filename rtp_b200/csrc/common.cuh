@@ -181,6 +181,9 @@ __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.w
 // Makes writes done through the generic proxy (also a peer GPU's stores, once observed with an
 // acquire load) visible to later reads through the async proxy (TMA).
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// The same for shared-memory writes only (a tile written with st.shared that a UMMA or a bulk copy reads next): it
+// does not have to order the thread's global accesses, which makes it far cheaper inside a loop.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------
 // tcgen05: TMEM allocation, UMMA issue, commit, TMEM loads

@@ -18,6 +18,9 @@
 //               -> dQ += dS K.
 //   dK/dV kernel (CTA = key block): per query block: S, dP -> P, dS tiles -> dV += P^T dO, dK += dS^T Q.  The P / dS
 //               tiles are written row-per-thread once and read by the UMMA as MN-major A operands (= transposed).
+// Each kernel is compiled in four variants (additive / key-padding masks yes or no, dropout yes or no): the mask and
+// Philox code unrolled over a row's registers is several times larger than the plain softmax and, when merely branched
+// over, slowed the row threads down through instruction fetch alone.
 // Every mbarrier wait is bounded; on expiry the CTA records a status code, drains its copies and UMMAs, frees its TMEM
 // and returns.
 #include <cuda.h>
@@ -68,6 +71,7 @@ struct MaskArgs {
 
 struct alignas(64) FlashParams {
   CUtensorMap mq, mk, mv, mdo;         // 3-D maps {columns, dim1, dim2}; *_seq1 tells which of dim1 / dim2 is the sequence
+  CUtensorMap mq64, mdo64, mk64, mv64; // the same tensors with boxes of 64 rows (backward kernels)
   int q_seq1, k_seq1, v_seq1, do_seq1;
   DRef q, k, v, o, dout, dq, dk, dv;
   float* lse;
@@ -76,18 +80,18 @@ struct alignas(64) FlashParams {
   MaskArgs m;
   unsigned long long* status;
   unsigned long long timeout_ns;
+  long long* trace;                    // tuning aid (rtp_flash_debug_set_trace): SM clock stamps of CTA 0, else null
 };
 
 struct Ctl {
-  uint64_t bar[16];
+  uint64_t bar[24];
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
 // Exchange area of the two threads of a row (forward): per block one partial row maximum each way, double-buffered by
-// block parity, published with a sequence number the partner spins on (bounded).
+// block parity.  The two warps that share 32 rows meet at an mbarrier of their own (64 arrivals per exchange).
 struct Xchg {
   float val[2][2][128];
-  uint32_t seq[2][128];
 };
 
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) {
@@ -129,13 +133,29 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, 
   }
 }
 
+// The backward kernels walk the other sequence in sub-blocks of 64 rows, three stages deep.
+constexpr int kHalf = 64;                 // rows per sub-block
+constexpr int kHalfTile = kHalf * 128;    // one [64 x 64] bf16 sub-tile with 128-byte rows
+constexpr int kBwdStages = 3;
+template <int SUB>
+__device__ __forceinline__ void load_tile64(uint32_t dst, const CUtensorMap* map, int seq1, int col, int b, int s0,
+                                            uint32_t bar) {
+  const unsigned long long m = reinterpret_cast<unsigned long long>(map);
+#pragma unroll
+  for (int u = 0; u < SUB; ++u) {
+    if (seq1) tma_load_3d_s(dst + u * kHalfTile, m, col + u * 64, s0, b, bar);
+    else tma_load_3d_s(dst + u * kHalfTile, m, col + u * 64, b, s0, bar);
+  }
+}
+
 // x[i] = log2-domain score of (row, col0 + i): scale, additive mask, key padding, causal and sequence bounds.
 // Masked entries become -inf.  `plain` = nothing but the scale applies to this block.
-template <int NC>
+template <int NC, bool MSK>
 __device__ __forceinline__ void score_chunk(float* x, int row, int col0, int b, const MaskArgs& m, bool plain) {
 #pragma unroll
   for (int i = 0; i < NC; ++i) x[i] *= m.scale_log2;
   if (plain) return;
+  if constexpr (MSK) {
   if (m.mask && row < m.Sq) {
     if (m.mask_fp32) {
       const float* mp = reinterpret_cast<const float*>(m.mask) + (long long)row * m.mask_ld + col0;
@@ -170,6 +190,7 @@ __device__ __forceinline__ void score_chunk(float* x, int row, int col0, int b, 
     const unsigned char* kp = m.kpm + (long long)b * m.kpm_ld + col0;
 #pragma unroll
     for (int i = 0; i < NC; ++i) if (col0 + i < m.Sk && __ldg(kp + i)) x[i] = -INFINITY;
+  }
   }
   if (m.causal && col0 + NC - 1 > row) {
 #pragma unroll
@@ -223,33 +244,28 @@ __device__ __forceinline__ void teardown_cta(uint32_t tmem, int warp) {
     tmem_dealloc(tmem, 512);
   }
 }
-// Publishes `v` to the other thread of the row and returns the partner's value for sequence number `seq` (> 0).
-// Bounded: gives up (returns v) when the CTA aborts or the budget runs out.
-__device__ __forceinline__ float xchg_row(Xchg* x, int wg, int rt, uint32_t seq, float v, volatile uint32_t* abort_flag,
-                                          unsigned long long* status, unsigned long long timeout_ns, bool& ok) {
-  volatile float* mine = &x->val[seq & 1][wg][rt];
-  volatile float* theirs = &x->val[seq & 1][wg ^ 1][rt];
-  volatile uint32_t* my_seq = &x->seq[wg][rt];
-  volatile uint32_t* their_seq = &x->seq[wg ^ 1][rt];
-  *mine = v;
-  __threadfence_block();
-  *my_seq = seq;
-  uint32_t it = 0;
-  unsigned long long t0 = 0;
-  while (*their_seq < seq) {
-    if ((++it & 0x3ff) == 0) {
-      if (*abort_flag) { ok = false; return v; }
-      if (t0 == 0) t0 = globaltimer_ns();
-      else if (globaltimer_ns() - t0 > timeout_ns) {
-        *abort_flag = 1;
-        atomicCAS(status, (unsigned long long)ST_OK, (unsigned long long)ST_TIMEOUT_MBAR);
-        ok = false;
-        return v;
-      }
-    }
+// Publishes `v` to the other thread of the row and returns the partner's value; `n` counts the exchanges of this row
+// group from 0.  The arrive releases the value, the (bounded) wait acquires the partner's.
+__device__ __forceinline__ float xchg_row(Xchg* x, uint64_t* xbar, int wg, int rt, uint32_t n, float v,
+                                          volatile uint32_t* abort_flag, unsigned long long* status,
+                                          unsigned long long timeout_ns, bool& ok) {
+  x->val[n & 1][wg][rt] = v;
+  mbar_arrive(xbar);
+  if (!mbar_wait(xbar, n & 1u, abort_flag, status, timeout_ns)) { ok = false; return v; }
+  return x->val[n & 1][wg ^ 1][rt];
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max64(const float* s) {
+  float m0 = s[0], m1 = s[1], m2 = s[2], m3 = s[3];
+#pragma unroll
+  for (int i = 4; i < 64; i += 4) {
+    m0 = fmaxf(m0, s[i]); m1 = fmaxf(m1, s[i + 1]); m2 = fmaxf(m2, s[i + 2]); m3 = fmaxf(m3, s[i + 3]);
   }
-  __threadfence_block();
-  return *theirs;
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 // After an abort: wait (bounded) for the copies this thread has issued, so that none lands in a dead CTA.
 __device__ __forceinline__ void drain_loads(uint64_t* const* bars, const uint32_t* parity, const bool* issued, int n) {
@@ -272,9 +288,9 @@ __device__ __forceinline__ void drain_mma(uint64_t* bar) {
 // =====================================================================================================  forward
 // barriers
 enum { F_QFULL = 0, F_KFULL = 1, F_KEMPTY = 3, F_VFULL = 5, F_VEMPTY = 7, F_SFULL = 9, F_SEMPTY = 11, F_PFULL = 13,
-       F_PVDONE = 14, F_DRAIN = 15 };
+       F_PVDONE = 14, F_DRAIN = 15, F_XCHG = 16 /* .. 19: one per group of 32 rows */ };
 
-template <int HD>
+template <int HD, bool MSK, bool DRP>
 __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_constant__ FlashParams p) {
   constexpr int SUB = HD / 64;
   constexpr int TILE = SUB * kSub;
@@ -298,10 +314,10 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
   int nkb = (M.Sk + kBlk - 1) / kBlk;
   if (M.causal) nkb = min(nkb, qb + 1);
 
-  // counts by barrier index: Q/K/V full and empty 1 each, S full 1, S empty 8 (one per row warp), P full 256, rest 1
-  const int counts[16] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 8, 8, kRowThreads, 1, 1};
-  if (tid < kRowThreads) xc->seq[tid >> 7][tid & 127] = 0;
-  const uint32_t tmem = setup_cta(ctl, counts, 16, warp, lane);
+  // counts by barrier index: Q/K/V full and empty 1 each, S full 1, S empty 8 (one per row warp), P full 256, drain 1,
+  // row exchange 64 (two warps)
+  const int counts[20] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 8, 8, kRowThreads, 1, 1, 64, 64, 64, 64};
+  const uint32_t tmem = setup_cta(ctl, counts, 20, warp, lane);
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   unsigned long long* status = p.status;
   const unsigned long long tmo = p.timeout_ns;
@@ -360,8 +376,12 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
           issue_s(n);
         }
         const int st = j & 1;
+        long long* tm = (p.trace && blockIdx.x == 0 && j < 16) ? p.trace + 256 + j * 8 : nullptr;
+        if (tm) tm[0] = clock64();                       // S of the next block issued
         if (!mbar_wait(&bar[F_VFULL + st], (uint32_t)(j >> 1) & 1u, abort_flag, status, tmo)) { ok = false; break; }
+        if (tm) tm[1] = clock64();                       // V landed
         if (!mbar_wait(&bar[F_PFULL], (uint32_t)j & 1u, abort_flag, status, tmo)) { ok = false; break; }
+        if (tm) tm[2] = clock64();                       // P written
         tc_fence_after();
         const uint32_t vb = aV + st * TILE;
 #pragma unroll
@@ -370,6 +390,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
                     make_smem_desc(vb + kk * 2048, kSub, 1024), id_o, (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&bar[F_VEMPTY + st]);
         umma_commit(&bar[F_PVDONE]);
+        if (tm) tm[3] = clock64();                       // P V issued
       }
       if (!ok && issued) drain_mma(&bar[F_DRAIN]);
     }
@@ -382,11 +403,15 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
     constexpr int OC = HD / 64;                        // 32-column chunks of O per thread
     float m_used = -INFINITY, l = 0.f;                  // l: this thread's half of the row sum
     bool ok = true;
+    // stamps of two row warps of CTA 0: [warp 0 | warp 4][block < 16][event < 8]
+    long long* tr = (p.trace && blockIdx.x == 0 && lane == 0 && (warp & 3) == 0) ? p.trace + (warp >> 2) * 128 : nullptr;
     for (int j = 0; j < nkb; ++j) {
       const int buf = j & 1;
+      if (tr && j < 16) tr[j * 8 + 0] = clock64();
       uint32_t good = mbar_wait(&bar[F_SFULL + buf], (uint32_t)(j >> 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
       if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
       tc_fence_after();
+      if (tr && j < 16) tr[j * 8 + 1] = clock64();
       float s[64];
 #pragma unroll
       for (int c = 0; c < 2; ++c) tmem_ld32f(lane_addr + (uint32_t)(buf * 128 + wg * 64 + c * 32), s + 32 * c);
@@ -394,34 +419,44 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[F_SEMPTY + buf]);
+      if (tr && j < 16) tr[j * 8 + 2] = clock64();
       const int col0 = j * kBlk + wg * 64;
-      const bool plain = !M.mask && !M.kpm && !(M.causal && j == qb) && (j * kBlk + kBlk <= M.Sk);
+      const bool plain = !(MSK && (M.mask || M.kpm)) && !(M.causal && j == qb) && (j * kBlk + kBlk <= M.Sk);
+      // a block that only needs the scale keeps the raw scores: the scale rides in the exponent's multiply-add
+      if (!plain) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) score_chunk<32>(s + 32 * c, row, col0 + 32 * c, b, M, plain);
-      float mx = s[0];
-#pragma unroll
-      for (int i = 1; i < 64; ++i) mx = fmaxf(mx, s[i]);
+        for (int c = 0; c < 2; ++c) score_chunk<32, MSK>(s + 32 * c, row, col0 + 32 * c, b, M, false);
+      }
+      float mx = max64(s);
+      if (plain) mx *= M.scale_log2;      // the scale is positive: the maximum commutes with it
       // both threads of the row must scale with the same reference: exchange the partial maxima
       bool xok = true;
-      mx = fmaxf(mx, xchg_row(xc, wg, rt, (uint32_t)j + 1u, mx, abort_flag, status, tmo, xok));
+      mx = fmaxf(mx, xchg_row(xc, &bar[F_XCHG + (warp & 3)], wg, rt, (uint32_t)j, mx, abort_flag, status, tmo, xok));
       if (!__all_sync(0xffffffffu, xok ? 1u : 0u)) { ok = false; break; }
+      if (tr && j < 16) tr[j * 8 + 3] = clock64();
       const float cand = fmaxf(m_used, mx);
       const bool need = cand > m_used + kRescaleGap;
       const float m_new = need ? cand : m_used;
       const float mref = (m_new == -INFINITY) ? 0.f : m_new;
-      float rs = 0.f;
+      const float mul = plain ? M.scale_log2 : 1.f;
+      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        s[i] = exp2f(s[i] - mref);
-        rs += s[i];
+      for (int i = 0; i < 64; i += 4) {
+        s[i] = ex2_approx(fmaf(s[i], mul, -mref));
+        s[i + 1] = ex2_approx(fmaf(s[i + 1], mul, -mref));
+        s[i + 2] = ex2_approx(fmaf(s[i + 2], mul, -mref));
+        s[i + 3] = ex2_approx(fmaf(s[i + 3], mul, -mref));
+        r0 += s[i]; r1 += s[i + 1]; r2 += s[i + 2]; r3 += s[i + 3];
       }
+      const float rs = (r0 + r1) + (r2 + r3);
+      if (tr && j < 16) tr[j * 8 + 4] = clock64() + (rs < -1.f ? 1 : 0);
       if (j > 0) {
         // P V of the previous block must be complete before the P tile is overwritten and before O is rescaled
         good = mbar_wait(&bar[F_PVDONE], (uint32_t)(j - 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
         if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, need)) {
-          const float alpha = need ? exp2f(m_used - cand) : 1.f;
+          const float alpha = need ? ex2_approx(m_used - cand) : 1.f;
 #pragma unroll
           for (int c = 0; c < OC; ++c) {
             float o[32];
@@ -437,7 +472,8 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
       }
       m_used = m_new;
       l += rs;
-      if (M.thresh) {
+      if (tr && j < 16) tr[j * 8 + 5] = clock64();
+      if constexpr (DRP) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const uint32_t keep = keep_bits<32>(M, offset, bh, min(row, M.Sq - 1), col0 + 32 * c);
@@ -448,9 +484,11 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
 #pragma unroll
       for (int c = 0; c < 8; ++c)
         *reinterpret_cast<uint4*>(sP + wg * kSub + sw128(rt, c)) = pack8f(s + 8 * c);
-      fence_proxy_async();
+      if (tr && j < 16) tr[j * 8 + 6] = clock64();
+      fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bar[F_PFULL]);
+      if (tr && j < 16) tr[j * 8 + 7] = clock64();
     }
     if (ok && nkb > 0) {
       uint32_t good = mbar_wait(&bar[F_PVDONE], (uint32_t)(nkb - 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
@@ -458,7 +496,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
     }
     if (ok) {
       bool xok = true;
-      const float l_all = l + xchg_row(xc, wg, rt, (uint32_t)nkb + 1u, l, abort_flag, status, tmo, xok);
+      const float l_all = l + xchg_row(xc, &bar[F_XCHG + (warp & 3)], wg, rt, (uint32_t)nkb, l, abort_flag, status, tmo, xok);
       if (!__all_sync(0xffffffffu, xok ? 1u : 0u)) ok = false;
       if (ok) {
         tc_fence_after();
@@ -493,20 +531,29 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
 }
 
 // =====================================================================================================  dQ
-enum { Q_QFULL = 0, Q_KVFULL = 1, Q_KVEMPTY = 3, Q_SDPFULL = 5, Q_DSFULL = 6, Q_DONE = 7, Q_DRAIN = 8 };
+// CTA = 128 queries of one (batch, head); the keys are walked in sub-blocks of 64, three stages of K / V deep:
+//   S = Q K^T and dP = dO V^T      [128 queries x 64 keys] each, in TMEM, double-buffered
+//   row threads (TMEM lane = query, two threads per query with 32 keys each): dS = P (dP - delta) as bf16 into a
+//                                  [128 x 64] K-major shared tile
+//   dQ += dS K                     contraction over the 64 keys; B = the K stage read MN-major
+// The products of sub-block i+1 run while the row threads work on sub-block i.
+enum { Q_QFULL = 0, Q_KVFULL = 1 /* 3 stages */, Q_KVEMPTY = 4 /* 3 stages */, Q_SDPFULL = 7 /* 2 */, Q_SDPEMPTY = 9 /* 2 */,
+       Q_DSFULL = 11, Q_DSEMPTY = 12, Q_DONE = 13, Q_DRAIN = 14 };
 
-template <int HD>
+template <int HD, bool MSK, bool DRP>
 __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_constant__ FlashParams p) {
   constexpr int SUB = HD / 64;
-  constexpr int TILE = SUB * kSub;
+  constexpr int TILE = SUB * kSub;          // Q or dO: 128 rows
+  constexpr int KT = SUB * kHalfTile;       // one stage of K or V: 64 rows
+  constexpr int NS = kBwdStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = sm;
   uint8_t* sG = sQ + TILE;            // dO
-  uint8_t* sK = sG + TILE;            // 2 stages
-  uint8_t* sV = sK + 2 * TILE;        // 2 stages
-  uint8_t* sS = sV + 2 * TILE;        // dS [128 x 128] bf16
-  Ctl* ctl = reinterpret_cast<Ctl*>(sS + 2 * kSub);
+  uint8_t* sK = sG + TILE;            // NS stages
+  uint8_t* sV = sK + NS * KT;         // NS stages
+  uint8_t* sS = sV + NS * KT;         // dS [128 queries x 64 keys] bf16
+  Ctl* ctl = reinterpret_cast<Ctl*>(sS + kSub);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const MaskArgs& M = p.m;
   const int nqb = (M.Sq + kBlk - 1) / kBlk;
@@ -515,10 +562,12 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
   const int bh = (int)(blockIdx.x % BH);
   const int b = bh / p.H, h = bh % p.H;
   const int q0 = qb * kBlk;
-  int nkb = (M.Sk + kBlk - 1) / kBlk;
-  if (M.causal) nkb = min(nkb, qb + 1);
-  const int counts[16] = {1, 1, 1, 1, 1, 1, kRowThreads, 1, 1, 1, 1, 1, 1, 1, 1, 1};
-  const uint32_t tmem = setup_cta(ctl, counts, 9, warp, lane);
+  int nsb = (M.Sk + kHalf - 1) / kHalf;                 // key sub-blocks
+  if (M.causal) nsb = min(nsb, 2 * (qb + 1));
+  // counts by barrier index: Q/dO full 1; K/V stage full and empty 1; S/dP full 1, S/dP empty 8 (one per row warp);
+  // dS full 256; the rest 1
+  const int counts[15] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 8, 8, kRowThreads, 1, 1, 1};
+  const uint32_t tmem = setup_cta(ctl, counts, 15, warp, lane);
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   unsigned long long* status = p.status;
   const unsigned long long tmo = p.timeout_ns;
@@ -528,62 +577,72 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
     if (elect_one()) {
       const int cq = head_col(p.q, h), ck = head_col(p.k, h), cv = head_col(p.v, h), cg = head_col(p.dout, h);
       bool ok = true;
-      uint64_t* dbar[3]; uint32_t dpar[3]; bool dis[3] = {false, false, false};
+      uint64_t* dbar[1 + NS]; uint32_t dpar[1 + NS]; bool dis[1 + NS];
+      for (int i = 0; i < 1 + NS; ++i) dis[i] = false;
       mbar_arrive_expect_tx(&bar[Q_QFULL], 2 * TILE);
       load_tile<SUB>(smem_u32(sQ), &p.mq, p.q_seq1, cq, b, q0, smem_u32(&bar[Q_QFULL]));
       load_tile<SUB>(smem_u32(sG), &p.mdo, p.do_seq1, cg, b, q0, smem_u32(&bar[Q_QFULL]));
       dbar[0] = &bar[Q_QFULL]; dpar[0] = 0; dis[0] = true;
-      for (int j = 0; j < nkb && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      for (int j = 0; j < nsb && ok; ++j) {
+        const int st = j % NS;
+        const uint32_t ph = (uint32_t)(j / NS) & 1u;
         if (!mbar_wait(&bar[Q_KVEMPTY + st], ph ^ 1u, abort_flag, status, tmo)) { ok = false; break; }
-        mbar_arrive_expect_tx(&bar[Q_KVFULL + st], 2 * TILE);
-        load_tile<SUB>(smem_u32(sK + st * TILE), &p.mk, p.k_seq1, ck, b, j * kBlk, smem_u32(&bar[Q_KVFULL + st]));
-        load_tile<SUB>(smem_u32(sV + st * TILE), &p.mv, p.v_seq1, cv, b, j * kBlk, smem_u32(&bar[Q_KVFULL + st]));
+        mbar_arrive_expect_tx(&bar[Q_KVFULL + st], 2 * KT);
+        load_tile64<SUB>(smem_u32(sK + st * KT), &p.mk64, p.k_seq1, ck, b, j * kHalf, smem_u32(&bar[Q_KVFULL + st]));
+        load_tile64<SUB>(smem_u32(sV + st * KT), &p.mv64, p.v_seq1, cv, b, j * kHalf, smem_u32(&bar[Q_KVFULL + st]));
         dbar[1 + st] = &bar[Q_KVFULL + st]; dpar[1 + st] = ph; dis[1 + st] = true;
       }
-      if (!ok || *abort_flag) drain_loads(dbar, dpar, dis, 3);
+      if (!ok || *abort_flag) drain_loads(dbar, dpar, dis, 1 + NS);
     }
   } else if (warp == kMmaWarp) {
     if (elect_one()) {
-      const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0), id_q = make_idesc_bf16(128, HD, 0, 1);
+      const uint32_t id_s = make_idesc_bf16(128, kHalf, 0, 0), id_q = make_idesc_bf16(128, HD, 0, 1);
       const uint32_t aQ = smem_u32(sQ), aG = smem_u32(sG), aK = smem_u32(sK), aV = smem_u32(sV), aS = smem_u32(sS);
       bool ok = mbar_wait(&bar[Q_QFULL], 0, abort_flag, status, tmo);
       bool issued = false;
-      for (int j = 0; j < nkb && ok; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&bar[Q_KVFULL + st], (uint32_t)(j >> 1) & 1u, abort_flag, status, tmo)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t kb = aK + st * TILE, vb = aV + st * TILE;
-        // S = Q K^T  (columns 0..127),  dP = dO V^T  (columns 128..255)
+      // S = Q K^T (columns 0..63 of the buffer), dP = dO V^T (columns 64..127)
+      auto issue_sdp = [&](int n) {
+        const uint32_t ks = aK + (n % NS) * KT, vs = aV + (n % NS) * KT, d = tmem + (uint32_t)((n & 1) * 128);
 #pragma unroll
         for (int u = 0; u < SUB; ++u)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem, make_smem_desc(aQ + u * kSub + kk * 32, 16, 1024), make_smem_desc(kb + u * kSub + kk * 32, 16, 1024),
+            umma_bf16(d, make_smem_desc(aQ + u * kSub + kk * 32, 16, 1024), make_smem_desc(ks + u * kHalfTile + kk * 32, 16, 1024),
                       id_s, (u | kk) ? 1u : 0u);
 #pragma unroll
         for (int u = 0; u < SUB; ++u)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem + 128, make_smem_desc(aG + u * kSub + kk * 32, 16, 1024),
-                      make_smem_desc(vb + u * kSub + kk * 32, 16, 1024), id_s, (u | kk) ? 1u : 0u);
-        umma_commit(&bar[Q_SDPFULL]);
-        issued = true;
+            umma_bf16(d + 64, make_smem_desc(aG + u * kSub + kk * 32, 16, 1024),
+                      make_smem_desc(vs + u * kHalfTile + kk * 32, 16, 1024), id_s, (u | kk) ? 1u : 0u);
+        umma_commit(&bar[Q_SDPFULL + (n & 1)]);
+      };
+      if (ok && nsb > 0) ok = mbar_wait(&bar[Q_KVFULL], 0, abort_flag, status, tmo);
+      if (ok && nsb > 0) { tc_fence_after(); issue_sdp(0); issued = true; }
+      for (int j = 0; j < nsb && ok; ++j) {
+        if (j + 1 < nsb) {
+          const int n = j + 1;
+          if (!mbar_wait(&bar[Q_KVFULL + n % NS], (uint32_t)(n / NS) & 1u, abort_flag, status, tmo)) { ok = false; break; }
+          if (!mbar_wait(&bar[Q_SDPEMPTY + (n & 1)], ((uint32_t)(n >> 1) & 1u) ^ 1u, abort_flag, status, tmo)) { ok = false; break; }
+          tc_fence_after();
+          issue_sdp(n);
+        }
         if (!mbar_wait(&bar[Q_DSFULL], (uint32_t)j & 1u, abort_flag, status, tmo)) { ok = false; break; }
         tc_fence_after();
-        // dQ += dS K   (A = dS, K-major over the keys; B = K block read MN-major)
+        // dQ += dS K   (A = dS, K-major over the 64 keys; B = the K stage read MN-major)
+        const uint32_t ks = aK + (j % NS) * KT;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem + 256, make_smem_desc(aS + (kk >> 2) * kSub + (kk & 3) * 32, 16, 1024),
-                    make_smem_desc(kb + kk * 2048, kSub, 1024), id_q, (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&bar[Q_KVEMPTY + st]);
-        if (j == nkb - 1) umma_commit(&bar[Q_DONE]);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tmem + 256, make_smem_desc(aS + kk * 32, 16, 1024), make_smem_desc(ks + kk * 2048, kHalfTile, 1024), id_q,
+                    (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&bar[Q_KVEMPTY + j % NS]);
+        umma_commit(&bar[Q_DSEMPTY]);
+        if (j == nsb - 1) umma_commit(&bar[Q_DONE]);
       }
       if (!ok && issued) drain_mma(&bar[Q_DRAIN]);
     }
   } else {
-    const int wg = warp >> 2, rt = tid & 127;          // column half and row of this thread
+    const int wg = warp >> 2, rt = tid & 127;          // key half and query row of this thread
     const int row = q0 + rt;
     const bool live = row < M.Sq;
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -604,37 +663,42 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
       lse2 = p.lse[(long long)bh * M.Sq + row];
     }
     bool ok = true;
-    for (int j = 0; j < nkb; ++j) {
-      uint32_t good = mbar_wait(&bar[Q_SDPFULL], (uint32_t)j & 1u, abort_flag, status, tmo) ? 1u : 0u;
+    for (int j = 0; j < nsb; ++j) {
+      const int buf = j & 1;
+      uint32_t good = mbar_wait(&bar[Q_SDPFULL + buf], (uint32_t)(j >> 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
       if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
       tc_fence_after();
-      const int col0 = j * kBlk;
-      const bool plain = !M.mask && !M.kpm && !(M.causal && j == qb) && (col0 + kBlk <= M.Sk);
+      float x[32], dp[32];
+      tmem_ld32f(lane_addr + (uint32_t)(buf * 128 + wg * 32), x);
+      tmem_ld32f(lane_addr + (uint32_t)(buf * 128 + 64 + wg * 32), dp);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[Q_SDPEMPTY + buf]);
+      const int col0 = j * kHalf + wg * 32;
+      // the diagonal crosses the last two sub-blocks of a causal query block
+      const bool plain = !(MSK && (M.mask || M.kpm)) && !(M.causal && j >= 2 * qb) && (j * kHalf + kHalf <= M.Sk);
+      score_chunk<32, MSK>(x, row, col0, b, M, plain);
+      uint32_t keep = 0xffffffffu;
+      if constexpr (DRP) keep = keep_bits<32>(M, offset, bh, min(row, M.Sq - 1), col0);
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * wg + cc;
-        float x[32], dp[32];
-        tmem_ld32f(lane_addr + (uint32_t)(c * 32), x);
-        tmem_ld32f(lane_addr + (uint32_t)(128 + c * 32), dp);
-        tmem_ld_wait();
-        score_chunk<32>(x, row, col0 + 32 * c, b, M, plain);
-        uint32_t keep = 0xffffffffu;
-        if (M.thresh) keep = keep_bits<32>(M, offset, bh, min(row, M.Sq - 1), col0 + 32 * c);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pr = exp2f(x[i] - lse2);
-          const float d = ((keep >> i) & 1u) ? dp[i] * M.drop_scale : 0.f;
-          x[i] = pr * (d - delta);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(sS + wg * kSub + sw128(rt, cc * 4 + q)) = pack8f(x + 8 * q);
+      for (int i = 0; i < 32; ++i) {
+        const float pr = ex2_approx(x[i] - lse2);
+        const float d = ((keep >> i) & 1u) ? dp[i] * M.drop_scale : 0.f;
+        x[i] = pr * (d - delta);
       }
-      fence_proxy_async();
+      if (j > 0) {
+        // the product of the previous sub-block must have read the dS tile
+        good = mbar_wait(&bar[Q_DSEMPTY], (uint32_t)(j - 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
+        if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(sS + sw128(rt, wg * 4 + c)) = pack8f(x + 8 * c);
+      fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bar[Q_DSFULL]);
     }
-    if (ok && nkb > 0) {
+    if (ok && nsb > 0) {
       uint32_t good = mbar_wait(&bar[Q_DONE], 0, abort_flag, status, tmo) ? 1u : 0u;
       if (!__all_sync(0xffffffffu, good)) ok = false;
     }
@@ -645,7 +709,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
       for (int cc = 0; cc < HD / 64; ++cc) {
         const int c = wg * (HD / 64) + cc;
         float o[32];
-        if (nkb > 0) {
+        if (nsb > 0) {
           tmem_ld32f(lane_addr + (uint32_t)(256 + c * 32), o);
           tmem_ld_wait();
         } else {
@@ -665,147 +729,225 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dq_kernel(const __grid_cons
 }
 
 // =====================================================================================================  dK / dV
-enum { K_KVFULL = 0, K_QGFULL = 1, K_QGEMPTY = 3, K_SDPFULL = 5, K_DSFULL = 6, K_DONE = 7, K_DRAIN = 8 };
+// CTA = 128 keys of one (batch, head).  The rows of every product are KEYS (transposed formulation), and the queries are
+// walked in sub-blocks of 64:
+//   S^T = K Q^T and dP^T = V dO^T            [128 keys x 64 queries] each, in TMEM, double-buffered
+//   row threads (TMEM lane = key, two threads per key with 32 queries each): P^T and dS^T as bf16 into two
+//                                            [128 x 64] K-major shared tiles
+//   dV += P^T dO,  dK += dS^T Q              contraction over the 64 queries; B = the dO / Q stage read MN-major
+// With 64-query stages three of them fit beside K and V also at head_dim 128, and the double-buffered S^T / dP^T let the
+// products of sub-block i+1 run while the row threads work on sub-block i.  The per-query statistics (log-sum-exp and
+// delta) of a stage are put into shared memory by the producer warp and read as broadcasts.
+enum { K_KVFULL = 0, K_QGFULL = 1 /* 3 stages */, K_QGEMPTY = 4 /* 3 stages */, K_SDPFULL = 7 /* 2 */, K_SDPEMPTY = 9 /* 2 */,
+       K_DSFULL = 11, K_DSEMPTY = 12, K_DONE = 13, K_DRAIN = 14 };
 
-template <int HD, int NS>
+template <int HD, bool MSK, bool DRP>
 __global__ void __launch_bounds__(kThreads, 1) flash_dkv_kernel(const __grid_constant__ FlashParams p) {
   constexpr int SUB = HD / 64;
-  constexpr int TILE = SUB * kSub;
+  constexpr int TILE = SUB * kSub;          // K or V: 128 rows
+  constexpr int QT = SUB * kHalfTile;       // one stage of Q or dO: 64 rows
+  constexpr int NS = kBwdStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = sm;
   uint8_t* sV = sK + TILE;
   uint8_t* sQ = sV + TILE;            // NS stages
-  uint8_t* sG = sQ + NS * TILE;       // NS stages (dO)
-  uint8_t* sP = sG + NS * TILE;       // dropped probabilities [q][keys]
-  uint8_t* sS = sP + 2 * kSub;        // dS [q][keys]
-  Ctl* ctl = reinterpret_cast<Ctl*>(sS + 2 * kSub);
+  uint8_t* sG = sQ + NS * QT;         // NS stages (dO)
+  uint8_t* sP = sG + NS * QT;         // dropped probabilities, transposed: [keys][64 queries]
+  uint8_t* sS = sP + kSub;            // dS transposed
+  Ctl* ctl = reinterpret_cast<Ctl*>(sS + kSub);
+  float* sStat = reinterpret_cast<float*>(sS + kSub + 256);   // per stage: 64 log-sum-exp values, 64 deltas
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const MaskArgs& M = p.m;
-  const int nqb = (M.Sq + kBlk - 1) / kBlk;
+  const int nsub = (M.Sq + kHalf - 1) / kHalf;
   const int BH = p.B * p.H;
   // with a causal mask the first key blocks see the most query blocks: they go first
   const int kb = (int)(blockIdx.x / BH);
   const int bh = (int)(blockIdx.x % BH);
   const int b = bh / p.H, h = bh % p.H;
   const int k0 = kb * kBlk;
-  const int i0 = M.causal ? kb : 0;
-  const int nit = nqb - i0;
-  const int counts[16] = {1, 1, 1, 1, 1, 1, kRowThreads, 1, 1, 1, 1, 1, 1, 1, 1, 1};
-  const uint32_t tmem = setup_cta(ctl, counts, 9, warp, lane);
+  const int s_begin = M.causal ? k0 / kHalf : 0;
+  const int nit = max(nsub - s_begin, 0);
+  // counts by barrier index: K/V full 1; stage full 33 (the copy's issuer + 32 lanes that wrote the statistics); stage
+  // empty 1; S/dP full 1, S/dP empty 8 (one per row warp); dS full 256; the rest 1
+  const int counts[15] = {1, 33, 33, 33, 1, 1, 1, 1, 1, 8, 8, kRowThreads, 1, 1, 1};
+  const uint32_t tmem = setup_cta(ctl, counts, 15, warp, lane);
   volatile uint32_t* abort_flag = &ctl->abort_flag;
   unsigned long long* status = p.status;
   const unsigned long long tmo = p.timeout_ns;
   uint64_t* bar = ctl->bar;
 
   if (warp == kProducerWarp) {
-    if (elect_one()) {
-      const int cq = head_col(p.q, h), ck = head_col(p.k, h), cv = head_col(p.v, h), cg = head_col(p.dout, h);
-      bool ok = true;
-      uint64_t* dbar[3]; uint32_t dpar[3]; bool dis[3] = {false, false, false};
+    // the whole warp walks the stages: lane 0 issues the copies, every lane fetches the statistics of two queries
+    const int cq = head_col(p.q, h), ck = head_col(p.k, h), cv = head_col(p.v, h), cg = head_col(p.dout, h);
+    bool ok = true;
+    uint64_t* dbar[1 + NS]; uint32_t dpar[1 + NS]; bool dis[1 + NS];
+    for (int i = 0; i < 1 + NS; ++i) dis[i] = false;
+    if (lane == 0) {
       mbar_arrive_expect_tx(&bar[K_KVFULL], 2 * TILE);
       load_tile<SUB>(smem_u32(sK), &p.mk, p.k_seq1, ck, b, k0, smem_u32(&bar[K_KVFULL]));
       load_tile<SUB>(smem_u32(sV), &p.mv, p.v_seq1, cv, b, k0, smem_u32(&bar[K_KVFULL]));
       dbar[0] = &bar[K_KVFULL]; dpar[0] = 0; dis[0] = true;
-      for (int it = 0; it < nit && ok; ++it) {
-        const int st = it % NS;
-        const uint32_t ph = (uint32_t)(it / NS) & 1u;
-        if (!mbar_wait(&bar[K_QGEMPTY + st], ph ^ 1u, abort_flag, status, tmo)) { ok = false; break; }
-        mbar_arrive_expect_tx(&bar[K_QGFULL + st], 2 * TILE);
-        load_tile<SUB>(smem_u32(sQ + st * TILE), &p.mq, p.q_seq1, cq, b, (i0 + it) * kBlk, smem_u32(&bar[K_QGFULL + st]));
-        load_tile<SUB>(smem_u32(sG + st * TILE), &p.mdo, p.do_seq1, cg, b, (i0 + it) * kBlk, smem_u32(&bar[K_QGFULL + st]));
+    }
+    for (int it = 0; it < nit; ++it) {
+      const int st = it % NS;
+      const uint32_t ph = (uint32_t)(it / NS) & 1u;
+      const uint32_t good = mbar_wait(&bar[K_QGEMPTY + st], ph ^ 1u, abort_flag, status, tmo) ? 1u : 0u;
+      if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+      const int q0 = (s_begin + it) * kHalf;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&bar[K_QGFULL + st], 2 * QT);
+        load_tile64<SUB>(smem_u32(sQ + st * QT), &p.mq64, p.q_seq1, cq, b, q0, smem_u32(&bar[K_QGFULL + st]));
+        load_tile64<SUB>(smem_u32(sG + st * QT), &p.mdo64, p.do_seq1, cg, b, q0, smem_u32(&bar[K_QGFULL + st]));
         dbar[1 + st] = &bar[K_QGFULL + st]; dpar[1 + st] = ph; dis[1 + st] = true;
       }
-      if (!ok || *abort_flag) drain_loads(dbar, dpar, dis, 1 + NS);
+      float2 ls = make_float2(INFINITY, INFINITY), dl = make_float2(0.f, 0.f);
+      const int q = q0 + 2 * lane;
+      const long long base = (long long)bh * M.Sq;
+      if (q < M.Sq) { ls.x = __ldg(p.lse + base + q); dl.x = __ldg(p.delta + base + q); }
+      if (q + 1 < M.Sq) { ls.y = __ldg(p.lse + base + q + 1); dl.y = __ldg(p.delta + base + q + 1); }
+      float* stat = sStat + st * 2 * kHalf;
+      *reinterpret_cast<float2*>(stat + 2 * lane) = ls;
+      *reinterpret_cast<float2*>(stat + kHalf + 2 * lane) = dl;
+      mbar_arrive(&bar[K_QGFULL + st]);
     }
+    if (lane == 0 && (!ok || *abort_flag)) drain_loads(dbar, dpar, dis, 1 + NS);
   } else if (warp == kMmaWarp) {
     if (elect_one()) {
-      const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0), id_t = make_idesc_bf16(128, HD, 1, 1);
+      const uint32_t id_s = make_idesc_bf16(128, kHalf, 0, 0), id_t = make_idesc_bf16(128, HD, 0, 1);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aG = smem_u32(sG);
       const uint32_t aP = smem_u32(sP), aS = smem_u32(sS);
       bool ok = mbar_wait(&bar[K_KVFULL], 0, abort_flag, status, tmo);
       bool issued = false;
-      for (int it = 0; it < nit && ok; ++it) {
-        const int st = it % NS;
-        if (!mbar_wait(&bar[K_QGFULL + st], (uint32_t)(it / NS) & 1u, abort_flag, status, tmo)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t qb_ = aQ + st * TILE, gb = aG + st * TILE;
-        // S = Q K^T (columns 0..127), dP = dO V^T (columns 128..255): rows = queries
+      // S^T = K Q^T (columns 0..63 of the buffer), dP^T = V dO^T (columns 64..127): rows = keys
+      auto issue_sdp = [&](int n) {
+        const uint32_t qs = aQ + (n % NS) * QT, gs = aG + (n % NS) * QT, d = tmem + (uint32_t)((n & 1) * 128);
 #pragma unroll
         for (int u = 0; u < SUB; ++u)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem, make_smem_desc(qb_ + u * kSub + kk * 32, 16, 1024), make_smem_desc(aK + u * kSub + kk * 32, 16, 1024),
+            umma_bf16(d, make_smem_desc(aK + u * kSub + kk * 32, 16, 1024), make_smem_desc(qs + u * kHalfTile + kk * 32, 16, 1024),
                       id_s, (u | kk) ? 1u : 0u);
 #pragma unroll
         for (int u = 0; u < SUB; ++u)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem + 128, make_smem_desc(gb + u * kSub + kk * 32, 16, 1024),
-                      make_smem_desc(aV + u * kSub + kk * 32, 16, 1024), id_s, (u | kk) ? 1u : 0u);
-        umma_commit(&bar[K_SDPFULL]);
-        issued = true;
+            umma_bf16(d + 64, make_smem_desc(aV + u * kSub + kk * 32, 16, 1024),
+                      make_smem_desc(gs + u * kHalfTile + kk * 32, 16, 1024), id_s, (u | kk) ? 1u : 0u);
+        umma_commit(&bar[K_SDPFULL + (n & 1)]);
+      };
+      if (ok && nit > 0) ok = mbar_wait(&bar[K_QGFULL], 0, abort_flag, status, tmo);
+      if (ok && nit > 0) { tc_fence_after(); issue_sdp(0); issued = true; }
+      for (int it = 0; it < nit && ok; ++it) {
+        if (it + 1 < nit) {
+          const int n = it + 1;
+          if (!mbar_wait(&bar[K_QGFULL + n % NS], (uint32_t)(n / NS) & 1u, abort_flag, status, tmo)) { ok = false; break; }
+          if (!mbar_wait(&bar[K_SDPEMPTY + (n & 1)], ((uint32_t)(n >> 1) & 1u) ^ 1u, abort_flag, status, tmo)) { ok = false; break; }
+          tc_fence_after();
+          issue_sdp(n);
+        }
+        long long* tm = (p.trace && blockIdx.x == 0 && it < 16) ? p.trace + 256 + it * 8 : nullptr;
+        if (tm) tm[0] = clock64();                       // S / dP of the next sub-block issued
         if (!mbar_wait(&bar[K_DSFULL], (uint32_t)it & 1u, abort_flag, status, tmo)) { ok = false; break; }
+        if (tm) tm[1] = clock64();                       // dS written
         tc_fence_after();
-        // dV += P^T dO, dK += dS^T Q: rows = keys; both operands are read MN-major (contraction over the 128 queries)
+        const uint32_t qs = aQ + (it % NS) * QT, gs = aG + (it % NS) * QT;
+        // dV += P^T dO, dK += dS^T Q: A = the transposed tiles (K-major over the 64 queries), B = the stage, MN-major
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem + 256, make_smem_desc(aP + kk * 2048, kSub, 1024), make_smem_desc(gb + kk * 2048, kSub, 1024), id_t,
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tmem + 256, make_smem_desc(aP + kk * 32, 16, 1024), make_smem_desc(gs + kk * 2048, kHalfTile, 1024), id_t,
                     (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem + 256 + HD, make_smem_desc(aS + kk * 2048, kSub, 1024), make_smem_desc(qb_ + kk * 2048, kSub, 1024),
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tmem + 256 + HD, make_smem_desc(aS + kk * 32, 16, 1024), make_smem_desc(qs + kk * 2048, kHalfTile, 1024),
                     id_t, (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&bar[K_QGEMPTY + st]);
+        umma_commit(&bar[K_QGEMPTY + it % NS]);
+        umma_commit(&bar[K_DSEMPTY]);
         if (it == nit - 1) umma_commit(&bar[K_DONE]);
+        if (tm) tm[2] = clock64();                       // dV / dK issued
       }
       if (!ok && issued) drain_mma(&bar[K_DRAIN]);
     }
   } else {
-    const int wg = warp >> 2, rt = tid & 127;          // column half and row of this thread
+    const int wg = warp >> 2, rt = tid & 127;          // query half and key row of this thread
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const unsigned long long offset = M.offset + (M.step_ptr ? __ldg(M.step_ptr) * 65536ull : 0ull);
+    const int key = k0 + rt;
+    bool key_dead = key >= M.Sk;
+    if constexpr (MSK) key_dead = key_dead || (M.kpm && __ldg(M.kpm + (long long)b * M.kpm_ld + key));
+    const bool keys_plain = !(MSK && (M.mask || M.kpm)) && (k0 + kBlk <= M.Sk);
     bool ok = true;
+    long long* tr = (p.trace && blockIdx.x == 0 && lane == 0 && (warp & 3) == 0) ? p.trace + (warp >> 2) * 128 : nullptr;
     for (int it = 0; it < nit; ++it) {
-      const int qb = i0 + it;
-      const int row = qb * kBlk + rt;
-      float delta = 0.f, lse2 = INFINITY;
-      if (row < M.Sq) {
-        delta = __ldg(p.delta + (long long)bh * M.Sq + row);
-        lse2 = __ldg(p.lse + (long long)bh * M.Sq + row);
-      }
-      uint32_t good = mbar_wait(&bar[K_SDPFULL], (uint32_t)it & 1u, abort_flag, status, tmo) ? 1u : 0u;
+      const int st = it % NS, buf = it & 1;
+      const int qbase = (s_begin + it) * kHalf + wg * 32;      // first query of this thread
+      if (tr && it < 16) tr[it * 8 + 0] = clock64();
+      uint32_t good = mbar_wait(&bar[K_QGFULL + st], (uint32_t)(it / NS) & 1u, abort_flag, status, tmo) ? 1u : 0u;
+      if (tr && it < 16) tr[it * 8 + 1] = clock64();
+      if (good) good = mbar_wait(&bar[K_SDPFULL + buf], (uint32_t)(it >> 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
       if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
       tc_fence_after();
-      const bool plain = !M.mask && !M.kpm && !(M.causal && qb == kb) && (k0 + kBlk <= M.Sk);
+      if (tr && it < 16) tr[it * 8 + 2] = clock64();
+      float x[32], dp[32];
+      tmem_ld32f(lane_addr + (uint32_t)(buf * 128 + wg * 32), x);
+      tmem_ld32f(lane_addr + (uint32_t)(buf * 128 + 64 + wg * 32), dp);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[K_SDPEMPTY + buf]);
+      if (tr && it < 16) tr[it * 8 + 3] = clock64();
+      // the diagonal crosses the first two sub-blocks of a causal key block
+      const bool plain = keys_plain && !(M.causal && it < 2);
+      const float4* lse4 = reinterpret_cast<const float4*>(sStat + st * 2 * kHalf + wg * 32);
+      const float4* del4 = reinterpret_cast<const float4*>(sStat + st * 2 * kHalf + kHalf + wg * 32);
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = 2 * wg + cc;
-        float x[32], dp[32];
-        tmem_ld32f(lane_addr + (uint32_t)(c * 32), x);
-        tmem_ld32f(lane_addr + (uint32_t)(128 + c * 32), dp);
-        tmem_ld_wait();
-        score_chunk<32>(x, row, k0 + 32 * c, b, M, plain);
-        uint32_t keep = 0xffffffffu;
-        if (M.thresh) keep = keep_bits<32>(M, offset, bh, min(row, M.Sq - 1), k0 + 32 * c);
+      for (int g = 0; g < 8; ++g) {
+        const float4 L4 = lse4[g], D4 = del4[g];
+        const float lse_[4] = {L4.x, L4.y, L4.z, L4.w}, del_[4] = {D4.x, D4.y, D4.z, D4.w};
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pr = exp2f(x[i] - lse2);
-          const bool kp = (keep >> i) & 1u;
+        for (int e = 0; e < 4; ++e) {
+          const int i = 4 * g + e;
+          const int q = qbase + i;
+          float xs = x[i] * M.scale_log2;
+          if (!plain) {
+            if constexpr (MSK) {
+              if (M.mask && q < M.Sq && key < M.Sk) {
+                const long long mi = (long long)q * M.mask_ld + key;
+                xs += (M.mask_fp32 ? __ldg(reinterpret_cast<const float*>(M.mask) + mi)
+                                   : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(M.mask) + mi))) * kLog2e;
+              }
+            }
+            if (key_dead || (M.causal && key > q)) xs = -INFINITY;
+          }
+          const float pr = ex2_approx(xs - lse_[e]);
+          bool kp = true;
+          if constexpr (DRP) {
+            const unsigned long long idx = ((unsigned long long)bh * M.Sq + min(q, M.Sq - 1)) * (unsigned long long)M.Sk + key;
+            kp = dropout_keep(M.seed, offset, idx, M.thresh);
+          }
           const float d = kp ? dp[i] * M.drop_scale : 0.f;
-          dp[i] = pr * (d - delta);               // dS
+          dp[i] = pr * (d - del_[e]);             // dS
           x[i] = kp ? pr * M.drop_scale : 0.f;    // dropped probability
         }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t off = (uint32_t)wg * kSub + sw128(rt, cc * 4 + q);
-          *reinterpret_cast<uint4*>(sP + off) = pack8f(x + 8 * q);
-          *reinterpret_cast<uint4*>(sS + off) = pack8f(dp + 8 * q);
-        }
       }
-      fence_proxy_async();
+      if (tr && it < 16) tr[it * 8 + 4] = clock64() + (x[0] == 12345.f ? 1 : 0);
+      if (it > 0) {
+        // the products of the previous sub-block must have read the two tiles
+        good = mbar_wait(&bar[K_DSEMPTY], (uint32_t)(it - 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
+        if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+      }
+      if (tr && it < 16) tr[it * 8 + 5] = clock64();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t off = sw128(rt, wg * 4 + c);
+        *reinterpret_cast<uint4*>(sP + off) = pack8f(x + 8 * c);
+        *reinterpret_cast<uint4*>(sS + off) = pack8f(dp + 8 * c);
+      }
+      if (tr && it < 16) tr[it * 8 + 6] = clock64();
+      fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bar[K_DSFULL]);
+      if (tr && it < 16) tr[it * 8 + 7] = clock64();
     }
     if (ok && nit > 0) {
       uint32_t good = mbar_wait(&bar[K_DONE], 0, abort_flag, status, tmo) ? 1u : 0u;
@@ -813,7 +955,6 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dkv_kernel(const __grid_con
     }
     if (ok) {
       tc_fence_after();
-      const int key = k0 + rt;
       __nv_bfloat16* dvp = key < M.Sk ? row_ptr(p.dv, b, key, h) : nullptr;
       __nv_bfloat16* dkp = key < M.Sk ? row_ptr(p.dk, b, key, h) : nullptr;
 #pragma unroll
@@ -844,6 +985,7 @@ __global__ void __launch_bounds__(kThreads, 1) flash_dkv_kernel(const __grid_con
 
 // =====================================================================================================  host
 thread_local std::string g_ferr;
+long long* g_flash_trace = nullptr;
 int ffail(const std::string& s) { g_ferr = s; return -1; }
 
 uint32_t thresh_of(float pdrop) {
@@ -854,7 +996,7 @@ uint32_t thresh_of(float pdrop) {
 }
 
 // 3-D map {width columns, dim1, dim2} over a [batch, seq, width] view; the dimension with the smaller stride comes first.
-int make_map3(CUtensorMap* m, int* seq1, const RtpFlashRef& r, int B, int S, const char* what) {
+int make_map3(CUtensorMap* m, int* seq1, const RtpFlashRef& r, int B, int S, const char* what, unsigned rows = 128u) {
   EncodeTiledFn enc = get_encode_tiled();
   if (!enc) return ffail("cuTensorMapEncodeTiled entry point not found");
   if ((reinterpret_cast<uintptr_t>(r.ptr) & 15) != 0) return ffail(std::string(what) + ": base is not 16-byte aligned");
@@ -865,7 +1007,7 @@ int make_map3(CUtensorMap* m, int* seq1, const RtpFlashRef& r, int B, int S, con
   cuuint64_t dims[3] = {(cuuint64_t)r.width, (cuuint64_t)(s_first ? S : B), (cuuint64_t)(s_first ? B : S)};
   cuuint64_t strides[2] = {(cuuint64_t)(s_first ? r.ss : r.sb) * 2, (cuuint64_t)(s_first ? r.sb : r.ss) * 2};
   if (B == 1) strides[1] = strides[0] * (cuuint64_t)S;   // a single batch: any legal pitch
-  cuuint32_t box[3] = {64u, s_first ? 128u : 1u, s_first ? 1u : 128u};
+  cuuint32_t box[3] = {64u, s_first ? rows : 1u, s_first ? 1u : rows};
   cuuint32_t estr[3] = {1u, 1u, 1u};
   CUresult rc = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, r.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -902,6 +1044,7 @@ int fill_common(const RtpFlashArgs* a, FlashParams& P) {
   P.m.seed = a->seed; P.m.offset = a->offset; P.m.step_ptr = a->step_ptr;
   P.status = a->status;
   P.timeout_ns = 2000000000ull;
+  P.trace = g_flash_trace;
   P.lse = a->lse;
   P.delta = a->delta;
   if (check_ref(a->q, "q", a->head_dim) || check_ref(a->k, "k", a->head_dim) || check_ref(a->v, "v", a->head_dim) ||
@@ -914,10 +1057,12 @@ int fill_common(const RtpFlashArgs* a, FlashParams& P) {
   return 0;
 }
 constexpr int smem_fwd(int hd) { return 1024 + (hd / 64) * kSub * 5 + 2 * kSub + 256 + (int)sizeof(Xchg); }
-constexpr int smem_dq(int hd) { return 1024 + (hd / 64) * kSub * 6 + 2 * kSub + 256; }
-constexpr int smem_dkv(int hd, int ns) { return 1024 + (hd / 64) * kSub * (2 + 2 * ns) + 4 * kSub + 256; }
+constexpr int smem_dq(int hd) { return 1024 + (hd / 64) * (2 * kSub + 2 * kBwdStages * kHalfTile) + kSub + 256; }
+constexpr int smem_dkv(int hd) {
+  return 1024 + (hd / 64) * (2 * kSub + 2 * kBwdStages * kHalfTile) + 2 * kSub + 256 + kBwdStages * 2 * kHalf * 4;
+}
 static_assert(sizeof(Ctl) <= 256, "control block");
-static_assert(smem_dq(128) <= 232448 && smem_dkv(128, 1) <= 232448 && smem_dkv(64, 2) <= 232448, "shared memory budget");
+static_assert(smem_dq(128) <= 232448 && smem_dkv(128) <= 232448 && smem_fwd(128) <= 232448, "shared memory budget");
 
 template <auto Kern>
 int launch_flash(const FlashParams& P, int grid, int smem, cudaStream_t stream, const char* what) {
@@ -933,14 +1078,21 @@ int launch_flash(const FlashParams& P, int grid, int smem, cudaStream_t stream, 
 extern "C" {
 
 const char* rtp_flash_last_error(void) { return g_ferr.c_str(); }
+void rtp_flash_debug_set_trace(long long* device_buffer_512_words) { g_flash_trace = device_buffer_512_words; }
 
 int rtp_flash_fwd(const RtpFlashArgs* a, void* stream) {
   static thread_local FlashParams P;
   if (fill_common(a, P)) return -1;
   if (!a->lse) return ffail("flash attention: lse buffer required");
   const int grid = ((a->Sq + kBlk - 1) / kBlk) * a->B * a->H;
-  if (a->head_dim == 64) return launch_flash<flash_fwd_kernel<64>>(P, grid, smem_fwd(64), (cudaStream_t)stream, "flash_fwd");
-  return launch_flash<flash_fwd_kernel<128>>(P, grid, smem_fwd(128), (cudaStream_t)stream, "flash_fwd");
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool msk = a->mask || a->kpm, drp = P.m.thresh != 0;
+#define RTP_FWD(HD, MSK, DRP) launch_flash<flash_fwd_kernel<HD, MSK, DRP>>(P, grid, smem_fwd(HD), s, "flash_fwd")
+#define RTP_FWD_HD(HD) (msk ? (drp ? RTP_FWD(HD, true, true) : RTP_FWD(HD, true, false)) \
+                            : (drp ? RTP_FWD(HD, false, true) : RTP_FWD(HD, false, false)))
+  return a->head_dim == 64 ? RTP_FWD_HD(64) : RTP_FWD_HD(128);
+#undef RTP_FWD_HD
+#undef RTP_FWD
 }
 
 int rtp_flash_bwd(const RtpFlashArgs* a, void* stream) {
@@ -951,16 +1103,24 @@ int rtp_flash_bwd(const RtpFlashArgs* a, void* stream) {
       check_ref(a->dv, "dv", a->head_dim))
     return -1;
   if (make_map3(&P.mdo, &P.do_seq1, a->dout, a->B, a->Sq, "dout")) return -1;
+  if (make_map3(&P.mq64, &P.q_seq1, a->q, a->B, a->Sq, "q", 64u)) return -1;
+  if (make_map3(&P.mdo64, &P.do_seq1, a->dout, a->B, a->Sq, "dout", 64u)) return -1;
+  if (make_map3(&P.mk64, &P.k_seq1, a->k, a->B, a->Sk, "k", 64u)) return -1;
+  if (make_map3(&P.mv64, &P.v_seq1, a->v, a->B, a->Sk, "v", 64u)) return -1;
   P.dout = dref(a->dout); P.dq = dref(a->dq); P.dk = dref(a->dk); P.dv = dref(a->dv);
   const int gq = ((a->Sq + kBlk - 1) / kBlk) * a->B * a->H;
   const int gk = ((a->Sk + kBlk - 1) / kBlk) * a->B * a->H;
   cudaStream_t s = (cudaStream_t)stream;
-  if (a->head_dim == 64) {
-    if (launch_flash<flash_dq_kernel<64>>(P, gq, smem_dq(64), s, "flash_dq")) return -1;
-    return launch_flash<flash_dkv_kernel<64, 2>>(P, gk, smem_dkv(64, 2), s, "flash_dkv");
-  }
-  if (launch_flash<flash_dq_kernel<128>>(P, gq, smem_dq(128), s, "flash_dq")) return -1;
-  return launch_flash<flash_dkv_kernel<128, 1>>(P, gk, smem_dkv(128, 1), s, "flash_dkv");
+  const bool msk = a->mask || a->kpm, drp = P.m.thresh != 0;
+#define RTP_BWD(HD, MSK, DRP)                                                                              \
+  (launch_flash<flash_dq_kernel<HD, MSK, DRP>>(P, gq, smem_dq(HD), s, "flash_dq")                          \
+       ? -1                                                                                                \
+       : launch_flash<flash_dkv_kernel<HD, MSK, DRP>>(P, gk, smem_dkv(HD), s, "flash_dkv"))
+#define RTP_BWD_HD(HD) (msk ? (drp ? RTP_BWD(HD, true, true) : RTP_BWD(HD, true, false)) \
+                            : (drp ? RTP_BWD(HD, false, true) : RTP_BWD(HD, false, false)))
+  return a->head_dim == 64 ? RTP_BWD_HD(64) : RTP_BWD_HD(128);
+#undef RTP_BWD_HD
+#undef RTP_BWD
 }
 
 }  // extern "C"

@@ -42,6 +42,9 @@ typedef struct {
 int rtp_flash_fwd(const RtpFlashArgs* a, void* stream);
 int rtp_flash_bwd(const RtpFlashArgs* a, void* stream);   // two launches: dQ (+ delta), then dK / dV
 const char* rtp_flash_last_error(void);
+// Tuning aid: while a device buffer of 512 64-bit words is set, CTA 0 of the forward kernel stamps the SM clock at the
+// steps of its first 16 key blocks (row warps 0 and 4: words 0..255, UMMA issuer: 256..383).  Null switches it off.
+void rtp_flash_debug_set_trace(long long* device_buffer_512_words);
 
 #ifdef __cplusplus
 }

@@ -12,6 +12,50 @@ def use_kernels(x: torch.Tensor) -> bool:
     return x.is_cuda and x.dtype == torch.bfloat16 and get_backend() != "functional"
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# Recomputed activations.  The output of a cheap elementwise / normalisation op is usually consumed by a rotated linear,
+# which would save it for its weight gradient although the op's own backward already keeps the op's INPUT.  Such outputs
+# are tagged with how to rebuild them; a fused linear that receives a tagged tensor saves the (already saved) sources
+# instead and rebuilds its input in backward, so the output lives only between the two forward launches.  For a GPT
+# block this removes the [tokens, 4 d_model] GELU output and both LayerNorm outputs from the saved set (6 of 17
+# d_model-sized rows per token and layer) for one extra elementwise pass each in backward.
+# ---------------------------------------------------------------------------------------------------------------------
+_RECOMPUTE = True
+
+
+def set_activation_recompute(on: bool) -> bool:
+    """Turns the tagging on or off (default on); returns the previous setting."""
+    global _RECOMPUTE
+    old, _RECOMPUTE = _RECOMPUTE, bool(on)
+    return old
+
+
+def _tag(out: torch.Tensor, kind: str, *srcs):
+    if _RECOMPUTE and torch.is_grad_enabled():
+        out._rtp_recompute = (kind, srcs)
+    return out
+
+
+def recompute_tag(x: torch.Tensor):
+    """The (kind, sources) tag of a tensor produced by one of the ops below, or None."""
+    return getattr(x, "_rtp_recompute", None)
+
+
+def recompute(kind: str, srcs):
+    """Rebuilds a tagged tensor from its sources."""
+    from . import kernels as K
+    if kind == "gelu":
+        return K.gelu_fwd(srcs[0])
+    if kind == "swiglu":
+        g, u = srcs
+        return K.swiglu_fwd(g.reshape(-1, g.shape[-1]), u.reshape(-1, u.shape[-1])).view(g.shape)
+    if kind == "norm":
+        x, weight, bias, eps, rms = srcs
+        y = K.norm_fwd(x.reshape(-1, x.shape[-1]), None, weight, bias, eps=eps, rms=rms, save_h=False)[0]
+        return y.view(x.shape)
+    raise ValueError(f"unknown recompute kind {kind!r}")
+
+
 class _NormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, eps, rms):
@@ -33,13 +77,15 @@ class _NormFn(torch.autograd.Function):
 
 def layer_norm(x, weight, bias, eps=1e-5):
     if use_kernels(x) and x.shape[-1] % 8 == 0:
-        return _NormFn.apply(x, weight, bias, eps, False)
+        y = _NormFn.apply(x, weight, bias, eps, False)
+        return _tag(y, "norm", x, weight, bias, eps, False) if x.is_contiguous() else y
     return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
 
 
 def rms_norm(x, weight, eps=1e-5):
     if use_kernels(x) and x.shape[-1] % 8 == 0:
-        return _NormFn.apply(x, weight, None, eps, True)
+        y = _NormFn.apply(x, weight, None, eps, True)
+        return _tag(y, "norm", x, weight, None, eps, True) if x.is_contiguous() else y
     xf = x.float()
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
 
@@ -129,7 +175,8 @@ class _GeluFn(torch.autograd.Function):
 
 def gelu(x):
     if use_kernels(x) and x.numel() % 8 == 0:
-        return _GeluFn.apply(x)
+        y = _GeluFn.apply(x)
+        return _tag(y, "gelu", x) if x.is_contiguous() else y
     return F.gelu(x)
 
 
@@ -154,5 +201,8 @@ class _SwigluFn(torch.autograd.Function):
 def swiglu(g, u):
     """silu(g) * u."""
     if use_kernels(g) and g.shape[-1] % 8 == 0:
-        return _SwigluFn.apply(g, u)
+        # halves of a packed projection arrive as strided views: the contiguous copies made here are the tensors the
+        # kernel's backward keeps, and the ones a following linear rebuilds its input from
+        g, u = g.contiguous(), u.contiguous()
+        return _tag(_SwigluFn.apply(g, u), "swiglu", g, u)
     return F.silu(g) * u

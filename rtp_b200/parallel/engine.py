@@ -252,7 +252,7 @@ class LinSpec:
     the rotated module (it carries the ``_displaced`` flag of the in-place mode)."""
 
     __slots__ = ("ring", "flat", "has_bias", "bias_off", "shard_bytes", "row", "in_f", "out_f", "places", "owner",
-                 "inplace", "grad_mode")
+                 "inplace", "grad_mode", "recompute")
 
     def __init__(self, ring, flat, has_bias, bias_off, row, in_f, out_f, places, owner=None, inplace=False):
         self.ring, self.flat, self.has_bias, self.bias_off = ring, flat, has_bias, bias_off
@@ -260,6 +260,9 @@ class LinSpec:
         self.row, self.in_f, self.out_f, self.places, self.owner, self.inplace = row, in_f, out_f, places, owner, inplace
         # a spec is built per call, outside autograd.Function.forward (which always runs with grad mode off)
         self.grad_mode = torch.is_grad_enabled()
+        # (kind, sources) when the input of this call can be rebuilt in backward instead of being kept (see
+        # ops.functional.recompute), else None
+        self.recompute = None
 
     @property
     def info(self):
@@ -368,14 +371,30 @@ class _FusedSubLinearFn(torch.autograd.Function):
         else:
             y = linear_fwd_raw(eng, spec.flat, spec.info, x2d, spec.row, spec.in_f, spec.out_f)
         ctx.spec, ctx.eng = spec, eng
-        ctx.save_for_backward(x2d)
+        # an input that its producer can rebuild is not kept: its sources (which the producer's own backward keeps
+        # anyway) are saved instead
+        rc = getattr(spec, "recompute", None) if needs_bwd else None
+        ctx.rc_kind = None
+        if rc is not None:
+            kind, srcs = rc
+            ctx.rc_kind, ctx.rc_is_tensor = kind, [torch.is_tensor(a) for a in srcs]
+            ctx.rc_consts = [a for a in srcs if not torch.is_tensor(a)]
+            ctx.save_for_backward(*[a for a in srcs if torch.is_tensor(a)])
+        else:
+            ctx.save_for_backward(x2d)
         ctx.x_shape = x.shape
         return y.view(*x.shape[:-1], spec.out_f)
 
     @staticmethod
     def backward(ctx, dy):
         spec = ctx.spec
-        (x2d,) = ctx.saved_tensors
+        if ctx.rc_kind is not None:
+            from ..ops import functional as FO
+            tensors, consts = list(ctx.saved_tensors), list(ctx.rc_consts)
+            srcs = [tensors.pop(0) if is_t else consts.pop(0) for is_t in ctx.rc_is_tensor]
+            x2d = _as_2d(FO.recompute(ctx.rc_kind, srcs))
+        else:
+            (x2d,) = ctx.saved_tensors
         dy2d = _as_2d(dy)
         if spec.inplace and spec.ring.world > 1:
             dx, gflat = _inplace_linear_bwd(ctx.eng, spec, x2d, dy2d, ctx.needs_input_grad[1])
@@ -404,6 +423,7 @@ def fused_linear(module, x, row=False):
     lin = module.linear
     spec = linear_spec(module, row, module.in_features, module.out_features, lin.weight, lin.bias)
     params = [p for p in (lin.weight, lin.bias) if p is not None]
+    spec.recompute = getattr(x, "_rtp_recompute", None)
     return _FusedSubLinearFn.apply(spec, x, *params)
 
 
@@ -685,6 +705,7 @@ def fused_mha(owner, sub, x, *, is_causal=False, attn_mask=None, key_padding_mas
                             (o_ob - o_ow, sub.out_proj.bias.numel(), sub.out_proj.bias.shape)])
     if spec_out is None:
         return _mha_inplace(owner, sub, x, is_causal, attn_mask, key_padding_mask, training), None
+    spec_qkv.recompute = getattr(x, "_rtp_recompute", None)
     qkv = _FusedSubLinearFn.apply(spec_qkv, x, sub.in_proj_weight, sub.in_proj_bias)       # [.., 3E] grouped per shard
     qkv2d = qkv.reshape(-1, 3 * E)
     causal = bool(is_causal) and attn_mask is None

@@ -88,6 +88,7 @@ class FlyweightWarpper(RotatedModule):
                 return NotImplemented
             spec = E.linear_spec(self, row, in_f, out_f, mod.weight, mod.bias)
             params = [p for p in (mod.weight, mod.bias) if p is not None]
+            spec.recompute = getattr(args[0], "_rtp_recompute", None)
             return E._FusedSubLinearFn.apply(spec, args[0], *params)
         if isinstance(mod, nn.Embedding):
             if len(args) != 1 or kwargs or not fused.use_fused(flat, flat):

@@ -36,3 +36,19 @@ def test_rank_leaving_between_steps_is_seen_before_the_next_launch():
            "--master-port", "29721", os.path.join(HERE, "_multi_gpu_leave_worker.py")]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=200)
     assert "DETECTED rank 1 left" in p.stdout and "NOT_DETECTED" not in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_mnist_example_trains_on_two_gpus_with_the_wrapper_on_the_fused_kernels():
+    """The reference's MNIST example (rtp_mnist.py) through RotatedTensorParallel(Net) in bf16: conv, linear and the
+    10-class head go through the wrapper's fused dispatch; the run must finish and learn the synthetic digits."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "rtp_b200.bench.mnist", "--gpus", "2", "--epochs", "2", "--train-samples", "1024",
+           "--test-samples", "256", "--dtype", "bf16", "--mode", "rtp"]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240, cwd=os.path.dirname(HERE))
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    lines = [ln for ln in p.stdout.splitlines() if "Test accuracy" in ln]
+    assert len(lines) == 2, p.stdout[-3000:]
+    first, last = (float(ln.split("Loss:")[1].split()[0]) for ln in (lines[0], lines[-1]))
+    assert last < first, lines
