@@ -66,6 +66,9 @@ def parse():
     ap.add_argument("--path", default="trainer", choices=["trainer", "module"],
                     help="README config of this framework: the fused trainer (default) or rotated modules + autograd "
                          "with a torch-style loop and ShardedAdam")
+    ap.add_argument("--keep-grads", action="store_true",
+                    help="fused trainer: keep every gradient until one Adam launch at the end of the step (more memory, "
+                         "a few launches fewer) instead of updating each decoder layer right after its backward")
     ap.add_argument("--adam-state", default="mixed", choices=["fp32", "mixed", "bf16"],
                     help="dtype policy of the Adam moments of this framework: mixed (default here) = first moment bf16, "
                          "second moment fp32; fp32 = both fp32 (the library's default); bf16 = both bf16, which is what "
@@ -239,10 +242,10 @@ def run_ours(args, cfg, rank, local, world):
             if p.dim() > 1:
                 p.uniform_(-cfg["initrange"], cfg["initrange"])
     model = model.to(device=dev, dtype=torch.bfloat16)
-    # keep_grads=None: a large model runs each layer's Adam update right after its backward (the gradients share one
-    # scratch buffer), a small one keeps the gradients and updates in one launch
+    # optimizer in backward (default): the gradients of one decoder layer share a scratch buffer and the layer's Adam
+    # update runs right after its backward; --keep-grads keeps every gradient and updates in one launch at the end
     trainer = FusedLMTrainer(model, lr=cfg["lr"], clip_value=cfg["clip"], use_graph=not args.no_graph,
-                             state_dtype=args.adam_state, keep_grads=None)
+                             state_dtype=args.adam_state, keep_grads=args.keep_grads)
     nb = max(8, args.steps + args.warmup)
     pinned = synthetic_batches(cfg, min(nb, 64), rank)
     dev_batches = [(a.to(dev), b.to(dev)) for a, b in pinned]

@@ -90,8 +90,14 @@ typedef struct {
   int grad_accumulate;             // 1: add the weight gradient to what grad_home already holds
   int bank, no_self_push;          // cross-launch prefetch, see RtpLinearFwd
   const void* next_home; unsigned long long next_bytes; int next_kind;
+  // Optional row of M ones (bf16).  Where rtp_linear_bwd_folds_bias() says yes and dbias_full is null, the bias gradient
+  // is one more GEMM phase of the launch (ones[1, M] x dy[M, out], fp32 accumulation) and needs no column-sum kernel.
+  const void* ones;
 } RtpLinearBwd;
 int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream);
+// 1 if the launch described by `op` computes the bias gradient itself from op->ones (1-rank ring, tiles on single CTAs,
+// M a multiple of 8), 0 if the caller has to supply the column sums in dbias_full.
+int rtp_linear_bwd_folds_bias(const RtpRing* ring, const RtpLinearBwd* op);
 
 // Rotating experts (MoE): rank r owns n_local whole experts; x / y hold the dispatched tokens expert-major
 // ([world*n_local*cap, features], expert g = rows [g*cap, (g+1)*cap)).  One launch applies ONE linear of every
@@ -182,6 +188,11 @@ int rtp_ws_ipc_get(void* ws, void* handle64);                    // 64-byte cuda
 int rtp_ws_ipc_open(const void* handle64, void** out);
 int rtp_ws_ipc_close(void* mapped);
 int rtp_ws_status(void* ws, unsigned long long* host_out, void* stream);  // reads the status word (synchronises stream)
+// Race-detection aid: copies the arrive[], done[] and uses[] counters of this rank's flag block to host_out
+// (3 * rtp_ws_num_counters() words; synchronises the stream).  At a quiescent point uses[] must be the same on every
+// rank of the ring and arrive[c] == done[c] == uses[c] * CTAs for every slot counter c.
+int rtp_ws_num_counters(void);
+int rtp_ws_counters(void* ws, unsigned long long* host_out, void* stream);
 void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i, int world);   // logical weight slot i = bank * 8 + index
 void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i, int world);
 int rtp_sm_count(void);

@@ -439,19 +439,9 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
       const float m_new = need ? cand : m_used;
       const float mref = (m_new == -INFINITY) ? 0.f : m_new;
       const float mul = plain ? M.scale_log2 : 1.f;
-      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
-#pragma unroll
-      for (int i = 0; i < 64; i += 4) {
-        s[i] = ex2_approx(fmaf(s[i], mul, -mref));
-        s[i + 1] = ex2_approx(fmaf(s[i + 1], mul, -mref));
-        s[i + 2] = ex2_approx(fmaf(s[i + 2], mul, -mref));
-        s[i + 3] = ex2_approx(fmaf(s[i + 3], mul, -mref));
-        r0 += s[i]; r1 += s[i + 1]; r2 += s[i + 2]; r3 += s[i + 3];
-      }
-      const float rs = (r0 + r1) + (r2 + r3);
-      if (tr && j < 16) tr[j * 8 + 4] = clock64() + (rs < -1.f ? 1 : 0);
       if (j > 0) {
-        // P V of the previous block must be complete before the P tile is overwritten and before O is rescaled
+        // P V of the previous block must be complete before the P tile is overwritten and before O is rescaled (it was
+        // issued a whole block ago: this wait is almost always over at once)
         good = mbar_wait(&bar[F_PVDONE], (uint32_t)(j - 1) & 1u, abort_flag, status, tmo) ? 1u : 0u;
         if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
         tc_fence_after();
@@ -470,20 +460,26 @@ __global__ void __launch_bounds__(kThreads, 1) flash_fwd_kernel(const __grid_con
           l *= alpha;
         }
       }
-      m_used = m_new;
-      l += rs;
-      if (tr && j < 16) tr[j * 8 + 5] = clock64();
-      if constexpr (DRP) {
+      if (tr && j < 16) tr[j * 8 + 4] = clock64();
+      // exponentials and the stores of P, eight columns at a time: the stores of one group issue while the special-
+      // function unit works on the next (the 64 ex2 of a thread are what bounds this loop)
+      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const uint32_t keep = keep_bits<32>(M, offset, bh, min(row, M.Sq - 1), col0 + 32 * c);
+      for (int c = 0; c < 8; ++c) {
+        float* e = s + 8 * c;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) s[32 * c + i] = ((keep >> i) & 1u) ? s[32 * c + i] * M.drop_scale : 0.f;
+        for (int i = 0; i < 8; ++i) e[i] = ex2_approx(fmaf(e[i], mul, -mref));
+        r0 += e[0] + e[4]; r1 += e[1] + e[5]; r2 += e[2] + e[6]; r3 += e[3] + e[7];
+        if constexpr (DRP) {
+          const uint32_t keep = keep_bits<8>(M, offset, bh, min(row, M.Sq - 1), col0 + 8 * c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) e[i] = ((keep >> i) & 1u) ? e[i] * M.drop_scale : 0.f;
         }
+        *reinterpret_cast<uint4*>(sP + wg * kSub + sw128(rt, c)) = pack8f(e);
       }
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(sP + wg * kSub + sw128(rt, c)) = pack8f(s + 8 * c);
+      m_used = m_new;
+      l += (r0 + r1) + (r2 + r3);
+      if (tr && j < 16) tr[j * 8 + 5] = clock64();
       if (tr && j < 16) tr[j * 8 + 6] = clock64();
       fence_proxy_async_smem();
       tc_fence_before();

@@ -173,12 +173,15 @@ int push_cta_policy(int ctas) {
   if (r >= ctas) r = 0;
   return r;
 }
-// Geometry of the small push ring (RTP_PUSH_RING): 0 = four 3840-byte chunks in flight per CTA, 1 = two of 7680 bytes.
+// How the pusher warp moves a shard (RTP_PUSH_RING): 2 = plain loads and peer stores through registers (default); bulk
+// copies through a shared-memory ring per CTA: 0 / 3 = four 3840-byte chunks, completion awaited 3 / 12 copies behind the
+// issue point; 1 / 4 = two 7680-byte chunks, 1 / 8 copies behind.
 int push_ring_policy() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("RTP_PUSH_RING");
-    v = e ? (atoi(e) == 1 ? 1 : 0) : 0;
+    v = e ? atoi(e) : 2;
+    if (v < 0 || v > 4) v = 2;
   }
   return v;
 }
@@ -435,6 +438,13 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
   return add_prefetch_pushes(R, P, op.next_home, op.next_bytes, 1 - op.bank, op.next_kind);
 }
 
+// Whether a backward launch computes its bias gradient as a GEMM phase of its own (see RtpLinearBwd::ones).  Needs the
+// pair decision of the launch to have been made (decide_pair).
+bool folds_bias(const RtpRing& R, const RtpLinearBwd& op) {
+  return R.world == 1 && !pair_mode() && op.M % 8 == 0 && op.out_features % 8 == 0 &&
+         (reinterpret_cast<uintptr_t>(op.ones) & 15) == 0;
+}
+
 int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   // Backward on a ring of N ranks.  Rank r visits the shards in the order r-1, r-2, ..., r (step s handles shard
   // j = r-1-s; weights are pushed by their owners into weight slot s).  The weight gradient of shard j computed here
@@ -444,7 +454,7 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   // GEMM phases of a launch are free to run concurrently across the grid.
   init_program(P);
   const int N = R.world, r = R.rank;
-  if (N < 1 || N > RTP_MAX_WORLD || 2 * N + 1 > RTP_MAX_PHASES) return fail("world size out of range");
+  if (N < 1 || N > RTP_MAX_WORLD || 2 * N + 2 > RTP_MAX_PHASES) return fail("world size out of range");
   const bool col = op.mode == 0;
   if (col ? (op.out_features % N) : (op.in_features % N)) return fail("features not divisible by world size");
   const int Os = col ? op.out_features / N : op.out_features;
@@ -506,6 +516,23 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
       }
       set_vec_ok(ph);
     }
+  }
+  if (op.bias_off >= 0 && !op.dbias_full && op.ones && folds_bias(R, op)) {
+    // ---- bias gradient as a GEMM: db[1, out] = ones[1, M] dy[M, out].  One row of A is real, the rest of the 128-row
+    //      tile is zero fill; the few extra tiles ride in the grid beside the weight-gradient tiles.
+    if (make_map_k(&P.maps[4], op.ones, 1, op.M, op.M)) return -1;
+    if (make_map_mn3(&P.maps[5], op.dy, op.out_features, op.M, op.ldy, (op.out_features % 64 == 0) ? 2 : 0, &P.map3d[5]))
+      return -1;
+    RtpPhase& ph = P.phases[np++];
+    init_phase(ph);
+    ph.a_map = 4; ph.a_mn = 0;
+    ph.b_map = 5; ph.b_mn = 1;
+    ph.M = 1; ph.N = op.out_features; ph.K = op.M;
+    ph.bn = 128;
+    __nv_bfloat16* db = reinterpret_cast<__nv_bfloat16*>(op.grad_home) + op.bias_off;
+    ph.d = db; ph.ldd = op.out_features;
+    if (op.grad_accumulate) { ph.c = db; ph.ldc = op.out_features; }
+    set_vec_ok(ph);
   }
   // The weight-gradient phases need only local operands, so they all come first and cover the time the weight shards
   // are in flight; the input-gradient phases follow, own shard first, then the visiting shards in order of arrival.
@@ -1031,6 +1058,10 @@ int rtp_linear_bwd(const RtpRing* ring, const RtpLinearBwd* op, void* stream) {
   params.ctas_per_rank = ring->ctas;
   return launch<1>(params, ring->ctas, false, (cudaStream_t)stream, true);
 }
+int rtp_linear_bwd_folds_bias(const RtpRing* ring, const RtpLinearBwd* op) {
+  decide_pair(op->M, op->mode == 0 ? op->in_features : op->in_features / ring->world, ring->ctas);
+  return (op->bias_off >= 0 && op->ones && folds_bias(*ring, *op)) ? 1 : 0;
+}
 int rtp_expert_fwd(const RtpRing* ring, const RtpExpertFwd* op, void* stream) {
   static thread_local rtp::GemmParams<1> params;
   decide_pair(0, 0, ring->ctas);   // pairs only when forced
@@ -1146,6 +1177,20 @@ int rtp_ws_status(void* ws, unsigned long long* host_out, void* stream) {
   if (e != cudaSuccess) return fail(std::string("status copy: ") + cudaGetErrorString(e));
   e = cudaStreamSynchronize((cudaStream_t)stream);
   if (e != cudaSuccess) return fail(std::string("status sync: ") + cudaGetErrorString(e));
+  return 0;
+}
+int rtp_ws_num_counters(void) { return RTP_NUM_CTR; }
+int rtp_ws_counters(void* ws, unsigned long long* host_out, void* stream) {
+  // arrive[], done[], uses[] of this rank's flag block, RTP_NUM_CTR words each (the words sit 128 bytes apart)
+  const RtpFlagBlock* f = ws_flags(ws);
+  const RtpFlagWord* src[3] = {f->arrive, f->done, f->uses};
+  for (int k = 0; k < 3; ++k) {
+    cudaError_t e = cudaMemcpy2DAsync(host_out + k * RTP_NUM_CTR, 8, src[k], sizeof(RtpFlagWord), 8, RTP_NUM_CTR,
+                                      cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(std::string("counter copy: ") + cudaGetErrorString(e));
+  }
+  cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(std::string("counter sync: ") + cudaGetErrorString(e));
   return 0;
 }
 void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i, int world) { return ws_wslot(ws, slot_bytes, i, world); }

@@ -54,6 +54,7 @@ struct SmemCtrl {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t handed;                  // phases the epilogue warps have handed to the signaller warp
+  uint32_t jobs_issued;             // push jobs whose stores the pusher warp has issued (store-pusher mode)
 };
 
 static_assert(sizeof(SmemCtrl) <= kCtlBytes, "control block outgrew its shared-memory slot");
@@ -93,6 +94,55 @@ struct PushCtx {
   unsigned long long* status;
   unsigned long long wait_ns, timeout_ns;
 };
+
+// Store-pusher: the whole warp streams this CTA's share of every job with plain loads and peer stores through
+// registers (16 x 16 bytes per lane in flight).  Peer stores are posted: the warp never waits for one, so all jobs of a
+// launch are on the link back to back.  A job whose stores have been ISSUED is handed to the signaller warp, which makes
+// them visible with its (batched) system fence and announces the job.  Measured on 8 B200s this is what keeps NVLink
+// busy: with the bulk-copy pusher below, the issuing thread has to wait for the completion of its own copies before it
+// may announce a job, and under an 8-way exchange a completion takes ~10 us, during which it issues nothing (7 x 1 MB
+// took 66 us: 106 GB/s).
+__device__ __noinline__ void run_pushes_stores(const PushCtx& c, SmemCtrl* ctl, int lane) {
+  const RtpProgram& P = *c.P;
+  bool ok = true;
+  for (int j = 0; j < P.n_pushes; ++j) {
+    const RtpPush& pu = P.pushes[j];
+    const bool tr = P.trace && c.cta == 0 && lane == 0 && j < 8;
+    if (tr) P.trace[3 * 256 + 200 + j * 4 + 0] = globaltimer_ns();
+    uint32_t good = ok ? 1u : 0u;
+    if (ok && lane == 0 && pu.credit_ptr)
+      good = wait_counter_ge(pu.credit_ptr, credit_target(P.flags, pu.credit_ctr, pu.credit_rel), c.abort_flag, c.status,
+                             c.wait_ns, ST_TIMEOUT_CREDIT) ? 1u : 0u;
+    good = __shfl_sync(0xffffffffu, good, 0);
+    if (!good) ok = false;
+    if (tr) P.trace[3 * 256 + 200 + j * 4 + 1] = globaltimer_ns();
+    if (ok) {
+      const unsigned long long units = pu.bytes >> 4;
+      const unsigned long long per = (units + c.sharers - 1) / c.sharers;
+      const unsigned long long lo = per * (unsigned long long)c.index;
+      unsigned long long hi = lo + per;
+      if (hi > units) hi = units;
+      const uint4* src = reinterpret_cast<const uint4*>(pu.src);
+      uint4* dst = reinterpret_cast<uint4*>(pu.dst);
+      unsigned long long i = lo + lane;
+      for (; i + 32 * 15 < hi; i += 32 * 16) {
+        uint4 v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) v[u] = __ldg(src + i + 32 * u);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) dst[i + 32 * u] = v[u];
+      }
+      for (; i < hi; i += 32) dst[i] = __ldg(src + i);
+    }
+    // every lane's stores are ordered before lane 0's release of the counter
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_block();
+      atomicAdd(&ctl->jobs_issued, 1u);
+    }
+    if (tr) P.trace[3 * 256 + 200 + j * 4 + 3] = globaltimer_ns();
+  }
+}
 
 template <int NS, int CHUNK, int LAG>
 __device__ __noinline__ void run_pushes(const PushCtx& c) {
@@ -263,6 +313,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       for (int i = 0; i < kMaxPushSlots; ++i) mbar_init(&ctl->push_full[i], 1);
       ctl->abort_flag = 0;
       ctl->handed = 0;
+      ctl->jobs_issued = 0;
     }
     mbar_fence_init();
   }
@@ -1000,7 +1051,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
     // CTAs [n_compute, G) are reserved for pushing when the program has push jobs: they own no GEMM tile, so their copy
     // engine is not shared with a tile pipeline and their tile memory serves as a deep ring.  Without reserved CTAs
     // every CTA moves 1/G of each job through its small ring.
-    if (elect_one() && P.n_pushes > 0) {
+    if (P.n_pushes > 0 && P.push_ring == 2 && !(P.n_compute > 0 && P.n_compute < G)) {
+      PushCtx pc;
+      pc.P = &P; pc.G = G; pc.cta = cta;
+      pc.abort_flag = abort_flag; pc.status = status; pc.wait_ns = wait_ns; pc.timeout_ns = timeout_ns;
+      pc.bars = nullptr; pc.ring = nullptr; pc.index = cta; pc.sharers = G;
+      run_pushes_stores(pc, ctl, lane);
+    } else if (elect_one() && P.n_pushes > 0) {
       const int n_comp = P.n_compute > 0 ? P.n_compute : G;
       PushCtx pc;
       pc.P = &P; pc.G = G; pc.cta = cta;
@@ -1018,7 +1075,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         }
       } else {
         pc.ring = staging + kStagingBytes; pc.index = cta; pc.sharers = G;
+        // LAG = how many newer copies may be outstanding when a job's completion is awaited.  The wait blocks the one
+        // issuing thread, so a small LAG stalls the stream whenever a completion is slow (8-way exchange: ~10 us); a
+        // large one announces small jobs only after everything has been issued.
         if (P.push_ring == 1) run_pushes<2, 2 * kPushChunk, 1>(pc);
+        else if (P.push_ring == 3) run_pushes<kPushSlots, kPushChunk, 12>(pc);
+        else if (P.push_ring == 4) run_pushes<2, 2 * kPushChunk, 8>(pc);
         else run_pushes<kPushSlots, kPushChunk, kPushSlots - 1>(pc);
       }
     }
@@ -1033,14 +1095,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       // phases that announce their output, in program order
       int n_sig = 0;
       for (int p = 0; p < P.n_phases; ++p) n_sig += P.phases[p].arrive_ptr != nullptr;
+      // push jobs come this way too when the pusher warp works with plain stores (it only ISSUES them)
+      const int n_jobs = (P.push_ring == 2 && !(P.n_compute > 0 && P.n_compute < G)) ? P.n_pushes : 0;
       int next_p = 0;         // next phase index to look at
       uint32_t sent = 0;      // announcing phases signalled so far
-      while ((int)sent < n_sig) {
-        // bounded: the epilogue warps hand every such phase over, also after an abort
+      uint32_t jsent = 0;     // push jobs signalled so far
+      while ((int)sent < n_sig || (int)jsent < n_jobs) {
+        // bounded: the epilogue warps hand every such phase over and the pusher warp every job, also after an abort
         const unsigned long long t0 = globaltimer_ns();
-        uint32_t have = 0;
+        uint32_t have = 0, jhave = 0;
         bool got = true;
-        while ((have = *reinterpret_cast<volatile uint32_t*>(&ctl->handed)) <= sent) {
+        while (true) {
+          have = *reinterpret_cast<volatile uint32_t*>(&ctl->handed);
+          jhave = *reinterpret_cast<volatile uint32_t*>(&ctl->jobs_issued);
+          if (have > sent || jhave > jsent) break;
           if (globaltimer_ns() - t0 > 2 * timeout_ns) { got = false; break; }
           __nanosleep(32);
         }
@@ -1054,6 +1122,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           if (live) red_relaxed_sys_add(P.phases[next_p].arrive_ptr, 1ull);
           ++next_p;
           ++sent;
+        }
+        for (; jsent < jhave; ++jsent) {
+          if (live && P.pushes[jsent].arrive_ptr) red_relaxed_sys_add(P.pushes[jsent].arrive_ptr, 1ull);
+          if (P.trace && cta == 0 && jsent < 8) P.trace[3 * 256 + 200 + jsent * 4 + 2] = globaltimer_ns();
         }
       }
     }

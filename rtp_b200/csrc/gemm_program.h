@@ -139,7 +139,8 @@ struct alignas(64) RtpProgram {
   int n_phases, n_pushes;
   int n_stages, stage_bytes;  // smem pipeline geometry (host: finalize_program)
   int n_compute;              // CTAs [0, n_compute) run GEMM tiles, [n_compute, grid) only push (0 / grid: none reserved)
-  int push_ring;              // small push ring: 0 = four 3840-byte chunks in flight, 1 = two 7680-byte chunks
+  int push_ring;              // pusher: 2 = plain loads + peer stores by the whole warp (default); bulk copies through a
+                              // shared-memory ring by one thread: 0 / 3 = four 3840-byte chunks, 1 / 4 = two of 7680 (see gemm.cu)
   RtpFlagBlock* flags;  // this rank's flag block (may be null when nothing synchronises)
   RtpFlagBlock* peer_flags[RTP_FLAG_MAX_WORLD];  // every rank's flag block as mapped here (credits are written there)
   int rank, world;

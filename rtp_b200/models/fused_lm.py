@@ -27,6 +27,7 @@ from ..ops import kernels as K
 from ..ops import _lib
 from ..parallel import engine as E
 from ..parallel.context import get_context
+from ..utils.timing import nvtx_range
 
 
 class _Lin:
@@ -49,9 +50,10 @@ class FusedLMTrainer:
         (see ``rtp_b200.ops.kernels.adam_state_dtypes``).
 
         ``keep_grads=True``: every parameter's ``.grad`` holds its gradient after ``step`` and Adam runs once at the end.
-        ``keep_grads=False`` (optimizer in backward): the gradient of each rotated layer lands in ONE shared scratch
-        buffer and that layer's Adam update runs right after its backward launch, so only one layer's gradient is alive
-        at a time (the gradients are 1/4 to 1/6 of the per-rank model state); ``.grad`` is not meaningful afterwards.
+        ``keep_grads=False`` (optimizer in backward): the gradients of one decoder layer (or of the head, or of the
+        embedding) land in ONE shared scratch buffer and that group's Adam update runs right after its last backward
+        launch, so only one group's gradient is alive at a time (the gradients are 1/4 to 1/6 of the per-rank model
+        state); ``.grad`` is not meaningful afterwards.
         Both modes apply the same updates.  ``keep_grads=None`` picks by size: a model whose per-rank share is under half a
         billion parameters keeps its gradients (one Adam launch per step instead of one per layer: such a step is bound by
         launches, not memory), a larger one updates in backward."""
@@ -150,10 +152,19 @@ class FusedLMTrainer:
                 d.gflat = torch.zeros_like(d.flat)
             self.emb_gflat = torch.zeros_like(self.emb._full_param)
         else:
-            nmax = max([d.flat.numel() for d in lins] + [self.emb._full_param.numel()])
+            # update groups in backward order: the head, then each decoder layer (its four linears side by side in the
+            # scratch, one Adam launch after the layer's last backward), then the embedding
+            groups = [[self.head]] + [[l[k] for k in ("ff2", "ff1", "out", "qkv")] for l in reversed(self.layers)]
+            offs, nmax = {}, self.emb._full_param.numel()
+            for grp in groups:
+                o = 0
+                for d in grp:
+                    offs[id(d)] = o
+                    o += E._round_up(d.flat.numel(), 64)
+                nmax = max(nmax, o)
             self.gscratch = torch.zeros(nmax, dtype=torch.bfloat16, device=self.dev)
             for d in lins:
-                d.gflat = self.gscratch[:d.flat.numel()]
+                d.gflat = self.gscratch[offs[id(d)]:offs[id(d)] + d.flat.numel()]
             self.emb_gflat = self.gscratch[:self.emb._full_param.numel()]
         # Adam plans over views of the flat buffers: one for everything, or one per layer
         entries = []
@@ -182,8 +193,11 @@ class FusedLMTrainer:
             self.plan = None
             self.emb_plan = K.AdamPlan(emb_e, self.dev)
             self.ln_plan = K.AdamPlan(ln_e, self.dev)
-            for d, es in zip(lins, per_lin):
-                d.plan = K.AdamPlan(es, self.dev)
+            by_lin = {id(d): es for d, es in zip(lins, per_lin)}
+            for grp in groups:
+                for d in grp:
+                    d.plan = None
+                grp[-1].plan = K.AdamPlan([e for d in grp for e in by_lin[id(d)]], self.dev)
 
     def _adam(self, plan):
         plan.step(self.step_dev, self.lr, self.betas[0], self.betas[1], self.eps, self.wd, self.adamw, self.clip)
@@ -292,13 +306,15 @@ class FusedLMTrainer:
 
     def _lin_bwd(self, d, x, dy, st, dx_out=None, need_dx=True, mask=None, mask_scale=1.0, dx_accumulate=False):
         dbuf = st["dbias"][: d.out_f]
+        n0 = _lib.launches
         E.linear_bwd_raw(self.eng, d.flat, d.info, x, dy, d.row, d.in_f, d.out_f, need_dx=need_dx, mask=mask,
                          mask_scale=mask_scale, grad_out=d.gflat, dx_out=dx_out, dx_accumulate=dx_accumulate,
                          dbias_buf=dbuf, **self._chain_args(d, 1))
-        self._count(2)  # column sums of dy + fused dgrad/wgrad program
-        if not self.keep_grads:
-            # The layer's shard is updated as soon as its gradient is complete.  Its home buffer is no longer read by
-            # anyone in this step: the pushes of it (by this launch or the one before) precede the update in stream order.
+        self._count(_lib.launches - n0)  # fused dgrad/wgrad program (+ column sums of dy where they are a kernel of their own)
+        if not self.keep_grads and d.plan is not None:
+            # The shards of a decoder layer (or the head) are updated as soon as the group's last gradient is complete.
+            # Their home buffers are no longer read by anyone in this step: the pushes of them (by their own launches or
+            # the ones before) precede the update in stream order.
             self._adam(d.plan)
 
     def _step_impl(self, st):
@@ -310,24 +326,26 @@ class FusedLMTrainer:
         self._embed_fwd(st)
         x = st["x0"]
         for li, (l, a) in enumerate(zip(self.layers, st["acts"])):
-            o = 16 * (li + 1)
-            self._lin_fwd(l["qkv"], x, a["qkv"])
-            K.attn_small_fwd(a["qkv"], S, B, self.heads, nshard=self.N, causal=True, drop_p=p, seed=self.seed,
-                             offset=o + 1, step=rs, out=a["ctx"])
-            self._lin_fwd(l["out"], a["ctx"], st["sa"])
-            K.norm_fwd(x, st["sa"], l["n1"].weight, l["n1"].bias, eps=l["eps"], drop_p=p, seed=self.seed, offset=o + 2,
-                       step=rs, out=a["x1"], h_out=a["h1"], mean_out=a["mean1"], rstd_out=a["rstd1"])
-            self._lin_fwd(l["ff1"], a["x1"], a["a1"], act=1, drop_p=p, offset=o + 3)
-            self._lin_fwd(l["ff2"], a["a1"], st["f"])
-            K.norm_fwd(a["x1"], st["f"], l["n2"].weight, l["n2"].bias, eps=l["eps"], drop_p=p, seed=self.seed,
-                       offset=o + 4, step=rs, out=a["x2"], h_out=a["h2"], mean_out=a["mean2"], rstd_out=a["rstd2"])
-            self._count(3)
-            x = a["x2"]
-        self._lin_fwd(self.head, x, st["logits"])
-        K_scale = self.loss_scale / M
-        rows = K.cross_entropy_into(st["logits"], st["tgt"].view(-1), st["loss_rows"], grad_scale=K_scale)
-        K.sum_f32(rows, st["loss"], scale=1.0 / M)
-        self._count(2)
+            with nvtx_range(f"forward layer {li}"):
+                o = 16 * (li + 1)
+                self._lin_fwd(l["qkv"], x, a["qkv"])
+                K.attn_small_fwd(a["qkv"], S, B, self.heads, nshard=self.N, causal=True, drop_p=p, seed=self.seed,
+                                 offset=o + 1, step=rs, out=a["ctx"])
+                self._lin_fwd(l["out"], a["ctx"], st["sa"])
+                K.norm_fwd(x, st["sa"], l["n1"].weight, l["n1"].bias, eps=l["eps"], drop_p=p, seed=self.seed, offset=o + 2,
+                           step=rs, out=a["x1"], h_out=a["h1"], mean_out=a["mean1"], rstd_out=a["rstd1"])
+                self._lin_fwd(l["ff1"], a["x1"], a["a1"], act=1, drop_p=p, offset=o + 3)
+                self._lin_fwd(l["ff2"], a["a1"], st["f"])
+                K.norm_fwd(a["x1"], st["f"], l["n2"].weight, l["n2"].bias, eps=l["eps"], drop_p=p, seed=self.seed,
+                           offset=o + 4, step=rs, out=a["x2"], h_out=a["h2"], mean_out=a["mean2"], rstd_out=a["rstd2"])
+                self._count(3)
+                x = a["x2"]
+        with nvtx_range("head + cross-entropy"):
+            self._lin_fwd(self.head, x, st["logits"])
+            K_scale = self.loss_scale / M
+            rows = K.cross_entropy_into(st["logits"], st["tgt"].view(-1), st["loss_rows"], grad_scale=K_scale)
+            K.sum_f32(rows, st["loss"], scale=1.0 / M)
+            self._count(2)
         # ---------------- backward
         self.ln_grad32.zero_()
         self.step_dev.add_(1)          # the Adam step of this iteration (the updates may run inside backward)
@@ -336,36 +354,38 @@ class FusedLMTrainer:
         self._lin_bwd(self.head, x, st["logits"], st, dx_out=dx)
         scale_keep = 1.0 / (1.0 - p) if p > 0 else 1.0
         for li in reversed(range(L)):
-            l, a = self.layers[li], st["acts"][li]
-            o = 16 * (li + 1)
-            xin = st["acts"][li - 1]["x2"] if li > 0 else st["x0"]
-            g = self.ln_grad32
-            k0 = 4 * li * D
-            # LN2: dx (grad of x2) -> dh2 (= grad of x1 via the residual) and df (through dropout)
-            dx1 = st["dxb"]
-            K.norm_bwd(dx, a["h2"], l["n2"].weight, a["mean2"], a["rstd2"], drop_p=p, seed=self.seed, offset=o + 4,
-                       step=rs, dgamma=g[k0 + 2 * D:k0 + 3 * D], dbeta=g[k0 + 3 * D:k0 + 4 * D], dx=dx1, dsub=st["dsub"])
-            # FFN2 backward; the ReLU+dropout backward of the hidden activation rides in its dgrad epilogue
-            self._lin_bwd(l["ff2"], a["a1"], st["dsub"], st, dx_out=st["dz1"], mask=a["a1"], mask_scale=scale_keep)
-            # FFN1 backward accumulates onto the residual gradient
-            self._lin_bwd(l["ff1"], a["x1"], st["dz1"], st, dx_out=dx1, dx_accumulate=True)
-            # LN1
-            dxin = dx  # reuse: dx is dead after LN2 backward
-            K.norm_bwd(dx1, a["h1"], l["n1"].weight, a["mean1"], a["rstd1"], drop_p=p, seed=self.seed, offset=o + 2,
-                       step=rs, dgamma=g[k0:k0 + D], dbeta=g[k0 + D:k0 + 2 * D], dx=dxin, dsub=st["dsub"])
-            self._lin_bwd(l["out"], a["ctx"], st["dsub"], st, dx_out=st["dctx"])
-            K.attn_small_bwd(a["qkv"], st["dctx"], S, B, self.heads, nshard=self.N, causal=True, drop_p=p,
-                             seed=self.seed, offset=o + 1, step=rs, out=st["dqkv"])
-            self._lin_bwd(l["qkv"], xin, st["dqkv"], st, dx_out=dxin, dx_accumulate=True)
-            self._count(3)
-            dx = dxin
+            with nvtx_range(f"backward layer {li}"):
+                l, a = self.layers[li], st["acts"][li]
+                o = 16 * (li + 1)
+                xin = st["acts"][li - 1]["x2"] if li > 0 else st["x0"]
+                g = self.ln_grad32
+                k0 = 4 * li * D
+                # LN2: dx (grad of x2) -> dh2 (= grad of x1 via the residual) and df (through dropout)
+                dx1 = st["dxb"]
+                K.norm_bwd(dx, a["h2"], l["n2"].weight, a["mean2"], a["rstd2"], drop_p=p, seed=self.seed, offset=o + 4,
+                           step=rs, dgamma=g[k0 + 2 * D:k0 + 3 * D], dbeta=g[k0 + 3 * D:k0 + 4 * D], dx=dx1, dsub=st["dsub"])
+                # FFN2 backward; the ReLU+dropout backward of the hidden activation rides in its dgrad epilogue
+                self._lin_bwd(l["ff2"], a["a1"], st["dsub"], st, dx_out=st["dz1"], mask=a["a1"], mask_scale=scale_keep)
+                # FFN1 backward accumulates onto the residual gradient
+                self._lin_bwd(l["ff1"], a["x1"], st["dz1"], st, dx_out=dx1, dx_accumulate=True)
+                # LN1
+                dxin = dx  # reuse: dx is dead after LN2 backward
+                K.norm_bwd(dx1, a["h1"], l["n1"].weight, a["mean1"], a["rstd1"], drop_p=p, seed=self.seed, offset=o + 2,
+                           step=rs, dgamma=g[k0:k0 + D], dbeta=g[k0 + D:k0 + 2 * D], dx=dxin, dsub=st["dsub"])
+                self._lin_bwd(l["out"], a["ctx"], st["dsub"], st, dx_out=st["dctx"])
+                K.attn_small_bwd(a["qkv"], st["dctx"], S, B, self.heads, nshard=self.N, causal=True, drop_p=p,
+                                 seed=self.seed, offset=o + 1, step=rs, out=st["dqkv"])
+                self._lin_bwd(l["qkv"], xin, st["dqkv"], st, dx_out=dxin, dx_accumulate=True)
+                self._count(3)
+                dx = dxin
         self._embed_bwd(st, dx)
         # ---------------- replicated-parameter gradients and optimizer
         if self.N > 1:
             dist.all_reduce(self.ln_grad32, group=self.ring.group)
             self._count(1)
         K.cast_f32_bf16(self.ln_grad32, self.ln_grad16)
-        self._adam(self.plan if self.keep_grads else self.ln_plan)
+        with nvtx_range("optimizer"):
+            self._adam(self.plan if self.keep_grads else self.ln_plan)
         self.rng_step.add_(1)
         self._count(3)
 

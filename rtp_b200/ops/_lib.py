@@ -79,6 +79,7 @@ class LinearBwd(C.Structure):
         ("dx_accumulate", C.c_int), ("grad_accumulate", C.c_int),
         ("bank", C.c_int), ("no_self_push", C.c_int),
         ("next_home", C.c_void_p), ("next_bytes", C.c_ulonglong), ("next_kind", C.c_int),
+        ("ones", C.c_void_p),
     ]
 
 
@@ -171,6 +172,8 @@ def lib():
         L.rtp_ws_ipc_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
         L.rtp_ws_ipc_close.argtypes = [C.c_void_p]
         L.rtp_ws_status.argtypes = [C.c_void_p, C.POINTER(C.c_ulonglong), C.c_void_p]
+        L.rtp_ws_counters.argtypes = [C.c_void_p, C.POINTER(C.c_ulonglong), C.c_void_p]
+        L.rtp_ws_num_counters.restype = C.c_int
         L.rtp_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
         L.rtp_gemm_batched.argtypes = [C.POINTER(GemmBatched), C.c_void_p]
         L.rtp_linear_fwd.argtypes = [C.POINTER(Ring), C.POINTER(LinearFwd), C.c_void_p]
@@ -199,19 +202,47 @@ def lib():
         L.rtp_flash_last_error.restype = C.c_char_p
         L.rtp_linear_fwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(LinearFwd), C.c_int, C.c_void_p]
         L.rtp_linear_bwd_emu.argtypes = [C.POINTER(Ring), C.POINTER(LinearBwd), C.c_int, C.c_void_p]
+        L.rtp_linear_bwd_folds_bias.argtypes = [C.POINTER(Ring), C.POINTER(LinearBwd)]
         _lib = L
     return _lib
 
 
 launches = 0      # calls into the library that launched kernels (every entry point launches at least one)
+_serialize = os.environ.get("RTP_SERIALIZE", "0") not in ("", "0")
+_after_launch_hooks = []     # callables run after every launch in serialised mode (the engines register their checks)
+_checking = False            # the checks themselves call into the library: no nesting
+
+
+def set_serialize(on: bool) -> bool:
+    """Serialised (bisect) mode: after every library launch the stream is synchronised and every status word is
+    read, so the first launch whose bounded wait ran out is named in the exception instead of surfacing at the next
+    ``check``.  Also switched on by ``RTP_SERIALIZE=1``.  Has no effect while a CUDA graph is being captured."""
+    global _serialize
+    old, _serialize = _serialize, bool(on)
+    return old
 
 
 def check(rc: int, what: str):
-    global launches
+    global launches, _checking
     launches += 1
     if rc != 0:
         msg = lib().rtp_last_error()
         raise RuntimeError(f"{what} failed: {msg.decode() if msg else rc}")
+    if _serialize and not _checking and not torch.cuda.is_current_stream_capturing():
+        torch.cuda.synchronize()
+        _checking = True
+        try:
+            for w in list(_status_words.values()):
+                v = int(w.item())
+                if v:
+                    w.zero_()
+                    raise RotationTimeout(STATUS_NAMES.get(v, f"status {v}"))
+            for hook in _after_launch_hooks:
+                hook()
+        except RotationTimeout as e:
+            raise RotationTimeout(f"{what}: {e}") from None
+        finally:
+            _checking = False
 
 
 def stream_ptr() -> int:

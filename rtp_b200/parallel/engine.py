@@ -142,6 +142,49 @@ class FusedEngine:
         if rc != 0:
             raise RuntimeError("rtp_ring_shift: " + _lib.lib().rtp_shift_last_error().decode())
 
+    def ones_row(self, n: int) -> torch.Tensor:
+        """A row of at least ``n`` bf16 ones (the A operand of the bias-gradient GEMM phase); grown on demand, and never
+        while a CUDA graph that captured the old row may still be replayed."""
+        row = getattr(self, "_ones", None)
+        if row is None or row.numel() < n:
+            if row is not None and torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("ones row would have to grow during graph capture")
+            row = torch.ones(max(n, 32768), dtype=torch.bfloat16, device=self.device)
+            self._old_ones = getattr(self, "_old_ones", []) + ([self._ones] if getattr(self, "_ones", None) is not None else [])
+            self._ones = row
+        return row
+
+    def counters(self):
+        """(arrive, done, uses) lists of this rank's slot counters (synchronises the stream)."""
+        L = _lib.lib()
+        n = int(L.rtp_ws_num_counters())
+        buf = (C.c_ulonglong * (3 * n))()
+        _lib.check(L.rtp_ws_counters(self.ws_local, buf, _lib.stream_ptr()), "rtp_ws_counters")
+        vals = list(buf)
+        return vals[:n], vals[n:2 * n], vals[2 * n:]
+
+    def verify_epochs(self):
+        """Race-detection aid, collective over the ring, to be called at a quiescent point (after a step, stream
+        synchronised everywhere): every slot must have seen the same number of fills on every rank (``uses``), every
+        fill must have arrived completely and been read completely (``arrive == done == uses * CTAs``).  A rank that
+        skipped or repeated a launch, or a producer that signalled a slot it did not fill, shows up here as an
+        ``EpochMismatch`` naming the counter, instead of as a wrong gradient later."""
+        ctx = self.ctx
+        torch.cuda.synchronize()
+        if ctx.world > 1:
+            dist.barrier(group=ctx.group)         # every rank's last launch (and its signals to us) is complete
+        arrive, done, uses = self.counters()
+        bad = [f"counter {c}: arrive {arrive[c]}, done {done[c]}, uses {uses[c]} x {self.ctas} CTAs"
+               for c in range(len(uses)) if ctx.world > 1 and (arrive[c] != uses[c] * self.ctas or done[c] != uses[c] * self.ctas)]
+        if ctx.world > 1:
+            gathered = [None] * ctx.world
+            dist.all_gather_object(gathered, uses, group=ctx.group)
+            for r, u in enumerate(gathered):
+                bad += [f"counter {c}: {uses[c]} fills on rank {ctx.rank}, {u[c]} on rank {r}"
+                        for c in range(len(uses)) if u[c] != uses[c]]
+        if bad:
+            raise EpochMismatch("; ".join(bad[:8]))
+
     def check(self):
         """Read the workspace status word (synchronises the stream); raise if a bounded wait expired."""
         _lib.check(_lib.lib().rtp_ws_status(self.ws_local, C.byref(self._host_status), _lib.stream_ptr()),
@@ -152,12 +195,18 @@ class FusedEngine:
             raise _lib.RotationTimeout(_lib.STATUS_NAMES.get(v, f"status {v}"))
 
 
+class EpochMismatch(RuntimeError):
+    """The slot counters of a ring disagree at a quiescent point: some rank ran a different sequence of fills."""
+
+
 def get_engine(ctx: RingContext) -> FusedEngine:
     key = (id(ctx.group), ctx.rank, ctx.world, torch.cuda.current_device())
     eng = _engines.get(key)
     if eng is None:
         eng = FusedEngine(ctx, _reserved_bytes)
         _engines[key] = eng
+        if check_all not in _lib._after_launch_hooks:
+            _lib._after_launch_hooks.append(check_all)
     elif ctx.world > 1 and _reserved_bytes > eng.slot_bytes:
         eng.grow(_reserved_bytes)
     return eng
@@ -228,7 +277,6 @@ def linear_bwd_raw(eng, flat, layout_info, x2d, dy2d, row, in_f, out_f, need_dx=
     dx = None
     if need_dx:
         dx = dx_out if dx_out is not None else torch.empty(M, in_f, dtype=torch.bfloat16, device=x2d.device)
-    dbias = K.colsum(dy2d, dbias_buf) if has_bias else None
     op = _lib.LinearBwd()
     op.mode, op.M, op.in_features, op.out_features = int(row), M, in_f, out_f
     op.home, op.bias_off, op.shard_bytes = flat.data_ptr(), bias_off, shard_bytes
@@ -237,7 +285,13 @@ def linear_bwd_raw(eng, flat, layout_info, x2d, dy2d, row, in_f, out_f, need_dx=
     if dx is not None:
         op.dx, op.lddx = dx.data_ptr(), dx.stride(0)
     op.grad_home = gflat.data_ptr()
-    op.dbias_full = dbias.data_ptr() if dbias is not None else None
+    if has_bias:
+        # On a 1-rank ring the bias gradient is one more GEMM phase of the launch (a row of ones times dy); elsewhere
+        # the column sums of dy come from a kernel of their own.
+        op.ones = eng.ones_row(M).data_ptr()
+        if not _lib.lib().rtp_linear_bwd_folds_bias(C.byref(eng.ring), C.byref(op)):
+            op.ones = None
+            op.dbias_full = K.colsum(dy2d, dbias_buf).data_ptr()
     if mask is not None:
         op.mask, op.ldmask, op.mask_scale = mask.data_ptr(), mask.stride(0), mask_scale
     op.dx_accumulate = int(dx_accumulate)

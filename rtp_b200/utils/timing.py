@@ -1,6 +1,8 @@
 """Device-side timing. The reference times with ``time.time()`` and one synchronize at the end
 (benchmarks/rtp_benchmark.py:146,205-208); here every number is taken with CUDA events on the launching stream
 and reduced with MAX over the ranks of the ring."""
+import contextlib
+import os
 import time
 
 import torch
@@ -43,3 +45,27 @@ class DeviceTimer:
             ms = (time.perf_counter() - self.t0) * 1e3
         self.ms = max_over_ranks(ms, self.group) if self.reduce_max else ms
         return False
+
+
+_NVTX = os.environ.get("RTP_NVTX", "0") not in ("", "0")
+
+
+def set_nvtx(on: bool) -> bool:
+    """Switches the NVTX ranges of the library on or off (``RTP_NVTX=1`` does the same); returns the old setting."""
+    global _NVTX
+    old, _NVTX = _NVTX, bool(on)
+    return old
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """A named NVTX range around a group of launches (the trainer marks forward / backward of every layer, the head
+    and the optimizer), visible to any timeline tool that reads NVTX; free when switched off."""
+    if _NVTX and torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        yield

@@ -371,6 +371,23 @@ def main():
     check(bool((buf == float((rank - 1) % world)).all().item()), "ring shift up")
     _lib.check_status(dev)
 
+    # ------------------------------------------------------------------ slot counters agree across the ring
+    try:
+        eng.verify_epochs()
+    except engine.EpochMismatch as e:
+        check(False, f"epoch check: {e}")
+    arrive, done, uses = eng.counters()
+    check(sum(uses) > 0, "the slot counters moved")
+
+    # ------------------------------------------------------------------ serialised (bisect) mode
+    old = _lib.set_serialize(True)
+    try:
+        lin_ser = ColumnParallelLinear(256, 256).to(dev, torch.bfloat16)
+        y_ser = lin_ser(torch.randn(64, 256, device=dev, dtype=torch.bfloat16))
+        check(bool(torch.isfinite(y_ser).all().item()), "serialised mode: fused linear")
+    finally:
+        _lib.set_serialize(old)
+
     dist.barrier()
     if rank == 0:
         print(f"worst LM grad rel err vs fp32 {worst:.4f}; trainer losses {[round(v, 3) for v in losses[::6]]}; "

@@ -208,6 +208,43 @@ def test_missing_producer_times_out_and_returns():
         L.rtp_ws_destroy(w)
 
 
+def test_serialised_mode_names_the_launch_whose_wait_ran_out():
+    """Bisect mode: with ``set_serialize(True)`` every launch is followed by a synchronise and a status read, so the
+    exception carries the name of the launch whose bounded wait expired (again a peer that is never launched)."""
+    from rtp_b200.ops import _lib
+    L = _lib.lib()
+    world, M, IN, OUT = 2, 128, 256, 256
+    Os, Ks = OUT // world, IN
+    nflat = Os * Ks + 128
+    wss, rings = _rings(world, 1 << 17, 8, L, _lib)
+    rings[0].timeout_ns = 200_000_000      # 0.2 s
+    flat = torch.zeros(nflat, device="cuda", dtype=BF)
+    x = torch.randn(M, IN, device="cuda", dtype=BF)
+    y = torch.zeros(M, OUT, device="cuda", dtype=BF)
+    op = _lib.LinearFwd()
+    op.mode, op.M, op.in_features, op.out_features = 0, M, IN, OUT
+    op.home, op.bias_off, op.shard_bytes = flat.data_ptr(), Os * Ks, nflat * 2
+    op.x, op.ldx, op.y, op.ldy = x.data_ptr(), IN, y.data_ptr(), OUT
+
+    def read_status():
+        st = C.c_ulonglong(0)
+        L.rtp_ws_status(wss[0], C.byref(st), _lib.stream_ptr())
+        if st.value:
+            raise _lib.RotationTimeout(_lib.STATUS_NAMES.get(st.value, str(st.value)))
+
+    _lib._after_launch_hooks.append(read_status)
+    old = _lib.set_serialize(True)
+    try:
+        with pytest.raises(_lib.RotationTimeout, match="forward of layer 3.*peer's data"):
+            _lib.check(L.rtp_linear_fwd(C.byref(rings[0]), C.byref(op), _lib.stream_ptr()), "forward of layer 3")
+    finally:
+        _lib.set_serialize(old)
+        _lib._after_launch_hooks.remove(read_status)
+    assert torch.ones(4, device="cuda").sum().item() == 4.0      # the context is alive
+    for w in wss:
+        L.rtp_ws_destroy(w)
+
+
 @pytest.mark.parametrize("world,L", [(2, 2), (4, 1), (4, 2)])
 def test_rotating_experts_fwd_bwd(world, L):
     """One linear of every expert while the expert blocks rotate: tokens of expert g only ever meet weights of g."""
