@@ -39,7 +39,7 @@ constexpr int kPushRingBytes = kPushSlots * kPushChunk;
 constexpr int kBigPushChunk = 16384;            // deep ring: 12 slots in the tile area
 constexpr int kMaxPushSlots = 12;
 static_assert(kMaxPushSlots * kBigPushChunk <= 196608, "deep push ring must fit the tile area");
-constexpr int kCtlBytes = 512;                  // barriers and CTA-wide words
+constexpr int kCtlBytes = 768;                  // barriers and CTA-wide words
 constexpr int kSmemBytes = kTileBytes + 1024 /*align slack*/ + kCtlBytes + kStagingBytes + kPushRingBytes;
 static_assert(kSmemBytes <= 232448, "over the 227 KB of shared memory a CTA can have");
 
@@ -55,6 +55,9 @@ struct SmemCtrl {
   uint32_t abort_flag;
   uint32_t handed;                  // phases the epilogue warps have handed to the signaller warp
   uint32_t jobs_issued;             // push jobs whose stores the pusher warp has issued (store-pusher mode)
+  // Copy of the flag block's uses[] (completed fills per slot; constant while a launch runs).  Every wait target is
+  // computed from it; read from global memory it cost a dependent ~0.7 us load in front of every counter poll.
+  unsigned long long uses[RTP_NUM_CTR];
 };
 
 static_assert(sizeof(SmemCtrl) <= kCtlBytes, "control block outgrew its shared-memory slot");
@@ -68,15 +71,15 @@ struct GemmParams {
 };
 __constant__ RtpProgram c_emu_progs[RTP_MAX_EMU_RANKS];
 
-__device__ __forceinline__ unsigned long long fill_target(const RtpFlagBlock* fb, int ctr, int rel, int plus,
+__device__ __forceinline__ unsigned long long fill_target(const unsigned long long* uses, int ctr, int rel, int plus,
                                                           int G) {
   // counters count one unit per CTA per fill of the slot
-  return (fb->uses[ctr].v + (unsigned long long)(rel + plus)) * (unsigned long long)G;
+  return (uses[ctr] + (unsigned long long)(rel + plus)) * (unsigned long long)G;
 }
 
 // a slot may be written again once `uses + rel` of its fills have been read completely (credits count whole fills)
-__device__ __forceinline__ unsigned long long credit_target(const RtpFlagBlock* fb, int ctr, int rel) {
-  return fb->uses[ctr].v + (unsigned long long)rel;
+__device__ __forceinline__ unsigned long long credit_target(const unsigned long long* uses, int ctr, int rel) {
+  return uses[ctr] + (unsigned long long)rel;
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -90,6 +93,7 @@ struct PushCtx {
   int G, cta, index, sharers;
   uint8_t* ring;
   uint64_t* bars;
+  const unsigned long long* uses;   // the CTA's copy of the slot fill counts
   volatile uint32_t* abort_flag;
   unsigned long long* status;
   unsigned long long wait_ns, timeout_ns;
@@ -111,7 +115,7 @@ __device__ __noinline__ void run_pushes_stores(const PushCtx& c, SmemCtrl* ctl, 
     if (tr) P.trace[3 * 256 + 200 + j * 4 + 0] = globaltimer_ns();
     uint32_t good = ok ? 1u : 0u;
     if (ok && lane == 0 && pu.credit_ptr)
-      good = wait_counter_ge(pu.credit_ptr, credit_target(P.flags, pu.credit_ctr, pu.credit_rel), c.abort_flag, c.status,
+      good = wait_counter_ge(pu.credit_ptr, credit_target(c.uses, pu.credit_ctr, pu.credit_rel), c.abort_flag, c.status,
                              c.wait_ns, ST_TIMEOUT_CREDIT) ? 1u : 0u;
     good = __shfl_sync(0xffffffffu, good, 0);
     if (!good) ok = false;
@@ -214,7 +218,7 @@ __device__ __noinline__ void run_pushes(const PushCtx& c) {
     const RtpPush& pu = P.pushes[j];
     if (s_start[s]) {
       if (P.trace && c.cta == P.n_compute % c.G && j < 8) P.trace[3 * 256 + 200 + j * 4 + 0] = globaltimer_ns();
-      if (pu.credit_ptr && !wait_counter_ge(pu.credit_ptr, credit_target(P.flags, pu.credit_ctr, pu.credit_rel), c.abort_flag,
+      if (pu.credit_ptr && !wait_counter_ge(pu.credit_ptr, credit_target(c.uses, pu.credit_ctr, pu.credit_rel), c.abort_flag,
                                             c.status, c.wait_ns, ST_TIMEOUT_CREDIT)) {
         ok = false;
         break;
@@ -328,6 +332,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
   const uint32_t tmem_base = ctl->tmem_base;
   // everything above touched only shared memory and TMEM; from here on the previous kernel of the stream must be complete
   pdl_wait();
+  // the previous launch has published its fill counts: one parallel read for all later wait targets (nothing waits
+  // on a ring of one rank)
+  if (P.flags && P.world != 1) {
+    if (threadIdx.x >= 96 && threadIdx.x < 96 + RTP_NUM_CTR) ctl->uses[threadIdx.x - 96] = __ldcg(&P.flags->uses[threadIdx.x - 96].v);
+    __syncthreads();
+  }
   if (threadIdx.x == 0) GEMM_STAMP(1);
 
   if (warp == 0) {
@@ -355,7 +365,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           if (ph.wait_ctr[w] >= 0) {
             any_wait = true;
             ok = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
-                                 fill_target(P.flags, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
+                                 fill_target(ctl->uses, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
                                  wait_ns, ST_TIMEOUT_ARRIVAL);
           }
         }
@@ -421,7 +431,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             if (!((seg_ready >> sg) & 1u)) {
               if (ph.wait_ctr[sg] >= 0) {
                 ok = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[sg]].v,
-                                     fill_target(P.flags, ph.wait_ctr[sg], ph.wait_rel[sg], 1, G), abort_flag, status,
+                                     fill_target(ctl->uses, ph.wait_ctr[sg], ph.wait_rel[sg], 1, G), abort_flag, status,
                                      wait_ns, ST_TIMEOUT_ARRIVAL);
                 if (!ok) break;
                 fence_proxy_async();
@@ -616,10 +626,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           for (int w = 0; w < RTP_MAX_WAITS && good; ++w)
             if (ph.wait_ctr[w] >= 0)
               good = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
-                                     fill_target(P.flags, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
+                                     fill_target(ctl->uses, ph.wait_ctr[w], ph.wait_rel[w], 1, G), abort_flag, status,
                                      wait_ns, ST_TIMEOUT_ARRIVAL);
           if (good && ph.credit_ptr)
-            good = wait_counter_ge(ph.credit_ptr, credit_target(P.flags, ph.credit_ctr, ph.credit_rel),
+            good = wait_counter_ge(ph.credit_ptr, credit_target(ctl->uses, ph.credit_ctr, ph.credit_rel),
                                    abort_flag, status, wait_ns, ST_TIMEOUT_CREDIT);
         }
         good = __shfl_sync(0xffffffffu, good, 0);
@@ -1055,6 +1065,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       PushCtx pc;
       pc.P = &P; pc.G = G; pc.cta = cta;
       pc.abort_flag = abort_flag; pc.status = status; pc.wait_ns = wait_ns; pc.timeout_ns = timeout_ns;
+      pc.uses = ctl->uses;
       pc.bars = nullptr; pc.ring = nullptr; pc.index = cta; pc.sharers = G;
       run_pushes_stores(pc, ctl, lane);
     } else if (elect_one() && P.n_pushes > 0) {
@@ -1062,6 +1073,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       PushCtx pc;
       pc.P = &P; pc.G = G; pc.cta = cta;
       pc.abort_flag = abort_flag; pc.status = status; pc.wait_ns = wait_ns; pc.timeout_ns = timeout_ns;
+      pc.uses = ctl->uses;
       pc.bars = &ctl->push_full[0];
       if (n_comp < G) {
         if (cta < n_comp) {
