@@ -320,6 +320,17 @@ int add_prefetch_pushes(const RtpRing& R, RtpProgram& P, const void* home, unsig
   return 0;
 }
 
+// Tile-segmented phases (one phase for all shards of a column-mode forward / weight gradient) can be switched off
+// with RTP_SEG_TILES=0: the builders then emit one phase per shard.
+bool seg_tiles_ok() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("RTP_SEG_TILES");
+    v = (e && atoi(e) == 0) ? 0 : 1;
+  }
+  return v == 1;
+}
+
 // ------------------------------------------------------------------------------------------------
 // program builders
 // ------------------------------------------------------------------------------------------------
@@ -374,6 +385,39 @@ int build_linear_fwd(const RtpRing& R, const RtpLinearFwd& op, RtpProgram& P) {
       if (op.bias_off >= 0) {
         const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(src) + op.bias_off;
         if (i == 0) ph.bias = b; else ph.bias_more[ph.n_bias_more++] = b;
+      }
+    }
+    ph.act = op.act;
+    ph.drop_thresh = drop_threshold(op.drop_p);
+    ph.drop_scale = op.drop_p > 0.f ? 1.f / (1.f - op.drop_p) : 1.f;
+    ph.drop_seed = op.seed; ph.drop_offset = op.offset; ph.drop_step_ptr = op.step_ptr;
+    set_vec_ok(ph);
+  } else if (col && N > 1 && seg_tiles_ok() && Os % bn == 0) {
+    // Column mode on a ring: y[:, block j] = x W_j^T + b_j for every shard is ONE phase whose output columns fall into N
+    // segments in the order of arrival of the shards (own shard first); a tile reads its shard's tensor map once the
+    // shard has arrived.
+    P.n_phases = 1;
+    RtpPhase& ph = P.phases[0];
+    init_phase(ph);
+    RtpSegTable& st = P.segtab[0];
+    ph.a_map = 0; ph.b_map = 1;
+    ph.M = op.M; ph.N = op.out_features; ph.K = Ks;
+    ph.bn = bn; ph.b_box = b_box;
+    ph.ldd = op.ldy; ph.d = op.y;
+    ph.tseg = 1; ph.tseg_len = Os; ph.tseg_n = N; ph.tseg_tab = 0;
+    for (int i = 0; i < N; ++i) {
+      const int j = mod(r + i, N);
+      const int slot = wb + i - 1;
+      const uint8_t* src = (i == 0) ? reinterpret_cast<const uint8_t*>(op.home) : ws_wslot(ws, R.slot_bytes, slot, R.world);
+      st.map[i] = (i == 0) ? 1 : 1 + i;
+      st.off_mn[i] = 0;
+      st.drop_add[i] = j;
+      st.d[i] = reinterpret_cast<__nv_bfloat16*>(op.y) + (long long)j * Os;
+      st.bias[i] = op.bias_off >= 0 ? reinterpret_cast<const __nv_bfloat16*>(src) + op.bias_off : nullptr;
+      if (i > 0) {
+        ph.wait_ctr[i] = RTP_CTR_W0 + slot; ph.wait_rel[i] = 0;
+        ph.done_ctr[i] = RTP_CTR_W0 + slot;
+        P.uses_inc[RTP_CTR_W0 + slot] = 1;
       }
     }
     ph.act = op.act;
@@ -486,6 +530,70 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
         return -1;
   }
   int np = 0;
+  const int bn_wg = pick_bn(Os, Ks, R.ctas);
+  const int tm = pair_mode() ? 256 : 128;
+  if (col && N > 1 && seg_tiles_ok() && Os % tm == 0) {
+    // ---- wgrad of every shard as ONE phase: dW[N * Os, Ks] = dy^T x, whose output rows fall into N segments, one per
+    //      owner: the tiles of segment s go to gradient slot s of owner j (local slot N-1 for the own shard).
+    RtpPhase& ph = P.phases[np++];
+    init_phase(ph);
+    RtpSegTable& st = P.segtab[0];
+    ph.a_map = 0; ph.a_mn = 1;
+    ph.b_map = 1; ph.b_mn = 1;
+    ph.M = op.out_features; ph.N = Ks; ph.K = op.M;
+    ph.bn = bn_wg;
+    ph.ldd = Ks;
+    ph.tseg = 2; ph.tseg_len = Os; ph.tseg_n = N; ph.tseg_tab = 0;
+    for (int s = 0; s < N; ++s) {
+      const int j = mod(r - 1 - s, N);
+      uint8_t* dst = ws_gslot(R.ws[j], R.slot_bytes, s, R.world);
+      st.map[s] = -1;
+      st.off_mn[s] = j * Os;
+      st.d[s] = dst;
+      st.bias[s] = nullptr;
+      st.credit_ptr[s] = &ws_flags(R.ws[R.rank])->credit[j][RTP_CTR_G0 + s].v;
+      st.credit_ctr[s] = RTP_CTR_G0 + s;
+      st.arrive_ptr[s] = &ws_flags(R.ws[j])->arrive[RTP_CTR_G0 + s].v;
+      if (op.bias_off >= 0 && op.dbias_full) {
+        st.vec_out[s] = reinterpret_cast<__nv_bfloat16*>(dst) + op.bias_off;
+        st.vec_off[s] = (long long)j * Os;
+      }
+    }
+    ph.d = st.d[0];
+    ph.arrive_ptr = st.arrive_ptr[0];     // marks the phase as one that announces its output
+    if (op.bias_off >= 0 && op.dbias_full) { ph.vec_add = op.dbias_full; ph.vec_len = Os; }
+    set_vec_ok(ph);
+  } else if (!col && N > 1 && seg_tiles_ok() && Ks % bn_wg == 0) {
+    // ---- row mode: dW_j = dy^T x[:, block j] for every shard as ONE phase whose output COLUMNS fall into N segments
+    RtpPhase& ph = P.phases[np++];
+    init_phase(ph);
+    RtpSegTable& st = P.segtab[0];
+    ph.a_map = 0; ph.a_mn = 1;
+    ph.b_map = 1; ph.b_mn = 1;
+    ph.M = Os; ph.N = op.in_features; ph.K = op.M;
+    ph.bn = bn_wg;
+    ph.ldd = Ks;
+    ph.tseg = 1; ph.tseg_len = Ks; ph.tseg_n = N; ph.tseg_tab = 0;
+    for (int s = 0; s < N; ++s) {
+      const int j = mod(r - 1 - s, N);
+      uint8_t* dst = ws_gslot(R.ws[j], R.slot_bytes, s, R.world);
+      st.map[s] = -1;
+      st.off_mn[s] = j * Ks;
+      st.d[s] = dst;
+      st.bias[s] = nullptr;
+      st.credit_ptr[s] = &ws_flags(R.ws[R.rank])->credit[j][RTP_CTR_G0 + s].v;
+      st.credit_ctr[s] = RTP_CTR_G0 + s;
+      st.arrive_ptr[s] = &ws_flags(R.ws[j])->arrive[RTP_CTR_G0 + s].v;
+      if (op.bias_off >= 0 && op.dbias_full) {
+        st.vec_out[s] = reinterpret_cast<__nv_bfloat16*>(dst) + op.bias_off;
+        st.vec_off[s] = 0;
+      }
+    }
+    ph.d = st.d[0];
+    ph.arrive_ptr = st.arrive_ptr[0];     // marks the phase as one that announces its output
+    if (op.bias_off >= 0 && op.dbias_full) { ph.vec_add = op.dbias_full; ph.vec_len = Os; }
+    set_vec_ok(ph);
+  } else
   for (int s = 0; s < N; ++s) {
     const int j = mod(r - 1 - s, N);
     // ---- wgrad: dW_j = dy_j^T x  -> gradient slot s of owner j (own shard: straight into the home gradient when
@@ -555,6 +663,34 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
       const bool last = s == N - 1;   // own shard
       ph.seg_a_off_k[q] = j * Os;
       ph.seg_b_map[q] = last ? 3 : 4 + s;
+      if (!last) {
+        ph.wait_ctr[q] = RTP_CTR_W0 + wb + s; ph.wait_rel[q] = 0;
+        ph.done_ctr[q] = RTP_CTR_W0 + wb + s;
+        P.uses_inc[RTP_CTR_W0 + wb + s] = 1;
+      }
+    }
+    set_vec_ok(ph);
+  } else if (!col && N > 1 && op.dx && !op.mask && !op.dx_accumulate && seg_tiles_ok() &&
+             Ks % pick_bn(op.M, Ks, R.ctas) == 0) {
+    // Row mode on a ring: dx[:, block j] = dy W_j for every shard is ONE phase whose output columns fall into N segments
+    // in the order of arrival of the shards (own shard first).
+    RtpPhase& ph = P.phases[np++];
+    init_phase(ph);
+    RtpSegTable& st = P.segtab[1];
+    ph.a_map = 2; ph.a_mn = 0;
+    ph.b_map = 3; ph.b_mn = 1;
+    ph.M = op.M; ph.N = op.in_features; ph.K = Os;
+    ph.bn = pick_bn(op.M, Ks, R.ctas);
+    ph.ldd = op.lddx; ph.d = op.dx;
+    ph.tseg = 1; ph.tseg_len = Ks; ph.tseg_n = N; ph.tseg_tab = 1;
+    for (int q = 0; q < N; ++q) {
+      const int s = (q == 0) ? N - 1 : q - 1;
+      const int j = mod(r - 1 - s, N);
+      const bool last = s == N - 1;   // own shard
+      st.map[q] = last ? 3 : 4 + s;
+      st.off_mn[q] = 0;
+      st.d[q] = reinterpret_cast<__nv_bfloat16*>(op.dx) + (long long)j * Ks;
+      st.bias[q] = nullptr;
       if (!last) {
         ph.wait_ctr[q] = RTP_CTR_W0 + wb + s; ph.wait_rel[q] = 0;
         ph.done_ctr[q] = RTP_CTR_W0 + wb + s;

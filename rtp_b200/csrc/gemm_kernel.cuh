@@ -69,7 +69,7 @@ struct GemmParams {
   RtpProgram prog[NEMU == 1 ? 1 : 1];
   int ctas_per_rank;
 };
-__constant__ RtpProgram c_emu_progs[RTP_MAX_EMU_RANKS];
+__device__ RtpProgram c_emu_progs[RTP_MAX_EMU_RANKS];   // global, not constant memory: four programs exceed the 64 KB constant bank
 
 __device__ __forceinline__ unsigned long long fill_target(const unsigned long long* uses, int ctr, int rel, int plus,
                                                           int G) {
@@ -361,7 +361,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         if ((unit - ph.cta_off + GU) % GU >= total) continue;
         const int nseg = ph.nseg > 1 ? ph.nseg : 1;
         bool any_wait = false;
-        for (int w = 0; w < RTP_MAX_WAITS && ok && nseg == 1; ++w) {
+        for (int w = 0; w < RTP_MAX_WAITS && ok && nseg == 1 && !ph.tseg; ++w) {
           if (ph.wait_ctr[w] >= 0) {
             any_wait = true;
             ok = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
@@ -404,8 +404,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         const int b_dx = p_b_mn ? 0 : kBK, b_dy = p_b_mn ? kBK : 0;
         const int b_ix = p_b_mn ? 64 : 0, b_iy = p_b_mn ? 0 : ph.b_box;  // per box inside a stage
         const uint32_t b_ismem = p_b_mn ? 8192u : (uint32_t)ph.b_box * 128u;
-        const bool a3 = p_a_mn && P.map3d[ph.a_map];
+        bool a3 = p_a_mn && P.map3d[ph.a_map];
         bool b3 = p_b_mn && P.map3d[ph.b_map];
+        const int p_tseg = ph.tseg, p_tseg_len = ph.tseg_len;
+        const RtpSegTable& segs = P.segtab[ph.tseg_tab];
+        unsigned long long ma_t = ma;
         if (p == 0) GEMM_STAMP(2);
         for (int t = (unit - p_cta_off + GU) % GU; t < total && ok; t += GU) {
           // unbatched phases (the common case) skip the divisions by the batch geometry
@@ -418,10 +421,37 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           const int kblocks = p_causal == 2 ? min(kblocks_full, (m0u + TM + kBK - 1) / kBK) : kblocks_full;
           const int kb0 = p_causal == 3 ? m0u / kBK : 0;   // contraction index = query, output row = key: queries before the key contribute nothing
           const int zo = p_batch1 ? 0 : z / p_batch_inner, zi = p_batch1 ? 0 : z - zo * p_batch_inner;
-          const int a_mn0 = m0 + p_a_off_mn + zo * p_a_bo_mn + zi * p_a_bi_mn;
+          int a_mn0 = m0 + p_a_off_mn + zo * p_a_bo_mn + zi * p_a_bi_mn;
           const int a_k0 = p_a_off_k + zo * p_a_bo_k + zi * p_a_bi_k;
-          const int b_mn0 = n0 + (int)crank * bn_local + p_b_off_mn + zo * p_b_bo_mn + zi * p_b_bi_mn;
+          int b_mn0 = n0 + (int)crank * bn_local + p_b_off_mn + zo * p_b_bo_mn + zi * p_b_bi_mn;
           const int b_k0 = p_b_off_k + zo * p_b_bo_k + zi * p_b_bi_k;
+          if (p_tseg) {
+            // the tile belongs to one segment: its shard must have arrived; operand coordinates are local to the shard
+            const int sgt = (p_tseg == 1 ? n0 : m0u) / p_tseg_len;
+            if (!((seg_ready >> sgt) & 1u)) {
+              if (ph.wait_ctr[sgt] >= 0) {
+                ok = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[sgt]].v,
+                                     fill_target(ctl->uses, ph.wait_ctr[sgt], ph.wait_rel[sgt], 1, G), abort_flag, status,
+                                     wait_ns, ST_TIMEOUT_ARRIVAL);
+                if (!ok) break;
+                fence_proxy_async();
+              }
+              seg_ready |= 1u << sgt;
+            }
+            if (p_tseg == 1) {
+              b_mn0 += segs.off_mn[sgt] - sgt * p_tseg_len;
+              if (segs.map[sgt] >= 0) {
+                mb = reinterpret_cast<unsigned long long>(&P.maps[segs.map[sgt]]);
+                b3 = p_b_mn && P.map3d[segs.map[sgt]];
+              }
+            } else {
+              a_mn0 += segs.off_mn[sgt] - sgt * p_tseg_len;
+              if (segs.map[sgt] >= 0) {
+                ma_t = reinterpret_cast<unsigned long long>(&P.maps[segs.map[sgt]]);
+                a3 = p_a_mn && P.map3d[segs.map[sgt]];
+              }
+            }
+          }
           int ax = (p_a_mn ? a_mn0 : a_k0) + kb0 * a_dx, ay = (p_a_mn ? a_k0 : a_mn0) + kb0 * a_dy;
           int bx = (p_b_mn ? b_mn0 : b_k0) + kb0 * b_dx, by = (p_b_mn ? b_k0 : b_mn0) + kb0 * b_dy;
           if (P.trace && cta == 0 && tr_n < 60) P.trace[0 * 256 + tr_n * 4 + 0] = globaltimer_ns();
@@ -455,10 +485,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
               const uint32_t bar = full_s + stage * 8;
               mbar_arrive_expect_tx_s(bar, tx);
               if (a3) {
-                tma_load_3d_s(sa, ma, 0, ay, ax >> 6, bar);       // both 64-wide halves of A in one copy
+                tma_load_3d_s(sa, ma_t, 0, ay, ax >> 6, bar);     // both 64-wide halves of A in one copy
               } else {
-                tma_load_2d_s(sa, ma, ax, ay, bar);
-                if (na == 2) tma_load_2d_s(sa + 8192, ma, ax + 64, ay, bar);
+                tma_load_2d_s(sa, ma_t, ax, ay, bar);
+                if (na == 2) tma_load_2d_s(sa + 8192, ma_t, ax + 64, ay, bar);
               }
               if (b3) {
                 tma_load_3d_s(sb, mb, 0, by, bx >> 6, bar);       // all 64-wide column blocks of B in one copy
@@ -622,7 +652,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         // A CTA without tiles waits too: the counters only mean "every CTA is past fill u" if no CTA
         // publishes its signal for fill u+1 before fill u+1 exists.
         uint32_t good = 1;
-        if (lane == 0) {
+        // (a tile-segmented phase waits per tile: the producer for the tile's shard, this warp for the tile's destination)
+        if (lane == 0 && !ph.tseg) {
           for (int w = 0; w < RTP_MAX_WAITS && good; ++w)
             if (ph.wait_ctr[w] >= 0)
               good = wait_counter_ge(&P.flags->arrive[ph.wait_ctr[w]].v,
@@ -725,14 +756,17 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       }
       // phase fields used per element live in registers (reading them from parameter space inside the loops costs a
       // dependent constant load each time)
-      const int e_M = ph.M;
-      const int e_N = ph.N;
+      const int p_M = ph.M;
+      const int p_N = ph.N;
       const int e_bn = ph.bn;
+      const int p_tseg = ph.tseg, p_tseg_len = ph.tseg_len;
+      const RtpSegTable& segs = P.segtab[ph.tseg_tab];
+      uint32_t cred_ready = 0;        // segments whose destination has been seen to be free
       const float e_alpha = ph.alpha;
       const const void* e_c = ph.c;
       const long long e_ldc = ph.ldc;
       const int e_c_fp32 = ph.c_fp32;
-      const const void* e_bias = ph.bias;
+      const void* const p_bias = ph.bias;
       const int e_nbias_more = ph.n_bias_more;
       const int e_act = ph.act;
       const const void* e_mask = ph.mask;
@@ -741,7 +775,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const uint32_t e_drop_thresh = ph.drop_thresh;
       const float e_drop_scale = ph.drop_scale;
       const unsigned long long e_drop_seed = ph.drop_seed;
-      void* const e_d = ph.d;
+      void* const p_d = ph.d;
       const long long e_ldd = ph.ldd;
       const int e_d_fp32 = ph.d_fp32;
       const int e_vec_ok = ph.vec_ok;
@@ -753,17 +787,36 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
       const long long e_c_bi = ph.c_bi;
       const int e_cta_off = ph.cta_off;
       // vector accesses of the straight-line path: operands 16-byte aligned (vec_ok), bias too, dropout index a multiple of 4
-      bool e_bias_al = !e_bias || (reinterpret_cast<uintptr_t>(e_bias) & 15) == 0;
+      bool e_bias_al = !p_bias || (reinterpret_cast<uintptr_t>(p_bias) & 15) == 0;
       for (int nb = 0; nb < e_nbias_more; ++nb) e_bias_al = e_bias_al && (reinterpret_cast<uintptr_t>(ph.bias_more[nb]) & 15) == 0;
-      const bool e_fast_ok = e_vec_ok && e_bias_al && (!e_drop_thresh || (e_N & 3) == 0);
+      if (p_tseg)
+        for (int sgi = 0; sgi < ph.tseg_n; ++sgi)
+          e_bias_al = e_bias_al && (reinterpret_cast<uintptr_t>(segs.bias[sgi]) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(segs.d[sgi]) & 15) == 0;
+      const bool e_fast_ok = e_vec_ok && e_bias_al && (!e_drop_thresh || ((p_tseg == 1 ? p_tseg_len : p_N) & 3) == 0);
       for (int t = tile_cta ? (unit - e_cta_off + GU) % GU : total; t < total && ok; t += GU) {
         const bool e_batch1 = e_batch_inner == 1 && per_batch == total;
         const int z = e_batch1 ? 0 : t / per_batch, tt = e_batch1 ? t : t - z * per_batch;
         const int tn = tt / tiles_m;
-        const int m0u = (tt - tn * tiles_m) * TM;
-        const int m0 = m0u + (int)crank * kBM;
-        const int n0 = tn * e_bn;
+        int m0u = (tt - tn * tiles_m) * TM;
+        int n0 = tn * e_bn;
         if (e_causal == 1 && n0 > m0u + TM - 1) continue;
+        // Tile-segmented phase: from here on the tile lives in its segment's coordinates (local row / column, the
+        // segment's destination, bias and extent).
+        int e_M = p_M, e_N = p_N;
+        void* e_d = p_d;
+        const void* e_bias = p_bias;
+        unsigned long long drop_off_t = drop_off;
+        int sgt = 0;
+        if (p_tseg) {
+          sgt = (p_tseg == 1 ? n0 : m0u) / p_tseg_len;
+          if (p_tseg == 1) { n0 -= sgt * p_tseg_len; e_N = p_tseg_len; }
+          else { m0u -= sgt * p_tseg_len; e_M = p_tseg_len; }
+          e_d = segs.d[sgt];
+          e_bias = segs.bias[sgt];
+          drop_off_t += (unsigned long long)segs.drop_add[sgt];
+        }
+        const int m0 = m0u + (int)crank * kBM;
         const long long zoff_d = e_batch1 ? 0ll : (long long)(z / e_batch_inner) * e_d_bo + (long long)(z % e_batch_inner) * e_d_bi;
         const long long zoff_c = e_batch1 ? 0ll : (long long)(z / e_batch_inner) * e_c_bo + (long long)(z % e_batch_inner) * e_c_bi;
         uint32_t good = 1;
@@ -772,6 +825,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         if (lane == 0) good = mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag, status, timeout_ns);
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) { ok = false; break; }
+        if (p_tseg && segs.credit_ptr[sgt] && !((cred_ready >> sgt) & 1u)) {
+          // first tile of this CTA for the segment: the destination slot must have been read by its owner
+          if (lane == 0)
+            good = wait_counter_ge(segs.credit_ptr[sgt], credit_target(ctl->uses, segs.credit_ctr[sgt], 0), abort_flag, status,
+                                   wait_ns, ST_TIMEOUT_CREDIT);
+          good = __shfl_sync(0xffffffffu, good, 0);
+          if (!good) { ok = false; break; }
+          cred_ready |= 1u << sgt;
+        }
         tc_fence_after();
         if (tr_on) P.trace[2 * 256 + tr_e * 4 + 1] = globaltimer_ns();
         const int row = m0 + quad * 32 + lane;
@@ -855,7 +917,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
                   ((unsigned long long)row * (unsigned long long)e_N + (unsigned long long)col0) >> 2;
 #pragma unroll
               for (int q = 0; q < 8; ++q) {
-                const uint4 rr = philox4x32(e_drop_seed, drop_off, e4 + q);
+                const uint4 rr = philox4x32(e_drop_seed, drop_off_t, e4 + q);
                 v[4 * q] = rr.x >= e_drop_thresh ? v[4 * q] * e_drop_scale : 0.f;
                 v[4 * q + 1] = rr.y >= e_drop_thresh ? v[4 * q + 1] * e_drop_scale : 0.f;
                 v[4 * q + 2] = rr.z >= e_drop_thresh ? v[4 * q + 2] * e_drop_scale : 0.f;
@@ -944,8 +1006,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
             if (e_drop_thresh) {
               // element index = position in the logical [M, N] output; 8 | col so two philox calls cover the group
               const unsigned long long e = (unsigned long long)row * (unsigned long long)e_N + (unsigned long long)col;
-              uint4 r0 = philox4x32(e_drop_seed, drop_off, e >> 2);
-              uint4 r1 = philox4x32(e_drop_seed, drop_off, (e >> 2) + 1);
+              uint4 r0 = philox4x32(e_drop_seed, drop_off_t, e >> 2);
+              uint4 r1 = philox4x32(e_drop_seed, drop_off_t, (e >> 2) + 1);
               const uint32_t rw[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
               for (int i = 0; i < 8; ++i) v[i] = rw[i] >= e_drop_thresh ? v[i] * e_drop_scale : 0.f;
@@ -1014,6 +1076,24 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       // small vector job (bias-gradient hop) by CTA 0
+      if (ok && cta == 0 && p_tseg) {
+        // bias-gradient rows of every segment (fp32 column sums -> the segment's destination)
+        for (int sgi = 0; sgi < ph.tseg_n; ++sgi) {
+          if (!segs.vec_out[sgi]) continue;
+          if (segs.credit_ptr[sgi] && !((cred_ready >> sgi) & 1u)) {
+            uint32_t good = 1;
+            if (lane == 0)
+              good = wait_counter_ge(segs.credit_ptr[sgi], credit_target(ctl->uses, segs.credit_ctr[sgi], 0), abort_flag, status,
+                                     wait_ns, ST_TIMEOUT_CREDIT);
+            good = __shfl_sync(0xffffffffu, good, 0);
+            if (!good) { ok = false; break; }
+            cred_ready |= 1u << sgi;
+          }
+          __nv_bfloat16* vo = reinterpret_cast<__nv_bfloat16*>(segs.vec_out[sgi]);
+          const float* va = ph.vec_add + segs.vec_off[sgi];
+          for (int i = epi_tid; i < ph.vec_len; i += 128) vo[i] = __float2bfloat16(va[i]);
+        }
+      }
       if (ok && does_vec) {
         for (int i = epi_tid; i < ph.vec_len; i += 128) {
           float x = ph.vec_add[i];
@@ -1131,7 +1211,17 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         if (live) __threadfence_system();
         while (sent < have) {
           while (P.phases[next_p].arrive_ptr == nullptr) ++next_p;
-          if (live) red_relaxed_sys_add(P.phases[next_p].arrive_ptr, 1ull);
+          const RtpPhase& sp = P.phases[next_p];
+          if (live) {
+            if (sp.tseg) {
+              // a tile-segmented phase announces every segment's destination
+              const RtpSegTable& st = P.segtab[sp.tseg_tab];
+              for (int i = 0; i < sp.tseg_n; ++i)
+                if (st.arrive_ptr[i]) red_relaxed_sys_add(st.arrive_ptr[i], 1ull);
+            } else {
+              red_relaxed_sys_add(sp.arrive_ptr, 1ull);
+            }
+          }
           ++next_p;
           ++sent;
         }

@@ -73,6 +73,12 @@ struct RtpPhase {
   int nseg;
   int seg_a_off_k[RTP_MAX_WAITS];
   int seg_b_map[RTP_MAX_WAITS];
+  // Tile-segmented phase (tseg != 0): the OUTPUT falls into tseg_n segments of tseg_len columns (tseg = 1) or rows
+  // (tseg = 2), one per weight shard; M / N of the phase span all segments.  Per-segment operands, destinations and
+  // counters come from RtpProgram::segtab[tseg_tab] (wait_ctr[i] / done_ctr[i] of this phase belong to segment i).
+  // One phase instead of one per shard: the fixed cost of a phase (counter polls, hand-off, done reports: ~3 us) is
+  // paid once per launch instead of N times.
+  int tseg, tseg_len, tseg_n, tseg_tab;
   // synchronisation (all optional)
   int wait_ctr[RTP_MAX_WAITS];  // local arrival counters that must reach fill (uses + rel + 1) before operands are read
   int wait_rel[RTP_MAX_WAITS];
@@ -125,6 +131,21 @@ struct RtpPhase {
   long long r_n;  // elements, multiple of 8
 };
 
+// Per-segment data of a tile-segmented phase (see RtpPhase::tseg).  Segment order = order of arrival of the shards.
+struct RtpSegTable {
+  int map[RTP_MAX_WAITS];        // tensor map of the segmented operand (B if tseg = 1, A if tseg = 2); -1: the phase's own
+  int off_mn[RTP_MAX_WAITS];     // mn offset of that operand for the segment (tile coordinates are local to the segment)
+  int drop_add[RTP_MAX_WAITS];   // added to the phase's dropout offset
+  void* d[RTP_MAX_WAITS];        // output base of the segment (pitch = the phase's ldd)
+  const void* bias[RTP_MAX_WAITS];
+  unsigned long long* credit_ptr[RTP_MAX_WAITS];   // local credit counter that must reach uses + 0 before d[i] is written
+  int credit_ctr[RTP_MAX_WAITS];
+  unsigned long long* arrive_ptr[RTP_MAX_WAITS];   // remote arrival counter bumped once per CTA when the phase is done
+  void* vec_out[RTP_MAX_WAITS];                    // per-segment vector job: vec_out[i][k] = vec_add[vec_off[i] + k], k < vec_len
+  long long vec_off[RTP_MAX_WAITS];
+};
+#define RTP_MAX_SEGTABS 3
+
 struct RtpPush {
   const void* src;
   void* dst;  // peer memory
@@ -153,5 +174,6 @@ struct alignas(64) RtpProgram {
   alignas(64) CUtensorMap maps[RTP_MAX_MAPS];
   RtpPhase phases[RTP_MAX_PHASES];
   RtpPush pushes[RTP_MAX_PUSHES];
+  RtpSegTable segtab[RTP_MAX_SEGTABS];
 };
 
