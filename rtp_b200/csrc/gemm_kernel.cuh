@@ -454,6 +454,17 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
           }
           int ax = (p_a_mn ? a_mn0 : a_k0) + kb0 * a_dx, ay = (p_a_mn ? a_k0 : a_mn0) + kb0 * a_dy;
           int bx = (p_b_mn ? b_mn0 : b_k0) + kb0 * b_dx, by = (p_b_mn ? b_k0 : b_mn0) + kb0 * b_dy;
+          // Self-check: a tiled copy must start on a 16-byte boundary in its innermost coordinate (8 elements; a whole
+          // 64-element block for the 3-D maps).  A violation is recorded with the phase and the coordinate and the
+          // copy is never issued.
+          if (((a3 ? (ax & 63) : (ax & 7)) | (b3 ? (bx & 63) : (bx & 7))) != 0) {
+            atomicCAS(status, (unsigned long long)ST_OK,
+                      (unsigned long long)ST_BAD_ARGUMENT | ((unsigned long long)(p & 0xff) << 8) |
+                          ((unsigned long long)(uint32_t)(ax & 0xfffff) << 16) | ((unsigned long long)(uint32_t)(bx & 0xfffff) << 40));
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
           if (P.trace && cta == 0 && tr_n < 60) P.trace[0 * 256 + tr_n * 4 + 0] = globaltimer_ns();
           for (int sg = 0; sg < nseg && ok; ++sg) {
           if (nseg > 1) {

@@ -236,7 +236,7 @@ def check(rc: int, what: str):
                 v = int(w.item())
                 if v:
                     w.zero_()
-                    raise RotationTimeout(STATUS_NAMES.get(v, f"status {v}"))
+                    raise RotationTimeout(status_text(v))
             for hook in _after_launch_hooks:
                 hook()
         except RotationTimeout as e:
@@ -267,6 +267,15 @@ STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "wait for a peer's dat
                 3: "wait for a peer's free slot timed out", 4: "bad argument"}
 
 
+def status_text(v: int) -> str:
+    """Status word of a kernel in words.  A bad-argument code from the rotation GEMM's producer carries the phase and the
+    two offending copy coordinates in its upper bits."""
+    if (v & 0xff) == 4 and v > 0xff:
+        return (f"bad argument: unaligned copy coordinate in phase {(v >> 8) & 0xff} "
+                f"(A x = {(v >> 16) & 0xfffff}, B x = {(v >> 40) & 0xfffff})")
+    return STATUS_NAMES.get(v, f"status {v}")
+
+
 class RotationTimeout(RuntimeError):
     """A bounded device-side wait expired; the kernel returned early and its outputs are invalid."""
 
@@ -277,4 +286,4 @@ def check_status(device=None):
     v = int(w.item())
     if v != 0:
         w.zero_()
-        raise RotationTimeout(STATUS_NAMES.get(v, f"status {v}"))
+        raise RotationTimeout(status_text(v))

@@ -192,7 +192,7 @@ class FusedEngine:
         v = self._host_status.value
         if v:
             _lib.check(_lib.lib().rtp_ws_reset(self.ws_local, _lib.stream_ptr()), "rtp_ws_reset")
-            raise _lib.RotationTimeout(_lib.STATUS_NAMES.get(v, f"status {v}"))
+            raise _lib.RotationTimeout(_lib.status_text(v))
 
 
 class EpochMismatch(RuntimeError):
