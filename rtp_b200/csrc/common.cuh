@@ -1,7 +1,7 @@
 // Shared device helpers for the sm_100a kernels of rtp_b200: mbarrier, TMA, tcgen05 (TMEM + UMMA)
 // wrappers written as inline PTX, system-scope flag operations for peer memory, and bounded waits.
 //
-// Every wait in this library is bounded: a spin that runs out of budget records an error code in a
+// Every wait in this library is bounded: a spin that runs out of time records an error code in a
 // status word and the kernel returns normally, so a missing producer never hangs a GPU.
 #pragma once
 #include <cuda.h>
@@ -16,9 +16,9 @@ namespace rtp {
 // ---------------------------------------------------------------------------------------------
 enum : unsigned long long {
   ST_OK = 0,
-  ST_TIMEOUT_MBAR = 1,       // an mbarrier wait inside a CTA ran out of budget
-  ST_TIMEOUT_ARRIVAL = 2,    // a wait for a peer's "data arrived" counter ran out of budget
-  ST_TIMEOUT_CREDIT = 3,     // a wait for a peer's "slot free" counter ran out of budget
+  ST_TIMEOUT_MBAR = 1,       // an mbarrier wait inside a CTA ran out of time
+  ST_TIMEOUT_ARRIVAL = 2,    // a wait for a peer's "data arrived" counter ran out of time
+  ST_TIMEOUT_CREDIT = 3,     // a wait for a peer's "slot free" counter ran out of time
   ST_BAD_ARGUMENT = 4,
 };
 

@@ -71,7 +71,7 @@ def main():
             fails.append(msg)
             print(f"[rank {rank}] FAIL {msg}", flush=True)
 
-    def judge(name, fused, func, oracle, floor=4e-3, tiles=True):
+    def compare(name, fused, func, oracle, floor=4e-3, tiles=True):
         ef, en = rel_err(fused, oracle), rel_err(func, oracle)
         check(ef <= 2 * en + floor, f"{name}: fused error {ef:.4g} vs functional {en:.4g} (fp32 oracle)")
         if tiles:
@@ -119,10 +119,10 @@ def main():
             engine.check_all()
             _lib.check_status(dev)
             fused_ran(n0, cls.__name__)
-            judge(f"{cls.__name__} y rep {rep}", y, yf, y_or)
-            judge(f"{cls.__name__} dx", x.grad, gx_f, dx_or)
-            judge(f"{cls.__name__} dW", m.linear.weight.grad, gw_f, dW_sh)
-            judge(f"{cls.__name__} db", m.linear.bias.grad, gb_f, db_sh, tiles=False)
+            compare(f"{cls.__name__} y rep {rep}", y, yf, y_or)
+            compare(f"{cls.__name__} dx", x.grad, gx_f, dx_or)
+            compare(f"{cls.__name__} dW", m.linear.weight.grad, gw_f, dW_sh)
+            compare(f"{cls.__name__} db", m.linear.bias.grad, gb_f, db_sh, tiles=False)
             zero_grads(m)
             x.grad = None
         if getattr(m, "inplace", False):
@@ -130,7 +130,7 @@ def main():
             with torch.no_grad():
                 y1, y2 = m(x), m(x)
             check(torch.equal(y1, y2) and not m._displaced, f"{cls.__name__}: repeated no-grad forwards differ")
-            judge(f"{cls.__name__} no-grad y", y1, yf, y_or)
+            compare(f"{cls.__name__} no-grad y", y1, yf, y_or)
 
     # ------------------------------------------------------------------ a head whose width the kernels cannot take
     torch.manual_seed(1)
@@ -163,7 +163,7 @@ def main():
     engine.check_all()
     fused_ran(n0, "ParallelEmbedding")
     check(torch.equal(e, ef), "embedding forward differs from the functional path")
-    judge("embedding dW", emb.embedding.weight.grad, ge_f, g_or.chunk(world, dim=1)[rank], floor=1e-2)
+    compare("embedding dW", emb.embedding.weight.grad, ge_f, g_or.chunk(world, dim=1)[rank], floor=1e-2)
 
     # ------------------------------------------------------------------ attention: causal, masks, dropout, in-place
     torch.manual_seed(3)
@@ -205,8 +205,8 @@ def main():
             engine.check_all()
             _lib.check_status(dev)
             fused_ran(n0, f"{cls.__name__} {kind}")
-            judge(f"{cls.__name__} L{L_} {kind} y", yk, yf, yr.detach(), floor=1e-2)
-            judge(f"{cls.__name__} L{L_} {kind} dx", xq.grad, gx_f, xr.grad, floor=1.5e-2)
+            compare(f"{cls.__name__} L{L_} {kind} y", yk, yf, yr.detach(), floor=1e-2)
+            compare(f"{cls.__name__} L{L_} {kind} dx", xq.grad, gx_f, xr.grad, floor=1.5e-2)
             # in_proj gradient of the full layer needs every rank's batch: compare with the functional path
             e_in = rel_err(mha.MultiheadAttention.in_proj_weight.grad, gin_f)
             check(e_in < 3e-2, f"{cls.__name__} L{L_} {kind} d(in_proj): {e_in:.4g} vs functional")
@@ -268,7 +268,7 @@ def main():
             res[be] = (out.detach().clone(), {n: p.grad.clone() for n, p in wrapped.named_parameters()})
         set_backend("auto")
         out_or = ref32(img.float())
-        judge(f"wrapper(inplace={inplace}) logits", res["auto"][0], res["functional"][0], out_or.detach(), floor=1e-2)
+        compare(f"wrapper(inplace={inplace}) logits", res["auto"][0], res["functional"][0], out_or.detach(), floor=1e-2)
         full_g = {n: p.grad for n, p in ref32.named_parameters()}
         for n, g in res["auto"][1].items():
             base = n.replace("module.", "")
@@ -276,7 +276,7 @@ def main():
             if g.shape != fg.shape:                      # a shard: cut the oracle the same way
                 dim = [i for i, (a_, b_) in enumerate(zip(g.shape, fg.shape)) if a_ != b_][0]
                 fg = fg.chunk(world, dim=dim)[rank]
-            judge(f"wrapper(inplace={inplace}) grad {n}", g, res["functional"][1][n], fg, floor=1.5e-2,
+            compare(f"wrapper(inplace={inplace}) grad {n}", g, res["functional"][1][n], fg, floor=1.5e-2,
                   tiles=g.dim() == 2)
 
     # ------------------------------------------------------------------ whole LM: fused trainer and module path vs fp32 oracle

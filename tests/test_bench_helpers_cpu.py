@@ -84,3 +84,31 @@ def test_guard_bands_catch_an_overrun():
     torch.as_strided(t, (1,), (1,), storage_offset=t.storage_offset() + 35).fill_(3.0)   # one element past the end
     with pytest.raises(AssertionError, match="AFTER tensor 'overrun'"):
         check_guards()
+
+
+def test_both_arms_moe_configs_take_one_expert_per_rank():
+    """The reference's rotating expert layer only works with one local expert and a capacity factor of 1.0: the configs
+    that both arms can run say so (0 experts = as many as ranks)."""
+    import bench
+    for name in ("moe-cf1", "moe-small-cf1"):
+        assert bench.CONFIGS[name]["n_experts"] == 0 and bench.CONFIGS[name]["capacity_factor"] == 1.0
+    assert bench.CONFIGS["moe"]["n_experts"] == 8
+
+
+def test_status_text_decodes_the_producer_self_check():
+    from rtp_b200.ops import _lib
+    assert _lib.status_text(2) == _lib.STATUS_NAMES[2]
+    code = 4 | (3 << 8) | (520 << 16) | (12 << 40)
+    text = _lib.status_text(code)
+    assert "phase 3" in text and "A x = 520" in text and "B x = 12" in text
+
+
+def test_recompute_tags_are_a_gpu_only_affair():
+    """On CPU tensors the functional ops are plain PyTorch and nothing is tagged; the switch round-trips."""
+    import torch
+    from rtp_b200.ops import functional as FO
+    x = torch.randn(4, 16, requires_grad=True)
+    y = FO.gelu(x)
+    assert FO.recompute_tag(y) is None
+    old = FO.set_activation_recompute(False)
+    assert FO.set_activation_recompute(old) is False
