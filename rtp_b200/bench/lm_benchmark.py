@@ -69,7 +69,8 @@ def train(args, rank, world, device, dtype):
     start_step = 0
     if args.resume:
         from ..checkpoint import load_sharded
-        start_step = load_sharded(args.resume, model, None if fused else opt)
+        # the fused trainer plays the optimizer's part: its state_dict carries the Adam moments and the step counters
+        start_step = load_sharded(args.resume, model, trainer if fused else opt)
     if device.type == "cuda":
         torch.cuda.reset_peak_memory_stats(device)
     tokens, t_ms, e0 = 0, 0.0, None
@@ -116,7 +117,7 @@ def train(args, rank, world, device, dtype):
     peak = peak_memory_gib(device) if device.type == "cuda" else 0.0
     if args.checkpoint_dir:
         from ..checkpoint import save_sharded
-        save_sharded(args.checkpoint_dir, model, None if fused else opt, step=start_step + args.max_batch)
+        save_sharded(args.checkpoint_dir, model, trainer if fused else opt, step=start_step + args.max_batch)
     log.summary(mode=args.mode, world=world, tokens_per_s_per_rank=wps_rank, tokens_per_s_box=wps_rank * world,
                 ms_per_step=t_ms / max(args.max_batch, 1), peak_allocated_gib=peak, final_loss=loss_val)
     if rank == 0:
