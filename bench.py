@@ -66,6 +66,9 @@ def parse():
     ap.add_argument("--path", default="trainer", choices=["trainer", "module"],
                     help="README config of this framework: the fused trainer (default) or rotated modules + autograd "
                          "with a torch-style loop and ShardedAdam")
+    ap.add_argument("--loss-chunk-rows", type=int, default=0,
+                    help="GPT / Llama configs: evaluate LM head + cross-entropy this many tokens at a time, forward and "
+                         "backward of the head inside the loss, so that the [tokens, vocab] logits never exist (0 = off)")
     ap.add_argument("--keep-grads", action="store_true",
                     help="fused trainer: keep every gradient until one Adam launch at the end of the step (more memory, "
                          "a few launches fewer) instead of updating each decoder layer right after its backward")
@@ -291,10 +294,12 @@ def run_ours_module(args, cfg, rank, local, world):
     on_dev = dict(device=dev, dtype=torch.bfloat16)      # shards are created and initialised on the GPU
     if fam == "gpt":
         from rtp_b200.models.gpt import GPT, GPTConfig
-        model = GPT(GPTConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"]), **on_dev)
+        model = GPT(GPTConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"],
+                              loss_chunk_rows=args.loss_chunk_rows), **on_dev)
     elif fam == "llama":
         from rtp_b200.models.llama import Llama, LlamaConfig
-        model = Llama(LlamaConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"]), **on_dev)
+        model = Llama(LlamaConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"],
+                                  loss_chunk_rows=args.loss_chunk_rows), **on_dev)
     else:
         if world >= 8:
             # Rotating experts on 8 ranks faulted twice in plain runs with an illegal-instruction error whose cause has

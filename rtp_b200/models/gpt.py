@@ -29,6 +29,7 @@ class GPTConfig:
     max_seq_len: int = 2048
     dropout: float = 0.0
     init_std: float = 0.02
+    loss_chunk_rows: int = 0     # > 0: LM head + cross-entropy this many tokens at a time (no full logits)
 
     @staticmethod
     def gpt_1p3b():
@@ -80,6 +81,9 @@ class GPT(nn.Module):
         x = self.drop(self.tok(ids) + self.pos[:S])
         for blk in self.blocks:
             x = blk(x)
+        if targets is not None and self.cfg.loss_chunk_rows > 0:
+            # head and loss chunk by chunk: the [tokens, vocab] logits never exist as a whole
+            return FO.chunked_head_loss(self.ln_f(x), targets, self.head, self.cfg.loss_chunk_rows)
         logits = self.head(self.ln_f(x))
         if targets is None:
             return logits

@@ -29,6 +29,7 @@ class LlamaConfig:
     rope_theta: float = 10000.0
     norm_eps: float = 1e-5
     init_std: float = 0.02
+    loss_chunk_rows: int = 0     # > 0: LM head + cross-entropy this many tokens at a time (no full logits)
 
     @staticmethod
     def llama_13b():
@@ -119,6 +120,9 @@ class Llama(nn.Module):
         x = self.tok(ids)
         for blk in self.blocks:
             x = blk(x, cos, sin)
+        if targets is not None and self.cfg.loss_chunk_rows > 0:
+            # head and loss chunk by chunk: the [tokens, vocab] logits never exist as a whole
+            return FO.chunked_head_loss(self.norm(x), targets, self.head, self.cfg.loss_chunk_rows)
         logits = self.head(self.norm(x))
         if targets is None:
             return logits

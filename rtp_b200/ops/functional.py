@@ -206,3 +206,67 @@ def swiglu(g, u):
         g, u = g.contiguous(), u.contiguous()
         return _tag(_SwigluFn.apply(g, u), "swiglu", g, u)
     return F.silu(g) * u
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# LM head + cross-entropy without the [tokens, vocab] logits
+# ---------------------------------------------------------------------------------------------------------------------
+class _ChunkedHeadLossFn(torch.autograd.Function):
+    """Mean token cross-entropy of ``head(hidden)``, evaluated ``chunk_rows`` tokens at a time.  Forward AND backward of the
+    head run chunk by chunk inside ``forward`` (the loss is the last op of a language model, so nothing is lost by doing
+    the head's backward early): only one chunk of logits and of their gradient exists at any time — 0.4 GB instead of
+    2 x 1.6 GB for 16 384 tokens of a 50 304-word vocabulary at 4 096 rows per chunk.  ``backward`` scales the stashed
+    gradients by the incoming one.  The reference computes the full logits and hands them to ``nn.CrossEntropyLoss``
+    (benchmarks/rtp_benchmark.py:182, rtp/models/transformer_lm_rtp.py:218-228).
+
+    A rotated head pushes its shards once per chunk and direction; with N ranks that is 2 (N-1)/N of the head's bytes per
+    chunk over NVLink, small against a chunk's GEMMs."""
+
+    @staticmethod
+    def forward(ctx, hidden, target, head, chunk_rows, ignore_index, *params):
+        h2d = hidden.reshape(-1, hidden.shape[-1])
+        t1d = target.reshape(-1)
+        M = h2d.shape[0]
+        n_valid = (t1d != ignore_index).sum().clamp(min=1)
+        dx = torch.empty_like(h2d)
+        gsum = [None] * len(params)
+        total = torch.zeros((), dtype=torch.float32, device=h2d.device)
+        for r0 in range(0, M, chunk_rows):
+            r1 = min(r0 + chunk_rows, M)
+            with torch.enable_grad():
+                hc = h2d[r0:r1].detach().requires_grad_(True)
+                logits = head(hc)
+                # sum over the chunk's tokens; the division by the global count happens once, below
+                loss_c = F.cross_entropy(logits.float(), t1d[r0:r1], ignore_index=ignore_index, reduction="sum") \
+                    if not use_kernels(logits) or logits.shape[-1] % 8 else \
+                    cross_entropy(logits, t1d[r0:r1], ignore_index) * (t1d[r0:r1] != ignore_index).sum().clamp(min=1)
+                grads = torch.autograd.grad(loss_c, [hc] + list(params), allow_unused=True)
+            total += loss_c.detach().float()
+            dx[r0:r1] = grads[0]
+            for k, g in enumerate(grads[1:]):
+                if g is None:
+                    continue
+                gsum[k] = g.detach().float() if gsum[k] is None else gsum[k].add_(g)     # fp32 across the chunks
+            del logits, loss_c, grads, hc
+        inv = 1.0 / n_valid.to(torch.float32)
+        ctx.save_for_backward(dx, inv, *[g if g is not None else torch.zeros(0, device=h2d.device) for g in gsum])
+        ctx.has = [g is not None for g in gsum]
+        ctx.dtypes = [p.dtype for p in params]
+        ctx.shape = hidden.shape
+        return total * inv
+
+    @staticmethod
+    def backward(ctx, gout):
+        dx, inv, *gs = ctx.saved_tensors
+        scale = (gout.to(torch.float32) * inv)
+        dh = (dx.float() * scale).to(dx.dtype).view(ctx.shape)
+        gp = [(g * scale).to(dt) if has else None for g, has, dt in zip(gs, ctx.has, ctx.dtypes)]
+        return (dh, None, None, None, None, *gp)
+
+
+def chunked_head_loss(hidden, target, head, chunk_rows: int = 4096, ignore_index: int = -100):
+    """``cross_entropy(head(hidden), target)`` without ever holding more than ``chunk_rows`` rows of logits (see
+    :class:`_ChunkedHeadLossFn`).  ``head`` is any module (a rotated ``ColumnParallelLinear`` included); its parameters
+    receive their gradients through autograd as usual."""
+    params = [p for p in head.parameters() if p.requires_grad]
+    return _ChunkedHeadLossFn.apply(hidden, target, head, int(chunk_rows), ignore_index, *params)
