@@ -191,6 +191,15 @@ int rtp_ws_status(void* ws, unsigned long long* host_out, void* stream);  // rea
 // Race-detection aid: copies the arrive[], done[] and uses[] counters of this rank's flag block to host_out
 // (3 * rtp_ws_num_counters() words; synchronises the stream).  At a quiescent point uses[] must be the same on every
 // rank of the ring and arrive[c] == done[c] == uses[c] * CTAs for every slot counter c.
+// Program lint (host only, no GPU needed): builds the rotation programs of every rank of a made-up ring and checks copy
+// alignment, tile segments, overlapping output tiles and the cross-rank counter protocol (one producer per arrival
+// counter, matching credit, writes inside the slot, `done` reports, equal fill counts).  Returns the number of problems;
+// `report` receives one line per problem.
+// `inject` (0 = off) damages rank 0's program in one of five ways so that the lint can be tested itself.
+int rtp_lint_linear(int world, int ctas, unsigned long long slot_bytes, int mode, int M, int in_features, int out_features,
+                    int has_bias, int backward, int need_dx, int inject, char* report, int cap);
+int rtp_lint_experts(int world, int ctas, unsigned long long slot_bytes, int n_local, int cap_tokens, int in_features,
+                     int out_features, int has_bias, int backward, int need_dx, char* report, int cap);
 int rtp_ws_num_counters(void);
 int rtp_ws_counters(void* ws, unsigned long long* host_out, void* stream);
 void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i, int world);   // logical weight slot i = bank * 8 + index

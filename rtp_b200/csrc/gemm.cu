@@ -17,6 +17,8 @@
 #include <cooperative_groups.h>
 #include <mutex>
 #include <string>
+#include <vector>
+#include <algorithm>
 #include <cstring>
 #include <cstdio>
 #include <cstdlib>
@@ -1089,6 +1091,264 @@ int run_emu(const RtpRing* rings, const Op* ops, Builder build, cudaStream_t str
   return launch<NEMU>(params, rings[0].ctas * NEMU, true, stream);
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Program lint: builds the programs of ALL ranks of a ring on the host (no GPU needed: tensor maps are recorded by a
+// stand-in encoder, workspaces and operands are made-up addresses) and checks what the kernel relies on:
+//   * every tiled copy starts on a 16-byte boundary of its innermost coordinate and inside its tensor;
+//   * tile segments divide the output evenly and no two tiles of non-accumulating phases write the same bytes;
+//   * the cross-rank protocol is consistent: every arrival counter a rank waits on has exactly ONE producer on the
+//     ring (a push job or a phase / segment that announces its output), that producer waits for the matching credit in
+//     its own flag block and writes inside the slot the counter belongs to, the consumer reports the slot `done`, and
+//     the per-slot fill counts advance identically on every rank.
+// The tile arithmetic mirrors rtp_gemm_kernel's producer and epilogue.
+// ------------------------------------------------------------------------------------------------
+struct Lint {
+  std::string rep;
+  int problems = 0;
+  void bad(const std::string& s) {
+    ++problems;
+    if (rep.size() < 6000) rep += s + "\n";
+  }
+};
+std::string lstr(long long v) { return std::to_string(v); }
+
+const rtp::HostTensorMap* host_map(const CUtensorMap* m) {
+  const rtp::HostTensorMap* h = reinterpret_cast<const rtp::HostTensorMap*>(m);
+  return h->magic == rtp::kHostMapMagic ? h : nullptr;
+}
+
+// one tiled copy of operand `which` ('A' / 'B') of phase p: coordinate (mn, k) in elements
+// (`may_be_outside`: the second CTA of a pair may start past a ragged edge; such a copy reads the fill value)
+void lint_copy(Lint& L, int rank, int p, char which, const RtpProgram& P, int map, bool mn_major, long long mn, long long k,
+               bool may_be_outside) {
+  const rtp::HostTensorMap* h = host_map(&P.maps[map]);
+  const std::string at = "rank " + lstr(rank) + " phase " + lstr(p) + " operand " + which + " (map " + lstr(map) + "): ";
+  if (!h) { L.bad(at + "tensor map was never encoded"); return; }
+  if (mn < 0 || k < 0) { L.bad(at + "negative coordinate (" + lstr(mn) + ", " + lstr(k) + ")"); return; }
+  if (P.map3d[map]) {
+    if (mn % 64) L.bad(at + "3-D map needs the mn coordinate to be a multiple of 64, got " + lstr(mn));
+    if (!may_be_outside && ((unsigned long long)(mn / 64) >= h->dims[2] || (unsigned long long)k >= h->dims[1]))
+      L.bad(at + "copy starts outside the tensor: (mn " + lstr(mn) + ", k " + lstr(k) + ")");
+  } else {
+    const long long x = mn_major ? mn : k, y = mn_major ? k : mn;
+    if (x % 8) L.bad(at + "innermost coordinate " + lstr(x) + " is not a multiple of 8 elements (16 bytes)");
+    if (!may_be_outside && ((unsigned long long)x >= h->dims[0] || (unsigned long long)y >= h->dims[1]))
+      L.bad(at + "copy starts outside the tensor: (x " + lstr(x) + ", y " + lstr(y) + ")");
+  }
+}
+
+struct LintRect {
+  unsigned long long base;   // address of the tile's first element
+  long long rows, cols, pitch;   // cols and pitch in bytes
+  int rank, phase;
+};
+bool rects_overlap(const LintRect& a, const LintRect& b) {
+  if (a.pitch != b.pitch) {
+    const unsigned long long a1 = a.base + (a.rows - 1) * a.pitch + a.cols, b1 = b.base + (b.rows - 1) * b.pitch + b.cols;
+    return a.base < b1 && b.base < a1;   // cannot decompose: report any intersection of the spans
+  }
+  const long long P = a.pitch;
+  long long d = (long long)(b.base - a.base);
+  long long q = d >= 0 ? d / P : -((-d + P - 1) / P);
+  const long long rem = d - q * P;   // 0 <= rem < P
+  auto rows_meet = [&](long long off) {   // row i of a meets row j of b with i = j + off
+    const long long lo = off < 0 ? -off : 0, hi = std::min(b.rows - 1, a.rows - 1 - off);
+    return lo <= hi;
+  };
+  if (rem < a.cols && rows_meet(q)) return true;
+  if (rem - P + b.cols > 0 && rows_meet(q + 1)) return true;
+  return false;
+}
+
+void lint_program(Lint& L, const RtpRing& R, int rank, const RtpProgram& P, bool pair, std::vector<LintRect>& rects) {
+  const int TM = pair ? 256 : 128;
+  for (int p = 0; p < P.n_phases; ++p) {
+    const RtpPhase& ph = P.phases[p];
+    if (ph.kind != RTP_KIND_GEMM) continue;
+    const std::string at = "rank " + lstr(rank) + " phase " + lstr(p) + ": ";
+    if (ph.bn != 128 && ph.bn != 256) L.bad(at + "tile width " + lstr(ph.bn));
+    if (ph.batch != 1) continue;   // batched windows (attention) are not part of the rotation programs
+    const RtpSegTable& st = P.segtab[ph.tseg_tab];
+    if (ph.tseg) {
+      const int unit = ph.tseg == 1 ? ph.bn : TM;
+      if (ph.tseg_len % unit) L.bad(at + "segment length " + lstr(ph.tseg_len) + " is not a multiple of the tile (" + lstr(unit) + ")");
+      if ((long long)ph.tseg_n * ph.tseg_len != (ph.tseg == 1 ? ph.N : ph.M)) L.bad(at + "segments do not add up to the phase's extent");
+      if (ph.tseg_n < 1 || ph.tseg_n > RTP_MAX_WAITS) L.bad(at + "segment count " + lstr(ph.tseg_n));
+    }
+    const int tiles_m = (ph.M + TM - 1) / TM, tiles_n = (ph.N + ph.bn - 1) / ph.bn;
+    const int nseg = ph.nseg > 1 ? ph.nseg : 1;
+    for (int tn = 0; tn < tiles_n; ++tn)
+      for (int tm = 0; tm < tiles_m; ++tm)
+        for (int half = 0; half < (pair ? 2 : 1); ++half) {
+          int m0u = tm * TM, n0 = tn * ph.bn;
+          const int bn_local = pair ? ph.bn / 2 : ph.bn;
+          long long a_mn = m0u + half * 128 + ph.a_off_mn, b_mn = n0 + half * bn_local + ph.b_off_mn;
+          int a_map = ph.a_map, b_map = ph.b_map;
+          int sg = 0;
+          long long e_M = ph.M, e_N = ph.N;
+          unsigned long long d = reinterpret_cast<unsigned long long>(ph.d);
+          if (ph.tseg) {
+            sg = (ph.tseg == 1 ? n0 : m0u) / ph.tseg_len;
+            if (sg >= ph.tseg_n) { L.bad(at + "tile outside the segments"); continue; }
+            if (ph.tseg == 1) {
+              b_mn += st.off_mn[sg] - (long long)sg * ph.tseg_len;
+              if (st.map[sg] >= 0) b_map = st.map[sg];
+              n0 -= sg * ph.tseg_len; e_N = ph.tseg_len;
+            } else {
+              a_mn += st.off_mn[sg] - (long long)sg * ph.tseg_len;
+              if (st.map[sg] >= 0) a_map = st.map[sg];
+              m0u -= sg * ph.tseg_len; e_M = ph.tseg_len;
+            }
+            d = reinterpret_cast<unsigned long long>(st.d[sg]);
+            if (!st.d[sg]) L.bad(at + "segment " + lstr(sg) + " has no destination");
+          }
+          for (int s = 0; s < nseg; ++s) {
+            const long long a_k = ph.a_off_k + (nseg > 1 ? ph.seg_a_off_k[s] : 0);
+            lint_copy(L, rank, p, 'A', P, a_map, ph.a_mn != 0, a_mn, a_k, half == 1);
+            lint_copy(L, rank, p, 'B', P, nseg > 1 ? ph.seg_b_map[s] : b_map, ph.b_mn != 0, b_mn, ph.b_off_k, half == 1);
+          }
+          {
+            const long long m0 = m0u + half * 128;
+            if (m0 >= e_M) continue;
+            const int elt = ph.d_fp32 ? 4 : 2;
+            LintRect r;
+            r.base = d + ((unsigned long long)m0 * ph.ldd + n0) * elt;
+            r.rows = std::min<long long>(128, e_M - m0);
+            r.cols = std::min<long long>(ph.bn, e_N - n0) * elt;
+            r.pitch = ph.ldd * elt;
+            r.rank = rank; r.phase = p;
+            if (!ph.c) rects.push_back(r);
+          }
+        }
+  }
+  (void)R;
+}
+
+// which (rank, counter) does an arrival pointer belong to?
+bool find_arrive(const RtpRing& R, const unsigned long long* ptr, int* t_out, int* c_out) {
+  for (int t = 0; t < R.world; ++t)
+    for (int c = 0; c < RTP_NUM_CTR; ++c)
+      if (ptr == &ws_flags(R.ws[t])->arrive[c].v) { *t_out = t; *c_out = c; return true; }
+  return false;
+}
+void slot_range(const RtpRing& R, int t, int c, unsigned long long* lo, unsigned long long* hi) {
+  uint8_t* base = c < RTP_CTR_G0 ? ws_wslot(R.ws[t], R.slot_bytes, c - RTP_CTR_W0, R.world)
+                                 : ws_gslot(R.ws[t], R.slot_bytes, c - RTP_CTR_G0, R.world);
+  *lo = reinterpret_cast<unsigned long long>(base);
+  *hi = *lo + R.slot_bytes;
+}
+
+struct LintProducer { int rank; int t, c; const unsigned long long* credit_ptr; int credit_ctr; unsigned long long lo, hi; std::string what; };
+
+void lint_ring(Lint& L, const std::vector<RtpRing>& rings, const std::vector<RtpProgram>& progs) {
+  const int N = (int)rings.size();
+  std::vector<LintProducer> prods;
+  for (int r = 0; r < N; ++r) {
+    const RtpProgram& P = progs[r];
+    for (int j = 0; j < P.n_pushes; ++j) {
+      const RtpPush& pu = P.pushes[j];
+      LintProducer pr{r, -1, -1, pu.credit_ptr, pu.credit_ctr, reinterpret_cast<unsigned long long>(pu.dst),
+                      reinterpret_cast<unsigned long long>(pu.dst) + pu.bytes, "push " + lstr(j)};
+      if (!pu.arrive_ptr || !find_arrive(rings[r], pu.arrive_ptr, &pr.t, &pr.c))
+        L.bad("rank " + lstr(r) + " push " + lstr(j) + ": arrival pointer is not an arrival counter of the ring");
+      else prods.push_back(pr);
+    }
+    for (int p = 0; p < P.n_phases; ++p) {
+      const RtpPhase& ph = P.phases[p];
+      if (!ph.arrive_ptr) continue;
+      if (ph.tseg) {
+        const RtpSegTable& st = P.segtab[ph.tseg_tab];
+        for (int i = 0; i < ph.tseg_n; ++i) {
+          if (!st.arrive_ptr[i]) continue;
+          const unsigned long long d = reinterpret_cast<unsigned long long>(st.d[i]);
+          const long long rows = ph.tseg == 2 ? ph.tseg_len : ph.M, cols = ph.tseg == 1 ? ph.tseg_len : ph.N;
+          LintProducer pr{r, -1, -1, st.credit_ptr[i], st.credit_ctr[i], d, d + ((rows - 1) * ph.ldd + cols) * 2,
+                          "phase " + lstr(p) + " segment " + lstr(i)};
+          if (!find_arrive(rings[r], st.arrive_ptr[i], &pr.t, &pr.c))
+            L.bad("rank " + lstr(r) + " " + pr.what + ": arrival pointer is not an arrival counter of the ring");
+          else prods.push_back(pr);
+        }
+      } else {
+        const unsigned long long d = reinterpret_cast<unsigned long long>(ph.d);
+        LintProducer pr{r, -1, -1, ph.credit_ptr, ph.credit_ctr, d, d + (((long long)ph.M - 1) * ph.ldd + ph.N) * (ph.d_fp32 ? 4 : 2),
+                        "phase " + lstr(p)};
+        if (ph.kind != RTP_KIND_GEMM) { pr.lo = pr.hi = 0; }
+        if (!find_arrive(rings[r], ph.arrive_ptr, &pr.t, &pr.c))
+          L.bad("rank " + lstr(r) + " phase " + lstr(p) + ": arrival pointer is not an arrival counter of the ring");
+        else prods.push_back(pr);
+      }
+    }
+  }
+  // consumers
+  for (int t = 0; t < N; ++t) {
+    const RtpProgram& P = progs[t];
+    bool waits[RTP_NUM_CTR] = {false}, dones[RTP_NUM_CTR] = {false};
+    for (int p = 0; p < P.n_phases; ++p)
+      for (int w = 0; w < RTP_MAX_WAITS; ++w) {
+        if (P.phases[p].wait_ctr[w] >= 0) waits[P.phases[p].wait_ctr[w]] = true;
+        if (P.phases[p].done_ctr[w] >= 0) dones[P.phases[p].done_ctr[w]] = true;
+      }
+    for (int c = 0; c < RTP_NUM_CTR; ++c) {
+      int n = 0;
+      for (const LintProducer& pr : prods) n += (pr.t == t && pr.c == c);
+      const std::string at = "rank " + lstr(t) + " counter " + lstr(c) + ": ";
+      if (waits[c] && n != 1) L.bad(at + "waited on, but " + lstr(n) + " producers announce it (must be exactly one)");
+      if (!waits[c] && n > 0) L.bad(at + lstr(n) + " producer(s) announce it, nobody waits");
+      if (waits[c] && !dones[c]) L.bad(at + "waited on but never reported done (its credit would never return)");
+      if (waits[c] != (P.uses_inc[c] != 0)) L.bad(at + "fill count and waits disagree (uses_inc " + lstr(P.uses_inc[c]) + ")");
+      if (P.uses_inc[c] != progs[0].uses_inc[c]) L.bad(at + "fill count advances differently from rank 0");
+    }
+  }
+  for (const LintProducer& pr : prods) {
+    const std::string at = "rank " + lstr(pr.rank) + " " + pr.what + " -> rank " + lstr(pr.t) + " counter " + lstr(pr.c) + ": ";
+    if (pr.credit_ptr != &ws_flags(rings[pr.rank].ws[pr.rank])->credit[pr.t][pr.c].v || pr.credit_ctr != pr.c)
+      L.bad(at + "does not wait for the matching credit in its own flag block");
+    unsigned long long lo, hi;
+    slot_range(rings[pr.rank], pr.t, pr.c, &lo, &hi);
+    if (pr.hi > pr.lo && (pr.lo < lo || pr.hi > hi)) L.bad(at + "writes outside the slot the counter belongs to");
+  }
+}
+
+// Self-test of the lint: damages rank 0's program the way a builder bug would.
+void lint_inject(RtpProgram& P, int what) {
+  if (what == 1 && P.n_pushes >= 2) P.pushes[0].arrive_ptr = P.pushes[1].arrive_ptr;   // two producers for one counter
+  if (what == 2) P.phases[0].a_off_k += 4;                                               // a copy off its 16-byte boundary
+  if (what == 3 && P.n_pushes >= 1) P.pushes[0].credit_ctr += 1;                          // waits for the wrong credit
+  if (what == 4 && P.phases[0].tseg && P.phases[0].tseg_n >= 2)                          // two segments, one destination
+    P.segtab[P.phases[0].tseg_tab].d[1] = P.segtab[P.phases[0].tseg_tab].d[0];
+  if (what == 5 && P.n_pushes >= 1) P.pushes[0].bytes += 1ull << 33;                      // a push that leaves its slot
+}
+
+// made-up addresses: workspaces 64 GB apart, operands of rank r in a region of their own
+void* fake_ws(int t) { return reinterpret_cast<void*>((unsigned long long)(t + 1) << 36); }
+void* fake_buf(int r, int which) { return reinterpret_cast<void*>(((unsigned long long)(0x100 + r) << 36) + ((unsigned long long)which << 32)); }
+
+void fake_rings(std::vector<RtpRing>& rings, int world, int ctas, unsigned long long slot_bytes) {
+  rings.assign(world, RtpRing{});
+  for (int r = 0; r < world; ++r) {
+    rings[r].rank = r; rings[r].world = world; rings[r].slot_bytes = slot_bytes; rings[r].ctas = ctas;
+    for (int t = 0; t < world; ++t) rings[r].ws[t] = fake_ws(t);
+  }
+}
+
+int lint_finish(Lint& L, std::vector<LintRect>& rects, char* report, int cap) {
+  // tiles of non-accumulating phases must not write the same bytes (per rank: other ranks write other memory)
+  for (size_t i = 0; i < rects.size() && L.problems < 64; ++i)
+    for (size_t j = i + 1; j < rects.size(); ++j)
+      if (rects[i].rank == rects[j].rank && rects_overlap(rects[i], rects[j])) {
+        L.bad("rank " + lstr(rects[i].rank) + ": a tile of phase " + lstr(rects[i].phase) + " and a tile of phase " +
+              lstr(rects[j].phase) + " write the same bytes");
+        break;
+      }
+  if (report && cap > 0) {
+    const size_t n = std::min<size_t>(L.rep.size(), (size_t)cap - 1);
+    memcpy(report, L.rep.data(), n);
+    report[n] = 0;
+  }
+  return L.problems;
+}
+
 }  // namespace
 
 extern "C" {
@@ -1335,5 +1595,92 @@ int rtp_ws_counters(void* ws, unsigned long long* host_out, void* stream) {
 }
 void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i, int world) { return ws_wslot(ws, slot_bytes, i, world); }
 void* rtp_ws_gslot(void* ws, unsigned long long slot_bytes, int i, int world) { return ws_gslot(ws, slot_bytes, i, world); }
+
+
+// ---- program lint (host only; see the comment above lint_program) -------------------------------------------------
+int rtp_lint_linear(int world, int ctas, unsigned long long slot_bytes, int mode, int M, int in_features, int out_features,
+                    int has_bias, int backward, int need_dx, int inject, char* report, int cap) {
+  rtp::host_tmap_mode() = true;
+  Lint L;
+  std::vector<RtpRing> rings;
+  fake_rings(rings, world, ctas, slot_bytes);
+  std::vector<RtpProgram> progs(world);
+  std::vector<LintRect> rects;
+  const bool col = mode == 0;
+  const long long Os = col ? out_features / world : out_features, Ks = col ? in_features : in_features / world;
+  int rc = 0;
+  for (int r = 0; r < world && rc == 0; ++r) {
+    bool pair;
+    if (!backward) {
+      RtpLinearFwd op = {};
+      op.mode = mode; op.M = M; op.in_features = in_features; op.out_features = out_features;
+      op.home = fake_buf(r, 0); op.bias_off = has_bias ? Os * Ks : -1;
+      op.shard_bytes = (unsigned long long)((Os * Ks + (has_bias ? Os : 0)) * 2 + 15) & ~15ull;
+      op.x = fake_buf(r, 1); op.ldx = in_features; op.y = fake_buf(r, 2); op.ldy = out_features;
+      decide_pair(op.M, (world > 1 && col) ? out_features / world : out_features, ctas);
+      pair = pair_mode();
+      rc = build_linear_fwd(rings[r], op, progs[r]);
+    } else {
+      RtpLinearBwd op = {};
+      op.mode = mode; op.M = M; op.in_features = in_features; op.out_features = out_features;
+      op.home = fake_buf(r, 0); op.bias_off = has_bias ? Os * Ks : -1;
+      op.shard_bytes = (unsigned long long)((Os * Ks + (has_bias ? Os : 0)) * 2 + 15) & ~15ull;
+      op.x = fake_buf(r, 1); op.ldx = in_features; op.dy = fake_buf(r, 2); op.ldy = out_features;
+      if (need_dx) { op.dx = fake_buf(r, 3); op.lddx = in_features; }
+      op.grad_home = fake_buf(r, 4);
+      if (has_bias) op.dbias_full = reinterpret_cast<const float*>(fake_buf(r, 5));
+      decide_pair(op.M, col ? in_features : in_features / world, ctas);
+      pair = pair_mode();
+      rc = build_linear_bwd(rings[r], op, progs[r]);
+    }
+    if (rc) { L.bad("rank " + lstr(r) + ": builder refused: " + g_err); break; }
+    finalize_program(progs[r], ctas, pair);
+    if (r == 0) lint_inject(progs[0], inject);
+    lint_program(L, rings[r], r, progs[r], pair, rects);
+  }
+  if (rc == 0 && world > 1) lint_ring(L, rings, progs);
+  rtp::host_tmap_mode() = false;
+  return lint_finish(L, rects, report, cap);
+}
+
+int rtp_lint_experts(int world, int ctas, unsigned long long slot_bytes, int n_local, int cap_tokens, int in_features,
+                     int out_features, int has_bias, int backward, int need_dx, char* report, int cap) {
+  rtp::host_tmap_mode() = true;
+  Lint L;
+  std::vector<RtpRing> rings;
+  fake_rings(rings, world, ctas, slot_bytes);
+  std::vector<RtpProgram> progs(world);
+  std::vector<LintRect> rects;
+  const long long block = (long long)out_features * in_features + (has_bias ? out_features : 0);
+  const long long stride = (block + 7) & ~7ll;
+  int rc = 0;
+  for (int r = 0; r < world && rc == 0; ++r) {
+    decide_pair(0, 0, ctas);
+    if (!backward) {
+      RtpExpertFwd op = {};
+      op.cap = cap_tokens; op.n_local = n_local; op.in_features = in_features; op.out_features = out_features;
+      op.home = fake_buf(r, 0); op.expert_stride = stride; op.bias_off = has_bias ? (long long)out_features * in_features : -1;
+      op.shard_bytes = (unsigned long long)(stride * n_local * 2 + 15) & ~15ull;
+      op.x = fake_buf(r, 1); op.ldx = in_features; op.y = fake_buf(r, 2); op.ldy = out_features;
+      rc = build_expert_fwd(rings[r], op, progs[r]);
+    } else {
+      RtpExpertBwd op = {};
+      op.cap = cap_tokens; op.n_local = n_local; op.in_features = in_features; op.out_features = out_features;
+      op.home = fake_buf(r, 0); op.expert_stride = stride; op.bias_off = has_bias ? (long long)out_features * in_features : -1;
+      op.shard_bytes = (unsigned long long)(stride * n_local * 2 + 15) & ~15ull;
+      op.x = fake_buf(r, 1); op.ldx = in_features; op.dy = fake_buf(r, 2); op.ldy = out_features;
+      if (need_dx) { op.dx = fake_buf(r, 3); op.lddx = in_features; }
+      op.grad_home = fake_buf(r, 4);
+      if (has_bias) op.dbias_full = reinterpret_cast<const float*>(fake_buf(r, 5));
+      rc = build_expert_bwd(rings[r], op, progs[r]);
+    }
+    if (rc) { L.bad("rank " + lstr(r) + ": builder refused: " + g_err); break; }
+    finalize_program(progs[r], ctas, pair_mode());
+    lint_program(L, rings[r], r, progs[r], pair_mode(), rects);
+  }
+  if (rc == 0 && world > 1) lint_ring(L, rings, progs);
+  rtp::host_tmap_mode() = false;
+  return lint_finish(L, rects, report, cap);
+}
 
 }  // extern "C"

@@ -1,0 +1,36 @@
+"""The host-side lint of the rotation programs: clean on the shapes and ring sizes the library is used with, and it
+notices each kind of damage a builder bug would do (the lint's own self-test through its injection switch)."""
+import pytest
+
+from rtp_b200.utils import lint
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+def test_linear_programs_are_clean(world):
+    for mode, (M, i, o) in [(0, (1024, 2048, 6144)), (1, (1024, 2048, 2048)), (0, (1000, 512, 1024)),
+                            (0, (8192, 2048, 32000)), (1, (256, 4096, 512))]:
+        if (o % world if mode == 0 else i % world):
+            continue
+        for bwd in (False, True):
+            n, lines = lint.lint_linear(world, mode, M, i, o, backward=bwd)
+            assert n == 0, (world, mode, M, i, o, bwd, lines[:5])
+
+
+@pytest.mark.parametrize("world,n_local", [(2, 4), (4, 2), (8, 1)])
+def test_expert_programs_are_clean(world, n_local):
+    for bwd in (False, True):
+        n, lines = lint.lint_experts(world, n_local, 2560, 2048, 8192, backward=bwd)
+        assert n == 0, (world, n_local, bwd, lines[:5])
+
+
+@pytest.mark.parametrize("inject,needle", [(1, "producers announce it"), (2, "not a multiple of 8 elements"),
+                                           (3, "matching credit"), (4, "write the same bytes"),
+                                           (5, "outside the slot")])
+def test_the_lint_notices_damage(inject, needle):
+    n, lines = lint.lint_linear(4, 0, 1024, 2048, 2048, backward=False, inject=inject)
+    assert n > 0 and any(needle in ln for ln in lines), (inject, lines[:6])
+
+
+def test_a_shard_that_does_not_fit_its_slot_is_refused():
+    n, lines = lint.lint_linear(2, 0, 1024, 2048, 2048, slot_bytes=1 << 16)
+    assert n == 1 and "larger than workspace slot" in lines[0]
