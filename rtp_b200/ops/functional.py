@@ -237,9 +237,11 @@ class _ChunkedHeadLossFn(torch.autograd.Function):
                 hc = h2d[r0:r1].detach().requires_grad_(True)
                 logits = head(hc)
                 # sum over the chunk's tokens; the division by the global count happens once, below
-                loss_c = F.cross_entropy(logits.float(), t1d[r0:r1], ignore_index=ignore_index, reduction="sum") \
-                    if not use_kernels(logits) or logits.shape[-1] % 8 else \
-                    cross_entropy(logits, t1d[r0:r1], ignore_index) * (t1d[r0:r1] != ignore_index).sum().clamp(min=1)
+                tc = t1d[r0:r1]
+                if use_kernels(logits) and logits.shape[-1] % 8 == 0:
+                    loss_c = cross_entropy(logits, tc, ignore_index) * (tc != ignore_index).sum().clamp(min=1)
+                else:
+                    loss_c = F.cross_entropy(logits.float(), tc, ignore_index=ignore_index, reduction="sum")
                 grads = torch.autograd.grad(loss_c, [hc] + list(params), allow_unused=True)
             total += loss_c.detach().float()
             dx[r0:r1] = grads[0]
