@@ -599,8 +599,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) rtp_gemm_kernel(const __grid_c
         }
       }
       if (!ok && issued_any) {
-        // make sure no MMA is still reading smem / writing TMEM before tear-down
-        umma_commit(&ctl->drain);
+        // make sure no MMA is still reading smem / writing TMEM before tear-down (a kernel keeps ONE cta_group for all of
+        // its tcgen05 instructions: in a pair the commit is the pair form; the second CTA's drain barrier takes the
+        // other arrival and nobody waits on it)
+        if (PAIR) umma_commit_pair(&ctl->drain); else umma_commit(&ctl->drain);
         unsigned long long t0 = globaltimer_ns();
         while (!mbar_try_wait(&ctl->drain, 0)) {
           if (globaltimer_ns() - t0 > 2000000ull) break;
