@@ -301,10 +301,11 @@ def run_ours_module(args, cfg, rank, local, world):
         model = Llama(LlamaConfig(cfg["vocab"], cfg["ninp"], cfg["nlayers"], cfg["nhead"], cfg["nhid"], cfg["seq_len"],
                                   loss_chunk_rows=args.loss_chunk_rows), **on_dev)
     else:
-        if world >= 8:
-            # Rotating experts on 8 ranks faulted twice in plain runs with an illegal-instruction error whose cause has
-            # not been found; with a synchronise and a status read after every launch the same step runs clean.  Until
-            # then this size runs serialised, and the JSON line says so.
+        if world > 2 or (world > 1 and cfg["ninp"] >= 2048):
+            # Full-size rotating experts on 8 ranks faulted twice in plain runs with an illegal-instruction error whose
+            # cause has not been found; with a synchronise and a status read after every launch the same step runs
+            # clean (4 and 8 ranks).  Plain mode has only been seen clean on one GPU and, with the small shapes, on
+            # two; every other size runs serialised, and the JSON line says so.
             from rtp_b200.ops import _lib
             _lib.set_serialize(True)
             run_ours_module.serialised = True

@@ -13,6 +13,30 @@ from ..parallel.rotated import rotated_apply
 from ..parallel.context import get_context
 
 
+_plain_guard_done = False
+
+
+def _guard_plain_launches(world: int, on_gpu: bool) -> None:
+    """A training step with rotating experts on 8 GPUs ended twice with an illegal-instruction error when its kernels
+    were queued back to back, and ran clean (4 and 8 GPUs) with a synchronise and a status read after every launch; the
+    cause is not known.  Until it is, the first rotating-expert layer that runs on a ring of more than two GPUs turns
+    that serialised mode on for the process (``RTP_MOE_PLAIN=1`` opts out).  Launches inside a CUDA-graph capture are
+    not covered: serialised mode skips them."""
+    global _plain_guard_done
+    if _plain_guard_done or not on_gpu or world <= 2:
+        return
+    _plain_guard_done = True
+    import os
+    import warnings
+    from ..parallel.context import get_backend
+    if get_backend() == "functional" or os.environ.get("RTP_MOE_PLAIN", "0") not in ("", "0"):
+        return
+    from ..ops import _lib
+    if not _lib.set_serialize(True):      # returns the previous setting
+        warnings.warn("rtp_b200: rotating experts on more than two GPUs run with serialised launches (a synchronise "
+                      "after every library launch); set RTP_MOE_PLAIN=1 to queue them back to back", stacklevel=3)
+
+
 class _AllToAll(torch.autograd.Function):
     @staticmethod
     def forward(ctx: Any, group, input: Tensor) -> Tensor:  # type: ignore
@@ -176,6 +200,7 @@ class WeightMOELayer(RotatedModule):
         assert (input[0].shape[0] * input[0].shape[1]) % len(self.experts) == 0, \
             "number of tokens must be a multiple of the number of local experts"
         d_model = input[0].shape[2]
+        _guard_plain_launches(self.world_size, input[0].is_cuda)
         reshaped = input[0].reshape(-1, d_model)
         self.l_aux, dispatch, combine = _route(self.gate, reshaped)
         dispatched = dispatch(reshaped)                          # [E, C, M]

@@ -112,3 +112,30 @@ def test_recompute_tags_are_a_gpu_only_affair():
     assert FO.recompute_tag(y) is None
     old = FO.set_activation_recompute(False)
     assert FO.set_activation_recompute(old) is False
+
+
+def test_rotating_experts_guard_serialises_large_rings(monkeypatch):
+    """Rotating experts on more than two GPUs switch the process to serialised launches, once; small rings, CPU
+    tensors and the opt-out leave the setting alone."""
+    import warnings
+    from rtp_b200.module import moe
+    from rtp_b200.ops import _lib
+    old = _lib.set_serialize(False)
+    try:
+        for world, on_gpu in ((8, False), (2, True), (1, True)):
+            monkeypatch.setattr(moe, "_plain_guard_done", False)
+            moe._guard_plain_launches(world, on_gpu)
+            assert not _lib._serialize and not moe._plain_guard_done
+        monkeypatch.setattr(moe, "_plain_guard_done", False)
+        monkeypatch.setenv("RTP_MOE_PLAIN", "1")
+        moe._guard_plain_launches(4, True)
+        assert not _lib._serialize and moe._plain_guard_done
+        monkeypatch.setattr(moe, "_plain_guard_done", False)
+        monkeypatch.delenv("RTP_MOE_PLAIN")
+        with warnings.catch_warnings(record=True) as seen:
+            warnings.simplefilter("always")
+            moe._guard_plain_launches(4, True)
+            moe._guard_plain_launches(8, True)       # second call: nothing more
+        assert _lib._serialize and len(seen) == 1 and "RTP_MOE_PLAIN" in str(seen[0].message)
+    finally:
+        _lib.set_serialize(old)
