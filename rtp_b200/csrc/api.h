@@ -200,6 +200,11 @@ int rtp_lint_linear(int world, int ctas, unsigned long long slot_bytes, int mode
                     int has_bias, int backward, int need_dx, int inject, char* report, int cap);
 int rtp_lint_experts(int world, int ctas, unsigned long long slot_bytes, int n_local, int cap_tokens, int in_features,
                      int out_features, int has_bias, int backward, int need_dx, char* report, int cap);
+// The same for a chain of rotated linears with cross-launch prefetch, as the fused trainer issues them: `spec` holds 7
+// ints per launch (mode, M, in_features, out_features, has_bias, backward, need_dx); launch k reads bank k & 1 and pushes
+// the shards of launch k + 1 into the other bank.  `flip_bank_at` >= 0 builds that launch with the wrong bank (self-test).
+int rtp_lint_linear_chain(int world, int ctas, unsigned long long slot_bytes, int n_launches, const int* spec,
+                          int flip_bank_at, char* report, int cap);
 int rtp_ws_num_counters(void);
 int rtp_ws_counters(void* ws, unsigned long long* host_out, void* stream);
 void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i, int world);   // logical weight slot i = bank * 8 + index

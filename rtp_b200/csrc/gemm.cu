@@ -511,6 +511,9 @@ int build_linear_bwd(const RtpRing& R, const RtpLinearBwd& op, RtpProgram& P) {
   const int Os = col ? op.out_features / N : op.out_features;
   const int Ks = col ? op.in_features : op.in_features / N;
   if (N > 1 && op.shard_bytes > R.slot_bytes) return fail("shard larger than workspace slot");
+  // shards pushed ahead by the previous launch must be read here: nobody else returns their slots' credits
+  if (N > 1 && op.no_self_push && !op.dx)
+    return fail("a backward launch whose weight shards were pushed ahead has to compute the input gradient (dx is null)");
   if (op.grad_accumulate && N > 1) return fail("grad_accumulate is only supported on a 1-rank ring");
   if (op.bank < 0 || op.bank >= RTP_NUM_WBANKS) return fail("bank out of range");
   const int wb = op.bank * RTP_NUM_SLOTS;   // first weight slot of the bank this launch reads
@@ -1680,6 +1683,111 @@ int rtp_lint_experts(int world, int ctas, unsigned long long slot_bytes, int n_l
     lint_program(L, rings[r], r, progs[r], pair_mode(), rects);
   }
   if (rc == 0 && world > 1) lint_ring(L, rings, progs);
+  rtp::host_tmap_mode() = false;
+  return lint_finish(L, rects, report, cap);
+}
+
+
+// Chain lint: the rotated linears of a training step as the fused trainer issues them.  Launch k reads its visiting
+// shards from weight-slot bank k & 1; launch 0 pushes its own shards, every later launch finds them pushed by its
+// predecessor, and every launch but the last pushes the home shard of its successor into the other bank.  `spec` holds
+// 7 ints per launch: mode, M, in_features, out_features, has_bias, backward, need_dx.  Checked per launch, with the
+// producers of a launch taken to be its own pushes into its bank plus the predecessor's pushes into that bank: the
+// same ring rules as rtp_lint_linear (one producer per awaited counter, matching credit, writes inside the slot, slot
+// reported done, identical fill counts), and in addition that a launch never pushes ahead into a bank it fills or reads
+// itself and that the last launch pushes nothing ahead.  `flip_bank_at` >= 0 builds that launch with the wrong bank (a
+// self-test: the lint must complain).
+int rtp_lint_linear_chain(int world, int ctas, unsigned long long slot_bytes, int n_launches, const int* spec,
+                          int flip_bank_at, char* report, int cap) {
+  rtp::host_tmap_mode() = true;
+  Lint L;
+  std::vector<RtpRing> rings;
+  fake_rings(rings, world, ctas, slot_bytes);
+  std::vector<LintRect> rects;     // per-launch tile overlap is the business of rtp_lint_linear: not collected here
+  std::vector<std::vector<RtpProgram>> progs(n_launches, std::vector<RtpProgram>(world));
+  auto shard_elems = [&](const int* sp) {
+    const bool col = sp[0] == 0;
+    const long long Os = col ? sp[3] / world : sp[3], Ks = col ? sp[2] : sp[2] / world;
+    return Os * Ks + (sp[4] ? Os : 0);
+  };
+  int rc = 0;
+  for (int k = 0; k < n_launches && rc == 0; ++k) {
+    const int* sp = spec + 7 * k;
+    const int* nx = k + 1 < n_launches ? spec + 7 * (k + 1) : nullptr;
+    const bool col = sp[0] == 0;
+    const long long Os = col ? sp[3] / world : sp[3], Ks = col ? sp[2] : sp[2] / world;
+    const int bank = (k & 1) ^ (k == flip_bank_at ? 1 : 0);
+    for (int r = 0; r < world && rc == 0; ++r) {
+      const void* next_home = nx ? fake_buf(r, 8 + ((k + 1) & 7)) : nullptr;
+      const unsigned long long next_bytes = nx ? (unsigned long long)(shard_elems(nx) * 2 + 15) & ~15ull : 0;
+      bool pair;
+      if (!sp[5]) {
+        RtpLinearFwd op = {};
+        op.mode = sp[0]; op.M = sp[1]; op.in_features = sp[2]; op.out_features = sp[3];
+        op.home = fake_buf(r, 8 + (k & 7)); op.bias_off = sp[4] ? Os * Ks : -1;
+        op.shard_bytes = (unsigned long long)(shard_elems(sp) * 2 + 15) & ~15ull;
+        op.x = fake_buf(r, 1); op.ldx = sp[2]; op.y = fake_buf(r, 2); op.ldy = sp[3];
+        op.bank = bank; op.no_self_push = k > 0;
+        op.next_home = next_home; op.next_bytes = next_bytes; op.next_kind = nx ? nx[5] : 0;
+        decide_pair(op.M, (world > 1 && col) ? sp[3] / world : sp[3], ctas);
+        pair = pair_mode();
+        rc = build_linear_fwd(rings[r], op, progs[k][r]);
+      } else {
+        RtpLinearBwd op = {};
+        op.mode = sp[0]; op.M = sp[1]; op.in_features = sp[2]; op.out_features = sp[3];
+        op.home = fake_buf(r, 8 + (k & 7)); op.bias_off = sp[4] ? Os * Ks : -1;
+        op.shard_bytes = (unsigned long long)(shard_elems(sp) * 2 + 15) & ~15ull;
+        op.x = fake_buf(r, 1); op.ldx = sp[2]; op.dy = fake_buf(r, 2); op.ldy = sp[3];
+        if (sp[6]) { op.dx = fake_buf(r, 3); op.lddx = sp[2]; }
+        op.grad_home = fake_buf(r, 4);
+        if (sp[4]) op.dbias_full = reinterpret_cast<const float*>(fake_buf(r, 5));
+        op.bank = bank; op.no_self_push = k > 0;
+        op.next_home = next_home; op.next_bytes = next_bytes; op.next_kind = nx ? nx[5] : 0;
+        decide_pair(op.M, col ? sp[2] : sp[2] / world, ctas);
+        pair = pair_mode();
+        rc = build_linear_bwd(rings[r], op, progs[k][r]);
+      }
+      if (rc) { L.bad("launch " + lstr(k) + " rank " + lstr(r) + ": builder refused: " + g_err); break; }
+      finalize_program(progs[k][r], ctas, pair);
+    }
+  }
+  auto w_bank = [](int ctr) { return (ctr >= RTP_CTR_W0 && ctr < RTP_CTR_G0) ? (ctr - RTP_CTR_W0) / RTP_NUM_SLOTS : -1; };
+  for (int k = 0; k < n_launches && rc == 0 && world > 1; ++k) {
+    const int bank = k & 1;          // the bank the chain rule gives this launch, whatever it was built with
+    std::vector<RtpProgram> merged(world);
+    const size_t before = L.rep.size();
+    for (int r = 0; r < world; ++r) {
+      const RtpProgram& P = progs[k][r];
+      RtpProgram& Q = merged[r];
+      Q = P;
+      Q.n_pushes = 0;
+      for (int j = 0; j < P.n_pushes; ++j) {
+        const int b = w_bank(P.pushes[j].credit_ctr);
+        if (b == bank || b < 0) Q.pushes[Q.n_pushes++] = P.pushes[j];
+        else {
+          if (k + 1 == n_launches) L.bad("launch " + lstr(k) + " rank " + lstr(r) + ": the last launch pushes ahead");
+          if (P.uses_inc[P.pushes[j].credit_ctr])
+            L.bad("launch " + lstr(k) + " rank " + lstr(r) + " push " + lstr(j) + ": pushes ahead into a slot that the launch fills itself");
+        }
+      }
+      if (k > 0) {
+        const RtpProgram& B = progs[k - 1][r];
+        for (int j = 0; j < B.n_pushes; ++j)
+          if (w_bank(B.pushes[j].credit_ctr) == bank) {
+            if (Q.n_pushes >= RTP_MAX_PUSHES) { L.bad("launch " + lstr(k) + ": too many producers"); break; }
+            Q.pushes[Q.n_pushes++] = B.pushes[j];
+          }
+      }
+      for (int p = 0; p < P.n_phases; ++p)
+        for (int w = 0; w < RTP_MAX_WAITS; ++w) {
+          const int b = w_bank(P.phases[p].wait_ctr[w]);
+          if (b >= 0 && b != bank)
+            L.bad("launch " + lstr(k) + " rank " + lstr(r) + " phase " + lstr(p) + ": reads bank " + lstr(b) + ", the chain gives it bank " + lstr(bank));
+        }
+    }
+    lint_ring(L, rings, merged);
+    if (L.rep.size() > before) L.rep.insert(before, "launch " + lstr(k) + ":\n");
+  }
   rtp::host_tmap_mode() = false;
   return lint_finish(L, rects, report, cap);
 }

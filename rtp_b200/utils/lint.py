@@ -44,6 +44,31 @@ def lint_experts(world: int, n_local: int, cap: int, in_features: int, out_featu
     return n, [ln for ln in buf.value.decode().splitlines() if ln]
 
 
+def lint_chain(world: int, launches, ctas: int = 148, slot_bytes: int = 1 << 30, flip_bank_at: int = -1
+               ) -> Tuple[int, List[str]]:
+    """A chain of rotated linears with cross-launch prefetch, as ``FusedLMTrainer`` issues them (launch k reads
+    weight-slot bank ``k & 1`` and pushes the shards of launch k + 1 into the other bank).  ``launches``: one tuple
+    ``(mode, M, in_features, out_features, bias, backward, need_dx)`` per launch.  ``flip_bank_at`` builds that launch
+    with the wrong bank, to test the lint itself."""
+    f = _lib.lib().rtp_lint_linear_chain
+    f.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int, C.POINTER(C.c_int), C.c_int, C.c_char_p, C.c_int]
+    f.restype = C.c_int
+    flat = [int(v) for l in launches for v in l]
+    assert len(flat) == 7 * len(launches)
+    arr = (C.c_int * len(flat))(*flat)
+    buf = C.create_string_buffer(8192)
+    n = f(world, ctas, slot_bytes, len(launches), arr, flip_bank_at, buf, 8192)
+    return n, [ln for ln in buf.value.decode().splitlines() if ln]
+
+
+def lm_chain(M: int, D: int, H: int, V: int, layers: int):
+    """The chain of a transformer LM step: per layer QKV (column), attention output (row), FFN up and down (column),
+    then the head, and the same linears backwards."""
+    per_layer = [(0, M, D, 3 * D), (1, M, D, D), (0, M, D, H), (0, M, H, D)]
+    fwd = per_layer * layers + [(0, M, D, V)]
+    return [(m, t, i, o, 1, 0, 1) for (m, t, i, o) in fwd] + [(m, t, i, o, 1, 1, 1) for (m, t, i, o) in reversed(fwd)]
+
+
 def sweep(worlds=(1, 2, 3, 4, 5, 6, 7, 8)) -> int:
     """Every rotated linear of the README LM, GPT-1.3B, Llama-13B and the MoE config on every ring size."""
     shapes = []
@@ -67,6 +92,14 @@ def sweep(worlds=(1, 2, 3, 4, 5, 6, 7, 8)) -> int:
                     total += n
                     for ln in lines[:4]:
                         print(f"world {N} experts x{nl} {i}->{o} {'backward' if bwd else 'forward'}: {ln}")
+        if N > 1:
+            for (M, D, H, V, layers) in ((1024, 2048, 2048, 10240, 10), (16384, 2048, 8192, 50304, 2)):
+                if (3 * D) % (8 * N) or H % (8 * N) or V % (8 * N):
+                    continue
+                n, lines = lint_chain(N, lm_chain(M, D, H, V, layers))
+                total += n
+                for ln in lines[:6]:
+                    print(f"world {N} chain D{D} H{H} V{V} x{layers}: {ln}")
     return total
 
 

@@ -34,3 +34,23 @@ def test_the_lint_notices_damage(inject, needle):
 def test_a_shard_that_does_not_fit_its_slot_is_refused():
     n, lines = lint.lint_linear(2, 0, 1024, 2048, 2048, slot_bytes=1 << 16)
     assert n == 1 and "larger than workspace slot" in lines[0]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_prefetch_chain_of_a_training_step_is_clean(world):
+    """The rotated linears of an LM step chained by cross-launch prefetch: every shard a launch waits for is pushed by
+    exactly one launch (itself or its predecessor) into the bank it reads."""
+    for (M, D, H, V, layers) in ((1024, 2048, 2048, 10240, 10), (4096, 1024, 4096, 8192, 2)):
+        n, lines = lint.lint_chain(world, lint.lm_chain(M, D, H, V, layers))
+        assert n == 0, (world, D, lines[:6])
+
+
+def test_the_chain_lint_notices_a_wrong_bank_and_an_unread_prefetch():
+    chain = lint.lm_chain(1024, 2048, 2048, 10240, 2)
+    n, lines = lint.lint_chain(4, chain, flip_bank_at=3)
+    assert n > 0 and any("the chain gives it bank" in ln for ln in lines), lines[:6]
+    # a backward launch that needs no input gradient would never read (and never release) the shards pushed ahead for it
+    last = len(chain) - 1
+    chain[last] = chain[last][:6] + (0,)
+    n, lines = lint.lint_chain(4, chain)
+    assert n > 0 and any("pushed ahead" in ln for ln in lines), lines[:6]
