@@ -205,6 +205,10 @@ int rtp_lint_experts(int world, int ctas, unsigned long long slot_bytes, int n_l
 // the shards of launch k + 1 into the other bank.  `flip_bank_at` >= 0 builds that launch with the wrong bank (self-test).
 int rtp_lint_linear_chain(int world, int ctas, unsigned long long slot_bytes, int n_launches, const int* spec,
                           int flip_bank_at, char* report, int cap);
+// And for the programs without GEMM tiles: kind 0 = rotated embedding lookup (a = V, b = D, c = tokens), 1 = one-hop
+// reduce of `world` blocks (a = elements per block).
+int rtp_lint_transport(int world, int ctas, unsigned long long slot_bytes, int kind, long long a, long long b, long long c,
+                       char* report, int cap);
 int rtp_ws_num_counters(void);
 int rtp_ws_counters(void* ws, unsigned long long* host_out, void* stream);
 void* rtp_ws_wslot(void* ws, unsigned long long slot_bytes, int i, int world);   // logical weight slot i = bank * 8 + index

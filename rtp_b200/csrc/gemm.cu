@@ -1792,4 +1792,41 @@ int rtp_lint_linear_chain(int world, int ctas, unsigned long long slot_bytes, in
   return lint_finish(L, rects, report, cap);
 }
 
+
+// The programs without GEMM tiles: kind 0 = rotated embedding lookup (a = V, b = D, c = tokens), 1 = one-hop reduce of
+// `world` blocks of a elements.  Only the ring rules apply (there are no tiled copies).  The hop-by-hop reduce-scatter
+// (rtp_reduce_scatter_cols) fills the same slot several times per launch, which these one-fill-per-launch rules do not
+// describe: it is not linted.
+int rtp_lint_transport(int world, int ctas, unsigned long long slot_bytes, int kind, long long a, long long b, long long c,
+                       char* report, int cap) {
+  if (kind != 0 && kind != 1) return fail("rtp_lint_transport: kind must be 0 or 1");
+  rtp::host_tmap_mode() = true;
+  Lint L;
+  std::vector<RtpRing> rings;
+  fake_rings(rings, world, ctas, slot_bytes);
+  std::vector<RtpProgram> progs(world);
+  std::vector<LintRect> rects;
+  int rc = 0;
+  for (int r = 0; r < world && rc == 0; ++r) {
+    decide_pair(0, 0, 0, false);
+    if (kind == 0) {
+      RtpEmbedFwd op = {};
+      op.V = (int)a; op.D = (int)b; op.Ds = (int)(b / world); op.T = (int)c;
+      op.home = fake_buf(r, 0); op.shard_bytes = ((unsigned long long)a * (unsigned long long)op.Ds * 2 + 15) & ~15ull;
+      op.ids = reinterpret_cast<const long long*>(fake_buf(r, 1));
+      op.out = fake_buf(r, 2); op.ld_out = b; op.scale = 1.f; op.tokens_per_pos = 1;
+      rc = build_embed_fwd(rings[r], op, progs[r]);
+    } else {
+      RtpReduceBlocks op = {};
+      op.src = fake_buf(r, 0); op.block_elems = a; op.out = fake_buf(r, 2);
+      rc = build_reduce_blocks(rings[r], op, progs[r]);
+    }
+    if (rc) { L.bad("rank " + lstr(r) + ": builder refused: " + g_err); break; }
+    finalize_program(progs[r], ctas, false);
+  }
+  if (rc == 0 && world > 1) lint_ring(L, rings, progs);
+  rtp::host_tmap_mode() = false;
+  return lint_finish(L, rects, report, cap);
+}
+
 }  // extern "C"

@@ -61,6 +61,20 @@ def lint_chain(world: int, launches, ctas: int = 148, slot_bytes: int = 1 << 30,
     return n, [ln for ln in buf.value.decode().splitlines() if ln]
 
 
+def lint_transport(world: int, kind: str, a: int, b: int = 0, c: int = 0, ctas: int = 148, slot_bytes: int = 1 << 30
+                   ) -> Tuple[int, List[str]]:
+    """The programs without GEMM tiles: ``kind`` "embedding" (rotated lookup: a = vocabulary, b = embedding dim, c =
+    tokens) or "reduce" (one-hop reduce of ``world`` blocks of ``a`` elements, the embedding gradient's route)."""
+    f = _lib.lib().rtp_lint_transport
+    f.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_int, C.c_longlong, C.c_longlong, C.c_longlong, C.c_char_p, C.c_int]
+    f.restype = C.c_int
+    buf = C.create_string_buffer(8192)
+    n = f(world, ctas, slot_bytes, {"embedding": 0, "reduce": 1}[kind], a, b, c, buf, 8192)
+    if n < 0:
+        raise ValueError(_lib.lib().rtp_last_error().decode())
+    return n, [ln for ln in buf.value.decode().splitlines() if ln]
+
+
 def lm_chain(M: int, D: int, H: int, V: int, layers: int):
     """The chain of a transformer LM step: per layer QKV (column), attention output (row), FFN up and down (column),
     then the head, and the same linears backwards."""
@@ -92,6 +106,13 @@ def sweep(worlds=(1, 2, 3, 4, 5, 6, 7, 8)) -> int:
                     total += n
                     for ln in lines[:4]:
                         print(f"world {N} experts x{nl} {i}->{o} {'backward' if bwd else 'forward'}: {ln}")
+        for (V, D, T) in ((10240, 2048, 1024), (50304, 2048, 16384), (32000, 5120, 8192)):
+            if D % (8 * N) == 0:
+                for kind, args in (("embedding", (V, D, T)), ("reduce", (V * (D // N),))):
+                    n, lines = lint_transport(N, kind, *args)
+                    total += n
+                    for ln in lines[:4]:
+                        print(f"world {N} {kind} V{V} D{D}: {ln}")
         if N > 1:
             for (M, D, H, V, layers) in ((1024, 2048, 2048, 10240, 10), (16384, 2048, 8192, 50304, 2)):
                 if (3 * D) % (8 * N) or H % (8 * N) or V % (8 * N):

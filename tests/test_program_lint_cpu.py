@@ -54,3 +54,16 @@ def test_the_chain_lint_notices_a_wrong_bank_and_an_unread_prefetch():
     chain[last] = chain[last][:6] + (0,)
     n, lines = lint.lint_chain(4, chain)
     assert n > 0 and any("pushed ahead" in ln for ln in lines), lines[:6]
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_embedding_and_one_hop_reduce_programs_are_clean(world):
+    for (V, D, T) in ((10240, 2048, 1024), (32000, 5120, 8192)):
+        n, lines = lint.lint_transport(world, "embedding", V, D, T)
+        assert n == 0, (world, "embedding", lines[:4])
+        n, lines = lint.lint_transport(world, "reduce", V * (D // world))
+        assert n == 0, (world, "reduce", lines[:4])
+    # a block that does not fit its gradient slot is refused by the builder
+    if world > 1:
+        n, lines = lint.lint_transport(world, "reduce", 1 << 20, slot_bytes=1 << 16)
+        assert n == 1 and "larger than workspace slot" in lines[0]
