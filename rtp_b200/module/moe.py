@@ -14,6 +14,7 @@ from ..parallel.context import get_context
 
 
 _plain_guard_done = False
+_capture_warned = False
 
 
 def _guard_plain_launches(world: int, on_gpu: bool) -> None:
@@ -22,12 +23,20 @@ def _guard_plain_launches(world: int, on_gpu: bool) -> None:
     cause is not known.  Until it is, the first rotating-expert layer that runs on a ring of more than two GPUs turns
     that serialised mode on for the process (``RTP_MOE_PLAIN=1`` opts out).  Launches inside a CUDA-graph capture are
     not covered: serialised mode skips them."""
-    global _plain_guard_done
-    if _plain_guard_done or not on_gpu or world <= 2:
+    global _plain_guard_done, _capture_warned
+    if not on_gpu or world <= 2:
         return
-    _plain_guard_done = True
     import os
     import warnings
+    if (not _capture_warned and torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+            and os.environ.get("RTP_MOE_PLAIN", "0") in ("", "0")):
+        _capture_warned = True
+        warnings.warn("rtp_b200: rotating experts on more than two GPUs are being captured into a CUDA graph; replayed "
+                      "launches are queued back to back, which is the mode in which the open fault was seen",
+                      stacklevel=3)
+    if _plain_guard_done:
+        return
+    _plain_guard_done = True
     from ..parallel.context import get_backend
     if get_backend() == "functional" or os.environ.get("RTP_MOE_PLAIN", "0") not in ("", "0"):
         return
