@@ -4,7 +4,6 @@
 the partials."""
 from typing import Optional, Tuple
 
-import torch
 from torch import Tensor
 
 from .module.attention import SubParallelMultiheadAttention

@@ -5,12 +5,10 @@ Every weight matrix is sharded 1/N and rotated: token embedding ``[V, D/N]`` (em
 reference's ParallelEmbedding), attention = ``ParallelMultiheadAttention`` (head shards), FFN =
 column-rotated ``D -> F`` followed by row-rotated ``F -> D``, head = column-rotated ``D -> V``.
 Activations are ``[batch, seq, dim]``."""
-import math
 from dataclasses import dataclass
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from ..module.attention import ParallelMultiheadAttention
 from ..module.embedding import ParallelEmbedding

@@ -5,12 +5,10 @@ Rotation plan per block: packed QKV projection = column-rotated ``D -> 3D`` whos
 projection of its own batch once the N column blocks are assembled), output projection = row-rotated ``D -> D``;
 SwiGLU = column-rotated packed gate/up ``D -> 2F`` (shard rows ``[gate_r; up_r]``) and row-rotated ``F -> D``.
 Embedding ``[V, D/N]`` and LM head ``[V/N, D]`` rotate as well.  Activations are ``[batch, seq, dim]``."""
-import math
 from dataclasses import dataclass
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from ..module.embedding import ParallelEmbedding
 from ..module.linear import ColumnParallelLinear, RowParallelLinear

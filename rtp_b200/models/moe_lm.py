@@ -5,7 +5,6 @@ from dataclasses import dataclass
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from ..module.attention import ParallelMultiheadAttention
 from ..module.embedding import ParallelEmbedding

@@ -3,7 +3,6 @@ concatenated on dim 1 (reference: rtp/module/conv.py:17-129)."""
 from typing import Optional
 
 import torch
-import torch.nn.functional as F
 from torch import nn
 
 from ..parallel import fused

@@ -1,10 +1,7 @@
 """Classic (Megatron-style) tensor-parallel layers: the TP baseline of the benchmarks
 (reference: rtp/module/layers.py).  Weights are sharded exactly like their rotated counterparts, but
 instead of rotating weights the *activations* are all-gathered / all-reduced."""
-from typing import Optional
 
-import torch
-import torch.nn.functional as F
 from torch import nn
 
 from ..parallel.context import get_context

@@ -8,7 +8,6 @@ import os
 from dataclasses import dataclass
 from typing import Optional
 
-import torch
 import torch.distributed as dist
 
 _BACKEND = os.environ.get("RTP_BACKEND", "auto")  # auto | functional | fused

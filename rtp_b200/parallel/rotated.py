@@ -16,7 +16,7 @@ Differences by design:
   * ``inplace=True`` rotates the single flat buffer itself through a small staging chunk and, in
     no-grad mode, performs the N-th restoring shift.
 """
-from typing import Callable, List, Optional, Sequence, Tuple
+from typing import Callable, List, Sequence, Tuple
 
 import torch
 

@@ -7,7 +7,6 @@ its ``.module`` is the local shard, so state_dict keys are ``<path>.module.weigh
 reference.  Unlike the reference, the rotating attention wrapper is really installed in the parent module,
 and ``inplace=True`` produces correct gradients.
 """
-import copy
 from typing import Any, List, Optional
 
 import torch

@@ -10,7 +10,6 @@ import threading
 import time
 from typing import Optional
 
-import torch.distributed as dist
 
 
 class RankFailure(RuntimeError):
