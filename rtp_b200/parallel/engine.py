@@ -233,14 +233,6 @@ def check_all():
 # --------------------------------------------------------------------------------------------------
 # rotated linear on the fused kernels
 # --------------------------------------------------------------------------------------------------
-def _linear_desc(module, row):
-    lay = module._layout
-    has_bias = module.linear.bias is not None
-    bias_off = lay.offset_of("bias") if has_bias else -1
-    shard_bytes = _round_up(lay.numel * 2, 16)
-    return has_bias, bias_off, shard_bytes
-
-
 def _set_prefetch(op, bank, pushed, next_flat, next_kind):
     """Cross-launch prefetch fields of a linear op: read weight-slot bank ``bank`` (already filled by the previous launch
     if ``pushed``) and push ``next_flat``, the home shard of the next rotated linear on the stream, into the other bank."""
