@@ -181,3 +181,8 @@ def _inplace_displaced_guard(rank, world):
 
 def test_inplace_displaced_guard():
     run_distributed(_inplace_displaced_guard, 2)
+
+
+def test_rotating_experts_with_one_gate_row_per_rank_on_eight_ranks():
+    """The MoE case on a ring of 8: one expert and ONE row of the gate weight per rank (the shape of the 8-GPU runs)."""
+    run_distributed(_moe, 8, False, timeout=300)
